@@ -1,0 +1,130 @@
+"""bf16 GEMM on the tcgen05 kernel (``csrc/gemm_bf16.cu``) and the autograd linear built on it.
+
+``gemm(a, b, a_mn, b_mn, out=..., accumulate=...)`` computes ``D = A . B^T`` where the logical
+operands are A[M,K] and B[N,K]; ``a_mn`` / ``b_mn`` say that the *stored* matrix is the transpose
+([K,M] / [K,N]), which the kernel consumes directly through MN-major shared-memory descriptors.
+
+CPU tensors take a plain PyTorch fp32 path (used by the CPU test-suite and the gloo plumbing
+tests); CUDA tensors always run the native kernel.
+
+Parity: ``pt.ops.gemm`` call sites in primus/backends/megatron/core/extensions/primus_turbo.py:1182-1189
+and the fused main-grad accumulation of primus/backends/megatron/core/tensor_parallel/layers.py:171-181.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_BLOCK_N_OVERRIDE: int | None = None
+
+
+def _pick_block_n(M: int, N: int) -> int:
+    if _BLOCK_N_OVERRIDE:
+        return _BLOCK_N_OVERRIDE
+    if N <= 128:
+        return 128
+    # prefer the tile that wastes fewer SM-waves
+    t256 = -(-M // 128) * -(-N // 256)
+    t128 = -(-M // 128) * -(-N // 128)
+    w256 = -(-t256 // 148) * 2.0  # a 256-wide tile costs twice a 128-wide one
+    w128 = -(-t128 // 148) * 1.08  # 128-wide tiles re-read A more often: small penalty
+    return 256 if w256 <= w128 else 128
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    accumulate: bool = False,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """D[M,N] (+)= A . B^T with fp32 accumulation. See module docstring for layouts."""
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    assert K == Kb, f"K mismatch: {K} vs {Kb}"
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if a.is_cuda else a.dtype
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (M, N)
+        out_dtype = out.dtype
+    if accumulate:
+        assert out_dtype == torch.float32, "accumulate mode writes fp32"
+
+    if not a.is_cuda:
+        A = a.float().t() if a_mn else a.float()
+        B = b.float() if b_mn else b.float().t()
+        r = A @ B
+        if accumulate:
+            out.add_(r)
+        else:
+            out.copy_(r.to(out_dtype))
+        return out
+
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        if not accumulate:
+            out.zero_()
+        return out
+    mode = 0 if out_dtype == torch.bfloat16 else (2 if accumulate else 1)
+    _lib.call(
+        "gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn), int(b_mn), mode, _pick_block_n(M, N), max_ctas, _lib.status_word(a.device),
+    )
+    return out
+
+
+class LinearFn(torch.autograd.Function):
+    """y = x W^T.  Backward: dx = dy W (MN-major B), dW accumulated in fp32 into ``main_grad``
+    when the weight owns one (Megatron ``main_grad`` convention), else returned as a bf16 grad."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        y = gemm(x2, weight)
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = shape
+        ctx.weight_ref = weight
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = wgrad(dy2, x2, ctx.weight_ref)
+        return dx, dw
+
+
+def wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
+    """dW = dy^T x. Accumulates into ``weight.main_grad`` (fp32) if present and returns None;
+    otherwise returns the gradient in the weight's dtype."""
+    main_grad = getattr(weight, "main_grad", None)
+    if main_grad is not None:
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+        weight.grad_added_to_main_grad = True
+        return None
+    if dy2.is_cuda:
+        return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+    return (dy2.float().t() @ x2.float()).to(weight.dtype)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return LinearFn.apply(x, weight)

@@ -1,0 +1,156 @@
+"""Memory-bound kernels (RMSNorm, RoPE, SwiGLU, cross-entropy, AdamW, norms) vs PyTorch fp32 references."""
+import pytest
+import torch
+
+from primus_b200.ops import fused as F
+from primus_b200.ops import optim as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    assert err <= atol + rtol * b.abs().max().item(), f"err {err}"
+
+
+@pytest.mark.parametrize("H", [256, 4096, 2048 + 64])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(H, with_res):
+    T = 300
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    r = torch.randn(T, H, device="cuda").bfloat16().requires_grad_() if with_res else None
+    w = torch.nn.Parameter((1 + 0.1 * torch.randn(H, device="cuda")).bfloat16())
+    out = F.rmsnorm(x, w, 1e-5, r)
+    xr = x.detach().float().requires_grad_()
+    rr = r.detach().float().requires_grad_() if with_res else None
+    wr = w.detach().float().requires_grad_()
+    xs = xr + rr if with_res else xr
+    yr = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    if with_res:
+        y, xsum = out
+        dy, ds = torch.randn_like(y), torch.randn_like(xsum)
+        torch.autograd.backward([y, xsum], [dy, ds])
+        torch.autograd.backward([yr, xs], [dy.float(), ds.float()])
+        _close(xsum, xs)
+        _close(r.grad, rr.grad)
+    else:
+        y = out
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad, rtol=2e-2, atol=0.3)
+
+
+def test_rmsnorm_main_grad_accumulates():
+    T, H = 1000, 1024
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = torch.nn.Parameter(torch.ones(H, device="cuda").bfloat16())
+    w.main_grad = torch.zeros(H, device="cuda")
+    for _ in range(2):
+        F.rmsnorm(x, w, 1e-5).backward(torch.ones(T, H, device="cuda").bfloat16())
+    xr = x.detach().float()
+    ref = 2 * (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5)).sum(0)
+    _close(w.main_grad, ref, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("rot", [128, 64])
+def test_rope(rot):
+    T, h, d = 257, 6, 128
+    cos, sin = F.rope_tables(512, rot, 10000.0, "cuda")
+    x = torch.randn(T, h, d, device="cuda").bfloat16().requires_grad_()
+    pos = torch.randint(0, 512, (T,), device="cuda", dtype=torch.int32)
+    y = F.rope(x, cos, sin, pos, rot)
+    ref = F.rope_ref(x.detach(), cos, sin, pos, rot)
+    _close(y, ref)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gref = F.rope_ref(dy, cos, -sin, pos, rot)
+    _close(x.grad, gref)
+
+
+@pytest.mark.parametrize("probs,clamp", [(False, 0.0), (True, 0.0), (True, 7.0)])
+def test_swiglu(probs, clamp):
+    T, I = 333, 1408
+    x = (3 * torch.randn(T, 2 * I, device="cuda")).bfloat16().requires_grad_()
+    p = torch.rand(T, device="cuda").requires_grad_() if probs else None
+    y = F.swiglu(x, p, clamp)
+    xr = x.detach().float().requires_grad_()
+    pr = p.detach().clone().requires_grad_() if probs else None
+    g, u = xr[:, :I], xr[:, I:]
+    if clamp > 0:
+        g, u = g.clamp(max=clamp), u.clamp(-clamp, clamp)
+    yr = torch.nn.functional.silu(g) * u
+    if probs:
+        yr = yr * pr[:, None]
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    if probs:
+        _close(p.grad, pr.grad, rtol=2e-2, atol=0.5)
+
+
+@pytest.mark.parametrize("V", [32000, 128256])
+def test_cross_entropy(V):
+    T = 64
+    logits = (2 * torch.randn(T, V, device="cuda")).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    lr = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, labels, reduction="none")
+    scale = torch.rand(T, device="cuda")
+    (ref * scale).sum().backward()
+    lg = logits.clone().requires_grad_()
+    loss = F.cross_entropy(lg, labels)
+    (loss * scale).sum().backward()
+    _close(loss, ref, rtol=1e-3, atol=1e-2)
+    assert (lg.grad.float() - lr.grad).abs().max().item() <= 1e-2
+
+
+def test_adamw_and_norms():
+    n = 1_000_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ss = torch.zeros(1, device="cuda")
+    coef = torch.zeros(1, device="cuda")
+    nrm = torch.zeros(1, device="cuda")
+    for step in (1, 2, 3):
+        O.sumsq_(g, ss)
+        O.clip_coef_(ss, 1.0, coef, nrm)
+        ref.grad = g.clone()
+        torch.nn.utils.clip_grad_norm_([ref], 1.0)
+        opt.step()
+        O.adamw_step_(p, m, v, g, pb, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
+                      grad_scale=coef)
+    assert abs(nrm.item() - g.norm().item()) <= 1e-3 * g.norm().item()
+    _close(p, ref.detach(), rtol=1e-4, atol=1e-5)
+    _close(pb, ref.detach(), rtol=1e-2, atol=1e-2)
+    # skip flag leaves state untouched
+    before = p.clone()
+    skip = torch.ones(1, device="cuda", dtype=torch.int32)
+    O.adamw_step_(p, m, v, g, pb, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=4, skip=skip)
+    assert torch.equal(p, before)
+    # bf16 gradients
+    gb = g.bfloat16()
+    O.sumsq_(gb, ss)
+    assert abs(ss.item() - gb.float().pow(2).sum().item()) <= 1e-3 * ss.item()
+
+
+def test_embedding_backward_main_grad():
+    V, H, T = 1000, 256, 4096
+    w = torch.nn.Parameter(torch.randn(V, H, device="cuda").bfloat16())
+    w.main_grad = torch.zeros(V, H, device="cuda")
+    tok = torch.randint(0, V, (T,), device="cuda")
+    y = F.embedding(tok, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref = torch.zeros(V, H, device="cuda").index_add_(0, tok, dy.float())
+    _close(w.main_grad, ref, rtol=1e-3, atol=1e-3)

@@ -1,0 +1,474 @@
+// Flash-attention backward for sm_100a.
+//
+// One templated kernel runs in two modes that share all plumbing:
+//   MODE_DKDV: a CTA owns 128 KV rows of one KV head (resident tiles X1 = K, X2 = V) and streams
+//              64-row tiles of Q / dO (Y1, Y2) of every query head of the group;
+//              S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T  ->  dV += P^T dO,  dK += dS^T Q.
+//   MODE_DQ  : a CTA owns 128 query rows of one head (X1 = Q, X2 = dO) and streams 64-row tiles of
+//              K / V;  S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K.
+// In both modes the accumulators live in tensor memory for the whole loop (no atomics, results are
+// bit-reproducible), the S / dP tiles are double-buffered in TMEM where capacity allows, the
+// streamed tiles are used twice from one shared-memory copy (K-major operand for the first GEMM,
+// MN-major operand for the second), and the 128 softmax threads (one per resident row) turn
+// S / dP into bf16 P / dS tiles in 128B-swizzled shared memory.
+//
+// Replaces the backward of `flash_attn_func` (primus/backends/megatron/core/extensions/
+// primus_turbo.py:812-823); deterministic by construction (cf. the `deterministic=` flag there, :805).
+#include "common.cuh"
+
+namespace {
+
+constexpr int BR = 128;  // resident rows
+constexpr int BC = 64;   // streamed rows per step
+constexpr int BW_THREADS = 192;
+constexpr int XATOM = 128 * 128;  // bytes of a [128 rows x 64 bf16] atom
+constexpr int YATOM = 64 * 128;   // bytes of a [64 rows x 64 bf16] atom
+enum { MODE_DKDV = 0, MODE_DQ = 1 };
+
+template <int DQK, int DV, int MODE>
+struct BwCfg {
+  static constexpr int ACC_COLS = (MODE == MODE_DKDV) ? (DQK + DV) : DQK;
+  static constexpr int SBUF = (ACC_COLS + 256 <= 512) ? 2 : 1;
+  static constexpr int X1_BYTES = BR * DQK * 2;
+  static constexpr int X2_BYTES = BR * DV * 2;
+  static constexpr int Y1_BYTES = BC * DQK * 2;
+  static constexpr int Y2_BYTES = BC * DV * 2;
+  static constexpr int STAT_BYTES = 512;  // 64 lse + 64 delta
+  static constexpr int P_BYTES = BR * BC * 2;
+  static constexpr int SMEM_BYTES =
+      X1_BYTES + X2_BYTES + 2 * (Y1_BYTES + Y2_BYTES) + 2 * P_BYTES + 2 * STAT_BYTES + 1024 + 256;
+};
+
+struct BwBars {
+  uint64_t x_full;
+  uint64_t y_full[2], y_empty[2];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full;
+  uint64_t pds_free;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (pb::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!pb::mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > PB_WAIT_CYCLES) return false;
+  }
+  return true;
+}
+#define BW_WAIT(bar, parity, code)             \
+  if (!bw_wait((bar), (parity), abort_flag)) { \
+    atomicCAS(status, 0, (code));              \
+    bars->abort_flag = 1;                      \
+    ok = false;                                \
+    break;                                     \
+  }
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          pb::smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(pb::smem_u32(bar))
+      : "memory");
+}
+
+template <int DQK, int DV, int MODE>
+__global__ void __launch_bounds__(BW_THREADS, 1)
+flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
+                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
+                      const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
+                      const float* __restrict__ lse, const float* __restrict__ delta, int seq, int hq, int hkv,
+                      float scale, int causal, int* status) {
+  using C = BwCfg<DQK, DV, MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* x1_smem = smem;
+  uint8_t* x2_smem = x1_smem + C::X1_BYTES;
+  uint8_t* y1_smem = x2_smem + C::X2_BYTES;           // 2 stages
+  uint8_t* y2_smem = y1_smem + 2 * C::Y1_BYTES;       // 2 stages
+  uint8_t* p_smem = y2_smem + 2 * C::Y2_BYTES;
+  uint8_t* ds_smem = p_smem + C::P_BYTES;
+  float* stat_smem = reinterpret_cast<float*>(ds_smem + C::P_BYTES);  // 2 stages x (64 lse, 64 delta)
+  BwBars* bars = reinterpret_cast<BwBars*>(reinterpret_cast<uint8_t*>(stat_smem) + 2 * C::STAT_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = hq / hkv;
+  const int num_rb = seq / BR;
+  const int num_c = seq / BC;
+  const int rb = (MODE == MODE_DKDV) ? blockIdx.x : (num_rb - 1 - blockIdx.x);
+  const int xhead = blockIdx.y;  // MODE_DKDV: kv head; MODE_DQ: query head
+  const int batch = blockIdx.z;
+  const int tok0 = batch * seq;
+  // streamed-tile schedule
+  const int c_start = (MODE == MODE_DKDV && causal) ? 2 * rb : 0;
+  const int n_per_head = (MODE == MODE_DKDV) ? (num_c - c_start) : (causal ? 2 * rb + 2 : num_c);
+  const int n_iter = (MODE == MODE_DKDV) ? g * n_per_head : n_per_head;
+  volatile int* abort_flag = &bars->abort_flag;
+  const float sl2 = scale * 1.4426950408889634f;
+
+  if (threadIdx.x == 0) {
+    pb::mbar_init(&bars->x_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      pb::mbar_init(&bars->y_full[i], 1);
+      pb::mbar_init(&bars->y_empty[i], 1);
+      pb::mbar_init(&bars->s_full[i], 1);
+      pb::mbar_init(&bars->s_empty[i], 128);
+    }
+    pb::mbar_init(&bars->p_full, 128);
+    pb::mbar_init(&bars->pds_free, 1);
+    bars->abort_flag = 0;
+    pb::fence_barrier_init();
+  }
+  if (warp == 1) {
+    pb::tmem_alloc<1>(&bars->tmem_base, 512);
+    pb::tmem_relinquish<1>();
+  }
+  pb::tc_fence_before();
+  __syncthreads();
+  pb::tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tmem_sbuf = tmem_base + C::ACC_COLS;  // [buf][S 64 | dP 64]
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      bool ok = true;
+      pb::mbar_expect_tx(&bars->x_full, C::X1_BYTES + C::X2_BYTES);
+#pragma unroll
+      for (int a = 0; a < DQK / 64; ++a)
+        pb::tma_load_3d(x1_smem + a * XATOM, &tmX1, &bars->x_full, a * 64, xhead, tok0 + rb * BR);
+#pragma unroll
+      for (int a = 0; a < DV / 64; ++a)
+        pb::tma_load_3d(x2_smem + a * XATOM, &tmX2, &bars->x_full, a * 64, xhead, tok0 + rb * BR);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int st = i & 1;
+        const int yhead = (MODE == MODE_DKDV) ? (xhead * g + i / n_per_head) : (xhead / g);
+        const int cs = c_start + i % n_per_head;
+        BW_WAIT(&bars->y_empty[st], ((i >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
+        const uint32_t bytes = C::Y1_BYTES + C::Y2_BYTES + (MODE == MODE_DKDV ? C::STAT_BYTES : 0);
+        pb::mbar_expect_tx(&bars->y_full[st], bytes);
+#pragma unroll
+        for (int a = 0; a < DQK / 64; ++a)
+          pb::tma_load_3d(y1_smem + st * C::Y1_BYTES + a * YATOM, &tmY1, &bars->y_full[st], a * 64, yhead,
+                          tok0 + cs * BC);
+#pragma unroll
+        for (int a = 0; a < DV / 64; ++a)
+          pb::tma_load_3d(y2_smem + st * C::Y2_BYTES + a * YATOM, &tmY2, &bars->y_full[st], a * 64, yhead,
+                          tok0 + cs * BC);
+        if (MODE == MODE_DKDV) {
+          const long off = ((long)batch * hq + yhead) * seq + cs * BC;
+          bulk_load_1d(stat_smem + st * 128, lse + off, 256, &bars->y_full[st]);
+          bulk_load_1d(stat_smem + st * 128 + 64, delta + off, 256, &bars->y_full[st]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = pb::make_idesc_bf16(BR, BC, 0, 0);
+      constexpr uint32_t idesc_a1 = pb::make_idesc_bf16(BR, DQK, 0, 1);  // acc(DQK) += dS . Y1
+      constexpr uint32_t idesc_a2 = pb::make_idesc_bf16(BR, DV, 0, 1);   // acc(DV)  += P  . Y2
+      const uint32_t x1a = pb::smem_u32(x1_smem), x2a = pb::smem_u32(x2_smem);
+      const uint32_t pa = pb::smem_u32(p_smem), dsa = pb::smem_u32(ds_smem);
+      bool ok = true;
+      auto issue_sdp = [&](int i) {
+        const int st = i & 1;
+        const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
+        const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
+        const uint32_t ts = tmem_sbuf + (i % C::SBUF) * 128;
+#pragma unroll
+        for (int k = 0; k < DQK / 16; ++k)
+          pb::umma_f16_ss(ts, pb::make_smem_desc(x1a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
+                          pb::make_smem_desc(y1a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
+                          k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < DV / 16; ++k)
+          pb::umma_f16_ss(ts + 64, pb::make_smem_desc(x2a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
+                          pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
+                          k > 0 ? 1u : 0u);
+        pb::umma_commit(&bars->s_full[i % C::SBUF]);
+      };
+      do {
+        BW_WAIT(&bars->x_full, 0, PB_ERR_TIMEOUT_MMA);
+        BW_WAIT(&bars->y_full[0], 0, PB_ERR_TIMEOUT_MMA);
+        pb::tc_fence_after();
+        issue_sdp(0);
+      } while (false);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int st = i & 1;
+        if (C::SBUF == 2 && i + 1 < n_iter) {
+          const int in = i + 1;
+          BW_WAIT(&bars->y_full[in & 1], (in >> 1) & 1, PB_ERR_TIMEOUT_MMA);
+          BW_WAIT(&bars->s_empty[in & 1], ((in >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
+          pb::tc_fence_after();
+          issue_sdp(in);
+        }
+        BW_WAIT(&bars->p_full, i & 1, PB_ERR_TIMEOUT_MMA);
+        pb::tc_fence_after();
+        const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
+        const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
+        if (MODE == MODE_DKDV) {
+#pragma unroll
+          for (int k = 0; k < BC / 16; ++k)
+            pb::umma_f16_ss(tmem_base + DQK, pb::make_smem_desc(pa + k * 32, 0, 1024, 2),
+                            pb::make_smem_desc(y2a + k * 2048, YATOM, 1024, 2), idesc_a2, (i > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BC / 16; ++k)
+          pb::umma_f16_ss(tmem_base, pb::make_smem_desc(dsa + k * 32, 0, 1024, 2),
+                          pb::make_smem_desc(y1a + k * 2048, YATOM, 1024, 2), idesc_a1, (i > 0 || k > 0) ? 1u : 0u);
+        pb::umma_commit(&bars->y_empty[st]);
+        pb::umma_commit(&bars->pds_free);
+        if (C::SBUF == 1 && i + 1 < n_iter) {
+          const int in = i + 1;
+          BW_WAIT(&bars->y_full[in & 1], (in >> 1) & 1, PB_ERR_TIMEOUT_MMA);
+          BW_WAIT(&bars->s_empty[0], (in & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
+          pb::tc_fence_after();
+          issue_sdp(in);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax-gradient threads
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const uint32_t lane_addr = uint32_t(wq * 32) << 16;
+    const int row_g = rb * BR + row;
+    float lse2_row = 0.f, delta_row = 0.f;
+    if (MODE == MODE_DQ) {
+      const long off = ((long)batch * hq + xhead) * seq + row_g;
+      lse2_row = lse[off] * 1.4426950408889634f;
+      delta_row = delta[off];
+    }
+    bool ok = true;
+    for (int i = 0; i < n_iter && ok; ++i) {
+      const int sb = i % C::SBUF;
+      const int st = i & 1;
+      const int cs = c_start + i % n_per_head;
+      BW_WAIT(&bars->s_full[sb], (C::SBUF == 2) ? ((i >> 1) & 1) : (i & 1), PB_ERR_TIMEOUT_EPILOGUE);
+      if (MODE == MODE_DKDV) {
+        BW_WAIT(&bars->y_full[st], (i >> 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // lse / delta tile visible
+      }
+      pb::tc_fence_after();
+      const uint32_t ts = tmem_sbuf + lane_addr + sb * 128;
+      const bool diag = causal && (cs >= 2 * rb) && (cs <= 2 * rb + 1);
+      const float* st_lse = stat_smem + st * 128;
+      const float* st_delta = st_lse + 64;
+      uint32_t pk[2][16], dsk[2][16];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s[32], dp[32];
+        pb::tmem_ld_32x32b_x32(ts + c * 32, s);
+        pb::tmem_ld_32x32b_x32(ts + 64 + c * 32, dp);
+        pb::tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + e + u;
+            const int col_g = cs * BC + col;
+            float l2, dl;
+            if (MODE == MODE_DKDV) {
+              l2 = st_lse[col] * 1.4426950408889634f;
+              dl = st_delta[col];
+            } else {
+              l2 = lse2_row;
+              dl = delta_row;
+            }
+            float p = pb::fast_exp2(fmaf(__uint_as_float(s[e + u]), sl2, -l2));
+            if (diag) {
+              const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
+              if (!valid) p = 0.f;
+            }
+            pv[u] = p;
+            dv[u] = p * (__uint_as_float(dp[e + u]) - dl) * scale;
+          }
+          pk[c][e / 2] = pb::pack_bf16x2(pv[0], pv[1]);
+          dsk[c][e / 2] = pb::pack_bf16x2(dv[0], dv[1]);
+        }
+      }
+      pb::tc_fence_before();
+      pb::mbar_arrive(&bars->s_empty[sb]);
+      if (i > 0) {
+        BW_WAIT(&bars->pds_free, (i - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // previous P / dS consumed
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = c * 4 + q4;
+          const int off = row * 128 + ((chunk ^ (row & 7)) << 4);
+          if (MODE == MODE_DKDV)
+            *reinterpret_cast<uint4*>(p_smem + off) =
+                make_uint4(pk[c][4 * q4], pk[c][4 * q4 + 1], pk[c][4 * q4 + 2], pk[c][4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(ds_smem + off) =
+              make_uint4(dsk[c][4 * q4], dsk[c][4 * q4 + 1], dsk[c][4 * q4 + 2], dsk[c][4 * q4 + 3]);
+        }
+      }
+      pb::fence_proxy_async_smem();
+      pb::mbar_arrive(&bars->p_full);
+    }
+    // ---- epilogue: accumulators -> bf16 -> (dead) resident tiles -> TMA store
+    do {
+      if (!ok) break;
+      BW_WAIT(&bars->pds_free, (n_iter - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      pb::tc_fence_after();
+      auto drain = [&](uint32_t tcol, int ncols, uint8_t* dst) {
+#pragma unroll 1
+        for (int c = 0; c < ncols / 32; ++c) {
+          uint32_t r[32];
+          pb::tmem_ld_32x32b_x32(tmem_base + lane_addr + tcol + c * 32, r);
+          pb::tmem_wait_ld();
+          uint8_t* atom = dst + (c >> 1) * XATOM + row * 128;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = pb::pack_bf16x2(__uint_as_float(r[8 * q4 + 0]), __uint_as_float(r[8 * q4 + 1]));
+            v.y = pb::pack_bf16x2(__uint_as_float(r[8 * q4 + 2]), __uint_as_float(r[8 * q4 + 3]));
+            v.z = pb::pack_bf16x2(__uint_as_float(r[8 * q4 + 4]), __uint_as_float(r[8 * q4 + 5]));
+            v.w = pb::pack_bf16x2(__uint_as_float(r[8 * q4 + 6]), __uint_as_float(r[8 * q4 + 7]));
+            const int chunk = (c & 1) * 4 + q4;
+            *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = v;
+          }
+        }
+      };
+      drain(0, DQK, x1_smem);
+      if (MODE == MODE_DKDV) drain(DQK, DV, x2_smem);
+      pb::fence_proxy_async_smem();
+      pb::named_bar_sync(1, 128);
+      if (threadIdx.x == 64) {
+#pragma unroll
+        for (int a = 0; a < DQK / 64; ++a)
+          pb::tma_store_3d(&tmO1, x1_smem + a * XATOM, a * 64, xhead, tok0 + rb * BR);
+        if (MODE == MODE_DKDV) {
+#pragma unroll
+          for (int a = 0; a < DV / 64; ++a)
+            pb::tma_store_3d(&tmO2, x2_smem + a * XATOM, a * 64, xhead, tok0 + rb * BR);
+        }
+        pb::tma_store_commit();
+        pb::tma_store_wait_all<0>();
+      }
+    } while (false);
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  pb::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    pb::tc_fence_after();
+    pb::tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO * O
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int seq, int hq, int dv, long o_row, long do_row,
+                                  long total_rows) {
+  const long wid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= total_rows * hq) return;
+  const long t = wid / hq;
+  const int h = wid % hq;
+  const __nv_bfloat16* op = o + t * o_row + (long)h * dv;
+  const __nv_bfloat16* dp = d_o + t * do_row + (long)h * dv;
+  float s = 0.f;
+  for (int i = lane * 2; i < dv; i += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + i));
+    s += a.x * b.x + a.y * b.y;
+  }
+  s = pb::warp_sum(s);
+  if (lane == 0) {
+    const long b = t / seq, pos = t % seq;
+    delta[(b * hq + h) * seq + pos] = s;
+  }
+}
+
+struct BwdArgs {
+  const void *d_o, *q, *k, *v, *o;
+  const float* lse;
+  float* delta;
+  void *dq, *dk, *dv;
+  int batch, seq, hq, hkv;
+  long q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row;
+  float scale;
+  int causal;
+  int* status;
+  cudaStream_t stream;
+};
+
+template <int DQK, int DV>
+int launch_bwd(const BwdArgs& a) {
+  const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  const long T = (long)a.batch * a.seq;
+  {
+    const long warps = T * a.hq;
+    const int threads = 256;
+    const long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<(unsigned)blocks, threads, 0, a.stream>>>(
+        (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o, a.delta, a.seq, a.hq, DV, a.o_row, a.do_row, T);
+  }
+  int rc;
+  CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64, dq_m, dk_m, dv_m;
+#define MK(m, p, heads, d, row, br) \
+  if ((rc = pbh::make_tmap_3d(&m, p, bf, 2, T, heads, d, d, row, br, 1, 64, sw))) return rc;
+  MK(q128, a.q, a.hq, DQK, a.q_row, 128) MK(do128, a.d_o, a.hq, DV, a.do_row, 128)
+  MK(k128, a.k, a.hkv, DQK, a.k_row, 128) MK(v128, a.v, a.hkv, DV, a.v_row, 128)
+  MK(q64, a.q, a.hq, DQK, a.q_row, 64) MK(do64, a.d_o, a.hq, DV, a.do_row, 64)
+  MK(k64, a.k, a.hkv, DQK, a.k_row, 64) MK(v64, a.v, a.hkv, DV, a.v_row, 64)
+  MK(dq_m, a.dq, a.hq, DQK, a.dq_row, 128) MK(dk_m, a.dk, a.hkv, DQK, a.dk_row, 128)
+  MK(dv_m, a.dv, a.hkv, DV, a.dv_row, 128)
+#undef MK
+  {
+    using C = BwCfg<DQK, DV, MODE_DKDV>;
+    auto kern = flash_attn_bwd_kernel<DQK, DV, MODE_DKDV>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr_set = true;
+    }
+    dim3 grid(a.seq / BR, a.hkv, a.batch);
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m, a.lse, a.delta, a.seq,
+                                                       a.hq, a.hkv, a.scale, a.causal, a.status);
+  }
+  {
+    using C = BwCfg<DQK, DV, MODE_DQ>;
+    auto kern = flash_attn_bwd_kernel<DQK, DV, MODE_DQ>;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr_set = true;
+    }
+    dim3 grid(a.seq / BR, a.hq, a.batch);
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m, a.lse, a.delta, a.seq,
+                                                       a.hq, a.hkv, a.scale, a.causal, a.status);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Layouts as in pb_flash_attn_fwd. delta: fp32 scratch [batch, hq, seq] (written here).
+extern "C" int pb_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
+                                 int hq, int hkv, int d_qk, int d_v, long q_row, long k_row, long v_row, long o_row,
+                                 long do_row, long dq_row, long dk_row, long dv_row, float scale, int causal,
+                                 int* status, cudaStream_t stream) {
+  if (seq % 128 || hq % hkv) return -2;
+  if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
+  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, hq, hkv, q_row, k_row, v_row, o_row,
+            do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
+  if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
+  if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
+  if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
+  return -3;
+}

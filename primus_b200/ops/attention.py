@@ -1,0 +1,97 @@
+"""Flash attention (causal / full; MHA, GQA, MQA and the MLA head shape d_qk=192, d_v=128) on the
+tcgen05 kernels in ``csrc/flash_attn_{fwd,bwd}.cu``.
+
+Tensors are token-major: q ``[B*S, Hq, Dqk]``, k ``[B*S, Hkv, Dqk]``, v ``[B*S, Hkv, Dv]`` — views into
+a packed QKV projection output are accepted (only the last dim must be contiguous and the head
+stride must equal the head dim).  CPU tensors run a plain fp32 softmax(QK^T)V reference, which is
+also the oracle of the GPU tests.
+
+Parity: `flash_attn_func` use in primus/backends/megatron/core/extensions/primus_turbo.py:812-823,888-990.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+
+def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None):
+    """fp32 reference. Returns (out [T,Hq,Dv], lse [B,Hq,S])."""
+    T, hq, dqk = q.shape
+    hkv, dv = k.shape[1], v.shape[2]
+    S = T // batch
+    scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
+    g = hq // hkv
+    qf = q.float().view(batch, S, hq, dqk).permute(0, 2, 1, 3)
+    kf = k.float().view(batch, S, hkv, dqk).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().view(batch, S, hkv, dv).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).reshape(T, hq, dv)
+    return o.to(q.dtype), lse
+
+
+def _check_view(t, d):
+    assert t.stride(2) == 1 and t.stride(1) == d, "heads must be contiguous [.., H, D] views"
+    assert t.data_ptr() % 16 == 0
+
+
+def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float):
+    T, hq, dqk = q.shape
+    hkv, dv = k.shape[1], v.shape[2]
+    S = T // batch
+    for t, d in ((q, dqk), (k, dqk), (v, dv)):
+        _check_view(t, d)
+    o = torch.empty(T, hq, dv, dtype=q.dtype, device=q.device)
+    lse = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
+    _lib.call("flash_attn_fwd", q, k, v, o, lse, batch, S, hq, hkv, dqk, dv, q.stride(0), k.stride(0),
+              v.stride(0), o.stride(0), float(scale), int(causal), _lib.status_word(q.device))
+    return o, lse
+
+
+def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, dq=None, dk=None, dv=None):
+    """Returns (dq, dk, dv); optional pre-allocated outputs may be strided views (packed dQKV)."""
+    T, hq, dqk = q.shape
+    hkv, dvd = k.shape[1], v.shape[2]
+    S = T // batch
+    dq = torch.empty(T, hq, dqk, dtype=q.dtype, device=q.device) if dq is None else dq
+    dk = torch.empty(T, hkv, dqk, dtype=q.dtype, device=q.device) if dk is None else dk
+    dv = torch.empty(T, hkv, dvd, dtype=q.dtype, device=q.device) if dv is None else dv
+    do = do if (do.stride(2) == 1 and do.stride(1) == dvd) else do.contiguous()
+    for t, d in ((q, dqk), (k, dqk), (v, dvd), (o, dvd), (do, dvd), (dq, dqk), (dk, dqk), (dv, dvd)):
+        _check_view(t, d)
+    delta = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
+    _lib.call("flash_attn_bwd", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, hq, hkv, dqk, dvd,
+              q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0),
+              dv.stride(0), float(scale), int(causal), _lib.status_word(q.device))
+    return dq, dk, dv
+
+
+class FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, batch, causal, scale):
+        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.args = (batch, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        batch, causal, scale = ctx.args
+        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale)
+        return dq, dk, dv, None, None, None
+
+
+def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None):
+    """softmax(scale * Q K^T [+ causal mask]) V, token-major layout (see module docstring)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if not q.is_cuda:
+        return attention_ref(q, k, v, batch, causal, scale)[0]
+    return FlashAttnFn.apply(q, k, v, batch, causal, scale)

@@ -1,0 +1,145 @@
+"""Datasets and batch staging.
+
+``MockGPTDataset`` is the synthetic pre-training dataset (uniform-random token ids from a fixed seed,
+labels = inputs shifted by one) that ``mock_data: true`` selects in the reference
+(primus/backends/megatron/patches/args/mock_data_patches.py:32-45).  ``BatchStager`` keeps batches
+in pinned host memory and copies them to the device on a side stream one step ahead, the role of
+the reference's CUDA prefetch iterator (primus/backends/megatron/data/cuda_prefetch.py:27-84) and
+``DataLoaderStore`` (primus/backends/megatron/data_loader_store.py:97-132).
+"""
+from __future__ import annotations
+
+from typing import Iterator, Optional
+
+import numpy as np
+import torch
+
+
+class MockGPTDataset:
+    """Deterministic random token sequences. Sample ``i`` is a function of (seed, i) only, so every
+    data-parallel rank can draw its own samples without communication and a resumed run sees the
+    same stream."""
+
+    def __init__(self, vocab_size: int, seq_length: int, seed: int = 1234, num_samples: int = 1 << 40):
+        self.vocab_size, self.seq_length, self.seed, self.num_samples = vocab_size, seq_length, seed, num_samples
+
+    def __len__(self):
+        return self.num_samples
+
+    def __getitem__(self, idx: int) -> dict:
+        rng = np.random.Generator(np.random.PCG64([self.seed, idx]))
+        x = rng.integers(0, self.vocab_size, size=self.seq_length + 1, dtype=np.int64)
+        return {"tokens": torch.from_numpy(x[:-1].copy()), "labels": torch.from_numpy(x[1:].copy()),
+                "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
+
+
+class IndexedTokenDataset:
+    """Memory-mapped token file (one flat int32/uint16 array) cut into fixed-length samples.
+    ``path.bin`` holds the ids; an optional ``path.idx.npy`` holds document start offsets."""
+
+    def __init__(self, path: str, seq_length: int, dtype=np.int32):
+        self.data = np.memmap(path, dtype=dtype, mode="r")
+        self.seq_length = seq_length
+        self.num_samples = (len(self.data) - 1) // seq_length
+
+    def __len__(self):
+        return self.num_samples
+
+    def __getitem__(self, idx: int) -> dict:
+        s = idx * self.seq_length
+        x = torch.from_numpy(np.asarray(self.data[s:s + self.seq_length + 1], dtype=np.int64))
+        return {"tokens": x[:-1].clone(), "labels": x[1:].clone(),
+                "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
+
+
+class MicroBatchSampler:
+    """Yields the sample indices of successive micro-batches for one data-parallel rank.
+
+    Global sample order is 0,1,2,...; global batch ``g`` covers ``[g*gbs, (g+1)*gbs)``; inside it, rank
+    ``r`` takes micro-batch ``m`` = samples ``g*gbs + (m*dp + r)*mbs + [0, mbs)`` (Megatron's
+    interleaving).  ``consumed_samples`` makes the stream resumable."""
+
+    def __init__(self, global_batch: int, micro_batch: int, dp_size: int, dp_rank: int, consumed_samples: int = 0):
+        assert global_batch % (micro_batch * dp_size) == 0
+        self.gbs, self.mbs, self.dp, self.rank = global_batch, micro_batch, dp_size, dp_rank
+        self.consumed = consumed_samples
+        self.num_micro = global_batch // (micro_batch * dp_size)
+
+    def next_global_batch(self) -> list[list[int]]:
+        base = self.consumed
+        out = [[base + (m * self.dp + self.rank) * self.mbs + i for i in range(self.mbs)] for m in range(self.num_micro)]
+        self.consumed += self.gbs
+        return out
+
+    def state_dict(self):
+        return {"consumed_samples": self.consumed}
+
+    def load_state_dict(self, sd):
+        self.consumed = sd["consumed_samples"]
+
+
+def collate(samples: list[dict]) -> dict:
+    return {k: torch.stack([s[k] for s in samples]) for k in samples[0]}
+
+
+class BatchStager:
+    """Double-buffered pinned-host -> device staging of micro-batches on a side stream."""
+
+    def __init__(self, dataset, sampler: MicroBatchSampler, device, pin: Optional[bool] = None):
+        self.dataset, self.sampler, self.device = dataset, sampler, torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.pin = self.cuda if pin is None else pin
+        self.stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self._next = None
+        self.h2d_bytes_last_step = 0
+
+    def _load_host(self) -> list[dict]:
+        mbs = []
+        for idxs in self.sampler.next_global_batch():
+            b = collate([self.dataset[i] for i in idxs])
+            if self.pin:
+                b = {k: v.pin_memory() for k, v in b.items()}
+            mbs.append(b)
+        return mbs
+
+    def _to_device(self, host_mbs: list[dict]):
+        if not self.cuda:
+            return host_mbs, None, sum(v.numel() * v.element_size() for b in host_mbs for v in b.values())
+        nbytes = 0
+        with torch.cuda.stream(self.stream):
+            dev = []
+            for b in host_mbs:
+                d = {}
+                for k, v in b.items():
+                    d[k] = v.to(self.device, non_blocking=True)
+                    nbytes += v.numel() * v.element_size()
+                dev.append(d)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        return dev, ev, nbytes
+
+    def prefetch(self):
+        if self._next is None:
+            self._next = self._to_device(self._load_host())
+
+    def next_step(self) -> list[dict]:
+        """Micro-batches of the next global step (device tensors); also starts staging the one after."""
+        self.prefetch()
+        dev, ev, nbytes = self._next
+        self._next = None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            for b in dev:
+                for v in b.values():
+                    v.record_stream(torch.cuda.current_stream())
+        self.h2d_bytes_last_step = nbytes
+        return dev
+
+    def state_dict(self):
+        # a prefetched-but-unconsumed step must be replayed after a resume
+        c = self.sampler.consumed - (self.sampler.gbs if self._next is not None else 0)
+        return {"consumed_samples": c}
+
+    def load_state_dict(self, sd):
+        self._next = None
+        self.sampler.load_state_dict(sd)

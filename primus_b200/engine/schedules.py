@@ -1,0 +1,123 @@
+"""Learning-rate / weight-decay schedules and the micro-batch calculator.
+
+Keys and semantics follow the reference's trainer preset
+(primus/configs/modules/megatron/trainer_base.yaml:72-118): ``lr``, ``min_lr``, ``lr_decay_style``
+(constant | linear | cosine | inverse-square-root | WSD), ``lr_warmup_iters`` / ``lr_warmup_fraction`` /
+``lr_warmup_init``, ``lr_decay_iters``, ``lr_wsd_decay_style`` / ``lr_wsd_decay_iters``,
+``start_weight_decay`` / ``end_weight_decay`` / ``weight_decay_incr_style``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+
+@dataclass
+class LRScheduler:
+    max_lr: float = 3e-4
+    min_lr: float = 0.0
+    warmup_iters: int = 0
+    warmup_init: float = 0.0
+    decay_iters: Optional[int] = None
+    decay_style: str = "cosine"
+    wsd_decay_iters: int = 0
+    wsd_decay_style: str = "exponential"
+    start_wd: float = 0.1
+    end_wd: float = 0.1
+    wd_incr_style: str = "constant"
+    num_iters: int = 0
+
+    def get_lr(self, it: Optional[int] = None) -> float:
+        it = self.num_iters if it is None else it
+        if self.warmup_iters > 0 and it <= self.warmup_iters:
+            return self.warmup_init + (self.max_lr - self.warmup_init) * it / self.warmup_iters
+        if self.decay_style == "constant" or not self.decay_iters:
+            return self.max_lr
+        if it > self.decay_iters:
+            return self.min_lr
+        if self.decay_style == "inverse-square-root":
+            w = max(self.warmup_iters, 1)
+            return max(self.min_lr, self.max_lr * math.sqrt(w) / math.sqrt(max(it, 1)))
+        span = self.decay_iters - self.warmup_iters
+        ratio = (it - self.warmup_iters) / max(span, 1)
+        delta = self.max_lr - self.min_lr
+        if self.decay_style == "linear":
+            coeff = 1.0 - ratio
+        elif self.decay_style == "cosine":
+            coeff = 0.5 * (math.cos(math.pi * ratio) + 1.0)
+        elif self.decay_style == "WSD":
+            anneal_start = self.decay_iters - self.wsd_decay_iters
+            if it <= anneal_start:
+                coeff = 1.0
+            else:
+                r = (it - anneal_start) / max(self.wsd_decay_iters, 1)
+                coeff = {"linear": 1.0 - r, "cosine": 0.5 * (math.cos(math.pi * r) + 1.0),
+                         "exponential": 2.0 * 0.5 ** r - 1.0}[self.wsd_decay_style]
+        else:
+            raise ValueError(f"unknown lr_decay_style {self.decay_style}")
+        return self.min_lr + coeff * delta
+
+    def get_wd(self, it: Optional[int] = None, total: Optional[int] = None) -> float:
+        it = self.num_iters if it is None else it
+        total = total or self.decay_iters or 1
+        if self.wd_incr_style == "constant" or it > total:
+            return self.end_wd
+        r = it / total
+        if self.wd_incr_style == "linear":
+            c = r
+        elif self.wd_incr_style == "cosine":
+            c = 0.5 * (math.cos(math.pi * (1 - r)) + 1.0)
+        else:
+            raise ValueError(self.wd_incr_style)
+        return self.start_wd + c * (self.end_wd - self.start_wd)
+
+    def step(self, n: int = 1):
+        self.num_iters += n
+
+    def state_dict(self):
+        return {"num_iters": self.num_iters}
+
+    def load_state_dict(self, sd):
+        self.num_iters = sd["num_iters"]
+
+
+def num_microbatches(global_batch: int, micro_batch: int, dp: int) -> int:
+    """GA = GBS / (MBS * DP) (primus/backends/megatron/data_loader_store.py:17,26)."""
+    if global_batch % (micro_batch * dp):
+        raise ValueError(f"global batch {global_batch} not divisible by micro batch {micro_batch} x dp {dp}")
+    return global_batch // (micro_batch * dp)
+
+
+def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float:
+    """Model FLOPs per token for one forward+backward pass (3 x forward), Megatron's accounting:
+    2*m*n*k per GEMM, attention scores counted over the full (non-causal) square unless
+    ``causal_half``.  This is the numerator of the ``TFLOP/s/GPU`` figure in the training log
+    (primus/backends/megatron/patches/training_log/print_rank_last_patches.py:435-466)."""
+    h, L, V = cfg.hidden_size, cfg.num_layers, cfg.padded_vocab_size
+    fwd = 0.0
+    for i in range(L):
+        if cfg.multi_latent_attention:
+            qd = cfg.qk_head_dim + cfg.qk_pos_emb_head_dim
+            nh = cfg.num_attention_heads
+            if cfg.q_lora_rank:
+                fwd += 2 * h * cfg.q_lora_rank + 2 * cfg.q_lora_rank * nh * qd
+            else:
+                fwd += 2 * h * nh * qd
+            fwd += 2 * h * (cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
+            fwd += 2 * cfg.kv_lora_rank * nh * (cfg.qk_head_dim + cfg.v_head_dim)
+            fwd += 2 * nh * cfg.v_head_dim * h
+            attn = 2 * seq_len * nh * (qd + cfg.v_head_dim)
+        else:
+            fwd += 2 * h * cfg.qkv_width + 2 * cfg.num_attention_heads * cfg.kv_channels * h
+            attn = 4 * seq_len * cfg.num_attention_heads * cfg.kv_channels
+        fwd += attn * (0.5 if causal_half else 1.0)
+        if cfg.is_moe_layer(i):
+            fwd += 2 * h * cfg.num_experts
+            fwd += cfg.moe_router_topk * 6 * h * cfg.moe_ffn_hidden_size
+            if cfg.moe_shared_expert_intermediate_size:
+                fwd += 6 * h * cfg.moe_shared_expert_intermediate_size
+        else:
+            fwd += 6 * h * cfg.ffn_hidden_size
+    fwd += 2 * h * V
+    return 3.0 * fwd

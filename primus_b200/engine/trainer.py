@@ -1,0 +1,326 @@
+"""The training engine: model + buffers + optimizer + schedule + data, and the per-step loop.
+
+One :class:`Trainer` per process (one process per GPU).  A step is
+
+    zero grads -> forward/backward over the micro-batches (pipeline schedule when PP > 1)
+    -> finalize grads (DP reduce-scatter / all-reduce, SP norm-weight all-reduce, tied-embedding
+       all-reduce) -> clip + AdamW on the local shards -> parameter all-gather -> LR step,
+
+which is the loop the reference delegates to ``megatron.training.pretrain``
+(primus/backends/megatron/megatron_pretrain_trainer.py:254-260; grads finalisation
+primus/backends/megatron/core/distributed/finalize_model_grad.py:23-74).  The log line carries the
+reference's throughput fields — elapsed ms per iteration, TFLOP/s/GPU and tokens/s/GPU with the
+windowed harmonic mean (primus/backends/megatron/patches/training_log/print_rank_last_patches.py:435-548).
+"""
+from __future__ import annotations
+
+import gc
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import TransformerConfig
+from ..models.gpt import build_model
+from ..parallel import state as ps
+from ..parallel.distributed import DistributedOptimizer, ParamGradBuffer
+from . import schedules
+from .data import BatchStager, MicroBatchSampler, MockGPTDataset
+
+
+@dataclass
+class TrainConfig:
+    """Trainer-level options (names follow primus/configs/modules/megatron/trainer_base.yaml)."""
+    micro_batch_size: int = 1
+    global_batch_size: int = 8
+    seq_length: int = 512
+    train_iters: int = 10
+    lr: float = 3e-4
+    min_lr: float = 0.0
+    lr_decay_style: str = "cosine"
+    lr_warmup_iters: int = 0
+    lr_decay_iters: Optional[int] = None
+    weight_decay: float = 0.1
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-8
+    clip_grad: float = 1.0
+    use_distributed_optimizer: bool = True
+    overlap_grad_reduce: bool = False
+    overlap_param_gather: bool = False
+    ddp_bucket_size: Optional[int] = None
+    seed: int = 1234
+    data_seed: int = 1234
+    mock_data: bool = True
+    data_path: Optional[str] = None
+    log_interval: int = 1
+    log_avg_skip_iterations: int = 2
+    log_avg_reset_interval: int = 50
+    check_for_nan_in_loss_and_grad: bool = True
+    calculate_per_token_loss: bool = False
+    save: Optional[str] = None
+    load: Optional[str] = None
+    save_interval: Optional[int] = None
+    exit_interval: Optional[int] = None
+    exit_duration_in_mins: Optional[float] = None
+    eval_interval: Optional[int] = None
+    eval_iters: int = 0
+    pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv
+    manual_gc: bool = True
+    fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
+    profile: bool = False
+    profile_step_start: int = 3
+    profile_step_end: int = 4
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "TrainConfig":
+        import dataclasses
+
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in names})
+
+
+class ThroughputMeter:
+    """tokens/s/GPU = seq * global_batch / elapsed_s / world; running figure = harmonic mean over a
+    window that skips the first iterations and is reset periodically."""
+
+    def __init__(self, skip: int = 2, reset_interval: int = 50):
+        self.skip, self.reset_interval = skip, reset_interval
+        self.seen = 0
+        self.inv_sum = 0.0
+        self.n = 0
+
+    def update(self, tokens_per_s_gpu: float) -> float:
+        self.seen += 1
+        if self.seen <= self.skip:
+            return tokens_per_s_gpu
+        if self.reset_interval and self.n >= self.reset_interval:
+            self.inv_sum, self.n = 0.0, 0
+        self.inv_sum += 1.0 / max(tokens_per_s_gpu, 1e-9)
+        self.n += 1
+        return self.n / self.inv_sum
+
+
+class Trainer:
+    def __init__(self, model_cfg: TransformerConfig, train_cfg: TrainConfig, device: Optional[str] = None,
+                 log_fn: Callable[[str], None] = print):
+        self.mcfg, self.tcfg = model_cfg, train_cfg
+        self.log = log_fn
+        st = ps.get_state()
+        if not st.initialized:
+            st = ps.initialize_model_parallel(
+                tp=model_cfg.tensor_model_parallel_size, pp=model_cfg.pipeline_model_parallel_size,
+                cp=model_cfg.context_parallel_size, ep=model_cfg.expert_model_parallel_size,
+                etp=model_cfg.expert_tensor_parallel_size, virtual_pp=model_cfg.virtual_pipeline_model_parallel_size)
+        self.st = st
+        if device is None:
+            device = f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        self.is_cuda = self.device.type == "cuda"
+        model_cfg.seq_length = train_cfg.seq_length
+        # ---------------------------------------------------------------- model chunks
+        vpp = model_cfg.virtual_pipeline_model_parallel_size if st.pp > 1 else None
+        self.model_chunks = []
+        for v in range(vpp or 1):
+            m = build_model(model_cfg, self.device, st.pp_rank, st.pp, v if vpp else None, vpp, seed=train_cfg.seed)
+            self.model_chunks.append(m)
+        self.model = self.model_chunks[0]
+        # ---------------------------------------------------------------- buffers + optimizer
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        dense, expert = [], []
+        for m in self.model_chunks:
+            for p in m.parameters():
+                (expert if getattr(p, "is_expert", False) else dense).append(p)
+        self.buffers = []
+        if dense:
+            self.buffers.append(ParamGradBuffer(
+                dense, st.dp_cp_group if st.cp > 1 else st.dp_group, st.dp * st.cp, st.dp_rank * st.cp + st.cp_rank,
+                train_cfg.ddp_bucket_size, torch.float32, train_cfg.use_distributed_optimizer,
+                train_cfg.overlap_grad_reduce, True, self.comm_stream))
+        if expert:
+            self.buffers.append(ParamGradBuffer(
+                expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
+                train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream))
+        norm_groups = [st.mp_group] if (st.tp > 1 or st.pp > 1) else []
+        self.optimizer = DistributedOptimizer(
+            self.buffers, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
+            weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
+            check_for_nan=train_cfg.check_for_nan_in_loss_and_grad)
+        self.scheduler = schedules.LRScheduler(
+            max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_iters=train_cfg.lr_warmup_iters,
+            decay_iters=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style,
+            start_wd=train_cfg.weight_decay, end_wd=train_cfg.weight_decay)
+        # ---------------------------------------------------------------- data
+        self.num_microbatches = schedules.num_microbatches(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp)
+        if train_cfg.mock_data or not train_cfg.data_path:
+            ds = MockGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
+        else:
+            from .data import IndexedTokenDataset
+
+            ds = IndexedTokenDataset(train_cfg.data_path, train_cfg.seq_length)
+        self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank)
+        self.stager = BatchStager(ds, self.sampler, self.device)
+        self.iteration = 0
+        self.meter = ThroughputMeter(train_cfg.log_avg_skip_iterations, train_cfg.log_avg_reset_interval)
+        self.flops_per_token = schedules.model_flops_per_token(model_cfg, train_cfg.seq_length)
+        self.loss_accum = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.last_metrics: dict = {}
+        self._gc_disabled = False
+
+    # ------------------------------------------------------------------ one micro-batch
+    def _loss_weights(self, batch: dict) -> torch.Tensor:
+        mask = batch["loss_mask"]
+        if self.tcfg.calculate_per_token_loss:
+            return mask / float(self.num_microbatches)  # normalised later by the global token count
+        denom = mask.sum().clamp(min=1.0)
+        return mask / denom / float(self.num_microbatches)
+
+    def forward_backward_no_pipelining(self, micro_batches: list[dict]) -> torch.Tensor:
+        model = self.model
+        total = self.loss_accum
+        total.zero_()
+        n = len(micro_batches)
+        for i, mb in enumerate(micro_batches):
+            last = i == n - 1
+            for buf in self.buffers:
+                buf.is_last_microbatch = last
+            w = self._loss_weights(mb)
+            loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True)
+            loss.backward()
+            total += loss.detach()
+        return total
+
+    # ------------------------------------------------------------------ grads
+    def finalize_grads(self):
+        st = self.st
+        for m in self.model_chunks:
+            for p in m.parameters():
+                if p.grad is not None:  # gradients that came through plain autograd
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                    p.grad = None
+        for buf in self.buffers:
+            buf.finish_grad_sync()
+        # sequence-parallel: norm weights saw only this rank's token shard
+        if st.tp > 1 and self.mcfg.sequence_parallel:
+            grads = [p.main_grad for m in self.model_chunks for p in m.parameters()
+                     if getattr(p, "sequence_parallel", False)]
+            if grads and not self.tcfg.use_distributed_optimizer:
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=st.tp_group)
+                o = 0
+                for g in grads:
+                    g.copy_(flat[o:o + g.numel()].view_as(g))
+                    o += g.numel()
+
+    def _pre_sync_sp_norm_grads(self):
+        """With the distributed optimizer the norm-weight all-reduce over TP must precede the DP
+        reduce-scatter (afterwards each rank only holds a shard)."""
+        st = self.st
+        if st.tp > 1 and self.mcfg.sequence_parallel and self.tcfg.use_distributed_optimizer:
+            grads = [p.main_grad for m in self.model_chunks for p in m.parameters()
+                     if getattr(p, "sequence_parallel", False)]
+            if grads:
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat, group=st.tp_group)
+                o = 0
+                for g in grads:
+                    g.copy_(flat[o:o + g.numel()].view_as(g))
+                    o += g.numel()
+
+    # ------------------------------------------------------------------ step
+    def train_step(self) -> torch.Tensor:
+        """One optimizer step. Returns the (device) mean loss of this rank's micro-batches."""
+        micro_batches = self.stager.next_step()
+        for buf in self.buffers:
+            buf.zero_grad()
+        if self.st.pp > 1:
+            from ..parallel.pipeline import run_pipeline_schedule
+
+            loss = run_pipeline_schedule(self, micro_batches)
+        else:
+            loss = self.forward_backward_no_pipelining(micro_batches)
+        self.stager.prefetch()  # stage the next step's batch while the optimizer runs
+        self._pre_sync_sp_norm_grads()
+        self.finalize_grads()
+        lr = self.scheduler.get_lr(self.iteration + 1)
+        self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+        self.scheduler.step()
+        self.iteration += 1
+        return loss
+
+    def reduced_loss(self, loss: torch.Tensor) -> float:
+        """Average over data-parallel ranks and fetch to the host (synchronises)."""
+        l = loss.detach().clone()
+        if self.st.dp > 1:
+            dist.all_reduce(l, group=self.st.dp_group)
+            l /= self.st.dp
+        if self.st.pp > 1:
+            dist.broadcast(l, src=self.st.pp_ranks[-1], group=self.st.pp_group)
+        return float(l.item())
+
+    # ------------------------------------------------------------------ loop
+    def train(self, num_iters: Optional[int] = None, on_step: Optional[Callable] = None) -> list[float]:
+        tc = self.tcfg
+        n = num_iters if num_iters is not None else tc.train_iters - self.iteration
+        losses = []
+        if tc.manual_gc and not self._gc_disabled:
+            gc.disable()  # the reference disables Python GC around trainer.train()
+            self._gc_disabled = True
+        start_wall = time.time()
+        try:
+            for _ in range(n):
+                t0 = time.perf_counter()
+                loss = self.train_step()
+                if self.iteration % tc.log_interval == 0 or on_step is not None:
+                    lv = self.reduced_loss(loss)  # synchronises
+                    dt = time.perf_counter() - t0
+                    losses.append(lv)
+                    self._log_step(lv, dt)
+                    if tc.check_for_nan_in_loss_and_grad and not math.isfinite(lv):
+                        raise FloatingPointError(f"non-finite loss at iteration {self.iteration}: {lv}")
+                    if on_step is not None:
+                        on_step(self, lv)
+                if tc.save and tc.save_interval and self.iteration % tc.save_interval == 0:
+                    self.save_checkpoint()
+                if tc.exit_interval and self.iteration % tc.exit_interval == 0:
+                    break
+                if tc.exit_duration_in_mins and (time.time() - start_wall) / 60.0 > tc.exit_duration_in_mins:
+                    break
+        finally:
+            if self._gc_disabled:
+                gc.enable()
+                self._gc_disabled = False
+        return losses
+
+    def _log_step(self, loss: float, dt: float):
+        tc, st = self.tcfg, self.st
+        tokens = tc.seq_length * tc.global_batch_size
+        tps_gpu = tokens / dt / max(st.world_size, 1)
+        avg = self.meter.update(tps_gpu)
+        tflops = tokens * self.flops_per_token / dt / max(st.world_size, 1) / 1e12
+        gn = float(self.optimizer.grad_norm.item())
+        mem = torch.cuda.max_memory_allocated(self.device) / 2**30 if self.is_cuda else 0.0
+        self.last_metrics = dict(iteration=self.iteration, loss=loss, ms=dt * 1e3, tokens_per_s_gpu=tps_gpu,
+                                 tokens_per_s_gpu_avg=avg, tflops_gpu=tflops, grad_norm=gn, mem_gib=mem,
+                                 lr=self.scheduler.get_lr(self.iteration))
+        if st.rank == st.world_size - 1 or st.world_size == 1:
+            self.log(
+                f" iteration {self.iteration:8d}/{tc.train_iters:8d} | elapsed time per iteration (ms): {dt * 1e3:.1f} | "
+                f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
+                f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
+                f"lm loss: {loss:.6E} | grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
+
+    # ------------------------------------------------------------------ checkpoint
+    def save_checkpoint(self, path: Optional[str] = None):
+        from . import checkpoint
+
+        checkpoint.save_checkpoint(self, path or self.tcfg.save)
+
+    def load_checkpoint(self, path: Optional[str] = None) -> int:
+        from . import checkpoint
+
+        return checkpoint.load_checkpoint(self, path or self.tcfg.load)

@@ -1,0 +1,317 @@
+"""Decoder-only GPT family (Llama / Qwen3 / DeepSeek-style) on the primus_b200 ops.
+
+Activations are token-major 2-D tensors ``[tokens, hidden]`` (``tokens = micro_batch * seq`` or its
+sequence-parallel shard).  The residual stream travels between layers as a pair
+``(delta, residual)`` so that the residual add is fused into the next RMSNorm.
+
+Parameter names follow the Megatron-core checkpoint layout that the reference's converters define
+(primus/backends/megatron/checkpoint/native_loader_llama.py:194-239, native_loader_qwen3.py:250-283,
+native_loader_deepseek.py:252-302): ``embedding.word_embeddings.weight``,
+``decoder.layers.{i}.self_attention.linear_qkv.{layer_norm_weight,weight}``,
+``...linear_proj.weight``, ``...mlp.linear_fc1.{layer_norm_weight,weight}``, ``...mlp.linear_fc2.weight``,
+``decoder.final_layernorm.weight``, ``output_layer.weight``.  Internally ``linear_qkv.weight`` rows are
+ordered ``[all q heads | all k heads | all v heads]``; :mod:`primus_b200.engine.checkpoint` converts to
+and from the per-query-group interleaved order of the checkpoint format.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import fused, gemm, layers
+from ..parallel import state as ps
+from ..parallel import tensor_parallel as tpc
+from .config import TransformerConfig
+
+
+def _param(shape, std, dtype, device, is_norm=False, seed_offset=0):
+    if is_norm:
+        p = torch.ones(shape, dtype=dtype, device=device)
+    else:
+        p = torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, std).to(dtype)
+    return nn.Parameter(p)
+
+
+class ParamHolder(nn.Module):
+    """A module that only owns named parameters (keeps checkpoint key paths identical to mcore)."""
+
+    def __init__(self, **params):
+        super().__init__()
+        for k, v in params.items():
+            self.register_parameter(k, v)
+
+
+class SelfAttention(nn.Module):
+    def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
+        super().__init__()
+        self.cfg = cfg
+        dt = cfg.torch_dtype
+        h, d = cfg.hidden_size, cfg.kv_channels
+        assert cfg.num_attention_heads % tp == 0 and cfg.num_query_groups % tp == 0, "heads must divide by TP"
+        self.hq = cfg.num_attention_heads // tp
+        self.hkv = cfg.num_query_groups // tp
+        std = cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        self.linear_qkv = ParamHolder(
+            layer_norm_weight=_param((h,), 0, dt, device, is_norm=True),
+            weight=_param(((self.hq + 2 * self.hkv) * d, h), std, dt, device),
+        )
+        self.linear_proj = ParamHolder(weight=_param((h, self.hq * d), out_std, dt, device))
+        if cfg.qk_layernorm:
+            self.q_layernorm = ParamHolder(weight=_param((d,), 0, dt, device, is_norm=True))
+            self.k_layernorm = ParamHolder(weight=_param((d,), 0, dt, device, is_norm=True))
+        self.linear_qkv.weight.tensor_model_parallel = tp > 1
+        self.linear_qkv.weight.partition_dim = 0
+        self.linear_proj.weight.tensor_model_parallel = tp > 1
+        self.linear_proj.weight.partition_dim = 1
+        self.linear_qkv.layer_norm_weight.sequence_parallel = cfg.sequence_parallel
+
+    def forward(self, hidden, residual, rope, batch):
+        cfg = self.cfg
+        st = ps.get_state()
+        tpg = st.tp_group
+        sp = cfg.sequence_parallel and st.tp > 1
+        qkv, xsum = layers.norm_linear(hidden, residual, self.linear_qkv.layer_norm_weight,
+                                       self.linear_qkv.weight, cfg.norm_epsilon, tpg, sp)
+        d = cfg.kv_channels
+        if cfg.qk_layernorm:
+            qkv = self._qk_norm(qkv, d)
+        cos, sin, pos = rope
+        scale = cfg.attention_softmax_scale
+        ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
+                                        rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
+        out = gemm.linear(ctx_out, self.linear_proj.weight)
+        if sp:
+            out = tpc.reduce_scatter_seq(out, tpg)
+        elif tpg is not None:
+            out = tpc.all_reduce(out, tpg)
+        return out, xsum
+
+    def _qk_norm(self, qkv, d):
+        """Per-head RMSNorm of q and k (Qwen3)."""
+        T = qkv.shape[0]
+        hq, hkv = self.hq, self.hkv
+        q = qkv[:, : hq * d].reshape(T * hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].reshape(T * hkv, d)
+        v = qkv[:, (hq + hkv) * d:]
+        qn = fused.rmsnorm(q, self.q_layernorm.weight, self.cfg.norm_epsilon).reshape(T, hq * d)
+        kn = fused.rmsnorm(k, self.k_layernorm.weight, self.cfg.norm_epsilon).reshape(T, hkv * d)
+        return torch.cat([qn, kn, v], dim=1)
+
+
+class MLP(nn.Module):
+    """Dense SwiGLU MLP: fc1 = [gate; up] stacked on the output dim, fc2 row-parallel."""
+
+    def __init__(self, cfg: TransformerConfig, device, tp: int, ffn: Optional[int] = None, with_norm: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        dt = cfg.torch_dtype
+        h = cfg.hidden_size
+        ffn = ffn or cfg.ffn_hidden_size
+        assert ffn % tp == 0
+        self.ffn_local = ffn // tp
+        std = cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        p = dict(weight=_param((2 * self.ffn_local, h), std, dt, device))
+        if with_norm:
+            p["layer_norm_weight"] = _param((h,), 0, dt, device, is_norm=True)
+        self.linear_fc1 = ParamHolder(**p)
+        self.linear_fc2 = ParamHolder(weight=_param((h, self.ffn_local), out_std, dt, device))
+        self.linear_fc1.weight.tensor_model_parallel = tp > 1
+        self.linear_fc1.weight.partition_dim = 0
+        self.linear_fc2.weight.tensor_model_parallel = tp > 1
+        self.linear_fc2.weight.partition_dim = 1
+        if with_norm:
+            self.linear_fc1.layer_norm_weight.sequence_parallel = cfg.sequence_parallel
+
+    def forward(self, hidden, residual):
+        cfg = self.cfg
+        st = ps.get_state()
+        tpg = st.tp_group
+        sp = cfg.sequence_parallel and st.tp > 1
+        h1, xsum = layers.norm_linear(hidden, residual, self.linear_fc1.layer_norm_weight, self.linear_fc1.weight,
+                                      cfg.norm_epsilon, tpg, sp)
+        out = layers.swiglu_linear(h1, self.linear_fc2.weight, None, cfg.activation_func_clamp_value)
+        if sp:
+            out = tpc.reduce_scatter_seq(out, tpg)
+        elif tpg is not None:
+            out = tpc.all_reduce(out, tpg)
+        return out, xsum
+
+    def forward_normed(self, y):
+        """MLP on an already-normalised input (shared experts / per-expert use). No TP comm."""
+        h1 = gemm.linear(y, self.linear_fc1.weight)
+        return layers.swiglu_linear(h1, self.linear_fc2.weight, None, self.cfg.activation_func_clamp_value)
+
+
+class TransformerLayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        if cfg.multi_latent_attention:
+            from .mla import MLASelfAttention
+
+            self.self_attention = MLASelfAttention(cfg, layer_idx, device, tp)
+        else:
+            self.self_attention = SelfAttention(cfg, layer_idx, device, tp)
+        if cfg.is_moe_layer(layer_idx):
+            from .moe import MoELayer
+
+            self.pre_mlp_layernorm = ParamHolder(weight=_param((cfg.hidden_size,), 0, cfg.torch_dtype, device, True))
+            self.pre_mlp_layernorm.weight.sequence_parallel = cfg.sequence_parallel
+            self.mlp = MoELayer(cfg, layer_idx, device, tp)
+            self.is_moe = True
+        else:
+            self.mlp = MLP(cfg, device, tp)
+            self.is_moe = False
+
+    def forward(self, hidden, residual, rope, batch):
+        attn_out, res1 = self.self_attention(hidden, residual, rope, batch)
+        if self.is_moe:
+            y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon, res1)
+            mlp_out = self.mlp(y)
+        else:
+            mlp_out, res2 = self.mlp(attn_out, res1)
+        return mlp_out, res2
+
+
+class LanguageModelEmbedding(nn.Module):
+    def __init__(self, cfg: TransformerConfig, device, tp: int):
+        super().__init__()
+        V = cfg.padded_vocab_size // tp
+        self.word_embeddings = ParamHolder(weight=_param((V, cfg.hidden_size), cfg.init_method_std, cfg.torch_dtype, device))
+        self.word_embeddings.weight.tensor_model_parallel = tp > 1
+        self.word_embeddings.weight.partition_dim = 0
+        self.vocab_local = V
+
+    def forward(self, tokens_flat):
+        st = ps.get_state()
+        w = self.word_embeddings.weight
+        if st.tp == 1:
+            return fused.embedding(tokens_flat, w)
+        out = fused.embedding(tokens_flat, w, st.tp_rank * self.vocab_local, partial=True)
+        return out  # partial sums; caller reduces (all-reduce or reduce-scatter under SP)
+
+
+class Decoder(nn.Module):
+    def __init__(self, cfg: TransformerConfig, layer_indices, device, tp: int, post_process: bool):
+        super().__init__()
+        self.layers = nn.ModuleDict({str(i): TransformerLayer(cfg, i, device, tp) for i in layer_indices})
+        self.layer_indices = list(layer_indices)
+        if post_process:
+            self.final_layernorm = ParamHolder(weight=_param((cfg.hidden_size,), 0, cfg.torch_dtype, device, True))
+            self.final_layernorm.weight.sequence_parallel = cfg.sequence_parallel
+
+
+class GPTModel(nn.Module):
+    """One pipeline stage (or the whole model when PP=1) of a decoder-only LM.
+
+    ``forward(tokens, labels, loss_weights, hidden_in=None)`` on the last stage returns per-token losses
+    ``[batch, seq]``, or the scalar ``sum(loss_weights * loss)`` when weights are given, or logits when
+    ``labels`` is None; other stages return the ``(delta, residual, batch, seq)`` hand-off."""
+
+    def __init__(self, cfg: TransformerConfig, device="cpu", pre_process: bool = True, post_process: bool = True,
+                 layer_indices: Optional[list[int]] = None):
+        super().__init__()
+        self.cfg = cfg
+        self.pre_process = pre_process
+        self.post_process = post_process
+        tp = ps.get_state().tp
+        if layer_indices is None:
+            layer_indices = list(range(cfg.num_layers))
+        if pre_process:
+            self.embedding = LanguageModelEmbedding(cfg, device, tp)
+        self.decoder = Decoder(cfg, layer_indices, device, tp, post_process)
+        if post_process and cfg.untie_embeddings_and_output_weights:
+            self.output_layer = ParamHolder(
+                weight=_param((cfg.padded_vocab_size // tp, cfg.hidden_size), cfg.init_method_std, cfg.torch_dtype, device))
+            self.output_layer.weight.tensor_model_parallel = tp > 1
+            self.output_layer.weight.partition_dim = 0
+        self._rope_cache = {}
+
+    # ------------------------------------------------------------------ helpers
+    def rope_tables(self, device, seq: int):
+        cfg = self.cfg
+        d = cfg.qk_pos_emb_head_dim if cfg.multi_latent_attention else int(cfg.kv_channels * cfg.rotary_percent)
+        key = (str(device), seq, d)
+        if key not in self._rope_cache:
+            cos, sin = fused.rope_tables(max(seq, 1), d, cfg.rotary_base, device, cfg.rotary_scaling_factor)
+            self._rope_cache[key] = (cos, sin)
+        return self._rope_cache[key]
+
+    def output_weight(self):
+        if self.cfg.untie_embeddings_and_output_weights:
+            return self.output_layer.weight
+        return self.embedding.word_embeddings.weight
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tokens=None, labels=None, loss_weights=None, hidden_in=None, position_ids=None,
+                unit_upstream=False):
+        cfg = self.cfg
+        st = ps.get_state()
+        sp = cfg.sequence_parallel and st.tp > 1
+        if self.pre_process:
+            batch, seq = tokens.shape
+            x = self.embedding(tokens.reshape(-1))
+            if st.tp > 1:
+                x = tpc.reduce_scatter_seq(x, st.tp_group) if sp else tpc.all_reduce(x, st.tp_group)
+            hidden, residual = x, None
+        else:
+            hidden, residual, batch, seq = hidden_in
+        device = hidden.device
+        cos, sin = self.rope_tables(device, seq)
+        pos = None
+        if batch > 1 or position_ids is not None:
+            pos = (position_ids.reshape(-1).to(torch.int32) if position_ids is not None
+                   else torch.arange(seq, device=device, dtype=torch.int32).repeat(batch))
+        rope = (cos, sin, pos)
+        for i in self.decoder.layer_indices:
+            layer = self.decoder.layers[str(i)]
+            hidden, residual = _run_layer(layer, hidden, residual, rope, batch, cfg)
+        if not self.post_process:
+            return hidden, residual, batch, seq
+        w = self.output_weight()
+        if labels is None:
+            y, _ = fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual) \
+                if residual is not None else (fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon), None)
+            if sp:
+                y = tpc.gather_seq(y, st.tp_group)
+            return gemm.linear(y, w)
+        logits, _ = layers.norm_linear(hidden, residual, self.decoder.final_layernorm.weight, w, cfg.norm_epsilon,
+                                       st.tp_group, sp)
+        vocab_local = w.shape[0]
+        loss = fused.cross_entropy(logits, labels.reshape(-1), st.tp_rank * vocab_local,
+                                   st.tp_group if st.tp > 1 else None,
+                                   None if loss_weights is None else loss_weights.reshape(-1), unit_upstream)
+        return loss if loss_weights is not None else loss.view(batch, seq)
+
+
+def _run_layer(layer, hidden, residual, rope, batch, cfg):
+    recompute = cfg.recompute_granularity == "full" and (
+        cfg.recompute_layer_ids is None or layer.layer_idx in cfg.recompute_layer_ids)
+    if recompute and torch.is_grad_enabled():
+        from torch.utils.checkpoint import checkpoint
+
+        if residual is None:
+            return checkpoint(lambda h: layer(h, None, rope, batch), hidden, use_reentrant=False)
+        return checkpoint(lambda h, r: layer(h, r, rope, batch), hidden, residual, use_reentrant=False)
+    return layer(hidden, residual, rope, batch)
+
+
+def build_model(cfg: TransformerConfig, device="cpu", pp_rank: int = 0, pp_size: int = 1,
+                vp_stage: Optional[int] = None, vp_size: Optional[int] = None, seed: Optional[int] = None) -> GPTModel:
+    """Build the model chunk owned by (pp_rank, vp_stage) with an even layer split."""
+    from ..parallel.pipeline_layout import layers_for_stage
+
+    idx = layers_for_stage(cfg.num_layers, pp_size, pp_rank, vp_size, vp_stage)
+    n_virtual = pp_size * (vp_size or 1)
+    stage_id = (vp_stage or 0) * pp_size + pp_rank
+    if seed is not None:
+        st = ps.get_state()
+        torch.manual_seed(seed + 100 * stage_id + 2718 * st.tp_rank)
+    return GPTModel(cfg, device, pre_process=(stage_id == 0), post_process=(stage_id == n_virtual - 1),
+                    layer_indices=idx)

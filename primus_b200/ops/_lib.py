@@ -72,10 +72,17 @@ def stream_ptr() -> ctypes.c_void_p:
     return _PTR(torch.cuda.current_stream().cuda_stream)
 
 
+# Number of device kernels each launcher enqueues (default 1); used for the launch counter below.
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "sumsq": 2, "flash_attn_bwd": 3}
+LAUNCH_COUNT = 0
+
+
 def call(name: str, *args) -> None:
     """Invoke ``pb_<name>`` with converted arguments; the current CUDA stream is appended."""
+    global LAUNCH_COUNT
     fn = getattr(load(), "pb_" + name)
     fn.restype = ctypes.c_int
+    LAUNCH_COUNT += _KERNELS_PER_CALL.get(name, 1)
     rc = fn(*[_conv(a) for a in args], stream_ptr())
     if rc != 0:
         raise NativeLibraryError(f"pb_{name} failed with code {rc}")

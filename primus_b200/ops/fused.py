@@ -246,18 +246,23 @@ def cross_entropy_ref(logits, labels, vocab_start=0, group=None):
 class CrossEntropyFn(torch.autograd.Function):
     """loss[t] = logsumexp(logits[t]) - logits[t, label[t]].  The gradient w.r.t. the logits is
     computed in the forward pass and stored *in place of the logits* (which are dead afterwards),
-    so no [T, V] buffer outlives the call besides the bf16 logits themselves."""
+    so no [T, V] buffer outlives the call besides the bf16 logits themselves.
+
+    With ``weights`` the result is the scalar ``sum_t weights[t] * loss[t]`` and the stored gradient is
+    already multiplied by ``weights[t]``; ``unit_upstream`` promises that the caller back-propagates a
+    gradient of exactly 1 into that scalar, which removes the only remaining pass over the logits."""
 
     @staticmethod
-    def forward(ctx, logits, labels, vocab_start, group):
+    def forward(ctx, logits, labels, vocab_start, group, weights, unit_upstream):
         V = logits.shape[-1]
         l2 = logits.reshape(-1, V)
         rows = l2.shape[0]
         lab = labels.reshape(-1).contiguous()
-        ones = torch.ones(rows, dtype=torch.float32, device=logits.device)
+        gsc = (weights.reshape(-1).float().contiguous() if weights is not None
+               else torch.ones(rows, dtype=torch.float32, device=logits.device))
         loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
         if group is None or dist.get_world_size(group) == 1:
-            _lib.call("ce_fused", l2, lab, ones, loss, rows, V, l2.stride(0))
+            _lib.call("ce_fused", l2, lab, gsc, loss, rows, V, l2.stride(0))
         else:
             st = torch.empty(3, rows, dtype=torch.float32, device=logits.device)
             _lib.call("ce_stats", l2, lab, st[0], st[1], st[2], rows, V, l2.stride(0), int(vocab_start))
@@ -267,24 +272,34 @@ class CrossEntropyFn(torch.autograd.Function):
             dist.all_reduce(st[1:], group=group)
             lse = gmax + st[1].log()
             loss = lse - st[2]
-            _lib.call("ce_grad", l2, lab, lse.contiguous(), ones, rows, V, l2.stride(0), int(vocab_start))
+            _lib.call("ce_grad", l2, lab, lse.contiguous(), gsc, rows, V, l2.stride(0), int(vocab_start))
         ctx.save_for_backward(l2)
         ctx.shape = logits.shape
+        ctx.unit = bool(unit_upstream and weights is not None)
+        ctx.weighted = weights is not None
         ctx.mark_non_differentiable(labels)
+        if weights is not None:
+            return (loss * gsc).sum()
         return loss.view(labels.shape)
 
     @staticmethod
     def backward(ctx, dloss):
         (g,) = ctx.saved_tensors
-        g.mul_(dloss.reshape(-1, 1).to(g.dtype))
-        return g.view(ctx.shape), None, None, None
+        if not ctx.unit:
+            if ctx.weighted:
+                g.mul_(dloss.to(g.dtype))
+            else:
+                g.mul_(dloss.reshape(-1, 1).to(g.dtype))
+        return g.view(ctx.shape), None, None, None, None, None
 
 
-def cross_entropy(logits, labels, vocab_start=0, group=None):
-    """Per-token loss (fp32), same shape as ``labels``. Consumes (overwrites) ``logits`` on CUDA."""
+def cross_entropy(logits, labels, vocab_start=0, group=None, weights=None, unit_upstream=False):
+    """Per-token loss (fp32, shape of ``labels``), or ``sum(weights * loss)`` when ``weights`` is given.
+    Consumes (overwrites) ``logits`` on CUDA."""
     if not logits.is_cuda:
-        return cross_entropy_ref(logits, labels, vocab_start, group if _dist_group_active(group) else None)
-    return CrossEntropyFn.apply(logits, labels, vocab_start, group)
+        loss = cross_entropy_ref(logits, labels, vocab_start, group if _dist_group_active(group) else None)
+        return (loss * weights.reshape(loss.shape).float()).sum() if weights is not None else loss
+    return CrossEntropyFn.apply(logits, labels, vocab_start, group, weights, unit_upstream)
 
 
 def _dist_group_active(group) -> bool:

@@ -1,0 +1,228 @@
+"""Fused layer-level autograd functions that keep the saved-activation set minimal.
+
+* :func:`norm_linear`  — (residual add +) RMSNorm + GEMM.  Saves only the residual stream and
+  the per-row rstd; the normalised activations are recomputed in backward (one cheap
+  memory-bound pass) instead of being stored.  Mirrors the role of
+  ``TELayerNormColumnParallelLinear`` / ``PrimusTurboLayerNormColumnParallelLinear``
+  (primus/backends/megatron/core/extensions/primus_turbo.py:1689-1830) and of the fused
+  residual+norm forward (fused_residual_rmsnorm.py:327-453).
+* :func:`swiglu_linear` — SwiGLU (optionally weighted by routing probs) + GEMM; saves the FC1
+  output only and recomputes the activation in backward.
+* :func:`rope_attention` — RoPE applied in place on the packed QKV projection followed by flash
+  attention; backward applies the inverse rotation in place on the packed dQKV.
+
+Each function has a CPU composition of the reference ops with ordinary autograd.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..parallel import tensor_parallel as tp_comm
+from . import _lib, attention, fused, gemm
+
+
+# ----------------------------------------------------------------------------------------------
+class NormLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, residual, norm_w, weight, eps, tp_group, sp):
+        H = hidden.shape[-1]
+        x2 = hidden.reshape(-1, H)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=hidden.device)
+        if residual is not None:
+            r2 = residual.reshape(-1, H)
+            xsum = torch.empty_like(x2)
+            _lib.call("rmsnorm_fwd", x2, r2, norm_w, y, xsum, rstd, rows, H, x2.stride(0), y.stride(0), float(eps))
+        else:
+            xsum = x2
+            _lib.call("rmsnorm_fwd", x2, None, norm_w, y, None, rstd, rows, H, x2.stride(0), y.stride(0), float(eps))
+        if sp:
+            y = tp_comm.all_gather_dim0(y, tp_group)
+        out = gemm.gemm(y, weight)
+        ctx.save_for_backward(xsum, norm_w, weight, rstd)
+        ctx.eps = eps
+        ctx.tp = (tp_group, sp)
+        ctx.set_materialize_grads(False)
+        ctx.has_res = residual is not None
+        ctx.shape = hidden.shape
+        ctx.refs = (norm_w, weight)
+        if residual is not None:
+            return out, xsum.view(hidden.shape)
+        return out, hidden
+
+    @staticmethod
+    def backward(ctx, dout, dxsum):
+        xsum, norm_w, weight, rstd = ctx.saved_tensors
+        norm_w_ref, weight_ref = ctx.refs
+        if dout is None:
+            dout = torch.zeros(xsum.shape[0] * (torch.distributed.get_world_size(ctx.tp[0]) if ctx.tp[1] else 1),
+                               weight.shape[0], dtype=xsum.dtype, device=xsum.device)
+        rows, H = xsum.shape
+        tp_group, sp = ctx.tp
+        dout2 = dout.reshape(-1, dout.shape[-1])
+        if not dout2.is_contiguous():
+            dout2 = dout2.contiguous()
+        # recompute the normalised activations (not stored in forward)
+        y = torch.empty_like(xsum)
+        _lib.call("rmsnorm_fwd", xsum, None, norm_w, y, None, None, rows, H, xsum.stride(0), y.stride(0),
+                  float(ctx.eps))
+        if sp:
+            y = tp_comm.all_gather_dim0(y, tp_group)
+        dw = gemm.wgrad(dout2, y, weight_ref)
+        dy = gemm.gemm(dout2, weight, b_mn=True)
+        del y
+        if sp:
+            dy = tp_comm.reduce_scatter_dim0(dy, tp_group)
+        elif tp_group is not None:
+            torch.distributed.all_reduce(dy, group=tp_group)
+        dres = None
+        if dxsum is not None:
+            dres = dxsum.reshape(rows, H)
+            if not dres.is_contiguous():
+                dres = dres.contiguous()
+        dx = torch.empty_like(xsum)
+        P = _lib.call_ret("rmsnorm_bwd_num_partials", rows)
+        sc = fused.scratch(xsum.device, "rmsnorm_dw", P * H)
+        main_grad = getattr(norm_w_ref, "main_grad", None)
+        if main_grad is not None:
+            _lib.call("rmsnorm_bwd", dy, xsum, norm_w, rstd, dres, dx, main_grad, sc, rows, H, xsum.stride(0),
+                      dy.stride(0), 1)
+            dnw = None
+        else:
+            dwf = torch.empty(H, dtype=torch.float32, device=xsum.device)
+            _lib.call("rmsnorm_bwd", dy, xsum, norm_w, rstd, dres, dx, dwf, sc, rows, H, xsum.stride(0),
+                      dy.stride(0), 0)
+            dnw = dwf.to(norm_w.dtype)
+        dx = dx.view(ctx.shape)
+        return dx, (dx if ctx.has_res else None), dnw, dw, None, None, None
+
+
+def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_parallel=False):
+    """Returns (linear(rmsnorm(hidden + residual)), hidden + residual).
+
+    ``weight`` may be a column-parallel shard: with ``sequence_parallel`` the normalised local token
+    shard is all-gathered over ``tp_group`` before the GEMM (reduce-scatter of the input gradient in
+    backward); without it the input gradient is all-reduced."""
+    sp = bool(sequence_parallel and tp_group is not None)
+    if not hidden.is_cuda:
+        if residual is not None:
+            y, xsum = fused.rmsnorm_ref(hidden, norm_w, eps, residual)
+        else:
+            y, xsum = fused.rmsnorm_ref(hidden, norm_w, eps, None), hidden
+        if sp:
+            y = tp_comm.gather_seq(y, tp_group)
+        elif tp_group is not None:
+            y = tp_comm.copy_to_tp(y, tp_group)
+        return gemm.linear(y, weight), xsum
+    return NormLinearFn.apply(hidden, residual, norm_w, weight, eps, tp_group, sp)
+
+
+# ----------------------------------------------------------------------------------------------
+class SwiGLULinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h1, weight, probs, clamp):
+        I2 = h1.shape[-1]
+        I = I2 // 2
+        x2 = h1.reshape(-1, I2)
+        T = x2.shape[0]
+        act = torch.empty(T, I, dtype=h1.dtype, device=h1.device)
+        p = probs.reshape(-1).float().contiguous() if probs is not None else None
+        _lib.call("swiglu_fwd", x2, p, act, T, I, float(clamp))
+        out = gemm.gemm(act, weight)
+        ctx.save_for_backward(x2, weight, p if p is not None else torch.empty(0))
+        ctx.has_probs = probs is not None
+        ctx.probs_meta = (probs.shape, probs.dtype) if probs is not None else None
+        ctx.clamp = clamp
+        ctx.shape = h1.shape
+        ctx.weight_ref = weight
+        return out.view(*h1.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, weight, p = ctx.saved_tensors
+        T, I2 = x2.shape
+        I = I2 // 2
+        pp = p if ctx.has_probs else None
+        dout2 = dout.reshape(T, -1)
+        if not dout2.is_contiguous():
+            dout2 = dout2.contiguous()
+        act = torch.empty(T, I, dtype=x2.dtype, device=x2.device)
+        _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp))
+        dw = gemm.wgrad(dout2, act, ctx.weight_ref)
+        dact = gemm.gemm(dout2, weight, b_mn=True, out=act)  # reuse the activation buffer
+        din = torch.empty_like(x2)
+        dprobs = torch.empty(T, dtype=torch.float32, device=x2.device) if ctx.has_probs else None
+        _lib.call("swiglu_bwd", dact, x2, pp, din, dprobs, T, I, float(ctx.clamp))
+        dp = None
+        if ctx.has_probs:
+            shape, dt = ctx.probs_meta
+            dp = dprobs.view(shape).to(dt)
+        return din.view(ctx.shape), dw, dp, None
+
+
+def swiglu_linear(h1, weight, probs=None, clamp=0.0):
+    """linear(swiglu(h1) * probs) with the activation recomputed in backward."""
+    if not h1.is_cuda:
+        return gemm.linear(fused.swiglu_ref(h1, probs, clamp), weight)
+    return SwiGLULinearFn.apply(h1, weight, probs, clamp)
+
+
+# ----------------------------------------------------------------------------------------------
+class RopeAttentionFn(torch.autograd.Function):
+    """qkv: packed projection output [T, (Hq + 2 Hkv) * D] laid out [q heads | k heads | v heads].
+    RoPE is applied in place to the q and k slices (the projection output has no other consumer)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale):
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].view(T, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        if cos is not None:
+            # q and k heads are adjacent in the packed layout: one launch covers both
+            qk = qkv[:, : (hq + hkv) * d].view(T, hq + hkv, d)
+            fused.rope_inplace_(qk, cos, sin, pos, rot_dim)
+        o, lse = attention.flash_attn_fwd(q, k, v, batch, causal, scale)
+        ctx.save_for_backward(qkv, o, lse, cos if cos is not None else torch.empty(0),
+                              sin if sin is not None else torch.empty(0), pos if pos is not None else torch.empty(0))
+        ctx.meta = (batch, hq, hkv, d, rot_dim, causal, scale, cos is not None, pos is not None)
+        return o.view(T, hq * d)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, cos, sin, pos = ctx.saved_tensors
+        batch, hq, hkv, d, rot_dim, causal, scale, has_rope, has_pos = ctx.meta
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].view(T, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        dqkv = torch.empty_like(qkv)
+        dq = dqkv[:, : hq * d].view(T, hq, d)
+        dk = dqkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
+        dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        do3 = do.reshape(T, hq, d)
+        attention.flash_attn_bwd(do3, q, k, v, o, lse, batch, causal, scale, dq=dq, dk=dk, dv=dv)
+        if has_rope:
+            dqk = dqkv[:, : (hq + hkv) * d].view(T, hq + hkv, d)
+            fused.rope_inplace_(dqk, cos, sin, pos if has_pos else None, rot_dim, backward=True)
+        return dqkv, None, None, None, None, None, None, None, None, None, None
+
+
+def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=True, scale=None):
+    """Self-attention on a packed QKV tensor; returns [T, Hq*D]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    rot_dim = rot_dim or d
+    if not qkv.is_cuda:
+        T = qkv.shape[0]
+        q = qkv[:, : hq * d].reshape(T, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].reshape(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
+        if cos is not None:
+            q = fused.rope_ref(q, cos, sin, pos, rot_dim)
+            k = fused.rope_ref(k, cos, sin, pos, rot_dim)
+        o = attention.attention_ref(q, k, v, batch, causal, scale)[0]
+        return o.reshape(T, hq * d)
+    return RopeAttentionFn.apply(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale)

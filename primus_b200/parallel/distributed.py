@@ -1,0 +1,289 @@
+"""Data-parallel parameter/gradient buffers and the ZeRO-1 distributed optimizer.
+
+* :class:`ParamGradBuffer` places every parameter of one (dtype, data-parallel group) class in a flat
+  bf16 ``param_data`` buffer and gives each a view into a flat fp32 ``grad_data`` buffer as
+  ``param.main_grad`` — the convention the reference relies on
+  (primus/backends/megatron/core/distributed/finalize_model_grad.py:35-38,71-74,
+  primus/backends/megatron/core/extensions/primus_turbo.py:197-213).  The buffer is cut into buckets;
+  when every parameter of a bucket reported its gradient in the last micro-batch the bucket's
+  reduce-scatter starts on a side stream (``overlap_grad_reduce``).
+* :class:`DistributedOptimizer` keeps fp32 master weights and Adam moments only for this rank's
+  1/dp shard of every bucket, updates them with the fused AdamW kernel (clip coefficient and
+  non-finite skip flag stay on the device: no host sync in a step), writes bf16 parameters back into
+  the shard region and all-gathers the buckets (``overlap_param_gather`` issues them asynchronously
+  on the side stream; the first forward waits per bucket).
+  Reference semantics: primus/configs/modules/megatron/trainer_base.yaml:161-195 and
+  primus/backends/megatron/core/distributed/sdma_param_gather.py:126-243 (param all-gather).
+
+With ``use_distributed_optimizer=False`` gradients are all-reduced and every rank updates all
+parameters (plain DDP).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Iterable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import optim as optim_ops
+
+
+@dataclass
+class Bucket:
+    index: int
+    start: int  # offsets into the flat buffer (elements)
+    end: int
+    params: list = field(default_factory=list)
+    pending: set = field(default_factory=set)
+    rs_handle: Optional[object] = None
+    ag_handle: Optional[object] = None
+    rs_event: Optional[object] = None
+
+
+class ParamGradBuffer:
+    def __init__(self, params: list[torch.nn.Parameter], dp_group, dp_size: int, dp_rank: int,
+                 bucket_size: Optional[int] = None, grad_dtype=torch.float32, use_distributed_optimizer=True,
+                 overlap_grad_reduce=False, average_in_collective=True, comm_stream=None):
+        assert params, "empty parameter list"
+        self.params = params
+        self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
+        self.use_distributed_optimizer = use_distributed_optimizer
+        self.overlap_grad_reduce = overlap_grad_reduce and dp_size > 1
+        self.comm_stream = comm_stream
+        device = params[0].device
+        self.device = device
+        self.param_dtype = params[0].dtype
+        self.grad_dtype = grad_dtype if params[0].dtype != torch.float32 else torch.float32
+        align = 128 * dp_size  # every bucket splits into dp equal, 256-byte aligned shards
+        if bucket_size is None:
+            bucket_size = max(40_000_000, 1_000_000 * dp_size)
+        # parameters are laid out in reverse order so that buckets fill in backward order
+        offsets = {}
+        buckets: list[Bucket] = []
+        cur_start, cur = 0, 0
+        cur_params = []
+        for p in reversed(params):
+            n = p.numel()
+            offsets[p] = cur
+            cur += -(-n // 64) * 64  # keep every parameter 128-byte aligned for TMA
+            cur_params.append(p)
+            if cur - cur_start >= bucket_size:
+                cur = -(-cur // align) * align
+                buckets.append(Bucket(len(buckets), cur_start, cur, cur_params))
+                cur_start, cur_params = cur, []
+        if cur_params:
+            cur = -(-cur // align) * align
+            buckets.append(Bucket(len(buckets), cur_start, cur, cur_params))
+        self.numel = cur
+        self.buckets = buckets
+        self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=device)
+        self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=device)
+        self.param_offsets = offsets
+        self.param_to_bucket = {}
+        for b in buckets:
+            for p in b.params:
+                self.param_to_bucket[p] = b
+        for p in params:
+            o = offsets[p]
+            view = self.param_data[o:o + p.numel()].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.grad_data[o:o + p.numel()].view(p.shape)
+            p.grad_added_to_main_grad = False
+            p._grad_ready_cb = self._on_grad_ready
+        self.is_last_microbatch = True
+        self.grad_scale = 1.0 / dp_size if average_in_collective else 1.0
+        self._rs_out: dict[int, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ shards
+    def shard_range(self, b: Bucket) -> tuple[int, int]:
+        n = (b.end - b.start) // self.dp_size
+        s = b.start + self.dp_rank * n
+        return s, s + n
+
+    def zero_grad(self):
+        self.grad_data.zero_()
+        for b in self.buckets:
+            b.pending = set(b.params)
+            b.rs_handle = None
+            b.rs_event = None
+
+    # ------------------------------------------------------------------ grad sync
+    def _on_grad_ready(self, p):
+        if not (self.overlap_grad_reduce and self.is_last_microbatch):
+            return
+        b = self.param_to_bucket[p]
+        b.pending.discard(p)
+        if not b.pending and b.rs_handle is None:
+            self._start_bucket_sync(b, async_op=True)
+
+    def _start_bucket_sync(self, b: Bucket, async_op: bool):
+        g = self.grad_data[b.start:b.end]
+        stream = self.comm_stream if (async_op and self.comm_stream is not None) else None
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream)
+        else:
+            import contextlib
+
+            ctx = contextlib.nullcontext()
+        with ctx:
+            on_cpu = g.device.type == "cpu"
+            # NCCL averages inside the collective; gloo has no AVG, so pre-scale there
+            op = dist.ReduceOp.SUM if (on_cpu or self.grad_scale == 1.0) else dist.ReduceOp.AVG
+            if on_cpu and self.grad_scale != 1.0:
+                g.mul_(self.grad_scale)
+            if self.use_distributed_optimizer:
+                s, e = self.shard_range(b)
+                out = self.grad_data[s:e]
+                if on_cpu:
+                    dist.all_reduce(g, group=self.dp_group)
+                    b.rs_handle = True
+                else:
+                    b.rs_handle = dist.reduce_scatter_tensor(out, g, op=op, group=self.dp_group,
+                                                             async_op=async_op) or True
+            else:
+                b.rs_handle = dist.all_reduce(g, op=op, group=self.dp_group, async_op=async_op) or True
+            if stream is not None:
+                b.rs_event = torch.cuda.Event()
+                b.rs_event.record(stream)
+
+    def finish_grad_sync(self):
+        """Reduce every bucket that has not been started and wait for all of them."""
+        if self.dp_size == 1:
+            return
+        for b in self.buckets:
+            if b.rs_handle is None:
+                self._start_bucket_sync(b, async_op=False)
+        for b in self.buckets:
+            if b.rs_handle is not True and b.rs_handle is not None and hasattr(b.rs_handle, "wait"):
+                b.rs_handle.wait()
+            if b.rs_event is not None:
+                torch.cuda.current_stream().wait_event(b.rs_event)
+
+    # ------------------------------------------------------------------ param sync
+    def start_param_sync(self, async_op=False):
+        if self.dp_size == 1 or not self.use_distributed_optimizer:
+            return
+        for b in reversed(self.buckets):  # forward order: the embedding-side buckets are needed first
+            s, e = self.shard_range(b)
+            full = self.param_data[b.start:b.end]
+            if full.device.type == "cpu":
+                parts = [torch.empty(e - s, dtype=full.dtype) for _ in range(self.dp_size)]
+                dist.all_gather(parts, self.param_data[s:e].clone(), group=self.dp_group)
+                full.copy_(torch.cat(parts))
+                continue
+            b.ag_handle = dist.all_gather_into_tensor(full, self.param_data[s:e], group=self.dp_group,
+                                                      async_op=async_op)
+
+    def finish_param_sync(self):
+        for b in self.buckets:
+            if b.ag_handle is not None and hasattr(b.ag_handle, "wait"):
+                b.ag_handle.wait()
+            b.ag_handle = None
+
+
+class DistributedOptimizer:
+    """AdamW over the local shards of one or more :class:`ParamGradBuffer`."""
+
+    def __init__(self, buffers: list[ParamGradBuffer], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                 clip_grad=1.0, no_wd_filter=None, norm_groups: Iterable = (), check_for_nan=True):
+        self.buffers = buffers
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.clip_grad = clip_grad
+        self.norm_groups = [g for g in norm_groups if g is not None]
+        self.check_for_nan = check_for_nan
+        self.step_count = 0
+        self.state = []
+        dev = buffers[0].device
+        for buf in buffers:
+            for b in buf.buckets:
+                s, e = (buf.shard_range(b) if buf.use_distributed_optimizer else (b.start, b.end))
+                master = buf.param_data[s:e].float().clone()
+                # weight decay is skipped for 1-D parameters (norm weights, biases): per-element mask ranges
+                wd_ranges = self._wd_ranges(buf, b, s, e, no_wd_filter)
+                self.state.append(dict(buf=buf, bucket=b, s=s, e=e, master=master,
+                                       m=torch.zeros_like(master), v=torch.zeros_like(master), wd_ranges=wd_ranges))
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.skip = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    @staticmethod
+    def _wd_ranges(buf, b, s, e, no_wd_filter):
+        """Sub-ranges of [s, e) with their weight-decay multiplier (1-D params get 0)."""
+        no_wd_filter = no_wd_filter or (lambda p: p.dim() <= 1)
+        ranges = []
+        items = sorted(((buf.param_offsets[p], p) for p in b.params), key=lambda t: t[0])
+        pos = s
+        for o, p in items:
+            lo, hi = max(o, s), min(o + p.numel(), e)
+            if lo >= hi:
+                continue
+            if lo > pos:
+                ranges.append((pos, lo, 0.0))  # alignment padding
+            ranges.append((lo, hi, 0.0 if no_wd_filter(p) else 1.0))
+            pos = hi
+        if pos < e:
+            ranges.append((pos, e, 0.0))
+        # merge neighbours with the same multiplier
+        merged = []
+        for r in ranges:
+            if merged and merged[-1][2] == r[2] and merged[-1][1] == r[0]:
+                merged[-1] = (merged[-1][0], r[1], r[2])
+            else:
+                merged.append(r)
+        return merged
+
+    # ------------------------------------------------------------------
+    def compute_grad_norm(self):
+        """Global L2 norm of the (already reduced) gradients, left on the device."""
+        self.sumsq.zero_()
+        self.skip.zero_()
+        for st in self.state:
+            g = st["buf"].grad_data[st["s"]:st["e"]]
+            optim_ops.sumsq_(g, self.sumsq, accumulate=True)
+        if self.buffers[0].dp_size > 1 and self.buffers[0].use_distributed_optimizer:
+            dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
+        for g in self.norm_groups:
+            dist.all_reduce(self.sumsq, group=g)
+        if self.check_for_nan:
+            self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
+        optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
+        return self.grad_norm
+
+    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None):
+        lr = self.lr if lr is None else lr
+        wd = self.weight_decay if weight_decay is None else weight_decay
+        self.step_count += 1
+        self.compute_grad_norm()
+        for st in self.state:
+            buf = st["buf"]
+            for lo, hi, mult in st["wd_ranges"]:
+                a, b_ = lo - st["s"], hi - st["s"]
+                out = buf.param_data[lo:hi] if buf.param_dtype == torch.bfloat16 else None
+                optim_ops.adamw_step_(st["master"][a:b_], st["m"][a:b_], st["v"][a:b_], buf.grad_data[lo:hi], out,
+                                      lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps,
+                                      weight_decay=wd * mult, step=self.step_count, grad_scale=self.coef,
+                                      skip=self.skip)
+                if out is None:
+                    buf.param_data[lo:hi].copy_(st["master"][a:b_])
+        for buf in self.buffers:
+            buf.start_param_sync(async_op=False)
+            buf.finish_param_sync()
+        return self.grad_norm
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        return {"step": self.step_count,
+                "shards": [dict(master=s["master"], exp_avg=s["m"], exp_avg_sq=s["v"], start=s["s"], end=s["e"])
+                           for s in self.state]}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd["step"]
+        for s, t in zip(self.state, sd["shards"]):
+            s["master"].copy_(t["master"])
+            s["m"].copy_(t["exp_avg"])
+            s["v"].copy_(t["exp_avg_sq"])

@@ -104,6 +104,7 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -126,7 +127,10 @@ def main() -> int:
     _lib.require()
     warmup = max(args.warmup, 3)
 
-    mcfg = TransformerConfig(**MODELS[args.model], params_dtype="bf16", seq_length=args.seq)
+    mdict = dict(MODELS[args.model])
+    if args.layers:
+        mdict["num_layers"] = args.layers
+    mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq)
     gbs = args.batch_per_gpu * world
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,
@@ -197,7 +201,7 @@ def main() -> int:
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": value / (BASELINE_TOK_S_GPU * world) if args.model == "llama3.1_8B" else None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
-            "config": {"model": args.model, "global_batch": gbs, "seq_len": args.seq,
+            "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
                        "micro_batch": args.micro_batch, "parallelism": f"dp{world}",
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},

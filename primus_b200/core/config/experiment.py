@@ -93,8 +93,17 @@ def _resolve_module(name: str, spec: dict) -> ModuleConfig:
         params = mod
     if spec.get("model"):
         model = load_preset(spec["model"], "models", framework)
-        # module and model presets live in disjoint key spaces; parallel sizes may appear in both
-        params = merge_without_override(params, model, excepts=set(params) & set(model) & _SHARED_KEYS)
+        # module and model presets live in (mostly) disjoint key spaces: a key defined in both with two
+        # different non-null values is an error, except the parallelism / precision keys below where the
+        # module preset wins
+        for k in set(params) & set(model):
+            a, b = params[k], model[k]
+            if a is None:
+                params[k] = b
+            elif b is not None and a != b and k not in _SHARED_KEYS:
+                raise KeyError(f"key {k!r} defined with different values in module preset ({a!r}) and "
+                               f"model preset ({b!r})")
+        params = merge_without_override(params, model, excepts=set(params) & set(model))
     ov = spec.get("overrides") or {}
     trainer_class = ov.pop("trainer_class", trainer_class) if isinstance(ov, dict) else trainer_class
     params = deep_merge(params, ov)

@@ -1,0 +1,68 @@
+"""``PretrainTrainer``: the trainer the CLI runs for ``train pretrain``.  It maps the resolved
+experiment parameters onto :class:`TransformerConfig` / :class:`TrainConfig`, initialises the process
+groups and drives :class:`primus_b200.engine.trainer.Trainer`
+(counterpart of primus/backends/megatron/megatron_pretrain_trainer.py:128-291 in the reference)."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..core.utils import logger as logutil
+from ..models.config import TransformerConfig
+from ..parallel import state as ps
+from .base_trainer import BaseTrainer
+from .trainer import TrainConfig, Trainer
+
+COMPLETED_MESSAGE = "Training completed."
+
+
+class PretrainTrainer(BaseTrainer):
+    def setup(self):
+        p = self.params
+        backend = p.get("distributed_backend", "nccl")
+        if not torch.cuda.is_available():
+            backend = "gloo"
+        if self.world_size > 1 or "RANK" in os.environ:
+            ps.init_distributed(backend, float(p.get("distributed_timeout_minutes", 10)))
+        if torch.cuda.is_available():
+            torch.cuda.set_device(self.local_rank)
+
+    def build_configs(self):
+        p = self.params
+        mcfg = TransformerConfig.from_dict(p)
+        tcfg = TrainConfig.from_dict(p)
+        return mcfg, tcfg
+
+    def init(self):
+        mcfg, tcfg = self.build_configs()
+        ps.initialize_model_parallel(
+            tp=mcfg.tensor_model_parallel_size, pp=mcfg.pipeline_model_parallel_size, cp=mcfg.context_parallel_size,
+            ep=mcfg.expert_model_parallel_size, etp=mcfg.expert_tensor_parallel_size or 1,
+            virtual_pp=mcfg.virtual_pipeline_model_parallel_size)
+        self.engine = Trainer(mcfg, tcfg, log_fn=logutil.log_rank_all)
+        if tcfg.load:
+            self.engine.load_checkpoint()
+        logutil.log_rank_0(f"model parameters: {mcfg.num_parameters() / 1e9:.3f} B; "
+                           f"dp={ps.dp_size()} tp={ps.tp_size()} pp={ps.pp_size()} ep={ps.ep_size()}")
+
+    def train(self):
+        def publish(tr, loss):
+            if self.runtime_state is not None:
+                self.runtime_state.update_metrics(**tr.last_metrics)
+
+        self.losses = self.engine.train(on_step=publish)
+        tc = self.engine.tcfg
+        if tc.save and not self.params.get("disable_last_saving", False):
+            self.engine.save_checkpoint()
+        logutil.log_rank_0(COMPLETED_MESSAGE)
+
+    def cleanup(self):
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.barrier()
+            if os.environ.get("PRIMUS_EXIT_FAST") == "1":
+                os._exit(0)
+            dist.destroy_process_group()
+            ps.destroy_model_parallel()

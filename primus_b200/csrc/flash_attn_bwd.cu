@@ -14,13 +14,18 @@
 //
 // Replaces the backward of `flash_attn_func` (primus/backends/megatron/core/extensions/
 // primus_turbo.py:812-823); deterministic by construction (cf. the `deterministic=` flag there, :805).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int BR = 128;  // resident rows
 constexpr int BC = 64;   // streamed rows per step
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 576;   // warp0 TMA, warp1 MMA, warps 2..17: four compute warpgroups
+constexpr int BW_COMPUTE = 512;
+constexpr int BW_WGS = 4;
+constexpr int BW_COLS = BC / BW_WGS;  // streamed-tile columns per compute thread (16)
 constexpr int XATOM = 128 * 128;  // bytes of a [128 rows x 64 bf16] atom
 constexpr int YATOM = 64 * 128;   // bytes of a [64 rows x 64 bf16] atom
 enum { MODE_DKDV = 0, MODE_DQ = 1 };
@@ -35,13 +40,18 @@ struct BwCfg {
   static constexpr int Y2_BYTES = BC * DV * 2;
   static constexpr int STAT_BYTES = 512;  // 64 lse + 64 delta
   static constexpr int P_BYTES = BR * BC * 2;
-  static constexpr int SMEM_BYTES =
-      X1_BYTES + X2_BYTES + 2 * (Y1_BYTES + Y2_BYTES) + 2 * P_BYTES + 2 * STAT_BYTES + 1024 + 256;
+  static constexpr int FIXED_BYTES = X1_BYTES + X2_BYTES + 2 * P_BYTES + 1024 + 512;
+  static constexpr int STAGE_BYTES = Y1_BYTES + Y2_BYTES + STAT_BYTES;
+  static constexpr int NS_FIT = (232448 - FIXED_BYTES) / STAGE_BYTES;
+  // streamed-tile ring depth: a stage is held from the first GEMM (S/dP) to the last (dK/dQ) of its
+  // step, so at least three stages are needed to keep a load in flight behind the running step
+  static constexpr int NS = NS_FIT >= 4 ? 4 : (NS_FIT >= 3 ? 3 : 2);
+  static constexpr int SMEM_BYTES = FIXED_BYTES + NS * STAGE_BYTES;
 };
 
 struct BwBars {
   uint64_t x_full;
-  uint64_t y_full[2], y_empty[2];
+  uint64_t y_full[4], y_empty[4];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full;
   uint64_t pds_free;
@@ -86,12 +96,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* x1_smem = smem;
   uint8_t* x2_smem = x1_smem + C::X1_BYTES;
-  uint8_t* y1_smem = x2_smem + C::X2_BYTES;           // 2 stages
-  uint8_t* y2_smem = y1_smem + 2 * C::Y1_BYTES;       // 2 stages
-  uint8_t* p_smem = y2_smem + 2 * C::Y2_BYTES;
+  uint8_t* y1_smem = x2_smem + C::X2_BYTES;           // NS stages
+  uint8_t* y2_smem = y1_smem + C::NS * C::Y1_BYTES;   // NS stages
+  uint8_t* p_smem = y2_smem + C::NS * C::Y2_BYTES;
   uint8_t* ds_smem = p_smem + C::P_BYTES;
-  float* stat_smem = reinterpret_cast<float*>(ds_smem + C::P_BYTES);  // 2 stages x (64 lse, 64 delta)
-  BwBars* bars = reinterpret_cast<BwBars*>(reinterpret_cast<uint8_t*>(stat_smem) + 2 * C::STAT_BYTES);
+  float* stat_smem = reinterpret_cast<float*>(ds_smem + C::P_BYTES);  // NS stages x (64 lse, 64 delta)
+  BwBars* bars = reinterpret_cast<BwBars*>(reinterpret_cast<uint8_t*>(stat_smem) + C::NS * C::STAT_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -111,13 +121,15 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
 
   if (threadIdx.x == 0) {
     pb::mbar_init(&bars->x_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       pb::mbar_init(&bars->y_full[i], 1);
       pb::mbar_init(&bars->y_empty[i], 1);
-      pb::mbar_init(&bars->s_full[i], 1);
-      pb::mbar_init(&bars->s_empty[i], 128);
     }
-    pb::mbar_init(&bars->p_full, 128);
+    for (int i = 0; i < 2; ++i) {
+      pb::mbar_init(&bars->s_full[i], 1);
+      pb::mbar_init(&bars->s_empty[i], BW_COMPUTE);
+    }
+    pb::mbar_init(&bars->p_full, BW_COMPUTE);
     pb::mbar_init(&bars->pds_free, 1);
     bars->abort_flag = 0;
     pb::fence_barrier_init();
@@ -144,10 +156,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       for (int a = 0; a < DV / 64; ++a)
         pb::tma_load_3d(x2_smem + a * XATOM, &tmX2, &bars->x_full, a * 64, xhead, tok0 + rb * BR);
       for (int i = 0; i < n_iter && ok; ++i) {
-        const int st = i & 1;
+        const int st = i % C::NS;
         const int yhead = (MODE == MODE_DKDV) ? (xhead * g + i / n_per_head) : (xhead / g);
         const int cs = c_start + i % n_per_head;
-        BW_WAIT(&bars->y_empty[st], ((i >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
+        BW_WAIT(&bars->y_empty[st], ((i / C::NS) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
         const uint32_t bytes = C::Y1_BYTES + C::Y2_BYTES + (MODE == MODE_DKDV ? C::STAT_BYTES : 0);
         pb::mbar_expect_tx(&bars->y_full[st], bytes);
 #pragma unroll
@@ -175,7 +187,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       const uint32_t pa = pb::smem_u32(p_smem), dsa = pb::smem_u32(ds_smem);
       bool ok = true;
       auto issue_sdp = [&](int i) {
-        const int st = i & 1;
+        const int st = i % C::NS;
         const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
         const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
         const uint32_t ts = tmem_sbuf + (i % C::SBUF) * 128;
@@ -198,10 +210,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
         issue_sdp(0);
       } while (false);
       for (int i = 0; i < n_iter && ok; ++i) {
-        const int st = i & 1;
+        const int st = i % C::NS;
         if (C::SBUF == 2 && i + 1 < n_iter) {
           const int in = i + 1;
-          BW_WAIT(&bars->y_full[in & 1], (in >> 1) & 1, PB_ERR_TIMEOUT_MMA);
+          BW_WAIT(&bars->y_full[in % C::NS], (in / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
           BW_WAIT(&bars->s_empty[in & 1], ((in >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
           pb::tc_fence_after();
           issue_sdp(in);
@@ -224,7 +236,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
         pb::umma_commit(&bars->pds_free);
         if (C::SBUF == 1 && i + 1 < n_iter) {
           const int in = i + 1;
-          BW_WAIT(&bars->y_full[in & 1], (in >> 1) & 1, PB_ERR_TIMEOUT_MMA);
+          BW_WAIT(&bars->y_full[in % C::NS], (in / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
           BW_WAIT(&bars->s_empty[0], (in & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
           pb::tc_fence_after();
           issue_sdp(in);
@@ -233,63 +245,69 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
     }
   } else {
     // ------------------------------------------------------------------ softmax-gradient threads
-    const int wq = warp & 3;
+    const int wq = warp & 3;              // TMEM lane quarter of this warp
+    const int wg = (warp - 2) >> 2;       // compute warpgroup: owns columns [16*wg, 16*wg+16) of each step
     const int row = wq * 32 + lane;
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     const int row_g = rb * BR + row;
     float lse2_row = 0.f, delta_row = 0.f;
     if (MODE == MODE_DQ) {
       const long off = ((long)batch * hq + xhead) * seq + row_g;
-      lse2_row = lse[off] * 1.4426950408889634f;
+      lse2_row = lse[off];  // already in log2 units
       delta_row = delta[off];
     }
     bool ok = true;
     for (int i = 0; i < n_iter && ok; ++i) {
       const int sb = i % C::SBUF;
-      const int st = i & 1;
+      const int st = i % C::NS;
       const int cs = c_start + i % n_per_head;
       BW_WAIT(&bars->s_full[sb], (C::SBUF == 2) ? ((i >> 1) & 1) : (i & 1), PB_ERR_TIMEOUT_EPILOGUE);
       if (MODE == MODE_DKDV) {
-        BW_WAIT(&bars->y_full[st], (i >> 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // lse / delta tile visible
+        BW_WAIT(&bars->y_full[st], (i / C::NS) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // lse / delta tile visible
       }
       pb::tc_fence_after();
       const uint32_t ts = tmem_sbuf + lane_addr + sb * 128;
       const bool diag = causal && (cs >= 2 * rb) && (cs <= 2 * rb + 1);
       const float* st_lse = stat_smem + st * 128;
       const float* st_delta = st_lse + 64;
-      uint32_t pk[2][16], dsk[2][16];
+      uint32_t pk[BW_COLS / 2], dsk[BW_COLS / 2];
+      {
+        const int c0 = wg * BW_COLS;  // first column of this warpgroup's slice
+        uint32_t s[BW_COLS], dp[BW_COLS];
+        pb::tmem_ld_32x32b_x16(ts + c0, s);
+        pb::tmem_ld_32x32b_x16(ts + 64 + c0, dp);
+        float l2v[BW_COLS], dlv[BW_COLS];
+        if (MODE == MODE_DKDV) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t s[32], dp[32];
-        pb::tmem_ld_32x32b_x32(ts + c * 32, s);
-        pb::tmem_ld_32x32b_x32(ts + 64 + c * 32, dp);
-        pb::tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            const int col_g = cs * BC + col;
-            float l2, dl;
-            if (MODE == MODE_DKDV) {
-              l2 = st_lse[col] * 1.4426950408889634f;
-              dl = st_delta[col];
-            } else {
-              l2 = lse2_row;
-              dl = delta_row;
-            }
-            float p = pb::fast_exp2(fmaf(__uint_as_float(s[e + u]), sl2, -l2));
-            if (diag) {
-              const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
-              if (!valid) p = 0.f;
-            }
-            pv[u] = p;
-            dv[u] = p * (__uint_as_float(dp[e + u]) - dl) * scale;
+          for (int e = 0; e < BW_COLS; e += 4) {
+            *reinterpret_cast<float4*>(l2v + e) = *reinterpret_cast<const float4*>(st_lse + c0 + e);
+            *reinterpret_cast<float4*>(dlv + e) = *reinterpret_cast<const float4*>(st_delta + c0 + e);
           }
-          pk[c][e / 2] = pb::pack_bf16x2(pv[0], pv[1]);
-          dsk[c][e / 2] = pb::pack_bf16x2(dv[0], dv[1]);
         }
+        pb::tmem_wait_ld();
+        auto body = [&](auto diag_tag) {
+          constexpr bool DIAG = decltype(diag_tag)::value;
+#pragma unroll
+          for (int e = 0; e < BW_COLS; e += 2) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const float l2 = (MODE == MODE_DKDV) ? l2v[e + u] : lse2_row;
+              const float dl = (MODE == MODE_DKDV) ? dlv[e + u] : delta_row;
+              float p = pb::fast_exp2(fmaf(__uint_as_float(s[e + u]), sl2, -l2));
+              if (DIAG) {
+                const int col_g = cs * BC + c0 + e + u;
+                const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
+                if (!valid) p = 0.f;
+              }
+              pv[u] = p;
+              dv[u] = p * (__uint_as_float(dp[e + u]) - dl) * scale;
+            }
+            pk[e / 2] = pb::pack_bf16x2(pv[0], pv[1]);
+            dsk[e / 2] = pb::pack_bf16x2(dv[0], dv[1]);
+          }
+        };
+        if (diag) body(std::true_type{}); else body(std::false_type{});
       }
       pb::tc_fence_before();
       pb::mbar_arrive(&bars->s_empty[sb]);
@@ -297,17 +315,13 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
         BW_WAIT(&bars->pds_free, (i - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // previous P / dS consumed
       }
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = c * 4 + q4;
-          const int off = row * 128 + ((chunk ^ (row & 7)) << 4);
-          if (MODE == MODE_DKDV)
-            *reinterpret_cast<uint4*>(p_smem + off) =
-                make_uint4(pk[c][4 * q4], pk[c][4 * q4 + 1], pk[c][4 * q4 + 2], pk[c][4 * q4 + 3]);
-          *reinterpret_cast<uint4*>(ds_smem + off) =
-              make_uint4(dsk[c][4 * q4], dsk[c][4 * q4 + 1], dsk[c][4 * q4 + 2], dsk[c][4 * q4 + 3]);
-        }
+      for (int q2 = 0; q2 < BW_COLS / 8; ++q2) {
+        const int chunk = wg * (BW_COLS / 8) + q2;
+        const int off = row * 128 + ((chunk ^ (row & 7)) << 4);
+        if (MODE == MODE_DKDV)
+          *reinterpret_cast<uint4*>(p_smem + off) = make_uint4(pk[4 * q2], pk[4 * q2 + 1], pk[4 * q2 + 2], pk[4 * q2 + 3]);
+        *reinterpret_cast<uint4*>(ds_smem + off) =
+            make_uint4(dsk[4 * q2], dsk[4 * q2 + 1], dsk[4 * q2 + 2], dsk[4 * q2 + 3]);
       }
       pb::fence_proxy_async_smem();
       pb::mbar_arrive(&bars->p_full);
@@ -319,7 +333,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       pb::tc_fence_after();
       auto drain = [&](uint32_t tcol, int ncols, uint8_t* dst) {
 #pragma unroll 1
-        for (int c = 0; c < ncols / 32; ++c) {
+        for (int c = wg; c < ncols / 32; c += BW_WGS) {
           uint32_t r[32];
           pb::tmem_ld_32x32b_x32(tmem_base + lane_addr + tcol + c * 32, r);
           pb::tmem_wait_ld();
@@ -339,7 +353,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       drain(0, DQK, x1_smem);
       if (MODE == MODE_DKDV) drain(DQK, DV, x2_smem);
       pb::fence_proxy_async_smem();
-      pb::named_bar_sync(1, 128);
+      pb::named_bar_sync(1, BW_COMPUTE);
       if (threadIdx.x == 64) {
 #pragma unroll
         for (int a = 0; a < DQK / 64; ++a)
@@ -366,9 +380,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   }
 }
 
-// delta[b, h, s] = sum_d dO * O
+// delta[b, h, s] = sum_d dO * O ;  lse2 = lse * log2(e) (so the main kernels need no per-element multiply)
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                  float* __restrict__ delta, int seq, int hq, int dv, long o_row, long do_row,
+                                  const float* __restrict__ lse, float* __restrict__ delta,
+                                  float* __restrict__ lse2, int seq, int hq, int dv, long o_row, long do_row,
                                   long total_rows) {
   const long wid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -386,7 +401,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   s = pb::warp_sum(s);
   if (lane == 0) {
     const long b = t / seq, pos = t % seq;
-    delta[(b * hq + h) * seq + pos] = s;
+    const long idx = (b * hq + h) * seq + pos;
+    delta[idx] = s;
+    lse2[idx] = lse[idx] * 1.4426950408889634f;
   }
 }
 
@@ -413,7 +430,8 @@ int launch_bwd(const BwdArgs& a) {
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
     attn_delta_kernel<<<(unsigned)blocks, threads, 0, a.stream>>>(
-        (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o, a.delta, a.seq, a.hq, DV, a.o_row, a.do_row, T);
+        (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o, a.lse, a.delta, a.delta + (long)a.batch * a.hq * a.seq,
+        a.seq, a.hq, DV, a.o_row, a.do_row, T);
   }
   int rc;
   CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64, dq_m, dk_m, dv_m;
@@ -436,7 +454,7 @@ int launch_bwd(const BwdArgs& a) {
       attr_set = true;
     }
     dim3 grid(a.seq / BR, a.hkv, a.batch);
-    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m, a.lse, a.delta, a.seq,
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
                                                        a.hq, a.hkv, a.scale, a.causal, a.status);
   }
   {
@@ -449,7 +467,7 @@ int launch_bwd(const BwdArgs& a) {
       attr_set = true;
     }
     dim3 grid(a.seq / BR, a.hq, a.batch);
-    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m, a.lse, a.delta, a.seq,
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
                                                        a.hq, a.hkv, a.scale, a.causal, a.status);
   }
   return (int)cudaGetLastError();
@@ -457,7 +475,8 @@ int launch_bwd(const BwdArgs& a) {
 
 }  // namespace
 
-// Layouts as in pb_flash_attn_fwd. delta: fp32 scratch [batch, hq, seq] (written here).
+// Layouts as in pb_flash_attn_fwd. delta: fp32 scratch [2, batch, hq, seq] (written here: row sums of dO*O,
+// then the log-sum-exp in log2 units).
 extern "C" int pb_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                                  const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
                                  int hq, int hkv, int d_qk, int d_v, long q_row, long k_row, long v_row, long o_row,

@@ -1,12 +1,15 @@
 // Flash-attention forward for sm_100a (causal or full, GQA / MQA / MLA head shapes).
 //
-// One CTA owns 128 query rows of one head and walks the KV sequence in blocks of 128:
-//   warp 0      : TMA producer (Q once, then K / V blocks through mbarrier rings)
-//   warp 1      : tcgen05 issuer:  S = Q K^T  (into one of two TMEM S buffers)  and  O += P V
-//   warps 2..5  : softmax, one thread per query row: S is read with tcgen05.ld, P = exp2(..) is
-//                 written as bf16 into 128B-swizzled shared memory (the A operand of the PV MMA),
-//                 O is rescaled in tensor memory only when the running max grew by more than 2^8.
-// S is double-buffered so that Q K^T of block j+1 runs while softmax works on block j.
+// One CTA owns two 128-row query tiles of one head and walks the KV sequence in blocks of 128:
+//   warp 0       : TMA producer (both Q tiles once, then K / V blocks through mbarrier rings)
+//   warp 1       : tcgen05 issuer:  S_t = Q_t K^T  and  O_t += P_t V  for both tiles t
+//   warps 2..5   : softmax warpgroup of tile 0        warps 6..9 : softmax warpgroup of tile 1
+// One thread owns one query row: it reads S from tensor memory (tcgen05.ld), keeps the running
+// max / sum, and writes P = exp2(.) back as packed bf16 *into the same TMEM columns* (tcgen05.st);
+// the P.V MMA takes its A operand straight from tensor memory, so P never touches shared memory.
+// The two tiles ping-pong: while one warpgroup does softmax, the tensor core runs the other tile's
+// P.V and the next Q K^T, and both tiles share every K / V block that is loaded.
+// O is rescaled in tensor memory only when the running max grew by more than 2^8.
 // V is consumed straight from its [kv, d] row-major tile through an MN-major descriptor, so no
 // transposes are needed.  All waits are bounded.
 //
@@ -20,26 +23,25 @@ namespace {
 constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int ATOM_BYTES = 128 * 128;  // 128 rows x 64 bf16
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;
 
 template <int DQK, int DV>
 struct FaCfg {
   static constexpr int KS = 2;                      // K stages
   static constexpr int VS = (DQK > 128) ? 1 : 2;    // V stages
-  static constexpr int Q_BYTES = BQ * DQK * 2;
+  static constexpr int Q_BYTES = BQ * DQK * 2;      // one tile
   static constexpr int K_BYTES = BKV * DQK * 2;
   static constexpr int V_BYTES = BKV * DV * 2;
-  static constexpr int P_BYTES = BQ * BKV * 2;
-  static constexpr int SMEM_BYTES = Q_BYTES + KS * K_BYTES + VS * V_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = 2 * Q_BYTES + KS * K_BYTES + VS * V_BYTES + 1024 + 256;
 };
 
 struct FaBars {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2];
   uint64_t v_full[2], v_empty[2];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full;
-  uint64_t pv_done;
+  uint64_t s_full[2];   // per tile
+  uint64_t p_full[2];   // per tile
+  uint64_t pv_done[2];  // per tile
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -71,21 +73,25 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   using C = FaCfg<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_smem = smem;
-  uint8_t* k_smem = q_smem + C::Q_BYTES;
+  uint8_t* q_smem = smem;  // two tiles
+  uint8_t* k_smem = q_smem + 2 * C::Q_BYTES;
   uint8_t* v_smem = k_smem + C::KS * C::K_BYTES;
-  uint8_t* p_smem = v_smem + C::VS * C::V_BYTES;
-  FaBars* bars = reinterpret_cast<FaBars*>(p_smem + C::P_BYTES);
+  FaBars* bars = reinterpret_cast<FaBars*>(v_smem + C::VS * C::V_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_qb = seq / BQ;
-  const int qb = num_qb - 1 - blockIdx.x;  // heaviest (longest KV range) blocks first
+  const int num_q128 = seq / BQ;
+  const int num_pairs = (num_q128 + 1) / 2;
+  const int pair = num_pairs - 1 - blockIdx.x;  // heaviest (longest KV range) pairs first
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / (hq / hkv);
   const int tok0 = batch * seq;
-  const int n_blocks = causal ? (qb + 1) : (seq / BKV);
+  const int qt[2] = {2 * pair, 2 * pair + 1};  // 128-row query tile indices
+  const bool active1 = qt[1] < num_q128;
+  const int n_kv = seq / BKV;
+  const int nb[2] = {causal ? qt[0] + 1 : n_kv, active1 ? (causal ? qt[1] + 1 : n_kv) : 0};
+  const int n_max = nb[0] > nb[1] ? nb[0] : nb[1];
   volatile int* abort_flag = &bars->abort_flag;
 
   if (threadIdx.x == 0) {
@@ -96,10 +102,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       pb::mbar_init(&bars->v_full[i], 1);
       pb::mbar_init(&bars->v_empty[i], 1);
       pb::mbar_init(&bars->s_full[i], 1);
-      pb::mbar_init(&bars->s_empty[i], 128);
+      pb::mbar_init(&bars->p_full[i], 128);
+      pb::mbar_init(&bars->pv_done[i], 1);
     }
-    pb::mbar_init(&bars->p_full, 128);
-    pb::mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     pb::fence_barrier_init();
     pb::prefetch_tmap(&tmQ);
@@ -115,17 +120,20 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   pb::tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tmem_o = tmem_base + 256;
+  // TMEM columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+DV)  O_1 [384,384+DV);  P_t aliases S_t[0,64)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       bool ok = true;
-      pb::mbar_expect_tx(&bars->q_full, C::Q_BYTES);
+      pb::mbar_expect_tx(&bars->q_full, (active1 ? 2 : 1) * C::Q_BYTES);
+      for (int t = 0; t < (active1 ? 2 : 1); ++t) {
 #pragma unroll
-      for (int a = 0; a < DQK / 64; ++a)
-        pb::tma_load_3d(q_smem + a * ATOM_BYTES, &tmQ, &bars->q_full, a * 64, head, tok0 + qb * BQ);
-      for (int j = 0; j < n_blocks && ok; ++j) {
+        for (int a = 0; a < DQK / 64; ++a)
+          pb::tma_load_3d(q_smem + t * C::Q_BYTES + a * ATOM_BYTES, &tmQ, &bars->q_full, a * 64, head,
+                          tok0 + qt[t] * BQ);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
         const int ks = j % C::KS, vs = j % C::VS;
         FA_WAIT(&bars->k_empty[ks], ((j / C::KS) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
         pb::mbar_expect_tx(&bars->k_full[ks], C::K_BYTES);
@@ -146,76 +154,92 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc_s = pb::make_idesc_bf16(BQ, BKV, 0, 0);
       constexpr uint32_t idesc_o = pb::make_idesc_bf16(BQ, DV, 0, 1);
-      const uint32_t qa = pb::smem_u32(q_smem);
-      const uint32_t pa = pb::smem_u32(p_smem);
       bool ok = true;
-      auto issue_s = [&](int j) {
+      auto issue_s = [&](int t, int j) {
+        const uint32_t qa = pb::smem_u32(q_smem + t * C::Q_BYTES);
         const uint32_t ka = pb::smem_u32(k_smem + (j % C::KS) * C::K_BYTES);
-        const uint32_t d = tmem_base + (j & 1) * 128;
+        const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int k = 0; k < DQK / 16; ++k) {
           const uint32_t off = (k / 4) * ATOM_BYTES + (k % 4) * 32;
           pb::umma_f16_ss(d, pb::make_smem_desc(qa + off, 0, 1024, 2), pb::make_smem_desc(ka + off, 0, 1024, 2),
                           idesc_s, k > 0 ? 1u : 0u);
         }
-        pb::umma_commit(&bars->k_empty[j % C::KS]);
-        pb::umma_commit(&bars->s_full[j & 1]);
+        pb::umma_commit(&bars->s_full[t]);
       };
       do {
         FA_WAIT(&bars->q_full, 0, PB_ERR_TIMEOUT_MMA);
         FA_WAIT(&bars->k_full[0], 0, PB_ERR_TIMEOUT_MMA);
         pb::tc_fence_after();
-        issue_s(0);
+        issue_s(0, 0);
+        if (active1) issue_s(1, 0);
+        pb::umma_commit(&bars->k_empty[0]);
       } while (false);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks) {
-          const int jn = j + 1;
-          FA_WAIT(&bars->k_full[jn % C::KS], (jn / C::KS) & 1, PB_ERR_TIMEOUT_MMA);
-          FA_WAIT(&bars->s_empty[jn & 1], ((jn >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
-          pb::tc_fence_after();
-          issue_s(jn);
-        }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const bool has_next = j + 1 < n_max;
+        bool next_k_ready = false;
         FA_WAIT(&bars->v_full[j % C::VS], (j / C::VS) & 1, PB_ERR_TIMEOUT_MMA);
-        FA_WAIT(&bars->p_full, j & 1, PB_ERR_TIMEOUT_MMA);
-        pb::tc_fence_after();
         const uint32_t va = pb::smem_u32(v_smem + (j % C::VS) * C::V_BYTES);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= nb[t]) continue;
+          FA_WAIT(&bars->p_full[t], j & 1, PB_ERR_TIMEOUT_MMA);
+          pb::tc_fence_after();
+          const uint32_t d = tmem_base + 256 + t * 128;
+          const uint32_t pa = tmem_base + t * 128;  // P_t: packed bf16, 8 columns per 16-wide k step
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t da = pb::make_smem_desc(pa + (k / 4) * ATOM_BYTES + (k % 4) * 32, 0, 1024, 2);
-          const uint64_t db = pb::make_smem_desc(va + k * 2048, ATOM_BYTES, 1024, 2);
-          pb::umma_f16_ss(tmem_o, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BKV / 16; ++k) {
+            const uint64_t db = pb::make_smem_desc(va + k * 2048, ATOM_BYTES, 1024, 2);
+            pb::umma_f16_ts(d, pa + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          }
+          pb::umma_commit(&bars->pv_done[t]);
+          if (j + 1 < nb[t]) {
+            if (!next_k_ready) {
+              FA_WAIT(&bars->k_full[(j + 1) % C::KS], ((j + 1) / C::KS) & 1, PB_ERR_TIMEOUT_MMA);
+              pb::tc_fence_after();
+              next_k_ready = true;
+            }
+            issue_s(t, j + 1);
+          }
         }
+        if (!ok) break;
         pb::umma_commit(&bars->v_empty[j % C::VS]);
-        pb::umma_commit(&bars->pv_done);
+        if (has_next) pb::umma_commit(&bars->k_empty[(j + 1) % C::KS]);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 2) >> 2;  // tile / warpgroup
     const int wq = warp & 3;
     const int row = wq * 32 + lane;
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_addr + t * 128;
+    const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
+    const int n_blocks = nb[t];
     float m_ref = -1e30f;
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks && ok; ++j) {
-      const int b = j & 1;
-      FA_WAIT(&bars->s_full[b], (j >> 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      FA_WAIT(&bars->s_full[t], j & 1, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
-      const uint32_t t_s = tmem_base + lane_addr + b * 128;
-      const bool diag = causal && (j == qb);
-      // pass 1: row maximum
-      float mx = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        pb::tmem_ld_32x32b_x32(t_s + c * 32, r);
-        pb::tmem_wait_ld();
+      const bool diag = causal && (j == qt[t]);
+      // the whole S row (128 fp32) is read once and stays in registers for both passes
+      uint32_t sr[128];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[i]);
-          if (!diag || (c * 32 + i) <= row) mx = fmaxf(mx, v);
-        }
+      for (int c = 0; c < 4; ++c) pb::tmem_ld_32x32b_x32(t_s + c * 32, sr + c * 32);
+      pb::tmem_wait_ld();
+      if (diag) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i > row) sr[i] = 0xff800000u;  // -inf: masked out of max and exp
       }
+      // pass 1: row maximum (four independent chains)
+      float mx4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(sr[i + u]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx * scale_log2);
       const bool grow = m_new > m_ref + 8.f;
       const bool any = __any_sync(0xffffffffu, grow);
@@ -225,63 +249,46 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         m_ref = m_new;
         l *= alpha;
       }
-      if (j > 0) {
-        FA_WAIT(&bars->pv_done, (j - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      if (j > 0 && any) {
+        FA_WAIT(&bars->pv_done[t], (j - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
         pb::tc_fence_after();
-        if (any) {
-          const uint32_t t_o = tmem_o + lane_addr;
 #pragma unroll 1
-          for (int c = 0; c < DV / 32; ++c) {
-            uint32_t r[32];
-            pb::tmem_ld_32x32b_x32(t_o + c * 32, r);
-            pb::tmem_wait_ld();
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t r[32];
+          pb::tmem_ld_32x32b_x32(t_o + c * 32, r);
+          pb::tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            pb::tmem_st_32x32b_x32(t_o + c * 32, r);
-          }
-          pb::tmem_wait_st();
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          pb::tmem_st_32x32b_x32(t_o + c * 32, r);
         }
       }
-      // pass 2: probabilities -> bf16 -> swizzled shared memory (K-major A operand of P.V)
-      uint8_t* prow = p_smem + row * 128;
-#pragma unroll 1
+      // pass 2: P = exp2(S * scale - m) as packed bf16, written over the (already read) S columns
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        pb::tmem_ld_32x32b_x32(t_s + c * 32, r);
-        pb::tmem_wait_ld();
-        float p[32];
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = pb::fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_ref));
-          if (diag && (c * 32 + i) > row) e = 0.f;
-          p[i] = e;
-          l += e;
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = pb::fast_exp2(fmaf(__uint_as_float(sr[c * 32 + i]), scale_log2, -m_ref));
+          const float e1 = pb::fast_exp2(fmaf(__uint_as_float(sr[c * 32 + i + 1]), scale_log2, -m_ref));
+          l4[(i >> 1) & 3] += e0 + e1;
+          pk[i >> 1] = pb::pack_bf16x2(e0, e1);
         }
-        uint8_t* atom = prow + (c >> 1) * ATOM_BYTES;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 v;
-          v.x = pb::pack_bf16x2(p[8 * i + 0], p[8 * i + 1]);
-          v.y = pb::pack_bf16x2(p[8 * i + 2], p[8 * i + 3]);
-          v.z = pb::pack_bf16x2(p[8 * i + 4], p[8 * i + 5]);
-          v.w = pb::pack_bf16x2(p[8 * i + 6], p[8 * i + 7]);
-          const int chunk = (c & 1) * 4 + i;
-          *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = v;
-        }
+        pb::tmem_st_32x32b_x16(t_s + c * 16, pk);
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      pb::tmem_wait_st();
       pb::tc_fence_before();
-      pb::mbar_arrive(&bars->s_empty[b]);
-      pb::fence_proxy_async_smem();
-      pb::mbar_arrive(&bars->p_full);
+      pb::mbar_arrive(&bars->p_full[t]);
     }
-    // epilogue: O / l -> bf16 -> shared -> TMA store; log-sum-exp for the backward pass
+    // epilogue: O / l -> bf16 -> shared (the tile's dead Q buffer) -> TMA store; log-sum-exp
     do {
-      if (!ok) break;
-      FA_WAIT(&bars->pv_done, (n_blocks - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      if (!ok || n_blocks == 0) break;
+      FA_WAIT(&bars->pv_done[t], (n_blocks - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
       const float inv = 1.f / l;
-      const uint32_t t_o = tmem_o + lane_addr;
-      uint8_t* orow = p_smem + row * 128;  // P is dead: reuse it as the output staging tile
+      uint8_t* stage = q_smem + t * C::Q_BYTES;
+      uint8_t* orow = stage + row * 128;
 #pragma unroll 1
       for (int c = 0; c < DV / 32; ++c) {
         uint32_t r[32];
@@ -299,13 +306,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) << 4)) = v;
         }
       }
-      lse[((long)batch * hq + head) * seq + qb * BQ + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      lse[((long)batch * hq + head) * seq + qt[t] * BQ + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
       pb::fence_proxy_async_smem();
-      pb::named_bar_sync(1, 128);
-      if (threadIdx.x == 64) {
+      pb::named_bar_sync(1 + t, 128);
+      if ((threadIdx.x & 127) == 64) {  // one thread per warpgroup (first lane of warps 2 and 6)
 #pragma unroll
         for (int a = 0; a < DV / 64; ++a)
-          pb::tma_store_3d(&tmO, p_smem + a * ATOM_BYTES, a * 64, head, tok0 + qb * BQ);
+          pb::tma_store_3d(&tmO, stage + a * ATOM_BYTES, a * 64, head, tok0 + qt[t] * BQ);
         pb::tma_store_commit();
         pb::tma_store_wait_all<0>();
       }
@@ -344,7 +351,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid(seq / BQ, hq, batch);
+  dim3 grid((seq / BQ + 1) / 2, hq, batch);
   kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, hq, hkv,
                                                    scale * 1.4426950408889634f, causal, status);
   return (int)cudaGetLastError();

@@ -66,7 +66,7 @@ def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, 
     do = do if (do.stride(2) == 1 and do.stride(1) == dvd) else do.contiguous()
     for t, d in ((q, dqk), (k, dqk), (v, dvd), (o, dvd), (do, dvd), (dq, dqk), (dk, dqk), (dv, dvd)):
         _check_view(t, d)
-    delta = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
+    delta = torch.empty(2, batch, hq, S, dtype=torch.float32, device=q.device)  # [rowsum(dO*O), lse*log2e]
     _lib.call("flash_attn_bwd", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, hq, hkv, dqk, dvd,
               q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0),
               dv.stride(0), float(scale), int(causal), _lib.status_word(q.device))

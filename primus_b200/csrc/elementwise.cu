@@ -689,3 +689,46 @@ int pb_embedding_bwd(const void* dy, const long* tokens, float* dw, long T, int 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of pb_rmsnorm_bwd (declared in primus_b200_noalloc.h).
+//
+// For callers that cannot allocate at the call site (a host application that owns every cudaMalloc,
+// a pre-planned memory arena, a latency-critical loop): the partial weight gradients go to a fixed
+// array in this library's device image rather than to caller-provided scratch.  Host code must not
+// pass the array's name to a kernel (on the host that name is only a stand-in for the symbol); its
+// device address is looked up once per device with cudaGetSymbolAddress, with that device current.
+#include "primus_b200_noalloc.h"
+
+namespace {
+static __device__ __align__(256) float g_noalloc_rmsnorm_partials[(long)PB_NOALLOC_MAX_PARTIALS * PB_NOALLOC_MAX_H];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                      const void* dres, void* dx, float* dw, long rows, int H, long ldx,
+                                      long lddy, int dw_accumulate, cudaStream_t s) {
+  if (H <= 0 || H % 8 || ldx % 8 || lddy % 8 || rows < 0) return PB_NOALLOC_ERR_BAD_ARG;
+  if (H > PB_NOALLOC_MAX_H) return PB_NOALLOC_ERR_TOO_LARGE;  // the built-in scratch holds rows of <= 8192 floats
+  if (rows == 0) return 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return PB_NOALLOC_ERR_BAD_ARG;
+  if (!g_noalloc_scratch_ptr[dev]) {
+    // once per device: device address of the scratch array of the image loaded on *this* device
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_rmsnorm_partials);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_scratch_ptr[dev] = p;
+  }
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  const int P = (int)(rows < PB_NOALLOC_MAX_PARTIALS ? rows : PB_NOALLOC_MAX_PARTIALS);
+  // every one of the P partial rows is fully written by its CTA before the reduction reads it
+  rmsnorm_bwd_kernel<<<P, RN_THREADS, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                             (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
+                                             (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
+  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
+  return (int)cudaGetLastError();
+}

@@ -732,3 +732,90 @@ extern "C" int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// MoE token movement.
+//   moe_gather_rows : out[r, :] = x[src[r], :] (* scale[r])   (src[r] < 0 -> zero row: expert padding)
+//   moe_combine_rows: out[t, :] = sum_k y[pos[t, k], :]        (pos < 0 skipped)  -- the un-weighted top-k
+//                     combine (routing probabilities are applied inside the expert activation) and, read
+//                     the other way round, the backward of the gather.
+// One warp moves one row with 16-byte accesses.  Replaces the permutation kernels of
+// primus/backends/transformer_engine/pytorch/common/triton/permutation.py:189-305.
+namespace {
+
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src,
+                                       const float* __restrict__ scale, __nv_bfloat16* __restrict__ out, long R,
+                                       int H, const int* __restrict__ limit_rows) {
+  const int lane = threadIdx.x & 31;
+  const long warp_global = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const long num_warps = ((long)gridDim.x * blockDim.x) >> 5;
+  const long lim = limit_rows ? (long)limit_rows[0] : R;
+  const int nv = H / 8;
+  for (long r = warp_global; r < R && r < lim; r += num_warps) {
+    const int s = src[r];
+    Bf8* o = reinterpret_cast<Bf8*>(out + r * H);
+    if (s < 0) {
+      Bf8 z;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+      for (int v = lane; v < nv; v += 32) o[v] = z;
+      continue;
+    }
+    const Bf8* in = reinterpret_cast<const Bf8*>(x + (long)s * H);
+    if (scale) {
+      const float sc = scale[r];
+      for (int v = lane; v < nv; v += 32) {
+        float f[8];
+        bf8_to_f(in[v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= sc;
+        o[v] = f_to_bf8(f);
+      }
+    } else {
+      for (int v = lane; v < nv; v += 32) o[v] = in[v];
+    }
+  }
+}
+
+__global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos,
+                                        __nv_bfloat16* __restrict__ out, long T, int topk, int H) {
+  const int lane = threadIdx.x & 31;
+  const long warp_global = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const long num_warps = ((long)gridDim.x * blockDim.x) >> 5;
+  const int nv = H / 8;
+  for (long t = warp_global; t < T; t += num_warps) {
+    Bf8* o = reinterpret_cast<Bf8*>(out + t * H);
+    for (int v = lane; v < nv; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < topk; ++k) {
+        const int p = pos[t * topk + k];
+        if (p < 0) continue;
+        float f[8];
+        bf8_to_f(reinterpret_cast<const Bf8*>(y + (long)p * H)[v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+      o[v] = f_to_bf8(acc);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int pb_moe_gather_rows(const void* x, const int* src, const float* scale, void* out, long R, int H,
+                                  const int* limit_rows, cudaStream_t s) {
+  if (H % 8) return -2;
+  if (R == 0) return 0;
+  moe_gather_rows_kernel<<<grid_for(R * 32, 256), 256, 0, s>>>((const __nv_bfloat16*)x, src, scale,
+                                                              (__nv_bfloat16*)out, R, H, limit_rows);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int pb_moe_combine_rows(const void* y, const int* pos, void* out, long T, int topk, int H,
+                                   cudaStream_t s) {
+  if (H % 8) return -2;
+  if (T == 0) return 0;
+  moe_combine_rows_kernel<<<grid_for(T * 32, 256), 256, 0, s>>>((const __nv_bfloat16*)y, pos, (__nv_bfloat16*)out, T,
+                                                               topk, H);
+  return (int)cudaGetLastError();
+}

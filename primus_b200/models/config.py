@@ -43,6 +43,9 @@ class TransformerConfig:
     qk_head_dim: int = 128
     qk_pos_emb_head_dim: int = 64
     v_head_dim: int = 128
+    mscale: float = 0.707
+    mscale_all_dim: float = 0.707
+    original_max_position_embeddings: int = 4096
     # mixture of experts
     num_experts: Optional[int] = None
     moe_router_topk: int = 2

@@ -83,11 +83,7 @@ class SelfAttention(nn.Module):
         scale = cfg.attention_softmax_scale
         ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
                                         rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
-        out = gemm.linear(ctx_out, self.linear_proj.weight)
-        if sp:
-            out = tpc.reduce_scatter_seq(out, tpg)
-        elif tpg is not None:
-            out = tpc.all_reduce(out, tpg)
+        out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 
     def _qk_norm(self, qkv, d):
@@ -134,11 +130,7 @@ class MLP(nn.Module):
         sp = cfg.sequence_parallel and st.tp > 1
         h1, xsum = layers.norm_linear(hidden, residual, self.linear_fc1.layer_norm_weight, self.linear_fc1.weight,
                                       cfg.norm_epsilon, tpg, sp)
-        out = layers.swiglu_linear(h1, self.linear_fc2.weight, None, cfg.activation_func_clamp_value)
-        if sp:
-            out = tpc.reduce_scatter_seq(out, tpg)
-        elif tpg is not None:
-            out = tpc.all_reduce(out, tpg)
+        out = layers.swiglu_linear(h1, self.linear_fc2.weight, None, cfg.activation_func_clamp_value, tpg, sp)
         return out, xsum
 
     def forward_normed(self, y):

@@ -1,0 +1,160 @@
+"""Mixture-of-experts layer: router + routed experts (grouped GEMMs) + optional shared experts.
+
+Parameter names: ``router.weight [E, H]`` (+ ``router.expert_bias``), stacked routed experts
+``experts.fc1_weight.weight [E_local, 2I, H]`` / ``experts.fc2_weight.weight [E_local, H, I]`` (the EP-sharded
+layout of the reference's MegaMoE module, primus/backends/megatron/core/extensions/mega_moe.py:272-305),
+``shared_experts.linear_fc{1,2}.weight``.  The checkpoint module splits the stacked tensors into the
+per-expert ``linear_fc1.weight{e}`` keys of the grouped-MLP layout on request.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ..ops import fused, gemm, layers
+from ..ops import moe as moe_ops
+from ..parallel import expert_parallel as epc
+from ..parallel import state as ps
+from .config import TransformerConfig
+
+
+class AuxLossScaler(torch.autograd.Function):
+    """Identity on the activation that injects d(aux_loss) into the backward pass (scaled like the main loss)."""
+    scale = 1.0
+
+    @staticmethod
+    def forward(ctx, x, aux_loss):
+        ctx.save_for_backward(aux_loss)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        (aux,) = ctx.saved_tensors
+        return g, torch.ones_like(aux) * AuxLossScaler.scale
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
+        super().__init__()
+        from .gpt import MLP, ParamHolder, _param
+
+        assert tp == 1, "MoE layers run with tensor_model_parallel_size 1 (expert parallelism shards the experts)"
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        st = ps.get_state()
+        self.ep, self.ep_rank = st.ep, st.ep_rank
+        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_ffn_hidden_size
+        assert E % self.ep == 0
+        self.e_local = E // self.ep
+        dt = cfg.torch_dtype
+        std = cfg.init_method_std
+        out_std = std / math.sqrt(2.0 * cfg.num_layers)
+        self.router = ParamHolder(weight=_param((E, H), std, dt, device))
+        if cfg.moe_router_enable_expert_bias:
+            self.router.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
+        # every EP rank draws the full expert set from the same stream and keeps its slice, so that the
+        # initial weights do not depend on the EP size
+        g = torch.Generator(device="cpu").manual_seed(977 + 31 * layer_idx)
+        lo, hi = self.ep_rank * self.e_local, (self.ep_rank + 1) * self.e_local
+        w1 = torch.empty(E, 2 * I, H).normal_(0.0, std, generator=g)[lo:hi].to(dt).to(device)
+        w2 = torch.empty(E, H, I).normal_(0.0, out_std, generator=g)[lo:hi].to(dt).to(device)
+        self.experts = nn.Module()
+        self.experts.fc1_weight = ParamHolder(weight=nn.Parameter(w1.contiguous()))
+        self.experts.fc2_weight = ParamHolder(weight=nn.Parameter(w2.contiguous()))
+        for p in (self.experts.fc1_weight.weight, self.experts.fc2_weight.weight):
+            p.is_expert = self.ep > 1
+            p.expert_parallel = self.ep > 1
+        if cfg.moe_shared_expert_intermediate_size:
+            self.shared_experts = MLP(cfg, device, 1, ffn=cfg.moe_shared_expert_intermediate_size, with_norm=False)
+        self.last_aux_loss = None
+        self.last_tokens_per_expert = None
+
+    # ------------------------------------------------------------------
+    def route(self, y):
+        cfg = self.cfg
+        logits = gemm.linear(y, self.router.weight)
+        bias = getattr(self.router, "expert_bias", None)
+        probs, idx, full = moe_ops.router_scores(
+            logits, cfg.moe_router_topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, bias,
+            cfg.moe_router_topk_scaling_factor, cfg.moe_router_num_groups, cfg.moe_router_group_topk)
+        if cfg.moe_router_force_load_balancing:
+            T = y.shape[0]
+            k = cfg.moe_router_topk
+            idx = (torch.arange(T * k, device=y.device) % cfg.num_experts).view(T, k)
+            probs = torch.full_like(probs, 1.0 / k)
+        aux = None
+        if cfg.moe_aux_loss_coeff and cfg.moe_router_load_balancing_type in ("aux_loss", "seq_aux_loss") \
+                and torch.is_grad_enabled():
+            seq = cfg.seq_length if cfg.moe_router_load_balancing_type == "seq_aux_loss" and \
+                y.shape[0] % cfg.seq_length == 0 else None
+            aux = moe_ops.load_balancing_loss(full, idx, cfg.num_experts, cfg.moe_router_topk,
+                                              cfg.moe_aux_loss_coeff, seq)
+            probs = AuxLossScaler.apply(probs, aux)
+            self.last_aux_loss = aux.detach()
+        return probs, idx
+
+    def experts_forward(self, x_perm, probs_perm, sched):
+        cfg = self.cfg
+        h1 = moe_ops.grouped_linear(x_perm, self.experts.fc1_weight.weight, sched)
+        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value)
+        return moe_ops.grouped_linear(act, self.experts.fc2_weight.weight, sched)
+
+    def forward(self, y):
+        cfg = self.cfg
+        T, H = y.shape
+        k = cfg.moe_router_topk
+        probs, idx = self.route(y)
+        flat_e = idx.reshape(-1)
+        counts_global = torch.bincount(flat_e, minlength=cfg.num_experts)
+        self.last_tokens_per_expert = counts_global
+        if self.ep == 1:
+            out = self._forward_local(y, probs, flat_e, counts_global, T, k)
+        else:
+            out = self._forward_ep(y, probs, flat_e, counts_global, T, k)
+        if hasattr(self, "shared_experts"):
+            out = out + self.shared_experts.forward_normed(y)
+        return out
+
+    # ------------------------------------------------------------------ single rank
+    def _forward_local(self, y, probs, flat_e, counts, T, k):
+        rows_cap = moe_ops.rows_capacity(T * k, self.e_local)
+        sched = moe_ops.build_schedule(counts.to(torch.int32), rows_cap)
+        src, pos = moe_ops.permutation_maps(flat_e, sched)
+        src_token = torch.where(src >= 0, src // k, src)
+        inv_pos = pos.view(T, k)
+        x_perm = moe_ops.gather_rows(y, src_token, inv_pos)
+        pf = torch.cat([probs.reshape(-1).float(), probs.new_zeros(1, dtype=torch.float32)])
+        probs_perm = pf[src.long()]  # src = -1 picks the appended zero
+        out_perm = self.experts_forward(x_perm, probs_perm, sched)
+        return moe_ops.combine_rows(out_perm, inv_pos, src_token)
+
+    # ------------------------------------------------------------------ expert parallel (NCCL all-to-all)
+    def _forward_ep(self, y, probs, flat_e, counts_global, T, k):
+        st = ps.get_state()
+        dev = y.device
+        in_splits, out_splits, recv_counts = epc.exchange_counts(counts_global, self.ep, self.ep_rank, st.ep_group)
+        order = torch.argsort(flat_e, stable=True)              # copies sorted by global expert = by destination
+        inv_order = torch.empty_like(order)
+        inv_order[order] = torch.arange(order.numel(), device=dev)
+        tok_sorted = (order // k).to(torch.int32)
+        send = moe_ops.gather_rows(y, tok_sorted, inv_order.view(T, k).to(torch.int32))
+        send_probs = probs.reshape(-1).float()[order]
+        recv = epc.all_to_all(send, in_splits, out_splits, st.ep_group)
+        recv_probs = epc.all_to_all(send_probs, in_splits, out_splits, st.ep_group)
+        R = recv.shape[0]
+        # arrival order is [source rank][local expert]
+        e_ids = torch.arange(self.e_local, device=dev).repeat(self.ep)
+        expert_of_row = torch.repeat_interleave(e_ids, recv_counts.reshape(-1), output_size=R)
+        counts_local = recv_counts.sum(0).to(torch.int32)
+        rows_cap = moe_ops.rows_capacity(R, self.e_local)
+        sched = moe_ops.build_schedule(counts_local, rows_cap)
+        src, pos = moe_ops.permutation_maps(expert_of_row, sched)
+        x_perm = moe_ops.gather_rows(recv, src, pos.view(R, 1))
+        pf = torch.cat([recv_probs, recv_probs.new_zeros(1)])
+        probs_perm = pf[src.long()]
+        out_perm = self.experts_forward(x_perm, probs_perm, sched)
+        back = moe_ops.combine_rows(out_perm, pos.view(R, 1), src)       # padded layout -> arrival order
+        ret = epc.all_to_all(back, out_splits, in_splits, st.ep_group)   # -> this rank's sorted copies
+        return moe_ops.combine_rows(ret, inv_order.view(T, k).to(torch.int32), tok_sorted)

@@ -19,6 +19,7 @@ import math
 
 import torch
 
+from ..parallel import fused_tp
 from ..parallel import tensor_parallel as tp_comm
 from . import _lib, attention, fused, gemm
 
@@ -40,8 +41,9 @@ class NormLinearFn(torch.autograd.Function):
             xsum = x2
             _lib.call("rmsnorm_fwd", x2, None, norm_w, y, None, rstd, rows, H, x2.stride(0), y.stride(0), float(eps))
         if sp:
-            y = tp_comm.all_gather_dim0(y, tp_group)
-        out = gemm.gemm(y, weight)
+            out, _ = fused_tp.ag_gemm(y, weight, tp_group, fused=fused_tp.ENABLED)
+        else:
+            out = gemm.gemm(y, weight)
         ctx.save_for_backward(xsum, norm_w, weight, rstd)
         ctx.eps = eps
         ctx.tp = (tp_group, sp)
@@ -72,12 +74,13 @@ class NormLinearFn(torch.autograd.Function):
         if sp:
             y = tp_comm.all_gather_dim0(y, tp_group)
         dw = gemm.wgrad(dout2, y, weight_ref)
-        dy = gemm.gemm(dout2, weight, b_mn=True)
         del y
         if sp:
-            dy = tp_comm.reduce_scatter_dim0(dy, tp_group)
-        elif tp_group is not None:
-            torch.distributed.all_reduce(dy, group=tp_group)
+            dy = fused_tp.gemm_rs(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED)
+        else:
+            dy = gemm.gemm(dout2, weight, b_mn=True)
+            if tp_group is not None:
+                torch.distributed.all_reduce(dy, group=tp_group)
         dres = None
         if dxsum is not None:
             dres = dxsum.reshape(rows, H)
@@ -123,7 +126,7 @@ def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_p
 # ----------------------------------------------------------------------------------------------
 class SwiGLULinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h1, weight, probs, clamp):
+    def forward(ctx, h1, weight, probs, clamp, tp_group, sp):
         I2 = h1.shape[-1]
         I = I2 // 2
         x2 = h1.reshape(-1, I2)
@@ -131,28 +134,39 @@ class SwiGLULinearFn(torch.autograd.Function):
         act = torch.empty(T, I, dtype=h1.dtype, device=h1.device)
         p = probs.reshape(-1).float().contiguous() if probs is not None else None
         _lib.call("swiglu_fwd", x2, p, act, T, I, float(clamp))
-        out = gemm.gemm(act, weight)
+        if sp:
+            out = fused_tp.gemm_rs(act, weight, tp_group, fused=fused_tp.ENABLED)
+        else:
+            out = gemm.gemm(act, weight)
+            if tp_group is not None:
+                torch.distributed.all_reduce(out, group=tp_group)
+        ctx.tp = (tp_group, sp)
         ctx.save_for_backward(x2, weight, p if p is not None else torch.empty(0))
         ctx.has_probs = probs is not None
         ctx.probs_meta = (probs.shape, probs.dtype) if probs is not None else None
         ctx.clamp = clamp
         ctx.shape = h1.shape
         ctx.weight_ref = weight
-        return out.view(*h1.shape[:-1], weight.shape[0])
+        return out
 
     @staticmethod
     def backward(ctx, dout):
         x2, weight, p = ctx.saved_tensors
+        tp_group, sp = ctx.tp
         T, I2 = x2.shape
         I = I2 // 2
         pp = p if ctx.has_probs else None
-        dout2 = dout.reshape(T, -1)
+        dout2 = dout.reshape(-1, dout.shape[-1])
         if not dout2.is_contiguous():
             dout2 = dout2.contiguous()
         act = torch.empty(T, I, dtype=x2.dtype, device=x2.device)
         _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp))
-        dw = gemm.wgrad(dout2, act, ctx.weight_ref)
-        dact = gemm.gemm(dout2, weight, b_mn=True, out=act)  # reuse the activation buffer
+        if sp:
+            dact, dout2 = fused_tp.ag_gemm(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED)
+            dw = gemm.wgrad(dout2, act, ctx.weight_ref)
+        else:
+            dw = gemm.wgrad(dout2, act, ctx.weight_ref)
+            dact = gemm.gemm(dout2, weight, b_mn=True, out=act)  # reuse the activation buffer
         din = torch.empty_like(x2)
         dprobs = torch.empty(T, dtype=torch.float32, device=x2.device) if ctx.has_probs else None
         _lib.call("swiglu_bwd", dact, x2, pp, din, dprobs, T, I, float(ctx.clamp))
@@ -160,14 +174,49 @@ class SwiGLULinearFn(torch.autograd.Function):
         if ctx.has_probs:
             shape, dt = ctx.probs_meta
             dp = dprobs.view(shape).to(dt)
-        return din.view(ctx.shape), dw, dp, None
+        return din.view(ctx.shape), dw, dp, None, None, None
 
 
-def swiglu_linear(h1, weight, probs=None, clamp=0.0):
-    """linear(swiglu(h1) * probs) with the activation recomputed in backward."""
+def swiglu_linear(h1, weight, probs=None, clamp=0.0, tp_group=None, sequence_parallel=False):
+    """linear(swiglu(h1) * probs) with the activation recomputed in backward.  ``weight`` may be a
+    row-parallel shard: the partial outputs are reduce-scattered over tokens (sequence parallel) or
+    all-reduced over ``tp_group``."""
+    sp = bool(sequence_parallel and tp_group is not None)
     if not h1.is_cuda:
-        return gemm.linear(fused.swiglu_ref(h1, probs, clamp), weight)
-    return SwiGLULinearFn.apply(h1, weight, probs, clamp)
+        out = gemm.linear(fused.swiglu_ref(h1, probs, clamp), weight)
+        if sp:
+            return tp_comm.reduce_scatter_seq(out, tp_group)
+        return tp_comm.all_reduce(out, tp_group) if tp_group is not None else out
+    return SwiGLULinearFn.apply(h1, weight, probs, clamp, tp_group, sp)
+
+
+class RowParallelLinearFn(torch.autograd.Function):
+    """reduce_scatter(x @ W^T) over tokens with a row-parallel weight shard (attention output projection)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, tp_group):
+        out = fused_tp.gemm_rs(x, weight, tp_group, fused=fused_tp.ENABLED)
+        ctx.save_for_backward(x, weight)
+        ctx.group = tp_group
+        ctx.weight_ref = weight
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, weight = ctx.saved_tensors
+        dout = dout.contiguous()
+        dx, dout_full = fused_tp.ag_gemm(dout, weight, ctx.group, b_mn=True, fused=fused_tp.ENABLED)
+        dw = gemm.wgrad(dout_full, x, ctx.weight_ref)
+        return dx, dw, None
+
+
+def row_parallel_linear(x, weight, tp_group=None, sequence_parallel=False):
+    if tp_group is None:
+        return gemm.linear(x, weight)
+    if sequence_parallel and x.is_cuda:
+        return RowParallelLinearFn.apply(x, weight, tp_group)
+    out = gemm.linear(x, weight)
+    return tp_comm.reduce_scatter_seq(out, tp_group) if sequence_parallel else tp_comm.all_reduce(out, tp_group)
 
 
 # ----------------------------------------------------------------------------------------------

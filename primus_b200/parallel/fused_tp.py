@@ -1,0 +1,148 @@
+"""Tensor-parallel GEMMs fused with their collective (``csrc/gemm_tp_fused.cu``).
+
+``ag_gemm(x_shard, w)``  : ``all_gather(x_shard) @ w.T``   -> (out [T, N], gathered [T, K])
+``gemm_rs(x, w)``        : ``reduce_scatter(x @ w.T)``     -> out [T/tp, N]
+
+Both run as ONE persistent kernel in which communication CTAs move peer data over NVLink with P2P
+loads while GEMM CTAs (tcgen05) work on the tiles whose operands / destinations are ready.  The
+NCCL pair (``all_gather_into_tensor`` + GEMM, GEMM + ``reduce_scatter_tensor``) stays available as the
+baseline (``fused=False``) and is what CPU/gloo runs use.
+
+Workspaces (symmetric activation shard, symmetric partial-product buffer, local gather buffer, fp32
+accumulator, counters) are cached per (group, shape): the tensors returned by ``ag_gemm`` (``gathered``)
+are views of such a workspace and are valid until the next fused call with the same shape.
+
+Which GEMMs use which form follows the reference's user-buffer table
+(primus/backends/transformer_engine/pytorch/module/base.py:141-159): all-gather overlap for
+qkv/fc1 fprop and proj/fc2 dgrad, reduce-scatter overlap for proj/fc2 fprop and qkv/fc1 dgrad.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib, gemm as gemm_ops
+from . import tensor_parallel as tpc
+from .symm_mem import SymmetricBuffer
+
+COMM_CTAS = int(os.environ.get("PRIMUS_B200_TP_COMM_CTAS", "16"))
+# Fused kernels on/off (config key ``tp_comm_overlap``); off = NCCL collective + GEMM.
+ENABLED = os.environ.get("PRIMUS_B200_TP_FUSED", "0") == "1"
+
+
+class _Instance:
+    """Everything one (mode, M, N, K) fused op needs; flag slots and epochs are private to it."""
+    _next_slot = 0
+
+    def __init__(self, ctx: "FusedTPContext", mode: int, M: int, N: int, K: int):
+        self.mode, self.M, self.N, self.K = mode, M, N, K
+        tp = ctx.tp
+        dev = ctx.device
+        self.epoch = 0
+        self.slot = _Instance._next_slot
+        _Instance._next_slot += 1
+        assert self.slot < 60, "too many distinct fused TP shapes"
+        self.counters = torch.zeros(2 * tp, dtype=torch.int32, device=dev)
+        Tl = M // tp
+        if mode == 0:
+            self.sym = SymmetricBuffer(Tl * K * 2, ctx.group, dev)       # activation shard of every rank
+            self.gather = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+            self.acc = None
+            self.out_rs = None
+        else:
+            self.sym = SymmetricBuffer(M * N * 2, ctx.group, dev)        # partial product of every rank
+            self.gather = None
+            self.acc = torch.empty(Tl, N, dtype=torch.float32, device=dev)
+        # flag slot range of this instance inside the symmetric buffer's own flag area
+        self.peer_payload = (ctypes.c_long * 8)(*[self.sym.peer_ptr(r) for r in range(tp)], *([0] * (8 - tp)))
+        self.peer_flags = (ctypes.c_long * 8)(*[self.sym.peer_ptr(r) + self.sym.nbytes for r in range(tp)],
+                                               *([0] * (8 - tp)))
+        self.local_flags = self.sym.flags
+
+
+class FusedTPContext:
+    def __init__(self, group):
+        self.group = group
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._inst: dict = {}
+
+    def instance(self, mode: int, M: int, N: int, K: int) -> _Instance:
+        key = (mode, M, N, K)
+        inst = self._inst.get(key)
+        if inst is None:
+            inst = _Instance(self, mode, M, N, K)
+            self._inst[key] = inst
+        return inst
+
+    def supported(self, M: int, N: int, K: int) -> bool:
+        return self.tp >= 2 and M % self.tp == 0 and (M // self.tp) % 128 == 0 and K % 8 == 0 and N % 8 == 0
+
+
+_CTX: dict = {}
+
+
+def get_context(group) -> FusedTPContext:
+    key = id(group)
+    if key not in _CTX:
+        _CTX[key] = FusedTPContext(group)
+    return _CTX[key]
+
+
+def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):
+    null = ctypes.c_void_p(0)
+    inst.epoch += 1
+    lib = _lib.require()
+    fn = lib.pb_gemm_tp_fused
+    fn.restype = ctypes.c_int
+    vp = ctypes.c_void_p
+    _lib.LAUNCH_COUNT += 1
+    rc = fn(ctypes.c_int(inst.mode), ctypes.c_int(ctx.tp), ctypes.c_int(ctx.rank), ctypes.c_int(inst.epoch),
+            ctypes.c_int(COMM_CTAS), vp(A.data_ptr()), vp(B.data_ptr()), vp(D.data_ptr()), ctypes.c_int(inst.M),
+            ctypes.c_int(inst.N), ctypes.c_int(inst.K), ctypes.c_long(B.stride(0)), ctypes.c_int(int(b_mn)),
+            inst.peer_payload if inst.mode == 0 else null,
+            vp(inst.gather.data_ptr()) if inst.mode == 0 else null,
+            inst.peer_payload if inst.mode == 1 else null,
+            vp(inst.acc.data_ptr()) if inst.mode == 1 else null,
+            vp(out_rs.data_ptr()) if out_rs is not None else null,
+            vp(inst.counters.data_ptr()), inst.peer_flags, vp(inst.local_flags.data_ptr()),
+            vp(_lib.status_word(ctx.device).data_ptr()), _lib.stream_ptr())
+    if rc != 0:
+        raise _lib.NativeLibraryError(f"pb_gemm_tp_fused failed with code {rc}")
+
+
+def ag_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: bool = True):
+    """Returns (all_gather(x_shard) @ W^T, gathered x). ``w``: [N, K] or, with ``b_mn``, [K, N]."""
+    tp = dist.get_world_size(group)
+    Tl, K = x_shard.shape
+    M = Tl * tp
+    N = w.shape[1] if b_mn else w.shape[0]
+    ctx = get_context(group) if (fused and x_shard.is_cuda) else None
+    if ctx is None or not ctx.supported(M, N, K):
+        g = tpc.all_gather_dim0(x_shard, group)
+        return gemm_ops.gemm(g, w, b_mn=b_mn), g
+    inst = ctx.instance(0, M, N, K)
+    inst.sym.local(torch.bfloat16, Tl * K).view(Tl, K).copy_(x_shard)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x_shard.device)
+    _launch(ctx, inst, inst.gather, w, out, b_mn)
+    return out, inst.gather
+
+
+def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: bool = True) -> torch.Tensor:
+    """Returns reduce_scatter(x @ W^T) over dim 0."""
+    tp = dist.get_world_size(group)
+    M, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    ctx = get_context(group) if (fused and x.is_cuda) else None
+    if ctx is None or not ctx.supported(M, N, K) or not x.is_contiguous():
+        return tpc.reduce_scatter_dim0(gemm_ops.gemm(x, w, b_mn=b_mn), group)
+    inst = ctx.instance(1, M, N, K)
+    partial = inst.sym.local(torch.bfloat16, M * N).view(M, N)
+    out = torch.empty(M // tp, N, dtype=torch.bfloat16, device=x.device)
+    _launch(ctx, inst, x, w, partial, b_mn, out_rs=out)
+    return out

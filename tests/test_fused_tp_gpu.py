@@ -1,0 +1,42 @@
+"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels vs the NCCL + GEMM composition (2 GPUs)."""
+import pytest
+import torch
+
+from tests.mp_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, shapes):
+    import torch.distributed as dist
+
+    from primus_b200.ops import _lib
+    from primus_b200.parallel import fused_tp
+
+    group = dist.group.WORLD
+    torch.manual_seed(1234 + rank)
+    for (T, N, K, b_mn) in shapes:
+        Tl = T // world
+        for it in range(3):  # several epochs through the same workspace
+            x_shard = torch.randn(Tl, K, device="cuda").bfloat16()
+            w = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.05).bfloat16()
+            out, gathered = fused_tp.ag_gemm(x_shard, w, group, b_mn=b_mn, fused=True)
+            ref, gref = fused_tp.ag_gemm(x_shard, w, group, b_mn=b_mn, fused=False)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            assert torch.equal(gathered, gref), f"gathered activations differ (T={T} it={it})"
+            err = (out.float() - ref.float()).abs().max().item()
+            assert err <= 2e-2 * ref.float().abs().max().item() + 1e-3, f"ag_gemm err {err}"
+            x = torch.randn(T, K, device="cuda").bfloat16()
+            out2 = fused_tp.gemm_rs(x, w, group, b_mn=b_mn, fused=True)
+            ref2 = fused_tp.gemm_rs(x, w, group, b_mn=b_mn, fused=False)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            err2 = (out2.float() - ref2.float()).abs().max().item()
+            assert err2 <= 3e-2 * ref2.float().abs().max().item() + 1e-2, f"gemm_rs err {err2}"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_matches_nccl_composition():
+    shapes = [(512, 256, 128, False), (2048, 1280, 1024, False), (1024, 768, 512, True)]
+    run_ranks(_worker, 2, "nccl", args=(shapes,), timeout=240)

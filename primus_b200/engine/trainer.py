@@ -69,7 +69,9 @@ class TrainConfig:
     exit_duration_in_mins: Optional[float] = None
     eval_interval: Optional[int] = None
     eval_iters: int = 0
-    pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv
+    pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv | v-half | v-min
+    pipeline_model_parallel_layout: Optional[str] = None
+    decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
     profile: bool = False
@@ -81,7 +83,14 @@ class TrainConfig:
         import dataclasses
 
         names = {f.name for f in dataclasses.fields(cls)}
-        return cls(**{k: v for k, v in d.items() if k in names})
+        kw = {k: v for k, v in d.items() if k in names}
+        if "pipeline_schedule" not in d and d.get("pp_algorithm"):
+            kw["pipeline_schedule"] = d["pp_algorithm"]
+        if d.get("tp_comm_overlap"):
+            from ..parallel import fused_tp
+
+            fused_tp.ENABLED = True
+        return cls(**kw)
 
 
 class ThroughputMeter:
@@ -123,10 +132,21 @@ class Trainer:
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
         # ---------------------------------------------------------------- model chunks
+        from ..parallel import pipeline_schedules as pps
+
+        algo = train_cfg.pipeline_schedule.lower().replace("_", "-")
+        v_family = algo in ("zbv", "zbv-formatted", "zbv-greedy", "v-half", "v-min")
         vpp = model_cfg.virtual_pipeline_model_parallel_size if st.pp > 1 else None
+        self.pp_chunks = 1 if st.pp == 1 else (2 if v_family else (vpp or 1))
+        self.pp_placement = "v" if (v_family and st.pp > 1) else "interleaved"
+        n_stages = st.pp * self.pp_chunks
+        self.loss_pp_rank = pps.rank_of_stage(n_stages - 1, st.pp, self.pp_placement)[0] if st.pp > 1 else 0
         self.model_chunks = []
-        for v in range(vpp or 1):
-            m = build_model(model_cfg, self.device, st.pp_rank, st.pp, v if vpp else None, vpp, seed=train_cfg.seed)
+        for c in range(self.pp_chunks):
+            sid = pps.stage_of(st.pp_rank, c, st.pp, self.pp_placement) if st.pp > 1 else 0
+            m = build_model(model_cfg, self.device, sid, n_stages, seed=train_cfg.seed,
+                            layout=getattr(train_cfg, "pipeline_model_parallel_layout", None),
+                            manual_split=getattr(train_cfg, "decoder_pipeline_manual_split_list", None))
             self.model_chunks.append(m)
         self.model = self.model_chunks[0]
         # ---------------------------------------------------------------- buffers + optimizer
@@ -259,7 +279,7 @@ class Trainer:
             dist.all_reduce(l, group=self.st.dp_group)
             l /= self.st.dp
         if self.st.pp > 1:
-            dist.broadcast(l, src=self.st.pp_ranks[-1], group=self.st.pp_group)
+            dist.broadcast(l, src=self.st.pp_ranks[self.loss_pp_rank], group=self.st.pp_group)
         return float(l.item())
 
     # ------------------------------------------------------------------ loop

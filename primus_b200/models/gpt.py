@@ -294,16 +294,14 @@ def _run_layer(layer, hidden, residual, rope, batch, cfg):
     return layer(hidden, residual, rope, batch)
 
 
-def build_model(cfg: TransformerConfig, device="cpu", pp_rank: int = 0, pp_size: int = 1,
-                vp_stage: Optional[int] = None, vp_size: Optional[int] = None, seed: Optional[int] = None) -> GPTModel:
-    """Build the model chunk owned by (pp_rank, vp_stage) with an even layer split."""
+def build_model(cfg: TransformerConfig, device="cpu", stage_id: int = 0, n_stages: int = 1,
+                seed: Optional[int] = None, layout: Optional[str] = None, manual_split=None) -> GPTModel:
+    """Build the model chunk that owns global (virtual) pipeline stage ``stage_id`` of ``n_stages``."""
     from ..parallel.pipeline_layout import layers_for_stage
 
-    idx = layers_for_stage(cfg.num_layers, pp_size, pp_rank, vp_size, vp_stage)
-    n_virtual = pp_size * (vp_size or 1)
-    stage_id = (vp_stage or 0) * pp_size + pp_rank
+    idx = layers_for_stage(cfg.num_layers, n_stages, stage_id, None, None, layout, manual_split)
     if seed is not None:
         st = ps.get_state()
         torch.manual_seed(seed + 100 * stage_id + 2718 * st.tp_rank)
-    return GPTModel(cfg, device, pre_process=(stage_id == 0), post_process=(stage_id == n_virtual - 1),
+    return GPTModel(cfg, device, pre_process=(stage_id == 0), post_process=(stage_id == n_stages - 1),
                     layer_indices=idx)

@@ -226,21 +226,44 @@ def swiglu(x, probs=None, clamp=0.0):
 
 # ----------------------------------------------------------------------------------------------
 # Cross entropy (optionally vocab-parallel over a TP group)
-def cross_entropy_ref(logits, labels, vocab_start=0, group=None):
-    """Per-token loss, fp32. Vocab-parallel when ``group`` is given (logits hold a vocab slice)."""
-    lf = logits.float()
-    V = lf.shape[-1]
-    m = lf.max(-1).values
-    if group is not None:
+class _VocabParallelCERef(torch.autograd.Function):
+    """Plain-PyTorch vocab-parallel cross entropy with an explicit backward (collectives are not
+    differentiable, so the gradient (softmax - onehot) is formed by hand from the reduced statistics)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, vocab_start, group):
+        lf = logits.detach().float()
+        V = lf.shape[-1]
+        m = lf.max(-1).values
         dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
-    se = (lf - m[..., None]).exp().sum(-1)
-    lab = labels - vocab_start
-    inr = (lab >= 0) & (lab < V)
-    tgt = torch.where(inr, lf.gather(-1, lab.clamp(0, V - 1)[..., None]).squeeze(-1), torch.zeros_like(m))
-    if group is not None:
+        ex = (lf - m[..., None]).exp()
+        se = ex.sum(-1)
+        lab = labels - vocab_start
+        inr = (lab >= 0) & (lab < V)
+        tgt = torch.where(inr, lf.gather(-1, lab.clamp(0, V - 1)[..., None]).squeeze(-1), torch.zeros_like(m))
         dist.all_reduce(se, group=group)
         dist.all_reduce(tgt, group=group)
-    return m + se.log() - tgt
+        p = ex / se[..., None]
+        onehot = torch.zeros_like(p)
+        onehot.scatter_(-1, lab.clamp(0, V - 1)[..., None], inr[..., None].to(p.dtype))
+        ctx.save_for_backward(p - onehot)
+        ctx.dtype = logits.dtype
+        return m + se.log() - tgt
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (g,) = ctx.saved_tensors
+        return (g * dloss[..., None]).to(ctx.dtype), None, None, None
+
+
+def cross_entropy_ref(logits, labels, vocab_start=0, group=None):
+    """Per-token loss, fp32. Vocab-parallel when ``group`` is given (logits hold a vocab slice)."""
+    if group is not None:
+        return _VocabParallelCERef.apply(logits, labels, vocab_start, group)
+    lf = logits.float()
+    lse = torch.logsumexp(lf, dim=-1)
+    tgt = lf.gather(-1, labels[..., None]).squeeze(-1)
+    return lse - tgt
 
 
 class CrossEntropyFn(torch.autograd.Function):

@@ -107,13 +107,57 @@ class LinearFn(torch.autograd.Function):
         return dx, dw
 
 
+class WGradStore:
+    """Deferred weight-gradient GEMMs for zero-bubble pipeline schedules: while a ``B`` node runs
+    (``begin(key)`` .. ``end()``), linear layers queue their dW GEMM instead of executing it; the matching
+    ``W`` node replays the queue with ``flush(key)``.  (Role of the reference's ``WGradRunningCache``,
+    primus/core/pipeline_parallel/handler/wgrad_handler.py:17-78.)"""
+
+    def __init__(self):
+        self.current = None
+        self.queues: dict = {}
+
+    def begin(self, key):
+        self.current = key
+        self.queues.setdefault(key, [])
+
+    def end(self):
+        self.current = None
+
+    def put(self, dy2, x2, weight) -> bool:
+        if self.current is None or getattr(weight, "main_grad", None) is None:
+            return False
+        self.queues[self.current].append((dy2, x2, weight))
+        return True
+
+    def flush(self, key):
+        with torch.no_grad():
+            for dy2, x2, weight in self.queues.pop(key, []):
+                _wgrad_into_main_grad(dy2.detach(), x2.detach(), weight)
+
+    def flush_all(self):
+        for k in list(self.queues):
+            self.flush(k)
+
+
+WGRAD_STORE = WGradStore()
+
+
+def _wgrad_into_main_grad(dy2, x2, weight):
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.main_grad, accumulate=True)
+    weight.grad_added_to_main_grad = True
+    cb = getattr(weight, "_grad_ready_cb", None)
+    if cb is not None:
+        cb(weight)
+
+
 def wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
     """dW = dy^T x. Accumulates into ``weight.main_grad`` (fp32) if present and returns None;
     otherwise returns the gradient in the weight's dtype."""
     main_grad = getattr(weight, "main_grad", None)
     if main_grad is not None:
-        gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
-        weight.grad_added_to_main_grad = True
+        if not WGRAD_STORE.put(dy2, x2, weight):
+            _wgrad_into_main_grad(dy2, x2, weight)
         return None
     if dy2.is_cuda:
         return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)

@@ -1,0 +1,150 @@
+"""Pipeline-parallel runtime: executes a schedule table (``pipeline_schedules``) on this rank.
+
+Every ``F`` node runs one model chunk on one micro-batch, ``B`` / ``BW`` run its backward, ``W`` runs the
+weight-gradient GEMMs that a ``B`` node deferred (``ops.gemm.WGRAD_STORE``), and activations / gradients
+travel between neighbouring stages with NCCL (gloo on CPU) point-to-point operations: sends are
+asynchronous and complete in the background, receives are posted when the consumer node is reached.
+Forward-direction and backward-direction traffic use two separate communicators so that a pending
+send in one direction can never block the other (the reference orders even / odd ranks instead:
+primus/backends/megatron/core/pipeline_parallel/primuspipe/handlers/communication_handler.py:40-133).
+Hand-offs between two chunks that live on the same rank (the fold of a V schedule) stay local.
+
+Counterpart of ``PrimusPipelineParallelLauncher.run`` / ``ScheduleRunner``
+(primus/backends/megatron/core/pipeline_parallel/primuspipe/pipeline_launcher.py:141-346,
+handlers/fwd_handler.py:40-122, handlers/bwd_handler.py:31-128).
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+import torch.distributed as dist
+
+from ..ops import gemm as gemm_ops
+from . import pipeline_schedules as sched
+from . import state as ps
+
+
+class PipelineTimeline:
+    """Optional per-node wall-clock record (the data the reference dumps for its pipeline visualiser,
+    primus/backends/megatron/core/pipeline_parallel/pp_visualizer.py)."""
+
+    def __init__(self):
+        self.events = []
+
+    def add(self, node, t0, t1):
+        self.events.append({"kind": node.kind, "mb": node.mb, "chunk": node.chunk, "start": t0, "end": t1})
+
+
+def _p2p_shape(trainer, batch, seq):
+    st = trainer.st
+    T = batch * seq
+    if trainer.mcfg.sequence_parallel and st.tp > 1:
+        T //= st.tp
+    return (2, T, trainer.mcfg.hidden_size)
+
+
+def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: PipelineTimeline | None = None):
+    st = trainer.st
+    pp, r = st.pp, st.pp_rank
+    m = len(micro_batches)
+    key = (trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp)
+    cache = getattr(trainer, "_pp_schedule_cache", {})
+    if key not in cache:
+        algo = trainer.tcfg.pipeline_schedule
+        if st.virtual_pp and st.virtual_pp > 1 and algo == "1f1b":
+            algo = "interleaved"
+        cache[key] = sched.build_schedule(algo, pp, m, st.virtual_pp)
+        trainer._pp_schedule_cache = cache
+    sch = cache[key]
+    chunks, placement = sch["chunks"], sch["placement"]
+    assert chunks == len(trainer.model_chunks), \
+        f"schedule {sch['algorithm']} needs {chunks} model chunks per rank, trainer built {len(trainer.model_chunks)}"
+    S = pp * chunks
+    nodes = sch["table"][r]
+    dtype = trainer.mcfg.torch_dtype
+    dev = trainer.device
+    fwd_g, bwd_g = st.pp_fwd_group, st.pp_bwd_group
+    inputs, outputs, local_act, local_grad = {}, {}, {}, {}
+    sends = []
+    total = trainer.loss_accum
+    total.zero_()
+    split_w = any(n.kind == "W" for n in nodes)
+    for buf in trainer.buffers:
+        buf.is_last_microbatch = False
+
+    def global_rank(pp_rank):
+        return st.pp_ranks[pp_rank]
+
+    for node in nodes:
+        t0 = time.perf_counter() if timeline is not None else 0.0
+        s = sched.stage_of(r, node.chunk, pp, placement)
+        mb = micro_batches[node.mb]
+        batch, seq = mb["tokens"].shape
+        model = trainer.model_chunks[node.chunk]
+        k = (node.mb, node.chunk)
+        if node.kind == "F":
+            if s == 0:
+                hidden_in = None
+            else:
+                pr, pc = sched.rank_of_stage(s - 1, pp, placement)
+                if pr == r:
+                    x = local_act.pop((node.mb, pc))
+                else:
+                    x = torch.empty(_p2p_shape(trainer, batch, seq), dtype=dtype, device=dev)
+                    dist.recv(x, src=global_rank(pr), group=fwd_g)
+                x.requires_grad_(True)
+                inputs[k] = x
+                hidden_in = (x[0], x[1], batch, seq)
+            if s == S - 1:
+                w = trainer._loss_weights(mb)
+                out = model(mb["tokens"] if s == 0 else None, mb["labels"], loss_weights=w, hidden_in=hidden_in,
+                            unit_upstream=True)
+                outputs[k] = out
+                total += out.detach()
+            else:
+                h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in)
+                if res is None:
+                    res = torch.zeros_like(h)
+                y = torch.stack([h, res])
+                outputs[k] = y
+                nr, nc = sched.rank_of_stage(s + 1, pp, placement)
+                if nr == r:
+                    local_act[(node.mb, node.chunk)] = y.detach().clone()
+                else:
+                    sends.append((dist.isend(y.detach(), dst=global_rank(nr), group=fwd_g), y))
+        elif node.kind in ("B", "BW"):
+            out = outputs.pop(k)
+            if split_w and node.kind == "B":
+                gemm_ops.WGRAD_STORE.begin(k)
+            if s == S - 1:
+                out.backward()
+            else:
+                nr, nc = sched.rank_of_stage(s + 1, pp, placement)
+                if nr == r:
+                    g = local_grad.pop((node.mb, nc))
+                else:
+                    g = torch.empty_like(out)
+                    dist.recv(g, src=global_rank(nr), group=bwd_g)
+                torch.autograd.backward(out, g)
+            if split_w and node.kind == "B":
+                gemm_ops.WGRAD_STORE.end()
+            if s > 0:
+                x = inputs.pop(k)
+                pr, pc = sched.rank_of_stage(s - 1, pp, placement)
+                if pr == r:
+                    local_grad[(node.mb, node.chunk)] = x.grad
+                else:
+                    sends.append((dist.isend(x.grad, dst=global_rank(pr), group=bwd_g), x.grad))
+        elif node.kind == "W":
+            gemm_ops.WGRAD_STORE.flush(k)
+        if timeline is not None:
+            if trainer.is_cuda:
+                torch.cuda.synchronize()
+            timeline.add(node, t0, time.perf_counter())
+    for h, _keep in sends:
+        h.wait()
+    gemm_ops.WGRAD_STORE.flush_all()
+    for buf in trainer.buffers:
+        buf.is_last_microbatch = True
+    return total

@@ -40,6 +40,8 @@ class ParallelState:
     tp_group: Optional[object] = None
     cp_group: Optional[object] = None
     pp_group: Optional[object] = None
+    pp_fwd_group: Optional[object] = None  # forward-direction p2p communicator
+    pp_bwd_group: Optional[object] = None  # backward-direction p2p communicator
     dp_group: Optional[object] = None
     dp_cp_group: Optional[object] = None
     ep_group: Optional[object] = None
@@ -156,6 +158,8 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1
     st.dp_group, st.dp_ranks = make("dp")
     st.dp_cp_group, _ = make("dp_cp")
     st.pp_group, st.pp_ranks = make("pp")
+    st.pp_fwd_group, _ = make("pp")
+    st.pp_bwd_group, _ = make("pp")
     st.mp_group, _ = make("mp")
     st.ep_group, st.ep_ranks = make("ep")
     st.edp_group, edp_ranks = make("edp")

@@ -19,7 +19,8 @@ execute_hooks() {
   for f in "${files[@]}"; do
     LOG_DEBUG "hook: $f"
     local out rc
-    if [[ "$f" == *.py ]]; then out="$(python3 "$f" "$@")"; rc=$?; else out="$(bash "$f" "$@")"; rc=$?; fi
+    rc=0
+    if [[ "$f" == *.py ]]; then out="$(python3 "$f" "$@")" || rc=$?; else out="$(bash "$f" "$@")" || rc=$?; fi
     (( rc == 0 )) || die "hook $f failed with code $rc" 1
     local line
     while IFS= read -r line; do

@@ -1,0 +1,76 @@
+"""Rank functions for the multi-process CPU (gloo) tests; importable by spawned children."""
+import torch
+
+
+def tiny_cfgs(tp=1, pp=1, ep=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4):
+    from primus_b200.engine.trainer import TrainConfig
+    from primus_b200.models.config import TransformerConfig
+
+    kw = dict(num_layers=layers, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+              vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+              expert_model_parallel_size=ep, sequence_parallel=sp, make_vocab_size_divisible_by=64,
+              virtual_pipeline_model_parallel_size=vpp)
+    if moe:
+        kw.update(num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq=[0, 1] * (layers // 2),
+                  moe_aux_loss_coeff=1e-2)
+    mc = TransformerConfig(**kw)
+    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=iters, lr=1e-2,
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, pipeline_schedule=schedule,
+                     log_interval=1)
+    return mc, tc
+
+
+def full_reference_state(mc_kwargs, seed=7):
+    """State dict of the un-sharded single-process model (deterministic)."""
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    kw = dict(mc_kwargs)
+    kw.update(tensor_model_parallel_size=1, pipeline_model_parallel_size=1, expert_model_parallel_size=1,
+              sequence_parallel=False, virtual_pipeline_model_parallel_size=None)
+    torch.manual_seed(seed)
+    m = GPTModel(TransformerConfig(**kw), "cpu")
+    return {k: v.detach().clone() for k, v in m.state_dict().items()}
+
+
+def load_from_full(trainer, full_sd):
+    """Copy the matching slice of the full model into every parameter of this rank's chunks."""
+    from primus_b200.engine import checkpoint as C
+
+    st, cfg = trainer.st, trainer.mcfg
+    for m in trainer.model_chunks:
+        for name, p in m.named_parameters():
+            full = full_sd[name]
+            spec = C.shard_spec(name, p, cfg, st)
+            if spec["kind"] == "qkv":
+                # full tensor is [q | k | v]; shard every part separately
+                hq, hkv, d = cfg.num_attention_heads, cfg.num_query_groups, cfg.kv_channels
+                q, k, v = full[:hq * d], full[hq * d:(hq + hkv) * d], full[(hq + hkv) * d:]
+                n, i = spec["count"], spec["index"]
+                part = torch.cat([t.chunk(n, 0)[i] for t in (q, k, v)], 0)
+            else:
+                part = C.slice_global(name, full, spec)
+            p.data.copy_(part)
+    C._refresh_master_weights(trainer)
+
+
+def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
+    import json
+
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+
+    full_sd = full_reference_state(mc_kwargs_full)
+    ps.destroy_model_parallel()
+    mc, tc = tiny_cfgs(**kwargs)
+    ps.initialize_model_parallel(tp=mc.tensor_model_parallel_size, pp=mc.pipeline_model_parallel_size,
+                                 ep=mc.expert_model_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size)
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    load_from_full(tr, full_sd)
+    losses = tr.train()
+    if rank == 0:
+        with open(outq_path, "w") as f:
+            json.dump(losses, f)

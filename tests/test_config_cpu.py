@@ -1,0 +1,150 @@
+"""Config system: YAML env substitution and extends, presets, experiment resolution, CLI overrides, patches."""
+import os
+
+import pytest
+import yaml
+
+from primus_b200.core.config import experiment, overrides, presets, yaml_loader
+from primus_b200.core.config.merge import deep_merge, merge_without_override
+from primus_b200.core.patches import registry as R
+
+
+def test_env_substitution_and_coercion(tmp_path, monkeypatch):
+    p = tmp_path / "a.yaml"
+    p.write_text("a: ${PB_T_INT:7}\nb: ${PB_T_BOOL:false}\nc: pre-${PB_T_STR:x}-post\nd: ${PB_T_F:1.5}\ne: 12\n")
+    monkeypatch.setenv("PB_T_STR", "mid")
+    d = yaml_loader.load_yaml(p)
+    assert d == {"a": 7, "b": False, "c": "pre-mid-post", "d": 1.5, "e": 12}
+    monkeypatch.setenv("PB_T_INT", "9")
+    assert yaml_loader.load_yaml(p)["a"] == 9
+
+
+def test_required_env_raises(tmp_path):
+    p = tmp_path / "a.yaml"
+    p.write_text("a: ${PB_SURELY_UNSET_VAR}\n")
+    with pytest.raises(KeyError):
+        yaml_loader.load_yaml(p)
+
+
+def test_extends_chain_and_cycle(tmp_path):
+    (tmp_path / "base.yaml").write_text("x: 1\nnested: {a: 1, b: 2}\n")
+    (tmp_path / "mid.yaml").write_text("extends: base.yaml\ny: 2\nnested: {b: 3}\n")
+    (tmp_path / "top.yaml").write_text("extends: [mid.yaml]\nx: 5\n")
+    d = yaml_loader.load_yaml(tmp_path / "top.yaml")
+    assert d == {"x": 5, "y": 2, "nested": {"a": 1, "b": 3}}
+    (tmp_path / "c1.yaml").write_text("extends: c2.yaml\n")
+    (tmp_path / "c2.yaml").write_text("extends: c1.yaml\n")
+    with pytest.raises(ValueError):
+        yaml_loader.load_yaml(tmp_path / "c1.yaml")
+
+
+def test_merge_helpers():
+    assert deep_merge({"a": {"b": 1}}, {"a": {"c": 2}}) == {"a": {"b": 1, "c": 2}}
+    with pytest.raises(KeyError):
+        merge_without_override({"a": 1}, {"a": 2})
+
+
+def test_cli_overrides_forms():
+    o = overrides.parse_cli_overrides(["a=1", "--b=2.5", "--c", "hello", "--flag", "x.y.z=[1,2]", "--n", "none"])
+    assert o == {"a": 1, "b": 2.5, "c": "hello", "flag": True, "x": {"y": {"z": [1, 2]}}, "n": None}
+    with pytest.raises(ValueError):
+        overrides.parse_cli_overrides(["positional"])
+
+
+def test_preset_traversal_guard():
+    with pytest.raises((ValueError, FileNotFoundError)):
+        presets.preset_path("../../../etc/passwd", "models")
+    assert presets.load_preset("megatron/llama3.1_8B.yaml", "models", "megatron")["num_layers"] == 32
+
+
+def test_every_model_preset_builds_a_config():
+    from primus_b200.models.config import TransformerConfig
+
+    root = presets.CONFIG_ROOT / "models"
+    names = sorted(p.name for p in root.glob("*.yaml"))
+    assert len(names) >= 30
+    for n in names:
+        cfg = TransformerConfig.from_dict(presets.load_preset(n, "models"))
+        assert cfg.num_parameters() > 0, n
+    c8 = TransformerConfig.from_dict(presets.load_preset("llama3.1_8B", "models"))
+    assert abs(c8.num_parameters() / 1e9 - 8.03) < 0.02
+    lite = TransformerConfig.from_dict(presets.load_preset("deepseek_v2_lite", "models"))
+    assert 15.0 < lite.num_parameters() / 1e9 < 16.5 and lite.moe_layer_pattern[:2] == [0, 1]
+    q = TransformerConfig.from_dict(presets.load_preset("qwen3_30B_A3B", "models"))
+    assert 29.5 < q.num_parameters() / 1e9 < 31.5
+
+
+def test_experiment_resolution_and_alias(tmp_path, monkeypatch):
+    exp = tmp_path / "exp.yaml"
+    exp.write_text(yaml.safe_dump({
+        "work_group": "wg", "user_name": "u", "exp_name": "e", "workspace": str(tmp_path / "out"),
+        "env": {"PB_TEST_ENV_BLOCK": 3},
+        "modules": {"pre_trainer": {"framework": "megatron", "config": "pre_trainer.yaml", "model": "llama_tiny.yaml",
+                                    "overrides": {"train_iters": 3, "lr": 0.5}},
+                    "not_a_module": {"x": 1}}}))
+    e = experiment.load_experiment(str(exp), {"lr": 0.25, "seq_length": 64}, "pre_trainer")
+    m = e.module("pre_trainer")
+    assert m.params["train_iters"] == 3 and m.params["lr"] == 0.25 and m.params["seq_length"] == 64
+    assert m.params["num_layers"] == 4 and m.trainer_class == "PretrainTrainer"
+    assert e.module("post_trainer") is m  # alias
+    assert "not_a_module" not in e.modules
+    assert e.exp_root_path.endswith(os.path.join("out", "wg", "u", "e"))
+    experiment.apply_env_block(e)
+    assert os.environ["PB_TEST_ENV_BLOCK"] == "3"
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("work_group: x\n")
+    with pytest.raises(KeyError):
+        experiment.load_experiment(str(bad))
+
+
+def test_example_configs_all_load():
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "configs")
+    files = [f for f in os.listdir(root) if f.endswith(".yaml")]
+    assert files
+    for f in files:
+        e = experiment.load_experiment(os.path.join(root, f))
+        assert e.modules, f
+
+
+def test_patch_registry_phases_priority_selection(monkeypatch):
+    reg = R.PatchRegistry()
+    calls = []
+    R.register_patch("t.b", "build_args", priority=20, registry=reg)(lambda c: calls.append("b"))
+    R.register_patch("t.a", "build_args", priority=10, registry=reg)(lambda c: calls.append("a"))
+    R.register_patch("t.cond", "build_args", condition=lambda c: c.get_param("x") == 1, registry=reg)(
+        lambda c: calls.append("cond"))
+    R.register_patch("t.setup", "setup", registry=reg)(lambda c: calls.append("setup"))
+    ctx = R.PatchContext(phase="build_args", params={"x": 0})
+    assert R.run_patches("build_args", ctx, registry=reg) == ["t.a", "t.b"] and calls == ["a", "b"]
+    ctx.params["x"] = 1
+    assert "t.cond" in R.run_patches("build_args", ctx, registry=reg, dry_run=True)
+    monkeypatch.setenv("PRIMUS_PATCHES", "none")
+    assert R.run_patches("build_args", ctx, registry=reg) == []
+    monkeypatch.setenv("PRIMUS_PATCHES", "t.b")
+    assert R.run_patches("build_args", ctx, registry=reg) == ["t.b"]
+    with pytest.raises(ValueError):
+        reg.register(R.FunctionPatch("t.a", lambda c: None, "build_args"))
+    with pytest.raises(ValueError):
+        reg.register(R.FunctionPatch("t.z", lambda c: None, "nope"))
+
+
+def test_version_ranges():
+    assert R.version_in_range("0.12.1", ">=0.8,<0.13")
+    assert not R.version_in_range("0.13.0", ">=0.8,<0.13")
+    assert R.version_in_range("1.2.7", "==1.2.*") and not R.version_in_range("1.3.0", "==1.2.*")
+
+
+def test_builtin_build_args_patches(tmp_path):
+    from primus_b200.core.patches import builtin  # noqa: F401
+
+    params = {"mock_data": True, "vocab_size": None, "data_path": "a b", "num_experts": 4, "num_layers": 3,
+              "moe_layer_freq": "([0]*1+[1]*2)", "tensor_model_parallel_size": 1, "sequence_parallel": True,
+              "save_interval": 5, "save": None}
+    ctx = R.PatchContext(phase="build_args", params=params, extra={"exp_root_path": str(tmp_path)})
+    R.run_patches("build_args", ctx)
+    assert params["tokenizer_type"] == "NullTokenizer" and params["vocab_size"] == 131072
+    assert params["moe_layer_freq"] == [0, 1, 1] and params["sequence_parallel"] is False
+    assert params["save"].endswith("checkpoints")
+    bad = R.PatchContext(phase="build_args", params={"use_turbo_mega_moe": True, "expert_model_parallel_size": 16})
+    with pytest.raises(ValueError):
+        R.run_patches("build_args", bad)

@@ -1,0 +1,57 @@
+"""Multi-process CPU (gloo) plumbing: DP with the distributed optimizer, TP (+SP), PP schedules and EP must
+reproduce the single-process loss trajectory from identical initial weights and the same global batches."""
+import dataclasses
+import json
+
+import pytest
+import torch
+
+from tests import dist_workers as W
+from tests.mp_utils import run_ranks
+
+
+def _single(kwargs):
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+
+    mc, tc = W.tiny_cfgs(**{**kwargs, "tp": 1, "pp": 1, "ep": 1, "sp": False, "vpp": None, "schedule": "1f1b"})
+    mck = _mc_kwargs(mc)
+    full = W.full_reference_state(mck)
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    W.load_from_full(tr, full)
+    out = tr.train()
+    ps.destroy_model_parallel()
+    return out, mck
+
+
+def _mc_kwargs(mc):
+    d = {f.name: getattr(mc, f.name) for f in dataclasses.fields(mc)}
+    return d
+
+
+CASES = {
+    "dp2": dict(world=2, kw=dict()),
+    "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
+    "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
+    "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
+    "pp2_interleaved": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved")),
+    "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
+    "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
+    "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),
+    "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_parallel_matches_single_process(name, tmp_path):
+    case = CASES[name]
+    kw = dict(seq=32, gbs=8, mbs=2, iters=3, layers=4, **case["kw"])
+    ref, mck = _single(kw)
+    out = tmp_path / "losses.json"
+    run_ranks(W.train_worker, case["world"], "gloo", args=(kw, mck, str(out)), timeout=240)
+    got = json.loads(out.read_text())
+    assert len(got) == len(ref)
+    for a, b in zip(got, ref):
+        assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), f"{name}: {got} vs {ref}"

@@ -338,7 +338,7 @@ class Trainer:
     def save_checkpoint(self, path: Optional[str] = None):
         from . import checkpoint
 
-        checkpoint.save_checkpoint(self, path or self.tcfg.save)
+        return checkpoint.save_checkpoint(self, path or self.tcfg.save)
 
     def load_checkpoint(self, path: Optional[str] = None) -> int:
         from . import checkpoint

@@ -104,6 +104,9 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); dp = gpus / tp")
+    ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
+    ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -130,13 +133,18 @@ def main() -> int:
     mdict = dict(MODELS[args.model])
     if args.layers:
         mdict["num_layers"] = args.layers
-    mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq)
-    gbs = args.batch_per_gpu * world
+    mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
+                             sequence_parallel=args.tp > 1)
+    if args.fused_tp:
+        from primus_b200.parallel import fused_tp
+
+        fused_tp.ENABLED = True
+    gbs = args.batch_per_gpu * world // args.tp
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,
                        clip_grad=1.0, use_distributed_optimizer=True, overlap_grad_reduce=world > 1,
-                       log_interval=10 ** 9, manual_gc=True)
-    ps.initialize_model_parallel(tp=1, pp=1)
+                       log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp)
+    ps.initialize_model_parallel(tp=args.tp, pp=1)
     trainer = Trainer(mcfg, tcfg, device=f"cuda:{local_rank}", log_fn=lambda s: None)
 
     def barrier():
@@ -202,7 +210,7 @@ def main() -> int:
             "vs_baseline": value / (BASELINE_TOK_S_GPU * world) if args.model == "llama3.1_8B" else None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
             "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
-                       "micro_batch": args.micro_batch, "parallelism": f"dp{world}",
+                       "micro_batch": args.micro_batch, "parallelism": f"dp{world // args.tp}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},
             "tokens_per_s_per_gpu": value / world,

@@ -67,6 +67,13 @@ class TrainConfig:
     save_interval: Optional[int] = None
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    exit_signal_handler: bool = False
+    check_for_spiky_loss: bool = False
+    check_for_large_grads: bool = False
+    rerun_mode: str = "disabled"
+    error_injection_rate: float = 0.0
+    error_injection_type: str = "transient_error"
+    log_straggler: bool = False
     eval_interval: Optional[int] = None
     eval_iters: int = 0
     pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv | v-half | v-min
@@ -160,7 +167,8 @@ class Trainer:
             self.buffers.append(ParamGradBuffer(
                 dense, st.dp_cp_group if st.cp > 1 else st.dp_group, st.dp * st.cp, st.dp_rank * st.cp + st.cp_rank,
                 train_cfg.ddp_bucket_size, torch.float32, train_cfg.use_distributed_optimizer,
-                train_cfg.overlap_grad_reduce, True, self.comm_stream))
+                train_cfg.overlap_grad_reduce, True, self.comm_stream,
+                symmetric=train_cfg.fused_dp_optimizer and train_cfg.use_distributed_optimizer))
         if expert:
             self.buffers.append(ParamGradBuffer(
                 expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
@@ -290,7 +298,12 @@ class Trainer:
         if tc.manual_gc and not self._gc_disabled:
             gc.disable()  # the reference disables Python GC around trainer.train()
             self._gc_disabled = True
+        from . import fault
+
         start_wall = time.time()
+        guard = fault.LossGuard(tc.check_for_nan_in_loss_and_grad, tc.check_for_spiky_loss, 10.0, tc.check_for_large_grads)
+        exit_flag = fault.GracefulExit() if tc.exit_signal_handler else None
+        straggler = fault.StragglerDetector() if tc.log_straggler else None
         try:
             for _ in range(n):
                 t0 = time.perf_counter()
@@ -300,17 +313,33 @@ class Trainer:
                     dt = time.perf_counter() - t0
                     losses.append(lv)
                     self._log_step(lv, dt)
-                    if tc.check_for_nan_in_loss_and_grad and not math.isfinite(lv):
-                        raise FloatingPointError(f"non-finite loss at iteration {self.iteration}: {lv}")
+                    problem = guard.check(lv, float(self.optimizer.grad_norm.item()))
+                    if problem and not math.isfinite(lv):
+                        raise FloatingPointError(f"iteration {self.iteration}: {problem}")
+                    if problem:
+                        self.log(f"[guard] iteration {self.iteration}: {problem}")
+                    if straggler is not None:
+                        straggler.record(dt)
+                        if self.iteration % max(tc.log_interval * 10, 10) == 0:
+                            rep = straggler.report()
+                            if rep.get("stragglers"):
+                                self.log(f"[straggler] slow ranks {rep['stragglers']} (median {rep['median_s']:.3f} s)")
                     if on_step is not None:
                         on_step(self, lv)
                 if tc.save and tc.save_interval and self.iteration % tc.save_interval == 0:
                     self.save_checkpoint()
+                if exit_flag is not None and exit_flag.requested:
+                    self.log(f"signal {exit_flag.signum} received: checkpointing at iteration {self.iteration} and leaving")
+                    if tc.save:
+                        self.save_checkpoint()
+                    break
                 if tc.exit_interval and self.iteration % tc.exit_interval == 0:
                     break
                 if tc.exit_duration_in_mins and (time.time() - start_wall) / 60.0 > tc.exit_duration_in_mins:
                     break
         finally:
+            if exit_flag is not None:
+                exit_flag.restore()
             if self._gc_disabled:
                 gc.enable()
                 self._gc_disabled = False

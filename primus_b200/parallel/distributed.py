@@ -45,7 +45,7 @@ class Bucket:
 class ParamGradBuffer:
     def __init__(self, params: list[torch.nn.Parameter], dp_group, dp_size: int, dp_rank: int,
                  bucket_size: Optional[int] = None, grad_dtype=torch.float32, use_distributed_optimizer=True,
-                 overlap_grad_reduce=False, average_in_collective=True, comm_stream=None):
+                 overlap_grad_reduce=False, average_in_collective=True, comm_stream=None, symmetric=False):
         assert params, "empty parameter list"
         self.params = params
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
@@ -78,8 +78,19 @@ class ParamGradBuffer:
             buckets.append(Bucket(len(buckets), cur_start, cur, cur_params))
         self.numel = cur
         self.buckets = buckets
-        self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=device)
-        self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=device)
+        self.symmetric = bool(symmetric and dp_size > 1 and device.type == "cuda" and self.param_dtype == torch.bfloat16)
+        if self.symmetric:
+            # peer-mapped buffers: the fused optimizer kernels read peers' gradients and write peers' parameters
+            from .symm_mem import SymmetricBuffer
+
+            self.sym_param = SymmetricBuffer(self.numel * 2, dp_group, device)
+            self.sym_grad = SymmetricBuffer(self.numel * 4, dp_group, device)
+            self.param_data = self.sym_param.local(torch.bfloat16, self.numel)
+            self.grad_data = self.sym_grad.local(torch.float32, self.numel)
+            self.overlap_grad_reduce = False
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=device)
+            self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=device)
         self.param_offsets = offsets
         self.param_to_bucket = {}
         for b in buckets:
@@ -152,7 +163,7 @@ class ParamGradBuffer:
 
     def finish_grad_sync(self):
         """Reduce every bucket that has not been started and wait for all of them."""
-        if self.dp_size == 1:
+        if self.dp_size == 1 or self.symmetric:  # symmetric buffers: the fused optimizer kernels do the reduction
             return
         for b in self.buckets:
             if b.rs_handle is None:
@@ -219,7 +230,9 @@ class DistributedOptimizer:
         items = sorted(((buf.param_offsets[p], p) for p in b.params), key=lambda t: t[0])
         pos = s
         for o, p in items:
-            lo, hi = max(o, s), min(o + p.numel(), e)
+            # ends are rounded up to 4 elements (the gap up to the next parameter is zero padding) so that
+            # every range can be processed with 16-byte accesses
+            lo, hi = max(o, s), min(-(-(o + p.numel()) // 4) * 4, e)
             if lo >= hi:
                 continue
             if lo > pos:
@@ -254,10 +267,70 @@ class DistributedOptimizer:
         optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
         return self.grad_norm
 
+    def _fused_step(self, lr: float, wd: float):
+        """Reduce-scatter, clip and AdamW + all-gather through peer memory (``csrc/dp_fused.cu``)."""
+        import ctypes
+
+        from ..ops import _lib
+        from ..ops.fused import scratch
+
+        self.sumsq.zero_()
+        self.skip.zero_()
+        P = _lib.call_ret("dp_num_partials")
+        for buf in self.buffers:
+            if buf.symmetric:
+                buf.sym_grad.barrier(0)  # every rank's gradients are final
+        for st in self.state:
+            buf = st["buf"]
+            if not buf.symmetric:
+                optim_ops.sumsq_(buf.grad_data[st["s"]:st["e"]], self.sumsq, accumulate=True)
+                continue
+            tbl = (ctypes.c_long * buf.dp_size)(*[buf.sym_grad.peer_ptr(r) for r in range(buf.dp_size)])
+            n = st["e"] - st["s"]
+            _lib.call("dp_reduce_scatter", tbl, buf.dp_size, buf.dp_rank, st["s"], n, buf.grad_data[st["s"]:st["e"]],
+                      1.0 / buf.dp_size, scratch(buf.device, "dp_partials", P), self.sumsq, 1)
+        for buf in self.buffers:
+            if buf.symmetric:
+                buf.sym_grad.barrier(1)  # everybody has read this rank's gradients: they may be zeroed again
+        dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
+        for g in self.norm_groups:
+            dist.all_reduce(self.sumsq, group=g)
+        if self.check_for_nan:
+            self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
+        optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
+        bc1 = 1.0 - self.betas[0] ** self.step_count
+        bc2 = 1.0 - self.betas[1] ** self.step_count
+        for st in self.state:
+            buf = st["buf"]
+            tbl = (ctypes.c_long * buf.dp_size)(*[buf.sym_param.peer_ptr(r) for r in range(buf.dp_size)]) \
+                if buf.symmetric else None
+            for lo, hi, mult in st["wd_ranges"]:
+                hi4 = min(-(-hi // 4) * 4, st["e"])  # ranges end on parameter boundaries; padding follows
+                a, b_ = lo - st["s"], hi4 - st["s"]
+                if buf.symmetric:
+                    _lib.call("dp_adamw_allgather", tbl, buf.dp_size, buf.dp_rank, lo, hi4 - lo, st["master"][a:b_],
+                              st["m"][a:b_], st["v"][a:b_], buf.grad_data[lo:hi4], float(lr), float(self.betas[0]),
+                              float(self.betas[1]), float(self.eps), float(wd * mult), float(bc1), float(bc2),
+                              self.coef, self.skip)
+                else:
+                    optim_ops.adamw_step_(st["master"][a:b_], st["m"][a:b_], st["v"][a:b_], buf.grad_data[lo:hi4],
+                                          buf.param_data[lo:hi4], lr=lr, beta1=self.betas[0], beta2=self.betas[1],
+                                          eps=self.eps, weight_decay=wd * mult, step=self.step_count,
+                                          grad_scale=self.coef, skip=self.skip)
+        for buf in self.buffers:
+            if buf.symmetric:
+                buf.sym_param.barrier(0)  # all parameter shards have landed everywhere
+            else:
+                buf.start_param_sync(async_op=False)
+                buf.finish_param_sync()
+        return self.grad_norm
+
     def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None):
         lr = self.lr if lr is None else lr
         wd = self.weight_decay if weight_decay is None else weight_decay
         self.step_count += 1
+        if any(buf.symmetric for buf in self.buffers):
+            return self._fused_step(lr, wd)
         self.compute_grad_norm()
         for st in self.state:
             buf = st["buf"]

@@ -1,0 +1,42 @@
+"""Fused data-parallel optimizer (P2P reduce-scatter + AdamW + all-gather through symmetric memory) must follow
+the NCCL path step for step (2 GPUs)."""
+import json
+
+import pytest
+import torch
+
+from tests.mp_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, fused, outp):
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import _lib
+    from primus_b200.parallel import state as ps
+
+    ps.initialize_model_parallel()
+    cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1408, num_attention_heads=4,
+                            num_query_groups=2, kv_channels=128, vocab_size=8192, params_dtype="bf16")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=256, train_iters=4, lr=1e-3,
+                     lr_decay_style="constant", fused_dp_optimizer=fused, ddp_bucket_size=1_000_000)
+    tr = Trainer(cfg, tc, device=f"cuda:{rank}", log_fn=lambda s: None)
+    losses = tr.train(4)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    checksum = float(sum(p.float().abs().sum() for p in tr.model.parameters()))
+    if rank == 0:
+        json.dump({"losses": losses, "checksum": checksum, "symmetric": bool(tr.buffers[0].symmetric)}, open(outp, "w"))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_dp_optimizer_matches_nccl(tmp_path):
+    a, b = str(tmp_path / "nccl.json"), str(tmp_path / "fused.json")
+    run_ranks(_worker, 2, "nccl", args=(False, a), timeout=240)
+    run_ranks(_worker, 2, "nccl", args=(True, b), timeout=240)
+    ra, rb = json.load(open(a)), json.load(open(b))
+    assert rb["symmetric"] and not ra["symmetric"]
+    for x, y in zip(ra["losses"], rb["losses"]):
+        assert abs(x - y) <= 2e-3 * max(1.0, abs(x)), (ra, rb)
+    assert abs(ra["checksum"] - rb["checksum"]) <= 1e-3 * ra["checksum"]

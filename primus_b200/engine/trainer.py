@@ -217,7 +217,8 @@ class Trainer:
             for buf in self.buffers:
                 buf.is_last_microbatch = last
             w = self._loss_weights(mb)
-            loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True)
+            loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True,
+                         position_ids=mb.get("position_ids") if getattr(self, "use_position_ids", False) else None)
             loss.backward()
             total += loss.detach()
         return total
@@ -275,7 +276,11 @@ class Trainer:
         self._pre_sync_sp_norm_grads()
         self.finalize_grads()
         lr = self.scheduler.get_lr(self.iteration + 1)
-        self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+        if getattr(self, "lora", None) is not None:  # adapter-only training: base weights stay frozen
+            self.optimizer.compute_grad_norm()
+            self.lora.optimizer_step(lr)
+        else:
+            self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
         self.scheduler.step()
         self.iteration += 1
         return loss

@@ -1,0 +1,109 @@
+"""SFT: formatters, answer-only masks, packing invariants, LoRA adapter training (base weights frozen, merge)."""
+import json
+
+import torch
+
+from primus_b200.engine import sft as S
+
+
+def test_formatters():
+    p, a = S.format_alpaca({"instruction": "Add", "input": "1 2", "output": "3"})
+    assert "### Input:\n1 2" in p and a == "3"
+    p, a = S.format_alpaca({"instruction": "Say hi", "output": "hi"})
+    assert "### Input" not in p
+    p, a = S.format_squad({"context": "C", "question": "Q", "answers": {"text": ["A"]}})
+    assert p.endswith("Answer:") and a == " A"
+    p, a = S.FORMATTERS["chatml"]({"messages": [{"role": "user", "content": "u"}, {"role": "assistant", "content": "v"}]})
+    assert p == "<|im_start|>user\nu<|im_end|>\n<|im_start|>assistant\n" and a == "v<|im_end|>\n"
+    p, a = S.FORMATTERS["openai"]({"conversations": [{"from": "human", "value": "u"}, {"from": "gpt", "value": "v"}]})
+    assert p == "user: u\nassistant: " and a == "v"
+
+
+def _records(n=40):
+    return [{"instruction": "repeat " + "x" * (i % 17), "output": "y" * (1 + i % 23)} for i in range(n)]
+
+
+def test_answer_only_loss_mask_and_padding():
+    ds = S.SFTDataset(_records(4), S.ByteTokenizer(), 512, "alpaca", True)
+    it = ds[0]
+    assert it["tokens"].shape == (512,) and it["loss_mask"].sum() > 0
+    n_prompt = len(S.ByteTokenizer().encode(S.format_alpaca(_records(1)[0])[0]))
+    assert it["loss_mask"][: n_prompt - 1].sum() == 0          # no loss on the prompt
+    assert it["loss_mask"][n_prompt - 1] == 1                   # first answer token is predicted from the last prompt token
+    full = S.SFTDataset(_records(4), S.ByteTokenizer(), 512, "alpaca", False)[0]
+    assert full["loss_mask"].sum() > it["loss_mask"].sum()
+
+
+def test_packing_invariants():
+    lengths = [5, 300, 200, 512, 17, 100, 250, 250, 9]
+    for algo in ("first_fit", "first_fit_decreasing", "first_fit_shuffle"):
+        bins = S.pack_bins(lengths, 512, algo, seed=3)
+        assert sorted(i for b in bins for i in b) == list(range(len(lengths)))
+        assert all(sum(lengths[i] for i in b) <= 512 for b in bins)
+    assert len(S.pack_bins(lengths, 512, "first_fit_decreasing")) <= len(S.pack_bins(lengths, 512, "first_fit"))
+    ds = S.SFTDataset(_records(), S.ByteTokenizer(), 512, "alpaca", True)
+    pk = S.PackedSFTDataset(ds)
+    assert len(pk) < len(ds) and pk.packing_efficiency() > 0.5
+    it = pk[0]
+    starts = (it["position_ids"] == 0).nonzero().flatten()
+    assert len(starts) >= 2                                     # several samples, positions restart
+
+
+def test_lora_trains_adapters_only(tmp_path):
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=6)
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    tr.lora = S.LoRAEngine(tr.model_chunks, rank=4, alpha=8.0, lr=5e-2)
+    h = tr.lora.holders[0]
+    base = h.base_weight.clone()
+    emb = tr.model.embedding.word_embeddings.weight.detach().clone()
+    losses = tr.train(6)
+    assert torch.equal(h.base_weight, base)                               # frozen
+    assert torch.equal(tr.model.embedding.word_embeddings.weight, emb)    # non-adapted parameters untouched
+    assert h.lora.lora_b.abs().sum() > 0                                  # adapters moved
+    assert not torch.equal(h.weight.detach(), base)                       # effective weight = base + BA
+    assert torch.allclose(h.weight.detach(), base + h.lora.delta(), atol=1e-5)
+    n = S.merge_lora(tr.model)
+    assert n == len(tr.lora.holders) and not hasattr(h, "lora")
+    assert any(".lora." in k for k in []) is False and len(losses) == 6
+
+
+def test_sft_trainer_through_cli(tmp_path):
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    data = tmp_path / "sft.jsonl"
+    data.write_text("\n".join(json.dumps(r) for r in _records(16)))
+    exp = tmp_path / "exp.yaml"
+    exp.write_text(f"""
+work_group: t
+user_name: u
+exp_name: sft
+workspace: {tmp_path}/out
+modules:
+  post_trainer:
+    config: sft_trainer.yaml
+    model: llama_tiny.yaml
+    overrides:
+      train_iters: 2
+      micro_batch_size: 2
+      global_batch_size: 4
+      seq_length: 128
+      vocab_size: 512
+      params_dtype: fp32
+      sft_dataset_name: {data}
+      sft_packing: true
+      peft: lora
+      lora_rank: 4
+""")
+    r = subprocess.run([sys.executable, "-m", "primus_b200.cli.main", "train", "posttrain", "--config", str(exp)],
+                       capture_output=True, text=True, cwd=root, env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "Training completed." in r.stderr

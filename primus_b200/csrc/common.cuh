@@ -25,6 +25,7 @@ enum PbStatus : int {
   PB_ERR_TIMEOUT_EPILOGUE = 3, // epilogue waited too long for an accumulator
   PB_ERR_TIMEOUT_FLAG = 4,     // wait on a global-memory flag (peer signal) ran out
   PB_ERR_BAD_ARG = 5,
+  PB_ERR_CAPACITY = 6,         // routed rows exceed the capacity of the expert-parallel buffers
 };
 
 #define PB_DEVICE __device__ __forceinline__

@@ -64,6 +64,7 @@ class TransformerConfig:
     moe_token_dispatcher_type: str = "alltoall"  # alltoall | allgather | mega
     moe_grouped_gemm: bool = True
     use_turbo_mega_moe: bool = False
+    moe_fused_capacity_factor: Optional[float] = None   # rows per rank = factor x T x k (None: worst case ep x T x k)
     # parallelism (sizes; groups live in primus_b200.parallel.state)
     tensor_model_parallel_size: int = 1
     sequence_parallel: bool = False

@@ -109,7 +109,9 @@ class MoELayer(nn.Module):
         flat_e = idx.reshape(-1)
         counts_global = torch.bincount(flat_e, minlength=cfg.num_experts)
         self.last_tokens_per_expert = counts_global
-        if self.ep == 1:
+        if cfg.use_turbo_mega_moe and y.is_cuda:
+            out = self._forward_fused(y, probs, idx, T, k)
+        elif self.ep == 1:
             out = self._forward_local(y, probs, flat_e, counts_global, T, k)
         else:
             out = self._forward_ep(y, probs, flat_e, counts_global, T, k)
@@ -129,6 +131,20 @@ class MoELayer(nn.Module):
         probs_perm = pf[src.long()]  # src = -1 picks the appended zero
         out_perm = self.experts_forward(x_perm, probs_perm, sched)
         return moe_ops.combine_rows(out_perm, inv_pos, src_token)
+
+    # ------------------------------------------------------------------ fused dispatch / combine (symmetric memory)
+    def _forward_fused(self, y, probs, idx, T, k):
+        """Dispatch and combine fused into the expert GEMMs; no host synchronisation on the routing result."""
+        from ..parallel import fused_ep
+
+        cfg = self.cfg
+        st = ps.get_state()
+        ws = fused_ep.get_workspace(st.ep_group if self.ep > 1 else None, T, k, cfg.num_experts, cfg.hidden_size,
+                                    cfg.moe_fused_capacity_factor)
+        plan = ws.plan(idx, probs)
+        h1, probs_perm = fused_ep.dispatch_gemm1(y, probs, self.experts.fc1_weight.weight, ws, plan)
+        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value)
+        return fused_ep.gemm2_combine(act, self.experts.fc2_weight.weight, ws, plan)
 
     # ------------------------------------------------------------------ expert parallel (NCCL all-to-all)
     def _forward_ep(self, y, probs, flat_e, counts_global, T, k):

@@ -114,6 +114,7 @@ STATUS_MESSAGES = {
     3: "epilogue timed out waiting for an accumulator",
     4: "timed out waiting for a peer flag in global memory",
     5: "bad argument detected on the device",
+    6: "routed rows exceed the capacity of the expert-parallel buffers (raise moe_fused_capacity_factor)",
 }
 
 

@@ -26,10 +26,64 @@ BLOCK_ROWS = 128
 
 # ----------------------------------------------------------------------------------------------
 # Router
+class RouterFn(torch.autograd.Function):
+    """Fused router (``csrc/router.cu``): logits [T, E] -> (probs [T, k] fp32, idx [T, k] int64, full [T, E] fp32,
+    counts [E] int32)."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, topk, sigmoid, pre_softmax, num_groups, group_topk, scale):
+        T, E = logits.shape
+        dev = logits.device
+        lg = logits.contiguous()
+        if lg.dtype not in (torch.bfloat16, torch.float32):
+            lg = lg.float()
+        probs = torch.empty(T, topk, dtype=torch.float32, device=dev)
+        idx = torch.empty(T, topk, dtype=torch.int32, device=dev)
+        full = torch.empty(T, E, dtype=torch.float32, device=dev)
+        counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        b = bias.float().contiguous() if bias is not None else None
+        _lib.call("router_fwd", lg, int(lg.dtype == torch.bfloat16), b, T, E, topk, int(sigmoid), int(pre_softmax),
+                  int(num_groups or 0), int(group_topk or 0), float(scale), probs, idx, full, counts)
+        ctx.save_for_backward(full, idx, probs)
+        ctx.cfg = (topk, int(sigmoid), int(pre_softmax), float(scale), logits.dtype)
+        idx64 = idx.long()
+        ctx.mark_non_differentiable(idx64, counts)
+        return probs, idx64, full, counts
+
+    @staticmethod
+    def backward(ctx, dprobs, _didx, dfull, _dcounts):
+        full, idx, probs = ctx.saved_tensors
+        topk, sigmoid, pre_softmax, scale, dt = ctx.cfg
+        T, E = full.shape
+        dlogits = torch.empty(T, E, dtype=torch.float32, device=full.device)
+        dp = dprobs.float().contiguous() if dprobs is not None else torch.zeros_like(probs)
+        df = dfull.float().contiguous() if dfull is not None else None
+        _lib.call("router_bwd", dp, df, full, idx, probs, T, E, topk, sigmoid, pre_softmax, scale, dlogits)
+        return dlogits.to(dt), None, None, None, None, None, None, None
+
+
 def router_scores(logits: torch.Tensor, topk: int, score_function: str = "softmax", pre_softmax: bool = False,
                   expert_bias: Optional[torch.Tensor] = None, scaling_factor: Optional[float] = None,
-                  num_groups: Optional[int] = None, group_topk: Optional[int] = None):
-    """Returns (probs [T, k] fp32, idx [T, k] int64, full scores [T, E] fp32 used by the aux losses)."""
+                  num_groups: Optional[int] = None, group_topk: Optional[int] = None, return_counts: bool = False):
+    """Returns (probs [T, k] fp32, idx [T, k] int64, full scores [T, E] fp32 used by the aux losses) and, with
+    ``return_counts``, the per-expert token counts (int32 [E])."""
+    if score_function not in ("softmax", "sigmoid"):
+        raise ValueError(f"unknown moe_router_score_function {score_function!r}")
+    if logits.is_cuda and logits.shape[1] <= 1024 and topk <= 32:
+        probs, idx, full, counts = RouterFn.apply(logits, expert_bias, topk, score_function == "sigmoid", pre_softmax,
+                                                  num_groups, group_topk, scaling_factor or 1.0)
+        return (probs, idx, full, counts) if return_counts else (probs, idx, full)
+    out = router_scores_ref(logits, topk, score_function, pre_softmax, expert_bias, scaling_factor, num_groups,
+                            group_topk)
+    if return_counts:
+        return (*out, torch.bincount(out[1].reshape(-1), minlength=logits.shape[1]).to(torch.int32))
+    return out
+
+
+def router_scores_ref(logits: torch.Tensor, topk: int, score_function: str = "softmax", pre_softmax: bool = False,
+                      expert_bias: Optional[torch.Tensor] = None, scaling_factor: Optional[float] = None,
+                      num_groups: Optional[int] = None, group_topk: Optional[int] = None):
+    """Plain PyTorch router (CPU path and numerics oracle of the fused kernel)."""
     lf = logits.float()
     T, E = lf.shape
 
@@ -222,6 +276,22 @@ def _grouped_ref(x, w, sched: Schedule, trans_w: bool):
     return out
 
 
+def grouped_wgrad(dy, x, w, sched: Schedule):
+    """dW[e] = dy_e^T x_e over the rows of expert e.  Accumulates into ``w.main_grad`` (fp32) when the parameter
+    has one (returns None and fires the bucket callback), else returns the gradient in ``w.dtype``."""
+    E, N, K = w.shape
+    mg = getattr(w, "main_grad", None)
+    tgt = mg if mg is not None else torch.empty(E, N, K, dtype=torch.float32, device=x.device)
+    _lib.call("grouped_gemm", 2, dy, x, tgt, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
+              sched.padded, int(mg is not None), _lib.status_word(x.device))
+    if mg is None:
+        return tgt.to(w.dtype)
+    cb = getattr(w, "_grad_ready_cb", None)
+    if cb is not None:
+        cb(w)
+    return None
+
+
 class GroupedLinearFn(torch.autograd.Function):
     """y[rows of e] = x[rows of e] @ w[e]^T with w [E, N, K]; dW accumulates into ``w.main_grad`` when present."""
 
@@ -247,18 +317,7 @@ class GroupedLinearFn(torch.autograd.Function):
             dx = torch.empty_like(x)
             _lib.call("grouped_gemm", 1, dy, w, dx, x.shape[0], K, N, E, sched.mblock_expert, sched.row_start,
                       sched.padded, 0, _lib.status_word(x.device))
-        dw = None
-        if ctx.needs_input_grad[1]:
-            mg = getattr(ctx.w_ref, "main_grad", None)
-            tgt = mg if mg is not None else torch.empty(E, N, K, dtype=torch.float32, device=x.device)
-            _lib.call("grouped_gemm", 2, dy, x, tgt, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
-                      sched.padded, int(mg is not None), _lib.status_word(x.device))
-            if mg is None:
-                dw = tgt.to(w.dtype)
-            else:
-                cb = getattr(ctx.w_ref, "_grad_ready_cb", None)
-                if cb is not None:
-                    cb(ctx.w_ref)
+        dw = grouped_wgrad(dy, x, ctx.w_ref, sched) if ctx.needs_input_grad[1] else None
         return dx, dw, None
 
 

@@ -95,3 +95,33 @@ def test_moe_mla_model_step_matches_cpu_reference():
         a = g[name].grad.float().cpu()
         err = (a - p.grad).abs().max().item()
         assert err <= 0.1 * p.grad.abs().max().item() + 2e-3, f"{name}: {err}"
+
+
+@pytest.mark.parametrize("score,pre,groups,bias,scale,E,k", [
+    ("softmax", False, None, False, None, 64, 6),
+    ("softmax", True, None, False, 2.5, 8, 2),
+    ("sigmoid", False, (8, 3), True, 2.5, 256, 8),
+    ("sigmoid", False, None, False, None, 16, 1),
+    ("softmax", True, (4, 2), False, None, 160, 6),
+])
+def test_fused_router_matches_reference(score, pre, groups, bias, scale, E, k):
+    T = 333
+    torch.manual_seed(5)
+    logits = (torch.randn(T, E, device="cuda") * 2).bfloat16().requires_grad_()
+    eb = torch.randn(E, device="cuda") * 0.1 if bias else None
+    ng, gk = groups if groups else (None, None)
+    ref_in = logits.detach().clone().requires_grad_()
+    p_ref, i_ref, f_ref = M.router_scores_ref(ref_in, k, score, pre, eb, scale, ng, gk)
+    p, i, f, counts = M.router_scores(logits, k, score, pre, eb, scale, ng, gk, return_counts=True)
+    torch.cuda.synchronize()
+    assert torch.equal(i.sort(-1).values, i_ref.sort(-1).values)
+    order, order_ref = i.argsort(-1), i_ref.argsort(-1)
+    assert torch.allclose(p.gather(1, order), p_ref.gather(1, order_ref), rtol=1e-4, atol=1e-6)
+    assert torch.allclose(f, f_ref, rtol=1e-4, atol=1e-6)
+    assert torch.equal(counts.long(), torch.bincount(i_ref.reshape(-1), minlength=E))
+    wp = torch.randn(T, k, device="cuda")
+    wf = torch.randn(T, E, device="cuda")
+    (p.gather(1, order) * wp).sum().add((f * wf).sum()).backward()
+    (p_ref.gather(1, order_ref) * wp).sum().add((f_ref * wf).sum()).backward()
+    err = (logits.grad.float() - ref_in.grad.float()).abs().max().item()
+    assert err <= 2e-2 * ref_in.grad.float().abs().max().item() + 1e-5, err

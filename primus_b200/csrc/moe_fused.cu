@@ -47,7 +47,9 @@ constexpr int MAX_EP = 8;
 constexpr int RING_BYTES = STAGES * STAGE_BYTES;   // 192 KiB
 constexpr int ZERO_BYTES = 16384;                  // largest supported row (8192 bf16)
 constexpr int MAX_SLOTS = 48;
-constexpr int STORE_LAG = 4;
+constexpr int READ_LAG = 4;        // bulk stores that may still be reading their ring slot
+constexpr int PUBLISH_LAG = 12;    // stores between the last row of a chunk and its publication
+constexpr int MAX_WORKERS = 4;     // copy workers (elected threads with a private ring slice) per communication CTA
 constexpr int CHUNK_ROWS = 128;
 
 struct MoeArgs {
@@ -114,22 +116,121 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
                : "memory");
 }
 
-// Walks the chunks cta, cta + comm_ctas, ... of the copy list, skipping chunks of unused row blocks.
+// Walks the chunks first, first + stride, ... of the copy list, skipping chunks of unused row blocks.
 struct RowCursor {
   int chunk, row, end;  // current chunk, current list index, one past the chunk's last index
+  int stride;
   bool valid;
 };
 __device__ __forceinline__ void cursor_seek(const MoeArgs& a, RowCursor& c) {
   const int chunks = (a.list_len + CHUNK_ROWS - 1) / CHUNK_ROWS;
-  while (c.chunk < chunks && a.gather && a.mblock_expert[c.chunk] < 0) c.chunk += a.comm_ctas;
+  while (c.chunk < chunks && a.gather && a.mblock_expert[c.chunk] < 0) c.chunk += c.stride;
   c.valid = c.chunk < chunks;
   c.row = c.chunk * CHUNK_ROWS;
   c.end = min(c.row + CHUNK_ROWS, a.list_len);
 }
 __device__ __forceinline__ void cursor_next(const MoeArgs& a, RowCursor& c) {
   if (++c.row < c.end) return;
-  c.chunk += a.comm_ctas;
+  c.chunk += c.stride;
   cursor_seek(a, c);
+}
+
+// One copy worker = one elected thread with a private slice of the ring.  `worker` / `num_workers` number the
+// workers of the whole grid; chunk c of the list is handled by worker c % num_workers, so chunks are started
+// in list order across the grid.
+__device__ void copy_worker(const MoeArgs& a, uint8_t* ring, int nslot, int slot_bytes, uint64_t* bars,
+                            const uint8_t* zero, int worker, int num_workers) {
+  RowCursor ic{worker, 0, 0, num_workers, false}, rc{worker, 0, 0, num_workers, false};
+  cursor_seek(a, ic);
+  cursor_seek(a, rc);
+  long issued = 0, retired = 0;
+  uint64_t phase_mask = 0;
+  int ready_key = -1;          // (peer, row block) whose flag was seen last
+  bool ok = true;
+  // chunks whose last store has been committed but not yet published: (chunk, index of that store)
+  int pend_chunk[4];
+  long pend_q[4];
+  int pend_n = 0;
+
+  auto issue_one = [&]() {
+    const int s = a.list_src[ic.row];
+    if (s >= 0) {
+      const int p = s >> 24, row = s & 0xffffff;
+      if (!a.gather) {
+        const int key = p * a.ready_stride + (row >> 7);
+        if (key != ready_key) {
+          if (!pb::wait_flag_geq(a.local_ready + key, a.epoch)) {
+            atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+            ok = false;
+            return;
+          }
+          ready_key = key;
+        }
+      }
+      const int slot = (int)(issued % nslot);
+      pb::mbar_expect_tx(&bars[slot], a.row_bytes);
+      bulk_g2s(ring + (long)slot * slot_bytes, a.peer_src[p] + (long)row * a.row_bytes, a.row_bytes, &bars[slot]);
+    }
+    ++issued;
+    cursor_next(a, ic);
+  };
+  auto publish = [&](long completed_upto) {  // stores with index <= completed_upto are complete
+    int kept = 0;
+    for (int i = 0; i < pend_n; ++i) {
+      if (pend_q[i] <= completed_upto) {
+        __threadfence();
+        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.mb_words + pend_chunk[i]), "r"(a.epoch) : "memory");
+      } else {
+        pend_chunk[kept] = pend_chunk[i];
+        pend_q[kept] = pend_q[i];
+        ++kept;
+      }
+    }
+    pend_n = kept;
+  };
+
+  // slot reuse needs the store of row (issued - nslot) to have *read* its slot: keep READ_LAG stores unwaited
+  const int depth = nslot - READ_LAG - 1;
+  while (ok && ic.valid && issued < depth) issue_one();
+  while (ok && rc.valid) {
+    const int s = a.list_src[rc.row];
+    const int slot = (int)(retired % nslot);
+    uint8_t* gdst = a.dst + (long)rc.row * a.row_bytes;
+    if (s >= 0) {
+      if (!pb::mbar_wait(&bars[slot], (uint32_t)((phase_mask >> slot) & 1))) {
+        atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+        ok = false;
+        break;
+      }
+      phase_mask ^= (uint64_t(1) << slot);
+      bulk_s2g(gdst, ring + (long)slot * slot_bytes, a.row_bytes);
+    } else {
+      bulk_s2g(gdst, zero, a.row_bytes);
+    }
+    pb::tma_store_commit();
+    pb::tma_store_wait_read<READ_LAG>();
+    const long q = retired++;
+    if (a.gather) {
+      if (rc.row + 1 == rc.end) {
+        if (pend_n == 4) {  // only with chunks shorter than the publish lag; drain to stay correct
+          pb::tma_store_wait_all<0>();
+          publish(q);
+        }
+        pend_chunk[pend_n] = rc.chunk;
+        pend_q[pend_n] = q;
+        ++pend_n;
+      }
+      // a chunk is published PUBLISH_LAG stores after its last one: by then the wait for full completion is free
+      if (pend_n && q - pend_q[0] >= PUBLISH_LAG) {
+        pb::tma_store_wait_all<PUBLISH_LAG>();
+        publish(q - PUBLISH_LAG);
+      }
+    }
+    cursor_next(a, rc);
+    if (ic.valid) issue_one();
+  }
+  pb::tma_store_wait_all<0>();
+  if (a.gather && ok) publish(retired);
 }
 
 __device__ void comm_main(const MoeArgs& a) {
@@ -140,103 +241,23 @@ __device__ void comm_main(const MoeArgs& a) {
   const int cta = blockIdx.x;
   const int tid = threadIdx.x;
   const int slot_bytes = (a.row_bytes + 1023) & ~1023;
-  const int nslot = min(MAX_SLOTS, RING_BYTES / slot_bytes);
+  // several independent copy workers per CTA when the rows are small (one per warp 0..W-1)
+  const int W = max(1, min(MAX_WORKERS, RING_BYTES / (slot_bytes * 12)));
+  const int nslot = min(MAX_SLOTS, (RING_BYTES / W) / slot_bytes);
   for (int i = tid; i < a.row_bytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(zero)[i] = make_uint4(0, 0, 0, 0);
   if (tid == 0) {
-    for (int i = 0; i < nslot; ++i) pb::mbar_init(&bars[i], 1);
+    for (int i = 0; i < W * MAX_SLOTS; ++i) pb::mbar_init(&bars[i], 1);
     pb::fence_barrier_init();
   }
   pb::fence_proxy_async_smem();
   __syncthreads();
 
-  if (tid == 0) {
-    RowCursor ic{cta, 0, 0, false}, rc{cta, 0, 0, false};
-    cursor_seek(a, ic);
-    cursor_seek(a, rc);
-    long issued = 0, retired = 0;
-    uint64_t phase_mask = 0;
-    int ready_key = -1;          // (peer, row block) whose flag was seen last
-    bool ok = true;
-    // chunks whose last store has been committed but not yet published: (chunk, index of that store)
-    int pend_chunk[8];
-    long pend_q[8];
-    int pend_n = 0;
-
-    auto issue_one = [&]() {
-      const int s = a.list_src[ic.row];
-      if (s >= 0) {
-        const int p = s >> 24, row = s & 0xffffff;
-        if (!a.gather) {
-          const int key = p * a.ready_stride + (row >> 7);
-          if (key != ready_key) {
-            if (!pb::wait_flag_geq(a.local_ready + key, a.epoch)) {
-              atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
-              ok = false;
-              return;
-            }
-            ready_key = key;
-          }
-        }
-        const int slot = (int)(issued % nslot);
-        pb::mbar_expect_tx(&bars[slot], a.row_bytes);
-        bulk_g2s(ring + (long)slot * slot_bytes, a.peer_src[p] + (long)row * a.row_bytes, a.row_bytes, &bars[slot]);
-      }
-      ++issued;
-      cursor_next(a, ic);
-    };
-    auto publish = [&](long completed_upto) {  // stores with index <= completed_upto are complete
-      int kept = 0;
-      for (int i = 0; i < pend_n; ++i) {
-        if (pend_q[i] <= completed_upto) {
-          __threadfence();
-          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.mb_words + pend_chunk[i]), "r"(a.epoch) : "memory");
-        } else {
-          pend_chunk[kept] = pend_chunk[i];
-          pend_q[kept] = pend_q[i];
-          ++kept;
-        }
-      }
-      pend_n = kept;
-    };
-
-    const int depth = nslot - STORE_LAG - 1;
-    while (ok && ic.valid && issued < depth) issue_one();
-    while (ok && rc.valid) {
-      const int s = a.list_src[rc.row];
-      const int slot = (int)(retired % nslot);
-      uint8_t* gdst = a.dst + (long)rc.row * a.row_bytes;
-      if (s >= 0) {
-        if (!pb::mbar_wait(&bars[slot], (uint32_t)((phase_mask >> slot) & 1))) {
-          atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
-          ok = false;
-          break;
-        }
-        phase_mask ^= (uint64_t(1) << slot);
-        bulk_s2g(gdst, ring + (long)slot * slot_bytes, a.row_bytes);
-      } else {
-        bulk_s2g(gdst, zero, a.row_bytes);
-      }
-      pb::tma_store_commit();
-      pb::tma_store_wait_all<STORE_LAG>();
-      const long q = retired++;
-      if (a.gather && rc.row + 1 == rc.end) {
-        if (pend_n == 8) {  // cannot happen with 128-row chunks and a lag of 4 stores; drain to stay correct
-          pb::tma_store_wait_all<0>();
-          publish(q);
-        }
-        pend_chunk[pend_n] = rc.chunk;
-        pend_q[pend_n] = q;
-        ++pend_n;
-      }
-      cursor_next(a, rc);
-      if (a.gather && pend_n) publish(q - STORE_LAG);
-      if (ic.valid) issue_one();
-    }
-    pb::tma_store_wait_all<0>();
-    if (a.gather && ok) publish(retired);
-  } else if (tid >= 32 && tid < 64 && !a.gather && a.aux_dst != nullptr) {
+  const int warp = tid >> 5, lane = tid & 31;
+  if (warp < W && lane == 0) {
+    copy_worker(a, ring + (long)warp * (RING_BYTES / W), nslot, slot_bytes, bars + warp * MAX_SLOTS, zero,
+                cta * W + warp, a.comm_ctas * W);
+  } else if (warp == MAX_WORKERS && !a.gather && a.aux_dst != nullptr) {
     // per-row float (probability gradient) of the same copy list, one row per lane
-    const int lane = tid - 32;
     const int chunks = (a.list_len + CHUNK_ROWS - 1) / CHUNK_ROWS;
     for (int chunk = cta; chunk < chunks; chunk += a.comm_ctas) {
       const int end = min((chunk + 1) * CHUNK_ROWS, a.list_len);
@@ -256,6 +277,7 @@ __device__ void comm_main(const MoeArgs& a) {
     }
   }
 }
+
 
 // ------------------------------------------------------------------------------------------------
 // B_MN = 0: B [E, N, K] (forward).  B_MN = 1: B [E, K, N] (data gradient).
@@ -494,26 +516,44 @@ moe_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 //                     and writes (rank << 24 | token) and the probability into the destination's map, and
 //                     the pull list / inverse permutation used by the combine side locally.  Deterministic:
 //                     no atomics decide an order.
-__global__ void __launch_bounds__(1024)
-moe_plan_count_kernel(const int* __restrict__ idx, int TK, int E, int ep, int rank, int* const* peer_counts,
-                      int* __restrict__ src_map, int rows_cap) {
-  if (blockIdx.x > 0) {
-    const int nb = gridDim.x - 1;
-    for (int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x; i < rows_cap; i += nb * blockDim.x) src_map[i] = -1;
+constexpr int PLAN_SEG = 2048;   // routing entries per segment (one CTA of the count kernel)
+
+// grid: [0, n_seg) histogram one segment each; the rest reset the source map.  The CTA that finishes last
+// publishes the totals to the peers and clears the scratch for the next call.
+__global__ void __launch_bounds__(256)
+moe_plan_count_kernel(const int* __restrict__ idx, int TK, int E, int ep, int rank, int n_seg,
+                      int* __restrict__ seg_counts, int* __restrict__ scratch /* [E + 1] zero */,
+                      int* const* peer_counts, int* __restrict__ src_map, int rows_cap) {
+  if ((int)blockIdx.x >= n_seg) {
+    const int nb = gridDim.x - n_seg;
+    for (int i = (blockIdx.x - n_seg) * blockDim.x + threadIdx.x; i < rows_cap; i += nb * blockDim.x) src_map[i] = -1;
     return;
   }
   __shared__ int hist[1024];
+  __shared__ int s_last;
   for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < TK; i += blockDim.x) {
+  const int lo = blockIdx.x * PLAN_SEG, hi = min(lo + PLAN_SEG, TK);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const int e = idx[i];
     if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
   }
   __syncthreads();
-  for (int j = threadIdx.x; j < E * ep; j += blockDim.x) {
-    const int p = j / E, e = j - p * E;
-    peer_counts[p][rank * E + e] = hist[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    seg_counts[blockIdx.x * E + e] = hist[e];
+    if (hist[e]) atomicAdd(scratch + e, hist[e]);
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(scratch + E, 1) == n_seg - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int c = atomicExch(scratch + e, 0);
+    for (int p = 0; p < ep; ++p) peer_counts[p][rank * E + e] = c;
+  }
+  if (threadIdx.x == 0) scratch[E] = 0;
 }
 
 __device__ __forceinline__ int block_sum_256(int v, int* red) {
@@ -528,18 +568,27 @@ __device__ __forceinline__ int block_sum_256(int v, int* red) {
   return t;
 }
 
+// grid (E, n_seg): CTA (e, seg) places this rank's copies of expert e that lie in segment seg.
 __global__ void __launch_bounds__(256)
 moe_plan_assign_kernel(const int* __restrict__ idx, const float* __restrict__ probs, int TK, int k, int E, int ep,
-                       int rank, const int* __restrict__ counts_all, int* const* peer_src_map,
-                       float* const* peer_prob, int rows_cap, int* __restrict__ pull_src,
+                       int rank, const int* __restrict__ counts_all, const int* __restrict__ seg_counts,
+                       int* const* peer_src_map, float* const* peer_prob, int rows_cap, int* __restrict__ pull_src,
                        int* __restrict__ inv_order, int* __restrict__ tok_sorted, int* __restrict__ counts_local,
                        int* status) {
   __shared__ int red[8];
   __shared__ int warp_cnt[8];
-  const int e = blockIdx.x;
+  const int e = blockIdx.x, seg = blockIdx.y;
   const int e_local = E / ep;
   const int d = e / e_local, le = e - d * e_local;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  int tot_e = 0, base_me = 0;
+  for (int s = 0; s < ep; ++s) {
+    const int c = counts_all[s * E + e];
+    tot_e += c;
+    if (s < rank) base_me += c;
+  }
+  if (seg_counts[seg * E + e] == 0 && !(seg == 0 && d == rank)) return;  // nothing of e in this segment
 
   int part = 0;
   for (int l2 = tid; l2 < le; l2 += 256) {
@@ -550,23 +599,22 @@ moe_plan_assign_kernel(const int* __restrict__ idx, const float* __restrict__ pr
   const int row_start = block_sum_256(part, red);
   part = 0;
   for (int e2 = tid; e2 < e; e2 += 256) part += counts_all[rank * E + e2];
-  const int sorted_off = block_sum_256(part, red);
-  int tot_e = 0, base_me = 0;
-  for (int s = 0; s < ep; ++s) {
-    const int c = counts_all[s * E + e];
-    tot_e += c;
-    if (s < rank) base_me += c;
-  }
+  for (int s2 = tid; s2 < seg; s2 += 256) part += seg_counts[s2 * E + e];
+  const int sorted_base = block_sum_256(part, red);     // copies of earlier experts + of e in earlier segments
+  part = 0;
+  for (int s2 = tid; s2 < seg; s2 += 256) part += seg_counts[s2 * E + e];
+  const int seg_base = block_sum_256(part, red);        // copies of e in earlier segments
   const bool fits = row_start + (tot_e + BM - 1) / BM * BM <= rows_cap;
   if (!fits && tid == 0) atomicCAS(status, 0, PB_ERR_CAPACITY);
-  if (d == rank && tid == 0) counts_local[le] = fits ? tot_e : 0;
+  if (d == rank && seg == 0 && tid == 0) counts_local[le] = fits ? tot_e : 0;
 
   int* dst_map = peer_src_map[d];
   float* dst_prob = peer_prob[d];
   int running = 0;
-  for (int base = 0; base < TK; base += 256) {
+  const int lo = seg * PLAN_SEG, hi = min(lo + PLAN_SEG, TK);
+  for (int base = lo; base < hi; base += 256) {
     const int i = base + tid;
-    const bool f = (i < TK) && (idx[i] == e);
+    const bool f = (i < hi) && (idx[i] == e);
     const unsigned bal = __ballot_sync(0xffffffffu, f);
     if (lane == 0) warp_cnt[warp] = __popc(bal);
     __syncthreads();
@@ -579,8 +627,8 @@ moe_plan_assign_kernel(const int* __restrict__ idx, const float* __restrict__ pr
     }
     if (f) {
       const int r = running + woff + __popc(bal & ((1u << lane) - 1u));
-      const int row = row_start + base_me + r;
-      const int s = sorted_off + r;
+      const int row = row_start + base_me + seg_base + r;
+      const int s = sorted_base + r;
       const int tok = i / k;
       if (fits) {
         dst_map[row] = (rank << 24) | tok;
@@ -601,23 +649,30 @@ moe_plan_assign_kernel(const int* __restrict__ idx, const float* __restrict__ pr
 
 extern "C" {
 
-// peer_counts: host array of `ep` device pointers (int [ep * E] tables, one per rank).
-int pb_moe_plan_count(const int* idx, int TK, int E, int ep, int rank, int* const* peer_counts_dev, int* src_map,
-                      int rows_cap, cudaStream_t s) {
-  if (E > 1024 || ep < 1 || ep > MAX_EP || E % ep) return -2;
-  moe_plan_count_kernel<<<1 + 16, 1024, 0, s>>>(idx, TK, E, ep, rank, peer_counts_dev, src_map, rows_cap);
+int pb_moe_plan_num_segments(int TK) { return (TK + PLAN_SEG - 1) / PLAN_SEG; }
+
+// peer_counts_dev: device array of `ep` pointers (int [ep * E] tables, one per rank).
+// seg_counts: int [n_seg * E]; scratch: int [E + 1], zero-initialised once (the kernel leaves it zero).
+int pb_moe_plan_count(const int* idx, int TK, int E, int ep, int rank, int* seg_counts, int* scratch,
+                      int* const* peer_counts_dev, int* src_map, int rows_cap, cudaStream_t s) {
+  if (E > 1024 || ep < 1 || ep > MAX_EP || E % ep || TK < 1) return -2;
+  const int n_seg = pb_moe_plan_num_segments(TK);
+  moe_plan_count_kernel<<<n_seg + 32, 256, 0, s>>>(idx, TK, E, ep, rank, n_seg, seg_counts, scratch, peer_counts_dev,
+                                                   src_map, rows_cap);
   return (int)cudaGetLastError();
 }
 
 // peer_src_map_dev / peer_prob_dev: device arrays of `ep` pointers.
 int pb_moe_plan_assign(const int* idx, const float* probs, int TK, int k, int E, int ep, int rank,
-                       const int* counts_all, int* const* peer_src_map_dev, float* const* peer_prob_dev, int rows_cap,
-                       int* pull_src, int* inv_order, int* tok_sorted, int* counts_local, int* status,
-                       cudaStream_t s) {
+                       const int* counts_all, const int* seg_counts, int* const* peer_src_map_dev,
+                       float* const* peer_prob_dev, int rows_cap, int* pull_src, int* inv_order, int* tok_sorted,
+                       int* counts_local, int* status, cudaStream_t s) {
   if (E > 1024 || ep < 1 || ep > MAX_EP || E % ep || rows_cap >= (1 << 24) || TK / k >= (1 << 24)) return -2;
-  moe_plan_assign_kernel<<<E, 256, 0, s>>>(idx, probs, TK, k, E, ep, rank, counts_all, peer_src_map_dev,
-                                           peer_prob_dev, rows_cap, pull_src, inv_order, tok_sorted, counts_local,
-                                           status);
+  const int n_seg = pb_moe_plan_num_segments(TK);
+  if (n_seg > 65535) return -2;
+  moe_plan_assign_kernel<<<dim3(E, n_seg), 256, 0, s>>>(idx, probs, TK, k, E, ep, rank, counts_all, seg_counts,
+                                                       peer_src_map_dev, peer_prob_dev, rows_cap, pull_src, inv_order,
+                                                       tok_sorted, counts_local, status);
   return (int)cudaGetLastError();
 }
 

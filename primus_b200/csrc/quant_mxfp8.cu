@@ -1,0 +1,169 @@
+// MXFP8 quantisation: bf16 [R, C] -> E4M3 values with one UE8M0 (power-of-two) scale per 32 elements, in one
+// pass for both directions a training GEMM needs:
+//   row-wise : blocks of 32 along C (operand reduced over C: forward / data-gradient inputs)
+//   col-wise : blocks of 32 along R (operand reduced over R: weight-gradient inputs, transposed use)
+// Values keep the [R, C] layout in both cases.  Scales are written directly in the layout tcgen05 block-scaled
+// MMAs consume from TMEM: the operand's non-reduced dimension MN and reduced dimension K are tiled in
+// 128 x 128-element blocks of 512 bytes, block (mn / 128, k / 128) stored K-fastest, and inside a block
+//   offset(mn, kb) = (mn % 32) * 16 + ((mn % 128) / 32) * 4 + kb            (kb = (k % 128) / 32)
+// so a block is exactly what one `tcgen05.cp.32x128b.warpx4` moves from shared memory into 4 TMEM columns.
+//
+// Scale: e = ceil(log2(amax / 448)) (rounded up so that nothing saturates), stored biased by 127;
+// value = RN-even E4M3 of x * 2^-e.
+//
+// Replaces the Turbo / Transformer-Engine MXFP8 cast kernels
+// (primus/backends/megatron/core/extensions/primus_turbo.py: `pt.ops.quantize` users, float8 recipe mxfp8).
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE = 128;
+constexpr int PITCH = TILE + 8;  // bf16 elements per shared-memory row (272 B: conflict-free 16-byte row reads)
+
+__device__ __forceinline__ int e8m0_from_amax(float amax) {
+  const float v = amax * (1.0f / 448.0f);
+  const uint32_t b = __float_as_uint(v);
+  int e = (int)((b >> 23) & 0xff);        // biased exponent of v
+  if (b & 0x7fffff) e += 1;               // ceil for non powers of two
+  if (e < 0) e = 0;
+  if (e > 254) e = 254;
+  return (amax == 0.f) ? 0 : e;           // biased UE8M0
+}
+__device__ __forceinline__ float inv_scale_from_e8m0(int biased) {
+  int f = 254 - biased;                   // exponent field of 2^-(biased - 127)
+  if (f < 1) f = 1;
+  return __uint_as_float((uint32_t)f << 23);
+}
+__device__ __forceinline__ uint16_t cvt2(float a, float b) {
+  return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ long sf_offset(int mn, int k_blk32, int k_groups) {
+  // block (mn / 128, k_blk32 / 4), K-fastest
+  return ((long)(mn >> 7) * k_groups + (k_blk32 >> 2)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (k_blk32 & 3);
+}
+
+__global__ void __launch_bounds__(256)
+quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
+                   uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  uint8_t* qt = smem_q + TILE * PITCH * 2;
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int tid = threadIdx.x;
+  // load 128 x 128 bf16 (16 vectors of 16 B per row)
+  for (int v = tid; v < TILE * 16; v += 256) {
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
+  }
+  __syncthreads();
+  const int lane_mn = tid & 127, half = tid >> 7;
+  if (q_row) {
+    const int r = lane_mn;
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+      const int j = half * 2 + jj;
+      float f[32];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint4 d = *reinterpret_cast<const uint4*>(&tile[r * PITCH + j * 32 + v * 8]);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 t = __bfloat1622float2(h[u]);
+          f[v * 8 + 2 * u] = t.x;
+          f[v * 8 + 2 * u + 1] = t.y;
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      const int e = e8m0_from_amax(amax);
+      const float inv = inv_scale_from_e8m0(e);
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        w[i] = (uint32_t)cvt2(f[4 * i] * inv, f[4 * i + 1] * inv) |
+               ((uint32_t)cvt2(f[4 * i + 2] * inv, f[4 * i + 3] * inv) << 16);
+      uint4* dst = reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + j * 32);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      sf_row[sf_offset(row0 + r, (col0 >> 5) + j, C >> 7)] = (uint8_t)e;
+    }
+  }
+  if (q_col) {
+    const int c = lane_mn;
+#pragma unroll
+    for (int ii = 0; ii < 2; ++ii) {
+      const int i0 = (half * 2 + ii) * 32;
+      float f[32];
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        f[i] = __bfloat162float(tile[(i0 + i) * PITCH + c]);
+        amax = fmaxf(amax, fabsf(f[i]));
+      }
+      const int e = e8m0_from_amax(amax);
+      const float inv = inv_scale_from_e8m0(e);
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const uint16_t p = cvt2(f[i] * inv, f[i + 1] * inv);
+        qt[(i0 + i) * TILE + c] = (uint8_t)(p & 0xff);
+        qt[(i0 + i + 1) * TILE + c] = (uint8_t)(p >> 8);
+      }
+      sf_col[sf_offset(col0 + c, (row0 >> 5) + (i0 >> 5), R >> 7)] = (uint8_t)e;
+    }
+    __syncthreads();
+    for (int v = tid; v < TILE * 8; v += 256) {
+      const int r = v >> 3, c16 = (v & 7) * 16;
+      *reinterpret_cast<uint4*>(q_col + (long)(row0 + r) * C + col0 + c16) =
+          *reinterpret_cast<const uint4*>(&qt[r * TILE + c16]);
+    }
+  }
+}
+
+// value [R, C] fp8 + scales (operand layout with MN = R or C) -> fp32 [R, C]; test / debugging helper
+__global__ void dequant_mxfp8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf, int R, int C,
+                                     int colwise, float* __restrict__ out) {
+  const long n = (long)R * C;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / C), c = (int)(i - (long)r * C);
+    const int e = colwise ? sf[sf_offset(c, r >> 5, R >> 7)] : sf[sf_offset(r, c >> 5, C >> 7)];
+    const __nv_fp8_e4m3 v = *reinterpret_cast<const __nv_fp8_e4m3*>(q + i);
+    out[i] = float(v) * exp2f((float)(e - 127));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Any of the two outputs may be null.  R and C must be multiples of 128.
+// sf_row: R * C / 32 bytes, sf_col: R * C / 32 bytes.
+int pb_quant_mxfp8(const void* x, int R, int C, void* q_row, void* sf_row, void* q_col, void* sf_col, cudaStream_t s) {
+  if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
+  dim3 grid(C / TILE, R / TILE);
+  constexpr int SMEM = TILE * PITCH * 2 + TILE * TILE;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(quant_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  quant_mxfp8_kernel<<<grid, 256, SMEM, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), R, C,
+                                         reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row),
+                                         reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+int pb_dequant_mxfp8(const void* q, const void* sf, int R, int C, int colwise, float* out, cudaStream_t s) {
+  if (R % TILE || C % TILE) return -2;
+  dequant_mxfp8_kernel<<<1184, 256, 0, s>>>(reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const uint8_t*>(sf), R,
+                                           C, colwise, out);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

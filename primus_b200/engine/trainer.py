@@ -204,8 +204,29 @@ class Trainer:
         mask = batch["loss_mask"]
         if self.tcfg.calculate_per_token_loss:
             return mask / float(self.num_microbatches)  # normalised later by the global token count
+        if "_mask_total" in batch:
+            # context parallel: normalise by the whole sequence's token count; gradients are later averaged over
+            # dp x cp, so every rank's share is scaled back by cp
+            return mask * (float(self.st.cp) / batch["_mask_total"].clamp(min=1.0) / float(self.num_microbatches))
         denom = mask.sum().clamp(min=1.0)
         return mask / denom / float(self.num_microbatches)
+
+    def _cp_shard(self, mb: dict) -> dict:
+        """The slice of a micro-batch this context-parallel rank works on: ``seq / cp`` consecutive tokens of every
+        sequence, with their global position ids (contiguous split as in the all-to-all scheme; no zig-zag is
+        needed because attention itself runs on whole sequences)."""
+        st = self.st
+        if st.cp == 1:
+            return mb
+        b, S = mb["tokens"].shape
+        assert S % st.cp == 0, "sequence length must divide by the context-parallel size"
+        Sl = S // st.cp
+        lo = st.cp_rank * Sl
+        out = {k: v[:, lo:lo + Sl].contiguous() for k, v in mb.items() if torch.is_tensor(v) and v.dim() == 2 and v.shape[1] == S}
+        if "position_ids" not in out:
+            out["position_ids"] = torch.arange(lo, lo + Sl, device=mb["tokens"].device).repeat(b, 1)
+        out["_mask_total"] = mb["loss_mask"].sum()
+        return out
 
     def forward_backward_no_pipelining(self, micro_batches: list[dict]) -> torch.Tensor:
         model = self.model
@@ -218,7 +239,8 @@ class Trainer:
                 buf.is_last_microbatch = last
             w = self._loss_weights(mb)
             loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True,
-                         position_ids=mb.get("position_ids") if getattr(self, "use_position_ids", False) else None)
+                         position_ids=mb.get("position_ids") if (getattr(self, "use_position_ids", False)
+                                                                 or self.st.cp > 1) else None)
             loss.backward()
             total += loss.detach()
         return total
@@ -264,6 +286,8 @@ class Trainer:
     def train_step(self) -> torch.Tensor:
         """One optimizer step. Returns the (device) mean loss of this rank's micro-batches."""
         micro_batches = self.stager.next_step()
+        if self.st.cp > 1:
+            micro_batches = [self._cp_shard(mb) for mb in micro_batches]
         for buf in self.buffers:
             buf.zero_grad()
         if self.st.pp > 1:
@@ -288,7 +312,10 @@ class Trainer:
     def reduced_loss(self, loss: torch.Tensor) -> float:
         """Average over data-parallel ranks and fetch to the host (synchronises)."""
         l = loss.detach().clone()
-        if self.st.dp > 1:
+        if self.st.cp > 1:  # every context-parallel rank holds its slice's share (already scaled by cp)
+            dist.all_reduce(l, group=self.st.dp_cp_group)
+            l /= self.st.dp * self.st.cp
+        elif self.st.dp > 1:
             dist.all_reduce(l, group=self.st.dp_group)
             l /= self.st.dp
         if self.st.pp > 1:

@@ -81,8 +81,12 @@ class SelfAttention(nn.Module):
             qkv = self._qk_norm(qkv, d)
         cos, sin, pos = rope
         scale = cfg.attention_softmax_scale
-        ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
-                                        rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
+        if st.cp > 1:
+            ctx_out = layers.ulysses_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
+                                                    rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
+        else:
+            ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
+                                            rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 
@@ -255,7 +259,7 @@ class GPTModel(nn.Module):
         else:
             hidden, residual, batch, seq = hidden_in
         device = hidden.device
-        cos, sin = self.rope_tables(device, seq)
+        cos, sin = self.rope_tables(device, seq * st.cp)   # a context-parallel rank holds seq / cp of every sequence
         pos = None
         if batch > 1 or position_ids is not None:
             pos = (position_ids.reshape(-1).to(torch.int32) if position_ids is not None

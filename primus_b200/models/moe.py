@@ -76,14 +76,16 @@ class MoELayer(nn.Module):
         cfg = self.cfg
         logits = gemm.linear(y, self.router.weight)
         bias = getattr(self.router, "expert_bias", None)
-        probs, idx, full = moe_ops.router_scores(
+        probs, idx, full, counts = moe_ops.router_scores(
             logits, cfg.moe_router_topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, bias,
-            cfg.moe_router_topk_scaling_factor, cfg.moe_router_num_groups, cfg.moe_router_group_topk)
+            cfg.moe_router_topk_scaling_factor, cfg.moe_router_num_groups, cfg.moe_router_group_topk,
+            return_counts=True)
         if cfg.moe_router_force_load_balancing:
             T = y.shape[0]
             k = cfg.moe_router_topk
             idx = (torch.arange(T * k, device=y.device) % cfg.num_experts).view(T, k)
             probs = torch.full_like(probs, 1.0 / k)
+            counts = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(torch.int32)
         aux = None
         if cfg.moe_aux_loss_coeff and cfg.moe_router_load_balancing_type in ("aux_loss", "seq_aux_loss") \
                 and torch.is_grad_enabled():
@@ -93,7 +95,7 @@ class MoELayer(nn.Module):
                                               cfg.moe_aux_loss_coeff, seq)
             probs = AuxLossScaler.apply(probs, aux)
             self.last_aux_loss = aux.detach()
-        return probs, idx
+        return probs, idx, counts
 
     def experts_forward(self, x_perm, probs_perm, sched):
         cfg = self.cfg
@@ -105,9 +107,8 @@ class MoELayer(nn.Module):
         cfg = self.cfg
         T, H = y.shape
         k = cfg.moe_router_topk
-        probs, idx = self.route(y)
+        probs, idx, counts_global = self.route(y)
         flat_e = idx.reshape(-1)
-        counts_global = torch.bincount(flat_e, minlength=cfg.num_experts)
         self.last_tokens_per_expert = counts_global
         if cfg.use_turbo_mega_moe and y.is_cuda:
             out = self._forward_fused(y, probs, idx, T, k)

@@ -1,0 +1,231 @@
+"""MXFP8 (OCP microscaling: E4M3 values, one power-of-two UE8M0 scale per 32 elements) quantisation, GEMM and
+a linear layer built from them.
+
+A tensor is quantised in up to two directions because a block-scaled MMA needs the scales along the reduced
+dimension of each GEMM:
+
+==========  ===========================  ==============================
+GEMM        A operand                    B operand
+==========  ===========================  ==============================
+fprop       x   row-wise  (over in)      W   row-wise  (over in)
+dgrad       dy  row-wise  (over out)     W   col-wise  (over out)
+wgrad       dy  col-wise  (over tokens)  x   col-wise  (over tokens)
+==========  ===========================  ==============================
+
+so the forward pass stores the *col-wise fp8* copy of ``x`` for the backward pass instead of the bf16
+activation, and a weight is quantised (both directions) once per optimizer step.
+
+``quantize_mxfp8_ref`` / ``dequantize_mxfp8_ref`` restate the rounding rules in plain PyTorch (the numerics
+oracle and the CPU path).  Counterpart of the reference's fp8 recipes
+(primus/backends/megatron/core/extensions/primus_turbo.py float8 linear; MXFP8 recipe
+primus/backends/megatron/patches/args/rocm_arg_validation.py).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+BLOCK = 32
+TILE = 128
+
+
+@dataclass
+class MXFP8Tensor:
+    shape: tuple
+    q_row: Optional[torch.Tensor] = None   # uint8 view of E4M3 [R, C], scales along C
+    sf_row: Optional[torch.Tensor] = None  # uint8 [R * C / 32] (512-byte block layout, MN = R)
+    q_col: Optional[torch.Tensor] = None   # uint8 [R, C], scales along R
+    sf_col: Optional[torch.Tensor] = None  # uint8 [R * C / 32] (block layout, MN = C)
+
+
+def sf_offsets(mn: torch.Tensor, kblk: torch.Tensor, k_groups: int) -> torch.Tensor:
+    """Byte offset of the scale of row ``mn`` and 32-element block ``kblk`` in the 512-byte block layout."""
+    return ((mn // 128) * k_groups + kblk // 4) * 512 + (mn % 32) * 16 + ((mn % 128) // 32) * 4 + kblk % 4
+
+
+def _e8m0(amax: torch.Tensor) -> torch.Tensor:
+    v = (amax.float() * torch.tensor(1.0 / 448.0, dtype=torch.float32, device=amax.device))
+    bits = v.view(torch.int32)
+    e = (bits >> 23) & 0xFF
+    e = e + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    e = e.clamp(0, 254)
+    return torch.where(amax == 0, torch.zeros_like(e), e)
+
+
+def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) -> MXFP8Tensor:
+    R, C = x.shape
+    assert R % TILE == 0 and C % TILE == 0
+    xf = x.float()
+    out = MXFP8Tensor(shape=(R, C))
+    dev = x.device
+    for direction in ("row", "col"):
+        if (direction == "row" and not rowwise) or (direction == "col" and not colwise):
+            continue
+        if direction == "row":
+            blocks = xf.view(R, C // BLOCK, BLOCK)
+            e = _e8m0(blocks.abs().amax(-1))                       # [R, C/32]
+            inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
+            q = (blocks * inv[..., None]).reshape(R, C)
+            mn = torch.arange(R, device=dev)[:, None].expand(R, C // BLOCK)
+            kb = torch.arange(C // BLOCK, device=dev)[None, :].expand(R, C // BLOCK)
+            off = sf_offsets(mn, kb, C // TILE)
+        else:
+            blocks = xf.view(R // BLOCK, BLOCK, C)
+            e = _e8m0(blocks.abs().amax(1))                        # [R/32, C]
+            inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
+            q = (blocks * inv[:, None, :]).reshape(R, C)
+            mn = torch.arange(C, device=dev)[None, :].expand(R // BLOCK, C)
+            kb = torch.arange(R // BLOCK, device=dev)[:, None].expand(R // BLOCK, C)
+            off = sf_offsets(mn, kb, R // TILE)
+        q8 = q.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        sf = torch.zeros(R * C // BLOCK, dtype=torch.uint8, device=dev)
+        sf[off.reshape(-1)] = e.reshape(-1).to(torch.uint8)
+        if direction == "row":
+            out.q_row, out.sf_row = q8, sf
+        else:
+            out.q_col, out.sf_col = q8, sf
+    return out
+
+
+def dequantize_mxfp8_ref(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.Tensor:
+    R, C = q.shape
+    dev = q.device
+    r = torch.arange(R, device=dev)[:, None].expand(R, C)
+    c = torch.arange(C, device=dev)[None, :].expand(R, C)
+    off = sf_offsets(c, r // BLOCK, R // TILE) if colwise else sf_offsets(r, c // BLOCK, C // TILE)
+    e = sf[off.reshape(-1)].view(R, C).float()
+    return q.view(torch.float8_e4m3fn).float() * torch.exp2(e - 127.0)
+
+
+def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) -> MXFP8Tensor:
+    """bf16 [R, C] (R, C multiples of 128) -> MXFP8 in the requested directions (one kernel)."""
+    if not x.is_cuda:
+        return quantize_mxfp8_ref(x, rowwise, colwise)
+    R, C = x.shape
+    assert R % TILE == 0 and C % TILE == 0, "MXFP8 quantisation needs dimensions that are multiples of 128"
+    x = x.contiguous()
+    if x.dtype != torch.bfloat16:
+        x = x.bfloat16()
+    dev = x.device
+    out = MXFP8Tensor(shape=(R, C))
+    if rowwise:
+        out.q_row = torch.empty(R, C, dtype=torch.uint8, device=dev)
+        out.sf_row = torch.empty(R * C // BLOCK, dtype=torch.uint8, device=dev)
+    if colwise:
+        out.q_col = torch.empty(R, C, dtype=torch.uint8, device=dev)
+        out.sf_col = torch.empty(R * C // BLOCK, dtype=torch.uint8, device=dev)
+    _lib.call("quant_mxfp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
+    return out
+
+
+def dequantize_mxfp8(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.Tensor:
+    if not q.is_cuda:
+        return dequantize_mxfp8_ref(q, sf, colwise)
+    R, C = q.shape
+    out = torch.empty(R, C, dtype=torch.float32, device=q.device)
+    _lib.call("dequant_mxfp8", q, sf, R, C, int(colwise), out)
+    return out
+
+
+def gemm_mxfp8(a_q, a_sf, b_q, b_sf, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
+               out: Optional[torch.Tensor] = None, accumulate: bool = False, out_dtype=torch.bfloat16,
+               block_n: Optional[int] = None) -> torch.Tensor:
+    """D[M, N] (=|+=) A . B^T with MXFP8 operands.  ``a_q``: [M, K] (``a_mn`` False) or [K, M] (True); likewise
+    ``b_q`` with N.  fp32 ``out`` with ``accumulate`` adds into it (main-grad accumulation)."""
+    dev = a_q.device
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=dev)
+    mode = 0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1)
+    if block_n is None:
+        block_n = 256 if N >= 256 else 128
+    _lib.call("gemm_mxfp8", a_q, a_sf, b_q, b_sf, out, M, N, K, a_q.stride(0), b_q.stride(0), out.stride(0),
+              int(a_mn), int(b_mn), mode, block_n, 0, _lib.status_word(dev))
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+class _WeightCache:
+    """Quantised copies of a weight, refreshed when the parameter has been updated (version counter)."""
+
+    def __init__(self):
+        self.store: dict = {}
+
+    def get(self, w: torch.Tensor) -> MXFP8Tensor:
+        key = id(w)
+        ver = w._version
+        hit = self.store.get(key)
+        if hit is not None and hit[0] == ver and hit[1] == w.data_ptr():
+            return hit[2]
+        q = quantize_mxfp8(w.detach(), True, True)
+        self.store[key] = (ver, w.data_ptr(), q)
+        return q
+
+    def clear(self):
+        self.store.clear()
+
+
+WEIGHT_CACHE = _WeightCache()
+
+
+class LinearMXFP8Fn(torch.autograd.Function):
+    """y = x W^T with all three GEMMs in MXFP8 (fp32 accumulation; wgrad accumulates into ``w.main_grad`` when the
+    parameter has one)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        T, K = x2.shape
+        N = w.shape[0]
+        xq = quantize_mxfp8(x2, True, w.requires_grad)
+        wq = WEIGHT_CACHE.get(w)
+        y = gemm_mxfp8(xq.q_row, xq.sf_row, wq.q_row, wq.sf_row, T, N, K)
+        ctx.save_for_backward(xq.q_col if xq.q_col is not None else torch.empty(0),
+                              xq.sf_col if xq.sf_col is not None else torch.empty(0))
+        ctx.w_ref = w
+        ctx.dims = (T, N, K, shape)
+        return y.view(*shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_col, x_sf = ctx.saved_tensors
+        w = ctx.w_ref
+        T, N, K, shape = ctx.dims
+        dy2 = dy.reshape(T, N)
+        need_w = ctx.needs_input_grad[1]
+        dyq = quantize_mxfp8(dy2, ctx.needs_input_grad[0], need_w)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            wq = WEIGHT_CACHE.get(w)
+            # dx[T, K] = dy[T, N] . W[N, K]: B is W stored [K_red = N, N_out = K]
+            dx = gemm_mxfp8(dyq.q_row, dyq.sf_row, wq.q_col, wq.sf_col, T, K, N, b_mn=True).view(shape)
+        dw = None
+        if need_w:
+            mg = getattr(w, "main_grad", None)
+            tgt = mg if mg is not None else torch.empty(N, K, dtype=torch.float32, device=dy.device)
+            # dW[N, K] = dy^T . x: A is dy stored [K_red = T, M = N], B is x stored [K_red = T, N_out = K]
+            gemm_mxfp8(dyq.q_col, dyq.sf_col, x_col, x_sf, N, K, T, a_mn=True, b_mn=True, out=tgt,
+                       accumulate=mg is not None)
+            if mg is None:
+                dw = tgt.to(w.dtype)
+            else:
+                cb = getattr(w, "_grad_ready_cb", None)
+                if cb is not None:
+                    cb(w)
+        return dx, dw
+
+
+def linear_mxfp8(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """MXFP8 linear; falls back to the reference arithmetic (dequantised operands) on CPU tensors."""
+    if not x.is_cuda:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        xq = quantize_mxfp8_ref(x2, True, False)
+        wq = quantize_mxfp8_ref(w.detach(), True, False)
+        y = dequantize_mxfp8_ref(xq.q_row, xq.sf_row, False) @ dequantize_mxfp8_ref(wq.q_row, wq.sf_row, False).t()
+        return y.to(x.dtype).view(*shape[:-1], w.shape[0])
+    return LinearMXFP8Fn.apply(x, w)

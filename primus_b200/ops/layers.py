@@ -275,3 +275,60 @@ def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=T
         o = attention.attention_ref(q, k, v, batch, causal, scale)[0]
         return o.reshape(T, hq * d)
     return RopeAttentionFn.apply(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale)
+
+
+# ----------------------------------------------------------------------------------------------
+# Context parallelism (Ulysses): sequence-sharded activations, head-sharded attention
+class _SeqHeadAllToAll(torch.autograd.Function):
+    """Equal-split all-to-all over the context-parallel group; the backward pass is the same exchange."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        import torch.distributed as dist
+
+        ctx.group = group
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        g = g.contiguous()   # (empty_like of a permuted gradient would inherit its strides)
+        out = torch.empty_like(g)
+        dist.all_to_all_single(out, g, group=ctx.group)
+        return out, None
+
+
+def ulysses_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group, cp, rot_dim=None, causal=True, scale=None):
+    """Self-attention when every rank of the context-parallel group holds ``seq / cp`` tokens of each sequence.
+
+    RoPE is applied to the local tokens with their global positions, one all-to-all turns the sequence
+    sharding into a head sharding ([T/cp, all heads] -> [T, heads/cp]), attention runs over the full
+    sequence on ``hq/cp`` query and ``hkv/cp`` key/value heads, and the inverse all-to-all restores the
+    sequence sharding.  Same scheme as the reference's Ulysses attention
+    (primus/backends/megatron/core/extensions/primus_turbo.py: PrimusTurboAttention with cp_comm_type "a2a").
+    Returns [T/cp, hq * d]."""
+    assert hq % cp == 0 and hkv % cp == 0, "context parallelism (all-to-all) needs heads divisible by cp"
+    Tl = qkv.shape[0]
+    Sl = Tl // batch
+    hq_l, hkv_l = hq // cp, hkv // cp
+    q = qkv[:, : hq * d].reshape(Tl, hq, d)
+    k = qkv[:, hq * d: (hq + hkv) * d].reshape(Tl, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(Tl, hkv, d)
+    if cos is not None:
+        q = fused.rope(q, cos, sin, pos, rot_dim or d)
+        k = fused.rope(k, cos, sin, pos, rot_dim or d)
+    # [cp (destination), Tl, (hq_l + 2 hkv_l) * d]
+    send = torch.cat([q.reshape(Tl, cp, hq_l * d), k.reshape(Tl, cp, hkv_l * d), v.reshape(Tl, cp, hkv_l * d)], dim=2)
+    send = send.permute(1, 0, 2).contiguous()
+    recv = _SeqHeadAllToAll.apply(send, cp_group)                     # [cp (source), batch * Sl, chunk]
+    chunk = recv.shape[2]
+    full = recv.view(cp, batch, Sl, chunk).permute(1, 0, 2, 3).reshape(batch * cp * Sl, chunk)
+    out = rope_attention(full.contiguous(), None, None, None, batch, hq_l, hkv_l, d, rot_dim=rot_dim, causal=causal,
+                         scale=scale)                                  # [batch * S, hq_l * d]
+    back = out.view(batch, cp, Sl, hq_l * d).permute(1, 0, 2, 3).reshape(cp, Tl, hq_l * d).contiguous()
+    got = _SeqHeadAllToAll.apply(back, cp_group)                      # [cp (head group), Tl, hq_l * d]
+    return got.permute(1, 0, 2).reshape(Tl, hq * d)

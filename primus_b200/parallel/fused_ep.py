@@ -98,6 +98,9 @@ class FusedEP:
         self.peer_ready = host_table("ready")
         self.gather_words = torch.zeros(self.num_mb, dtype=torch.int32, device=self.device)
         self.tile_words = torch.zeros(self.num_mb, dtype=torch.int32, device=self.device)
+        self.n_seg = int(_lib.require().pb_moe_plan_num_segments(ctypes.c_int(T * k)))
+        self.seg_counts = torch.zeros(self.n_seg * E, dtype=torch.int32, device=self.device)
+        self.plan_scratch = torch.zeros(E + 1, dtype=torch.int32, device=self.device)
         self.gather_epoch = 0
         self.combine_epoch = 0
         self._published = False   # tokens of the current dispatch already ordered by the plan's barrier
@@ -111,15 +114,15 @@ class FusedEP:
         idx32 = idx.to(torch.int32).contiguous()
         p32 = probs.detach().float().contiguous()
         st = _lib.status_word(dev)
-        _lib.call("moe_plan_count", idx32, T * k, self.E, self.ep, self.rank, self.peer_counts_dev, self.src_map_sym,
-                  self.rows_cap)
+        _lib.call("moe_plan_count", idx32, T * k, self.E, self.ep, self.rank, self.seg_counts, self.plan_scratch,
+                  self.peer_counts_dev, self.src_map_sym, self.rows_cap)
         self.sym.barrier()
         pull_src = torch.empty(T * k, dtype=torch.int32, device=dev)
         inv_order = torch.empty(T, k, dtype=torch.int32, device=dev)
         tok_sorted = torch.empty(T * k, dtype=torch.int32, device=dev)
         counts_local = torch.empty(self.e_local, dtype=torch.int32, device=dev)
         _lib.call("moe_plan_assign", idx32, p32, T * k, k, self.E, self.ep, self.rank, self.counts_all,
-                  self.peer_src_map_dev, self.peer_prob_dev, self.rows_cap, pull_src, inv_order, tok_sorted,
+                  self.seg_counts, self.peer_src_map_dev, self.peer_prob_dev, self.rows_cap, pull_src, inv_order, tok_sorted,
                   counts_local, st)
         self._published = True   # the barrier above also separates the previous readers of x_sym from the next copy
         return _PendingPlan(self, T, k, counts_local, pull_src, inv_order, tok_sorted)

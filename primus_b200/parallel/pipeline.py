@@ -44,6 +44,11 @@ def _p2p_shape(trainer, batch, seq):
     return (2, T, trainer.mcfg.hidden_size)
 
 
+def _pos_ids(trainer, mb):
+    use = getattr(trainer, "use_position_ids", False) or trainer.st.cp > 1
+    return mb.get("position_ids") if use else None
+
+
 def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: PipelineTimeline | None = None):
     st = trainer.st
     pp, r = st.pp, st.pp_rank
@@ -99,11 +104,12 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
             if s == S - 1:
                 w = trainer._loss_weights(mb)
                 out = model(mb["tokens"] if s == 0 else None, mb["labels"], loss_weights=w, hidden_in=hidden_in,
-                            unit_upstream=True)
+                            unit_upstream=True, position_ids=_pos_ids(trainer, mb))
                 outputs[k] = out
                 total += out.detach()
             else:
-                h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in)
+                h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in,
+                                     position_ids=_pos_ids(trainer, mb))
                 if res is None:
                     res = torch.zeros_like(h)
                 y = torch.stack([h, res])

@@ -2,13 +2,13 @@
 import torch
 
 
-def tiny_cfgs(tp=1, pp=1, ep=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4):
+def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
     kw = dict(num_layers=layers, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
               vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
-              expert_model_parallel_size=ep, sequence_parallel=sp, make_vocab_size_divisible_by=64,
+              expert_model_parallel_size=ep, context_parallel_size=cp, sequence_parallel=sp, make_vocab_size_divisible_by=64,
               virtual_pipeline_model_parallel_size=vpp)
     if moe:
         kw.update(num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq=[0, 1] * (layers // 2),
@@ -30,6 +30,7 @@ def full_reference_state(mc_kwargs, seed=7):
     ps.initialize_model_parallel()
     kw = dict(mc_kwargs)
     kw.update(tensor_model_parallel_size=1, pipeline_model_parallel_size=1, expert_model_parallel_size=1,
+              context_parallel_size=1,
               sequence_parallel=False, virtual_pipeline_model_parallel_size=None)
     torch.manual_seed(seed)
     m = GPTModel(TransformerConfig(**kw), "cpu")
@@ -67,7 +68,7 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
     ps.destroy_model_parallel()
     mc, tc = tiny_cfgs(**kwargs)
     ps.initialize_model_parallel(tp=mc.tensor_model_parallel_size, pp=mc.pipeline_model_parallel_size,
-                                 ep=mc.expert_model_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size)
+                                 ep=mc.expert_model_parallel_size, cp=mc.context_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     load_from_full(tr, full_sd)
     losses = tr.train()

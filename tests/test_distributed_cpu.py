@@ -14,7 +14,7 @@ def _single(kwargs):
     from primus_b200.engine.trainer import Trainer
     from primus_b200.parallel import state as ps
 
-    mc, tc = W.tiny_cfgs(**{**kwargs, "tp": 1, "pp": 1, "ep": 1, "sp": False, "vpp": None, "schedule": "1f1b"})
+    mc, tc = W.tiny_cfgs(**{**kwargs, "tp": 1, "pp": 1, "ep": 1, "cp": 1, "sp": False, "vpp": None, "schedule": "1f1b"})
     mck = _mc_kwargs(mc)
     full = W.full_reference_state(mck)
     ps.destroy_model_parallel()
@@ -41,6 +41,8 @@ CASES = {
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
     "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
+    "cp2": dict(world=2, kw=dict(cp=2)),
+    "cp2_pp2": dict(world=4, kw=dict(cp=2, pp=2)),
 }
 
 

@@ -1,0 +1,86 @@
+"""MXFP8 quantisation and block-scaled GEMM kernels vs plain PyTorch restatements."""
+import pytest
+import torch
+
+from primus_b200.ops import _lib, fp8
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 384), (1024, 512)])
+def test_quantize_matches_reference_bitwise(R, C):
+    torch.manual_seed(0)
+    x = (torch.randn(R, C, device="cuda") * torch.exp(torch.randn(R, 1, device="cuda") * 3)).bfloat16()
+    x[5, 32:64] = 0
+    q = fp8.quantize_mxfp8(x)
+    ref = fp8.quantize_mxfp8_ref(x)
+    for name in ("q_row", "sf_row", "q_col", "sf_col"):
+        assert torch.equal(getattr(q, name), getattr(ref, name)), name
+    for colwise, qq, sf in ((False, q.q_row, q.sf_row), (True, q.q_col, q.sf_col)):
+        deq = fp8.dequantize_mxfp8(qq, sf, colwise)
+        assert torch.equal(deq, fp8.dequantize_mxfp8_ref(qq, sf, colwise))
+        err = (deq - x.float()).abs()
+        assert (err <= x.float().abs() * 0.0626 + 1e-30).all() or err.max() <= 0.07 * x.float().abs().max()
+
+
+def _ref_gemm(aq, asf, a_col, bq, bsf, b_col, a_mn, b_mn):
+    A = fp8.dequantize_mxfp8(aq, asf, a_col)
+    B = fp8.dequantize_mxfp8(bq, bsf, b_col)
+    A = A.t() if a_mn else A
+    B = B.t() if b_mn else B
+    return A @ B.t()
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 128, 256), (256, 512, 512, 256), (384, 128, 256, 128),
+                                      (512, 768, 1024, 256), (256, 384, 384, 128)])
+def test_gemm_fprop_layout(M, N, K, bn):
+    torch.manual_seed(1)
+    a = (torch.randn(M, K, device="cuda") * 2).bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    aq, bq = fp8.quantize_mxfp8(a, True, False), fp8.quantize_mxfp8(b, True, False)
+    out = fp8.gemm_mxfp8(aq.q_row, aq.sf_row, bq.q_row, bq.sf_row, M, N, K, block_n=bn)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = _ref_gemm(aq.q_row, aq.sf_row, False, bq.q_row, bq.sf_row, False, False, False)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 1e-2 * ref.abs().max().item(), (err, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("T,N,K", [(256, 256, 384), (512, 384, 256)])
+def test_linear_fwd_bwd_against_dequantised_reference(T, N, K):
+    torch.manual_seed(2)
+    x = torch.randn(T, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    dy = torch.randn(T, N, device="cuda").bfloat16()
+    y = fp8.linear_mxfp8(x, w)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    xq, wq, dyq = fp8.quantize_mxfp8(x.detach()), fp8.quantize_mxfp8(w.detach()), fp8.quantize_mxfp8(dy)
+    y_ref = _ref_gemm(xq.q_row, xq.sf_row, False, wq.q_row, wq.sf_row, False, False, False)
+    dx_ref = fp8.dequantize_mxfp8(dyq.q_row, dyq.sf_row, False) @ fp8.dequantize_mxfp8(wq.q_col, wq.sf_col, True)
+    dw_ref = fp8.dequantize_mxfp8(dyq.q_col, dyq.sf_col, True).t() @ fp8.dequantize_mxfp8(xq.q_col, xq.sf_col, True)
+    for got, ref, name in ((y, y_ref, "y"), (x.grad, dx_ref, "dx"), (w.grad, dw_ref, "dw")):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 1.5e-2 * ref.abs().max().item(), (name, err, ref.abs().max().item())
+    # and close to the bf16 result (quantisation noise only)
+    y_bf = x.detach().float() @ w.detach().float().t()
+    cos = torch.nn.functional.cosine_similarity(y.float().flatten(), y_bf.flatten(), dim=0).item()
+    assert cos > 0.995, cos
+
+
+def test_wgrad_accumulates_into_main_grad():
+    T, N, K = 256, 256, 256
+    torch.manual_seed(3)
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w.main_grad = torch.ones(N, K, dtype=torch.float32, device="cuda")
+    dy = torch.randn(T, N, device="cuda").bfloat16()
+    fp8.linear_mxfp8(x, w).backward(dy)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    xq, dyq = fp8.quantize_mxfp8(x), fp8.quantize_mxfp8(dy)
+    dw_ref = fp8.dequantize_mxfp8(dyq.q_col, dyq.sf_col, True).t() @ fp8.dequantize_mxfp8(xq.q_col, xq.sf_col, True)
+    err = (w.main_grad - 1.0 - dw_ref).abs().max().item()
+    assert err <= 1e-2 * dw_ref.abs().max().item(), err
+    assert w.grad is None

@@ -107,6 +107,8 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); dp = gpus / tp")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
+    ap.add_argument("--precision", default="mxfp8", choices=["bf16", "mxfp8"],
+                    help="linear-layer GEMM precision: bf16, or MXFP8 (E4M3 values, UE8M0 scale per 32 elements; fp32 accumulation)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -134,7 +136,8 @@ def main() -> int:
     if args.layers:
         mdict["num_layers"] = args.layers
     mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
-                             sequence_parallel=args.tp > 1)
+                             sequence_parallel=args.tp > 1, fp8="e4m3" if args.precision == "mxfp8" else None,
+                             fp8_recipe="mxfp8")
     if args.fused_tp:
         from primus_b200.parallel import fused_tp
 
@@ -208,7 +211,8 @@ def main() -> int:
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": value / (BASELINE_TOK_S_GPU * world) if args.model == "llama3.1_8B" else None,
-            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
+            "dtype": "bf16" if args.precision == "bf16" else "mxfp8 linear GEMMs (E4M3 + UE8M0 per 32, fp32 accumulate), bf16 attention / LM head / params, fp32 master",
+            "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
             "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
                        "micro_batch": args.micro_batch, "parallelism": f"dp{world // args.tp}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",

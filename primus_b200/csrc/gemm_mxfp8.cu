@@ -12,8 +12,10 @@
 // * TMEM holds the accumulator(s) plus 4 + BN/32 scale columns: a 128 x 256 tile leaves room for one
 //   accumulator only (the producer keeps prefetching the next tile while the epilogue drains it), a 128 x 128
 //   tile is double buffered,
-// * the epilogue reads the accumulator with tcgen05.ld and writes full 128-byte lines per row straight from
-//   registers (bf16 / fp32 store, or fp32 `red.add` into a main-grad buffer).
+// * the epilogue reads the accumulator with tcgen05.ld and writes full lines per row straight from registers;
+//   for bf16 output a thread first drains its whole row into packed registers and releases the accumulator, so
+//   the global stores overlap the next tile's MMAs (fp32 store / fp32 `red.add` into a main-grad buffer go
+//   32 columns at a time).
 //
 // Operand layouts as in csrc/gemm_bf16.cu: X_MN = 0 -> stored [MN, K] (K contiguous), X_MN = 1 -> stored
 // [K, MN] (MN contiguous); the scale tensors are always indexed (mn, k / 32).
@@ -242,27 +244,37 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       pb::tc_fence_after();
       const uint32_t t_row = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        pb::tmem_ld_32x32b_x32(t_row + c * 32, r);
-        pb::tmem_wait_ld();
-        const int n = n0 + c * 32;
-        if (m < M && n < N) {
-          if (OUT == OUT_BF16) {
-            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(Dv) + (long)m * ldd + n;
+      if (OUT == OUT_BF16) {
+        // drain the whole row into registers as packed bf16 (BN / 2 registers), hand the accumulator back to the
+        // MMA thread, and only then write to global memory: the next tile's MMAs overlap the stores
+        uint32_t packed[BN / 2];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (n + 8 * j < N) {
-                uint4 v;
-                v.x = pb::pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-                v.y = pb::pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                v.z = pb::pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                v.w = pb::pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-                reinterpret_cast<uint4*>(d)[j] = v;
-              }
-            }
-          } else {
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          pb::tmem_ld_32x32b_x32(t_row + c * 32, r);
+          pb::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[c * 16 + j] = pb::pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        }
+        pb::tc_fence_before();
+        pb::mbar_arrive(&bars->tmem_empty[acc]);
+        if (m < M) {
+          __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(Dv) + (long)m * ldd + n0;
+#pragma unroll
+          for (int j = 0; j < BN / 8; ++j)
+            if (n0 + 8 * j < N)
+              reinterpret_cast<uint4*>(d)[j] =
+                  make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          pb::tmem_ld_32x32b_x32(t_row + c * 32, r);
+          pb::tmem_wait_ld();
+          const int n = n0 + c * 32;
+          if (m < M && n < N) {
             float* d = reinterpret_cast<float*>(Dv) + (long)m * ldd + n;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -279,9 +291,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
         }
+        pb::tc_fence_before();
+        pb::mbar_arrive(&bars->tmem_empty[acc]);
       }
-      pb::tc_fence_before();
-      pb::mbar_arrive(&bars->tmem_empty[acc]);
       if (++acc == C::ACC_BUFS) {
         acc = 0;
         acc_phase ^= 1;

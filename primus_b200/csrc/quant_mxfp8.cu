@@ -45,24 +45,30 @@ __device__ __forceinline__ long sf_offset(int mn, int k_blk32, int k_groups) {
   return ((long)(mn >> 7) * k_groups + (k_blk32 >> 2)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (k_blk32 & 3);
 }
 
+constexpr int QPITCH = TILE + 16;  // bytes per row of the staged fp8 tiles (conflict-free 16-byte row accesses)
+constexpr int QUANT_SMEM = TILE * PITCH * 2 + 2 * TILE * QPITCH;
+
 __global__ void __launch_bounds__(256)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
-  uint8_t* qt = smem_q + TILE * PITCH * 2;
+  uint8_t* qr = smem_q + TILE * PITCH * 2;
+  uint8_t* qc = qr + TILE * QPITCH;
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
   const int tid = threadIdx.x;
   // load 128 x 128 bf16 (16 vectors of 16 B per row)
-  for (int v = tid; v < TILE * 16; v += 256) {
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
     const int r = v >> 4, c8 = (v & 15) * 8;
     const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
   }
   __syncthreads();
-  const int lane_mn = tid & 127, half = tid >> 7;
   if (q_row) {
-    const int r = lane_mn;
+    // thread -> (row r, two 32-element blocks): 64 contiguous bytes of the row
+    const int r = tid & 127, half = tid >> 7;
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj) {
       const int j = half * 2 + jj;
@@ -88,40 +94,46 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
       for (int i = 0; i < 8; ++i)
         w[i] = (uint32_t)cvt2(f[4 * i] * inv, f[4 * i + 1] * inv) |
                ((uint32_t)cvt2(f[4 * i + 2] * inv, f[4 * i + 3] * inv) << 16);
-      uint4* dst = reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + j * 32);
+      uint4* dst = reinterpret_cast<uint4*>(qr + r * QPITCH + j * 32);
       dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
       sf_row[sf_offset(row0 + r, (col0 >> 5) + j, C >> 7)] = (uint8_t)e;
     }
   }
   if (q_col) {
-    const int c = lane_mn;
+    // thread -> (column pair cp, 32-row block ib): one bf16x2 load and one 2-byte store per row
+    const int cp = tid & 63, ib = tid >> 6;
+    const int i0 = ib * 32, c = 2 * cp;
+    float f0[32], f1[32];
+    float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-    for (int ii = 0; ii < 2; ++ii) {
-      const int i0 = (half * 2 + ii) * 32;
-      float f[32];
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        f[i] = __bfloat162float(tile[(i0 + i) * PITCH + c]);
-        amax = fmaxf(amax, fabsf(f[i]));
-      }
-      const int e = e8m0_from_amax(amax);
-      const float inv = inv_scale_from_e8m0(e);
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const uint16_t p = cvt2(f[i] * inv, f[i + 1] * inv);
-        qt[(i0 + i) * TILE + c] = (uint8_t)(p & 0xff);
-        qt[(i0 + i + 1) * TILE + c] = (uint8_t)(p >> 8);
-      }
-      sf_col[sf_offset(col0 + c, (row0 >> 5) + (i0 >> 5), R >> 7)] = (uint8_t)e;
+    for (int i = 0; i < 32; ++i) {
+      const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[(i0 + i) * PITCH + c]));
+      f0[i] = t.x;
+      f1[i] = t.y;
+      a0 = fmaxf(a0, fabsf(t.x));
+      a1 = fmaxf(a1, fabsf(t.y));
     }
-    __syncthreads();
-    for (int v = tid; v < TILE * 8; v += 256) {
-      const int r = v >> 3, c16 = (v & 7) * 16;
+    const int e0 = e8m0_from_amax(a0), e1 = e8m0_from_amax(a1);
+    const float i0s = inv_scale_from_e8m0(e0), i1s = inv_scale_from_e8m0(e1);
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      *reinterpret_cast<uint16_t*>(qc + (i0 + i) * QPITCH + c) = cvt2(f0[i] * i0s, f1[i] * i1s);
+    sf_col[sf_offset(col0 + c, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e0;
+    sf_col[sf_offset(col0 + c + 1, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e1;
+  }
+  __syncthreads();
+  // coalesced 16-byte stores of the staged fp8 tiles (8 vectors per row)
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 3, c16 = (v & 7) * 16;
+    if (q_row)
+      *reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + c16) =
+          *reinterpret_cast<const uint4*>(qr + r * QPITCH + c16);
+    if (q_col)
       *reinterpret_cast<uint4*>(q_col + (long)(row0 + r) * C + col0 + c16) =
-          *reinterpret_cast<const uint4*>(&qt[r * TILE + c16]);
-    }
+          *reinterpret_cast<const uint4*>(qc + r * QPITCH + c16);
   }
 }
 
@@ -146,7 +158,7 @@ extern "C" {
 int pb_quant_mxfp8(const void* x, int R, int C, void* q_row, void* sf_row, void* q_col, void* sf_col, cudaStream_t s) {
   if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
   dim3 grid(C / TILE, R / TILE);
-  constexpr int SMEM = TILE * PITCH * 2 + TILE * TILE;
+  constexpr int SMEM = QUANT_SMEM;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(quant_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

@@ -67,15 +67,45 @@ def shard_spec(name: str, p: torch.Tensor, cfg, st) -> dict:
     return {"kind": "tp", "axis": int(getattr(p, "partition_dim", 0)), "index": st.tp_rank, "count": st.tp}
 
 
+def _mla_rope_rows(t: torch.Tensor, name: str, cfg, tp: int, to_internal: bool) -> torch.Tensor:
+    """MLA keeps the rotary dims of q / k in the *interleaved* pair order of the published DeepSeek weights in a
+    checkpoint (Megatron de-interleaves at run time); this engine rotates halves, so the rows that produce the
+    rotary dims are de-interleaved on load (even positions first, then odd) and re-interleaved on save."""
+    dr = cfg.qk_pos_emb_head_dim
+    if to_internal:
+        perm = torch.cat([torch.arange(0, dr, 2), torch.arange(1, dr, 2)])
+    else:
+        perm = torch.empty(dr, dtype=torch.long)
+        perm[0::2] = torch.arange(0, dr // 2)
+        perm[1::2] = torch.arange(dr // 2, dr)
+    perm = perm.to(t.device)
+    if name.endswith("linear_kv_down_proj.weight"):
+        lat = cfg.kv_lora_rank
+        return torch.cat([t[:lat], t[lat:][perm]], dim=0)
+    nh = cfg.num_attention_heads // tp
+    dn = cfg.qk_head_dim
+    x = t.reshape(nh, dn + dr, *t.shape[1:])
+    return torch.cat([x[:, :dn], x[:, dn:][:, perm]], dim=1).reshape(t.shape)
+
+
+def _is_mla_rope_weight(name: str, cfg) -> bool:
+    return cfg.multi_latent_attention and name.endswith(
+        ("linear_kv_down_proj.weight", "linear_q_up_proj.weight", "linear_q_proj.weight"))
+
+
 def to_saved_layout(name: str, t: torch.Tensor, cfg, tp: int) -> torch.Tensor:
     if name.endswith("linear_qkv.weight") and not cfg.multi_latent_attention:
         return qkv_internal_to_mcore(t, cfg.num_attention_heads // tp, cfg.num_query_groups // tp, cfg.kv_channels)
+    if _is_mla_rope_weight(name, cfg):
+        return _mla_rope_rows(t, name, cfg, tp, to_internal=False)
     return t
 
 
 def from_saved_layout(name: str, t: torch.Tensor, cfg, tp: int) -> torch.Tensor:
     if name.endswith("linear_qkv.weight") and not cfg.multi_latent_attention:
         return qkv_mcore_to_internal(t, cfg.num_attention_heads // tp, cfg.num_query_groups // tp, cfg.kv_channels)
+    if _is_mla_rope_weight(name, cfg):
+        return _mla_rope_rows(t, name, cfg, tp, to_internal=True)
     return t
 
 
@@ -120,6 +150,20 @@ def read_tracker(root: str) -> Optional[str]:
         return f.read().strip()
 
 
+_RENAMES = ((".self_attention.input_layernorm.", ".input_layernorm."),
+            (".mlp.experts.fc1_weight.weight", ".mlp.experts.linear_fc1.weight"),
+            (".mlp.experts.fc2_weight.weight", ".mlp.experts.linear_fc2.weight"))
+
+
+def saved_key(name: str) -> str:
+    """Name of a parameter inside a checkpoint: Megatron-core keys.  The MLA input norm is a layer-level module
+    there, and the expert weights are called ``linear_fc1 / linear_fc2`` (stored stacked ``[experts, out, in]`` here;
+    Megatron's grouped linear stores one ``weight{e}`` entry per expert)."""
+    for a, b in _RENAMES:
+        name = name.replace(a, b)
+    return name
+
+
 def model_named_parameters(trainer):
     for m in trainer.model_chunks:
         for name, p in m.named_parameters():
@@ -146,8 +190,9 @@ def save_checkpoint(trainer, root: str, release: bool = False) -> str:
         if not writer:
             continue
         t = to_saved_layout(name, p.detach(), cfg, st.tp).cpu().clone()
-        shards[name] = t
-        meta[name] = {"spec": spec, "shape": list(t.shape), "dtype": str(t.dtype), "file": f"__{st.rank}_0.distcp"}
+        key = saved_key(name)
+        shards[key] = t
+        meta[key] = {"spec": spec, "shape": list(t.shape), "dtype": str(t.dtype), "file": f"__{st.rank}_0.distcp"}
     payload = {"model": shards}
     if not getattr(trainer.tcfg, "no_save_optim", False):
         payload["optimizer"] = {k: ([{kk: (vv.cpu() if torch.is_tensor(vv) else vv) for kk, vv in s.items()} for s in v]
@@ -199,11 +244,12 @@ def load_checkpoint(trainer, root: str, finetune: bool = False, load_optim: bool
 
     missing, loaded = [], 0
     for name, p in model_named_parameters(trainer):
-        if name not in meta:
+        key = saved_key(name) if saved_key(name) in meta else name   # older checkpoints used the internal names
+        if key not in meta:
             missing.append(name)
             continue
-        entries = meta[name]
-        shards = [(e["spec"], file_payload(e["file"])["model"][name]) for e in entries]
+        entries = meta[key]
+        shards = [(e["spec"], file_payload(e["file"])["model"][key]) for e in entries]
         saved_tp = entries[0]["spec"]["count"] if entries[0]["spec"]["kind"] in ("qkv", "glu", "tp") else 1
         full = assemble_global(name, shards)
         spec = shard_spec(name, p, cfg, st)
@@ -213,7 +259,6 @@ def load_checkpoint(trainer, root: str, finetune: bool = False, load_optim: bool
             raise ValueError(f"{name}: checkpoint shard {tuple(mine.shape)} does not fit parameter {tuple(p.shape)}")
         p.data.copy_(mine.to(p.dtype))
         loaded += 1
-    unexpected = [k for k in meta if k not in {n for n, _ in model_named_parameters(trainer)}]
     if missing:
         raise KeyError(f"checkpoint {d} lacks {len(missing)} tensors, e.g. {missing[:4]}")
     common = torch.load(os.path.join(d, "common.pt"), map_location="cpu", weights_only=False)
@@ -246,6 +291,9 @@ def load_checkpoint(trainer, root: str, finetune: bool = False, load_optim: bool
 
 def _refresh_master_weights(trainer):
     """Re-derive fp32 master weights from the (just loaded) parameters; moments start from zero."""
+    from ..ops import gemm as _gemm
+
+    _gemm.bump_weight_generation()
     for s in trainer.optimizer.state:
         buf = s["buf"]
         s["master"].copy_(buf.param_data[s["s"]:s["e"]].float())

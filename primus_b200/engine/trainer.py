@@ -136,6 +136,10 @@ class Trainer:
         if device is None:
             device = f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu"
         self.device = torch.device(device)
+        from ..ops import gemm as _gemm
+
+        # fp8 recipe of the linear-layer GEMMs (attention, the LM head and the router stay in bf16)
+        _gemm.set_fp8_recipe("mxfp8" if (model_cfg.fp8 and model_cfg.fp8_recipe == "mxfp8") else None)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
         # ---------------------------------------------------------------- model chunks
@@ -358,6 +362,8 @@ class Trainer:
                                 self.log(f"[straggler] slow ranks {rep['stragglers']} (median {rep['median_s']:.3f} s)")
                     if on_step is not None:
                         on_step(self, lv)
+                if tc.eval_interval and tc.eval_iters and self.iteration % tc.eval_interval == 0:
+                    self.evaluate(tc.eval_iters)
                 if tc.save and tc.save_interval and self.iteration % tc.save_interval == 0:
                     self.save_checkpoint()
                 if exit_flag is not None and exit_flag.requested:
@@ -376,6 +382,47 @@ class Trainer:
                 gc.enable()
                 self._gc_disabled = False
         return losses
+
+    # ------------------------------------------------------------------ evaluation
+    def _eval_stager(self):
+        """Validation data: a separate stream of the same dataset class (mock data: a different seed; indexed data:
+        the ``valid_data_path`` file when given, else the tail of the training file)."""
+        if getattr(self, "_eval_stager_obj", None) is None:
+            tc, st = self.tcfg, self.st
+            if tc.mock_data or not tc.data_path:
+                ds = MockGPTDataset(self.mcfg.vocab_size, tc.seq_length, tc.data_seed + 1000003)
+            else:
+                from .data import IndexedTokenDataset
+
+                ds = IndexedTokenDataset(getattr(tc, "valid_data_path", None) or tc.data_path, tc.seq_length)
+            sampler = MicroBatchSampler(tc.global_batch_size, tc.micro_batch_size, st.dp, st.dp_rank)
+            self._eval_stager_obj = BatchStager(ds, sampler, self.device)
+        return self._eval_stager_obj
+
+    @torch.no_grad()
+    def evaluate(self, iters: int) -> float:
+        """Mean validation loss over ``iters`` global batches (forward only; no pipeline parallelism).  Logs the
+        ``validation loss at iteration`` line of the reference's evaluator
+        (primus/backends/megatron/training/evaluator.py:23-208)."""
+        if self.st.pp > 1:
+            self.log("evaluation skipped: forward-only pipeline schedule is not available")
+            return float("nan")
+        stager = self._eval_stager()
+        total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for _ in range(iters):
+            mbs = stager.next_step()
+            if self.st.cp > 1:
+                mbs = [self._cp_shard(mb) for mb in mbs]
+            for mb in mbs:
+                w = self._loss_weights(mb)
+                pos = mb.get("position_ids") if (getattr(self, "use_position_ids", False) or self.st.cp > 1) else None
+                total += self.model(mb["tokens"], mb["labels"], loss_weights=w, position_ids=pos).detach().float()
+        val = self.reduced_loss(total / max(iters, 1))
+        ppl = math.exp(min(val, 20.0))
+        self.last_metrics.update(validation_loss=val, validation_ppl=ppl)
+        if self.st.rank == self.st.world_size - 1 or self.st.world_size == 1:
+            self.log(f" validation loss at iteration {self.iteration} | lm loss value: {val:.6E} | lm loss PPL: {ppl:.6E} |")
+        return val
 
     def _log_step(self, loss: float, dt: float):
         tc, st = self.tcfg, self.st

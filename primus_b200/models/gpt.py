@@ -182,6 +182,7 @@ class LanguageModelEmbedding(nn.Module):
         self.word_embeddings = ParamHolder(weight=_param((V, cfg.hidden_size), cfg.init_method_std, cfg.torch_dtype, device))
         self.word_embeddings.weight.tensor_model_parallel = tp > 1
         self.word_embeddings.weight.partition_dim = 0
+        self.word_embeddings.weight._fp8_exempt = True   # also the LM head when embeddings are tied
         self.vocab_local = V
 
     def forward(self, tokens_flat):
@@ -227,6 +228,7 @@ class GPTModel(nn.Module):
                 weight=_param((cfg.padded_vocab_size // tp, cfg.hidden_size), cfg.init_method_std, cfg.torch_dtype, device))
             self.output_layer.weight.tensor_model_parallel = tp > 1
             self.output_layer.weight.partition_dim = 0
+            self.output_layer.weight._fp8_exempt = True   # the LM head stays in bf16 under an fp8 recipe
         self._rope_cache = {}
 
     # ------------------------------------------------------------------ helpers

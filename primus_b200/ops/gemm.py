@@ -18,6 +18,68 @@ from . import _lib
 
 _BLOCK_N_OVERRIDE: int | None = None
 
+# ----------------------------------------------------------------------------------------------
+# FP8 recipe: with ``set_fp8_recipe("mxfp8")`` every eligible GEMM (all dimensions multiples of 128, no operand
+# marked ``_fp8_exempt``) quantises its operands to MXFP8 on the fly and runs on the block-scaled kernel.
+# Weights are quantised (both directions) once per optimizer step; activations / gradients go through a
+# two-entry cache so that a gradient used by the data- and the weight-gradient GEMM is read once.
+_FP8_RECIPE: str | None = None
+_WEIGHT_GEN = 0
+_W_CACHE: dict = {}
+_ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
+
+
+def set_fp8_recipe(recipe: str | None) -> None:
+    global _FP8_RECIPE
+    assert recipe in (None, "", "mxfp8"), f"unsupported fp8 recipe {recipe!r}"
+    _FP8_RECIPE = recipe or None
+    _W_CACHE.clear()
+    _ACT_CACHE.clear()
+
+
+def fp8_recipe() -> str | None:
+    return _FP8_RECIPE
+
+
+def bump_weight_generation() -> None:
+    """Call after parameters changed in place (optimizer step, checkpoint load): cached quantised weights expire."""
+    global _WEIGHT_GEN
+    _WEIGHT_GEN += 1
+    _ACT_CACHE.clear()
+
+
+def _quantized(t: torch.Tensor, direction: str, single_use: bool = False):
+    """(values, scales) of ``t`` quantised along ``direction`` ("row": blocks along the last dim, "col": along dim 0)."""
+    from . import fp8
+
+    if isinstance(t, torch.nn.Parameter) or getattr(t, "_is_weight", False):
+        hit = _W_CACHE.get(id(t))
+        if hit is None or hit[0] != _WEIGHT_GEN or hit[1] != t.data_ptr():
+            hit = (_WEIGHT_GEN, t.data_ptr(), fp8.quantize_mxfp8(t.detach(), True, True))
+            _W_CACHE[id(t)] = hit
+        q = hit[2]
+    else:
+        key = (t.data_ptr(), tuple(t.shape), t._version)
+        q = None
+        for k_, _, q_ in _ACT_CACHE:
+            if k_ == key and getattr(q_, "q_" + direction) is not None:
+                q = q_
+                break
+        if q is None:
+            both = not torch.is_grad_enabled() and not single_use   # backward pass: a gradient feeds two GEMMs
+            q = fp8.quantize_mxfp8(t, both or direction == "row", both or direction == "col")
+            _ACT_CACHE.insert(0, (key, t, q))
+            del _ACT_CACHE[2:]
+    return (q.q_row, q.sf_row) if direction == "row" else (q.q_col, q.sf_col)
+
+
+def _fp8_eligible(a, b, out, M, N, K) -> bool:
+    if _FP8_RECIPE is None or (M % 128) or (N % 128) or (K % 128):
+        return False
+    if getattr(a, "_fp8_exempt", False) or getattr(b, "_fp8_exempt", False):
+        return False
+    return a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+
 
 def _pick_block_n(M: int, N: int) -> int:
     if _BLOCK_N_OVERRIDE:
@@ -35,6 +97,7 @@ def gemm(
     out_dtype: torch.dtype | None = None,
     accumulate: bool = False,
     max_ctas: int = 0,
+    fp8: bool | None = None,
 ) -> torch.Tensor:
     """D[M,N] (+)= A . B^T with fp32 accumulation. See module docstring for layouts."""
     assert a.dim() == 2 and b.dim() == 2
@@ -71,6 +134,12 @@ def gemm(
             out.zero_()
         return out
     mode = 0 if out_dtype == torch.bfloat16 else (2 if accumulate else 1)
+    if fp8 is not False and _fp8_eligible(a, b, out, M, N, K):
+        aq, asf = _quantized(a, "col" if a_mn else "row")
+        bq, bsf = _quantized(b, "col" if b_mn else "row", single_use=a_mn and b_mn)  # wgrad: B is the saved input
+        _lib.call("gemm_mxfp8", aq, asf, bq, bsf, out, M, N, K, aq.stride(0), bq.stride(0), out.stride(0),
+                  int(a_mn), int(b_mn), mode, 256 if N >= 256 else 128, max_ctas, _lib.status_word(a.device))
+        return out
     _lib.call(
         "gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn), int(b_mn), mode, _pick_block_n(M, N), max_ctas, _lib.status_word(a.device),
@@ -144,7 +213,8 @@ WGRAD_STORE = WGradStore()
 
 
 def _wgrad_into_main_grad(dy2, x2, weight):
-    gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.main_grad, accumulate=True)
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.main_grad, accumulate=True,
+         fp8=False if getattr(weight, "_fp8_exempt", False) else None)
     weight.grad_added_to_main_grad = True
     cb = getattr(weight, "_grad_ready_cb", None)
     if cb is not None:
@@ -160,7 +230,8 @@ def wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
             _wgrad_into_main_grad(dy2, x2, weight)
         return None
     if dy2.is_cuda:
-        return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype,
+                    fp8=False if getattr(weight, "_fp8_exempt", False) else None)
     return (dy2.float().t() @ x2.float()).to(weight.dtype)
 
 

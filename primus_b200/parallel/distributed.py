@@ -329,6 +329,9 @@ class DistributedOptimizer:
         lr = self.lr if lr is None else lr
         wd = self.weight_decay if weight_decay is None else weight_decay
         self.step_count += 1
+        from ..ops import gemm as _gemm
+
+        _gemm.bump_weight_generation()   # parameters change in place below: quantised copies expire
         if any(buf.symmetric for buf in self.buffers):
             return self._fused_step(lr, wd)
         self.compute_grad_norm()

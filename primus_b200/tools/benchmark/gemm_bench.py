@@ -52,6 +52,40 @@ def bench_shape(name, M, N, K, iters, compare):
     return rows
 
 
+def bench_shape_mxfp8(name, M, N, K, iters):
+    """MXFP8 GEMMs of a linear layer (operands pre-quantised: the GEMM kernel alone) and the quantisation kernel."""
+    from ...ops import fp8
+
+    if M % 128 or N % 128 or K % 128:
+        return []
+    n = rotating_count(M * K + N * K + M * N * 2)
+    xs = [fp8.quantize_mxfp8(torch.randn(M, K, device="cuda").bfloat16()) for _ in range(n)]
+    ws = [fp8.quantize_mxfp8((torch.randn(N, K, device="cuda") * 0.02).bfloat16()) for _ in range(n)]
+    dys = [fp8.quantize_mxfp8(torch.randn(M, N, device="cuda").bfloat16()) for _ in range(min(n, 4))]
+    xb = [torch.randn(M, K, device="cuda").bfloat16() for _ in range(min(n, 4))]
+    mg = torch.zeros(N, K, device="cuda")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    dx = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    fl = 2.0 * M * N * K
+    nd = len(dys)
+    runs = [("mxfp8 fprop", lambda i: fp8.gemm_mxfp8(xs[i % n].q_row, xs[i % n].sf_row, ws[i % n].q_row, ws[i % n].sf_row,
+                                                     M, N, K, out=out)),
+            ("mxfp8 dgrad", lambda i: fp8.gemm_mxfp8(dys[i % nd].q_row, dys[i % nd].sf_row, ws[i % n].q_col, ws[i % n].sf_col,
+                                                     M, K, N, b_mn=True, out=dx)),
+            ("mxfp8 wgrad+acc", lambda i: fp8.gemm_mxfp8(dys[i % nd].q_col, dys[i % nd].sf_col, xs[i % n].q_col,
+                                                         xs[i % n].sf_col, N, K, M, a_mn=True, b_mn=True, out=mg,
+                                                         accumulate=True))]
+    rows = []
+    for kind, fn in runs:
+        t = time_cuda(fn, iters)
+        rows.append({"gemm": name, "kind": kind, "M": M, "N": N, "K": K, "ms": t["ms_median"],
+                     "TFLOP/s": fl / t["ms_median"] / 1e9})
+    t = time_cuda(lambda i: fp8.quantize_mxfp8(xb[i % len(xb)]), iters)
+    rows.append({"gemm": name, "kind": "quantize row+col (GB/s in TFLOP/s column)", "M": M, "N": 0, "K": K,
+                 "ms": t["ms_median"], "TFLOP/s": M * K * (2 + 2 + 1 / 16) / t["ms_median"] / 1e6})
+    return rows
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--suite", default=None, help="model preset name (e.g. llama3.1_8B, llama3.1_70B, deepseek_v2_lite)")
@@ -60,6 +94,7 @@ def main(argv=None):
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-compare", action="store_true")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "mxfp8", "both"])
     ap.add_argument("--output", default=None)
     a = ap.parse_args(argv)
     shapes = [(f"{m}x{n}x{k}", m, n, k) for m, n, k in (a.shape or [])]
@@ -69,8 +104,11 @@ def main(argv=None):
         shapes = [("square8192", 8192, 8192, 8192)]
     rows = []
     for s in shapes:
-        rows += bench_shape(*s, a.iters, not a.no_compare)
-    emit(rows, a.output, "bf16 GEMM")
+        if a.dtype in ("bf16", "both"):
+            rows += bench_shape(*s, a.iters, not a.no_compare)
+        if a.dtype in ("mxfp8", "both"):
+            rows += bench_shape_mxfp8(*s, a.iters)
+    emit(rows, a.output, "GEMM")
     return rows
 
 

@@ -84,3 +84,32 @@ def test_wgrad_accumulates_into_main_grad():
     err = (w.main_grad - 1.0 - dw_ref).abs().max().item()
     assert err <= 1e-2 * dw_ref.abs().max().item(), err
     assert w.grad is None
+
+
+def test_model_training_with_mxfp8_recipe_tracks_bf16():
+    """Same tiny model, same data: the MXFP8 recipe's loss trajectory stays close to the bf16 one."""
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import gemm
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    losses = {}
+    try:
+        for recipe in (None, "e4m3"):
+            mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2,
+                                   num_query_groups=2, vocab_size=1024, params_dtype="bf16", seq_length=256, fp8=recipe,
+                                   fp8_recipe="mxfp8")
+            tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=256, train_iters=6, lr=2e-3,
+                             lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1)
+            torch.manual_seed(0)
+            tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
+            assert gemm.fp8_recipe() == ("mxfp8" if recipe else None)
+            losses[recipe] = tr.train()
+            torch.cuda.synchronize()
+            _lib.check_status()
+    finally:
+        gemm.set_fp8_recipe(None)
+    a, b = losses[None], losses["e4m3"]
+    assert all(abs(x - y) <= 0.02 * abs(x) for x, y in zip(a, b)), (a, b)

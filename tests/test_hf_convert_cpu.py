@@ -1,0 +1,88 @@
+"""Weight conversion Hugging Face <-> engine: logits of the engine's model (plain PyTorch path, fp32, CPU) must match
+the Hugging Face implementation of the same architecture with the same random weights."""
+import pytest
+import torch
+
+from primus_b200.engine import hf_convert as H
+
+transformers = pytest.importorskip("transformers")
+
+
+def _engine_logits(hf_model, hf_cfg_dict, tokens, **extra):
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    kw = H.config_from_hf(hf_cfg_dict)
+    kw.update(params_dtype="fp32", seq_length=tokens.shape[1], make_vocab_size_divisible_by=8, **extra)
+    cfg = TransformerConfig(**kw)
+    model = GPTModel(cfg, "cpu")
+    sd = H.hf_to_internal({k: v.detach().clone() for k, v in hf_model.state_dict().items()}, cfg)
+    missing = [k for k in model.state_dict() if k not in sd]
+    assert not missing, missing
+    model.load_state_dict(sd, strict=True)
+    with torch.no_grad():
+        logits = model(tokens)
+    # round trip of the converter
+    back = H.internal_to_hf(sd, cfg, stacked_experts=any(k.endswith('experts.gate_up_proj') for k in hf_model.state_dict()))
+    for k, v in hf_model.state_dict().items():
+        if k in back:
+            assert torch.equal(back[k], v), k
+    return logits[:, : cfg.vocab_size], cfg
+
+
+def _check(hf_model, hf_cfg, tokens, tol=2e-4, **extra):
+    hf_model.eval()
+    with torch.no_grad():
+        ref = hf_model(tokens).logits.reshape(-1, hf_cfg.vocab_size)
+    got, _ = _engine_logits(hf_model, hf_cfg.to_dict(), tokens, **extra)
+    err = (got - ref).abs().max().item()
+    assert err <= tol * max(1.0, ref.abs().max().item()), (err, ref.abs().max().item())
+
+
+def test_llama_matches_hf():
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    c = LlamaConfig(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=250, rope_theta=500000.0, rms_norm_eps=1e-5,
+                    max_position_embeddings=128, tie_word_embeddings=False, attention_bias=False)
+    _check(LlamaForCausalLM(c), c, torch.randint(0, 250, (2, 24)))
+
+
+def test_qwen3_dense_matches_hf():
+    Q = pytest.importorskip("transformers.models.qwen3")
+    torch.manual_seed(1)
+    c = Q.Qwen3Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=32, vocab_size=250, rope_theta=1e6, max_position_embeddings=128,
+                      tie_word_embeddings=False)
+    _check(Q.Qwen3ForCausalLM(c), c, torch.randint(0, 250, (1, 20)))
+
+
+def test_qwen3_moe_matches_hf():
+    Q = pytest.importorskip("transformers.models.qwen3_moe")
+    torch.manual_seed(2)
+    c = Q.Qwen3MoeConfig(hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=250, num_experts=8,
+                         num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+                         max_position_embeddings=128, tie_word_embeddings=False, router_aux_loss_coef=0.0)
+    _check(Q.Qwen3MoeForCausalLM(c), c, torch.randint(0, 250, (1, 16)))
+
+
+def test_deepseek_v3_matches_hf():
+    D = pytest.importorskip("transformers.models.deepseek_v3")
+    torch.manual_seed(3)
+    c = D.DeepseekV3Config(hidden_size=64, intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8, n_shared_experts=1,
+                           num_experts_per_tok=2, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16,
+                           qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, n_group=2, topk_group=1,
+                           routed_scaling_factor=2.5, norm_topk_prob=True, vocab_size=250, max_position_embeddings=128,
+                           rope_scaling=None, tie_word_embeddings=False)
+    m = D.DeepseekV3ForCausalLM(c)
+    with torch.no_grad():  # make the selection bias matter
+        for layer in m.model.layers[1:]:
+            layer.mlp.gate.e_score_correction_bias.copy_(torch.randn(8) * 0.1)
+            layer.mlp.gate.weight.copy_(torch.randn_like(layer.mlp.gate.weight) * 0.5)
+    _check(m, c, torch.randint(0, 250, (1, 16)))

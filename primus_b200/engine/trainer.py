@@ -50,6 +50,11 @@ class TrainConfig:
     adam_eps: float = 1e-8
     clip_grad: float = 1.0
     use_distributed_optimizer: bool = True
+    optimizer: str = "adam"          # adam | sgd | muon (sgd / muon need use_distributed_optimizer = false)
+    sgd_momentum: float = 0.9
+    muon_momentum: float = 0.95
+    muon_use_nesterov: bool = True
+    muon_num_ns_steps: int = 5
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     ddp_bucket_size: Optional[int] = None
@@ -178,8 +183,16 @@ class Trainer:
                 expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
                 train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream))
         norm_groups = [st.mp_group] if (st.tp > 1 or st.pp > 1) else []
-        self.optimizer = DistributedOptimizer(
-            self.buffers, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
+        from ..parallel import matrix_optimizers
+
+        extra = {}
+        if train_cfg.optimizer.lower() == "sgd":
+            extra = dict(sgd_momentum=train_cfg.sgd_momentum)
+        elif train_cfg.optimizer.lower() == "muon":
+            extra = dict(muon_momentum=train_cfg.muon_momentum, muon_use_nesterov=train_cfg.muon_use_nesterov,
+                         muon_num_ns_steps=train_cfg.muon_num_ns_steps)
+        self.optimizer = matrix_optimizers.build(
+            train_cfg.optimizer, self.buffers, **extra, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
             check_for_nan=train_cfg.check_for_nan_in_loss_and_grad)
         self.scheduler = schedules.LRScheduler(

@@ -131,19 +131,36 @@ def dequantize_mxfp8(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.
     return out
 
 
+# CTA-pair kernel (256 x 256 tiles, csrc/gemm_mxfp8_2cta.cu) for problems with at least this many rows / columns;
+# None disables it.
+TWO_CTA_MIN_DIM: Optional[int] = None
+
+
+def launch_gemm(a_q, a_sf, b_q, b_sf, out, M: int, N: int, K: int, a_mn: bool, b_mn: bool, mode: int,
+                block_n: Optional[int] = None, max_ctas: int = 0, two_cta: Optional[bool] = None) -> None:
+    dev = out.device
+    if two_cta is None:
+        two_cta = TWO_CTA_MIN_DIM is not None and M >= TWO_CTA_MIN_DIM and N >= TWO_CTA_MIN_DIM and block_n in (None, 256)
+    if two_cta:
+        _lib.call("gemm_mxfp8_2cta", a_q, a_sf, b_q, b_sf, out, M, N, K, a_q.stride(0), b_q.stride(0), out.stride(0),
+                  int(a_mn), int(b_mn), mode, max_ctas, _lib.status_word(dev))
+        return
+    if block_n is None:
+        block_n = 256 if N >= 256 else 128
+    _lib.call("gemm_mxfp8", a_q, a_sf, b_q, b_sf, out, M, N, K, a_q.stride(0), b_q.stride(0), out.stride(0),
+              int(a_mn), int(b_mn), mode, block_n, max_ctas, _lib.status_word(dev))
+
+
 def gemm_mxfp8(a_q, a_sf, b_q, b_sf, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False,
                out: Optional[torch.Tensor] = None, accumulate: bool = False, out_dtype=torch.bfloat16,
-               block_n: Optional[int] = None) -> torch.Tensor:
+               block_n: Optional[int] = None, two_cta: Optional[bool] = None) -> torch.Tensor:
     """D[M, N] (=|+=) A . B^T with MXFP8 operands.  ``a_q``: [M, K] (``a_mn`` False) or [K, M] (True); likewise
     ``b_q`` with N.  fp32 ``out`` with ``accumulate`` adds into it (main-grad accumulation)."""
     dev = a_q.device
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=dev)
     mode = 0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1)
-    if block_n is None:
-        block_n = 256 if N >= 256 else 128
-    _lib.call("gemm_mxfp8", a_q, a_sf, b_q, b_sf, out, M, N, K, a_q.stride(0), b_q.stride(0), out.stride(0),
-              int(a_mn), int(b_mn), mode, block_n, 0, _lib.status_word(dev))
+    launch_gemm(a_q, a_sf, b_q, b_sf, out, M, N, K, a_mn, b_mn, mode, block_n, 0, two_cta)
     return out
 
 

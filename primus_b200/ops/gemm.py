@@ -137,8 +137,9 @@ def gemm(
     if fp8 is not False and _fp8_eligible(a, b, out, M, N, K):
         aq, asf = _quantized(a, "col" if a_mn else "row")
         bq, bsf = _quantized(b, "col" if b_mn else "row", single_use=a_mn and b_mn)  # wgrad: B is the saved input
-        _lib.call("gemm_mxfp8", aq, asf, bq, bsf, out, M, N, K, aq.stride(0), bq.stride(0), out.stride(0),
-                  int(a_mn), int(b_mn), mode, 256 if N >= 256 else 128, max_ctas, _lib.status_word(a.device))
+        from . import fp8 as _fp8
+
+        _fp8.launch_gemm(aq, asf, bq, bsf, out, M, N, K, a_mn, b_mn, mode, None, max_ctas)
         return out
     _lib.call(
         "gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),

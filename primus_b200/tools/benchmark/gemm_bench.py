@@ -68,13 +68,17 @@ def bench_shape_mxfp8(name, M, N, K, iters):
     dx = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
     fl = 2.0 * M * N * K
     nd = len(dys)
-    runs = [("mxfp8 fprop", lambda i: fp8.gemm_mxfp8(xs[i % n].q_row, xs[i % n].sf_row, ws[i % n].q_row, ws[i % n].sf_row,
-                                                     M, N, K, out=out)),
-            ("mxfp8 dgrad", lambda i: fp8.gemm_mxfp8(dys[i % nd].q_row, dys[i % nd].sf_row, ws[i % n].q_col, ws[i % n].sf_col,
-                                                     M, K, N, b_mn=True, out=dx)),
-            ("mxfp8 wgrad+acc", lambda i: fp8.gemm_mxfp8(dys[i % nd].q_col, dys[i % nd].sf_col, xs[i % n].q_col,
-                                                         xs[i % n].sf_col, N, K, M, a_mn=True, b_mn=True, out=mg,
-                                                         accumulate=True))]
+    runs = []
+    for tag, two in (("mxfp8", False), ("mxfp8 cta-pair", True)):
+        runs += [(f"{tag} fprop", lambda i, two=two: fp8.gemm_mxfp8(xs[i % n].q_row, xs[i % n].sf_row, ws[i % n].q_row,
+                                                                    ws[i % n].sf_row, M, N, K, out=out, two_cta=two)),
+                 (f"{tag} dgrad", lambda i, two=two: fp8.gemm_mxfp8(dys[i % nd].q_row, dys[i % nd].sf_row, ws[i % n].q_col,
+                                                                    ws[i % n].sf_col, M, K, N, b_mn=True, out=dx,
+                                                                    two_cta=two)),
+                 (f"{tag} wgrad+acc", lambda i, two=two: fp8.gemm_mxfp8(dys[i % nd].q_col, dys[i % nd].sf_col,
+                                                                        xs[i % n].q_col, xs[i % n].sf_col, N, K, M,
+                                                                        a_mn=True, b_mn=True, out=mg, accumulate=True,
+                                                                        two_cta=two))]
     rows = []
     for kind, fn in runs:
         t = time_cuda(fn, iters)

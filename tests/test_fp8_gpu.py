@@ -113,3 +113,26 @@ def test_model_training_with_mxfp8_recipe_tracks_bf16():
         gemm.set_fp8_recipe(None)
     a, b = losses[None], losses["e4m3"]
     assert all(abs(x - y) <= 0.02 * abs(x) for x, y in zip(a, b)), (a, b)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024)])
+def test_cta_pair_gemm_all_layouts(M, N, K):
+    """256 x 256 tiles on CTA pairs: forward, data-gradient and weight-gradient operand layouts."""
+    torch.manual_seed(4)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    xq, wq, dyq = fp8.quantize_mxfp8(x), fp8.quantize_mxfp8(w), fp8.quantize_mxfp8(dy)
+    y = fp8.gemm_mxfp8(xq.q_row, xq.sf_row, wq.q_row, wq.sf_row, M, N, K, two_cta=True)
+    dx = fp8.gemm_mxfp8(dyq.q_row, dyq.sf_row, wq.q_col, wq.sf_col, M, K, N, b_mn=True, two_cta=True)
+    dw = torch.ones(N, K, dtype=torch.float32, device="cuda")
+    fp8.gemm_mxfp8(dyq.q_col, dyq.sf_col, xq.q_col, xq.sf_col, N, K, M, a_mn=True, b_mn=True, out=dw, accumulate=True,
+                   two_cta=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    y_ref = _ref_gemm(xq.q_row, xq.sf_row, False, wq.q_row, wq.sf_row, False, False, False)
+    dx_ref = fp8.dequantize_mxfp8(dyq.q_row, dyq.sf_row, False) @ fp8.dequantize_mxfp8(wq.q_col, wq.sf_col, True)
+    dw_ref = fp8.dequantize_mxfp8(dyq.q_col, dyq.sf_col, True).t() @ fp8.dequantize_mxfp8(xq.q_col, xq.sf_col, True)
+    for got, ref, name in ((y, y_ref, "y"), (dx, dx_ref, "dx"), (dw - 1.0, dw_ref, "dw")):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 1.5e-2 * ref.abs().max().item(), (name, err, ref.abs().max().item())

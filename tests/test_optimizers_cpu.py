@@ -1,0 +1,56 @@
+"""SGD / Muon update rules, evaluation loop and tokenizer builder (CPU)."""
+import torch
+
+from primus_b200.parallel import matrix_optimizers as MO
+
+
+def test_newton_schulz_orthogonalises():
+    torch.manual_seed(0)
+    for shape in ((64, 32), (32, 96), (48, 48)):
+        m = torch.randn(*shape)
+        o = MO.newton_schulz(m, steps=8)
+        s = torch.linalg.svdvals(o)
+        assert s.max() < 1.3 and s.min() > 0.5, (shape, s.min().item(), s.max().item())
+        u, _, vt = torch.linalg.svd(m, full_matrices=False)
+        cos = torch.nn.functional.cosine_similarity((u @ vt).flatten(), o.flatten(), dim=0)
+        assert cos > 0.98
+
+
+def _train(optimizer, iters=8, **kw):
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc = TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=128,
+                           params_dtype="fp32", seq_length=32)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=32, train_iters=iters, lr=kw.pop("lr", 2e-2),
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1, optimizer=optimizer,
+                     use_distributed_optimizer=optimizer == "adam", data_seed=3, **kw)
+    torch.manual_seed(0)
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    # a fixed batch so that the loss has to go down
+    fixed = tr.stager.next_step()
+    tr.stager.next_step = lambda: fixed
+    tr.stager.prefetch = lambda: None
+    return tr, tr.train()
+
+
+def test_sgd_and_muon_reduce_the_loss_on_a_fixed_batch():
+    for name, lr in (("sgd", 0.3), ("muon", 2e-2), ("adam", 1e-2)):
+        _, losses = _train(name, lr=lr)
+        assert losses[-1] < losses[0] - 0.3, (name, losses)
+
+
+def test_evaluation_and_tokenizer():
+    from primus_b200.engine import tokenizer as T
+
+    tr, _ = _train("adam", iters=2, eval_interval=1, eval_iters=2)
+    assert "validation_loss" in tr.last_metrics and tr.last_metrics["validation_loss"] > 0
+    tok = T.build_tokenizer("NullTokenizer", vocab_size=1000, make_vocab_size_divisible_by=128)
+    assert tok.vocab_size == 1001 and tok.eod == 1000 and tok.padded_vocab_size == 1024
+    assert tok.tokenize("5 17 999") == [5, 17, 999] and tok.detokenize([1, 2]) == "1 2"
+    import pytest
+    with pytest.raises(ValueError):
+        T.build_tokenizer("Llama3Tokenizer")

@@ -57,6 +57,7 @@ class Experiment:
     platform: dict
     env: dict
     modules: dict[str, ModuleConfig] = field(default_factory=dict)
+    schema_findings: list = field(default_factory=list)   # unknown / misplaced keys (core/config/schema_check.py)
 
     @property
     def exp_root_path(self) -> str:
@@ -128,6 +129,9 @@ def load_experiment(path: str, cli_overrides: Optional[dict] = None, module_for_
     platform = load_preset(plat_spec.get("config", "platform_local.yaml"), "platforms")
     platform = deep_merge(platform, plat_spec.get("overrides") or {})
     exp = Experiment(path=str(path), meta=meta, platform=platform, env=dict(raw.get("env") or {}))
+    from . import schema_check
+
+    exp.schema_findings = schema_check.check_experiment(raw, cli_overrides)
     for name, spec in (raw.get("modules") or {}).items():
         if "trainer" not in name:
             continue

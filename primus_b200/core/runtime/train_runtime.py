@@ -70,6 +70,10 @@ class PrimusRuntime:
         self.ctx.module_name = module_name
         self.ctx.params = exp.module(module_name).params
         apply_env_block(exp)
+        for finding in exp.schema_findings:   # typos must not turn into silently ignored settings
+            print(f"[primus_b200][config][WARNING] {finding}", flush=True)
+        if os.environ.get("PRIMUS_STRICT_CONFIG", "0") == "1" and exp.schema_findings:
+            raise KeyError("unknown configuration keys: " + "; ".join(exp.schema_findings))
         if self.export_config:
             exp.dump(self.export_config)
 

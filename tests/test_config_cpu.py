@@ -148,3 +148,23 @@ def test_builtin_build_args_patches(tmp_path):
     bad = R.PatchContext(phase="build_args", params={"use_turbo_mega_moe": True, "expert_model_parallel_size": 16})
     with pytest.raises(ValueError):
         R.run_patches("build_args", bad)
+
+
+def test_schema_check_flags_unknown_keys_with_suggestions(tmp_path):
+    from primus_b200.core.config import schema_check
+    from primus_b200.core.config.experiment import load_experiment
+
+    known = schema_check.known_keys("pre_trainer.yaml", "llama3.1_8B.yaml")
+    assert {"micro_batch_size", "num_layers", "use_turbo_mega_moe", "moe_fused_capacity_factor"} <= known
+    recs = schema_check.check_keys(["micro_batch_sizes", "num_layers", "totally_new_key"], known)
+    assert [r["key"] for r in recs] == ["micro_batch_sizes", "totally_new_key"]
+    assert "micro_batch_size" in recs[0]["suggestions"] and recs[1]["suggestions"] == []
+    cfg = tmp_path / "exp.yaml"
+    cfg.write_text(
+        "work_group: g\nuser_name: u\nexp_name: e\nworkspace: " + str(tmp_path) + "\n"
+        "modules:\n  pre_trainer:\n    framework: primus_b200\n    config: pre_trainer.yaml\n    model: llama3.1_8B.yaml\n"
+        "    overrides:\n      train_iter: 5\n      micro_batch_size: 1\n")
+    exp = load_experiment(str(cfg), {"global_batchsize": 8}, "pre_trainer")
+    joined = " ".join(exp.schema_findings)
+    assert "train_iter" in joined and "train_iters" in joined and "global_batchsize" in joined
+    assert "micro_batch_size'" not in joined

@@ -354,6 +354,12 @@ PB_DEVICE void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
       "r"(r[15])
       : "memory");
 }
+PB_DEVICE void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+      : "memory");
+}
 
 // Named barrier among a subset of warps (id 1..15; 0 is __syncthreads).
 PB_DEVICE void named_bar_sync(int id, int nthreads) {

@@ -7,10 +7,15 @@
 //   MODE_DQ  : a CTA owns 128 query rows of one head (X1 = Q, X2 = dO) and streams 64-row tiles of
 //              K / V;  S = Q K^T, dP = dO V^T  ->  dS  ->  dQ += dS K.
 // In both modes the accumulators live in tensor memory for the whole loop (no atomics, results are
-// bit-reproducible), the S / dP tiles are double-buffered in TMEM where capacity allows, the
+// bit-reproducible), the S / dP tiles are double-buffered in TMEM where capacity allows, and the
 // streamed tiles are used twice from one shared-memory copy (K-major operand for the first GEMM,
-// MN-major operand for the second), and the 128 softmax threads (one per resident row) turn
-// S / dP into bf16 P / dS tiles in 128B-swizzled shared memory.
+// MN-major operand for the second).  The softmax threads turn S / dP into bf16 P / dS *in tensor memory*:
+// a thread overwrites the first 8 of its own 16 S (dP) columns with the packed pair values, and the second
+// GEMM takes its A operand from there (`tcgen05.mma` with A in TMEM), one 16-wide K step per column group.
+// Nothing but mbarriers goes through shared memory between the two GEMMs of a step.  The per-step chain of
+// a softmax thread (TMEM load -> exp2 / multiply -> TMEM store -> arrive) is latency bound, so two teams of
+// 128 threads work on alternating steps (each thread owns one row and all 64 columns of its step) while
+// the MMA thread runs two steps ahead.
 //
 // Replaces the backward of `flash_attn_func` (primus/backends/megatron/core/extensions/
 // primus_turbo.py:812-823); deterministic by construction (cf. the `deterministic=` flag there, :805).
@@ -22,10 +27,9 @@ namespace {
 
 constexpr int BR = 128;  // resident rows
 constexpr int BC = 64;   // streamed rows per step
-constexpr int BW_THREADS = 576;   // warp0 TMA, warp1 MMA, warps 2..17: four compute warpgroups
-constexpr int BW_COMPUTE = 512;
-constexpr int BW_WGS = 4;
-constexpr int BW_COLS = BC / BW_WGS;  // streamed-tile columns per compute thread (16)
+constexpr int BW_THREADS = 320;   // warp0 TMA, warp1 MMA, warps 2..9: two softmax teams of 128 threads
+constexpr int BW_COMPUTE = 256;
+constexpr int BW_TEAMS = 2;       // team t handles steps i = t (mod 2): one thread per resident row, all 64 columns
 constexpr int XATOM = 128 * 128;  // bytes of a [128 rows x 64 bf16] atom
 constexpr int YATOM = 64 * 128;   // bytes of a [64 rows x 64 bf16] atom
 enum { MODE_DKDV = 0, MODE_DQ = 1 };
@@ -39,8 +43,7 @@ struct BwCfg {
   static constexpr int Y1_BYTES = BC * DQK * 2;
   static constexpr int Y2_BYTES = BC * DV * 2;
   static constexpr int STAT_BYTES = 512;  // 64 lse + 64 delta
-  static constexpr int P_BYTES = BR * BC * 2;
-  static constexpr int FIXED_BYTES = X1_BYTES + X2_BYTES + 2 * P_BYTES + 1024 + 512;
+  static constexpr int FIXED_BYTES = X1_BYTES + X2_BYTES + 1024 + 512;
   static constexpr int STAGE_BYTES = Y1_BYTES + Y2_BYTES + STAT_BYTES;
   static constexpr int NS_FIT = (232448 - FIXED_BYTES) / STAGE_BYTES;
   // streamed-tile ring depth: a stage is held from the first GEMM (S/dP) to the last (dK/dQ) of its
@@ -52,9 +55,9 @@ struct BwCfg {
 struct BwBars {
   uint64_t x_full;
   uint64_t y_full[4], y_empty[4];
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full;
-  uint64_t pds_free;
+  uint64_t s_full[2];
+  uint64_t p_ready[2]; // per team: P / dS of its current step are in tensor memory (one arrival per warp)
+  uint64_t acc_done;   // all MMAs of the CTA have completed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -98,9 +101,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   uint8_t* x2_smem = x1_smem + C::X1_BYTES;
   uint8_t* y1_smem = x2_smem + C::X2_BYTES;           // NS stages
   uint8_t* y2_smem = y1_smem + C::NS * C::Y1_BYTES;   // NS stages
-  uint8_t* p_smem = y2_smem + C::NS * C::Y2_BYTES;
-  uint8_t* ds_smem = p_smem + C::P_BYTES;
-  float* stat_smem = reinterpret_cast<float*>(ds_smem + C::P_BYTES);  // NS stages x (64 lse, 64 delta)
+  float* stat_smem = reinterpret_cast<float*>(y2_smem + C::NS * C::Y2_BYTES);  // NS stages x (64 lse, 64 delta)
   BwBars* bars = reinterpret_cast<BwBars*>(reinterpret_cast<uint8_t*>(stat_smem) + C::NS * C::STAT_BYTES);
 
   const int warp = threadIdx.x >> 5;
@@ -108,9 +109,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   const int g = hq / hkv;
   const int num_rb = seq / BR;
   const int num_c = seq / BC;
-  const int rb = (MODE == MODE_DKDV) ? blockIdx.x : (num_rb - 1 - blockIdx.x);
-  const int xhead = blockIdx.y;  // MODE_DKDV: kv head; MODE_DQ: query head
-  const int batch = blockIdx.z;
+  // grid (heads * batch, row blocks): blocks are issued x-fastest, so all heads of the longest row block start
+  // first and the short ones fill the tail (work per block is proportional to the number of streamed tiles)
+  const int rb = (MODE == MODE_DKDV) ? blockIdx.y : (num_rb - 1 - blockIdx.y);
+  const int nxh = (MODE == MODE_DKDV) ? hkv : hq;
+  const int xhead = blockIdx.x % nxh;  // MODE_DKDV: kv head; MODE_DQ: query head
+  const int batch = blockIdx.x / nxh;
   const int tok0 = batch * seq;
   // streamed-tile schedule
   const int c_start = (MODE == MODE_DKDV && causal) ? 2 * rb : 0;
@@ -125,12 +129,9 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       pb::mbar_init(&bars->y_full[i], 1);
       pb::mbar_init(&bars->y_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      pb::mbar_init(&bars->s_full[i], 1);
-      pb::mbar_init(&bars->s_empty[i], BW_COMPUTE);
-    }
-    pb::mbar_init(&bars->p_full, BW_COMPUTE);
-    pb::mbar_init(&bars->pds_free, 1);
+    for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->s_full[i], 1);
+    for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->p_ready[i], BW_COMPUTE / BW_TEAMS / 32);
+    pb::mbar_init(&bars->acc_done, 1);
     bars->abort_flag = 0;
     pb::fence_barrier_init();
   }
@@ -184,7 +185,6 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       constexpr uint32_t idesc_a1 = pb::make_idesc_bf16(BR, DQK, 0, 1);  // acc(DQK) += dS . Y1
       constexpr uint32_t idesc_a2 = pb::make_idesc_bf16(BR, DV, 0, 1);   // acc(DV)  += P  . Y2
       const uint32_t x1a = pb::smem_u32(x1_smem), x2a = pb::smem_u32(x2_smem);
-      const uint32_t pa = pb::smem_u32(p_smem), dsa = pb::smem_u32(ds_smem);
       bool ok = true;
       auto issue_sdp = [&](int i) {
         const int st = i % C::NS;
@@ -201,52 +201,50 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
           pb::umma_f16_ss(ts + 64, pb::make_smem_desc(x2a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
                           pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
                           k > 0 ? 1u : 0u);
-        pb::umma_commit(&bars->s_full[i % C::SBUF]);
+        pb::umma_commit(&bars->s_full[i & 1]);   // one barrier per softmax team (even / odd steps), also with one TMEM buffer
       };
+      // The S / dP GEMMs run SBUF steps ahead.  Step i + SBUF reuses the TMEM buffer of step i; it is issued after
+      // the second GEMMs of step i (same thread: the tensor pipe keeps the order), which themselves wait for the
+      // softmax threads to have replaced S / dP of step i by P / dS.
       do {
         BW_WAIT(&bars->x_full, 0, PB_ERR_TIMEOUT_MMA);
-        BW_WAIT(&bars->y_full[0], 0, PB_ERR_TIMEOUT_MMA);
-        pb::tc_fence_after();
-        issue_sdp(0);
+        for (int j = 0; j < C::SBUF && j < n_iter && ok; ++j) {
+          BW_WAIT(&bars->y_full[j % C::NS], (j / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
+          pb::tc_fence_after();
+          issue_sdp(j);
+        }
       } while (false);
       for (int i = 0; i < n_iter && ok; ++i) {
         const int st = i % C::NS;
-        if (C::SBUF == 2 && i + 1 < n_iter) {
-          const int in = i + 1;
-          BW_WAIT(&bars->y_full[in % C::NS], (in / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
-          BW_WAIT(&bars->s_empty[in & 1], ((in >> 1) & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
-          pb::tc_fence_after();
-          issue_sdp(in);
-        }
-        BW_WAIT(&bars->p_full, i & 1, PB_ERR_TIMEOUT_MMA);
+        BW_WAIT(&bars->p_ready[i & 1], (i >> 1) & 1, PB_ERR_TIMEOUT_MMA);
         pb::tc_fence_after();
         const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
         const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
+        const uint32_t ts = tmem_sbuf + (i % C::SBUF) * 128;
         if (MODE == MODE_DKDV) {
 #pragma unroll
-          for (int k = 0; k < BC / 16; ++k)
-            pb::umma_f16_ss(tmem_base + DQK, pb::make_smem_desc(pa + k * 32, 0, 1024, 2),
-                            pb::make_smem_desc(y2a + k * 2048, YATOM, 1024, 2), idesc_a2, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BC / 16; ++k)   // acc(DV) += P . Y2, A = packed P of K step k (TMEM columns 16k .. 16k+7)
+            pb::umma_f16_ts(tmem_base + DQK, ts + 16 * k, pb::make_smem_desc(y2a + k * 2048, YATOM, 1024, 2), idesc_a2,
+                            (i > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
-        for (int k = 0; k < BC / 16; ++k)
-          pb::umma_f16_ss(tmem_base, pb::make_smem_desc(dsa + k * 32, 0, 1024, 2),
-                          pb::make_smem_desc(y1a + k * 2048, YATOM, 1024, 2), idesc_a1, (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < BC / 16; ++k)     // acc(DQK) += dS . Y1
+          pb::umma_f16_ts(tmem_base, ts + 64 + 16 * k, pb::make_smem_desc(y1a + k * 2048, YATOM, 1024, 2), idesc_a1,
+                          (i > 0 || k > 0) ? 1u : 0u);
         pb::umma_commit(&bars->y_empty[st]);
-        pb::umma_commit(&bars->pds_free);
-        if (C::SBUF == 1 && i + 1 < n_iter) {
-          const int in = i + 1;
+        if (i + C::SBUF < n_iter) {
+          const int in = i + C::SBUF;
           BW_WAIT(&bars->y_full[in % C::NS], (in / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
-          BW_WAIT(&bars->s_empty[0], (in & 1) ^ 1, PB_ERR_TIMEOUT_MMA);
           pb::tc_fence_after();
           issue_sdp(in);
         }
       }
+      if (ok) pb::umma_commit(&bars->acc_done);
     }
   } else {
     // ------------------------------------------------------------------ softmax-gradient threads
     const int wq = warp & 3;              // TMEM lane quarter of this warp
-    const int wg = (warp - 2) >> 2;       // compute warpgroup: owns columns [16*wg, 16*wg+16) of each step
+    const int team = (warp - 2) >> 2;     // 0 / 1: even / odd steps
     const int row = wq * 32 + lane;
     const uint32_t lane_addr = uint32_t(wq * 32) << 16;
     const int row_g = rb * BR + row;
@@ -257,11 +255,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       delta_row = delta[off];
     }
     bool ok = true;
-    for (int i = 0; i < n_iter && ok; ++i) {
+    for (int i = team; i < n_iter && ok; i += BW_TEAMS) {
       const int sb = i % C::SBUF;
       const int st = i % C::NS;
       const int cs = c_start + i % n_per_head;
-      BW_WAIT(&bars->s_full[sb], (C::SBUF == 2) ? ((i >> 1) & 1) : (i & 1), PB_ERR_TIMEOUT_EPILOGUE);
+      BW_WAIT(&bars->s_full[team], (i >> 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
       if (MODE == MODE_DKDV) {
         BW_WAIT(&bars->y_full[st], (i / C::NS) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // lse / delta tile visible
       }
@@ -270,70 +268,63 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       const bool diag = causal && (cs >= 2 * rb) && (cs <= 2 * rb + 1);
       const float* st_lse = stat_smem + st * 128;
       const float* st_delta = st_lse + 64;
-      uint32_t pk[BW_COLS / 2], dsk[BW_COLS / 2];
-      {
-        const int c0 = wg * BW_COLS;  // first column of this warpgroup's slice
-        uint32_t s[BW_COLS], dp[BW_COLS];
-        pb::tmem_ld_32x32b_x16(ts + c0, s);
-        pb::tmem_ld_32x32b_x16(ts + 64 + c0, dp);
-        float l2v[BW_COLS], dlv[BW_COLS];
-        if (MODE == MODE_DKDV) {
+      uint32_t s[BC], dp[BC];
+      pb::tmem_ld_32x32b_x32(ts, s);
+      pb::tmem_ld_32x32b_x32(ts + 32, s + 32);
+      pb::tmem_ld_32x32b_x32(ts + 64, dp);
+      pb::tmem_ld_32x32b_x32(ts + 96, dp + 32);
+      pb::tmem_wait_ld();
+      auto body = [&](auto diag_tag) {
+        constexpr bool DIAG = decltype(diag_tag)::value;
 #pragma unroll
-          for (int e = 0; e < BW_COLS; e += 4) {
-            *reinterpret_cast<float4*>(l2v + e) = *reinterpret_cast<const float4*>(st_lse + c0 + e);
-            *reinterpret_cast<float4*>(dlv + e) = *reinterpret_cast<const float4*>(st_delta + c0 + e);
-          }
-        }
-        pb::tmem_wait_ld();
-        auto body = [&](auto diag_tag) {
-          constexpr bool DIAG = decltype(diag_tag)::value;
+        for (int kk = 0; kk < BC / 16; ++kk) {   // one 16-wide K step of the second GEMM at a time
+          uint32_t pk[8], dsk[8];
 #pragma unroll
-          for (int e = 0; e < BW_COLS; e += 2) {
-            float pv[2], dv[2];
+          for (int e4 = 0; e4 < 16; e4 += 4) {
+            const int c = kk * 16 + e4;
+            float4 l4 = make_float4(lse2_row, lse2_row, lse2_row, lse2_row);
+            float4 d4 = make_float4(delta_row, delta_row, delta_row, delta_row);
+            if (MODE == MODE_DKDV) {
+              l4 = *reinterpret_cast<const float4*>(st_lse + c);
+              d4 = *reinterpret_cast<const float4*>(st_delta + c);
+            }
+            const float l2[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], dv[4];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const float l2 = (MODE == MODE_DKDV) ? l2v[e + u] : lse2_row;
-              const float dl = (MODE == MODE_DKDV) ? dlv[e + u] : delta_row;
-              float p = pb::fast_exp2(fmaf(__uint_as_float(s[e + u]), sl2, -l2));
+            for (int u = 0; u < 4; ++u) {
+              float p = pb::fast_exp2(fmaf(__uint_as_float(s[c + u]), sl2, -l2[u]));
               if (DIAG) {
-                const int col_g = cs * BC + c0 + e + u;
+                const int col_g = cs * BC + c + u;
                 const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
                 if (!valid) p = 0.f;
               }
               pv[u] = p;
-              dv[u] = p * (__uint_as_float(dp[e + u]) - dl) * scale;
+              dv[u] = p * (__uint_as_float(dp[c + u]) - dl[u]) * scale;
             }
-            pk[e / 2] = pb::pack_bf16x2(pv[0], pv[1]);
-            dsk[e / 2] = pb::pack_bf16x2(dv[0], dv[1]);
+            pk[e4 / 2] = pb::pack_bf16x2(pv[0], pv[1]);
+            pk[e4 / 2 + 1] = pb::pack_bf16x2(pv[2], pv[3]);
+            dsk[e4 / 2] = pb::pack_bf16x2(dv[0], dv[1]);
+            dsk[e4 / 2 + 1] = pb::pack_bf16x2(dv[2], dv[3]);
           }
-        };
-        if (diag) body(std::true_type{}); else body(std::false_type{});
-      }
+          // P / dS (bf16 pairs) replace the first 8 of the 16 S / dP columns of this K step
+          if (MODE == MODE_DKDV) pb::tmem_st_32x32b_x8(ts + 16 * kk, pk);
+          pb::tmem_st_32x32b_x8(ts + 64 + 16 * kk, dsk);
+        }
+      };
+      if (diag) body(std::true_type{}); else body(std::false_type{});
+      pb::tmem_wait_st();
       pb::tc_fence_before();
-      pb::mbar_arrive(&bars->s_empty[sb]);
-      if (i > 0) {
-        BW_WAIT(&bars->pds_free, (i - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // previous P / dS consumed
-      }
-#pragma unroll
-      for (int q2 = 0; q2 < BW_COLS / 8; ++q2) {
-        const int chunk = wg * (BW_COLS / 8) + q2;
-        const int off = row * 128 + ((chunk ^ (row & 7)) << 4);
-        if (MODE == MODE_DKDV)
-          *reinterpret_cast<uint4*>(p_smem + off) = make_uint4(pk[4 * q2], pk[4 * q2 + 1], pk[4 * q2 + 2], pk[4 * q2 + 3]);
-        *reinterpret_cast<uint4*>(ds_smem + off) =
-            make_uint4(dsk[4 * q2], dsk[4 * q2 + 1], dsk[4 * q2 + 2], dsk[4 * q2 + 3]);
-      }
-      pb::fence_proxy_async_smem();
-      pb::mbar_arrive(&bars->p_full);
+      __syncwarp();
+      if (lane == 0) pb::mbar_arrive(&bars->p_ready[team]);   // one arrival per warp
     }
     // ---- epilogue: accumulators -> bf16 -> (dead) resident tiles -> TMA store
     do {
       if (!ok) break;
-      BW_WAIT(&bars->pds_free, (n_iter - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      BW_WAIT(&bars->acc_done, 0, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
       auto drain = [&](uint32_t tcol, int ncols, uint8_t* dst) {
 #pragma unroll 1
-        for (int c = wg; c < ncols / 32; c += BW_WGS) {
+        for (int c = team; c < ncols / 32; c += BW_TEAMS) {
           uint32_t r[32];
           pb::tmem_ld_32x32b_x32(tmem_base + lane_addr + tcol + c * 32, r);
           pb::tmem_wait_ld();
@@ -453,7 +444,7 @@ int launch_bwd(const BwdArgs& a) {
       if (e != cudaSuccess) return (int)e;
       attr_set = true;
     }
-    dim3 grid(a.seq / BR, a.hkv, a.batch);
+    dim3 grid(a.hkv * a.batch, a.seq / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
                                                        a.hq, a.hkv, a.scale, a.causal, a.status);
   }
@@ -466,7 +457,7 @@ int launch_bwd(const BwdArgs& a) {
       if (e != cudaSuccess) return (int)e;
       attr_set = true;
     }
-    dim3 grid(a.seq / BR, a.hq, a.batch);
+    dim3 grid(a.hq * a.batch, a.seq / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
                                                        a.hq, a.hkv, a.scale, a.causal, a.status);
   }

@@ -82,9 +82,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int num_q128 = seq / BQ;
   const int num_pairs = (num_q128 + 1) / 2;
-  const int pair = num_pairs - 1 - blockIdx.x;  // heaviest (longest KV range) pairs first
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
+  // grid (heads * batch, pairs): x-fastest issue order starts all heads of the heaviest (longest KV range) pair first
+  const int pair = num_pairs - 1 - blockIdx.y;
+  const int head = blockIdx.x % hq;
+  const int batch = blockIdx.x / hq;
   const int kv_head = head / (hq / hkv);
   const int tok0 = batch * seq;
   const int qt[2] = {2 * pair, 2 * pair + 1};  // 128-row query tile indices
@@ -102,7 +103,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       pb::mbar_init(&bars->v_full[i], 1);
       pb::mbar_init(&bars->v_empty[i], 1);
       pb::mbar_init(&bars->s_full[i], 1);
-      pb::mbar_init(&bars->p_full[i], 128);
+      pb::mbar_init(&bars->p_full[i], 4);   // one arrival per softmax warp of the tile
       pb::mbar_init(&bars->pv_done[i], 1);
     }
     bars->abort_flag = 0;
@@ -279,7 +280,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       pb::tmem_wait_st();
       pb::tc_fence_before();
-      pb::mbar_arrive(&bars->p_full[t]);
+      __syncwarp();
+      if (lane == 0) pb::mbar_arrive(&bars->p_full[t]);   // 128 arrivals on one mbarrier would serialise
     }
     // epilogue: O / l -> bf16 -> shared (the tile's dead Q buffer) -> TMA store; log-sum-exp
     do {
@@ -351,7 +353,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((seq / BQ + 1) / 2, hq, batch);
+  dim3 grid(hq * batch, (seq / BQ + 1) / 2, 1);
   kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, hq, hkv,
                                                    scale * 1.4426950408889634f, causal, status);
   return (int)cudaGetLastError();

@@ -89,6 +89,16 @@ class TrainConfig:
     profile: bool = False
     profile_step_start: int = 3
     profile_step_end: int = 4
+    profile_ranks: Optional[list] = None
+    disable_profiler_activity_cpu: bool = False
+    record_memory_history: bool = False
+    memory_snapshot_path: Optional[str] = None
+    nvtx_ranges: bool = False
+    tensorboard_dir: Optional[str] = None     # also the directory of metrics.jsonl and profiler traces
+    disable_tensorboard: bool = True
+    wandb_project: Optional[str] = None
+    mlflow_experiment_name: Optional[str] = None
+    exp_name: str = "exp"
 
     @classmethod
     def from_dict(cls, d: dict) -> "TrainConfig":
@@ -353,15 +363,29 @@ class Trainer:
         guard = fault.LossGuard(tc.check_for_nan_in_loss_and_grad, tc.check_for_spiky_loss, 10.0, tc.check_for_large_grads)
         exit_flag = fault.GracefulExit() if tc.exit_signal_handler else None
         straggler = fault.StragglerDetector() if tc.log_straggler else None
+        from . import observability as obs
+
+        st = self.st
+        out_dir = tc.tensorboard_dir or (os.path.join(tc.save, "tensorboard") if tc.save else None)
+        profiler = obs.StepProfiler(tc.profile, st.rank, tc.profile_step_start, tc.profile_step_end, tc.profile_ranks,
+                                    os.path.join(out_dir, "profiler") if out_dir else None, tc.exp_name,
+                                    not tc.disable_profiler_activity_cpu, record_memory_history=tc.record_memory_history,
+                                    memory_snapshot_path=tc.memory_snapshot_path, log=self.log)
+        writer = obs.MetricsWriter(st.rank, st.rank == st.world_size - 1 or st.world_size == 1, out_dir,
+                                   not tc.disable_tensorboard, tc.wandb_project, tc.mlflow_experiment_name, tc.exp_name,
+                                   log=self.log)
         try:
             for _ in range(n):
                 t0 = time.perf_counter()
-                loss = self.train_step()
+                with obs.nvtx_range(f"iteration {self.iteration + 1}", tc.nvtx_ranges):
+                    loss = self.train_step()
+                profiler.step()
                 if self.iteration % tc.log_interval == 0 or on_step is not None:
                     lv = self.reduced_loss(loss)  # synchronises
                     dt = time.perf_counter() - t0
                     losses.append(lv)
                     self._log_step(lv, dt)
+                    writer.write(self.iteration, self.last_metrics)
                     problem = guard.check(lv, float(self.optimizer.grad_norm.item()))
                     if problem and not math.isfinite(lv):
                         raise FloatingPointError(f"iteration {self.iteration}: {problem}")
@@ -389,6 +413,8 @@ class Trainer:
                 if tc.exit_duration_in_mins and (time.time() - start_wall) / 60.0 > tc.exit_duration_in_mins:
                     break
         finally:
+            profiler.close()
+            writer.close()
             if exit_flag is not None:
                 exit_flag.restore()
             if self._gc_disabled:

@@ -279,6 +279,12 @@ class GPTModel(nn.Module):
             if sp:
                 y = tpc.gather_seq(y, st.tp_group)
             return gemm.linear(y, w)
+        if cfg.cross_entropy_chunk_tokens > 0 and loss_weights is not None and unit_upstream and st.tp == 1:
+            # chunked linear + cross entropy: no [tokens, vocab] logits tensor
+            y = fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual)[0] \
+                if residual is not None else fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon)
+            return layers.chunked_linear_cross_entropy(y, w, labels.reshape(-1), loss_weights.reshape(-1), 0,
+                                                       cfg.cross_entropy_chunk_tokens)
         logits, _ = layers.norm_linear(hidden, residual, self.decoder.final_layernorm.weight, w, cfg.norm_epsilon,
                                        st.tp_group, sp)
         vocab_local = w.shape[0]

@@ -278,6 +278,59 @@ def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=T
 
 
 # ----------------------------------------------------------------------------------------------
+# Chunked linear + cross entropy: the [T, V] logits are never materialised
+class ChunkedLinearCEFn(torch.autograd.Function):
+    """``sum_t weights[t] * CE(y[t] W^T, labels[t])`` computed ``chunk`` tokens at a time.
+
+    The cross-entropy kernel leaves the (already weighted) gradient in place of a chunk's logits, so the same
+    pass also produces ``dy`` for the chunk and accumulates ``dW``; only ``dy`` ([T, h]) is kept for backward.
+    This relies on the caller back-propagating a gradient of exactly 1 into the returned scalar (the trainer's
+    ``unit_upstream`` promise).  Same idea as the reference's fused linear cross entropy
+    (primus/backends/megatron/patches/fused_linear_ce_patches.py:48-100,171: chunks of 4096 tokens)."""
+
+    @staticmethod
+    def forward(ctx, y, w, labels, weights, vocab_start, chunk):
+        T = y.shape[0]
+        lab = labels.reshape(-1)
+        wts = weights.reshape(-1)
+        total = torch.zeros((), dtype=torch.float32, device=y.device)
+        dy = torch.empty_like(y)
+        dw_local = None
+        has_main = getattr(w, "main_grad", None) is not None
+        for s in range(0, T, chunk):
+            e = min(s + chunk, T)
+            yc = y[s:e]
+            logits = gemm.gemm(yc, w)
+            total += fused.cross_entropy(logits, lab[s:e], vocab_start, None, wts[s:e], True)
+            if y.is_cuda:
+                dlogits = logits                       # overwritten with the weighted gradient
+            else:
+                p = torch.softmax(logits.float(), -1)
+                p[torch.arange(e - s), lab[s:e]] -= 1.0
+                dlogits = (p * wts[s:e, None].float()).to(y.dtype)
+            dy[s:e] = gemm.gemm(dlogits, w, b_mn=True)
+            if has_main:
+                gemm.wgrad(dlogits, yc, w)
+            else:
+                g = gemm.gemm(dlogits, yc, a_mn=True, b_mn=True, out_dtype=torch.float32)
+                dw_local = g if dw_local is None else dw_local + g
+        ctx.save_for_backward(dy)
+        ctx.dw_local = dw_local
+        ctx.w_dtype = w.dtype
+        return total
+
+    @staticmethod
+    def backward(ctx, g):
+        (dy,) = ctx.saved_tensors
+        dw = ctx.dw_local.to(ctx.w_dtype) if ctx.dw_local is not None else None
+        return dy, dw, None, None, None, None   # upstream gradient is 1 by contract
+
+
+def chunked_linear_cross_entropy(y, w, labels, weights, vocab_start=0, chunk=4096):
+    return ChunkedLinearCEFn.apply(y, w, labels, weights, vocab_start, chunk)
+
+
+# ----------------------------------------------------------------------------------------------
 # Context parallelism (Ulysses): sequence-sharded activations, head-sharded attention
 class _SeqHeadAllToAll(torch.autograd.Function):
     """Equal-split all-to-all over the context-parallel group; the backward pass is the same exchange."""

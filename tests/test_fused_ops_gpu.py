@@ -154,3 +154,26 @@ def test_embedding_backward_main_grad():
     y.backward(dy)
     ref = torch.zeros(V, H, device="cuda").index_add_(0, tok, dy.float())
     _close(w.main_grad, ref, rtol=1e-3, atol=1e-3)
+
+
+def test_chunked_linear_cross_entropy_matches_full_gpu():
+    """Chunked linear + cross entropy (no [tokens, vocab] logits) gives the loss trajectory of the plain path."""
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import _lib
+    from primus_b200.parallel import state as ps
+
+    res = {}
+    for chunk in (0, 128):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2, vocab_size=2048,
+                               params_dtype="bf16", seq_length=256, cross_entropy_chunk_tokens=chunk)
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=256, train_iters=4, lr=1e-3,
+                         lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1)
+        torch.manual_seed(0)
+        tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
+        res[chunk] = tr.train()
+        torch.cuda.synchronize()
+        _lib.check_status()
+    assert all(abs(a - b) <= 5e-3 * max(1.0, abs(a)) for a, b in zip(res[0], res[128])), res

@@ -54,3 +54,37 @@ def test_evaluation_and_tokenizer():
     import pytest
     with pytest.raises(ValueError):
         T.build_tokenizer("Llama3Tokenizer")
+
+
+def test_chunked_linear_cross_entropy_matches_full():
+    """Same loss trajectory with and without the chunked linear + cross-entropy path."""
+    import dataclasses
+
+    res = {}
+    for chunk in (0, 24):
+        from primus_b200.engine.trainer import TrainConfig, Trainer
+        from primus_b200.models.config import TransformerConfig
+        from primus_b200.parallel import state as ps
+
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc = TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=128,
+                               params_dtype="fp32", seq_length=32, cross_entropy_chunk_tokens=chunk)
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=32, train_iters=4, lr=1e-2,
+                         lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1)
+        torch.manual_seed(0)
+        tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+        res[chunk] = tr.train()
+    assert all(abs(a - b) <= 1e-4 * max(1.0, abs(a)) for a, b in zip(res[0], res[24])), res
+
+
+def test_profiler_trace_and_metrics_jsonl(tmp_path):
+    import json
+
+    tr, _ = _train("adam", iters=5, profile=True, profile_step_start=2, profile_step_end=3,
+                   tensorboard_dir=str(tmp_path), exp_name="unit")
+    lines = [json.loads(l) for l in (tmp_path / "metrics.jsonl").read_text().splitlines()]
+    assert [l["iteration"] for l in lines] == [1, 2, 3, 4, 5]
+    assert {"loss", "tokens_per_s_gpu", "grad_norm", "lr"} <= set(lines[0])
+    traces = list((tmp_path / "profiler").glob("primus-b200-exp[[]unit[]]-rank[[]0[]].*.pt.trace.json"))
+    assert len(traces) == 1 and traces[0].stat().st_size > 1000

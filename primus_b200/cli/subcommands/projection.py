@@ -14,7 +14,7 @@ import json
 
 def register_subcommand(subparsers):
     p = subparsers.add_parser("projection", help="memory / performance projection")
-    p.add_argument("suite", choices=["memory", "performance", "both"])
+    p.add_argument("suite", choices=["memory", "performance", "both", "tune"])
     p.add_argument("--config", "--exp", dest="config", default=None)
     p.add_argument("--model", default=None, help="model preset name instead of an experiment file")
     p.add_argument("--hardware", default="b200")
@@ -27,6 +27,25 @@ def register_subcommand(subparsers):
     p.add_argument("--benchmark", action="store_true")
     p.add_argument("--json", action="store_true")
     p.set_defaults(func=run)
+
+
+def run_tune(args, overrides):
+    """``primus projection tune --model M --world N``: enumerate legal parallel plans, keep those that fit, rank."""
+    from ...tools.tuner import search as tuner
+
+    cfg, plan, hw, _, overlap = resolve(args, overrides)
+    res = tuner.search(cfg, hw, plan.world, plan.global_batch, plan.seq, top=10, comm_overlap=overlap or 0.7)
+    rows = [c.as_dict() for c in res["best"]]
+    if args.json:
+        print(json.dumps({"enumerated": res["enumerated"], "fit_in_memory": res["fit_in_memory"], "best": rows}))
+    else:
+        from tabulate import tabulate
+
+        print(f"{res['enumerated']} legal plans, {res['fit_in_memory']} fit in {hw.hbm_gb:.0f} GB")
+        print(tabulate(rows, headers="keys"))
+        if res["best"]:
+            print("\noverrides of the best plan:\n  " + " ".join(res["best"][0].overrides()))
+    return res
 
 
 def resolve(args, overrides):
@@ -107,6 +126,8 @@ def run(args, overrides):
     from ...tools.projection.memory import project_memory
     from ...tools.projection.performance import project_performance
 
+    if args.suite == "tune":
+        return run_tune(args, overrides)
     cfg, plan, hw, sched, overlap = resolve(args, overrides)
     errs = plan.validate(cfg)
     if errs:

@@ -48,24 +48,13 @@ __device__ __forceinline__ long sf_offset(int mn, int k_blk32, int k_groups) {
 constexpr int QPITCH = TILE + 16;  // bytes per row of the staged fp8 tiles (conflict-free 16-byte row accesses)
 constexpr int QUANT_SMEM = TILE * PITCH * 2 + 2 * TILE * QPITCH;
 
-__global__ void __launch_bounds__(256)
-quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
-                   uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
-  extern __shared__ __align__(16) uint8_t smem_q[];
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
-  uint8_t* qr = smem_q + TILE * PITCH * 2;
-  uint8_t* qc = qr + TILE * QPITCH;
-  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+// Quantises the 128 x 128 bf16 tile staged in `tile` (row pitch PITCH) whose origin in the [R, C] tensor is
+// (row0, col0).  Called by all threads of a 256-thread CTA after the tile is complete (caller synchronises before).
+__device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, uint8_t* qr, uint8_t* qc, int R, int C,
+                                                     int row0, int col0, uint8_t* __restrict__ q_row,
+                                                     uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
+                                                     uint8_t* __restrict__ sf_col) {
   const int tid = threadIdx.x;
-  // load 128 x 128 bf16 (16 vectors of 16 B per row)
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int v = tid + it * 256;
-    const int r = v >> 4, c8 = (v & 15) * 8;
-    const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
-    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
-  }
-  __syncthreads();
   if (q_row) {
     // thread -> (row r, two 32-element blocks): 64 contiguous bytes of the row
     const int r = tid & 127, half = tid >> 7;
@@ -137,6 +126,123 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
   }
 }
 
+__global__ void __launch_bounds__(256)
+quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
+                   uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  uint8_t* qr = smem_q + TILE * PITCH * 2;
+  uint8_t* qc = qr + TILE * QPITCH;
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int tid = threadIdx.x;
+  // load 128 x 128 bf16 (16 vectors of 16 B per row)
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
+  }
+  __syncthreads();
+  quantize_staged_tile(tile, qr, qc, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
+}
+
+__device__ __forceinline__ void bf8_load(const __nv_bfloat16* p, float* f) {
+  const uint4 d = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const float2 t = __bfloat1622float2(h[u]);
+    f[2 * u] = t.x;
+    f[2 * u + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 bf8_pack(const float* f) {
+  uint4 o;
+  o.x = pb::pack_bf16x2(f[0], f[1]);
+  o.y = pb::pack_bf16x2(f[2], f[3]);
+  o.z = pb::pack_bf16x2(f[4], f[5]);
+  o.w = pb::pack_bf16x2(f[6], f[7]);
+  return o;
+}
+
+// SwiGLU forward fused with the quantisation of its output: h1 [T, 2I] = [gate | up] -> MXFP8 of
+// act[T, I] = silu(gate) * up (rounded to bf16 first, so the values equal quantising the un-fused kernel's output).
+__global__ void __launch_bounds__(256)
+swiglu_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, int T, int I, float clamp, uint8_t* __restrict__ q_row,
+                          uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  uint8_t* qr = smem_q + TILE * PITCH * 2;
+  uint8_t* qc = qr + TILE * QPITCH;
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const __nv_bfloat16* g = h1 + (long)(row0 + r) * 2 * I + col0 + c8;
+    float fg[8], fu[8], o[8];
+    bf8_load(g, fg);
+    bf8_load(g + I, fu);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gg = fg[j], uu = fu[j];
+      if (clamp > 0.f) {
+        gg = fminf(gg, clamp);
+        uu = fminf(fmaxf(uu, -clamp), clamp);
+      }
+      const float sig = 1.f / (1.f + __expf(-gg));
+      o[j] = gg * sig * uu * 1.f;
+    }
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = bf8_pack(o);
+  }
+  __syncthreads();
+  quantize_staged_tile(tile, qr, qc, T, I, row0, col0, q_row, sf_row, q_col, sf_col);
+}
+
+// SwiGLU backward fused with the quantisation of its output: (h1 [T, 2I], dact [T, I]) -> MXFP8 (both directions) of
+// dh1 [T, 2I] = [dgate | dup].  Grid (I / 128, T / 128, 2): z selects the gate or the up half.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_bfloat16* __restrict__ dact, int T, int I,
+                              float clamp, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
+                              uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  uint8_t* qr = smem_q + TILE * PITCH * 2;
+  uint8_t* qc = qr + TILE * QPITCH;
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int up_half = blockIdx.z;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const __nv_bfloat16* g = h1 + (long)(row0 + r) * 2 * I + col0 + c8;
+    float fg[8], fu[8], fd[8], o[8];
+    bf8_load(g, fg);
+    bf8_load(g + I, fu);
+    bf8_load(dact + (long)(row0 + r) * I + col0 + c8, fd);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float gg = fg[j], uu = fu[j];
+      float gmask = 1.f, umask = 1.f;
+      if (clamp > 0.f) {
+        if (gg > clamp) { gg = clamp; gmask = 0.f; }
+        if (uu > clamp) { uu = clamp; umask = 0.f; }
+        if (uu < -clamp) { uu = -clamp; umask = 0.f; }
+      }
+      const float sig = 1.f / (1.f + __expf(-gg));
+      const float sl = gg * sig;
+      const float d = fd[j] * 1.f;
+      o[j] = up_half ? d * sl * umask : d * uu * sig * (1.f + gg * (1.f - sig)) * gmask;
+    }
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = bf8_pack(o);
+  }
+  __syncthreads();
+  quantize_staged_tile(tile, qr, qc, T, 2 * I, row0, up_half * I + col0, q_row, sf_row, q_col, sf_col);
+}
+
 // value [R, C] fp8 + scales (operand layout with MN = R or C) -> fp32 [R, C]; test / debugging helper
 __global__ void dequant_mxfp8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf, int R, int C,
                                      int colwise, float* __restrict__ out) {
@@ -168,6 +274,44 @@ int pb_quant_mxfp8(const void* x, int R, int C, void* q_row, void* sf_row, void*
   quant_mxfp8_kernel<<<grid, 256, SMEM, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), R, C,
                                          reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row),
                                          reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+static int set_quant_smem(const void* kern) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QUANT_SMEM);
+  return (int)e;
+}
+
+// act = silu(gate) * up of h1 [T, 2I] (T, I multiples of 128) quantised to MXFP8; either output pair may be null.
+int pb_swiglu_quant_mxfp8(const void* h1, int T, int I, float clamp, void* q_row, void* sf_row, void* q_col,
+                          void* sf_col, cudaStream_t s) {
+  if (T % TILE || I % TILE || T <= 0 || I <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    int rc = set_quant_smem(reinterpret_cast<const void*>(swiglu_quant_mxfp8_kernel));
+    if (rc) return rc;
+    attr_set = true;
+  }
+  swiglu_quant_mxfp8_kernel<<<dim3(I / TILE, T / TILE), 256, QUANT_SMEM, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(h1), T, I, clamp, reinterpret_cast<uint8_t*>(q_row),
+      reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+// dh1 [T, 2I] = swiglu backward of (h1, dact) quantised to MXFP8 (outputs sized for [T, 2I]).
+int pb_swiglu_bwd_quant_mxfp8(const void* h1, const void* dact, int T, int I, float clamp, void* q_row, void* sf_row,
+                              void* q_col, void* sf_col, cudaStream_t s) {
+  if (T % TILE || I % TILE || T <= 0 || I <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    int rc = set_quant_smem(reinterpret_cast<const void*>(swiglu_bwd_quant_mxfp8_kernel));
+    if (rc) return rc;
+    attr_set = true;
+  }
+  swiglu_bwd_quant_mxfp8_kernel<<<dim3(I / TILE, T / TILE, 2), 256, QUANT_SMEM, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(h1), reinterpret_cast<const __nv_bfloat16*>(dact), T, I, clamp,
+      reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col),
+      reinterpret_cast<uint8_t*>(sf_col));
   return (int)cudaGetLastError();
 }
 

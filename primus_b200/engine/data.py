@@ -33,6 +33,23 @@ class MockGPTDataset:
                 "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
 
 
+class PatternGPTDataset(MockGPTDataset):
+    """Learnable synthetic data: every sample repeats a random period of ``period`` tokens, so a model that attends
+    ``period`` tokens back predicts everything after the first period (used for loss-curve comparisons between
+    precisions; random tokens alone can only be fitted by their unigram statistics)."""
+
+    def __init__(self, vocab_size: int, seq_length: int, seed: int = 1234, period: int = 32):
+        super().__init__(vocab_size, seq_length, seed)
+        self.period = period
+
+    def __getitem__(self, idx: int) -> dict:
+        rng = np.random.Generator(np.random.PCG64([self.seed, idx]))
+        base = rng.integers(0, self.vocab_size, size=self.period, dtype=np.int64)
+        x = np.tile(base, self.seq_length // self.period + 2)[: self.seq_length + 1]
+        return {"tokens": torch.from_numpy(x[:-1].copy()), "labels": torch.from_numpy(x[1:].copy()),
+                "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
+
+
 class IndexedTokenDataset:
     """Memory-mapped token file (one flat int32/uint16 array) cut into fixed-length samples.
     ``path.bin`` holds the ids; an optional ``path.idx.npy`` holds document start offsets."""

@@ -188,6 +188,10 @@ def apply_lora(model: nn.Module, target_modules=("linear_qkv", "linear_proj", "l
     """Attach adapters to the ``weight`` of every matching parameter holder and keep a copy of the base weight.
     The layer keeps computing with its ordinary ``weight``, which holds the *effective* weight
     ``W_base + scale * B A`` (see :class:`LoRAEngine`), so the fused GEMM path is unchanged."""
+    from ..ops import gemm as _gemm
+
+    _gemm.FUSE_SWIGLU_QUANT = False   # adapters read the gradients of the wrapped linear layers directly
+
     adapters = {}
     for name, mod in model.named_modules():
         if name.split(".")[-1] in target_modules and hasattr(mod, "weight") and mod.weight.dim() == 2:

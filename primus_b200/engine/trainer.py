@@ -61,6 +61,7 @@ class TrainConfig:
     seed: int = 1234
     data_seed: int = 1234
     mock_data: bool = True
+    mock_data_period: int = 0          # > 0: learnable periodic sequences instead of uniform-random tokens
     data_path: Optional[str] = None
     log_interval: int = 1
     log_avg_skip_iterations: int = 2
@@ -212,7 +213,13 @@ class Trainer:
         # ---------------------------------------------------------------- data
         self.num_microbatches = schedules.num_microbatches(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp)
         if train_cfg.mock_data or not train_cfg.data_path:
-            ds = MockGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
+            if train_cfg.mock_data_period:
+                from .data import PatternGPTDataset
+
+                ds = PatternGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed,
+                                       train_cfg.mock_data_period)
+            else:
+                ds = MockGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
         else:
             from .data import IndexedTokenDataset
 

@@ -122,6 +122,37 @@ def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) 
     return out
 
 
+def swiglu_quantize_mxfp8(h1: torch.Tensor, clamp: float = 0.0, rowwise: bool = True, colwise: bool = False) -> MXFP8Tensor:
+    """MXFP8 of ``silu(gate) * up`` for ``h1 = [gate | up]`` [T, 2I] without materialising the bf16 activation
+    (values identical to quantising the un-fused SwiGLU output)."""
+    T, I2 = h1.shape
+    I = I2 // 2
+    dev = h1.device
+    out = MXFP8Tensor(shape=(T, I))
+    if rowwise:
+        out.q_row = torch.empty(T, I, dtype=torch.uint8, device=dev)
+        out.sf_row = torch.empty(T * I // BLOCK, dtype=torch.uint8, device=dev)
+    if colwise:
+        out.q_col = torch.empty(T, I, dtype=torch.uint8, device=dev)
+        out.sf_col = torch.empty(T * I // BLOCK, dtype=torch.uint8, device=dev)
+    _lib.call("swiglu_quant_mxfp8", h1, T, I, float(clamp), out.q_row, out.sf_row, out.q_col, out.sf_col)
+    return out
+
+
+def swiglu_bwd_quantize_mxfp8(h1: torch.Tensor, dact: torch.Tensor, clamp: float = 0.0) -> MXFP8Tensor:
+    """MXFP8 (both directions) of the SwiGLU input gradient ``[dgate | dup]`` [T, 2I] from ``h1`` and ``dact`` [T, I]."""
+    T, I2 = h1.shape
+    I = I2 // 2
+    dev = h1.device
+    out = MXFP8Tensor(shape=(T, I2))
+    out.q_row = torch.empty(T, I2, dtype=torch.uint8, device=dev)
+    out.sf_row = torch.empty(T * I2 // BLOCK, dtype=torch.uint8, device=dev)
+    out.q_col = torch.empty(T, I2, dtype=torch.uint8, device=dev)
+    out.sf_col = torch.empty(T * I2 // BLOCK, dtype=torch.uint8, device=dev)
+    _lib.call("swiglu_bwd_quant_mxfp8", h1, dact, T, I, float(clamp), out.q_row, out.sf_row, out.q_col, out.sf_col)
+    return out
+
+
 def dequantize_mxfp8(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.Tensor:
     if not q.is_cuda:
         return dequantize_mxfp8_ref(q, sf, colwise)

@@ -69,8 +69,20 @@ def _quantized(t: torch.Tensor, direction: str, single_use: bool = False):
             both = not torch.is_grad_enabled() and not single_use   # backward pass: a gradient feeds two GEMMs
             q = fp8.quantize_mxfp8(t, both or direction == "row", both or direction == "col")
             _ACT_CACHE.insert(0, (key, t, q))
-            del _ACT_CACHE[2:]
+            del _ACT_CACHE[4:]
     return (q.q_row, q.sf_row) if direction == "row" else (q.q_col, q.sf_col)
+
+
+def register_quantized(t: torch.Tensor, q) -> None:
+    """Attach an already quantised copy (both directions) to ``t``: the next GEMMs that take ``t`` as an operand use
+    it instead of quantising.  ``t``'s own bf16 contents are then never read by an fp8-eligible GEMM, which lets a
+    producer that can emit MXFP8 directly (fused SwiGLU backward) skip writing them."""
+    _ACT_CACHE.insert(0, ((t.data_ptr(), tuple(t.shape), t._version), t, q))
+    del _ACT_CACHE[4:]
+
+
+# set to False by code that reads gradients of linear layers outside the GEMMs (adapters), see ops/layers.py
+FUSE_SWIGLU_QUANT = True
 
 
 def _fp8_eligible(a, b, out, M, N, K) -> bool:

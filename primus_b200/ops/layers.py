@@ -124,6 +124,18 @@ def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_p
 
 
 # ----------------------------------------------------------------------------------------------
+def _swiglu_fp8_fusable(h1, weight, probs, tp_group) -> bool:
+    """MXFP8 recipe on, plain (no routing probabilities, no tensor parallelism) and every dimension a multiple of 128:
+    the SwiGLU kernels then emit MXFP8 directly for the GEMMs around them."""
+    if gemm.fp8_recipe() is None or not gemm.FUSE_SWIGLU_QUANT or probs is not None or tp_group is not None:
+        return False
+    if getattr(weight, "_fp8_exempt", False) or h1.dtype != torch.bfloat16:
+        return False
+    T = h1.numel() // h1.shape[-1]
+    I = h1.shape[-1] // 2
+    return T % 128 == 0 and I % 128 == 0 and weight.shape[0] % 128 == 0 and weight.is_contiguous()
+
+
 class SwiGLULinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h1, weight, probs, clamp, tp_group, sp):
@@ -131,6 +143,25 @@ class SwiGLULinearFn(torch.autograd.Function):
         I = I2 // 2
         x2 = h1.reshape(-1, I2)
         T = x2.shape[0]
+        ctx.fp8_fused = _swiglu_fp8_fusable(h1, weight, probs, tp_group) and x2.is_contiguous()
+        if ctx.fp8_fused:
+            from . import fp8
+
+            # the producer of h1 must consume its gradient only through GEMMs (see backward)
+            ctx.grad_via_cache = type(h1.grad_fn).__name__ in ("NormLinearFnBackward", "LinearFnBackward")
+            aq = fp8.swiglu_quantize_mxfp8(x2, clamp, True, False)
+            wq, wsf = gemm._quantized(weight, "row")
+            N = weight.shape[0]
+            out = torch.empty(T, N, dtype=torch.bfloat16, device=h1.device)
+            fp8.launch_gemm(aq.q_row, aq.sf_row, wq, wsf, out, T, N, I, False, False, 0)
+            ctx.tp = (tp_group, sp)
+            ctx.save_for_backward(x2, weight, torch.empty(0))
+            ctx.has_probs = False
+            ctx.probs_meta = None
+            ctx.clamp = clamp
+            ctx.shape = h1.shape
+            ctx.weight_ref = weight
+            return out
         act = torch.empty(T, I, dtype=h1.dtype, device=h1.device)
         p = probs.reshape(-1).float().contiguous() if probs is not None else None
         _lib.call("swiglu_fwd", x2, p, act, T, I, float(clamp))
@@ -159,6 +190,39 @@ class SwiGLULinearFn(torch.autograd.Function):
         dout2 = dout.reshape(-1, dout.shape[-1])
         if not dout2.is_contiguous():
             dout2 = dout2.contiguous()
+        if ctx.fp8_fused:
+            from . import fp8
+
+            N = weight.shape[0]
+            dyq_row = gemm._quantized(dout2, "row")           # quantises both directions once (backward pass)
+            dyq_col = gemm._quantized(dout2, "col")
+            w_ref = ctx.weight_ref
+            dw = None
+            if ctx.needs_input_grad[1]:
+                aq = fp8.swiglu_quantize_mxfp8(x2, ctx.clamp, False, True)    # recomputed activation, col-wise
+                mg = getattr(w_ref, "main_grad", None)
+                tgt = mg if mg is not None else torch.empty(N, I, dtype=torch.float32, device=x2.device)
+                fp8.launch_gemm(dyq_col[0], dyq_col[1], aq.q_col, aq.sf_col, tgt, N, I, T, True, True,
+                                2 if mg is not None else 1)
+                if mg is None:
+                    dw = tgt.to(weight.dtype)
+                else:
+                    w_ref.grad_added_to_main_grad = True
+                    cb = getattr(w_ref, "_grad_ready_cb", None)
+                    if cb is not None:
+                        cb(w_ref)
+            wq, wsf = gemm._quantized(weight, "col")
+            dact = torch.empty(T, I, dtype=torch.bfloat16, device=x2.device)
+            fp8.launch_gemm(dyq_row[0], dyq_row[1], wq, wsf, dact, T, I, N, False, True, 0)
+            if ctx.grad_via_cache and gemm.WGRAD_STORE.current is None:   # (a deferred dW GEMM would outlive the cache entry)
+                # the gradient of h1 leaves as MXFP8 only: the bf16 tensor handed to autograd is a placeholder whose
+                # quantised copy is registered for the two GEMMs of the producing linear layer
+                din = torch.empty_like(x2)
+                gemm.register_quantized(din, fp8.swiglu_bwd_quantize_mxfp8(x2, dact, ctx.clamp))
+            else:
+                din = torch.empty_like(x2)
+                _lib.call("swiglu_bwd", dact, x2, None, din, None, T, I, float(ctx.clamp))
+            return din.view(ctx.shape), dw, None, None, None, None
         act = torch.empty(T, I, dtype=x2.dtype, device=x2.device)
         _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp))
         if sp:

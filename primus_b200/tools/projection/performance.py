@@ -116,6 +116,9 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
     f = per_stage * (mix(lt_dense.fwd, lt_moe.fwd) + mix(lt_dense.comm_fwd, lt_moe.comm_fwd))
     b = per_stage * (mix(lt_dense.bwd_input, lt_moe.bwd_input) + mix(lt_dense.comm_bwd, lt_moe.comm_bwd))
     w = per_stage * mix(lt_dense.bwd_weight, lt_moe.bwd_weight)
+    # fully recomputed layers run their forward pass (and its communication) a second time inside backward
+    rec = min(plan.recompute_layers, per_stage)
+    b += rec * (mix(lt_dense.fwd, lt_moe.fwd) + mix(lt_dense.comm_fwd, lt_moe.comm_fwd))
     f_last, b_last, w_last = f + head_fwd, b + head_bwd * 0.5, w + head_bwd * 0.5
     m = plan.grad_accum
     if plan.pp > 1:

@@ -136,3 +136,33 @@ def test_cta_pair_gemm_all_layouts(M, N, K):
     for got, ref, name in ((y, y_ref, "y"), (dx, dx_ref, "dx"), (dw - 1.0, dw_ref, "dw")):
         err = (got.float() - ref).abs().max().item()
         assert err <= 1.5e-2 * ref.abs().max().item(), (name, err, ref.abs().max().item())
+
+
+def test_fused_swiglu_quantisation_is_bitwise_equal_to_unfused():
+    """SwiGLU kernels that emit MXFP8 directly (forward activation, backward input gradient) must reproduce the
+    un-fused bf16 -> quantise path exactly: same loss trajectory bit for bit."""
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import gemm
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    out = {}
+    try:
+        for fuse in (True, False):
+            gemm.FUSE_SWIGLU_QUANT = fuse
+            mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2,
+                                   num_query_groups=2, vocab_size=1024, params_dtype="bf16", seq_length=256, fp8="e4m3",
+                                   fp8_recipe="mxfp8")
+            tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=256, train_iters=4, lr=2e-3,
+                             lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1)
+            torch.manual_seed(0)
+            tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
+            out[fuse] = tr.train()
+            torch.cuda.synchronize()
+            _lib.check_status()
+    finally:
+        gemm.FUSE_SWIGLU_QUANT = True
+        gemm.set_fp8_recipe(None)
+    assert out[True] == out[False], out

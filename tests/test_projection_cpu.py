@@ -100,3 +100,26 @@ def test_cli_returns_zero(args):
     r = subprocess.run([sys.executable, "-m", "primus_b200.cli.main", *args], capture_output=True, text=True, cwd=ROOT,
                        env=dict(os.environ, PYTHONPATH=ROOT))
     assert r.returncode == 0, r.stderr + r.stdout
+
+
+def test_tuner_ranks_only_legal_plans_that_fit():
+    from primus_b200.core.config.presets import load_preset
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.tools.projection.collective_model import Hardware
+    from primus_b200.tools.projection.memory import project_memory
+    from primus_b200.tools.tuner import search as tuner
+
+    cfg = TransformerConfig.from_dict(load_preset("llama3.1_70B", "models"))
+    hw = Hardware.from_yaml(load_preset("b200", "hardware"))
+    res = tuner.search(cfg, hw, world=8, global_batch=64, seq=8192, top=5)
+    assert res["enumerated"] > res["fit_in_memory"] > 0 and res["best"]
+    ts = [c.tokens_per_s_per_gpu for c in res["best"]]
+    assert ts == sorted(ts, reverse=True)
+    for c in res["best"]:
+        assert not c.plan.validate(cfg)
+        assert project_memory(cfg, c.plan)["peak_gb"] <= hw.hbm_gb
+        assert any(o.startswith("--tensor_model_parallel_size=") for o in c.overrides())
+    # an 8B model fits without model parallelism: the pure data-parallel plan is among the candidates that fit
+    cfg8 = TransformerConfig.from_dict(load_preset("llama3.1_8B", "models"))
+    res8 = tuner.search(cfg8, hw, world=8, global_batch=128, seq=8192, top=1000)
+    assert any((c.plan.tp, c.plan.pp, c.plan.cp) == (1, 1, 1) for c in res8["best"])

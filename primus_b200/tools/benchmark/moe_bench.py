@@ -26,8 +26,73 @@ MODELS = {  # hidden, moe ffn, experts, top-k, tokens per rank
 }
 
 
+def bench_kernels(args, H, I, E, k, T, world):
+    """Device time of every stage of the fused path (forward), with the roofline of the two fused kernels:
+    target = max(FLOPs / measured bf16 GEMM peak, bytes entering this GPU over NVLink / measured peer bandwidth)."""
+    from ...ops import fused
+    from ...ops import moe as moe_ops
+    from ...parallel import fused_ep
+    from ...parallel import state as ps
+    from .fused_comm_bench import _max_over_ranks, _peaks
+
+    st = ps.get_state()
+    ws = fused_ep.get_workspace(st.ep_group if world > 1 else None, T, k, E, H, args.capacity_factor)
+    torch.manual_seed(3 + (dist.get_rank() if dist.is_initialized() else 0))
+    e_local = E // world
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    logits = torch.randn(T, E, device="cuda")
+    probs, idx, _ = moe_ops.router_scores(logits, k)
+    w1 = (torch.randn(e_local, 2 * I, H, device="cuda") * 0.02).bfloat16()
+    w2 = (torch.randn(e_local, H, I, device="cuda") * 0.02).bfloat16()
+    state = {}
+
+    def f_plan(i):
+        state["plan"] = ws.plan(idx, probs)
+
+    def f_dispatch(i):
+        state["plan"] = ws.plan(idx, probs)          # a dispatch always follows a plan (barrier protocol)
+        state["xp"], state["h1"] = ws.dispatch_gemm(x, w1, state["plan"], False)
+
+    def f_full(i):
+        plan = ws.plan(idx, probs)
+        xp, h1 = ws.dispatch_gemm(x, w1, plan, False)
+        act = fused.swiglu(h1, plan.finalize().probs_perm, 0.0)
+        state["out"] = ws.gemm_combine(act, w2, plan, False)
+
+    t_plan = _max_over_ranks(time_cuda(f_plan, args.iters, args.warmup)["ms_median"])
+    t_disp = _max_over_ranks(time_cuda(f_dispatch, args.iters, args.warmup)["ms_median"])
+    t_full = _max_over_ranks(time_cuda(f_full, args.iters, args.warmup)["ms_median"])
+    h1 = state["h1"]
+    pp = state["plan"].finalize().probs_perm
+    t_act = _max_over_ranks(time_cuda(lambda i: fused.swiglu(h1, pp, 0.0), args.iters, args.warmup)["ms_median"])
+    torch.cuda.synchronize()
+    _lib_check()
+    peak, link = _peaks()
+    rows_rank = T * k                      # balanced routing: every rank receives as many rows as it sends
+    remote = rows_rank * (world - 1) / world * H * 2.0
+    t_gemm1 = t_disp - t_plan
+    t_gemm2 = t_full - t_disp - t_act
+    out = []
+    for name, t, fl in (("dispatch + GEMM1", t_gemm1, 2.0 * rows_rank * 2 * I * H),
+                        ("GEMM2 + combine (+ local top-k sum)", t_gemm2, 2.0 * rows_rank * H * I)):
+        target = max(fl / peak, remote / link) * 1e3
+        out.append({"model": args.model, "ep": world, "stage": name, "ms": t, "roofline_ms": target,
+                    "fraction_of_roofline": target / t, "bound": "compute" if fl / peak > remote / link else "nvlink"})
+    out.append({"model": args.model, "ep": world, "stage": "routing plan (2 kernels + barrier)", "ms": t_plan})
+    out.append({"model": args.model, "ep": world, "stage": "SwiGLU x prob", "ms": t_act})
+    out.append({"model": args.model, "ep": world, "stage": "whole fused forward (no router)", "ms": t_full})
+    return out
+
+
+def _lib_check():
+    from ...ops import _lib
+
+    _lib.check_status()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--kernels", action="store_true", help="time the stages of the fused forward separately")
     ap.add_argument("--model", default="deepseek_v2_lite", choices=sorted(MODELS))
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--experts", type=int, default=None, help="override the expert count (to fit small EP sizes)")
@@ -51,6 +116,11 @@ def main(argv=None):
     H, I, E, k, T = MODELS[args.model]
     T = args.tokens or T
     E = args.experts or E
+    if args.kernels:
+        rows = bench_kernels(args, H, I, E, k, T, world)
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            emit(rows, args.output, "fused expert-parallel forward, per stage")
+        return rows
     rows = []
     for fused in (False, True):
         cfg = TransformerConfig(num_layers=1, hidden_size=H, ffn_hidden_size=4 * H, num_attention_heads=H // 128,

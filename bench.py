@@ -141,7 +141,7 @@ def main() -> int:
     if args.fused_tp:
         from primus_b200.parallel import fused_tp
 
-        fused_tp.ENABLED = True
+        fused_tp.ENABLED = True          # all-gather -> GEMM; the reduce-scatter side stays on NCCL (faster at tp = 8)
     gbs = args.batch_per_gpu * world // args.tp
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,

@@ -113,6 +113,7 @@ class TrainConfig:
             from ..parallel import fused_tp
 
             fused_tp.ENABLED = True
+            fused_tp.ENABLED_RS = bool(d.get("tp_comm_overlap_rs", False))
         return cls(**kw)
 
 

@@ -76,7 +76,7 @@ class NormLinearFn(torch.autograd.Function):
         dw = gemm.wgrad(dout2, y, weight_ref)
         del y
         if sp:
-            dy = fused_tp.gemm_rs(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED)
+            dy = fused_tp.gemm_rs(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED_RS)
         else:
             dy = gemm.gemm(dout2, weight, b_mn=True)
             if tp_group is not None:
@@ -166,7 +166,7 @@ class SwiGLULinearFn(torch.autograd.Function):
         p = probs.reshape(-1).float().contiguous() if probs is not None else None
         _lib.call("swiglu_fwd", x2, p, act, T, I, float(clamp))
         if sp:
-            out = fused_tp.gemm_rs(act, weight, tp_group, fused=fused_tp.ENABLED)
+            out = fused_tp.gemm_rs(act, weight, tp_group, fused=fused_tp.ENABLED_RS)
         else:
             out = gemm.gemm(act, weight)
             if tp_group is not None:
@@ -259,7 +259,7 @@ class RowParallelLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, tp_group):
-        out = fused_tp.gemm_rs(x, weight, tp_group, fused=fused_tp.ENABLED)
+        out = fused_tp.gemm_rs(x, weight, tp_group, fused=fused_tp.ENABLED_RS)
         ctx.save_for_backward(x, weight)
         ctx.group = tp_group
         ctx.weight_ref = weight

@@ -31,7 +31,11 @@ from .symm_mem import SymmetricBuffer
 
 COMM_CTAS = int(os.environ.get("PRIMUS_B200_TP_COMM_CTAS", "16"))
 # Fused kernels on/off (config key ``tp_comm_overlap``); off = NCCL collective + GEMM.
+# all-gather -> GEMM fused kernel (column-parallel layers and the data gradients of row-parallel ones)
 ENABLED = os.environ.get("PRIMUS_B200_TP_FUSED", "0") == "1"
+# GEMM -> reduce-scatter fused kernel (row-parallel layers); measured slower than GEMM + NCCL at tp = 8, so it has a
+# switch of its own
+ENABLED_RS = os.environ.get("PRIMUS_B200_TP_FUSED_RS", "0") == "1"
 
 
 class _Instance:

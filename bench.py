@@ -11,7 +11,8 @@ master weights / main grads, synthetic uniform-random tokens, random-init N(0, 0
 Two timed regions, both on the device with CUDA events, max over ranks:
   value : K optimizer steps back to back (inputs still arrive from pinned host memory on a side stream);
   e2e   : K further steps through ``Trainer.train`` which also reads every step's loss back to the host.
-Rank 0 prints one JSON line.  ``--impl reference`` reports why the reference arm cannot run here.
+Rank 0 prints one JSON line.  ``--impl reference`` runs the reference's own CLI (TorchTitan backend) from
+``baseline/_ref`` on the same model and batch, or says why it cannot.
 """
 from __future__ import annotations
 
@@ -23,6 +24,7 @@ import subprocess
 import sys
 import threading
 import time
+from pathlib import Path
 
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -86,10 +88,124 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm(args):
-    why = ("reference (AMD-AGI/Primus) cannot be installed or run offline: its build backend (hatchling) is not in "
-           "the wheelhouse and its training path needs Megatron-LM, whose submodule directory is empty")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+def _reference_unavailable(why: str) -> int:
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def _reference_tokenizer_assets(path: Path) -> None:
+    """Word-level tokenizer files for the reference's mock data: its mock corpus is text made of space-separated
+    integers below 32000 (primus/backends/torchtitan/patches/mock_dataset_patches.py:28), and no Llama tokenizer can
+    be downloaded here.  Every integer maps to its own id, so the token stream is uniform random."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    path.mkdir(parents=True, exist_ok=True)
+    vocab = {str(i): i for i in range(32000)}
+    vocab.update({"<unk>": 32000, "<s>": 32001, "</s>": 32002})
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.add_special_tokens(["<s>", "</s>"])
+    tok.save(str(path / "tokenizer.json"))
+    (path / "tokenizer_config.json").write_text(json.dumps(
+        {"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True, "add_eos_token": True}))
+
+
+def reference_arm(args) -> int:
+    """Runs the unmodified reference (copied to ``baseline/_ref``) through its own CLI and its TorchTitan backend
+    (primus/cli/main.py -> primus/backends/torchtitan/torchtitan_pretrain_trainer.py:41): Llama-3.1-8B, seq 8192,
+    micro-batch 1, the same global batch, bf16 FSDP2 + torch.compile, mock data.  Its Megatron backend (the one its
+    published number comes from) cannot run: the Megatron-LM submodule directory is empty and Transformer-Engine /
+    Primus-Turbo are not installed.  Throughput comes from the reference's own per-step log line (``tps`` = tokens
+    per second per device, averaged since the previous line; it is logged every step, after the loss is read back)."""
+    import importlib.util
+    import re
+    import tempfile
+
+    root = Path(__file__).resolve().parent
+    ref = root / "baseline" / "_ref"
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.model != "llama3.1_8B":
+        return _reference_unavailable("reference arm is wired for llama3.1_8B only")
+    cfg = ref / "examples" / "torchtitan" / "configs" / "MI300X" / "llama3.1_8B-BF16-pretrain.yaml"
+    if not cfg.exists():
+        return _reference_unavailable(
+            "reference (AMD-AGI/Primus) is not present under baseline/_ref: pip cannot build it offline (its build "
+            "backend hatchling is not in the wheelhouse) and no copy of its package tree was placed there")
+    spec = importlib.util.find_spec("torchtitan")
+    if spec is None:
+        return _reference_unavailable("reference TorchTitan backend needs the torchtitan package; its Megatron "
+                                      "backend needs Megatron-LM, whose submodule directory is empty")
+    backend_path = str(Path(spec.origin).parent.parent)
+    try:   # every TorchTitan model preset of the reference sets model.hf_assets_path; its model-override patch
+        # (primus/backends/torchtitan/patches/model_override_patches.py:205-276) raises on any key of the preset that
+        # the installed TorchTitan's JobConfig.model does not declare
+        import dataclasses
+        from torchtitan.config.job_config import JobConfig
+        model_t = {f.name: f.type for f in dataclasses.fields(JobConfig)}["model"]
+        declared = {f.name for f in dataclasses.fields(model_t)}
+    except Exception as e:  # noqa: BLE001
+        return _reference_unavailable(f"cannot inspect the installed torchtitan ({type(e).__name__}: {e})")
+    if "hf_assets_path" not in declared:
+        return _reference_unavailable(
+            "reference TorchTitan backend needs a newer torchtitan than the one installed (0.1.0): its stock model "
+            "presets set model.hf_assets_path and its model-override patch raises \"'TransformerModelArgs' has no "
+            "field 'hf_assets_path'\" (observed on a B200 box); its pinned third_party/torchtitan and "
+            "third_party/Megatron-LM submodule directories are empty, Transformer-Engine / Primus-Turbo are not "
+            "installed, and pip cannot build the package offline (hatchling is not in the wheelhouse)")
+    if not os.path.exists("/dev/nvidiactl"):
+        return _reference_unavailable("reference TorchTitan backend needs a GPU")
+    work = Path(tempfile.mkdtemp(prefix="primus_ref_"))
+    _reference_tokenizer_assets(work / "tokenizer")
+    steps = args.warmup + args.steps
+    gbs = args.batch_per_gpu * world
+    env = dict(os.environ)
+    env["PYTHONPATH"] = str(ref) + os.pathsep + env.get("PYTHONPATH", "")
+    env.setdefault("RANK", "0"), env.setdefault("LOCAL_RANK", "0"), env.setdefault("WORLD_SIZE", "1")
+    env.setdefault("MASTER_ADDR", "127.0.0.1"), env.setdefault("MASTER_PORT", "29533")
+    env.setdefault("LOCAL_WORLD_SIZE", env["WORLD_SIZE"])
+    last = ""
+    for ac_mode in (["selective", "full"] if args.ref_ac == "auto" else [args.ref_ac]):
+        cmd = [sys.executable, "-m", "primus.cli.main", "train", "pretrain", "--config", str(cfg),
+               "--backend_path", backend_path,
+               "--training.mock_data", "true", "--training.steps", str(steps), "--training.seq_len", str(args.seq),
+               "--training.local_batch_size", str(args.micro_batch), "--training.global_batch_size", str(gbs),
+               "--training.gc_freq", "1000", "--metrics.log_freq", "1", "--lr_scheduler.warmup_steps", "2",
+               "--model.tokenizer_path", str(work / "tokenizer"),
+               "--activation_checkpoint.mode", ac_mode, "--activation_checkpoint.selective_ac_option", "op",
+               "--primus_turbo.enable_primus_turbo", "false"]
+        log = work / f"rank{rank}_{ac_mode}.log"
+        with open(log, "w") as f:
+            rc = subprocess.run(cmd, cwd=work, env=env, stdout=f, stderr=subprocess.STDOUT).returncode
+        text = re.sub(r"\x1b\[[0-9;]*m", "", log.read_text(errors="replace"))
+        if rank == 0 and args.ref_log:
+            Path(args.ref_log).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.ref_log).write_text(text[-200000:])
+        tps = [float(m.group(2).replace(",", "")) for m in
+               re.finditer(r"step:\s*(\d+).*?tps:\s*([\d,\.]+)", text)]
+        if rc == 0 and len(tps) >= steps:
+            break
+        last = " | ".join(l.strip()[-200:] for l in text.splitlines()[-400:] if "Error" in l or "error" in l)[-600:]
+        tps = []
+    if not tps:
+        return _reference_unavailable("reference TorchTitan path failed on this box: " + (last or "no step lines"))
+    if rank == 0:
+        timed = tps[-args.steps:]
+        tokens_rank_step = gbs // world * args.seq
+        ms = sum(tokens_rank_step / t * 1e3 for t in timed) / len(timed)
+        value = gbs * args.seq / (ms / 1e3)
+        print(json.dumps({
+            "impl": "reference", "metric": "tokens/s (Llama-3.1-8B pretraining, whole job)", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / (BASELINE_TOK_S_GPU * world),
+            "dtype": "bf16 (fp32 master parameters, bf16 compute, fp32 gradient reduction)",
+            "data": "synthetic: the reference's mock dataset (uniform-random ids below 32000), random-init weights",
+            "config": {"model": "llama3.1_8B", "global_batch": gbs, "seq_len": args.seq,
+                       "micro_batch": args.micro_batch, "parallelism": f"fsdp{world}",
+                       "backend": "reference CLI -> TorchTitan backend, torch.compile on, activation checkpoint "
+                                  + ac_mode + ", Primus-Turbo off (not installed)",
+                       "timing": "reference's own per-step tps log line (wall clock after the loss read-back)"},
+            "tokens_per_s_per_gpu": value / world}))
     return 0
 
 
@@ -109,6 +225,9 @@ def main() -> int:
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
     ap.add_argument("--precision", default="mxfp8", choices=["bf16", "mxfp8"],
                     help="linear-layer GEMM precision: bf16, or MXFP8 (E4M3 values, UE8M0 scale per 32 elements; fp32 accumulation)")
+    ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "selective", "full"],
+                    help="reference arm: activation checkpointing mode (auto = selective, then full if that fails)")
+    ap.add_argument("--ref-log", default=None, help="reference arm: copy rank 0's log of the reference run here")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
     args = ap.parse_args()
     if args.impl == "reference":

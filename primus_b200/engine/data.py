@@ -36,16 +36,44 @@ class MockGPTDataset:
 class PatternGPTDataset(MockGPTDataset):
     """Learnable synthetic data: every sample repeats a random period of ``period`` tokens, so a model that attends
     ``period`` tokens back predicts everything after the first period (used for loss-curve comparisons between
-    precisions; random tokens alone can only be fitted by their unigram statistics)."""
+    precisions; random tokens alone can only be fitted by their unigram statistics).  Tokens come from the first
+    ``alphabet`` ids, so the unigram fit alone already moves the loss from ln(vocab) to ln(alphabet) within a few
+    dozen steps, and copying from one period back moves it towards zero after that."""
 
-    def __init__(self, vocab_size: int, seq_length: int, seed: int = 1234, period: int = 32):
+    def __init__(self, vocab_size: int, seq_length: int, seed: int = 1234, period: int = 32, alphabet: int = 512):
         super().__init__(vocab_size, seq_length, seed)
         self.period = period
+        self.alphabet = min(alphabet, vocab_size)
 
     def __getitem__(self, idx: int) -> dict:
         rng = np.random.Generator(np.random.PCG64([self.seed, idx]))
-        base = rng.integers(0, self.vocab_size, size=self.period, dtype=np.int64)
+        base = rng.integers(0, self.alphabet, size=self.period, dtype=np.int64)
         x = np.tile(base, self.seq_length // self.period + 2)[: self.seq_length + 1]
+        return {"tokens": torch.from_numpy(x[:-1].copy()), "labels": torch.from_numpy(x[1:].copy()),
+                "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
+
+
+class MarkovGPTDataset(MockGPTDataset):
+    """Learnable synthetic data with a smooth loss curve: a first-order Markov chain over the first ``alphabet`` ids.
+    The next token is a fixed permutation of the current one with probability ``1 - noise`` and uniform otherwise, so
+    the loss falls steadily from ln(vocab) towards the chain's entropy as the model fits the transition table (no
+    sudden in-context-copying phase as with periodic sequences, whose timing is sensitive to rounding noise)."""
+
+    def __init__(self, vocab_size: int, seq_length: int, seed: int = 1234, alphabet: int = 512, noise: float = 0.15):
+        super().__init__(vocab_size, seq_length, seed)
+        self.alphabet = min(alphabet, vocab_size)
+        self.noise = noise
+        self.perm = np.random.Generator(np.random.PCG64([seed, 0x5EED])).permutation(self.alphabet).astype(np.int64)
+
+    def __getitem__(self, idx: int) -> dict:
+        rng = np.random.Generator(np.random.PCG64([self.seed, idx]))
+        n = self.seq_length + 1
+        jump = rng.random(n) < self.noise
+        fresh = rng.integers(0, self.alphabet, size=n, dtype=np.int64)
+        x = np.empty(n, dtype=np.int64)
+        x[0] = fresh[0]
+        for t in range(1, n):
+            x[t] = fresh[t] if jump[t] else self.perm[x[t - 1]]
         return {"tokens": torch.from_numpy(x[:-1].copy()), "labels": torch.from_numpy(x[1:].copy()),
                 "loss_mask": torch.ones(self.seq_length, dtype=torch.float32)}
 

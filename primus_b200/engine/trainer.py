@@ -62,6 +62,7 @@ class TrainConfig:
     data_seed: int = 1234
     mock_data: bool = True
     mock_data_period: int = 0          # > 0: learnable periodic sequences instead of uniform-random tokens
+    mock_data_kind: str = ""           # "markov": learnable first-order Markov chain (smooth loss curve)
     data_path: Optional[str] = None
     log_interval: int = 1
     log_avg_skip_iterations: int = 2
@@ -214,7 +215,11 @@ class Trainer:
         # ---------------------------------------------------------------- data
         self.num_microbatches = schedules.num_microbatches(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp)
         if train_cfg.mock_data or not train_cfg.data_path:
-            if train_cfg.mock_data_period:
+            if train_cfg.mock_data_kind == "markov":
+                from .data import MarkovGPTDataset
+
+                ds = MarkovGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
+            elif train_cfg.mock_data_period:
                 from .data import PatternGPTDataset
 
                 ds = PatternGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed,

@@ -30,11 +30,17 @@ _ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
 
 
 def set_fp8_recipe(recipe: str | None) -> None:
-    global _FP8_RECIPE
+    global _FP8_RECIPE, _WEIGHT_GEN
     assert recipe in (None, "", "mxfp8"), f"unsupported fp8 recipe {recipe!r}"
     _FP8_RECIPE = recipe or None
+    _WEIGHT_GEN += 1        # quantised weights cached elsewhere (expert weights) are keyed on this counter
     _W_CACHE.clear()
     _ACT_CACHE.clear()
+
+
+def weight_generation() -> int:
+    """Counter that changes whenever the optimizer (or a checkpoint load) rewrites parameters."""
+    return _WEIGHT_GEN
 
 
 def fp8_recipe() -> str | None:

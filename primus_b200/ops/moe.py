@@ -276,14 +276,52 @@ def _grouped_ref(x, w, sched: Schedule, trans_w: bool):
     return out
 
 
-def grouped_wgrad(dy, x, w, sched: Schedule):
+_EXPERT_W_CACHE: dict = {}
+
+
+def _grouped_fp8_eligible(x, w) -> bool:
+    """MXFP8 grouped GEMMs need the recipe switched on and every dimension a multiple of 128."""
+    from . import gemm
+
+    if not x.is_cuda or gemm.fp8_recipe() is None or getattr(w, "_fp8_exempt", False):
+        return False
+    E, N, K = w.shape
+    return x.shape[0] % 128 == 0 and N % 128 == 0 and K % 128 == 0 and x.dtype == torch.bfloat16
+
+
+def _quantized_expert_weight(w):
+    """Both MXFP8 directions of an expert weight [E, N, K] (quantised as the [E*N, K] matrix: blocks never straddle
+    experts because N is a multiple of 128), cached until the optimizer next changes the parameters."""
+    from . import fp8, gemm
+
+    gen = gemm.weight_generation()
+    hit = _EXPERT_W_CACHE.get(id(w))
+    if hit is None or hit[0] != gen or hit[1] != w.data_ptr():
+        E, N, K = w.shape
+        hit = (gen, w.data_ptr(), fp8.quantize_mxfp8(w.detach().view(E * N, K), True, True))
+        _EXPERT_W_CACHE[id(w)] = hit
+    return hit[2]
+
+
+def grouped_wgrad(dy, x, w, sched: Schedule, dyq=None):
     """dW[e] = dy_e^T x_e over the rows of expert e.  Accumulates into ``w.main_grad`` (fp32) when the parameter
-    has one (returns None and fires the bucket callback), else returns the gradient in ``w.dtype``."""
+    has one (returns None and fires the bucket callback), else returns the gradient in ``w.dtype``.
+    ``dyq``: the MXFP8 copy of ``dy`` (column direction) when the caller already has one; the MXFP8 path is taken when
+    the recipe is on and the shapes allow it."""
     E, N, K = w.shape
     mg = getattr(w, "main_grad", None)
     tgt = mg if mg is not None else torch.empty(E, N, K, dtype=torch.float32, device=x.device)
-    _lib.call("grouped_gemm", 2, dy, x, tgt, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
-              sched.padded, int(mg is not None), _lib.status_word(x.device))
+    if _grouped_fp8_eligible(x, w) and dy.shape[0] % 128 == 0:
+        from . import fp8
+
+        if dyq is None or dyq.q_col is None:
+            dyq = fp8.quantize_mxfp8(dy.contiguous(), False, True)
+        xq = fp8.quantize_mxfp8(x, False, True)
+        _lib.call("grouped_gemm_mxfp8", 2, dyq.q_col, dyq.sf_col, xq.q_col, xq.sf_col, tgt, x.shape[0], N, K, E,
+                  sched.mblock_expert, sched.row_start, sched.padded, int(mg is not None), _lib.status_word(x.device))
+    else:
+        _lib.call("grouped_gemm", 2, dy, x, tgt, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
+                  sched.padded, int(mg is not None), _lib.status_word(x.device))
     if mg is None:
         return tgt.to(w.dtype)
     cb = getattr(w, "_grad_ready_cb", None)
@@ -299,8 +337,17 @@ class GroupedLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, sched: Schedule):
         E, N, K = w.shape
         out = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
-        _lib.call("grouped_gemm", 0, x, w, out, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
-                  sched.padded, 0, _lib.status_word(x.device))
+        ctx.fp8 = _grouped_fp8_eligible(x, w)
+        if ctx.fp8:
+            from . import fp8
+
+            xq = fp8.quantize_mxfp8(x, True, False)
+            wq = _quantized_expert_weight(w)
+            _lib.call("grouped_gemm_mxfp8", 0, xq.q_row, xq.sf_row, wq.q_row, wq.sf_row, out, x.shape[0], N, K, E,
+                      sched.mblock_expert, sched.row_start, sched.padded, 0, _lib.status_word(x.device))
+        else:
+            _lib.call("grouped_gemm", 0, x, w, out, x.shape[0], N, K, E, sched.mblock_expert, sched.row_start,
+                      sched.padded, 0, _lib.status_word(x.device))
         ctx.save_for_backward(x, w)
         ctx.sched = sched
         ctx.w_ref = w
@@ -313,6 +360,17 @@ class GroupedLinearFn(torch.autograd.Function):
         E, N, K = w.shape
         dy = dy.contiguous()
         dx = None
+        if ctx.fp8:
+            from . import fp8
+
+            dyq = fp8.quantize_mxfp8(dy, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+            if ctx.needs_input_grad[0]:
+                wq = _quantized_expert_weight(w)
+                dx = torch.empty_like(x)
+                _lib.call("grouped_gemm_mxfp8", 1, dyq.q_row, dyq.sf_row, wq.q_col, wq.sf_col, dx, x.shape[0], K, N, E,
+                          sched.mblock_expert, sched.row_start, sched.padded, 0, _lib.status_word(x.device))
+            dw = grouped_wgrad(dy, x, ctx.w_ref, sched, dyq=dyq) if ctx.needs_input_grad[1] else None
+            return dx, dw, None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
             _lib.call("grouped_gemm", 1, dy, w, dx, x.shape[0], K, N, E, sched.mblock_expert, sched.row_start,

@@ -366,6 +366,9 @@ PB_DEVICE void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// logistic function with the fast reciprocal (every SwiGLU kernel uses this one expression, so fused and un-fused
+// variants round identically)
+PB_DEVICE float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 PB_DEVICE uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -106,36 +106,64 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // ------------------------------------------------------------------ RMSNorm backward
 // dx = rstd * (dy*w) - x * rstd^3 * mean(dy*w*x)  (+ dres when given)
 // dw partial sums per CTA go to `partial` [gridDim.x, H]; rmsnorm_dw_reduce_kernel folds them.
-__global__ void __launch_bounds__(RN_THREADS)
+// A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; VPT 16-byte vectors per thread per row.  The next row's
+// operands are fetched into registers before the current row's block reduction, so the reduction's two barriers
+// overlap the loads instead of serialising with them.
+template <int VPT>
+__global__ void __launch_bounds__(RN_THREADS, (VPT <= 2) ? 2 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ partial, int rows, int H, long ldx, long lddy) {
   __shared__ float red[32];
-  constexpr int MAXV = 4;  // up to 4 vectors (32 columns) per thread: H <= 8192
   const int nv = H / 8;
-  float wreg[MAXV][8];
-  float dw[MAXV][8];
+  float wreg[VPT][8];
+  float dw[VPT][8];
   const Bf8* wr = reinterpret_cast<const Bf8*>(w);
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k) {
+  for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * RN_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw[k][j] = 0.f;
     if (i < nv) bf8_to_f(wr[i], wreg[k]);
   }
-  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+  Bf8 nx[VPT], ng[VPT], nr[VPT];
+  float nrs = 0.f;
+  auto fetch = [&](long row) {
     const Bf8* dyr = reinterpret_cast<const Bf8*>(dy + row * lddy);
     const Bf8* xr = reinterpret_cast<const Bf8*>(x + row * ldx);
-    const float rs = rstd[row];
-    float fx[MAXV][8], fg[MAXV][8];
-    float dot = 0.f;
+    const Bf8* drr = dres ? reinterpret_cast<const Bf8*>(dres + row * ldx) : nullptr;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < VPT; ++k) {
       const int i = threadIdx.x + k * RN_THREADS;
       if (i < nv) {
-        bf8_to_f(xr[i], fx[k]);
-        bf8_to_f(dyr[i], fg[k]);
+        nx[k] = xr[i];
+        ng[k] = dyr[i];
+        if (drr) nr[k] = drr[i];
+      }
+    }
+    nrs = rstd[row];
+  };
+  long row = blockIdx.x;
+  if (row < rows) fetch(row);
+  for (; row < rows; row += gridDim.x) {
+    float fx[VPT][8], fg[VPT][8], fr[VPT][8];
+    const float rs = nrs;
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * RN_THREADS;
+      if (i < nv) {
+        bf8_to_f(nx[k], fx[k]);
+        bf8_to_f(ng[k], fg[k]);
+        if (dres) bf8_to_f(nr[k], fr[k]);
+      }
+    }
+    if (row + gridDim.x < rows) fetch(row + gridDim.x);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * RN_THREADS;
+      if (i < nv) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           dw[k][j] += fg[k][j] * fx[k][j] * rs;
@@ -147,26 +175,23 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     dot = block_sum<RN_THREADS>(dot, red);
     const float c = dot * rs * rs * rs / H;
     Bf8* dxr = reinterpret_cast<Bf8*>(dx + row * ldx);
-    const Bf8* drr = dres ? reinterpret_cast<const Bf8*>(dres + row * ldx) : nullptr;
 #pragma unroll
-    for (int k = 0; k < MAXV; ++k) {
+    for (int k = 0; k < VPT; ++k) {
       const int i = threadIdx.x + k * RN_THREADS;
       if (i < nv) {
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = fg[k][j] * rs - fx[k][j] * c;
-        if (drr) {
-          float r[8];
-          bf8_to_f(drr[i], r);
+        if (dres) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
+          for (int j = 0; j < 8; ++j) o[j] += fr[k][j];
         }
         dxr[i] = f_to_bf8(o);
       }
     }
   }
 #pragma unroll
-  for (int k = 0; k < MAXV; ++k) {
+  for (int k = 0; k < VPT; ++k) {
     const int i = threadIdx.x + k * RN_THREADS;
     if (i < nv) {
       float* p = partial + (long)blockIdx.x * H + (long)i * 8;
@@ -174,6 +199,14 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       *reinterpret_cast<float4*>(p + 4) = make_float4(dw[k][4], dw[k][5], dw[k][6], dw[k][7]);
     }
   }
+}
+
+template <typename... Args>
+void launch_rmsnorm_bwd(int P, int H, cudaStream_t s, Args... args) {
+  const int vpt = (H / 8 + RN_THREADS - 1) / RN_THREADS;
+  if (vpt <= 1) rmsnorm_bwd_kernel<1><<<P, RN_THREADS, 0, s>>>(args...);
+  else if (vpt == 2) rmsnorm_bwd_kernel<2><<<P, RN_THREADS, 0, s>>>(args...);
+  else rmsnorm_bwd_kernel<4><<<P, RN_THREADS, 0, s>>>(args...);
 }
 
 // dw[h] (+)= sum_p partial[p, h]
@@ -184,6 +217,34 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, floa
   float s = 0.f;
   for (int p = 0; p < P; ++p) s += partial[(long)p * H + h];
   dw[h] = accumulate ? dw[h] + s : s;
+}
+
+// ------------------------------------------------------------------ logit soft-capping
+// forward: y = cap * tanh(x / cap) (in place when y == x); backward: dx = dy * (1 - (y / cap)^2) from the saved output.
+// Replaces the reference's Triton `fused_softcap_kernel` (primus/backends/megatron/core/extensions/logits_processor.py:13-37).
+__global__ void softcap_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long nvec,
+                                   float cap, float inv_cap) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float f[8];
+    bf8_to_f(reinterpret_cast<const Bf8*>(x)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = cap * tanhf(f[j] * inv_cap);
+    reinterpret_cast<Bf8*>(y)[i] = f_to_bf8(f);
+  }
+}
+__global__ void softcap_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
+                                   __nv_bfloat16* __restrict__ dx, long nvec, float inv_cap) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float g[8], f[8];
+    bf8_to_f(reinterpret_cast<const Bf8*>(dy)[i], g);
+    bf8_to_f(reinterpret_cast<const Bf8*>(y)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float t = f[j] * inv_cap;
+      g[j] *= (1.f - t * t);
+    }
+    reinterpret_cast<Bf8*>(dx)[i] = f_to_bf8(g);
+  }
 }
 
 // ------------------------------------------------------------------ RoPE (rotate-half), in place
@@ -248,7 +309,7 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, const fl
         gg = fminf(gg, clamp);
         uu = fminf(fmaxf(uu, -clamp), clamp);
       }
-      const float sig = 1.f / (1.f + __expf(-gg));
+      const float sig = pb::fast_sigmoid(gg);
       o[j] = gg * sig * uu * p;
     }
     *reinterpret_cast<Bf8*>(out + t * (long)I + v * 8) = f_to_bf8(o);
@@ -281,7 +342,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
           if (uu > clamp) { uu = clamp; umask = 0.f; }
           if (uu < -clamp) { uu = -clamp; umask = 0.f; }
         }
-        const float sig = 1.f / (1.f + __expf(-gg));
+        const float sig = pb::fast_sigmoid(gg);
         const float sl = gg * sig;
         dp += fd[j] * sl * uu;
         const float d = fd[j] * p;
@@ -569,9 +630,8 @@ int pb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   if (H % 8 || ldx % 8 || lddy % 8 || H > 8192) return -2;
   if (rows == 0) return 0;
   const int P = pb_rmsnorm_bwd_num_partials(rows);
-  rmsnorm_bwd_kernel<<<P, RN_THREADS, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                             (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                             (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
+  launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+                     (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
   rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
   PB_CHECK_LAUNCH();
 }
@@ -583,6 +643,22 @@ int pb_rope(void* x, const int* pos, const float* cos_t, const float* sin_t, lon
   if (total == 0) return 0;
   rope_kernel<<<grid_for(total, 256), 256, 0, s>>>((__nv_bfloat16*)x, pos, cos_t, sin_t, T, heads, d,
                                                   rot_dim, ld, backward ? -1.f : 1.f);
+  PB_CHECK_LAUNCH();
+}
+
+int pb_softcap_fwd(const void* x, void* y, long n, float cap, cudaStream_t s) {
+  if (n % 8 || cap <= 0.f) return -2;
+  if (n == 0) return 0;
+  softcap_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n / 8, cap,
+                                                         1.f / cap);
+  PB_CHECK_LAUNCH();
+}
+
+int pb_softcap_bwd(const void* dy, const void* y, void* dx, long n, float cap, cudaStream_t s) {
+  if (n % 8 || cap <= 0.f) return -2;
+  if (n == 0) return 0;
+  softcap_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y,
+                                                         (__nv_bfloat16*)dx, n / 8, 1.f / cap);
   PB_CHECK_LAUNCH();
 }
 
@@ -726,9 +802,8 @@ extern "C" int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   float* scratch = g_noalloc_scratch_ptr[dev];
   const int P = (int)(rows < PB_NOALLOC_MAX_PARTIALS ? rows : PB_NOALLOC_MAX_PARTIALS);
   // every one of the P partial rows is fully written by its CTA before the reduction reads it
-  rmsnorm_bwd_kernel<<<P, RN_THREADS, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                             (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres,
-                                             (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
+  launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
+                     (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
   rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
   return (int)cudaGetLastError();
 }

@@ -90,26 +90,63 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
     }
   }
   if (q_col) {
-    // thread -> (column pair cp, 32-row block ib): one bf16x2 load and one 2-byte store per row
-    const int cp = tid & 63, ib = tid >> 6;
-    const int i0 = ib * 32, c = 2 * cp;
-    float f0[32], f1[32];
-    float a0 = 0.f, a1 = 0.f;
+    // warp -> (64-column half, 32-row block); lane -> (8-column group cg, row subset sub): rows 4*sub + j and
+    // 16 + 4*sub + j (j < 4), so that the two subsets sharing a shared-memory wavefront sit 64 bytes apart in the
+    // banks.  One 16-byte load and one 8-byte store per row; the column maxima are reduced across the four subsets
+    // with two shuffles on packed bf16 pairs.
+    const int lane = tid & 31, warp = tid >> 5;
+    const int cg = lane & 7, sub = lane >> 3;
+    const int cbase = (warp & 1) * 64 + cg * 8;
+    const int ib = warp >> 1;
+    uint4 d[8];
+    __nv_bfloat162 m[4];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tile[(i0 + i) * PITCH + c]));
-      f0[i] = t.x;
-      f1[i] = t.y;
-      a0 = fmaxf(a0, fabsf(t.x));
-      a1 = fmaxf(a1, fabsf(t.y));
+    for (int u = 0; u < 4; ++u) m[u] = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = ib * 32 + (i >> 2) * 16 + sub * 4 + (i & 3);
+      d[i] = *reinterpret_cast<const uint4*>(&tile[r * PITCH + cbase]);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d[i]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) m[u] = __hmax2(m[u], __habs2(h[u]));
     }
-    const int e0 = e8m0_from_amax(a0), e1 = e8m0_from_amax(a1);
-    const float i0s = inv_scale_from_e8m0(e0), i1s = inv_scale_from_e8m0(e1);
+    float inv[8];
+    int e[8];
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-      *reinterpret_cast<uint16_t*>(qc + (i0 + i) * QPITCH + c) = cvt2(f0[i] * i0s, f1[i] * i1s);
-    sf_col[sf_offset(col0 + c, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e0;
-    sf_col[sf_offset(col0 + c + 1, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e1;
+    for (int u = 0; u < 4; ++u) {
+      uint32_t w = *reinterpret_cast<uint32_t*>(&m[u]);
+      uint32_t o = __shfl_xor_sync(0xffffffffu, w, 8);
+      m[u] = __hmax2(m[u], *reinterpret_cast<__nv_bfloat162*>(&o));
+      w = *reinterpret_cast<uint32_t*>(&m[u]);
+      o = __shfl_xor_sync(0xffffffffu, w, 16);
+      m[u] = __hmax2(m[u], *reinterpret_cast<__nv_bfloat162*>(&o));
+      const float2 a = __bfloat1622float2(m[u]);
+      e[2 * u] = e8m0_from_amax(a.x);
+      e[2 * u + 1] = e8m0_from_amax(a.y);
+      inv[2 * u] = inv_scale_from_e8m0(e[2 * u]);
+      inv[2 * u + 1] = inv_scale_from_e8m0(e[2 * u + 1]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = ib * 32 + (i >> 2) * 16 + sub * 4 + (i & 3);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d[i]);
+      uint32_t w[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float2 t0 = __bfloat1622float2(h[2 * u]), t1 = __bfloat1622float2(h[2 * u + 1]);
+        w[u] = (uint32_t)cvt2(t0.x * inv[4 * u], t0.y * inv[4 * u + 1]) |
+               ((uint32_t)cvt2(t1.x * inv[4 * u + 2], t1.y * inv[4 * u + 3]) << 16);
+      }
+      *reinterpret_cast<uint2*>(qc + r * QPITCH + cbase) = make_uint2(w[0], w[1]);
+    }
+    // every lane of a column group holds the 8 scales; subset s writes those of columns 2s and 2s + 1
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (sub == u) {
+        sf_col[sf_offset(col0 + cbase + 2 * u, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e[2 * u];
+        sf_col[sf_offset(col0 + cbase + 2 * u + 1, (row0 >> 5) + ib, R >> 7)] = (uint8_t)e[2 * u + 1];
+      }
+    }
   }
   __syncthreads();
   // coalesced 16-byte stores of the staged fp8 tiles (8 vectors per row)
@@ -192,7 +229,7 @@ swiglu_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, int T, int I, fl
         gg = fminf(gg, clamp);
         uu = fminf(fmaxf(uu, -clamp), clamp);
       }
-      const float sig = 1.f / (1.f + __expf(-gg));
+      const float sig = pb::fast_sigmoid(gg);
       o[j] = gg * sig * uu * 1.f;
     }
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = bf8_pack(o);
@@ -202,24 +239,26 @@ swiglu_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, int T, int I, fl
 }
 
 // SwiGLU backward fused with the quantisation of its output: (h1 [T, 2I], dact [T, I]) -> MXFP8 (both directions) of
-// dh1 [T, 2I] = [dgate | dup].  Grid (I / 128, T / 128, 2): z selects the gate or the up half.
+// dh1 [T, 2I] = [dgate | dup].  One CTA per 128 x 128 tile of the activation: it reads gate, up and dact once, stages
+// the dgate and the dup tile, and quantises one after the other.
+constexpr int QUANT_SMEM_BWD = 2 * TILE * PITCH * 2 + 2 * TILE * QPITCH;
 __global__ void __launch_bounds__(256)
 swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_bfloat16* __restrict__ dact, int T, int I,
                               float clamp, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
                               uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
-  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
-  uint8_t* qr = smem_q + TILE * PITCH * 2;
+  __nv_bfloat16* tile_g = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  __nv_bfloat16* tile_u = tile_g + TILE * PITCH;
+  uint8_t* qr = smem_q + 2 * TILE * PITCH * 2;
   uint8_t* qc = qr + TILE * QPITCH;
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
-  const int up_half = blockIdx.z;
   const int tid = threadIdx.x;
-#pragma unroll
+#pragma unroll 2
   for (int it = 0; it < 8; ++it) {
     const int v = tid + it * 256;
     const int r = v >> 4, c8 = (v & 15) * 8;
     const __nv_bfloat16* g = h1 + (long)(row0 + r) * 2 * I + col0 + c8;
-    float fg[8], fu[8], fd[8], o[8];
+    float fg[8], fu[8], fd[8], og[8], ou[8];
     bf8_load(g, fg);
     bf8_load(g + I, fu);
     bf8_load(dact + (long)(row0 + r) * I + col0 + c8, fd);
@@ -232,15 +271,19 @@ swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_b
         if (uu > clamp) { uu = clamp; umask = 0.f; }
         if (uu < -clamp) { uu = -clamp; umask = 0.f; }
       }
-      const float sig = 1.f / (1.f + __expf(-gg));
+      const float sig = pb::fast_sigmoid(gg);
       const float sl = gg * sig;
       const float d = fd[j] * 1.f;
-      o[j] = up_half ? d * sl * umask : d * uu * sig * (1.f + gg * (1.f - sig)) * gmask;
+      og[j] = d * uu * sig * (1.f + gg * (1.f - sig)) * gmask;
+      ou[j] = d * sl * umask;
     }
-    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = bf8_pack(o);
+    *reinterpret_cast<uint4*>(&tile_g[r * PITCH + c8]) = bf8_pack(og);
+    *reinterpret_cast<uint4*>(&tile_u[r * PITCH + c8]) = bf8_pack(ou);
   }
   __syncthreads();
-  quantize_staged_tile(tile, qr, qc, T, 2 * I, row0, up_half * I + col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile(tile_g, qr, qc, T, 2 * I, row0, col0, q_row, sf_row, q_col, sf_col);
+  __syncthreads();   // the staged fp8 tiles are read by the stores of the first call
+  quantize_staged_tile(tile_u, qr, qc, T, 2 * I, row0, I + col0, q_row, sf_row, q_col, sf_col);
 }
 
 // value [R, C] fp8 + scales (operand layout with MN = R or C) -> fp32 [R, C]; test / debugging helper
@@ -304,11 +347,12 @@ int pb_swiglu_bwd_quant_mxfp8(const void* h1, const void* dact, int T, int I, fl
   if (T % TILE || I % TILE || T <= 0 || I <= 0) return -2;
   static bool attr_set = false;
   if (!attr_set) {
-    int rc = set_quant_smem(reinterpret_cast<const void*>(swiglu_bwd_quant_mxfp8_kernel));
-    if (rc) return rc;
+    cudaError_t e = cudaFuncSetAttribute(swiglu_bwd_quant_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         QUANT_SMEM_BWD);
+    if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  swiglu_bwd_quant_mxfp8_kernel<<<dim3(I / TILE, T / TILE, 2), 256, QUANT_SMEM, s>>>(
+  swiglu_bwd_quant_mxfp8_kernel<<<dim3(I / TILE, T / TILE), 256, QUANT_SMEM_BWD, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(h1), reinterpret_cast<const __nv_bfloat16*>(dact), T, I, clamp,
       reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col),
       reinterpret_cast<uint8_t*>(sf_col));

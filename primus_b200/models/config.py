@@ -80,8 +80,13 @@ class TransformerConfig:
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_layer_ids: Optional[List[int]] = None
     cross_entropy_chunk_tokens: int = 0  # >0: chunked linear-cross-entropy
+    final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)
+    router_logit_softcapping: float | None = None   # same on the MoE router logits
+    attn_logit_softcapping: float | None = None     # accepted for config parity; not supported by the attention kernels
 
     def __post_init__(self):
+        if self.attn_logit_softcapping:
+            raise NotImplementedError("attn_logit_softcapping is not supported by the flash-attention kernels")
         if self.num_query_groups is None:
             self.num_query_groups = self.num_attention_heads
         if self.kv_channels is None:

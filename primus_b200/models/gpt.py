@@ -278,8 +278,9 @@ class GPTModel(nn.Module):
                 if residual is not None else (fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon), None)
             if sp:
                 y = tpc.gather_seq(y, st.tp_group)
-            return gemm.linear(y, w)
-        if cfg.cross_entropy_chunk_tokens > 0 and loss_weights is not None and unit_upstream and st.tp == 1:
+            return fused.softcap(gemm.linear(y, w), cfg.final_logit_softcapping)
+        if (cfg.cross_entropy_chunk_tokens > 0 and loss_weights is not None and unit_upstream and st.tp == 1
+                and not cfg.final_logit_softcapping):
             # chunked linear + cross entropy: no [tokens, vocab] logits tensor
             y = fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual)[0] \
                 if residual is not None else fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon)
@@ -287,6 +288,7 @@ class GPTModel(nn.Module):
                                                        cfg.cross_entropy_chunk_tokens)
         logits, _ = layers.norm_linear(hidden, residual, self.decoder.final_layernorm.weight, w, cfg.norm_epsilon,
                                        st.tp_group, sp)
+        logits = fused.softcap(logits, cfg.final_logit_softcapping)
         vocab_local = w.shape[0]
         loss = fused.cross_entropy(logits, labels.reshape(-1), st.tp_rank * vocab_local,
                                    st.tp_group if st.tp > 1 else None,

@@ -74,7 +74,7 @@ class MoELayer(nn.Module):
     # ------------------------------------------------------------------
     def route(self, y):
         cfg = self.cfg
-        logits = gemm.linear(y, self.router.weight)
+        logits = fused.softcap(gemm.linear(y, self.router.weight), cfg.router_logit_softcapping)
         bias = getattr(self.router, "expert_bias", None)
         probs, idx, full, counts = moe_ops.router_scores(
             logits, cfg.moe_router_topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, bias,

@@ -225,6 +225,45 @@ def swiglu(x, probs=None, clamp=0.0):
 
 
 # ----------------------------------------------------------------------------------------------
+# Logit soft-capping: cap * tanh(x / cap)
+def softcap_ref(x, cap: float):
+    return (torch.tanh(x.float() / cap) * cap).to(x.dtype)
+
+
+class SoftcapFn(torch.autograd.Function):
+    """In-place soft-capping of (final / router) logits; the backward uses the saved output.
+    (Role of the reference's `fused_softcap`, primus/backends/megatron/core/extensions/logits_processor.py:41-50.)"""
+
+    @staticmethod
+    def forward(ctx, x, cap):
+        x = x.contiguous()
+        _lib.call("softcap_fwd", x, x, x.numel(), float(cap))
+        ctx.mark_dirty(x)
+        ctx.save_for_backward(x)
+        ctx.cap = cap
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(dy)
+        _lib.call("softcap_bwd", dy, y, dx, dy.numel(), float(ctx.cap))
+        return dx, None
+
+
+def softcap(x, cap: float | None):
+    """cap * tanh(x / cap); ``cap`` None or 0 is the identity.  On CUDA the bf16 input is overwritten."""
+    if not cap:
+        return x
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.numel() % 8:
+        return softcap_ref(x, cap)
+    if x.requires_grad and x.is_leaf:
+        x = x.clone()
+    return SoftcapFn.apply(x, cap)
+
+
+# ----------------------------------------------------------------------------------------------
 # Cross entropy (optionally vocab-parallel over a TP group)
 class _VocabParallelCERef(torch.autograd.Function):
     """Plain-PyTorch vocab-parallel cross entropy with an explicit backward (collectives are not

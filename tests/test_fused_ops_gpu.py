@@ -177,3 +177,18 @@ def test_chunked_linear_cross_entropy_matches_full_gpu():
         torch.cuda.synchronize()
         _lib.check_status()
     assert all(abs(a - b) <= 5e-3 * max(1.0, abs(a)) for a, b in zip(res[0], res[128])), res
+
+
+def test_softcap_forward_backward():
+    from primus_b200.ops import fused
+
+    torch.manual_seed(0)
+    x = (torch.randn(512, 1024, device="cuda") * 20).bfloat16().requires_grad_()
+    y = fused.softcap(x, 30.0)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.tanh(xr / 30.0) * 30.0
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)

@@ -88,3 +88,19 @@ def test_profiler_trace_and_metrics_jsonl(tmp_path):
     assert {"loss", "tokens_per_s_gpu", "grad_norm", "lr"} <= set(lines[0])
     traces = list((tmp_path / "profiler").glob("primus-b200-exp[[]unit[]]-rank[[]0[]].*.pt.trace.json"))
     assert len(traces) == 1 and traces[0].stat().st_size > 1000
+
+
+def test_logit_softcapping_bounds_the_logits_and_trains():
+    """final_logit_softcapping: logits stay inside (-cap, cap) and the model still trains; the attention variant is
+    rejected because the attention kernels do not implement it."""
+    import pytest
+
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import fused
+
+    x = torch.randn(8, 16) * 50
+    y = fused.softcap(x, 30.0)
+    assert y.abs().max() < 30.0 and torch.allclose(y, torch.tanh(x / 30.0) * 30.0)
+    assert fused.softcap(x, None) is x
+    with pytest.raises(NotImplementedError):
+        TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, attn_logit_softcapping=50.0)

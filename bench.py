@@ -339,6 +339,7 @@ def main() -> int:
             "tokens_per_s_per_gpu": value / world,
             "model_tflops_per_gpu": value / world * flops_tok / 1e12,
             "gpu_launches": launches, "loss": final_loss, "clocks": clocks,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
             "baseline_ref": "16224 tok/s/GPU, Llama-3.1-8B FP8 on 8x MI325X (reference docs)",
             "impl": "primus_b200",
         }

@@ -287,10 +287,23 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
   }
 }
 
+// gated-unit activations: kind 0 = SiLU (SwiGLU), 1 = tanh-approximated GELU (GEGLU)
+__device__ __forceinline__ float gate_act(float g, int kind, float& dact) {
+  if (kind == 0) {
+    const float sig = pb::fast_sigmoid(g);
+    dact = sig * (1.f + g * (1.f - sig));
+    return g * sig;
+  }
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (g + k1 * g * g * g));
+  dact = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+  return 0.5f * g * (1.f + t);
+}
+
 // ------------------------------------------------------------------ SwiGLU
 // in: [T, 2I] = [gate | up]; out[T, I] = silu(min(g,clamp)) * clip(u,+-clamp) * prob[t]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ probs,
-                                  __nv_bfloat16* __restrict__ out, long T, int I, float clamp) {
+                                  __nv_bfloat16* __restrict__ out, long T, int I, float clamp, int kind) {
   const int vec_per_row = I / 8;
   const long total = T * vec_per_row;
   for (long idx = blockIdx.x * (long)blockDim.x + threadIdx.x; idx < total;
@@ -309,8 +322,13 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, const fl
         gg = fminf(gg, clamp);
         uu = fminf(fmaxf(uu, -clamp), clamp);
       }
-      const float sig = pb::fast_sigmoid(gg);
-      o[j] = gg * sig * uu * p;
+      if (kind == 0) {
+        const float sig = pb::fast_sigmoid(gg);
+        o[j] = gg * sig * uu * p;
+      } else {
+        float unused;
+        o[j] = gate_act(gg, kind, unused) * uu * p;
+      }
     }
     *reinterpret_cast<Bf8*>(out + t * (long)I + v * 8) = f_to_bf8(o);
   }
@@ -319,7 +337,7 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, const fl
 // din[T,2I] from dy[T,I]; dprobs[t] = sum_i dy * silu(g) * u (one warp per row when probs given)
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ in,
                                   const float* __restrict__ probs, __nv_bfloat16* __restrict__ din,
-                                  float* __restrict__ dprobs, long T, int I, float clamp) {
+                                  float* __restrict__ dprobs, long T, int I, float clamp, int kind) {
   const int vec_per_row = I / 8;
   const int lane = threadIdx.x & 31;
   const long warp_global = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
@@ -342,11 +360,17 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __
           if (uu > clamp) { uu = clamp; umask = 0.f; }
           if (uu < -clamp) { uu = -clamp; umask = 0.f; }
         }
-        const float sig = pb::fast_sigmoid(gg);
-        const float sl = gg * sig;
+        float sl, dsl;
+        if (kind == 0) {
+          const float sig = pb::fast_sigmoid(gg);
+          sl = gg * sig;
+          dsl = sig * (1.f + gg * (1.f - sig));
+        } else {
+          sl = gate_act(gg, kind, dsl);
+        }
         dp += fd[j] * sl * uu;
         const float d = fd[j] * p;
-        og[j] = d * uu * sig * (1.f + gg * (1.f - sig)) * gmask;
+        og[j] = d * uu * dsl * gmask;
         ou[j] = d * sl * umask;
       }
       __nv_bfloat16* o = din + t * 2L * I + v * 8;
@@ -662,20 +686,21 @@ int pb_softcap_bwd(const void* dy, const void* y, void* dx, long n, float cap, c
   PB_CHECK_LAUNCH();
 }
 
-int pb_swiglu_fwd(const void* in, const float* probs, void* out, long T, int I, float clamp, cudaStream_t s) {
+// kind: 0 SiLU gate (SwiGLU), 1 tanh-GELU gate (GEGLU)
+int pb_swiglu_fwd(const void* in, const float* probs, void* out, long T, int I, float clamp, int kind, cudaStream_t s) {
   if (I % 8) return -2;
   if (T == 0) return 0;
   swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, s>>>((const __nv_bfloat16*)in, probs,
-                                                              (__nv_bfloat16*)out, T, I, clamp);
+                                                              (__nv_bfloat16*)out, T, I, clamp, kind);
   PB_CHECK_LAUNCH();
 }
 
 int pb_swiglu_bwd(const void* dy, const void* in, const float* probs, void* din, float* dprobs, long T,
-                  int I, float clamp, cudaStream_t s) {
+                  int I, float clamp, int kind, cudaStream_t s) {
   if (I % 8) return -2;
   if (T == 0) return 0;
   swiglu_bwd_kernel<<<grid_for(T * 32, 256), 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)in,
-                                                         probs, (__nv_bfloat16*)din, dprobs, T, I, clamp);
+                                                         probs, (__nv_bfloat16*)din, dprobs, T, I, clamp, kind);
   PB_CHECK_LAUNCH();
 }
 

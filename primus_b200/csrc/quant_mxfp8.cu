@@ -274,7 +274,8 @@ swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_b
       const float sig = pb::fast_sigmoid(gg);
       const float sl = gg * sig;
       const float d = fd[j] * 1.f;
-      og[j] = d * uu * sig * (1.f + gg * (1.f - sig)) * gmask;
+      const float dsl = sig * (1.f + gg * (1.f - sig));
+      og[j] = d * uu * dsl * gmask;
       ou[j] = d * sl * umask;
     }
     *reinterpret_cast<uint4*>(&tile_g[r * PITCH + c8]) = bf8_pack(og);

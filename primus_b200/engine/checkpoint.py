@@ -150,6 +150,12 @@ def read_tracker(root: str) -> Optional[str]:
         return f.read().strip()
 
 
+def latest_iteration(root: str) -> Optional[int]:
+    """Iteration of the newest checkpoint under ``root`` (None: nothing saved yet, or only a release checkpoint)."""
+    t = read_tracker(root)
+    return int(t) if t is not None and t.isdigit() else None
+
+
 _RENAMES = ((".self_attention.input_layernorm.", ".input_layernorm."),
             (".mlp.experts.fc1_weight.weight", ".mlp.experts.linear_fc1.weight"),
             (".mlp.experts.fc2_weight.weight", ".mlp.experts.linear_fc2.weight"))

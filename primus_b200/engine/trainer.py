@@ -75,6 +75,9 @@ class TrainConfig:
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
     exit_signal_handler: bool = False
+    pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
+    inprocess_restart: bool = False    # reload the newest checkpoint and continue after a failure all ranks agree on
+    inprocess_max_restarts: int = 3
     check_for_spiky_loss: bool = False
     check_for_large_grads: bool = False
     rerun_mode: str = "disabled"
@@ -328,6 +331,11 @@ class Trainer:
         micro_batches = self.stager.next_step()
         if self.st.cp > 1:
             micro_batches = [self._cp_shard(mb) for mb in micro_batches]
+        if self.st.pp > 1 and self.tcfg.pp_warmup and not getattr(self, "_pp_warmed", False):
+            from ..parallel.pipeline import pipeline_warmup
+
+            pipeline_warmup(self, micro_batches[0])
+            self._pp_warmed = True
         for buf in self.buffers:
             buf.zero_grad()
         if self.st.pp > 1:
@@ -364,9 +372,40 @@ class Trainer:
 
     # ------------------------------------------------------------------ loop
     def train(self, num_iters: Optional[int] = None, on_step: Optional[Callable] = None) -> list[float]:
+        """Runs the step loop.  With ``inprocess_restart`` a failure that every rank sees at the same step (non-finite
+        reduced loss, a persistent fault reported by the rerun state machine) does not end the process: the trainer
+        reloads the newest checkpoint under ``save`` and continues, up to ``inprocess_max_restarts`` times (the role
+        of the reference's in-process restart wrapper, primus/backends/megatron/megatron_pretrain_trainer.py:195-204).
+        Failures that only one rank can see are re-raised: they need the job-level restart."""
+        tc = self.tcfg
+        if not tc.inprocess_restart:
+            return self._train_loop(num_iters, on_step)
+        from . import checkpoint, fault
+
+        target = self.iteration + (num_iters if num_iters is not None else tc.train_iters - self.iteration)
+        losses: list[float] = []
+        restarts = 0
+        while True:
+            try:
+                self._train_loop(target - self.iteration, on_step, losses)
+                return losses
+            except (FloatingPointError, fault.PersistentFault) as e:
+                while losses and not math.isfinite(losses[-1]):
+                    losses.pop()             # the value that tripped the guard
+                latest = checkpoint.latest_iteration(tc.save) if tc.save else None
+                if restarts >= tc.inprocess_max_restarts or latest is None:
+                    raise
+                restarts += 1
+                self.log(f"[inprocess_restart] {type(e).__name__}: {e}; restart {restarts}/{tc.inprocess_max_restarts} "
+                         f"from iteration {latest}")
+                self.load_checkpoint(tc.save)
+                self.restarts = restarts
+
+    def _train_loop(self, num_iters: Optional[int] = None, on_step: Optional[Callable] = None,
+                    losses: Optional[list] = None) -> list[float]:
         tc = self.tcfg
         n = num_iters if num_iters is not None else tc.train_iters - self.iteration
-        losses = []
+        losses = [] if losses is None else losses
         if tc.manual_gc and not self._gc_disabled:
             gc.disable()  # the reference disables Python GC around trainer.train()
             self._gc_disabled = True

@@ -32,6 +32,7 @@ class TransformerConfig:
     qk_layernorm: bool = False
     untie_embeddings_and_output_weights: bool = True
     swiglu: bool = True
+    gated_activation: str = "silu"    # gate of the gated linear unit: "silu" (SwiGLU) or "gelu" (GEGLU, tanh form)
     add_bias_linear: bool = False
     activation_func_clamp_value: float = 0.0
     init_method_std: float = 0.02

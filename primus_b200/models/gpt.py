@@ -134,13 +134,15 @@ class MLP(nn.Module):
         sp = cfg.sequence_parallel and st.tp > 1
         h1, xsum = layers.norm_linear(hidden, residual, self.linear_fc1.layer_norm_weight, self.linear_fc1.weight,
                                       cfg.norm_epsilon, tpg, sp)
-        out = layers.swiglu_linear(h1, self.linear_fc2.weight, None, cfg.activation_func_clamp_value, tpg, sp)
+        out = layers.swiglu_linear(h1, self.linear_fc2.weight, None, cfg.activation_func_clamp_value, tpg, sp,
+                                   cfg.gated_activation)
         return out, xsum
 
     def forward_normed(self, y):
         """MLP on an already-normalised input (shared experts / per-expert use). No TP comm."""
         h1 = gemm.linear(y, self.linear_fc1.weight)
-        return layers.swiglu_linear(h1, self.linear_fc2.weight, None, self.cfg.activation_func_clamp_value)
+        return layers.swiglu_linear(h1, self.linear_fc2.weight, None, self.cfg.activation_func_clamp_value,
+                                    act=self.cfg.gated_activation)
 
 
 class TransformerLayer(nn.Module):

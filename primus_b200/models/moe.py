@@ -100,7 +100,7 @@ class MoELayer(nn.Module):
     def experts_forward(self, x_perm, probs_perm, sched):
         cfg = self.cfg
         h1 = moe_ops.grouped_linear(x_perm, self.experts.fc1_weight.weight, sched)
-        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value)
+        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value, cfg.gated_activation)
         return moe_ops.grouped_linear(act, self.experts.fc2_weight.weight, sched)
 
     def forward(self, y):
@@ -144,7 +144,7 @@ class MoELayer(nn.Module):
                                     cfg.moe_fused_capacity_factor)
         plan = ws.plan(idx, probs)
         h1, probs_perm = fused_ep.dispatch_gemm1(y, probs, self.experts.fc1_weight.weight, ws, plan)
-        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value)
+        act = fused.swiglu(h1, probs_perm, cfg.activation_func_clamp_value, cfg.gated_activation)
         return fused_ep.gemm2_combine(act, self.experts.fc2_weight.weight, ws, plan)
 
     # ------------------------------------------------------------------ expert parallel (NCCL all-to-all)

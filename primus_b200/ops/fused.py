@@ -174,13 +174,16 @@ def rope(x, cos, sin, pos=None, rot_dim=None):
 
 # ----------------------------------------------------------------------------------------------
 # SwiGLU: in [T, 2I] = [gate | up]
-def swiglu_ref(x, probs=None, clamp=0.0):
+GATE_KINDS = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1}
+
+
+def swiglu_ref(x, probs=None, clamp=0.0, act="silu"):
     I = x.shape[-1] // 2
     g, u = x[..., :I].float(), x[..., I:].float()
     if clamp and clamp > 0:
         g = g.clamp(max=clamp)
         u = u.clamp(-clamp, clamp)
-    y = torch.nn.functional.silu(g) * u
+    y = (torch.nn.functional.silu(g) if GATE_KINDS[act] == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
     if probs is not None:
         y = y * probs.float().reshape(*y.shape[:-1], 1)
     return y.to(x.dtype)
@@ -188,13 +191,14 @@ def swiglu_ref(x, probs=None, clamp=0.0):
 
 class SwiGLUFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, probs, clamp):
+    def forward(ctx, x, probs, clamp, act="silu"):
         I = x.shape[-1] // 2
         x2 = x.reshape(-1, 2 * I)
         T = x2.shape[0]
         out = torch.empty(T, I, dtype=x.dtype, device=x.device)
         p = probs.reshape(-1).float().contiguous() if probs is not None else None
-        _lib.call("swiglu_fwd", x2, p, out, T, I, float(clamp))
+        ctx.kind = GATE_KINDS[act]
+        _lib.call("swiglu_fwd", x2, p, out, T, I, float(clamp), ctx.kind)
         ctx.save_for_backward(x2, p if p is not None else torch.empty(0))
         ctx.has_probs = probs is not None
         ctx.clamp = clamp
@@ -213,15 +217,18 @@ class SwiGLUFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         din = torch.empty_like(x2)
         dprobs = torch.empty(T, dtype=torch.float32, device=x2.device) if ctx.has_probs else None
-        _lib.call("swiglu_bwd", dy2, x2, p if ctx.has_probs else None, din, dprobs, T, I, float(ctx.clamp))
+        _lib.call("swiglu_bwd", dy2, x2, p if ctx.has_probs else None, din, dprobs, T, I, float(ctx.clamp), ctx.kind)
         dp = dprobs.view(ctx.probs_shape).to(ctx.probs_dtype) if ctx.has_probs else None
-        return din.view(ctx.shape), dp, None
+        return din.view(ctx.shape), dp, None, None
 
 
-def swiglu(x, probs=None, clamp=0.0):
+def swiglu(x, probs=None, clamp=0.0, act="silu"):
+    """Gated linear unit ``act(gate) * up [* probs]`` for x = [gate | up]; ``act``: "silu" (SwiGLU) or "gelu" (GEGLU,
+    tanh approximation) -- the reference's swiglu_with_probs / geglu_with_probs
+    (primus/backends/megatron/core/extensions/primus_turbo.py:1954-1980)."""
     if not x.is_cuda:
-        return swiglu_ref(x, probs, clamp)
-    return SwiGLUFn.apply(x, probs, clamp)
+        return swiglu_ref(x, probs, clamp, act)
+    return SwiGLUFn.apply(x, probs, clamp, act)
 
 
 # ----------------------------------------------------------------------------------------------

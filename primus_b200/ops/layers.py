@@ -124,10 +124,12 @@ def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_p
 
 
 # ----------------------------------------------------------------------------------------------
-def _swiglu_fp8_fusable(h1, weight, probs, tp_group) -> bool:
+def _swiglu_fp8_fusable(h1, weight, probs, tp_group, act="silu") -> bool:
     """MXFP8 recipe on, plain (no routing probabilities, no tensor parallelism) and every dimension a multiple of 128:
     the SwiGLU kernels then emit MXFP8 directly for the GEMMs around them."""
     if gemm.fp8_recipe() is None or not gemm.FUSE_SWIGLU_QUANT or probs is not None or tp_group is not None:
+        return False
+    if fused.GATE_KINDS[act] != 0:      # the fused quantising kernels implement the SiLU gate only
         return False
     if getattr(weight, "_fp8_exempt", False) or h1.dtype != torch.bfloat16:
         return False
@@ -138,12 +140,13 @@ def _swiglu_fp8_fusable(h1, weight, probs, tp_group) -> bool:
 
 class SwiGLULinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h1, weight, probs, clamp, tp_group, sp):
+    def forward(ctx, h1, weight, probs, clamp, tp_group, sp, act="silu"):
+        ctx.kind = fused.GATE_KINDS[act]
         I2 = h1.shape[-1]
         I = I2 // 2
         x2 = h1.reshape(-1, I2)
         T = x2.shape[0]
-        ctx.fp8_fused = _swiglu_fp8_fusable(h1, weight, probs, tp_group) and x2.is_contiguous()
+        ctx.fp8_fused = _swiglu_fp8_fusable(h1, weight, probs, tp_group, act) and x2.is_contiguous()
         if ctx.fp8_fused:
             from . import fp8
 
@@ -162,13 +165,13 @@ class SwiGLULinearFn(torch.autograd.Function):
             ctx.shape = h1.shape
             ctx.weight_ref = weight
             return out
-        act = torch.empty(T, I, dtype=h1.dtype, device=h1.device)
+        act_buf = torch.empty(T, I, dtype=h1.dtype, device=h1.device)
         p = probs.reshape(-1).float().contiguous() if probs is not None else None
-        _lib.call("swiglu_fwd", x2, p, act, T, I, float(clamp))
+        _lib.call("swiglu_fwd", x2, p, act_buf, T, I, float(clamp), ctx.kind)
         if sp:
-            out = fused_tp.gemm_rs(act, weight, tp_group, fused=fused_tp.ENABLED_RS)
+            out = fused_tp.gemm_rs(act_buf, weight, tp_group, fused=fused_tp.ENABLED_RS)
         else:
-            out = gemm.gemm(act, weight)
+            out = gemm.gemm(act_buf, weight)
             if tp_group is not None:
                 torch.distributed.all_reduce(out, group=tp_group)
         ctx.tp = (tp_group, sp)
@@ -221,10 +224,10 @@ class SwiGLULinearFn(torch.autograd.Function):
                 gemm.register_quantized(din, fp8.swiglu_bwd_quantize_mxfp8(x2, dact, ctx.clamp))
             else:
                 din = torch.empty_like(x2)
-                _lib.call("swiglu_bwd", dact, x2, None, din, None, T, I, float(ctx.clamp))
-            return din.view(ctx.shape), dw, None, None, None, None
+                _lib.call("swiglu_bwd", dact, x2, None, din, None, T, I, float(ctx.clamp), 0)
+            return din.view(ctx.shape), dw, None, None, None, None, None
         act = torch.empty(T, I, dtype=x2.dtype, device=x2.device)
-        _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp))
+        _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp), ctx.kind)
         if sp:
             dact, dout2 = fused_tp.ag_gemm(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED)
             dw = gemm.wgrad(dout2, act, ctx.weight_ref)
@@ -233,25 +236,25 @@ class SwiGLULinearFn(torch.autograd.Function):
             dact = gemm.gemm(dout2, weight, b_mn=True, out=act)  # reuse the activation buffer
         din = torch.empty_like(x2)
         dprobs = torch.empty(T, dtype=torch.float32, device=x2.device) if ctx.has_probs else None
-        _lib.call("swiglu_bwd", dact, x2, pp, din, dprobs, T, I, float(ctx.clamp))
+        _lib.call("swiglu_bwd", dact, x2, pp, din, dprobs, T, I, float(ctx.clamp), ctx.kind)
         dp = None
         if ctx.has_probs:
             shape, dt = ctx.probs_meta
             dp = dprobs.view(shape).to(dt)
-        return din.view(ctx.shape), dw, dp, None, None, None
+        return din.view(ctx.shape), dw, dp, None, None, None, None
 
 
-def swiglu_linear(h1, weight, probs=None, clamp=0.0, tp_group=None, sequence_parallel=False):
+def swiglu_linear(h1, weight, probs=None, clamp=0.0, tp_group=None, sequence_parallel=False, act="silu"):
     """linear(swiglu(h1) * probs) with the activation recomputed in backward.  ``weight`` may be a
     row-parallel shard: the partial outputs are reduce-scattered over tokens (sequence parallel) or
     all-reduced over ``tp_group``."""
     sp = bool(sequence_parallel and tp_group is not None)
     if not h1.is_cuda:
-        out = gemm.linear(fused.swiglu_ref(h1, probs, clamp), weight)
+        out = gemm.linear(fused.swiglu_ref(h1, probs, clamp, act), weight)
         if sp:
             return tp_comm.reduce_scatter_seq(out, tp_group)
         return tp_comm.all_reduce(out, tp_group) if tp_group is not None else out
-    return SwiGLULinearFn.apply(h1, weight, probs, clamp, tp_group, sp)
+    return SwiGLULinearFn.apply(h1, weight, probs, clamp, tp_group, sp, act)
 
 
 class RowParallelLinearFn(torch.autograd.Function):

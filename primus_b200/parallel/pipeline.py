@@ -154,3 +154,60 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
     for buf in trainer.buffers:
         buf.is_last_microbatch = True
     return total
+
+
+def pipeline_warmup(trainer, micro_batch: dict) -> None:
+    """One throw-away forward + backward of every local model chunk on fabricated boundary tensors, all stages at
+    the same time (no stage waits for its neighbour), so that the first real iteration does not pay the one-time costs
+    (allocator growth, kernel attribute setup, communicator creation by the first tensor-parallel collectives)
+    serially along the pipeline.  RNG state is restored and the gradient buffers are zeroed afterwards; no optimizer
+    step is taken.  (The reference's pipeline warm-up patch:
+    primus/backends/megatron/patches/pp_warmup_patches.py:21-60,286.)"""
+    st = trainer.st
+    pp = st.pp
+    chunks = len(trainer.model_chunks)
+    S = pp * chunks
+    algo = trainer.tcfg.pipeline_schedule
+    if st.virtual_pp and st.virtual_pp > 1 and algo == "1f1b":
+        algo = "interleaved"
+    placement = sched.build_schedule(algo, pp, max(pp, 2), st.virtual_pp)["placement"]
+    dtype, dev = trainer.mcfg.torch_dtype, trainer.device
+    cpu_rng = torch.get_rng_state()
+    cuda_rng = torch.cuda.get_rng_state(dev) if trainer.is_cuda else None
+    from ..ops import gemm as gemm_mod
+
+    gen_before = gemm_mod.weight_generation()
+    for buf in trainer.buffers:
+        buf.is_last_microbatch = False          # gradients stay local: nothing is reduced or handed to the optimizer
+    batch, seq = micro_batch["tokens"].shape
+    try:
+        for c, model in enumerate(trainer.model_chunks):
+            s = sched.stage_of(st.pp_rank, c, pp, placement)
+            hidden_in = None
+            if s > 0:
+                x = torch.randn(_p2p_shape(trainer, batch, seq), device=dev).to(dtype) * 0.02
+                x.requires_grad_(True)
+                hidden_in = (x[0], x[1], batch, seq)
+            if s == S - 1:
+                out = model(micro_batch["tokens"] if s == 0 else None, micro_batch["labels"],
+                            loss_weights=trainer._loss_weights(micro_batch), hidden_in=hidden_in, unit_upstream=True,
+                            position_ids=_pos_ids(trainer, micro_batch))
+                out.backward()
+            else:
+                h, res, _, _ = model(micro_batch["tokens"] if s == 0 else None, hidden_in=hidden_in,
+                                     position_ids=_pos_ids(trainer, micro_batch))
+                y = torch.stack([h, res if res is not None else torch.zeros_like(h)])
+                torch.autograd.backward(y, torch.randn_like(y) * 1e-3)
+        gemm_ops.WGRAD_STORE.flush_all()
+    finally:
+        for buf in trainer.buffers:
+            buf.zero_grad()
+            buf.is_last_microbatch = True
+        for m in trainer.model_chunks:
+            for mod in m.modules():
+                if hasattr(mod, "last_aux_loss"):
+                    mod.last_aux_loss = None
+        torch.set_rng_state(cpu_rng)
+        if cuda_rng is not None:
+            torch.cuda.set_rng_state(cuda_rng, dev)
+        assert gemm_mod.weight_generation() == gen_before

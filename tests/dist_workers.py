@@ -2,7 +2,8 @@
 import torch
 
 
-def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4):
+def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
+              pp_warmup=False):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
@@ -16,7 +17,7 @@ def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2,
     mc = TransformerConfig(**kw)
     tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=iters, lr=1e-2,
                      lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, pipeline_schedule=schedule,
-                     log_interval=1)
+                     log_interval=1, pp_warmup=pp_warmup)
     return mc, tc
 
 

@@ -37,6 +37,7 @@ CASES = {
     "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
     "pp2_interleaved": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved")),
+    "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
     "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),

@@ -64,6 +64,46 @@ def test_graceful_exit_checkpoints_on_sigterm(tmp_path):
     assert open(os.path.join(tc.save, "latest_checkpointed_iteration.txt")).read().strip() == "2"
 
 
+def test_inprocess_restart_reloads_the_latest_checkpoint(tmp_path):
+    """A non-finite loss (injected on the host into the reduced loss) makes the trainer reload the newest checkpoint and
+    finish the run; without a checkpoint, or after too many restarts, the error is raised."""
+    import pytest
+
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=6)
+    tc.save, tc.save_interval = str(tmp_path / "ck"), 2
+    tc.inprocess_restart, tc.inprocess_max_restarts = True, 1
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    real = tr.reduced_loss
+    state = {"fired": 0}
+
+    def flaky(loss):
+        v = real(loss)
+        if tr.iteration == 5 and state["fired"] < 1:
+            state["fired"] += 1
+            return float("nan")
+        return v
+
+    tr.reduced_loss = flaky
+    losses = tr.train()
+    assert tr.iteration == 6 and tr.restarts == 1
+    assert len(losses) == 4 + 2 and all(l == l for l in losses)   # 4 good steps, restart from iteration 4, 2 more
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=4)
+    tc.inprocess_restart = True                     # nothing saved: nothing to restart from
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    tr.reduced_loss = lambda loss: float("nan")
+    with pytest.raises(FloatingPointError):
+        tr.train()
+
+
 def _lost_rank_worker(rank, world, store_path):
     import torch.distributed as dist
 

@@ -192,3 +192,26 @@ def test_softcap_forward_backward():
     yr.backward(g.float())
     torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("with_probs", [False, True])
+def test_gated_unit_activations(act, with_probs):
+    """SwiGLU / GEGLU (optionally weighted by routing probabilities) forward and backward vs the fp32 reference."""
+    from primus_b200.ops import fused
+
+    torch.manual_seed(1)
+    T, I = 384, 256
+    x = torch.randn(T, 2 * I, device="cuda").bfloat16().requires_grad_()
+    p = torch.rand(T, device="cuda").requires_grad_() if with_probs else None
+    y = fused.swiglu(x, p, 0.0, act)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    pr = p.detach().clone().requires_grad_() if with_probs else None
+    yr = fused.swiglu_ref(xr, pr, 0.0, act)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    if with_probs:
+        torch.testing.assert_close(p.grad, pr.grad, rtol=3e-2, atol=0.3)

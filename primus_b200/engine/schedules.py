@@ -120,4 +120,25 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
         else:
             fwd += 6 * h * cfg.ffn_hidden_size
     fwd += 2 * h * V
+    if getattr(cfg, "mtp_num_layers", None):
+        # every depth: one more layer of the last layer's kind, the 2h -> h projection and the shared output head
+        last = L - 1
+        layer = 0.0
+        if cfg.multi_latent_attention:
+            qd = cfg.qk_head_dim + cfg.qk_pos_emb_head_dim
+            nh = cfg.num_attention_heads
+            layer += (2 * h * cfg.q_lora_rank + 2 * cfg.q_lora_rank * nh * qd) if cfg.q_lora_rank else 2 * h * nh * qd
+            layer += 2 * h * (cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
+            layer += 2 * cfg.kv_lora_rank * nh * (cfg.qk_head_dim + cfg.v_head_dim) + 2 * nh * cfg.v_head_dim * h
+            layer += 2 * seq_len * nh * (qd + cfg.v_head_dim) * (0.5 if causal_half else 1.0)
+        else:
+            layer += 2 * h * cfg.qkv_width + 2 * cfg.num_attention_heads * cfg.kv_channels * h
+            layer += 4 * seq_len * cfg.num_attention_heads * cfg.kv_channels * (0.5 if causal_half else 1.0)
+        if cfg.is_moe_layer(last):
+            layer += 2 * h * cfg.num_experts + cfg.moe_router_topk * 6 * h * cfg.moe_ffn_hidden_size
+            if cfg.moe_shared_expert_intermediate_size:
+                layer += 6 * h * cfg.moe_shared_expert_intermediate_size
+        else:
+            layer += 6 * h * cfg.ffn_hidden_size
+        fwd += cfg.mtp_num_layers * (layer + 2 * (2 * h) * h + 2 * h * V)
     return 3.0 * fwd

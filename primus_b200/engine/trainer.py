@@ -75,6 +75,8 @@ class TrainConfig:
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
     exit_signal_handler: bool = False
+    dump_pp_data: bool = False         # per-node pipeline timeline (one JSON per pipeline rank and iteration; it
+    pp_dump_dir: Optional[str] = None  # synchronises after every node, so the timed iterations are slower)
     pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
     inprocess_restart: bool = False    # reload the newest checkpoint and continue after a failure all ranks agree on
     inprocess_max_restarts: int = 3
@@ -341,7 +343,16 @@ class Trainer:
         if self.st.pp > 1:
             from ..parallel.pipeline import run_pipeline_schedule
 
-            loss = run_pipeline_schedule(self, micro_batches)
+            timeline = None
+            if self.tcfg.dump_pp_data and self.st.dp_rank == 0 and self.st.tp_rank == 0:
+                from ..parallel.pipeline import PipelineTimeline
+
+                timeline = PipelineTimeline()
+            loss = run_pipeline_schedule(self, micro_batches, timeline)
+            if timeline is not None:
+                d = self.tcfg.pp_dump_dir or os.path.join(self.tcfg.save or ".", "pp_data")
+                timeline.dump(os.path.join(d, f"pp_rank{self.st.pp_rank}_iter{self.iteration + 1}.json"), self.st.pp_rank,
+                              self.iteration + 1, {"schedule": self.tcfg.pipeline_schedule, "pp": self.st.pp})
         else:
             loss = self.forward_backward_no_pipelining(micro_batches)
         self.stager.prefetch()  # stage the next step's batch while the optimizer runs

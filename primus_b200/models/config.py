@@ -81,6 +81,8 @@ class TransformerConfig:
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_layer_ids: Optional[List[int]] = None
     cross_entropy_chunk_tokens: int = 0  # >0: chunked linear-cross-entropy
+    mtp_num_layers: int | None = None               # multi-token prediction depths (DeepSeek-V3); None / 0: off
+    mtp_loss_scaling_factor: float = 0.1
     final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)
     router_logit_softcapping: float | None = None   # same on the MoE router logits
     attn_logit_softcapping: float | None = None     # accepted for config parity; not supported by the attention kernels

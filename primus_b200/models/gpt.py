@@ -206,6 +206,22 @@ class Decoder(nn.Module):
             self.final_layernorm.weight.sequence_parallel = cfg.sequence_parallel
 
 
+class MultiTokenPredictionLayer(nn.Module):
+    """One depth of multi-token prediction (DeepSeek-V3): the hidden state of the previous depth and the embedding of
+    the token one further ahead are normalised, concatenated, projected back to ``hidden_size`` and run through one
+    transformer layer; the shared output head then predicts the token after that.  Parameter names follow mcore:
+    ``mtp.layers.{k}.{enorm,hnorm,eh_proj,transformer_layer.*,final_layernorm}``."""
+
+    def __init__(self, cfg: TransformerConfig, device, tp: int):
+        super().__init__()
+        h = cfg.hidden_size
+        self.enorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
+        self.hnorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
+        self.eh_proj = ParamHolder(weight=_param((h, 2 * h), cfg.init_method_std, cfg.torch_dtype, device))
+        self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device, tp)
+        self.final_layernorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
+
+
 class GPTModel(nn.Module):
     """One pipeline stage (or the whole model when PP=1) of a decoder-only LM.
 
@@ -231,6 +247,14 @@ class GPTModel(nn.Module):
             self.output_layer.weight.tensor_model_parallel = tp > 1
             self.output_layer.weight.partition_dim = 0
             self.output_layer.weight._fp8_exempt = True   # the LM head stays in bf16 under an fp8 recipe
+        if post_process and cfg.mtp_num_layers:
+            st = ps.get_state()
+            if not pre_process or tp > 1 or st.cp > 1:
+                raise NotImplementedError("multi-token prediction needs the embedding on the last pipeline stage and "
+                                          "tensor / context parallel size 1 (pp = tp = cp = 1)")
+            self.mtp = nn.Module()
+            self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
+                                             for _ in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
 
     # ------------------------------------------------------------------ helpers
@@ -275,6 +299,9 @@ class GPTModel(nn.Module):
         if not self.post_process:
             return hidden, residual, batch, seq
         w = self.output_weight()
+        mtp_loss = None
+        if cfg.mtp_num_layers and labels is not None and loss_weights is not None:
+            mtp_loss = self._mtp_loss(hidden, residual, tokens, labels, loss_weights, rope, batch, seq, w, unit_upstream)
         if labels is None:
             y, _ = fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual) \
                 if residual is not None else (fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon), None)
@@ -286,8 +313,9 @@ class GPTModel(nn.Module):
             # chunked linear + cross entropy: no [tokens, vocab] logits tensor
             y = fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual)[0] \
                 if residual is not None else fused.rmsnorm(hidden, self.decoder.final_layernorm.weight, cfg.norm_epsilon)
-            return layers.chunked_linear_cross_entropy(y, w, labels.reshape(-1), loss_weights.reshape(-1), 0,
+            loss = layers.chunked_linear_cross_entropy(y, w, labels.reshape(-1), loss_weights.reshape(-1), 0,
                                                        cfg.cross_entropy_chunk_tokens)
+            return loss if mtp_loss is None else loss + mtp_loss
         logits, _ = layers.norm_linear(hidden, residual, self.decoder.final_layernorm.weight, w, cfg.norm_epsilon,
                                        st.tp_group, sp)
         logits = fused.softcap(logits, cfg.final_logit_softcapping)
@@ -295,7 +323,32 @@ class GPTModel(nn.Module):
         loss = fused.cross_entropy(logits, labels.reshape(-1), st.tp_rank * vocab_local,
                                    st.tp_group if st.tp > 1 else None,
                                    None if loss_weights is None else loss_weights.reshape(-1), unit_upstream)
+        if mtp_loss is not None:
+            loss = loss + mtp_loss
         return loss if loss_weights is not None else loss.view(batch, seq)
+
+    def _mtp_loss(self, hidden, residual, tokens, labels, loss_weights, rope, batch, seq, w_out, unit_upstream):
+        """sum_k scale / D * CE(depth k): depth k (1-based) sees tokens shifted left by k and predicts labels shifted
+        left by k; the last k positions of every sequence carry no target and get weight 0."""
+        cfg = self.cfg
+        h = hidden if residual is None else hidden + residual
+        tok, lab = tokens.reshape(batch, seq), labels.reshape(batch, seq)
+        wts = loss_weights.reshape(batch, seq)
+        total = None
+        for k, layer in enumerate(self.mtp.layers, start=1):
+            tok, lab, wts = torch.roll(tok, -1, 1), torch.roll(lab, -1, 1), torch.roll(wts, -1, 1).clone()
+            wts[:, seq - k:] = 0
+            e = self.embedding(tok.reshape(-1))
+            x = torch.cat([fused.rmsnorm(e, layer.enorm.weight, cfg.norm_epsilon),
+                           fused.rmsnorm(h, layer.hnorm.weight, cfg.norm_epsilon)], -1)
+            x = gemm.linear(x, layer.eh_proj.weight)
+            hid, res = layer.transformer_layer(x, None, rope, batch)
+            logits, _ = layers.norm_linear(hid, res, layer.final_layernorm.weight, w_out, cfg.norm_epsilon, None, False)
+            logits = fused.softcap(logits, cfg.final_logit_softcapping)
+            lk = fused.cross_entropy(logits, lab.reshape(-1), 0, None, wts.reshape(-1), unit_upstream)
+            total = lk if total is None else total + lk
+            h = hid if res is None else hid + res
+        return total * (cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers)
 
 
 def _run_layer(layer, hidden, residual, rope, batch, cfg):

@@ -35,6 +35,15 @@ class PipelineTimeline:
     def add(self, node, t0, t1):
         self.events.append({"kind": node.kind, "mb": node.mb, "chunk": node.chunk, "start": t0, "end": t1})
 
+    def dump(self, path: str, pp_rank: int, iteration: int, extra: dict | None = None) -> None:
+        """One JSON file per (rank, iteration); ``primus_b200.tools.pp_vis`` merges them."""
+        import json
+        import os
+
+        os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+        with open(path, "w") as f:
+            json.dump({"pp_rank": pp_rank, "iteration": iteration, "events": self.events, **(extra or {})}, f)
+
 
 def _p2p_shape(trainer, batch, seq):
     st = trainer.st

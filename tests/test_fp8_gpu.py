@@ -210,3 +210,32 @@ def test_grouped_gemm_mxfp8_against_dequantised_reference(counts, N, K):
             torch.testing.assert_close(xg.grad[sl].float(), dx_ref, rtol=2e-2, atol=2e-2)
         dw_ref = 1.0 + dy_c[sl].float().t() @ x_c[sl].float()
         torch.testing.assert_close(w.main_grad[e], dw_ref, rtol=1e-3, atol=1e-2)
+
+
+def test_moe_model_with_mxfp8_recipe_tracks_bf16():
+    """MoE model (grouped expert GEMMs in MXFP8 under the recipe): loss trajectory stays close to bf16."""
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import gemm
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    losses = {}
+    try:
+        for recipe in (None, "e4m3"):
+            mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2,
+                                   num_query_groups=2, vocab_size=1024, params_dtype="bf16", seq_length=512,
+                                   num_experts=8, moe_router_topk=2, moe_ffn_hidden_size=256, moe_layer_freq=[0, 1],
+                                   moe_aux_loss_coeff=1e-2, fp8=recipe, fp8_recipe="mxfp8")
+            tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=512, train_iters=6, lr=2e-3,
+                             lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1)
+            torch.manual_seed(0)
+            tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
+            losses[recipe] = tr.train()
+            torch.cuda.synchronize()
+            _lib.check_status()
+    finally:
+        gemm.set_fp8_recipe(None)
+    a, b = losses[None], losses["e4m3"]
+    assert all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, b)), (a, b)

@@ -104,3 +104,36 @@ def test_logit_softcapping_bounds_the_logits_and_trains():
     assert fused.softcap(x, None) is x
     with pytest.raises(NotImplementedError):
         TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, attn_logit_softcapping=50.0)
+
+
+def test_multi_token_prediction_adds_a_trained_auxiliary_loss():
+    """mtp_num_layers: extra depths share the embedding and the output head, add scale / D * CE to the loss, receive
+    gradients, and the FLOPs model counts them."""
+    from primus_b200.engine import schedules
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    kw = dict(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=128,
+              params_dtype="fp32", seq_length=32)
+    torch.manual_seed(0)
+    base = GPTModel(TransformerConfig(**kw), "cpu")
+    torch.manual_seed(0)
+    cfg = TransformerConfig(**kw, mtp_num_layers=2, mtp_loss_scaling_factor=0.3)
+    m = GPTModel(cfg, "cpu")
+    names = [n for n, _ in m.named_parameters()]
+    assert "mtp.layers.1.eh_proj.weight" in names and "mtp.layers.0.transformer_layer.mlp.linear_fc2.weight" in names
+    tokens = torch.randint(0, 128, (2, 32))
+    labels = torch.roll(tokens, -1, 1)
+    w = torch.full((2, 32), 1.0 / 64)
+    main = base(tokens, labels, loss_weights=w, unit_upstream=True)
+    total = m(tokens, labels, loss_weights=w, unit_upstream=True)
+    aux = (total - main).item()
+    # two depths of ~ln(128) each, weighted 0.3 / 2, with 1 and 2 target-less positions per sequence
+    assert 0.2 * 4.85 < aux < 0.4 * 4.85, aux
+    total.backward()
+    assert m.mtp.layers[1].eh_proj.weight.grad.abs().sum() > 0
+    assert m.embedding.word_embeddings.weight.grad.abs().sum() > 0
+    assert schedules.model_flops_per_token(cfg, 32) > schedules.model_flops_per_token(TransformerConfig(**kw), 32)

@@ -63,3 +63,24 @@ def test_comm_expansion_v_fold_has_no_comm_on_the_fold():
     assert not any(n.kind == "RF" and n.chunk == 1 for n in last)
     first = full[0]
     assert any(n.kind == "SF" and n.chunk == 0 for n in first) and any(n.kind == "RF" and n.chunk == 1 for n in first)
+
+
+def test_pipeline_timeline_dump_and_viewer(tmp_path):
+    """Timeline files written by the runtime are merged into a chart, bubble fractions and a Chrome trace."""
+    import json
+
+    from primus_b200.parallel.pipeline import PipelineTimeline
+    from primus_b200.parallel.pipeline_schedules import Node
+    from primus_b200.tools import pp_vis
+
+    for r in range(2):
+        tl = PipelineTimeline()
+        for i in range(3):
+            tl.add(Node("F", i, 0), r * 0.1 + i * 0.2, r * 0.1 + i * 0.2 + 0.1)
+            tl.add(Node("B", i, 0), 1 + (1 - r) * 0.1 + i * 0.3, 1 + (1 - r) * 0.1 + i * 0.3 + 0.2)
+        tl.dump(str(tmp_path / f"pp_rank{r}_iter3.json"), r, 3, {"schedule": "1f1b", "pp": 2})
+    lines, bubbles = pp_vis.main([str(tmp_path), "--width", "60", "--trace", str(tmp_path / "t.json")])
+    assert len(lines) == 2 and all(0.3 < b < 0.7 for b in bubbles.values())
+    assert "F" in lines[0] and "B" in lines[1]
+    trace = json.loads((tmp_path / "t.json").read_text())
+    assert len(trace["traceEvents"]) == 12

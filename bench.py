@@ -221,6 +221,9 @@ def main() -> int:
     ap.add_argument("--batch-per-gpu", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); dp = gpus / tp")
+    ap.add_argument("--cp", type=int, default=1, help="context-parallel size; dp = gpus / (tp * cp)")
+    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather"],
+                    help="context-parallel scheme: all-to-all over heads (Ulysses) or K/V all-gather with zig-zag chunks")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
     ap.add_argument("--precision", default="mxfp8", choices=["bf16", "mxfp8"],
@@ -256,17 +259,17 @@ def main() -> int:
         mdict["num_layers"] = args.layers
     mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
                              sequence_parallel=args.tp > 1, fp8="e4m3" if args.precision == "mxfp8" else None,
-                             fp8_recipe="mxfp8")
+                             fp8_recipe="mxfp8", context_parallel_size=args.cp, cp_comm_type=args.cp_comm)
     if args.fused_tp:
         from primus_b200.parallel import fused_tp
 
         fused_tp.ENABLED = True          # all-gather -> GEMM; the reduce-scatter side stays on NCCL (faster at tp = 8)
-    gbs = args.batch_per_gpu * world // args.tp
+    gbs = args.batch_per_gpu * world // (args.tp * args.cp)
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,
                        clip_grad=1.0, use_distributed_optimizer=True, overlap_grad_reduce=world > 1,
                        log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp)
-    ps.initialize_model_parallel(tp=args.tp, pp=1)
+    ps.initialize_model_parallel(tp=args.tp, pp=1, cp=args.cp)
     trainer = Trainer(mcfg, tcfg, device=f"cuda:{local_rank}", log_fn=lambda s: None)
 
     def barrier():
@@ -333,7 +336,7 @@ def main() -> int:
             "dtype": "bf16" if args.precision == "bf16" else "mxfp8 linear GEMMs (E4M3 + UE8M0 per 32, fp32 accumulate), bf16 attention / LM head / params, fp32 master",
             "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
             "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
-                       "micro_batch": args.micro_batch, "parallelism": f"dp{world // args.tp}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
+                       "micro_batch": args.micro_batch, "parallelism": f"dp{world // (args.tp * args.cp)}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + (f"cp{args.cp}-{args.cp_comm}" if args.cp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},
             "tokens_per_s_per_gpu": value / world,

@@ -92,8 +92,9 @@ __global__ void __launch_bounds__(BW_THREADS, 1)
 flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                       const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                       const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
-                      const float* __restrict__ lse, const float* __restrict__ delta, int seq, int hq, int hkv,
-                      float scale, int causal, int* status) {
+                      const float* __restrict__ lse, const float* __restrict__ delta, int seq, int seq_k, int q_off,
+                      int hq, int hkv, float scale, int causal, int* status) {
+  // seq: query rows per sequence, seq_k: key rows per sequence, q_off: key position of query row 0 (multiple of 128)
   using C = BwCfg<DQK, DV, MODE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -107,18 +108,24 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = hq / hkv;
-  const int num_rb = seq / BR;
-  const int num_c = seq / BC;
+  const int seq_x = (MODE == MODE_DKDV) ? seq_k : seq;   // stationary operand (K, V | Q, dO)
+  const int seq_y = (MODE == MODE_DKDV) ? seq : seq_k;   // streamed operand (Q, dO | K, V)
+  const int num_rb = seq_x / BR;
+  const int num_c = seq_y / BC;
+  const int qo = q_off / BC;                              // offset in streamed-tile units
   // grid (heads * batch, row blocks): blocks are issued x-fastest, so all heads of the longest row block start
   // first and the short ones fill the tail (work per block is proportional to the number of streamed tiles)
   const int rb = (MODE == MODE_DKDV) ? blockIdx.y : (num_rb - 1 - blockIdx.y);
   const int nxh = (MODE == MODE_DKDV) ? hkv : hq;
   const int xhead = blockIdx.x % nxh;  // MODE_DKDV: kv head; MODE_DQ: query head
   const int batch = blockIdx.x / nxh;
-  const int tok0 = batch * seq;
-  // streamed-tile schedule
-  const int c_start = (MODE == MODE_DKDV && causal) ? 2 * rb : 0;
-  const int n_per_head = (MODE == MODE_DKDV) ? (num_c - c_start) : (causal ? 2 * rb + 2 : num_c);
+  const int tok0 = batch * seq_x;
+  const int toky0 = batch * seq_y;
+  // streamed-tile schedule: MODE_DKDV streams the query tiles at or after this key block, MODE_DQ the key tiles at or
+  // before this query block (query row i sits at key position q_off + i)
+  const int c_start = (MODE == MODE_DKDV && causal) ? max(0, 2 * rb - qo) : 0;
+  const int n_per_head = (MODE == MODE_DKDV) ? max(0, num_c - c_start)
+                                             : (causal ? min(num_c, 2 * rb + 2 + qo) : num_c);
   const int n_iter = (MODE == MODE_DKDV) ? g * n_per_head : n_per_head;
   volatile int* abort_flag = &bars->abort_flag;
   const float sl2 = scale * 1.4426950408889634f;
@@ -166,11 +173,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
 #pragma unroll
         for (int a = 0; a < DQK / 64; ++a)
           pb::tma_load_3d(y1_smem + st * C::Y1_BYTES + a * YATOM, &tmY1, &bars->y_full[st], a * 64, yhead,
-                          tok0 + cs * BC);
+                          toky0 + cs * BC);
 #pragma unroll
         for (int a = 0; a < DV / 64; ++a)
           pb::tma_load_3d(y2_smem + st * C::Y2_BYTES + a * YATOM, &tmY2, &bars->y_full[st], a * 64, yhead,
-                          tok0 + cs * BC);
+                          toky0 + cs * BC);
         if (MODE == MODE_DKDV) {
           const long off = ((long)batch * hq + yhead) * seq + cs * BC;
           bulk_load_1d(stat_smem + st * 128, lse + off, 256, &bars->y_full[st]);
@@ -265,7 +272,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       }
       pb::tc_fence_after();
       const uint32_t ts = tmem_sbuf + lane_addr + sb * 128;
-      const bool diag = causal && (cs >= 2 * rb) && (cs <= 2 * rb + 1);
+      const int cs_rel = (MODE == MODE_DKDV) ? cs + qo : cs - qo;   // streamed tile index in the stationary block's frame
+      const bool diag = causal && (cs_rel >= 2 * rb) && (cs_rel <= 2 * rb + 1);
       const float* st_lse = stat_smem + st * 128;
       const float* st_delta = st_lse + 64;
       uint32_t s[BC], dp[BC];
@@ -294,7 +302,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
             for (int u = 0; u < 4; ++u) {
               float p = pb::fast_exp2(fmaf(__uint_as_float(s[c + u]), sl2, -l2[u]));
               if (DIAG) {
-                const int col_g = cs * BC + c + u;
+                const int col_g = cs_rel * BC + c + u;
                 const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
                 if (!valid) p = 0.f;
               }
@@ -403,7 +411,7 @@ struct BwdArgs {
   const float* lse;
   float* delta;
   void *dq, *dk, *dv;
-  int batch, seq, hq, hkv;
+  int batch, seq, seq_k, q_off, hq, hkv;
   long q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row;
   float scale;
   int causal;
@@ -426,14 +434,15 @@ int launch_bwd(const BwdArgs& a) {
   }
   int rc;
   CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64, dq_m, dk_m, dv_m;
-#define MK(m, p, heads, d, row, br) \
-  if ((rc = pbh::make_tmap_3d(&m, p, bf, 2, T, heads, d, d, row, br, 1, 64, sw))) return rc;
-  MK(q128, a.q, a.hq, DQK, a.q_row, 128) MK(do128, a.d_o, a.hq, DV, a.do_row, 128)
-  MK(k128, a.k, a.hkv, DQK, a.k_row, 128) MK(v128, a.v, a.hkv, DV, a.v_row, 128)
-  MK(q64, a.q, a.hq, DQK, a.q_row, 64) MK(do64, a.d_o, a.hq, DV, a.do_row, 64)
-  MK(k64, a.k, a.hkv, DQK, a.k_row, 64) MK(v64, a.v, a.hkv, DV, a.v_row, 64)
-  MK(dq_m, a.dq, a.hq, DQK, a.dq_row, 128) MK(dk_m, a.dk, a.hkv, DQK, a.dk_row, 128)
-  MK(dv_m, a.dv, a.hkv, DV, a.dv_row, 128)
+  const long TK = (long)a.batch * a.seq_k;
+#define MK(m, p, rows, heads, d, row, br) \
+  if ((rc = pbh::make_tmap_3d(&m, p, bf, 2, rows, heads, d, d, row, br, 1, 64, sw))) return rc;
+  MK(q128, a.q, T, a.hq, DQK, a.q_row, 128) MK(do128, a.d_o, T, a.hq, DV, a.do_row, 128)
+  MK(k128, a.k, TK, a.hkv, DQK, a.k_row, 128) MK(v128, a.v, TK, a.hkv, DV, a.v_row, 128)
+  MK(q64, a.q, T, a.hq, DQK, a.q_row, 64) MK(do64, a.d_o, T, a.hq, DV, a.do_row, 64)
+  MK(k64, a.k, TK, a.hkv, DQK, a.k_row, 64) MK(v64, a.v, TK, a.hkv, DV, a.v_row, 64)
+  MK(dq_m, a.dq, T, a.hq, DQK, a.dq_row, 128) MK(dk_m, a.dk, TK, a.hkv, DQK, a.dk_row, 128)
+  MK(dv_m, a.dv, TK, a.hkv, DV, a.dv_row, 128)
 #undef MK
   {
     using C = BwCfg<DQK, DV, MODE_DKDV>;
@@ -444,9 +453,10 @@ int launch_bwd(const BwdArgs& a) {
       if (e != cudaSuccess) return (int)e;
       attr_set = true;
     }
-    dim3 grid(a.hkv * a.batch, a.seq / BR, 1);
-    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
-                                                       a.hq, a.hkv, a.scale, a.causal, a.status);
+    dim3 grid(a.hkv * a.batch, a.seq_k / BR, 1);
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m,
+                                                       a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.status);
   }
   {
     using C = BwCfg<DQK, DV, MODE_DQ>;
@@ -458,27 +468,38 @@ int launch_bwd(const BwdArgs& a) {
       attr_set = true;
     }
     dim3 grid(a.hq * a.batch, a.seq / BR, 1);
-    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m, a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq,
-                                                       a.hq, a.hkv, a.scale, a.causal, a.status);
+    kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m,
+                                                       a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.status);
   }
   return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// Layouts as in pb_flash_attn_fwd. delta: fp32 scratch [2, batch, hq, seq] (written here: row sums of dO*O,
-// then the log-sum-exp in log2 units).
-extern "C" int pb_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
-                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
-                                 int hq, int hkv, int d_qk, int d_v, long q_row, long k_row, long v_row, long o_row,
-                                 long do_row, long dq_row, long dk_row, long dv_row, float scale, int causal,
-                                 int* status, cudaStream_t stream) {
-  if (seq % 128 || hq % hkv) return -2;
+// Layouts as in pb_flash_attn_fwd_ex (q / o / d_o / dq: batch*seq rows; k / v / dk / dv: batch*seq_k rows).
+// delta: fp32 scratch [2, batch, hq, seq] (written here: row sums of dO*O, then the log-sum-exp in log2 units).
+extern "C" int pb_flash_attn_bwd_ex(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                    const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
+                                    int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row,
+                                    long v_row, long o_row, long do_row, long dq_row, long dk_row, long dv_row,
+                                    float scale, int causal, int* status, cudaStream_t stream) {
+  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv) return -2;
+  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
   if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
-  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, hq, hkv, q_row, k_row, v_row, o_row,
+  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row,
             do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
   if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
   if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
   if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
   return -3;
+}
+
+extern "C" int pb_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
+                                 int hq, int hkv, int d_qk, int d_v, long q_row, long k_row, long v_row, long o_row,
+                                 long do_row, long dq_row, long dk_row, long dv_row, float scale, int causal,
+                                 int* status, cudaStream_t stream) {
+  return pb_flash_attn_bwd_ex(d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq, 0, hq, hkv, d_qk, d_v, q_row,
+                              k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row, scale, causal, status, stream);
 }

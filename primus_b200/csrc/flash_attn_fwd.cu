@@ -68,8 +68,10 @@ template <int DQK, int DV>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                      float* __restrict__ lse, int seq, int hq, int hkv, float scale_log2, int causal,
-                      int* status) {
+                      float* __restrict__ lse, int seq, int seq_k, int q_off_blocks, int hq, int hkv,
+                      float scale_log2, int causal, int* status) {
+  // seq: query rows per sequence; seq_k: key rows per sequence; query row i sits at key position
+  // q_off_blocks * 128 + i (causal masking is relative to that position)
   using C = FaCfg<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -88,10 +90,12 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int batch = blockIdx.x / hq;
   const int kv_head = head / (hq / hkv);
   const int tok0 = batch * seq;
+  const int tokk0 = batch * seq_k;
   const int qt[2] = {2 * pair, 2 * pair + 1};  // 128-row query tile indices
   const bool active1 = qt[1] < num_q128;
-  const int n_kv = seq / BKV;
-  const int nb[2] = {causal ? qt[0] + 1 : n_kv, active1 ? (causal ? qt[1] + 1 : n_kv) : 0};
+  const int n_kv = seq_k / BKV;
+  const int nb[2] = {causal ? min(n_kv, qt[0] + q_off_blocks + 1) : n_kv,
+                     active1 ? (causal ? min(n_kv, qt[1] + q_off_blocks + 1) : n_kv) : 0};
   const int n_max = nb[0] > nb[1] ? nb[0] : nb[1];
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -141,13 +145,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int a = 0; a < DQK / 64; ++a)
           pb::tma_load_3d(k_smem + ks * C::K_BYTES + a * ATOM_BYTES, &tmK, &bars->k_full[ks], a * 64,
-                          kv_head, tok0 + j * BKV);
+                          kv_head, tokk0 + j * BKV);
         FA_WAIT(&bars->v_empty[vs], ((j / C::VS) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
         pb::mbar_expect_tx(&bars->v_full[vs], C::V_BYTES);
 #pragma unroll
         for (int a = 0; a < DV / 64; ++a)
           pb::tma_load_3d(v_smem + vs * C::V_BYTES + a * ATOM_BYTES, &tmV, &bars->v_full[vs], a * 64,
-                          kv_head, tok0 + j * BKV);
+                          kv_head, tokk0 + j * BKV);
       }
     }
   } else if (warp == 1) {
@@ -222,7 +226,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int j = 0; j < n_blocks && ok; ++j) {
       FA_WAIT(&bars->s_full[t], j & 1, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
-      const bool diag = causal && (j == qt[t]);
+      const bool diag = causal && (j == qt[t] + q_off_blocks);
       // the whole S row (128 fp32) is read once and stays in registers for both passes
       uint32_t sr[128];
 #pragma unroll
@@ -333,18 +337,19 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 }
 
 template <int DQK, int DV>
-int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq, int hq,
-               int hkv, long q_row, long k_row, long v_row, long o_row, float scale, int causal, int* status,
-               cudaStream_t stream) {
+int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq, int seq_k,
+               int q_off, int hq, int hkv, long q_row, long k_row, long v_row, long o_row, float scale, int causal,
+               int* status, cudaStream_t stream) {
   using C = FaCfg<DQK, DV>;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   const long T = (long)batch * seq;
+  const long TK = (long)batch * seq_k;
   CUtensorMap tq, tk, tv, to;
   int rc;
   if ((rc = pbh::make_tmap_3d(&tq, q, bf, 2, T, hq, DQK, DQK, q_row, BQ, 1, 64, sw))) return rc;
-  if ((rc = pbh::make_tmap_3d(&tk, k, bf, 2, T, hkv, DQK, DQK, k_row, BKV, 1, 64, sw))) return rc;
-  if ((rc = pbh::make_tmap_3d(&tv, v, bf, 2, T, hkv, DV, DV, v_row, BKV, 1, 64, sw))) return rc;
+  if ((rc = pbh::make_tmap_3d(&tk, k, bf, 2, TK, hkv, DQK, DQK, k_row, BKV, 1, 64, sw))) return rc;
+  if ((rc = pbh::make_tmap_3d(&tv, v, bf, 2, TK, hkv, DV, DV, v_row, BKV, 1, 64, sw))) return rc;
   if ((rc = pbh::make_tmap_3d(&to, o, bf, 2, T, hq, DV, DV, o_row, BQ, 1, 64, sw))) return rc;
   auto kern = flash_attn_fwd_kernel<DQK, DV>;
   static bool attr_set = false;
@@ -354,27 +359,41 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
     attr_set = true;
   }
   dim3 grid(hq * batch, (seq / BQ + 1) / 2, 1);
-  kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, hq, hkv,
+  kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, seq_k, q_off / BQ, hq, hkv,
                                                    scale * 1.4426950408889634f, causal, status);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// q: [batch*seq, hq, d_qk] (row pitch q_row elements, heads contiguous), k: [.., hkv, d_qk], v: [.., hkv, d_v],
-// o: [.., hq, d_v]; lse: [batch, hq, seq] fp32 (natural log). seq must be a multiple of 128.
+// q: [batch*seq, hq, d_qk] (row pitch q_row elements, heads contiguous), k: [batch*seq_k, hkv, d_qk],
+// v: [batch*seq_k, hkv, d_v], o: [batch*seq, hq, d_v]; lse: [batch, hq, seq] fp32 (natural log).  seq, seq_k and q_off
+// are multiples of 128.  Query row i of a sequence sits at key position q_off + i: with `causal` it attends to keys
+// [0, q_off + i] and q_off + seq must equal seq_k (the layout of a sequence chunk attending to the gathered prefix).
+extern "C" int pb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+                                    int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
+                                    long k_row, long v_row, long o_row, float scale, int causal, int* status,
+                                    cudaStream_t stream) {
+  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) ||
+      (o_row % 8))
+    return -2;
+  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
+  if (d_qk == 128 && d_v == 128)
+    return launch_fwd<128, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
+                                causal, status, stream);
+  if (d_qk == 192 && d_v == 128)
+    return launch_fwd<192, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
+                                causal, status, stream);
+  if (d_qk == 64 && d_v == 64)
+    return launch_fwd<64, 64>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
+                              causal, status, stream);
+  return -3;
+}
+
+// Self-attention form: seq_k = seq, q_off = 0.
 extern "C" int pb_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
                                  int seq, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row, long v_row,
                                  long o_row, float scale, int causal, int* status, cudaStream_t stream) {
-  if (seq % 128 || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) || (o_row % 8)) return -2;
-  if (d_qk == 128 && d_v == 128)
-    return launch_fwd<128, 128>(q, k, v, o, lse, batch, seq, hq, hkv, q_row, k_row, v_row, o_row, scale, causal,
-                                status, stream);
-  if (d_qk == 192 && d_v == 128)
-    return launch_fwd<192, 128>(q, k, v, o, lse, batch, seq, hq, hkv, q_row, k_row, v_row, o_row, scale, causal,
-                                status, stream);
-  if (d_qk == 64 && d_v == 64)
-    return launch_fwd<64, 64>(q, k, v, o, lse, batch, seq, hq, hkv, q_row, k_row, v_row, o_row, scale, causal,
-                              status, stream);
-  return -3;
+  return pb_flash_attn_fwd_ex(q, k, v, o, lse, batch, seq, seq, 0, hq, hkv, d_qk, d_v, q_row, k_row, v_row, o_row,
+                              scale, causal, status, stream);
 }

@@ -257,19 +257,33 @@ class Trainer:
         return mask / denom / float(self.num_microbatches)
 
     def _cp_shard(self, mb: dict) -> dict:
-        """The slice of a micro-batch this context-parallel rank works on: ``seq / cp`` consecutive tokens of every
-        sequence, with their global position ids (contiguous split as in the all-to-all scheme; no zig-zag is
-        needed because attention itself runs on whole sequences)."""
+        """The slice of a micro-batch this context-parallel rank works on, with global position ids.  All-to-all
+        scheme: ``seq / cp`` consecutive tokens of every sequence (attention itself runs on whole sequences, so no
+        balancing is needed).  All-gather scheme: the zig-zag chunks ``rank`` and ``2 cp - 1 - rank`` of ``2 cp``, so
+        that every rank has the same amount of causal attention work."""
         st = self.st
         if st.cp == 1:
             return mb
         b, S = mb["tokens"].shape
-        assert S % st.cp == 0, "sequence length must divide by the context-parallel size"
-        Sl = S // st.cp
-        lo = st.cp_rank * Sl
-        out = {k: v[:, lo:lo + Sl].contiguous() for k, v in mb.items() if torch.is_tensor(v) and v.dim() == 2 and v.shape[1] == S}
-        if "position_ids" not in out:
-            out["position_ids"] = torch.arange(lo, lo + Sl, device=mb["tokens"].device).repeat(b, 1)
+        dev = mb["tokens"].device
+        if getattr(self.mcfg, "cp_comm_type", "a2a") == "allgather":
+            assert S % (2 * st.cp) == 0, "sequence length must divide by 2 x the context-parallel size"
+            c = S // (2 * st.cp)
+            if self.is_cuda:
+                assert c % 128 == 0, "all-gather context parallelism needs seq / (2 cp) to be a multiple of 128"
+            pos = torch.cat([torch.arange(j * c, (j + 1) * c, device=dev) for j in (st.cp_rank, 2 * st.cp - 1 - st.cp_rank)])
+            out = {k: v.index_select(1, pos).contiguous() for k, v in mb.items()
+                   if torch.is_tensor(v) and v.dim() == 2 and v.shape[1] == S}
+            if "position_ids" not in mb:
+                out["position_ids"] = pos.repeat(b, 1)
+        else:
+            assert S % st.cp == 0, "sequence length must divide by the context-parallel size"
+            Sl = S // st.cp
+            lo = st.cp_rank * Sl
+            out = {k: v[:, lo:lo + Sl].contiguous() for k, v in mb.items()
+                   if torch.is_tensor(v) and v.dim() == 2 and v.shape[1] == S}
+            if "position_ids" not in out:
+                out["position_ids"] = torch.arange(lo, lo + Sl, device=dev).repeat(b, 1)
         out["_mask_total"] = mb["loss_mask"].sum()
         return out
 

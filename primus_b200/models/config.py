@@ -81,6 +81,7 @@ class TransformerConfig:
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_layer_ids: Optional[List[int]] = None
     cross_entropy_chunk_tokens: int = 0  # >0: chunked linear-cross-entropy
+    cp_comm_type: str = "a2a"                      # context parallelism: "a2a" (Ulysses) or "allgather" (zig-zag chunks)
     mtp_num_layers: int | None = None               # multi-token prediction depths (DeepSeek-V3); None / 0: off
     mtp_loss_scaling_factor: float = 0.1
     final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)

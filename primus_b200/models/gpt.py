@@ -81,7 +81,13 @@ class SelfAttention(nn.Module):
             qkv = self._qk_norm(qkv, d)
         cos, sin, pos = rope
         scale = cfg.attention_softmax_scale
-        if st.cp > 1:
+        if st.cp > 1 and cfg.cp_comm_type == "allgather":
+            ctx_out = layers.allgather_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group,
+                                                         st.cp, rot_dim=int(d * cfg.rotary_percent), causal=True,
+                                                         scale=scale)
+        elif st.cp > 1:
+            if cfg.cp_comm_type != "a2a":
+                raise NotImplementedError(f"cp_comm_type {cfg.cp_comm_type!r}: only a2a (Ulysses) and allgather are built")
             ctx_out = layers.ulysses_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
                                                     rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         else:

@@ -22,7 +22,7 @@ import math
 import torch
 import torch.nn as nn
 
-from ..ops import attention, fused, gemm
+from ..ops import attention, fused, gemm, layers
 from ..parallel import state as ps
 from .config import TransformerConfig
 
@@ -103,7 +103,7 @@ class MLASelfAttention(nn.Module):
             y, xsum = fused.rmsnorm(hidden, self.input_layernorm.weight, cfg.norm_epsilon), hidden
         T = y.shape[0]
         seq = T // batch
-        cos, sin = self.rope_tables(y.device, seq)
+        cos, sin = self.rope_tables(y.device, seq * ps.get_state().cp)   # positions are global under context parallelism
         pos = rope[2]
         if cfg.q_lora_rank:
             ql = gemm.linear(y, self.linear_q_down_proj.weight)
@@ -122,6 +122,13 @@ class MLASelfAttention(nn.Module):
         q_full = torch.cat([q_pe, q[..., :dn]], dim=-1)
         k_full = torch.cat([k_pe.expand(T, nh, dr), kv[..., :dn]], dim=-1)
         v = kv[..., dn:].contiguous()
-        ctx_out = attention.flash_attention(q_full, k_full, v, batch, True, self.softmax_scale)
+        st = ps.get_state()
+        if st.cp > 1:
+            if cfg.cp_comm_type != "allgather":
+                raise NotImplementedError("multi-latent attention under context parallelism needs cp_comm_type: allgather")
+            ctx_out = layers.allgather_cp_attention(q_full.contiguous(), k_full.contiguous(), v, batch, st.cp_group, st.cp,
+                                                    True, self.softmax_scale)
+        else:
+            ctx_out = attention.flash_attention(q_full, k_full, v, batch, True, self.softmax_scale)
         out = gemm.linear(ctx_out.reshape(T, nh * dv), self.linear_proj.weight)
         return out, xsum

@@ -17,19 +17,21 @@ import torch
 from . import _lib
 
 
-def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None):
-    """fp32 reference. Returns (out [T,Hq,Dv], lse [B,Hq,S])."""
+def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None, q_off: int = 0):
+    """fp32 reference. Returns (out [T,Hq,Dv], lse [B,Hq,S]).  ``k`` / ``v`` may hold more rows per sequence than ``q``
+    (a sequence chunk attending to a gathered prefix): query row i then sits at key position ``q_off + i``."""
     T, hq, dqk = q.shape
     hkv, dv = k.shape[1], v.shape[2]
     S = T // batch
+    SK = k.shape[0] // batch
     scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
     g = hq // hkv
-    qf = q.float().view(batch, S, hq, dqk).permute(0, 2, 1, 3)
-    kf = k.float().view(batch, S, hkv, dqk).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
-    vf = v.float().view(batch, S, hkv, dv).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    qf = q.float().reshape(batch, S, hq, dqk).permute(0, 2, 1, 3)
+    kf = k.float().reshape(batch, SK, hkv, dqk).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().reshape(batch, SK, hkv, dv).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:
-        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        mask = torch.ones(S, SK, dtype=torch.bool, device=q.device).tril(diagonal=q_off)
         s = s.masked_fill(~mask, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
@@ -42,32 +44,36 @@ def _check_view(t, d):
     assert t.data_ptr() % 16 == 0
 
 
-def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float):
+def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int = 0):
     T, hq, dqk = q.shape
     hkv, dv = k.shape[1], v.shape[2]
     S = T // batch
+    SK = k.shape[0] // batch
     for t, d in ((q, dqk), (k, dqk), (v, dv)):
         _check_view(t, d)
     o = torch.empty(T, hq, dv, dtype=q.dtype, device=q.device)
     lse = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
-    _lib.call("flash_attn_fwd", q, k, v, o, lse, batch, S, hq, hkv, dqk, dv, q.stride(0), k.stride(0),
+    _lib.call("flash_attn_fwd_ex", q, k, v, o, lse, batch, S, SK, int(q_off), hq, hkv, dqk, dv, q.stride(0), k.stride(0),
               v.stride(0), o.stride(0), float(scale), int(causal), _lib.status_word(q.device))
     return o, lse
 
 
-def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, dq=None, dk=None, dv=None):
+def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, dq=None, dk=None, dv=None,
+                   q_off: int = 0):
     """Returns (dq, dk, dv); optional pre-allocated outputs may be strided views (packed dQKV)."""
     T, hq, dqk = q.shape
     hkv, dvd = k.shape[1], v.shape[2]
     S = T // batch
+    TK = k.shape[0]
+    SK = TK // batch
     dq = torch.empty(T, hq, dqk, dtype=q.dtype, device=q.device) if dq is None else dq
-    dk = torch.empty(T, hkv, dqk, dtype=q.dtype, device=q.device) if dk is None else dk
-    dv = torch.empty(T, hkv, dvd, dtype=q.dtype, device=q.device) if dv is None else dv
+    dk = torch.empty(TK, hkv, dqk, dtype=q.dtype, device=q.device) if dk is None else dk
+    dv = torch.empty(TK, hkv, dvd, dtype=q.dtype, device=q.device) if dv is None else dv
     do = do if (do.stride(2) == 1 and do.stride(1) == dvd) else do.contiguous()
     for t, d in ((q, dqk), (k, dqk), (v, dvd), (o, dvd), (do, dvd), (dq, dqk), (dk, dqk), (dv, dvd)):
         _check_view(t, d)
     delta = torch.empty(2, batch, hq, S, dtype=torch.float32, device=q.device)  # [rowsum(dO*O), lse*log2e]
-    _lib.call("flash_attn_bwd", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, hq, hkv, dqk, dvd,
+    _lib.call("flash_attn_bwd_ex", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, SK, int(q_off), hq, hkv, dqk, dvd,
               q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0),
               dv.stride(0), float(scale), int(causal), _lib.status_word(q.device))
     return dq, dk, dv
@@ -75,23 +81,25 @@ def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, 
 
 class FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, batch, causal, scale):
-        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale)
+    def forward(ctx, q, k, v, batch, causal, scale, q_off=0):
+        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale, q_off)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (batch, causal, scale)
+        ctx.args = (batch, causal, scale, q_off)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        batch, causal, scale = ctx.args
-        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale)
-        return dq, dk, dv, None, None, None
+        batch, causal, scale, q_off = ctx.args
+        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale, q_off=q_off)
+        return dq, dk, dv, None, None, None, None
 
 
-def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None):
-    """softmax(scale * Q K^T [+ causal mask]) V, token-major layout (see module docstring)."""
+def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None, q_off: int = 0):
+    """softmax(scale * Q K^T [+ causal mask]) V, token-major layout (see module docstring).  With ``q_off`` the queries
+    are a chunk of a longer sequence whose keys / values ``[0, q_off + S)`` are given (sequence lengths and ``q_off``
+    multiples of 128): the building block of all-gather context parallelism."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not q.is_cuda:
-        return attention_ref(q, k, v, batch, causal, scale)[0]
-    return FlashAttnFn.apply(q, k, v, batch, causal, scale)
+        return attention_ref(q, k, v, batch, causal, scale, q_off)[0]
+    return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off)

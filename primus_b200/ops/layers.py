@@ -452,3 +452,130 @@ def ulysses_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group, cp, 
     back = out.view(batch, cp, Sl, hq_l * d).permute(1, 0, 2, 3).reshape(cp, Tl, hq_l * d).contiguous()
     got = _SeqHeadAllToAll.apply(back, cp_group)                      # [cp (head group), Tl, hq_l * d]
     return got.permute(1, 0, 2).reshape(Tl, hq * d)
+
+
+# ----------------------------------------------------------------------------------------------
+# Context parallelism (all-gather): zig-zag sequence sharding, K / V gathered, chunk-vs-prefix attention
+def zigzag_chunk_ids(cp: int, rank: int) -> tuple[int, int]:
+    """The two sequence chunks (of ``2 * cp``) a context-parallel rank holds: ``rank`` and ``2 cp - 1 - rank``, which
+    gives every rank the same amount of causal-attention work."""
+    return rank, 2 * cp - 1 - rank
+
+
+def _zigzag_to_natural_index(cp: int, batch: int, c: int, device) -> torch.Tensor:
+    """Row permutation that turns the all-gathered tensor ``[cp (owner), batch, 2 (slot), c]`` into natural order
+    ``[batch, 2 cp (chunk), c]``."""
+    owner = torch.tensor([j if j < cp else 2 * cp - 1 - j for j in range(2 * cp)], device=device)
+    slot = torch.tensor([0 if j < cp else 1 for j in range(2 * cp)], device=device)
+    b = torch.arange(batch, device=device).view(batch, 1, 1)
+    t = torch.arange(c, device=device).view(1, 1, c)
+    src = ((owner.view(1, -1, 1) * batch + b) * 2 + slot.view(1, -1, 1)) * c + t     # [batch, 2cp, c]
+    return src.reshape(-1)
+
+
+class AllGatherCPAttentionFn(torch.autograd.Function):
+    """Causal self-attention under all-gather context parallelism (the reference's ``cp_comm_type: allgather``, which
+    it takes from Transformer-Engine; primus/configs/models/megatron/language_model.yaml:151-153).
+
+    Every rank holds two zig-zag chunks of each sequence.  K and V (after RoPE) are all-gathered once, put back into
+    natural order, and each local query chunk at key position ``q_off`` attends to the key prefix ``[0, q_off + c)``
+    with the offset form of the flash-attention kernels; the backward reduce-scatters dK / dV to their owners.  No
+    constraint on the number of heads (works for MLA head shapes and for fewer KV heads than ranks)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, batch, group, cp, rank, causal, scale):
+        Tl, hq, dqk = q.shape
+        hkv, dv = k.shape[1], v.shape[2]
+        c = Tl // batch // 2
+        S = 2 * cp * c
+        W = hkv * (dqk + dv)
+        kv = torch.cat([k.reshape(Tl, hkv * dqk), v.reshape(Tl, hkv * dv)], dim=1).contiguous()
+        gathered = torch.empty(cp * Tl, W, dtype=kv.dtype, device=kv.device)
+        torch.distributed.all_gather_into_tensor(gathered, kv, group=group)
+        idx = _zigzag_to_natural_index(cp, batch, c, kv.device)
+        full = gathered.index_select(0, idx)                                     # [batch * S, W], natural order
+        kf = full[:, : hkv * dqk].unflatten(1, (hkv, dqk))
+        vf = full[:, hkv * dqk:].unflatten(1, (hkv, dv))
+        o = torch.empty(Tl, hq, dv, dtype=q.dtype, device=q.device)
+        lses = []
+        chunks = zigzag_chunk_ids(cp, rank)
+        for b in range(batch):
+            for slot, j in enumerate(chunks):
+                r0 = (b * 2 + slot) * c
+                q_off = j * c
+                kp, vp = kf[b * S: b * S + q_off + c], vf[b * S: b * S + q_off + c]
+                if q.is_cuda:
+                    ob, lse = attention.flash_attn_fwd(q[r0:r0 + c], kp, vp, 1, causal, scale, q_off if causal else 0)
+                else:
+                    ob, lse = attention.attention_ref(q[r0:r0 + c], kp, vp, 1, causal, scale, q_off if causal else 0)
+                o[r0:r0 + c] = ob
+                lses.append(lse)
+        ctx.save_for_backward(q, full, o, idx, *lses)
+        ctx.meta = (batch, group, cp, rank, causal, scale, hkv, dqk, dv, c)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, full, o, idx, *lses = ctx.saved_tensors
+        batch, group, cp, rank, causal, scale, hkv, dqk, dv, c = ctx.meta
+        Tl, hq, _ = q.shape
+        S = 2 * cp * c
+        W = hkv * (dqk + dv)
+        kf = full[:, : hkv * dqk].unflatten(1, (hkv, dqk))
+        vf = full[:, hkv * dqk:].unflatten(1, (hkv, dv))
+        do = do.contiguous()
+        dq = torch.empty_like(q)
+        dfull = torch.zeros(batch * S, W, dtype=torch.float32, device=q.device)
+        chunks = zigzag_chunk_ids(cp, rank)
+        n = 0
+        for b in range(batch):
+            for slot, j in enumerate(chunks):
+                r0 = (b * 2 + slot) * c
+                q_off = j * c
+                L = q_off + c
+                kp, vp = kf[b * S: b * S + L], vf[b * S: b * S + L]
+                if q.is_cuda:
+                    dqb, dkb, dvb = attention.flash_attn_bwd(do[r0:r0 + c], q[r0:r0 + c], kp, vp, o[r0:r0 + c], lses[n],
+                                                             1, causal, scale, q_off=q_off if causal else 0)
+                else:
+                    with torch.enable_grad():
+                        qr, kr, vr = (t.detach().float().requires_grad_() for t in (q[r0:r0 + c], kp, vp))
+                        orf, _ = attention.attention_ref(qr, kr, vr, 1, causal, scale, q_off if causal else 0)
+                        orf.backward(do[r0:r0 + c].float())
+                    dqb, dkb, dvb = qr.grad.to(q.dtype), kr.grad, vr.grad
+                dq[r0:r0 + c] = dqb
+                dfull[b * S: b * S + L, : hkv * dqk] += dkb.reshape(L, hkv * dqk).float()
+                dfull[b * S: b * S + L, hkv * dqk:] += dvb.reshape(L, hkv * dv).float()
+                n += 1
+        # natural order -> owner order, then every owner receives the sum of the cp contributions
+        dgath = torch.empty(cp * Tl, W, dtype=torch.float32, device=q.device)
+        dgath.index_copy_(0, idx, dfull)
+        from ..parallel import tensor_parallel as tp_comm_mod
+
+        dkv = tp_comm_mod.reduce_scatter_dim0(dgath.to(q.dtype), group)           # [Tl, W]
+        dk = dkv[:, : hkv * dqk].reshape(Tl, hkv, dqk)
+        dv_ = dkv[:, hkv * dqk:].reshape(Tl, hkv, dv)
+        return dq, dk, dv_, None, None, None, None, None, None
+
+
+def allgather_cp_attention(q, k, v, batch, cp_group, cp, causal=True, scale=None):
+    """q [Tl, hq, dqk], k [Tl, hkv, dqk], v [Tl, hkv, dv] of this rank's two zig-zag chunks per sequence (RoPE already
+    applied with global positions) -> attention output [Tl, hq, dv]."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    rank = torch.distributed.get_rank(cp_group)
+    return AllGatherCPAttentionFn.apply(q, k, v, batch, cp_group, cp, rank, causal, scale)
+
+
+def allgather_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group, cp, rot_dim=None, causal=True,
+                                scale=None):
+    """Packed-QKV form of :func:`allgather_cp_attention` (RoPE with the global positions of the local tokens)."""
+    Tl = qkv.shape[0]
+    q = qkv[:, : hq * d].reshape(Tl, hq, d)
+    k = qkv[:, hq * d: (hq + hkv) * d].reshape(Tl, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(Tl, hkv, d)
+    if cos is not None:
+        rope_fn = fused.rope if qkv.is_cuda else fused.rope_ref
+        q = rope_fn(q, cos, sin, pos, rot_dim or d)
+        k = rope_fn(k, cos, sin, pos, rot_dim or d)
+    out = allgather_cp_attention(q.contiguous(), k.contiguous(), v.contiguous(), batch, cp_group, cp, causal, scale)
+    return out.reshape(Tl, hq * d)

@@ -3,14 +3,16 @@ import torch
 
 
 def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
-              pp_warmup=False):
+              pp_warmup=False, cp_comm="a2a", mla=False):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
     kw = dict(num_layers=layers, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
               vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
               expert_model_parallel_size=ep, context_parallel_size=cp, sequence_parallel=sp, make_vocab_size_divisible_by=64,
-              virtual_pipeline_model_parallel_size=vpp)
+              virtual_pipeline_model_parallel_size=vpp, cp_comm_type=cp_comm)
+    if mla:
+        kw.update(multi_latent_attention=True, kv_lora_rank=32, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16)
     if moe:
         kw.update(num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq=[0, 1] * (layers // 2),
                   moe_aux_loss_coeff=1e-2)

@@ -73,3 +73,38 @@ def test_flash_attn_deterministic():
     o1, l1 = A.flash_attn_fwd(q, k, v, 1, True, 0.088)
     o2, l2 = A.flash_attn_fwd(q, k, v, 1, True, 0.088)
     assert torch.equal(o1, o2) and torch.equal(l1, l2)
+
+
+CHUNK_CASES = [
+    # batch, seq_q, q_off, hq, hkv, dqk, dv, causal
+    (1, 128, 128, 2, 2, 128, 128, True),
+    (1, 256, 384, 4, 2, 128, 128, True),
+    (2, 128, 256, 4, 1, 128, 128, True),
+    (1, 384, 0, 2, 2, 128, 128, True),
+    (1, 256, 256, 2, 2, 192, 128, True),
+    (1, 128, 0, 2, 2, 128, 128, False),     # cross attention: 128 queries over 384 keys
+]
+
+
+@pytest.mark.parametrize("case", CHUNK_CASES)
+def test_flash_attn_chunk_against_longer_keys(case):
+    """Queries of a sequence chunk at key position q_off attending to keys [0, q_off + seq_q) (forward and backward)."""
+    batch, sq, q_off, hq, hkv, dqk, dv, causal = case
+    sk = q_off + sq if causal else 384
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(batch * sq, hq, dqk, device="cuda", generator=g).bfloat16().requires_grad_()
+    k = torch.randn(batch * sk, hkv, dqk, device="cuda", generator=g).bfloat16().requires_grad_()
+    v = torch.randn(batch * sk, hkv, dv, device="cuda", generator=g).bfloat16().requires_grad_()
+    o = A.flash_attention(q, k, v, batch, causal, None, q_off if causal else 0)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = A.attention_ref(qr, kr, vr, batch, causal, None, q_off if causal else 0)
+    o_ref.backward(do.float())
+    assert (o.float() - o_ref.float()).abs().max().item() <= 2e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        tol = 3e-2 * b.abs().max().item() + 2e-2
+        assert err <= tol, f"{name}: err {err} tol {tol}"

@@ -44,6 +44,8 @@ CASES = {
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
     "cp2": dict(world=2, kw=dict(cp=2)),
     "cp2_pp2": dict(world=4, kw=dict(cp=2, pp=2)),
+    "cp2_allgather": dict(world=2, kw=dict(cp=2, cp_comm="allgather")),
+    "cp2_allgather_mla": dict(world=2, kw=dict(cp=2, cp_comm="allgather", mla=True)),
 }
 
 

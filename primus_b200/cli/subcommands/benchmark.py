@@ -1,4 +1,4 @@
-"""``primus benchmark {gemm,gemm-dense,gemm-deepseek,attention,nccl,strided-allgather,moe} [options]``
+"""``primus benchmark {gemm,gemm-dense,gemm-deepseek,attention,nccl,strided-allgather,moe,elementwise} [options]``
 (primus/cli/subcommands/benchmark.py:8-50 in the reference; ``rccl`` is accepted as an alias of ``nccl``)."""
 from __future__ import annotations
 
@@ -7,7 +7,7 @@ import argparse
 
 def register_subcommand(subparsers):
     p = subparsers.add_parser("benchmark", help="micro-benchmarks", add_help=True)
-    p.add_argument("suite", choices=["gemm", "gemm-dense", "gemm-deepseek", "attention", "nccl", "rccl", "strided-allgather", "moe"])
+    p.add_argument("suite", choices=["gemm", "gemm-dense", "gemm-deepseek", "attention", "nccl", "rccl", "strided-allgather", "moe", "elementwise"])
     p.add_argument("rest", nargs=argparse.REMAINDER, help="options of the suite (see --help of the suite)")
     p.set_defaults(func=run)
 
@@ -30,6 +30,10 @@ def run(args, unknown):
         from ...tools.benchmark import attention_bench
 
         attention_bench.main(rest)
+    elif args.suite == "elementwise":
+        from ...tools.benchmark import elementwise_bench
+
+        elementwise_bench.main(rest)
     elif args.suite == "moe":
         from ...tools.benchmark import moe_bench
 

@@ -231,6 +231,8 @@ def main() -> int:
     ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "selective", "full"],
                     help="reference arm: activation checkpointing mode (auto = selective, then full if that fails)")
     ap.add_argument("--ref-log", default=None, help="reference arm: copy rank 0's log of the reference run here")
+    ap.add_argument("--mem-fraction", type=float, default=0.0,
+                    help="cap this process's device memory (testing the out-of-memory fallback of the warm-up)")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -270,7 +272,6 @@ def main() -> int:
                        clip_grad=1.0, use_distributed_optimizer=True, overlap_grad_reduce=world > 1,
                        log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp)
     ps.initialize_model_parallel(tp=args.tp, pp=1, cp=args.cp)
-    trainer = Trainer(mcfg, tcfg, device=f"cuda:{local_rank}", log_fn=lambda s: None)
 
     def barrier():
         if world > 1:
@@ -278,9 +279,32 @@ def main() -> int:
         torch.cuda.synchronize()
 
     import gc
-    gc.disable()
-    for _ in range(warmup):
-        loss = trainer.train_step()
+    if args.mem_fraction:
+        torch.cuda.set_per_process_memory_fraction(args.mem_fraction, local_rank)
+    # One GPU holds all optimizer state of the 8B model (the peak is ~174 of 179 GiB): if the warm-up runs out of
+    # memory, retry with full activation recomputation of the first 4, then 8, layers and say so in `config`.
+    recomputed = 0
+    for attempt in range(3):
+        trainer = None
+        try:
+            trainer = Trainer(mcfg, tcfg, device=f"cuda:{local_rank}", log_fn=lambda s: None)
+            gc.disable()
+            for _ in range(warmup):
+                loss = trainer.train_step()
+            break
+        except torch.OutOfMemoryError:
+            gc.enable()
+            if world > 1 or attempt == 2:
+                raise
+            recomputed = 4 * (attempt + 1)
+            print(f"[bench] out of memory during warm-up: retrying with recomputation of {recomputed} layers",
+                  file=sys.stderr)
+        del trainer
+        loss = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        mcfg.recompute_granularity = "full"
+        mcfg.recompute_layer_ids = list(range(recomputed))
     barrier()
     _lib.check_status()
 
@@ -338,6 +362,7 @@ def main() -> int:
             "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
                        "micro_batch": args.micro_batch, "parallelism": f"dp{world // (args.tp * args.cp)}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + (f"cp{args.cp}-{args.cp_comm}" if args.cp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",
+                       "recompute": f"full recomputation of the first {recomputed} layers (out-of-memory fallback)" if recomputed else "none",
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},
             "tokens_per_s_per_gpu": value / world,
             "model_tflops_per_gpu": value / world * flops_tok / 1e12,

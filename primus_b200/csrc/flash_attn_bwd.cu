@@ -87,14 +87,16 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       : "memory");
 }
 
-template <int DQK, int DV, int MODE>
+template <int DQK, int DV, int MODE, bool WIN>
 __global__ void __launch_bounds__(BW_THREADS, 1)
 flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                       const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                       const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
                       const float* __restrict__ lse, const float* __restrict__ delta, int seq, int seq_k, int q_off,
-                      int hq, int hkv, float scale, int causal, int* status) {
-  // seq: query rows per sequence, seq_k: key rows per sequence, q_off: key position of query row 0 (multiple of 128)
+                      int hq, int hkv, float scale, int causal, int window_arg, int* status) {
+  const int window = WIN ? window_arg : 0;   // the instantiation without a window carries no code for it
+  // seq: query rows per sequence, seq_k: key rows per sequence, q_off: key position of query row 0 (multiple of 128);
+  // window > 0 (causal self-attention only): a query sees its last `window` keys, itself included
   using C = BwCfg<DQK, DV, MODE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -123,9 +125,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   const int toky0 = batch * seq_y;
   // streamed-tile schedule: MODE_DKDV streams the query tiles at or after this key block, MODE_DQ the key tiles at or
   // before this query block (query row i sits at key position q_off + i)
-  const int c_start = (MODE == MODE_DKDV && causal) ? max(0, 2 * rb - qo) : 0;
-  const int n_per_head = (MODE == MODE_DKDV) ? max(0, num_c - c_start)
-                                             : (causal ? min(num_c, 2 * rb + 2 + qo) : num_c);
+  const int c_start = (MODE == MODE_DKDV) ? (causal ? max(0, 2 * rb - qo) : 0)
+                                          : (window > 0 ? max(0, rb * BR + q_off - window + 1) / BC : 0);
+  const int c_end = (MODE == MODE_DKDV)
+                        ? (window > 0 ? min(num_c, (rb * BR + BR - 1 + window - 1 - q_off) / BC + 1) : num_c)
+                        : (causal ? min(num_c, 2 * rb + 2 + qo) : num_c);
+  const int n_per_head = max(0, c_end - c_start);
   const int n_iter = (MODE == MODE_DKDV) ? g * n_per_head : n_per_head;
   volatile int* abort_flag = &bars->abort_flag;
   const float sl2 = scale * 1.4426950408889634f;
@@ -273,7 +278,9 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       pb::tc_fence_after();
       const uint32_t ts = tmem_sbuf + lane_addr + sb * 128;
       const int cs_rel = (MODE == MODE_DKDV) ? cs + qo : cs - qo;   // streamed tile index in the stationary block's frame
-      const bool diag = causal && (cs_rel >= 2 * rb) && (cs_rel <= 2 * rb + 1);
+      // largest (query position - key position) inside this tile pair: beyond the window -> element-wise mask
+      const int max_diff = (MODE == MODE_DKDV) ? (cs_rel * BC + BC - 1 - rb * BR) : (rb * BR + BR - 1 - cs_rel * BC);
+      const bool diag = (causal && (cs_rel >= 2 * rb) && (cs_rel <= 2 * rb + 1)) || (window > 0 && max_diff >= window);
       const float* st_lse = stat_smem + st * 128;
       const float* st_delta = st_lse + 64;
       uint32_t s[BC], dp[BC];
@@ -303,8 +310,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
               float p = pb::fast_exp2(fmaf(__uint_as_float(s[c + u]), sl2, -l2[u]));
               if (DIAG) {
                 const int col_g = cs_rel * BC + c + u;
-                const bool valid = (MODE == MODE_DKDV) ? (col_g >= row_g) : (col_g <= row_g);
-                if (!valid) p = 0.f;
+                const int diff = (MODE == MODE_DKDV) ? (col_g - row_g) : (row_g - col_g);   // query - key position
+                if (diff < 0 || (window > 0 && diff >= window)) p = 0.f;
               }
               pv[u] = p;
               dv[u] = p * (__uint_as_float(dp[c + u]) - dl[u]) * scale;
@@ -411,7 +418,7 @@ struct BwdArgs {
   const float* lse;
   float* delta;
   void *dq, *dk, *dv;
-  int batch, seq, seq_k, q_off, hq, hkv;
+  int batch, seq, seq_k, q_off, window, hq, hkv;
   long q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row;
   float scale;
   int causal;
@@ -446,31 +453,31 @@ int launch_bwd(const BwdArgs& a) {
 #undef MK
   {
     using C = BwCfg<DQK, DV, MODE_DKDV>;
-    auto kern = flash_attn_bwd_kernel<DQK, DV, MODE_DKDV>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    auto kern = a.window > 0 ? flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[a.window > 0]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      attr_set = true;
+      attr_set[a.window > 0] = true;
     }
     dim3 grid(a.hkv * a.batch, a.seq_k / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m,
                                                        a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
-                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.status);
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.status);
   }
   {
     using C = BwCfg<DQK, DV, MODE_DQ>;
-    auto kern = flash_attn_bwd_kernel<DQK, DV, MODE_DQ>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    auto kern = a.window > 0 ? flash_attn_bwd_kernel<DQK, DV, MODE_DQ, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DQ, false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[a.window > 0]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      attr_set = true;
+      attr_set[a.window > 0] = true;
     }
     dim3 grid(a.hq * a.batch, a.seq / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m,
                                                        a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
-                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.status);
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.status);
   }
   return (int)cudaGetLastError();
 }
@@ -479,20 +486,31 @@ int launch_bwd(const BwdArgs& a) {
 
 // Layouts as in pb_flash_attn_fwd_ex (q / o / d_o / dq: batch*seq rows; k / v / dk / dv: batch*seq_k rows).
 // delta: fp32 scratch [2, batch, hq, seq] (written here: row sums of dO*O, then the log-sum-exp in log2 units).
+extern "C" int pb_flash_attn_bwd_win(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                     const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
+                                     int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row,
+                                     long v_row, long o_row, long do_row, long dq_row, long dk_row, long dv_row,
+                                     float scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv) return -2;
+  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
+  if (window < 0 || (window > 0 && (!causal || q_off != 0))) return -2;
+  if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
+  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, window, hq, hkv, q_row, k_row, v_row,
+            o_row, do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
+  if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
+  if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
+  if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
+  return -3;
+}
+
 extern "C" int pb_flash_attn_bwd_ex(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                                     const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
                                     int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row,
                                     long v_row, long o_row, long do_row, long dq_row, long dk_row, long dv_row,
                                     float scale, int causal, int* status, cudaStream_t stream) {
-  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv) return -2;
-  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
-  if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
-  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row,
-            do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
-  if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
-  if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
-  if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
-  return -3;
+  return pb_flash_attn_bwd_win(d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, hq, hkv, d_qk, d_v,
+                               q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row, scale, causal, 0, status,
+                               stream);
 }
 
 extern "C" int pb_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,

@@ -64,14 +64,19 @@ __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile
     break;                                         \
   }
 
-template <int DQK, int DV>
+template <int DQK, int DV, bool WIN>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                       float* __restrict__ lse, int seq, int seq_k, int q_off_blocks, int hq, int hkv,
-                      float scale_log2, int causal, int* status) {
+                      float scale_log2, int causal, int window_arg, const float* __restrict__ sinks_arg, int* status) {
+  // WIN = false: the plain instantiation carries no code for windows or sinks
+  const int window = WIN ? window_arg : 0;
+  const float* sinks = WIN ? sinks_arg : nullptr;
   // seq: query rows per sequence; seq_k: key rows per sequence; query row i sits at key position
-  // q_off_blocks * 128 + i (causal masking is relative to that position)
+  // q_off_blocks * 128 + i (causal masking is relative to that position).  window > 0 (causal only): a query attends
+  // to its last `window` keys, itself included.  sinks: optional per-query-head logit (natural-log units) that only
+  // adds exp(sink) to the softmax denominator.
   using C = FaCfg<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,8 +99,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int qt[2] = {2 * pair, 2 * pair + 1};  // 128-row query tile indices
   const bool active1 = qt[1] < num_q128;
   const int n_kv = seq_k / BKV;
-  const int nb[2] = {causal ? min(n_kv, qt[0] + q_off_blocks + 1) : n_kv,
-                     active1 ? (causal ? min(n_kv, qt[1] + q_off_blocks + 1) : n_kv) : 0};
+  // first key block any row of this CTA can see (both tiles stream from there; the later tile masks what lies
+  // before its own window)
+  const int j_lo = (window > 0) ? max(0, (qt[0] + q_off_blocks) * BQ - window + 1) / BKV : 0;
+  const int nb[2] = {(causal ? min(n_kv, qt[0] + q_off_blocks + 1) : n_kv) - j_lo,
+                     active1 ? (causal ? min(n_kv, qt[1] + q_off_blocks + 1) : n_kv) - j_lo : 0};
   const int n_max = nb[0] > nb[1] ? nb[0] : nb[1];
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -145,13 +153,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int a = 0; a < DQK / 64; ++a)
           pb::tma_load_3d(k_smem + ks * C::K_BYTES + a * ATOM_BYTES, &tmK, &bars->k_full[ks], a * 64,
-                          kv_head, tokk0 + j * BKV);
+                          kv_head, tokk0 + (j + j_lo) * BKV);
         FA_WAIT(&bars->v_empty[vs], ((j / C::VS) & 1) ^ 1, PB_ERR_TIMEOUT_TMA);
         pb::mbar_expect_tx(&bars->v_full[vs], C::V_BYTES);
 #pragma unroll
         for (int a = 0; a < DV / 64; ++a)
           pb::tma_load_3d(v_smem + vs * C::V_BYTES + a * ATOM_BYTES, &tmV, &bars->v_full[vs], a * 64,
-                          kv_head, tokk0 + j * BKV);
+                          kv_head, tokk0 + (j + j_lo) * BKV);
       }
     }
   } else if (warp == 1) {
@@ -222,11 +230,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int n_blocks = nb[t];
     float m_ref = -1e30f;
     float l = 0.f;
+    float l_scale = 1.f;
     bool ok = true;
     for (int j = 0; j < n_blocks && ok; ++j) {
       FA_WAIT(&bars->s_full[t], j & 1, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
-      const bool diag = causal && (j == qt[t] + q_off_blocks);
+      const bool diag = causal && (j + j_lo == qt[t] + q_off_blocks);
+      // keys of this block older than the window of this row: columns [0, lim)
+      const int lim = (window > 0) ? (qt[t] + q_off_blocks) * BQ + row - window + 1 - (j + j_lo) * BKV : 0;
+      const bool edge = __any_sync(0xffffffffu, lim > 0);
       // the whole S row (128 fp32) is read once and stays in registers for both passes
       uint32_t sr[128];
 #pragma unroll
@@ -236,6 +248,11 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 128; ++i)
           if (i > row) sr[i] = 0xff800000u;  // -inf: masked out of max and exp
+      }
+      if (edge) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i < lim) sr[i] = 0xff800000u;
       }
       // pass 1: row maximum (four independent chains)
       float mx4[4] = {-1e30f, -1e30f, -1e30f, -1e30f};
@@ -292,7 +309,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (!ok || n_blocks == 0) break;
       FA_WAIT(&bars->pv_done[t], (n_blocks - 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
       pb::tc_fence_after();
-      const float inv = 1.f / l;
+      if (sinks != nullptr) {   // the sink joins the denominator only
+        const float s2 = sinks[head] * 1.4426950408889634f;
+        const float m_fin = fmaxf(m_ref, s2);
+        const float a = exp2f(m_ref - m_fin);
+        l = l * a + exp2f(s2 - m_fin);
+        l_scale = a;
+        m_ref = m_fin;
+      }
+      const float inv = l_scale / l;
       uint8_t* stage = q_smem + t * C::Q_BYTES;
       uint8_t* orow = stage + row * 128;
 #pragma unroll 1
@@ -339,7 +364,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 template <int DQK, int DV>
 int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq, int seq_k,
                int q_off, int hq, int hkv, long q_row, long k_row, long v_row, long o_row, float scale, int causal,
-               int* status, cudaStream_t stream) {
+               int window, const float* sinks, int* status, cudaStream_t stream) {
   using C = FaCfg<DQK, DV>;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
@@ -351,16 +376,17 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
   if ((rc = pbh::make_tmap_3d(&tk, k, bf, 2, TK, hkv, DQK, DQK, k_row, BKV, 1, 64, sw))) return rc;
   if ((rc = pbh::make_tmap_3d(&tv, v, bf, 2, TK, hkv, DV, DV, v_row, BKV, 1, 64, sw))) return rc;
   if ((rc = pbh::make_tmap_3d(&to, o, bf, 2, T, hq, DV, DV, o_row, BQ, 1, 64, sw))) return rc;
-  auto kern = flash_attn_fwd_kernel<DQK, DV>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  const bool win = window > 0 || sinks != nullptr;
+  auto kern = win ? flash_attn_fwd_kernel<DQK, DV, true> : flash_attn_fwd_kernel<DQK, DV, false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[win]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    attr_set[win] = true;
   }
   dim3 grid(hq * batch, (seq / BQ + 1) / 2, 1);
   kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, seq_k, q_off / BQ, hq, hkv,
-                                                   scale * 1.4426950408889634f, causal, status);
+                                                   scale * 1.4426950408889634f, causal, window, sinks, status);
   return (int)cudaGetLastError();
 }
 
@@ -369,25 +395,36 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
 // q: [batch*seq, hq, d_qk] (row pitch q_row elements, heads contiguous), k: [batch*seq_k, hkv, d_qk],
 // v: [batch*seq_k, hkv, d_v], o: [batch*seq, hq, d_v]; lse: [batch, hq, seq] fp32 (natural log).  seq, seq_k and q_off
 // are multiples of 128.  Query row i of a sequence sits at key position q_off + i: with `causal` it attends to keys
-// [0, q_off + i] and q_off + seq must equal seq_k (the layout of a sequence chunk attending to the gathered prefix).
-extern "C" int pb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
-                                    int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
-                                    long k_row, long v_row, long o_row, float scale, int causal, int* status,
-                                    cudaStream_t stream) {
+// [0, q_off + i] (the last `window` of them when window > 0) and q_off + seq must equal seq_k (the layout of a
+// sequence chunk attending to the gathered prefix).  sinks: null or one fp32 logit per query head.
+extern "C" int pb_flash_attn_fwd_win(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+                                     int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
+                                     long k_row, long v_row, long o_row, float scale, int causal, int window,
+                                     const float* sinks, int* status, cudaStream_t stream) {
   if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) ||
       (o_row % 8))
     return -2;
   if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
+  if (window < 0 || (window > 0 && (!causal || q_off != 0))) return -2;
   if (d_qk == 128 && d_v == 128)
     return launch_fwd<128, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                                causal, status, stream);
+                                causal, window, sinks, status, stream);
   if (d_qk == 192 && d_v == 128)
     return launch_fwd<192, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                                causal, status, stream);
+                                causal, window, sinks, status, stream);
   if (d_qk == 64 && d_v == 64)
     return launch_fwd<64, 64>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                              causal, status, stream);
+                              causal, window, sinks, status, stream);
   return -3;
+}
+
+// No sliding window, no sinks.
+extern "C" int pb_flash_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+                                    int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
+                                    long k_row, long v_row, long o_row, float scale, int causal, int* status,
+                                    cudaStream_t stream) {
+  return pb_flash_attn_fwd_win(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, d_qk, d_v, q_row, k_row, v_row, o_row,
+                               scale, causal, 0, nullptr, status, stream);
 }
 
 // Self-attention form: seq_k = seq, q_off = 0.

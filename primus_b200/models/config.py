@@ -81,12 +81,28 @@ class TransformerConfig:
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_layer_ids: Optional[List[int]] = None
     cross_entropy_chunk_tokens: int = 0  # >0: chunked linear-cross-entropy
+    window_size: object = None                      # sliding-window attention: W, or Megatron's (left, right) = (W - 1, 0)
+    window_attn_skip_freq: object = None            # int N: every N-th layer attends fully; list: 1 = windowed, 0 = full
+    softmax_type: str = "vanilla"                   # "learnable": per-head sink logit in the softmax denominator
     cp_comm_type: str = "a2a"                      # context parallelism: "a2a" (Ulysses) or "allgather" (zig-zag chunks)
     mtp_num_layers: int | None = None               # multi-token prediction depths (DeepSeek-V3); None / 0: off
     mtp_loss_scaling_factor: float = 0.1
     final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)
     router_logit_softcapping: float | None = None   # same on the MoE router logits
     attn_logit_softcapping: float | None = None     # accepted for config parity; not supported by the attention kernels
+
+    def layer_window(self, layer_idx: int) -> int:
+        """Sliding-window width of a layer (0 = full attention)."""
+        if not self.window_size:
+            return 0
+        w = self.window_size
+        width = int(w[0]) + 1 if isinstance(w, (tuple, list)) else int(w)
+        f = self.window_attn_skip_freq
+        if f is None:
+            return width
+        if isinstance(f, int):
+            return 0 if (layer_idx + 1) % f == 0 else width
+        return width if f[layer_idx % len(f)] else 0
 
     def __post_init__(self):
         if self.attn_logit_softcapping:

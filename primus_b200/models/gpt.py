@@ -68,6 +68,12 @@ class SelfAttention(nn.Module):
         self.linear_proj.weight.tensor_model_parallel = tp > 1
         self.linear_proj.weight.partition_dim = 1
         self.linear_qkv.layer_norm_weight.sequence_parallel = cfg.sequence_parallel
+        self.window = cfg.layer_window(layer_idx)
+        self.has_sinks = cfg.softmax_type == "learnable"
+        if self.has_sinks:   # one sink logit per (local) query head, mcore name core_attention.softmax_offset
+            self.core_attention = ParamHolder(softmax_offset=nn.Parameter(torch.zeros(self.hq, dtype=dt, device=device)))
+            self.core_attention.softmax_offset.tensor_model_parallel = tp > 1
+            self.core_attention.softmax_offset.partition_dim = 0
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
@@ -81,6 +87,8 @@ class SelfAttention(nn.Module):
             qkv = self._qk_norm(qkv, d)
         cos, sin, pos = rope
         scale = cfg.attention_softmax_scale
+        if st.cp > 1 and (self.window or self.has_sinks):
+            raise NotImplementedError("sliding-window / sink attention is not available under context parallelism")
         if st.cp > 1 and cfg.cp_comm_type == "allgather":
             ctx_out = layers.allgather_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group,
                                                          st.cp, rot_dim=int(d * cfg.rotary_percent), causal=True,
@@ -91,8 +99,10 @@ class SelfAttention(nn.Module):
             ctx_out = layers.ulysses_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
                                                     rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         else:
+            sinks = self.core_attention.softmax_offset.float() if self.has_sinks else None
             ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
-                                            rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
+                                            rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
+                                            window=self.window, sinks=sinks)
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 

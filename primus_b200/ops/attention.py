@@ -17,9 +17,12 @@ import torch
 from . import _lib
 
 
-def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None, q_off: int = 0):
+def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None, q_off: int = 0,
+                  window: int = 0, sinks=None):
     """fp32 reference. Returns (out [T,Hq,Dv], lse [B,Hq,S]).  ``k`` / ``v`` may hold more rows per sequence than ``q``
-    (a sequence chunk attending to a gathered prefix): query row i then sits at key position ``q_off + i``."""
+    (a sequence chunk attending to a gathered prefix): query row i then sits at key position ``q_off + i``.
+    ``window`` > 0: a query sees its last ``window`` keys (itself included).  ``sinks`` [Hq]: a learned logit per head
+    that joins the softmax denominator only (GPT-OSS style attention sink)."""
     T, hq, dqk = q.shape
     hkv, dv = k.shape[1], v.shape[2]
     S = T // batch
@@ -32,8 +35,12 @@ def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None 
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if causal:
         mask = torch.ones(S, SK, dtype=torch.bool, device=q.device).tril(diagonal=q_off)
+        if window and window > 0:
+            mask &= torch.ones(S, SK, dtype=torch.bool, device=q.device).triu(diagonal=q_off - window + 1)
         s = s.masked_fill(~mask, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
+    if sinks is not None:
+        lse = torch.logaddexp(lse, sinks.float().view(1, hq, 1).expand_as(lse))
     p = torch.exp(s - lse[..., None])
     o = torch.matmul(p, vf).permute(0, 2, 1, 3).reshape(T, hq, dv)
     return o.to(q.dtype), lse
@@ -44,7 +51,7 @@ def _check_view(t, d):
     assert t.data_ptr() % 16 == 0
 
 
-def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int = 0):
+def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int = 0, window: int = 0, sinks=None):
     T, hq, dqk = q.shape
     hkv, dv = k.shape[1], v.shape[2]
     S = T // batch
@@ -53,13 +60,15 @@ def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int =
         _check_view(t, d)
     o = torch.empty(T, hq, dv, dtype=q.dtype, device=q.device)
     lse = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
-    _lib.call("flash_attn_fwd_ex", q, k, v, o, lse, batch, S, SK, int(q_off), hq, hkv, dqk, dv, q.stride(0), k.stride(0),
-              v.stride(0), o.stride(0), float(scale), int(causal), _lib.status_word(q.device))
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == hq and sinks.is_contiguous()
+    _lib.call("flash_attn_fwd_win", q, k, v, o, lse, batch, S, SK, int(q_off), hq, hkv, dqk, dv, q.stride(0), k.stride(0),
+              v.stride(0), o.stride(0), float(scale), int(causal), int(window or 0), sinks, _lib.status_word(q.device))
     return o, lse
 
 
 def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, dq=None, dk=None, dv=None,
-                   q_off: int = 0):
+                   q_off: int = 0, window: int = 0):
     """Returns (dq, dk, dv); optional pre-allocated outputs may be strided views (packed dQKV)."""
     T, hq, dqk = q.shape
     hkv, dvd = k.shape[1], v.shape[2]
@@ -73,33 +82,47 @@ def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, 
     for t, d in ((q, dqk), (k, dqk), (v, dvd), (o, dvd), (do, dvd), (dq, dqk), (dk, dqk), (dv, dvd)):
         _check_view(t, d)
     delta = torch.empty(2, batch, hq, S, dtype=torch.float32, device=q.device)  # [rowsum(dO*O), lse*log2e]
-    _lib.call("flash_attn_bwd_ex", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, SK, int(q_off), hq, hkv, dqk, dvd,
+    _lib.call("flash_attn_bwd_win", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, SK, int(q_off), hq, hkv, dqk, dvd,
               q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0),
-              dv.stride(0), float(scale), int(causal), _lib.status_word(q.device))
+              dv.stride(0), float(scale), int(causal), int(window or 0), _lib.status_word(q.device))
     return dq, dk, dv
+
+
+def sink_grad(do, o, lse, sinks, batch: int):
+    """Gradient of the per-head sink logits: d sink_h = - sum_rows exp(sink_h - lse_row) * rowsum(dO * O) (the sink has
+    no value vector, so it only enters through the softmax normaliser)."""
+    T, hq, _ = o.shape
+    S = T // batch
+    delta = (do.float() * o.float()).sum(-1).view(batch, S, hq).permute(0, 2, 1)      # [B, Hq, S]
+    p_sink = torch.exp(sinks.float().view(1, hq, 1) - lse)
+    return -(p_sink * delta).sum(dim=(0, 2)).to(sinks.dtype)
 
 
 class FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, batch, causal, scale, q_off=0):
-        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale, q_off)
-        ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (batch, causal, scale, q_off)
+    def forward(ctx, q, k, v, batch, causal, scale, q_off=0, window=0, sinks=None):
+        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale, q_off, window, sinks)
+        ctx.save_for_backward(q, k, v, o, lse, sinks if sinks is not None else torch.empty(0))
+        ctx.args = (batch, causal, scale, q_off, window, sinks is not None)
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse = ctx.saved_tensors
-        batch, causal, scale, q_off = ctx.args
-        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale, q_off=q_off)
-        return dq, dk, dv, None, None, None, None
+        q, k, v, o, lse, sinks = ctx.saved_tensors
+        batch, causal, scale, q_off, window, has_sinks = ctx.args
+        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale, q_off=q_off, window=window)
+        ds = sink_grad(do, o, lse, sinks, batch) if has_sinks else None
+        return dq, dk, dv, None, None, None, None, None, ds
 
 
-def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None, q_off: int = 0):
+def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None, q_off: int = 0,
+                    window: int = 0, sinks=None):
     """softmax(scale * Q K^T [+ causal mask]) V, token-major layout (see module docstring).  With ``q_off`` the queries
     are a chunk of a longer sequence whose keys / values ``[0, q_off + S)`` are given (sequence lengths and ``q_off``
-    multiples of 128): the building block of all-gather context parallelism."""
+    multiples of 128): the building block of all-gather context parallelism.  ``window`` / ``sinks``: sliding-window
+    attention and learned per-head sink logits (fp32 [Hq]) as the reference passes them to ``flash_attn_func``
+    (primus/backends/megatron/core/extensions/primus_turbo.py:876-883,924-942)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not q.is_cuda:
-        return attention_ref(q, k, v, batch, causal, scale, q_off)[0]
-    return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off)
+        return attention_ref(q, k, v, batch, causal, scale, q_off, window, sinks)[0]
+    return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off, window, sinks)

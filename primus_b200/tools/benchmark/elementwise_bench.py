@@ -39,6 +39,7 @@ def main(argv=None):
     ap.add_argument("--vocab", type=int, default=32768)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default=None, help="run only the rows whose name contains this text (short ncu captures)")
     ap.add_argument("--output", default=None)
     a = ap.parse_args(argv)
     from ...ops import _lib, fp8, fused
@@ -49,6 +50,8 @@ def main(argv=None):
     rows = []
 
     def add(name, fn, nbytes, nsets):
+        if a.only and a.only not in name:
+            return
         t = time_cuda(fn, a.iters)["ms_median"]
         gbs = nbytes / t / 1e6
         rows.append({"kernel": name, "ms": t, "algorithmic_MB": nbytes / 1e6, "GB/s": gbs,

@@ -108,3 +108,39 @@ def test_flash_attn_chunk_against_longer_keys(case):
         err = (a.float() - b).abs().max().item()
         tol = 3e-2 * b.abs().max().item() + 2e-2
         assert err <= tol, f"{name}: err {err} tol {tol}"
+
+
+WINDOW_CASES = [
+    # batch, seq, hq, hkv, d, window, sinks
+    (1, 512, 4, 2, 128, 128, False),
+    (1, 640, 2, 2, 128, 200, True),
+    (2, 384, 4, 1, 64, 128, True),
+    (1, 1024, 2, 1, 128, 300, False),
+    (1, 256, 2, 2, 128, 1000, True),     # window longer than the sequence
+    (1, 384, 4, 4, 128, 0, True),        # sinks only
+]
+
+
+@pytest.mark.parametrize("case", WINDOW_CASES)
+def test_flash_attn_sliding_window_and_sinks(case):
+    batch, seq, hq, hkv, d, window, with_sinks = case
+    q, k, v = _inputs(batch, seq, hq, hkv, d, d, seed=5)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    sinks = (torch.randn(hq, device="cuda") * 2).requires_grad_() if with_sinks else None
+    o = A.flash_attention(q, k, v, batch, True, None, 0, window, sinks)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sr = sinks.detach().clone().requires_grad_() if with_sinks else None
+    o_ref, _ = A.attention_ref(qr, kr, vr, batch, True, None, 0, window, sr)
+    o_ref.backward(do.float())
+    assert (o.float() - o_ref.float()).abs().max().item() <= 2e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        tol = 3e-2 * b.abs().max().item() + 2e-2
+        assert err <= tol, f"{name}: err {err} tol {tol}"
+    if with_sinks:
+        err = (sinks.grad - sr.grad).abs().max().item()
+        assert err <= 3e-2 * sr.grad.abs().max().item() + 2e-2, (sinks.grad, sr.grad)

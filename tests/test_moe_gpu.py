@@ -125,3 +125,35 @@ def test_fused_router_matches_reference(score, pre, groups, bias, scale, E, k):
     (p_ref.gather(1, order_ref) * wp).sum().add((f_ref * wf).sum()).backward()
     err = (logits.grad.float() - ref_in.grad.float()).abs().max().item()
     assert err <= 2e-2 * ref_in.grad.float().abs().max().item() + 1e-5, err
+
+
+@pytest.mark.parametrize("recipe", [None, "e4m3"])
+def test_moe_model_with_hidden_size_not_multiple_of_128(recipe):
+    """GPT-OSS-like widths (hidden 2880, 64-channel heads): every GEMM shape takes a supported path (bf16 kernels where
+    the MXFP8 ones need multiples of 128) and the loss goes down on a repeated batch."""
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import gemm
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    try:
+        mc = TransformerConfig(num_layers=2, hidden_size=2880, ffn_hidden_size=2880, num_attention_heads=64,
+                               num_query_groups=8, kv_channels=64, vocab_size=2048, params_dtype="bf16", seq_length=256,
+                               num_experts=32, moe_router_topk=4, moe_ffn_hidden_size=2880, moe_layer_freq=[1, 1],
+                               moe_shared_expert_intermediate_size=2880, moe_aux_loss_coeff=1e-3, fp8=recipe,
+                               fp8_recipe="mxfp8")
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=256, train_iters=8, lr=1e-3,
+                         lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1)
+        torch.manual_seed(0)
+        tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
+        fixed = tr.stager.next_step()
+        tr.stager.next_step = lambda: fixed
+        tr.stager.prefetch = lambda: None
+        losses = tr.train()
+        torch.cuda.synchronize()
+        _lib.check_status()
+    finally:
+        gemm.set_fp8_recipe(None)
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.5, losses

@@ -137,3 +137,38 @@ def test_multi_token_prediction_adds_a_trained_auxiliary_loss():
     assert m.mtp.layers[1].eh_proj.weight.grad.abs().sum() > 0
     assert m.embedding.word_embeddings.weight.grad.abs().sum() > 0
     assert schedules.model_flops_per_token(cfg, 32) > schedules.model_flops_per_token(TransformerConfig(**kw), 32)
+
+
+def test_sliding_window_and_sink_attention_in_the_model():
+    """window_size / window_attn_skip_freq pick the window per layer, softmax_type learnable adds a trained per-head
+    sink; a window at least as long as the sequence without sinks reproduces full attention."""
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    kw = dict(num_layers=4, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=128,
+              params_dtype="fp32", seq_length=32)
+    cfg = TransformerConfig(**kw, window_size=(7, 0), window_attn_skip_freq=2, softmax_type="learnable")
+    assert [cfg.layer_window(i) for i in range(4)] == [8, 0, 8, 0]
+    torch.manual_seed(0)
+    m = GPTModel(cfg, "cpu")
+    tokens = torch.randint(0, 128, (2, 32))
+    labels = torch.roll(tokens, -1, 1)
+    w = torch.full((2, 32), 1.0 / 64)
+    loss = m(tokens, labels, loss_weights=w, unit_upstream=True)
+    loss.backward()
+    g = m.decoder.layers["0"].self_attention.core_attention.softmax_offset.grad
+    assert g is not None and g.abs().sum() > 0
+    torch.manual_seed(0)
+    full = GPTModel(TransformerConfig(**kw), "cpu")
+    torch.manual_seed(0)
+    wide = GPTModel(TransformerConfig(**kw, window_size=32), "cpu")
+    a = full(tokens, labels, loss_weights=w, unit_upstream=True)
+    b = wide(tokens, labels, loss_weights=w, unit_upstream=True)
+    assert torch.allclose(a, b, atol=1e-6)
+    torch.manual_seed(0)
+    narrow = GPTModel(TransformerConfig(**kw, window_size=4), "cpu")
+    c = narrow(tokens, labels, loss_weights=w, unit_upstream=True)
+    assert abs(c.item() - a.item()) > 1e-6

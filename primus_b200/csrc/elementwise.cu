@@ -494,8 +494,29 @@ ce_fused_kernel(__nv_bfloat16* __restrict__ logits, const long* __restrict__ lab
 // ------------------------------------------------------------------ optimizer / flat-buffer helpers
 // AdamW over a flat shard. grads are multiplied by *grad_scale (device scalar: clip coefficient x
 // 1/loss-scale). When *skip != 0 (non-finite gradients found) nothing is updated.
-template <typename GradT>
-__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+__device__ __forceinline__ void load4(const float* p, float* o) {
+  *reinterpret_cast<float4*>(o) = *reinterpret_cast<const float4*>(p);
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* o) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(p);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float* o) {
+  *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(o);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* o) {
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(p);
+  h[0] = __floats2bfloat162_rn(o[0], o[1]);
+  h[1] = __floats2bfloat162_rn(o[2], o[3]);
+}
+__device__ __forceinline__ void store1(float* p, float o) { *p = o; }
+__device__ __forceinline__ void store1(__nv_bfloat16* p, float o) { *p = __float2bfloat16(o); }
+
+// GradT: fp32 or bf16 gradients; StateT: fp32 or bf16 moments (precision-aware optimizer: the moments can be kept in
+// bf16 to halve their memory; the arithmetic is fp32 either way and the master weights stay fp32).
+template <typename GradT, typename StateT>
+__global__ void adamw_kernel(float* __restrict__ master, StateT* __restrict__ m, StateT* __restrict__ v,
                              const GradT* __restrict__ grad, __nv_bfloat16* __restrict__ param_out,
                              long n, float lr, float beta1, float beta2, float eps, float wd,
                              float bc1, float bc2, const float* __restrict__ grad_scale,
@@ -507,22 +528,16 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
     float p[4], mm[4], vv[4], g[4];
     const bool full = i + 4 <= n;
     if (full) {
-      *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(master + i);
-      *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(m + i);
-      *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(v + i);
-      if constexpr (sizeof(GradT) == 4) {
-        *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(grad + i);
-      } else {
-        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(grad + i);
-        float2 a = __bfloat1622float2(gp[0]), b = __bfloat1622float2(gp[1]);
-        g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
-      }
+      load4(master + i, p);
+      load4(m + i, mm);
+      load4(v + i, vv);
+      load4(grad + i, g);
     } else {
       for (int j = 0; j < 4; ++j) {
         const bool in = i + j < n;
         p[j] = in ? master[i + j] : 0.f;
-        mm[j] = in ? m[i + j] : 0.f;
-        vv[j] = in ? v[i + j] : 0.f;
+        mm[j] = in ? (float)m[i + j] : 0.f;
+        vv[j] = in ? (float)v[i + j] : 0.f;
         g[j] = in ? (float)grad[i + j] : 0.f;
       }
     }
@@ -536,19 +551,15 @@ __global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, 
       p[j] = p[j] * (1.f - lr * wd) - lr * mh / (sqrtf(vh) + eps);
     }
     if (full) {
-      *reinterpret_cast<float4*>(master + i) = *reinterpret_cast<float4*>(p);
-      *reinterpret_cast<float4*>(m + i) = *reinterpret_cast<float4*>(mm);
-      *reinterpret_cast<float4*>(v + i) = *reinterpret_cast<float4*>(vv);
-      if (param_out) {
-        __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(param_out + i);
-        po[0] = __floats2bfloat162_rn(p[0], p[1]);
-        po[1] = __floats2bfloat162_rn(p[2], p[3]);
-      }
+      store4(master + i, p);
+      store4(m + i, mm);
+      store4(v + i, vv);
+      if (param_out) store4(param_out + i, p);
     } else {
       for (int j = 0; j < 4 && i + j < n; ++j) {
         master[i + j] = p[j];
-        m[i + j] = mm[j];
-        v[i + j] = vv[j];
+        store1(m + i + j, mm[j]);
+        store1(v + i + j, vv[j]);
         if (param_out) param_out[i + j] = __float2bfloat16(p[j]);
       }
     }
@@ -730,19 +741,29 @@ int pb_ce_fused(void* logits, const long* labels, const float* gscale, float* lo
   PB_CHECK_LAUNCH();
 }
 
+// state_is_bf16: the moments m, v are bf16 tensors (else fp32).
+int pb_adamw_ex(float* master, void* m, void* v, const void* grad, int grad_is_bf16, int state_is_bf16,
+                void* param_out, long n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                const float* grad_scale, const int* skip, cudaStream_t s) {
+  if (n == 0) return 0;
+  const int g = grid_for((n + 3) / 4, 256, 148 * 8);
+  __nv_bfloat16* po = (__nv_bfloat16*)param_out;
+#define PB_ADAMW(GT, ST)                                                                                          \
+  adamw_kernel<GT, ST><<<g, 256, 0, s>>>(master, (ST*)m, (ST*)v, (const GT*)grad, po, n, lr, beta1, beta2, eps, wd, \
+                                         bc1, bc2, grad_scale, skip)
+  if (grad_is_bf16 && state_is_bf16) PB_ADAMW(__nv_bfloat16, __nv_bfloat16);
+  else if (grad_is_bf16) PB_ADAMW(__nv_bfloat16, float);
+  else if (state_is_bf16) PB_ADAMW(float, __nv_bfloat16);
+  else PB_ADAMW(float, float);
+#undef PB_ADAMW
+  PB_CHECK_LAUNCH();
+}
+
 int pb_adamw(float* master, float* m, float* v, const void* grad, int grad_is_bf16, void* param_out,
              long n, float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
              const float* grad_scale, const int* skip, cudaStream_t s) {
-  if (n == 0) return 0;
-  const int g = grid_for((n + 3) / 4, 256, 148 * 8);
-  if (grad_is_bf16)
-    adamw_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)grad,
-                                                  (__nv_bfloat16*)param_out, n, lr, beta1, beta2, eps,
-                                                  wd, bc1, bc2, grad_scale, skip);
-  else
-    adamw_kernel<float><<<g, 256, 0, s>>>(master, m, v, (const float*)grad, (__nv_bfloat16*)param_out,
-                                          n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, skip);
-  PB_CHECK_LAUNCH();
+  return pb_adamw_ex(master, m, v, grad, grad_is_bf16, 0, param_out, n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale,
+                     skip, s);
 }
 
 int pb_sumsq_num_partials() { return 1184; }

@@ -78,6 +78,11 @@ class TrainConfig:
     dump_pp_data: bool = False         # per-node pipeline timeline (one JSON per pipeline rank and iteration; it
     pp_dump_dir: Optional[str] = None  # synchronises after every node, so the timed iterations are slower)
     pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
+    use_precision_aware_optimizer: bool = False   # Adam moments in exp_avg_dtype / exp_avg_sq_dtype ("fp32" | "bf16")
+    exp_avg_dtype: str = "fp32"
+    exp_avg_sq_dtype: str = "fp32"
+    main_params_dtype: str = "fp32"
+    main_grads_dtype: str = "fp32"
     inprocess_restart: bool = False    # reload the newest checkpoint and continue after a failure all ranks agree on
     inprocess_max_restarts: int = 3
     check_for_spiky_loss: bool = False
@@ -204,6 +209,14 @@ class Trainer:
         from ..parallel import matrix_optimizers
 
         extra = {}
+        if train_cfg.optimizer.lower() in ("adam", "adamw") and train_cfg.use_precision_aware_optimizer:
+            dts = {train_cfg.exp_avg_dtype, train_cfg.exp_avg_sq_dtype}
+            assert len(dts) == 1 and dts <= {"fp32", "bf16"}, "exp_avg_dtype and exp_avg_sq_dtype: both fp32 or both bf16"
+            assert train_cfg.main_params_dtype == "fp32" and train_cfg.main_grads_dtype == "fp32", \
+                "the master weights and the main gradients stay fp32"
+            if dts == {"bf16"}:
+                assert not train_cfg.fused_dp_optimizer, "the fused data-parallel optimizer keeps fp32 moments"
+                extra = dict(state_dtype=torch.bfloat16)
         if train_cfg.optimizer.lower() == "sgd":
             extra = dict(sgd_momentum=train_cfg.sgd_momentum)
         elif train_cfg.optimizer.lower() == "muon":

@@ -16,7 +16,8 @@ from .fused import scratch
 
 def adamw_step_(master, exp_avg, exp_avg_sq, grad, param_out, *, lr, beta1, beta2, eps, weight_decay,
                 step, grad_scale=None, skip=None):
-    """In-place AdamW on flat fp32 state. ``grad`` fp32 or bf16 (flat); ``param_out`` bf16 or None.
+    """In-place AdamW on flat state: fp32 master weights, fp32 or bf16 moments (both the same dtype).  ``grad`` fp32
+    or bf16 (flat); ``param_out`` bf16 or None.
 
     ``grad_scale``: 1-element fp32 tensor multiplied into the gradient (clip coefficient);
     ``skip``: 1-element int32 tensor, non-zero -> the update is skipped (non-finite gradients)."""
@@ -29,10 +30,12 @@ def adamw_step_(master, exp_avg, exp_avg_sq, grad, param_out, *, lr, beta1, beta
         g = grad.float()
         if grad_scale is not None:
             g = g * grad_scale.float()
-        exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
-        exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
-        denom = (exp_avg_sq / bc2).sqrt_().add_(eps)
-        master.mul_(1 - lr * weight_decay).addcdiv_(exp_avg / bc1, denom, value=-lr)
+        m32 = exp_avg.float().mul_(beta1).add_(g, alpha=1 - beta1)
+        v32 = exp_avg_sq.float().mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        exp_avg.copy_(m32)
+        exp_avg_sq.copy_(v32)
+        denom = (v32 / bc2).sqrt_().add_(eps)
+        master.mul_(1 - lr * weight_decay).addcdiv_(m32 / bc1, denom, value=-lr)
         if param_out is not None:
             param_out.copy_(master.to(param_out.dtype))
         return
@@ -40,7 +43,9 @@ def adamw_step_(master, exp_avg, exp_avg_sq, grad, param_out, *, lr, beta1, beta
     assert grad.numel() == n and grad.is_contiguous()
     if param_out is not None:
         assert param_out.dtype == torch.bfloat16 and param_out.numel() == n
-    _lib.call("adamw", master, exp_avg, exp_avg_sq, grad, int(grad.dtype == torch.bfloat16), param_out, n,
+    assert exp_avg.dtype == exp_avg_sq.dtype and exp_avg.dtype in (torch.float32, torch.bfloat16)
+    _lib.call("adamw_ex", master, exp_avg, exp_avg_sq, grad, int(grad.dtype == torch.bfloat16),
+              int(exp_avg.dtype == torch.bfloat16), param_out, n,
               float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(bc1), float(bc2),
               grad_scale, skip)
 

@@ -200,8 +200,12 @@ class DistributedOptimizer:
     """AdamW over the local shards of one or more :class:`ParamGradBuffer`."""
 
     def __init__(self, buffers: list[ParamGradBuffer], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                 clip_grad=1.0, no_wd_filter=None, norm_groups: Iterable = (), check_for_nan=True):
+                 clip_grad=1.0, no_wd_filter=None, norm_groups: Iterable = (), check_for_nan=True,
+                 state_dtype: torch.dtype = torch.float32):
+        """``state_dtype``: dtype of the two Adam moments (fp32, or bf16 with the precision-aware optimizer; the master
+        weights are always fp32 and the arithmetic of a step is fp32)."""
         self.buffers = buffers
+        self.state_dtype = state_dtype
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.clip_grad = clip_grad
         self.norm_groups = [g for g in norm_groups if g is not None]
@@ -216,7 +220,8 @@ class DistributedOptimizer:
                 # weight decay is skipped for 1-D parameters (norm weights, biases): per-element mask ranges
                 wd_ranges = self._wd_ranges(buf, b, s, e, no_wd_filter)
                 self.state.append(dict(buf=buf, bucket=b, s=s, e=e, master=master,
-                                       m=torch.zeros_like(master), v=torch.zeros_like(master), wd_ranges=wd_ranges))
+                                       m=torch.zeros_like(master, dtype=state_dtype),
+                                       v=torch.zeros_like(master, dtype=state_dtype), wd_ranges=wd_ranges))
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.coef = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)

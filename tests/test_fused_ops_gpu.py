@@ -215,3 +215,29 @@ def test_gated_unit_activations(act, with_probs):
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
     if with_probs:
         torch.testing.assert_close(p.grad, pr.grad, rtol=3e-2, atol=0.3)
+
+
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("grad_dtype", [torch.float32, torch.bfloat16])
+def test_adamw_kernel_state_dtypes(state_dtype, grad_dtype):
+    """AdamW kernel with fp32 / bf16 moments and gradients vs the plain PyTorch path on the same values."""
+    from primus_b200.ops import optim
+
+    torch.manual_seed(2)
+    n = 4096 * 3 + 5
+    master = torch.randn(n, device="cuda")
+    m = (torch.randn(n, device="cuda") * 0.01).to(state_dtype)
+    v = (torch.rand(n, device="cuda") * 1e-4).to(state_dtype)
+    g = torch.randn(n, device="cuda").to(grad_dtype)
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    ref = [t.detach().cpu().clone() for t in (master, m, v, g)]
+    ref_out = torch.empty(n, dtype=torch.bfloat16)
+    kw = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
+    optim.adamw_step_(master, m, v, g, out, **kw)
+    optim.adamw_step_(ref[0], ref[1], ref[2], ref[3], ref_out, **kw)
+    torch.cuda.synchronize()
+    tol = 1e-5 if state_dtype == torch.float32 else 1e-2
+    torch.testing.assert_close(master.cpu(), ref[0], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(m.cpu().float(), ref[1].float(), rtol=tol, atol=1e-6)
+    torch.testing.assert_close(v.cpu().float(), ref[2].float(), rtol=tol, atol=1e-9)
+    torch.testing.assert_close(out.cpu().float(), ref_out.float(), rtol=1e-2, atol=1e-2)

@@ -172,3 +172,16 @@ def test_sliding_window_and_sink_attention_in_the_model():
     narrow = GPTModel(TransformerConfig(**kw, window_size=4), "cpu")
     c = narrow(tokens, labels, loss_weights=w, unit_upstream=True)
     assert abs(c.item() - a.item()) > 1e-6
+
+
+def test_precision_aware_optimizer_keeps_bf16_moments():
+    """use_precision_aware_optimizer with bf16 moments: states are bf16, master weights fp32, and training follows
+    the fp32-moment run closely."""
+    tr32, l32 = _train("adam", iters=6, lr=1e-2)
+    tr16, l16 = _train("adam", iters=6, lr=1e-2, use_precision_aware_optimizer=True, exp_avg_dtype="bf16",
+                       exp_avg_sq_dtype="bf16")
+    st = tr16.optimizer.state[0]
+    assert st["m"].dtype == torch.bfloat16 and st["v"].dtype == torch.bfloat16 and st["master"].dtype == torch.float32
+    assert tr32.optimizer.state[0]["m"].dtype == torch.float32
+    assert all(abs(a - b) < 0.05 for a, b in zip(l32, l16)), (l32, l16)
+    assert l16[-1] < l16[0] - 0.3

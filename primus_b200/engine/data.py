@@ -143,7 +143,7 @@ class BatchStager:
         for idxs in self.sampler.next_global_batch():
             b = collate([self.dataset[i] for i in idxs])
             if self.pin:
-                b = {k: v.pin_memory() for k, v in b.items()}
+                b = {k: (v if k.startswith("host_") else v.pin_memory()) for k, v in b.items()}
             mbs.append(b)
         return mbs
 
@@ -156,6 +156,9 @@ class BatchStager:
             for b in host_mbs:
                 d = {}
                 for k, v in b.items():
+                    if k.startswith("host_"):      # host-side metadata (document boundaries): not copied
+                        d[k] = v
+                        continue
                     d[k] = v.to(self.device, non_blocking=True)
                     nbytes += v.numel() * v.element_size()
                 dev.append(d)
@@ -176,7 +179,8 @@ class BatchStager:
             torch.cuda.current_stream().wait_event(ev)
             for b in dev:
                 for v in b.values():
-                    v.record_stream(torch.cuda.current_stream())
+                    if v.is_cuda:
+                        v.record_stream(torch.cuda.current_stream())
         self.h2d_bytes_last_step = nbytes
         return dev
 

@@ -147,23 +147,49 @@ def pack_bins(lengths: list[int], capacity: int, algorithm: str = "first_fit_dec
 
 class PackedSFTDataset:
     """Several samples per sequence; position ids restart at every sample and the first label of a sample is
-    masked so that no loss crosses a boundary."""
+    masked so that no loss crosses a boundary.  With ``align`` > 1 every sample is padded to a multiple of ``align``
+    tokens (the attention kernels work on 128-token blocks) and ``host_cu_seqlens`` carries the sample boundaries
+    (cumulative token offsets, -1 padded to a fixed length) so that attention can be restricted to each sample: the
+    role of the packed-sequence (THD) parameters of the reference (sft/forward_step.py:184-232)."""
 
-    def __init__(self, base: SFTDataset, algorithm: str = "first_fit_decreasing", seed: int = 0):
+    def __init__(self, base: SFTDataset, algorithm: str = "first_fit_decreasing", seed: int = 0, align: int = 1,
+                 boundaries: bool = True):
         self.base = base
-        self.bins = pack_bins(base.lengths(), base.seq_length, algorithm, seed)
+        self.boundaries = boundaries
+        self.align = max(1, int(align))
+        assert base.seq_length % self.align == 0
+        lengths = [-(-l // self.align) * self.align for l in base.lengths()]
+        self.bins = pack_bins(lengths, base.seq_length, algorithm, seed)
+        self.max_docs = base.seq_length // self.align + 1 if self.align > 1 else base.seq_length + 1
 
     def __len__(self):
         return len(self.bins)
 
     def __getitem__(self, i: int) -> dict:
         out = {"tokens": [], "labels": [], "loss_mask": [], "position_ids": []}
+        seq = self.base.seq_length
+        cu = [0]
         for j in self.bins[i % len(self.bins)]:
             it = self.base.item(j)
-            room = self.base.seq_length - len(out["tokens"])
+            room = seq - len(out["tokens"])
+            if room <= 0:
+                break
+            n = min(len(it["tokens"]), room)
+            padn = min(-n % self.align, room - n)
             for k in out:
-                out[k] += it[k][:room]
-        return _pad(out, self.base.seq_length, self.base.pad_id)
+                out[k] += it[k][:n]
+            if padn:
+                out["tokens"] += [self.base.pad_id] * padn
+                out["labels"] += [self.base.pad_id] * padn
+                out["loss_mask"] += [0.0] * padn
+                out["position_ids"] += list(range(n, n + padn))
+            cu.append(len(out["tokens"]))
+        if cu[-1] < seq:
+            cu.append(seq)                       # the padding tail is a segment of its own
+        item = _pad(out, seq, self.base.pad_id)
+        if self.boundaries:
+            item["host_cu_seqlens"] = torch.tensor(cu + [-1] * (self.max_docs + 1 - len(cu)), dtype=torch.int32)
+        return item
 
     def packing_efficiency(self) -> float:
         used = sum(min(l, self.base.seq_length) for l in self.base.lengths())
@@ -283,7 +309,11 @@ class SFTTrainer(PretrainTrainer):
             ds = SFTDataset.from_jsonl(path, tok, eng.tcfg.seq_length, p.get("sft_dataset_format", "alpaca"),
                                        bool(p.get("sft_answer_only_loss", True)))
             if p.get("sft_packing"):
-                ds = PackedSFTDataset(ds, p.get("sft_packing_algorithm", "first_fit_decreasing"), eng.tcfg.seed)
+                # reset_attention_mask (default on): attention stays inside each packed sample; the GPU attention
+                # kernels need the samples aligned to their 128-token blocks
+                reset = bool(p.get("reset_attention_mask", True))
+                ds = PackedSFTDataset(ds, p.get("sft_packing_algorithm", "first_fit_decreasing"), eng.tcfg.seed,
+                                      align=128 if (reset and eng.is_cuda) else 1, boundaries=reset)
             eng.sampler = MicroBatchSampler(eng.tcfg.global_batch_size, eng.tcfg.micro_batch_size, eng.st.dp, eng.st.dp_rank)
             eng.stager = BatchStager(ds, eng.sampler, eng.device)
             eng.use_position_ids = True

@@ -312,7 +312,8 @@ class Trainer:
             w = self._loss_weights(mb)
             loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True,
                          position_ids=mb.get("position_ids") if (getattr(self, "use_position_ids", False)
-                                                                 or self.st.cp > 1) else None)
+                                                                 or self.st.cp > 1) else None,
+                         cu_seqlens=mb.get("host_cu_seqlens"))
             loss.backward()
             total += loss.detach()
         return total
@@ -545,7 +546,8 @@ class Trainer:
             for mb in mbs:
                 w = self._loss_weights(mb)
                 pos = mb.get("position_ids") if (getattr(self, "use_position_ids", False) or self.st.cp > 1) else None
-                total += self.model(mb["tokens"], mb["labels"], loss_weights=w, position_ids=pos).detach().float()
+                total += self.model(mb["tokens"], mb["labels"], loss_weights=w, position_ids=pos,
+                                    cu_seqlens=mb.get("host_cu_seqlens")).detach().float()
         val = self.reduced_loss(total / max(iters, 1))
         ppl = math.exp(min(val, 20.0))
         self.last_metrics.update(validation_loss=val, validation_ppl=ppl)

@@ -85,10 +85,12 @@ class SelfAttention(nn.Module):
         d = cfg.kv_channels
         if cfg.qk_layernorm:
             qkv = self._qk_norm(qkv, d)
-        cos, sin, pos = rope
+        cos, sin, pos = rope[:3]
+        segments = rope[3] if len(rope) > 3 else None
         scale = cfg.attention_softmax_scale
-        if st.cp > 1 and (self.window or self.has_sinks):
-            raise NotImplementedError("sliding-window / sink attention is not available under context parallelism")
+        if st.cp > 1 and (self.window or self.has_sinks or segments):
+            raise NotImplementedError("sliding-window / sink / per-document attention is not available under context "
+                                      "parallelism")
         if st.cp > 1 and cfg.cp_comm_type == "allgather":
             ctx_out = layers.allgather_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group,
                                                          st.cp, rot_dim=int(d * cfg.rotary_percent), causal=True,
@@ -102,7 +104,7 @@ class SelfAttention(nn.Module):
             sinks = self.core_attention.softmax_offset.float() if self.has_sinks else None
             ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
                                             rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
-                                            window=self.window, sinks=sinks)
+                                            window=self.window, sinks=sinks, segments=segments)
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 
@@ -290,7 +292,9 @@ class GPTModel(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens=None, labels=None, loss_weights=None, hidden_in=None, position_ids=None,
-                unit_upstream=False):
+                unit_upstream=False, cu_seqlens=None):
+        """``cu_seqlens`` (host int tensor [batch, L], -1 padded): cumulative token offsets of the documents packed
+        into each sequence; attention is then restricted to each document."""
         cfg = self.cfg
         st = ps.get_state()
         sp = cfg.sequence_parallel and st.tp > 1
@@ -308,7 +312,7 @@ class GPTModel(nn.Module):
         if batch > 1 or position_ids is not None:
             pos = (position_ids.reshape(-1).to(torch.int32) if position_ids is not None
                    else torch.arange(seq, device=device, dtype=torch.int32).repeat(batch))
-        rope = (cos, sin, pos)
+        rope = (cos, sin, pos, _segments(cu_seqlens, batch, seq))
         for i in self.decoder.layer_indices:
             layer = self.decoder.layers[str(i)]
             hidden, residual = _run_layer(layer, hidden, residual, rope, batch, cfg)
@@ -365,6 +369,18 @@ class GPTModel(nn.Module):
             total = lk if total is None else total + lk
             h = hid if res is None else hid + res
         return total * (cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers)
+
+
+def _segments(cu_seqlens, batch: int, seq: int):
+    """[(start, end)] token ranges in the flattened [batch * seq] layout, or None."""
+    if cu_seqlens is None:
+        return None
+    rows = cu_seqlens.reshape(batch, -1).tolist()
+    segs = []
+    for b, row in enumerate(rows):
+        cu = [c for c in row if c >= 0]
+        segs += [(b * seq + a, b * seq + e) for a, e in zip(cu[:-1], cu[1:]) if e > a]
+    return segs
 
 
 def _run_layer(layer, hidden, residual, rope, batch, cfg):

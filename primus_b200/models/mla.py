@@ -105,6 +105,8 @@ class MLASelfAttention(nn.Module):
         seq = T // batch
         cos, sin = self.rope_tables(y.device, seq * ps.get_state().cp)   # positions are global under context parallelism
         pos = rope[2]
+        if len(rope) > 3 and rope[3]:
+            raise NotImplementedError("per-document attention (packed sequences) is not built for multi-latent attention")
         if cfg.q_lora_rank:
             ql = gemm.linear(y, self.linear_q_down_proj.weight)
             ql = fused.rmsnorm(ql, self.linear_q_up_proj.layer_norm_weight, cfg.norm_epsilon)

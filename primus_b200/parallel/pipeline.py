@@ -113,12 +113,13 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
             if s == S - 1:
                 w = trainer._loss_weights(mb)
                 out = model(mb["tokens"] if s == 0 else None, mb["labels"], loss_weights=w, hidden_in=hidden_in,
-                            unit_upstream=True, position_ids=_pos_ids(trainer, mb))
+                            unit_upstream=True, position_ids=_pos_ids(trainer, mb),
+                            cu_seqlens=mb.get("host_cu_seqlens"))
                 outputs[k] = out
                 total += out.detach()
             else:
                 h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in,
-                                     position_ids=_pos_ids(trainer, mb))
+                                     position_ids=_pos_ids(trainer, mb), cu_seqlens=mb.get("host_cu_seqlens"))
                 if res is None:
                     res = torch.zeros_like(h)
                 y = torch.stack([h, res])

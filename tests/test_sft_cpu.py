@@ -107,3 +107,41 @@ modules:
                        capture_output=True, text=True, cwd=root, env=dict(os.environ, PYTHONPATH=root))
     assert r.returncode == 0, r.stderr[-2000:]
     assert "Training completed." in r.stderr
+
+
+def test_aligned_packing_and_document_boundaries():
+    ds = S.SFTDataset(_records(), S.ByteTokenizer(), 512, "alpaca", True)
+    pk = S.PackedSFTDataset(ds, align=128)
+    it = pk[0]
+    cu = [c for c in it["host_cu_seqlens"].tolist() if c >= 0]
+    assert cu[0] == 0 and cu[-1] == 512 and all(c % 128 == 0 for c in cu) and cu == sorted(set(cu))
+    # positions restart at every boundary that starts a sample; padding carries no loss
+    for a in cu[:-1]:
+        assert it["position_ids"][a] == 0 or it["loss_mask"][a:].sum() == 0
+    assert len(it["host_cu_seqlens"]) == 512 // 128 + 2
+    assert "host_cu_seqlens" not in S.PackedSFTDataset(ds, boundaries=False)[0]
+
+
+def test_attention_stays_inside_each_packed_document():
+    """A model run on two documents packed into one sequence (with their boundaries) gives each document the loss it
+    gets when run alone; without the boundaries the second document sees the first and its loss changes."""
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    torch.manual_seed(0)
+    m = GPTModel(TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4,
+                                   vocab_size=128, params_dtype="fp32", seq_length=32), "cpu")
+    a, b = torch.randint(0, 128, (1, 20)), torch.randint(0, 128, (1, 12))
+    tok = torch.cat([a, b], 1)
+    lab = torch.roll(tok, -1, 1)
+    pos = torch.cat([torch.arange(20), torch.arange(12)]).view(1, 32)
+    cu = torch.tensor([[0, 20, 32, -1]], dtype=torch.int32)
+    packed = m(tok, lab, position_ids=pos, cu_seqlens=cu)                    # per-token losses [1, 32]
+    alone_a = m(a, lab[:, :20], position_ids=pos[:, :20])
+    alone_b = m(b, lab[:, 20:], position_ids=pos[:, 20:])
+    assert torch.allclose(packed[:, :20], alone_a, atol=1e-5) and torch.allclose(packed[:, 20:], alone_b, atol=1e-5)
+    leaky = m(tok, lab, position_ids=pos)
+    assert torch.allclose(leaky[:, :20], alone_a, atol=1e-5) and not torch.allclose(leaky[:, 20:], alone_b, atol=1e-4)

@@ -168,3 +168,16 @@ def test_schema_check_flags_unknown_keys_with_suggestions(tmp_path):
     joined = " ".join(exp.schema_findings)
     assert "train_iter" in joined and "train_iters" in joined and "global_batchsize" in joined
     assert "micro_batch_size'" not in joined
+
+
+def test_example_configs_pass_the_schema_check():
+    """No example recipe uses a key that neither the model / trainer configs nor the presets know."""
+    import yaml
+
+    from primus_b200.core.config import schema_check
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "configs")
+    for f in sorted(os.listdir(root)):
+        with open(os.path.join(root, f)) as fh:
+            raw = yaml.safe_load(fh)
+        assert schema_check.check_experiment(raw) == [], f

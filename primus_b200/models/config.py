@@ -80,6 +80,8 @@ class TransformerConfig:
     fp8_recipe: str = "mxfp8"
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_layer_ids: Optional[List[int]] = None
+    cpu_offloading: bool = False                   # keep the saved activations of the first layers in pinned host memory
+    cpu_offloading_num_layers: int = 0
     cross_entropy_chunk_tokens: int = 0  # >0: chunked linear-cross-entropy
     window_size: object = None                      # sliding-window attention: W, or Megatron's (left, right) = (W - 1, 0)
     window_attn_skip_freq: object = None            # int N: every N-th layer attends fully; list: 1 = windowed, 0 = full

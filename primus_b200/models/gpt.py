@@ -392,6 +392,12 @@ def _run_layer(layer, hidden, residual, rope, batch, cfg):
         if residual is None:
             return checkpoint(lambda h: layer(h, None, rope, batch), hidden, use_reentrant=False)
         return checkpoint(lambda h, r: layer(h, r, rope, batch), hidden, residual, use_reentrant=False)
+    if cfg.cpu_offloading and torch.is_grad_enabled() and hidden.is_cuda and (
+            layer.layer_idx < (cfg.cpu_offloading_num_layers or 0)):
+        from ..engine.offload import offload_saved_activations
+
+        with offload_saved_activations():
+            return layer(hidden, residual, rope, batch)
     return layer(hidden, residual, rope, batch)
 
 

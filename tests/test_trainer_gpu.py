@@ -8,7 +8,7 @@ from primus_b200.ops import _lib
 pytestmark = pytest.mark.gpu
 
 
-def _run(kind: str, iters: int, save=None, load=None, resume_iters=None):
+def _run(kind: str, iters: int, save=None, load=None, resume_iters=None, **model_kw):
     from primus_b200.engine.trainer import TrainConfig, Trainer
     from primus_b200.models.config import TransformerConfig
     from primus_b200.ops import gemm
@@ -23,9 +23,10 @@ def _run(kind: str, iters: int, save=None, load=None, resume_iters=None):
     if kind == "moe":
         kw.update(num_experts=8, moe_router_topk=2, moe_ffn_hidden_size=256, moe_layer_freq=[0, 1],
                   moe_aux_loss_coeff=1e-2)
+    kw.update(model_kw)
     try:
         mc = TransformerConfig(**kw)
-        tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=256, train_iters=iters, lr=2e-3,
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=mc.seq_length, train_iters=iters, lr=2e-3,
                          lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1, save=save,
                          load=load, save_interval=iters if save else None)
         torch.manual_seed(0)
@@ -53,3 +54,13 @@ def test_resume_from_checkpoint_continues_bitwise(tmp_path):
     rest = _run("bf16", 6, load=str(tmp_path / "ck"), resume_iters=3)
     assert first == full[:3]
     assert rest == full[3:], (rest, full[3:])
+
+
+def test_activation_offload_changes_nothing_but_where_tensors_live():
+    from primus_b200.engine import offload
+
+    base = _run("bf16", 3, seq_length=2048)
+    before = offload.STATS["offloaded_tensors"]
+    off = _run("bf16", 3, seq_length=2048, cpu_offloading=True, cpu_offloading_num_layers=2)
+    assert offload.STATS["offloaded_tensors"] > before and offload.STATS["offloaded_bytes"] > 0
+    assert off == base, (off, base)

@@ -1,0 +1,74 @@
+"""Fully sharded data parallelism (``use_torch_fsdp2``): parameters, gradients and optimizer state sharded over the
+data-parallel ranks with PyTorch's ``fully_shard``; the layers still run this package's kernels on the gathered
+parameters.
+
+Every transformer layer is one sharding unit (parameters all-gathered right before the layer runs and freed after,
+gradients reduce-scattered in fp32 after its backward), the root module holds the embedding, the final norm and the
+output layer.  Sharded parameters and Adam state are fp32, compute parameters bf16.  Role of the reference's
+``core/distributed/torch_fully_sharded_data_parallel.py`` and ``optimizer/fsdp2_fp32_master_weight_opt``; scope: data
+parallelism only (tp = pp = cp = ep = 1), bf16 compute (no MXFP8 recipe), AdamW.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_model(model: torch.nn.Module, device: torch.device, compute_dtype: torch.dtype):
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    world = dist.get_world_size()
+    mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("dp",))
+    model.float()                                   # sharded (master) parameters are fp32
+    mp = MixedPrecisionPolicy(param_dtype=compute_dtype if compute_dtype != torch.float32 else None,
+                              reduce_dtype=torch.float32)
+    for layer in model.decoder.layers.values():
+        fully_shard(layer, mesh=mesh, mp_policy=mp)
+    fully_shard(model, mesh=mesh, mp_policy=mp)
+    return model
+
+
+class FSDP2Optimizer:
+    """AdamW over the sharded fp32 parameters with the interface the trainer uses (``step(lr, weight_decay)``,
+    ``grad_norm``, ``compute_grad_norm``, ``zero_grad``).  1-D parameters (norm weights) get no weight decay."""
+
+    def __init__(self, model, lr, betas, eps, weight_decay, clip_grad, check_for_nan=True):
+        self.model = model
+        self.clip_grad = clip_grad
+        self.check_for_nan = check_for_nan
+        decay = [p for p in model.parameters() if p.ndim > 1]
+        no_decay = [p for p in model.parameters() if p.ndim <= 1]
+        dev = next(model.parameters()).device
+        self.opt = torch.optim.AdamW(
+            [dict(params=decay, weight_decay=weight_decay), dict(params=no_decay, weight_decay=0.0)],
+            lr=lr, betas=betas, eps=eps, fused=dev.type == "cuda")
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.state = []
+        self.step_count = 0
+
+    def zero_grad(self):
+        self.opt.zero_grad(set_to_none=True)
+
+    def compute_grad_norm(self):
+        n = torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.clip_grad if self.clip_grad else float("inf"))
+        n = n.full_tensor() if hasattr(n, "full_tensor") else n
+        self.grad_norm.copy_(n.reshape(1).float())
+        return self.grad_norm
+
+    def step(self, lr=None, weight_decay=None):
+        from ..ops import gemm
+
+        norm = self.compute_grad_norm()
+        if self.check_for_nan and not bool(torch.isfinite(norm).item()):
+            self.zero_grad()
+            return False
+        for i, g in enumerate(self.opt.param_groups):
+            if lr is not None:
+                g["lr"] = lr
+            if weight_decay is not None and i == 0:
+                g["weight_decay"] = weight_decay
+        self.opt.step()
+        self.step_count += 1
+        gemm.bump_weight_generation()
+        return True

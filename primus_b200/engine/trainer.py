@@ -78,6 +78,7 @@ class TrainConfig:
     dump_pp_data: bool = False         # per-node pipeline timeline (one JSON per pipeline rank and iteration; it
     pp_dump_dir: Optional[str] = None  # synchronises after every node, so the timed iterations are slower)
     pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
+    use_torch_fsdp2: bool = False      # shard parameters / gradients / optimizer state over the data-parallel ranks
     use_precision_aware_optimizer: bool = False   # Adam moments in exp_avg_dtype / exp_avg_sq_dtype ("fp32" | "bf16")
     exp_avg_dtype: str = "fp32"
     exp_avg_sq_dtype: str = "fp32"
@@ -190,6 +191,28 @@ class Trainer:
         self.model = self.model_chunks[0]
         # ---------------------------------------------------------------- buffers + optimizer
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        self.fsdp = bool(train_cfg.use_torch_fsdp2) and st.world_size > 1
+        if self.fsdp:
+            self._init_fsdp2()
+        else:
+            self._init_buffers_and_optimizer()
+        self._init_schedule_and_data()
+
+    def _init_fsdp2(self):
+        from . import fsdp
+
+        model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
+        assert st.tp == st.pp == st.cp == st.ep == 1, "use_torch_fsdp2: data parallelism only (tp = pp = cp = ep = 1)"
+        assert not (model_cfg.fp8 and model_cfg.fp8_recipe), "use_torch_fsdp2 runs in bf16 (no MXFP8 recipe)"
+        assert train_cfg.optimizer.lower() in ("adam", "adamw"), "use_torch_fsdp2 uses AdamW"
+        fsdp.shard_model(self.model, self.device, model_cfg.torch_dtype)
+        self.buffers = []
+        self.optimizer = fsdp.FSDP2Optimizer(self.model, train_cfg.lr, (train_cfg.adam_beta1, train_cfg.adam_beta2),
+                                             train_cfg.adam_eps, train_cfg.weight_decay, train_cfg.clip_grad,
+                                             train_cfg.check_for_nan_in_loss_and_grad)
+
+    def _init_buffers_and_optimizer(self):
+        model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
         dense, expert = [], []
         for m in self.model_chunks:
             for p in m.parameters():
@@ -226,6 +249,9 @@ class Trainer:
             train_cfg.optimizer, self.buffers, **extra, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
             check_for_nan=train_cfg.check_for_nan_in_loss_and_grad)
+
+    def _init_schedule_and_data(self):
+        model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
         self.scheduler = schedules.LRScheduler(
             max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_iters=train_cfg.lr_warmup_iters,
             decay_iters=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style,
@@ -309,6 +335,8 @@ class Trainer:
             last = i == n - 1
             for buf in self.buffers:
                 buf.is_last_microbatch = last
+            if self.fsdp:      # gradients are reduce-scattered once, with the last micro-batch
+                model.set_requires_gradient_sync(last)
             w = self._loss_weights(mb)
             loss = model(mb["tokens"], mb["labels"], loss_weights=w, unit_upstream=True,
                          position_ids=mb.get("position_ids") if (getattr(self, "use_position_ids", False)
@@ -368,6 +396,8 @@ class Trainer:
             self._pp_warmed = True
         for buf in self.buffers:
             buf.zero_grad()
+        if self.fsdp:
+            self.optimizer.zero_grad()
         if self.st.pp > 1:
             from ..parallel.pipeline import run_pipeline_schedule
 
@@ -384,8 +414,9 @@ class Trainer:
         else:
             loss = self.forward_backward_no_pipelining(micro_batches)
         self.stager.prefetch()  # stage the next step's batch while the optimizer runs
-        self._pre_sync_sp_norm_grads()
-        self.finalize_grads()
+        if not self.fsdp:
+            self._pre_sync_sp_norm_grads()
+            self.finalize_grads()
         lr = self.scheduler.get_lr(self.iteration + 1)
         if getattr(self, "lora", None) is not None:  # adapter-only training: base weights stay frozen
             self.optimizer.compute_grad_norm()
@@ -576,6 +607,9 @@ class Trainer:
     # ------------------------------------------------------------------ checkpoint
     def save_checkpoint(self, path: Optional[str] = None):
         from . import checkpoint
+
+        if self.fsdp:
+            raise NotImplementedError("checkpointing under use_torch_fsdp2 is not built")
 
         return checkpoint.save_checkpoint(self, path or self.tcfg.save)
 

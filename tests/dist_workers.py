@@ -3,7 +3,7 @@ import torch
 
 
 def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
-              pp_warmup=False, cp_comm="a2a", mla=False):
+              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
@@ -19,7 +19,7 @@ def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2,
     mc = TransformerConfig(**kw)
     tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=iters, lr=1e-2,
                      lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, pipeline_schedule=schedule,
-                     log_interval=1, pp_warmup=pp_warmup)
+                     log_interval=1, pp_warmup=pp_warmup, use_torch_fsdp2=fsdp)
     return mc, tc
 
 
@@ -57,7 +57,12 @@ def load_from_full(trainer, full_sd):
                 part = torch.cat([t.chunk(n, 0)[i] for t in (q, k, v)], 0)
             else:
                 part = C.slice_global(name, full, spec)
-            p.data.copy_(part)
+            if hasattr(p, "device_mesh"):      # fully sharded parameter: hand every rank its shard of the full tensor
+                from torch.distributed.tensor import distribute_tensor
+
+                p.data.copy_(distribute_tensor(part.to(p.dtype), p.device_mesh, p.placements))
+            else:
+                p.data.copy_(part)
     C._refresh_master_weights(trainer)
 
 

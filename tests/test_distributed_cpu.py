@@ -33,6 +33,7 @@ def _mc_kwargs(mc):
 
 CASES = {
     "dp2": dict(world=2, kw=dict()),
+    "dp2_fsdp2": dict(world=2, kw=dict(fsdp=True)),
     "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
     "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),

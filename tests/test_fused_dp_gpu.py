@@ -40,3 +40,35 @@ def test_fused_dp_optimizer_matches_nccl(tmp_path):
     for x, y in zip(ra["losses"], rb["losses"]):
         assert abs(x - y) <= 2e-3 * max(1.0, abs(x)), (ra, rb)
     assert abs(ra["checksum"] - rb["checksum"]) <= 1e-3 * ra["checksum"]
+
+
+def _fsdp_worker(rank, world, fsdp, outp):
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.ops import _lib
+    from primus_b200.parallel import state as ps
+
+    ps.initialize_model_parallel()
+    cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1408, num_attention_heads=4,
+                            num_query_groups=2, kv_channels=128, vocab_size=8192, params_dtype="bf16")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=256, train_iters=4, lr=1e-3,
+                     lr_decay_style="constant", use_torch_fsdp2=fsdp)
+    torch.manual_seed(0)
+    tr = Trainer(cfg, tc, device=f"cuda:{rank}", log_fn=lambda s: None)
+    losses = tr.train(4)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    if rank == 0:
+        json.dump({"losses": losses, "fsdp": bool(tr.fsdp)}, open(outp, "w"))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp2_follows_the_distributed_optimizer(tmp_path):
+    """Fully sharded run (torch fully_shard around this package's layers) vs the ZeRO-1 distributed optimizer."""
+    a, b = str(tmp_path / "zero1.json"), str(tmp_path / "fsdp.json")
+    run_ranks(_fsdp_worker, 2, "nccl", args=(False, a), timeout=240)
+    run_ranks(_fsdp_worker, 2, "nccl", args=(True, b), timeout=240)
+    ra, rb = json.load(open(a)), json.load(open(b))
+    assert rb["fsdp"] and not ra["fsdp"]
+    for x, y in zip(ra["losses"], rb["losses"]):
+        assert abs(x - y) <= 5e-3 * max(1.0, abs(x)), (ra, rb)

@@ -42,7 +42,9 @@ def config_from_hf(hf: dict) -> dict:
     E = hf.get("num_experts") or hf.get("num_local_experts") or hf.get("n_routed_experts")
     if E:
         out.update(num_experts=E, moe_router_topk=hf.get("num_experts_per_tok", 2),
-                   moe_ffn_hidden_size=hf.get("moe_intermediate_size"))
+                   moe_ffn_hidden_size=hf.get("moe_intermediate_size") or hf.get("intermediate_size"))
+    if mt == "mixtral":     # every layer is sparse; probabilities are the softmax over the selected logits
+        out.update(moe_layer_freq=[1] * hf["num_hidden_layers"], moe_router_pre_softmax=False)
     if mt == "qwen3_moe":
         step = hf.get("decoder_sparse_step", 1)
         only = set(hf.get("mlp_only_layers") or [])
@@ -134,6 +136,15 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
         m = p + "mlp."
         if cfg.is_moe_layer(L):
             sd[p + "pre_mlp_layernorm.weight"] = hf[h + "post_attention_layernorm.weight"]
+            if h + "block_sparse_moe.gate.weight" in hf:     # published Mixtral checkpoints: w1 = gate, w3 = up, w2 = down
+                b = h + "block_sparse_moe."
+                sd[m + "router.weight"] = hf[b + "gate.weight"]
+                sd[m + "experts.fc1_weight.weight"] = torch.stack(
+                    [torch.cat([hf[b + f"experts.{e}.w1.weight"], hf[b + f"experts.{e}.w3.weight"]], 0)
+                     for e in range(cfg.num_experts)])
+                sd[m + "experts.fc2_weight.weight"] = torch.stack(
+                    [hf[b + f"experts.{e}.w2.weight"] for e in range(cfg.num_experts)])
+                continue
             sd[m + "router.weight"] = hf[h + "mlp.gate.weight"]
             if cfg.moe_router_enable_expert_bias:
                 sd[m + "router.expert_bias"] = hf[h + "mlp.gate.e_score_correction_bias"].float()

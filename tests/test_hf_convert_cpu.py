@@ -86,3 +86,33 @@ def test_deepseek_v3_matches_hf():
             layer.mlp.gate.e_score_correction_bias.copy_(torch.randn(8) * 0.1)
             layer.mlp.gate.weight.copy_(torch.randn_like(layer.mlp.gate.weight) * 0.5)
     _check(m, c, torch.randint(0, 250, (1, 16)))
+
+
+def test_mixtral_matches_hf():
+    from transformers import MixtralConfig, MixtralForCausalLM
+
+    torch.manual_seed(4)
+    c = MixtralConfig(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=250, num_local_experts=4, num_experts_per_tok=2,
+                      max_position_embeddings=128, tie_word_embeddings=False, router_aux_loss_coef=0.0,
+                      sliding_window=None)
+    m = MixtralForCausalLM(c)
+    _check(m, c, torch.randint(0, 250, (1, 16)))
+    # the layout of published checkpoints (block_sparse_moe.experts.N.w1 / w3 / w2) converts to the same weights
+    from primus_b200.models.config import TransformerConfig
+
+    cfg = TransformerConfig(**H.config_from_hf(c.to_dict()), params_dtype="fp32", seq_length=16,
+                            make_vocab_size_divisible_by=8)
+    sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    new = H.hf_to_internal(sd, cfg)
+    old = dict(sd)
+    for L in range(2):
+        h = f"model.layers.{L}."
+        gu, dn = old.pop(h + "mlp.experts.gate_up_proj"), old.pop(h + "mlp.experts.down_proj")
+        old[h + "block_sparse_moe.gate.weight"] = old.pop(h + "mlp.gate.weight")
+        for e in range(4):
+            old[h + f"block_sparse_moe.experts.{e}.w1.weight"] = gu[e, :96]
+            old[h + f"block_sparse_moe.experts.{e}.w3.weight"] = gu[e, 96:]
+            old[h + f"block_sparse_moe.experts.{e}.w2.weight"] = dn[e]
+    conv = H.hf_to_internal(old, cfg)
+    assert conv.keys() == new.keys() and all(torch.equal(conv[k], new[k]) for k in new)

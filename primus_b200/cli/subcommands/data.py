@@ -16,6 +16,8 @@ def register_subcommand(subparsers):
     t.add_argument("--tokenizer", default=None, help="HF tokenizer name/path; default: byte-level")
     t.add_argument("--json-key", default="text")
     t.add_argument("--append-eod", action="store_true")
+    t.add_argument("--format", default="flat", choices=["flat", "megatron"],
+                   help="flat: <prefix>.bin + <prefix>.idx.npy; megatron: the MMIDIDX .bin / .idx pair of Megatron-LM")
     i = sp.add_parser("inspect")
     i.add_argument("--path", required=True)
     i.add_argument("--seq-length", type=int, default=4096)
@@ -57,6 +59,13 @@ def run(args, unknown):
                 t.append(tok.eos_token_id if tok and tok.eos_token_id is not None else 0)
             ids.extend(t)
             starts.append(len(ids))
+    if args.format == "megatron":
+        from ...engine.indexed_dataset import write_indexed_dataset
+
+        arr = np.asarray(ids, dtype=np.int32)
+        write_indexed_dataset(args.output, [arr[a:b] for a, b in zip(starts[:-1], starts[1:])], dtype=np.int32)
+        print(f"wrote {len(ids)} tokens in {len(starts) - 1} documents to {args.output}.bin / .idx")
+        return 0
     np.asarray(ids, dtype=np.int32).tofile(args.output + ".bin")
     np.save(args.output + ".idx.npy", np.asarray(starts, dtype=np.int64))
     print(f"wrote {len(ids)} tokens in {len(starts) - 1} documents to {args.output}.bin")

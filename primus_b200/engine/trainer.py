@@ -62,6 +62,9 @@ class TrainConfig:
     data_seed: int = 1234
     mock_data: bool = True
     mock_data_period: int = 0          # > 0: learnable periodic sequences instead of uniform-random tokens
+    eod_token: Optional[int] = None    # indexed corpora: id of the end-of-document token
+    eod_mask_loss: bool = False        # ... no loss on it
+    reset_position_ids: bool = False   # ... positions restart after it
     mock_data_kind: str = ""           # "markov": learnable first-order Markov chain (smooth loss curve)
     data_path: Optional[str] = None
     log_interval: int = 1
@@ -127,6 +130,24 @@ class TrainConfig:
             fused_tp.ENABLED = True
             fused_tp.ENABLED_RS = bool(d.get("tp_comm_overlap_rs", False))
         return cls(**kw)
+
+
+def _open_corpus(data_path, seq_length: int, seed: int, tc):
+    """Token corpus for pre-training: a Megatron indexed dataset (``<prefix>.idx`` + ``<prefix>.bin``, or a
+    ``weight prefix ...`` blend) when the index file exists, else the flat token file of ``primus data tokenize``."""
+    import os
+
+    from .data import IndexedTokenDataset
+
+    parts = data_path.split() if isinstance(data_path, str) else list(data_path)
+    first = parts[1] if len(parts) > 1 else parts[0]
+    if os.path.exists(first + ".idx"):
+        from .indexed_dataset import build_gpt_dataset
+
+        return build_gpt_dataset(parts, seq_length, seed, eod_token=getattr(tc, "eod_token", None),
+                                 eod_mask_loss=bool(getattr(tc, "eod_mask_loss", False)),
+                                 reset_position_ids=bool(getattr(tc, "reset_position_ids", False)))
+    return IndexedTokenDataset(parts[0], seq_length)
 
 
 class ThroughputMeter:
@@ -271,11 +292,11 @@ class Trainer:
             else:
                 ds = MockGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
         else:
-            from .data import IndexedTokenDataset
-
-            ds = IndexedTokenDataset(train_cfg.data_path, train_cfg.seq_length)
+            ds = _open_corpus(train_cfg.data_path, train_cfg.seq_length, train_cfg.data_seed, train_cfg)
         self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank)
         self.stager = BatchStager(ds, self.sampler, self.device)
+        if train_cfg.reset_position_ids:
+            self.use_position_ids = True
         self.iteration = 0
         self.meter = ThroughputMeter(train_cfg.log_avg_skip_iterations, train_cfg.log_avg_reset_interval)
         self.flops_per_token = schedules.model_flops_per_token(model_cfg, train_cfg.seq_length)
@@ -555,7 +576,8 @@ class Trainer:
             else:
                 from .data import IndexedTokenDataset
 
-                ds = IndexedTokenDataset(getattr(tc, "valid_data_path", None) or tc.data_path, tc.seq_length)
+                ds = _open_corpus(getattr(tc, "valid_data_path", None) or tc.data_path, tc.seq_length,
+                                  tc.data_seed + 1000003, tc)
             sampler = MicroBatchSampler(tc.global_batch_size, tc.micro_batch_size, st.dp, st.dp_rank)
             self._eval_stager_obj = BatchStager(ds, sampler, self.device)
         return self._eval_stager_obj

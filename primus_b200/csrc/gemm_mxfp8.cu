@@ -12,8 +12,7 @@
 // * TMEM holds the accumulator(s) plus 4 + BN/32 scale columns: a 128 x 256 tile leaves room for one
 //   accumulator only (the producer keeps prefetching the next tile while the epilogue drains it), a 128 x 128
 //   tile is double buffered,
-// * the epilogue (eight warps: two per TMEM lane quarter, each half of the columns) reads the accumulator with
-//   tcgen05.ld and writes full lines per row straight from registers;
+// * the epilogue reads the accumulator with tcgen05.ld and writes full lines per row straight from registers;
 //   for bf16 output a thread first drains its whole row into packed registers and releases the accumulator, so
 //   the global stores overlap the next tile's MMAs (fp32 store / fp32 `red.add` into a main-grad buffer go
 //   32 columns at a time).
@@ -31,8 +30,8 @@ constexpr int BM = 128;
 constexpr int BK = 128;   // fp8 elements = bytes per swizzle row
 constexpr int UMMA_K = 32;
 constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
-constexpr int EPI_THREADS = 256;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
 constexpr int GROUP_M = 16;
 enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ADD = 2 };
 
@@ -228,18 +227,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   } else {
-    // two warps per TMEM lane quarter: warps 2-5 drain the first half of the accumulator columns, warps 6-9 the second
     const int lane_grp = warp & 3;
-    const int half = (warp - 2) >> 2;
     const int row = lane_grp * 32 + lane;
-    constexpr int HC = BN / 2;      // columns per epilogue warp
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int mb, nb;
       tile_coords(tile, num_m, num_n, mb, nb);
-      const int m = mb * BM + row, n0 = nb * BN + half * HC;
+      const int m = mb * BM + row, n0 = nb * BN;
       if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort_flag)) {
         atomicCAS(status, 0, PB_ERR_TIMEOUT_EPILOGUE);
         bars->abort_flag = 1;
@@ -247,13 +243,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         break;
       }
       pb::tc_fence_after();
-      const uint32_t t_row = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN + half * HC;
+      const uint32_t t_row = tmem_base + (uint32_t(lane_grp * 32) << 16) + acc * BN;
       if (OUT == OUT_BF16) {
-        // drain this warp's columns into registers as packed bf16, hand the accumulator back to the MMA thread, and
-        // only then write to global memory: the next tile's MMAs overlap the stores
-        uint32_t packed[HC / 2];
+        // drain the whole row into registers as packed bf16 (BN / 2 registers), hand the accumulator back to the
+        // MMA thread, and only then write to global memory: the next tile's MMAs overlap the stores
+        uint32_t packed[BN / 2];
 #pragma unroll
-        for (int c = 0; c < HC / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           pb::tmem_ld_32x32b_x32(t_row + c * 32, r);
           pb::tmem_wait_ld();
@@ -266,14 +262,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (m < M) {
           __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(Dv) + (long)m * ldd + n0;
 #pragma unroll
-          for (int j = 0; j < HC / 8; ++j)
+          for (int j = 0; j < BN / 8; ++j)
             if (n0 + 8 * j < N)
               reinterpret_cast<uint4*>(d)[j] =
                   make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < HC / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           pb::tmem_ld_32x32b_x32(t_row + c * 32, r);
           pb::tmem_wait_ld();

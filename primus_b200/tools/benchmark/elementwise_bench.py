@@ -81,16 +81,18 @@ def main(argv=None):
     res = [torch.randn(T, H, device=dev).bfloat16() for _ in range(n)]
     add("rmsnorm fwd + residual add", lambda i: fused.rmsnorm(xs[i % n], w, 1e-5, res[i % n]), T * H * 8, n)
     add("rmsnorm fwd", lambda i: fused.rmsnorm(xs[i % n], w, 1e-5), T * H * 4, n)
-    xr = [x.clone().requires_grad_() for x in xs]
-    wr = torch.nn.Parameter(w.clone())
-    ys = [fused.rmsnorm(x, wr, 1e-5) for x in xr]
     dy = [torch.randn(T, H, device=dev).bfloat16() for _ in range(n)]
-
-    def norm_bwd(i):
-        ys[i % n].backward(dy[i % n], retain_graph=True)
-
-    add("rmsnorm bwd (dx + dw)", norm_bwd, T * H * 6, n)
-    del ys, xr, dy, res
+    rstd = torch.rand(T, device=dev) + 0.5
+    dx = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    dwf = torch.empty(H, dtype=torch.float32, device=dev)
+    P = _lib.call_ret("rmsnorm_bwd_num_partials", T)
+    sc = fused.scratch(torch.device(dev, torch.cuda.current_device()), "rmsnorm_dw", P * H)
+    add("rmsnorm bwd (dx + dw partials + dw reduce)",
+        lambda i: _lib.call("rmsnorm_bwd", dy[i % n], xs[i % n], w, rstd, None, dx, dwf, sc, T, H, H, H, 0), T * H * 6, n)
+    add("rmsnorm bwd + residual gradient",
+        lambda i: _lib.call("rmsnorm_bwd", dy[i % n], xs[i % n], w, rstd, res[i % n], dx, dwf, sc, T, H, H, H, 0),
+        T * H * 8, n)
+    del dy, res
     # --- RoPE on [T, heads, 128]
     d = 128
     qs = [torch.randn(T, a.heads, d, device=dev).bfloat16() for _ in range(n)]

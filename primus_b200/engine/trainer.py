@@ -81,6 +81,8 @@ class TrainConfig:
     dump_pp_data: bool = False         # per-node pipeline timeline (one JSON per pipeline rank and iteration; it
     pp_dump_dir: Optional[str] = None  # synchronises after every node, so the timed iterations are slower)
     pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
+    timing_log_level: int = 0          # 0: no step timers; 1: forward-backward / optimizer ...; 2: + batch staging
+    timing_log_option: str = "minmax"  # max | minmax | all (how the per-rank times are reported)
     use_torch_fsdp2: bool = False      # shard parameters / gradients / optimizer state over the data-parallel ranks
     use_precision_aware_optimizer: bool = False   # Adam moments in exp_avg_dtype / exp_avg_sq_dtype ("fp32" | "bf16")
     exp_avg_dtype: str = "fp32"
@@ -303,6 +305,9 @@ class Trainer:
         self.loss_accum = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.last_metrics: dict = {}
         self._gc_disabled = False
+        from .timers import Timers
+
+        self.timers = Timers(train_cfg.timing_log_level, train_cfg.timing_log_option, self.is_cuda)
 
     # ------------------------------------------------------------------ one micro-batch
     def _loss_weights(self, batch: dict) -> torch.Tensor:
@@ -407,9 +412,11 @@ class Trainer:
     # ------------------------------------------------------------------ step
     def train_step(self) -> torch.Tensor:
         """One optimizer step. Returns the (device) mean loss of this rank's micro-batches."""
-        micro_batches = self.stager.next_step()
-        if self.st.cp > 1:
-            micro_batches = [self._cp_shard(mb) for mb in micro_batches]
+        timers = self.timers
+        with timers("batch-generator", 2):
+            micro_batches = self.stager.next_step()
+            if self.st.cp > 1:
+                micro_batches = [self._cp_shard(mb) for mb in micro_batches]
         if self.st.pp > 1 and self.tcfg.pp_warmup and not getattr(self, "_pp_warmed", False):
             from ..parallel.pipeline import pipeline_warmup
 
@@ -419,6 +426,7 @@ class Trainer:
             buf.zero_grad()
         if self.fsdp:
             self.optimizer.zero_grad()
+        timers("forward-backward", 1).start()
         if self.st.pp > 1:
             from ..parallel.pipeline import run_pipeline_schedule
 
@@ -434,18 +442,23 @@ class Trainer:
                               self.iteration + 1, {"schedule": self.tcfg.pipeline_schedule, "pp": self.st.pp})
         else:
             loss = self.forward_backward_no_pipelining(micro_batches)
+        timers("forward-backward", 1).stop()
         self.stager.prefetch()  # stage the next step's batch while the optimizer runs
         if not self.fsdp:
-            self._pre_sync_sp_norm_grads()
-            self.finalize_grads()
+            with timers("all-grads-sync", 1):
+                self._pre_sync_sp_norm_grads()
+                self.finalize_grads()
+        timers("optimizer", 1).start()
         lr = self.scheduler.get_lr(self.iteration + 1)
         if getattr(self, "lora", None) is not None:  # adapter-only training: base weights stay frozen
             self.optimizer.compute_grad_norm()
             self.lora.optimizer_step(lr)
         else:
             self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+        timers("optimizer", 1).stop()
         self.scheduler.step()
         self.iteration += 1
+        self._steps_since_timer_log = getattr(self, "_steps_since_timer_log", 0) + 1
         return loss
 
     def reduced_loss(self, loss: torch.Tensor) -> float:
@@ -625,6 +638,11 @@ class Trainer:
                 f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
                 f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
                 f"lm loss: {loss:.6E} | grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
+        if tc.timing_log_level > 0:
+            text = self.timers.log(normalizer=max(getattr(self, "_steps_since_timer_log", 1), 1))
+            self._steps_since_timer_log = 0
+            if text and (st.rank == st.world_size - 1 or st.world_size == 1):
+                self.log(text)
 
     # ------------------------------------------------------------------ checkpoint
     def save_checkpoint(self, path: Optional[str] = None):

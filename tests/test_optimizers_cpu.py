@@ -185,3 +185,28 @@ def test_precision_aware_optimizer_keeps_bf16_moments():
     assert tr32.optimizer.state[0]["m"].dtype == torch.float32
     assert all(abs(a - b) < 0.05 for a, b in zip(l32, l16)), (l32, l16)
     assert l16[-1] < l16[0] - 0.3
+
+
+def test_step_timers_report_per_phase_times():
+    logs = []
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc = TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=128,
+                           params_dtype="fp32", seq_length=32)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=32, train_iters=2, log_interval=1,
+                     timing_log_level=2, timing_log_option="minmax")
+    Trainer(mc, tc, device="cpu", log_fn=logs.append).train()
+    text = "\\n".join(logs)
+    assert "(min, max) time across ranks (ms):" in text
+    for name in ("forward-backward", "optimizer", "all-grads-sync", "batch-generator"):
+        assert name in text, name
+    quiet = []
+    tc.timing_log_level = 0
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    Trainer(mc, tc, device="cpu", log_fn=quiet.append).train()
+    assert "time across ranks" not in "\\n".join(quiet)

@@ -632,12 +632,19 @@ class Trainer:
         self.last_metrics = dict(iteration=self.iteration, loss=loss, ms=dt * 1e3, tokens_per_s_gpu=tps_gpu,
                                  tokens_per_s_gpu_avg=avg, tflops_gpu=tflops, grad_norm=gn, mem_gib=mem,
                                  lr=self.scheduler.get_lr(self.iteration))
+        aux = [m_.last_aux_loss for mc_ in self.model_chunks for m_ in mc_.modules()
+               if getattr(m_, "last_aux_loss", None) is not None]
+        moe_text = ""
+        if aux:   # per-layer load-balancing losses of the last micro-batch, averaged over this rank's MoE layers
+            v = float(torch.stack([a.detach().float().reshape(()) for a in aux]).mean().item())
+            self.last_metrics["load_balancing_loss"] = v
+            moe_text = f" load balancing loss: {v:.6E} |"
         if st.rank == st.world_size - 1 or st.world_size == 1:
             self.log(
                 f" iteration {self.iteration:8d}/{tc.train_iters:8d} | elapsed time per iteration (ms): {dt * 1e3:.1f} | "
                 f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
                 f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
-                f"lm loss: {loss:.6E} | grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
+                f"lm loss: {loss:.6E} |{moe_text} grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
         if tc.timing_log_level > 0:
             text = self.timers.log(normalizer=max(getattr(self, "_steps_since_timer_log", 1), 1))
             self._steps_since_timer_log = 0

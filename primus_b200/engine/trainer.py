@@ -456,6 +456,15 @@ class Trainer:
         else:
             self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
         timers("optimizer", 1).stop()
+        if self.mcfg.moe_router_enable_expert_bias:
+            st = self.st
+            groups = [st.dp_cp_group if st.cp > 1 else st.dp_group]
+            if self.mcfg.sequence_parallel and st.tp > 1:
+                groups.append(st.tp_group)
+            for chunk in self.model_chunks:
+                for mod in chunk.modules():
+                    if hasattr(mod, "update_expert_bias"):
+                        mod.update_expert_bias(groups)
         self.scheduler.step()
         self.iteration += 1
         self._steps_since_timer_log = getattr(self, "_steps_since_timer_log", 0) + 1

@@ -58,6 +58,7 @@ class TransformerConfig:
     moe_router_score_function: str = "softmax"  # softmax | sigmoid
     moe_router_pre_softmax: bool = False
     moe_router_enable_expert_bias: bool = False
+    moe_router_bias_update_rate: float = 1e-3      # aux-loss-free balancing: bias += rate * sign(mean load - load)
     moe_router_num_groups: Optional[int] = None
     moe_router_group_topk: Optional[int] = None
     moe_router_topk_scaling_factor: Optional[float] = None

@@ -54,6 +54,9 @@ class MoELayer(nn.Module):
         self.router = ParamHolder(weight=_param((E, H), std, dt, device))
         if cfg.moe_router_enable_expert_bias:
             self.router.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
+            # tokens routed to every expert since the last bias update (this rank's tokens)
+            self.router.register_buffer("local_tokens_per_expert", torch.zeros(E, dtype=torch.float32, device=device),
+                                        persistent=False)
         # every EP rank draws the full expert set from the same stream and keeps its slice, so that the
         # initial weights do not depend on the EP size
         g = torch.Generator(device="cpu").manual_seed(977 + 31 * layer_idx)
@@ -86,6 +89,8 @@ class MoELayer(nn.Module):
             idx = (torch.arange(T * k, device=y.device) % cfg.num_experts).view(T, k)
             probs = torch.full_like(probs, 1.0 / k)
             counts = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(torch.int32)
+        if bias is not None and torch.is_grad_enabled():
+            self.router.local_tokens_per_expert += counts.float()
         aux = None
         if cfg.moe_aux_loss_coeff and cfg.moe_router_load_balancing_type in ("aux_loss", "seq_aux_loss") \
                 and torch.is_grad_enabled():
@@ -96,6 +101,22 @@ class MoELayer(nn.Module):
             probs = AuxLossScaler.apply(probs, aux)
             self.last_aux_loss = aux.detach()
         return probs, idx, counts
+
+    @torch.no_grad()
+    def update_expert_bias(self, groups=()) -> None:
+        """Auxiliary-loss-free load balancing (DeepSeek-V3): after an optimizer step every expert's selection bias moves
+        by ``moe_router_bias_update_rate`` towards the mean load, using the token counts of the whole global batch
+        (``groups``: the process groups whose ranks saw different tokens).  The reference takes this from Megatron's
+        router (``moe_router_enable_expert_bias`` / ``moe_router_bias_update_rate`` in its DeepSeek-V3 presets)."""
+        r = self.router
+        if not hasattr(r, "expert_bias") or not self.cfg.moe_router_bias_update_rate:
+            return
+        load = r.local_tokens_per_expert.clone()
+        for g in groups:
+            if g is not None and torch.distributed.get_world_size(g) > 1:
+                torch.distributed.all_reduce(load, group=g)
+        r.expert_bias += self.cfg.moe_router_bias_update_rate * torch.sign(load.mean() - load)
+        r.local_tokens_per_expert.zero_()
 
     def experts_forward(self, x_perm, probs_perm, sched):
         cfg = self.cfg

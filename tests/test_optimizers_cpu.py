@@ -210,3 +210,32 @@ def test_step_timers_report_per_phase_times():
     ps.initialize_model_parallel()
     Trainer(mc, tc, device="cpu", log_fn=quiet.append).train()
     assert "time across ranks" not in "\\n".join(quiet)
+
+
+def test_expert_bias_moves_towards_balanced_load():
+    """moe_router_enable_expert_bias: after every step the bias of over-used experts goes down and that of
+    under-used ones up by the update rate, and the token counter restarts."""
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=1, moe=True)
+    mc.moe_router_enable_expert_bias, mc.moe_router_score_function = True, "sigmoid"
+    mc.moe_router_bias_update_rate = 0.01
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    layer = next(m for m in tr.model.modules() if hasattr(m, "update_expert_bias"))
+    seen = {}
+    orig = layer.update_expert_bias
+
+    def spy(groups=()):
+        seen["load"] = layer.router.local_tokens_per_expert.clone()
+        orig(groups)
+
+    layer.update_expert_bias = spy
+    tr.train()
+    load, bias = seen["load"], layer.router.expert_bias
+    assert load.sum() == 4 * 32 * mc.moe_router_topk            # every routed copy of the global batch was counted
+    assert torch.equal(bias, 0.01 * torch.sign(load.mean() - load))
+    assert layer.router.local_tokens_per_expert.abs().sum() == 0

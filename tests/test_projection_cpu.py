@@ -123,3 +123,14 @@ def test_tuner_ranks_only_legal_plans_that_fit():
     cfg8 = TransformerConfig.from_dict(load_preset("llama3.1_8B", "models"))
     res8 = tuner.search(cfg8, hw, world=8, global_batch=128, seq=8192, top=1000)
     assert any((c.plan.tp, c.plan.pp, c.plan.cp) == (1, 1, 1) for c in res8["best"])
+
+
+def test_model_stats_reproduce_known_parameter_counts():
+    from primus_b200.tools import model_stats
+
+    rows = {r["model"]: r for r in model_stats.main(["--model", "llama3.1_8B", "qwen3_30B_A3B", "deepseek_v3",
+                                                     "mixtral_8x7B_v0.1", "--json"])}
+    assert abs(rows["llama3.1_8B"]["params_B"] - 8.03) < 0.02
+    assert abs(rows["qwen3_30B_A3B"]["params_B"] - 30.5) < 0.1 and abs(rows["qwen3_30B_A3B"]["active_params_B"] - 3.3) < 0.1
+    assert abs(rows["deepseek_v3"]["params_B"] - 671) < 2 and abs(rows["deepseek_v3"]["active_params_B"] - 37.5) < 0.5
+    assert abs(rows["mixtral_8x7B_v0.1"]["params_B"] - 46.7) < 0.1

@@ -222,8 +222,8 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); dp = gpus / tp")
     ap.add_argument("--cp", type=int, default=1, help="context-parallel size; dp = gpus / (tp * cp)")
-    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather"],
-                    help="context-parallel scheme: all-to-all over heads (Ulysses) or K/V all-gather with zig-zag chunks")
+    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather", "p2p"],
+                    help="context-parallel scheme: all-to-all over heads (Ulysses), K/V all-gather with zig-zag chunks, or ring (p2p)")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
     ap.add_argument("--precision", default="mxfp8", choices=["bf16", "mxfp8"],

@@ -331,7 +331,7 @@ class Trainer:
             return mb
         b, S = mb["tokens"].shape
         dev = mb["tokens"].device
-        if getattr(self.mcfg, "cp_comm_type", "a2a") == "allgather":
+        if getattr(self.mcfg, "cp_comm_type", "a2a") in ("allgather", "p2p"):
             assert S % (2 * st.cp) == 0, "sequence length must divide by 2 x the context-parallel size"
             c = S // (2 * st.cp)
             if self.is_cuda:

@@ -95,9 +95,13 @@ class SelfAttention(nn.Module):
             ctx_out = layers.allgather_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group,
                                                          st.cp, rot_dim=int(d * cfg.rotary_percent), causal=True,
                                                          scale=scale)
+        elif st.cp > 1 and cfg.cp_comm_type == "p2p":
+            ctx_out = layers.ring_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
+                                                    rot_dim=int(d * cfg.rotary_percent), scale=scale)
         elif st.cp > 1:
             if cfg.cp_comm_type != "a2a":
-                raise NotImplementedError(f"cp_comm_type {cfg.cp_comm_type!r}: only a2a (Ulysses) and allgather are built")
+                raise NotImplementedError(f"cp_comm_type {cfg.cp_comm_type!r}: a2a (Ulysses), allgather and p2p (ring) "
+                                          "are built")
             ctx_out = layers.ulysses_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
                                                     rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         else:

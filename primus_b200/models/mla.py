@@ -126,10 +126,15 @@ class MLASelfAttention(nn.Module):
         v = kv[..., dn:].contiguous()
         st = ps.get_state()
         if st.cp > 1:
-            if cfg.cp_comm_type != "allgather":
-                raise NotImplementedError("multi-latent attention under context parallelism needs cp_comm_type: allgather")
-            ctx_out = layers.allgather_cp_attention(q_full.contiguous(), k_full.contiguous(), v, batch, st.cp_group, st.cp,
-                                                    True, self.softmax_scale)
+            if cfg.cp_comm_type == "p2p":
+                ctx_out = layers.ring_cp_attention(q_full.contiguous(), k_full.contiguous(), v, batch, st.cp_group, st.cp,
+                                                   self.softmax_scale)
+            elif cfg.cp_comm_type != "allgather":
+                raise NotImplementedError("multi-latent attention under context parallelism needs cp_comm_type "
+                                          "allgather or p2p")
+            else:
+                ctx_out = layers.allgather_cp_attention(q_full.contiguous(), k_full.contiguous(), v, batch, st.cp_group,
+                                                        st.cp, True, self.softmax_scale)
         else:
             ctx_out = attention.flash_attention(q_full, k_full, v, batch, True, self.softmax_scale)
         out = gemm.linear(ctx_out.reshape(T, nh * dv), self.linear_proj.weight)

@@ -608,3 +608,166 @@ def allgather_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group,
         k = rope_fn(k, cos, sin, pos, rot_dim or d)
     out = allgather_cp_attention(q.contiguous(), k.contiguous(), v.contiguous(), batch, cp_group, cp, causal, scale)
     return out.reshape(Tl, hq * d)
+
+
+# ----------------------------------------------------------------------------------------------
+# Context parallelism (ring / p2p): K / V blocks travel around the ring, partial results are merged by log-sum-exp
+def _block_fwd(q, k, v, causal, scale):
+    """(o, lse [Hq, c]) of one query chunk against one key chunk (same length), fp32 merge inputs."""
+    if q.is_cuda:
+        o, lse = attention.flash_attn_fwd(q, k, v, 1, causal, scale)
+    else:
+        o, lse = attention.attention_ref(q, k, v, 1, causal, scale)
+    return o.float(), lse[0].float()
+
+
+def _block_bwd(do, q, k, v, o, lse, causal, scale):
+    """Gradients of one (query chunk, key chunk) block given the *final* output and log-sum-exp of the query rows
+    (p = exp(s - lse) is then the block's share of the full softmax)."""
+    if q.is_cuda:
+        return attention.flash_attn_bwd(do, q, k, v, o, lse.unsqueeze(0).contiguous(), 1, causal, scale)
+    c, hq, d = q.shape
+    hkv = k.shape[1]
+    g = hq // hkv
+    qf, dof, of = q.float().permute(1, 0, 2), do.float().permute(1, 0, 2), o.float().permute(1, 0, 2)   # [Hq, c, d]
+    kf = k.float().permute(1, 0, 2).repeat_interleave(g, 0)
+    vf = v.float().permute(1, 0, 2).repeat_interleave(g, 0)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(c, k.shape[0], dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    p = torch.exp(s - lse.float().unsqueeze(-1))
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    dk = dk.view(hkv, g, -1, d).sum(1)
+    dv = dv.view(hkv, g, -1, v.shape[2]).sum(1)
+    return dq.permute(1, 0, 2).to(q.dtype), dk.permute(1, 0, 2).to(k.dtype), dv.permute(1, 0, 2).to(v.dtype)
+
+
+def _ring_exchange(send: torch.Tensor, group, cp: int, rank: int):
+    """Starts sending ``send`` to the next rank of the ring and receiving the previous rank's buffer; returns
+    (recv tensor, requests)."""
+    ranks = torch.distributed.get_process_group_ranks(group)
+    nxt, prv = ranks[(rank + 1) % cp], ranks[(rank - 1) % cp]
+    recv = torch.empty_like(send)
+    ops = [torch.distributed.P2POp(torch.distributed.isend, send, nxt, group),
+           torch.distributed.P2POp(torch.distributed.irecv, recv, prv, group)]
+    return recv, torch.distributed.batch_isend_irecv(ops)
+
+
+class RingCPAttentionFn(torch.autograd.Function):
+    """Causal self-attention under ring context parallelism (``cp_comm_type: p2p``, the reference's default, which it
+    takes from Transformer-Engine; primus/configs/models/megatron/language_model.yaml:151-153).
+
+    Zig-zag layout as in the all-gather scheme (chunks ``rank`` and ``2 cp - 1 - rank`` per sequence).  The packed
+    K / V buffer of every rank travels once around the ring; at each of the ``cp`` steps a rank attends its two query
+    chunks to the two key chunks it currently holds (a full block when the key chunk is earlier, the causal diagonal
+    when it is the same chunk, nothing when it is later) while the next buffer is already in flight, and merges the
+    partial outputs through their log-sum-exp.  The backward sends the K / V buffer around again together with its
+    gradient buffer, which returns to its owner after the last step."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, batch, group, cp, rank, scale):
+        Tl, hq, dqk = q.shape
+        hkv, dv = k.shape[1], v.shape[2]
+        c = Tl // batch // 2
+        mine = zigzag_chunk_ids(cp, rank)
+        kv = torch.cat([k.reshape(Tl, hkv * dqk), v.reshape(Tl, hkv * dv)], dim=1).contiguous()
+        o = torch.zeros(Tl, hq, dv, dtype=torch.float32, device=q.device)
+        lse = torch.full((hq, Tl), float("-inf"), dtype=torch.float32, device=q.device)
+        cur = kv
+        for s in range(cp):
+            nxt, reqs = (None, [])
+            if s + 1 < cp:
+                nxt, reqs = _ring_exchange(cur, group, cp, rank)
+            theirs = zigzag_chunk_ids(cp, (rank - s) % cp)
+            kc = cur[:, : hkv * dqk].unflatten(1, (hkv, dqk))
+            vc = cur[:, hkv * dqk:].unflatten(1, (hkv, dv))
+            for b in range(batch):
+                for qs, qi in enumerate(mine):
+                    for ks, kj in enumerate(theirs):
+                        if kj > qi:
+                            continue
+                        r0, k0 = (b * 2 + qs) * c, (b * 2 + ks) * c
+                        ob, lb = _block_fwd(q[r0:r0 + c], kc[k0:k0 + c], vc[k0:k0 + c], kj == qi, scale)
+                        old = lse[:, r0:r0 + c]
+                        new = torch.logaddexp(old, lb)
+                        w_old = torch.exp(old - new).t().unsqueeze(-1)           # [c, Hq, 1]
+                        w_new = torch.exp(lb - new).t().unsqueeze(-1)
+                        o[r0:r0 + c] = o[r0:r0 + c] * w_old + ob * w_new
+                        lse[:, r0:r0 + c] = new
+            for r in reqs:
+                r.wait()
+            cur = nxt if nxt is not None else cur
+        out = o.to(q.dtype)
+        ctx.save_for_backward(q, kv, out, lse)
+        ctx.meta = (batch, group, cp, rank, scale, hkv, dqk, dv, c)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, kv, o, lse = ctx.saved_tensors
+        batch, group, cp, rank, scale, hkv, dqk, dv, c = ctx.meta
+        Tl = q.shape[0]
+        mine = zigzag_chunk_ids(cp, rank)
+        do = do.contiguous()
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        # the travelling buffer: [K | V | dK | dV] (gradients in fp32 precision would double the traffic; they are
+        # accumulated in fp32 locally and travel in the compute dtype, as the activations do)
+        W = hkv * (dqk + dv)
+        cur_kv = kv
+        cur_d = torch.zeros(Tl, W, dtype=torch.float32, device=q.device)
+        for s in range(cp):
+            theirs = zigzag_chunk_ids(cp, (rank - s) % cp)
+            kc = cur_kv[:, : hkv * dqk].unflatten(1, (hkv, dqk))
+            vc = cur_kv[:, hkv * dqk:].unflatten(1, (hkv, dv))
+            nxt_kv, reqs = (None, [])
+            if s + 1 < cp:
+                nxt_kv, reqs = _ring_exchange(cur_kv, group, cp, rank)
+            for b in range(batch):
+                for qs, qi in enumerate(mine):
+                    for ks, kj in enumerate(theirs):
+                        if kj > qi:
+                            continue
+                        r0, k0 = (b * 2 + qs) * c, (b * 2 + ks) * c
+                        dqb, dkb, dvb = _block_bwd(do[r0:r0 + c], q[r0:r0 + c], kc[k0:k0 + c], vc[k0:k0 + c],
+                                                   o[r0:r0 + c], lse[:, r0:r0 + c], kj == qi, scale)
+                        dq[r0:r0 + c] += dqb.float()
+                        cur_d[k0:k0 + c, : hkv * dqk] += dkb.reshape(c, hkv * dqk).float()
+                        cur_d[k0:k0 + c, hkv * dqk:] += dvb.reshape(c, hkv * dv).float()
+            for r in reqs:
+                r.wait()
+            # the gradient buffer follows the K / V buffer: after this step it goes to the next rank, which holds
+            # the same K / V block next; after the last step it goes one more hop and is home
+            send_d = cur_d
+            cur_d, dreqs = _ring_exchange(send_d, group, cp, rank)
+            for r in dreqs:
+                r.wait()
+            cur_kv = nxt_kv if nxt_kv is not None else cur_kv
+        dkv = cur_d
+        dk = dkv[:, : hkv * dqk].reshape(Tl, hkv, dqk).to(q.dtype)
+        dv_ = dkv[:, hkv * dqk:].reshape(Tl, hkv, dv).to(q.dtype)
+        return dq.to(q.dtype), dk, dv_, None, None, None, None, None
+
+
+def ring_cp_attention(q, k, v, batch, cp_group, cp, scale=None):
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    rank = torch.distributed.get_rank(cp_group)
+    return RingCPAttentionFn.apply(q, k, v, batch, cp_group, cp, rank, scale)
+
+
+def ring_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group, cp, rot_dim=None, scale=None):
+    """Packed-QKV form of :func:`ring_cp_attention` (RoPE with the global positions of the local tokens)."""
+    Tl = qkv.shape[0]
+    q = qkv[:, : hq * d].reshape(Tl, hq, d)
+    k = qkv[:, hq * d: (hq + hkv) * d].reshape(Tl, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(Tl, hkv, d)
+    if cos is not None:
+        rope_fn = fused.rope if qkv.is_cuda else fused.rope_ref
+        q = rope_fn(q, cos, sin, pos, rot_dim or d)
+        k = rope_fn(k, cos, sin, pos, rot_dim or d)
+    out = ring_cp_attention(q.contiguous(), k.contiguous(), v.contiguous(), batch, cp_group, cp, scale)
+    return out.reshape(Tl, hq * d)

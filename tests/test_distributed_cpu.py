@@ -47,13 +47,16 @@ CASES = {
     "cp2_pp2": dict(world=4, kw=dict(cp=2, pp=2)),
     "cp2_allgather": dict(world=2, kw=dict(cp=2, cp_comm="allgather")),
     "cp2_allgather_mla": dict(world=2, kw=dict(cp=2, cp_comm="allgather", mla=True)),
+    "cp2_ring": dict(world=2, kw=dict(cp=2, cp_comm="p2p")),
+    "cp4_ring_mla": dict(world=4, kw=dict(cp=4, cp_comm="p2p", mla=True, seq=64)),
 }
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_parallel_matches_single_process(name, tmp_path):
     case = CASES[name]
-    kw = dict(seq=32, gbs=8, mbs=2, iters=3, layers=4, **case["kw"])
+    kw = dict(seq=32, gbs=8, mbs=2, iters=3, layers=4)
+    kw.update(case["kw"])
     ref, mck = _single(kw)
     out = tmp_path / "losses.json"
     run_ranks(W.train_worker, case["world"], "gloo", args=(kw, mck, str(out)), timeout=240)

@@ -282,9 +282,9 @@ def main() -> int:
     if args.mem_fraction:
         torch.cuda.set_per_process_memory_fraction(args.mem_fraction, local_rank)
     # One GPU holds all optimizer state of the 8B model (the peak is ~174 of 179 GiB): if the warm-up runs out of
-    # memory, retry with full activation recomputation of the first 4, then 8, layers and say so in `config`.
+    # memory, retry with full activation recomputation of the first 4, 8, then 16 layers and say so in `config`.
     recomputed = 0
-    for attempt in range(3):
+    for attempt in range(4):
         trainer = None
         try:
             trainer = Trainer(mcfg, tcfg, device=f"cuda:{local_rank}", log_fn=lambda s: None)
@@ -294,9 +294,9 @@ def main() -> int:
             break
         except torch.OutOfMemoryError:
             gc.enable()
-            if world > 1 or attempt == 2:
+            if world > 1 or attempt == 3:
                 raise
-            recomputed = 4 * (attempt + 1)
+            recomputed = 4 << attempt
             print(f"[bench] out of memory during warm-up: retrying with recomputation of {recomputed} layers",
                   file=sys.stderr)
         del trainer

@@ -60,6 +60,9 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // ------------------------------------------------------------------ RMSNorm forward
 // y = (x [+ res]) * rstd * w ; optionally writes the summed residual stream to xsum.
 constexpr int RN_THREADS = 256;
+// One row per CTA; VPT 16-byte vectors per thread stay in registers between the sum-of-squares pass and the scaling
+// pass, so every operand is read from memory exactly once.
+template <int VPT>
 __global__ void __launch_bounds__(RN_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
@@ -71,36 +74,51 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const Bf8* rr = res ? reinterpret_cast<const Bf8*>(res + row * ldx) : nullptr;
   Bf8* sr = xsum ? reinterpret_cast<Bf8*>(xsum + row * ldx) : nullptr;
   const int nv = H / 8;
+  float f[VPT][8];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < nv; i += RN_THREADS) {
-    float f[8];
-    bf8_to_f(xr[i], f);
-    if (rr) {
-      float g[8];
-      bf8_to_f(rr[i], g);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] += g[j];
-      Bf8 s = f_to_bf8(f);
-      sr[i] = s;
-      bf8_to_f(s, f);  // normalise exactly what later layers will read
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * RN_THREADS;
+    if (i < nv) {
+      bf8_to_f(xr[i], f[k]);
+      if (rr) {
+        float g[8];
+        bf8_to_f(rr[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[k][j] += g[j];
+        Bf8 s = f_to_bf8(f[k]);
+        sr[i] = s;
+        bf8_to_f(s, f[k]);  // normalise exactly what later layers will read
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[k][j] * f[k][j];
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
   }
   ss = block_sum<RN_THREADS>(ss, red);
   const float rstd = rsqrtf(ss / H + eps);
   if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
-  const Bf8* src = rr ? reinterpret_cast<const Bf8*>(sr) : xr;
   const Bf8* wr = reinterpret_cast<const Bf8*>(w);
   Bf8* yr = reinterpret_cast<Bf8*>(y + row * ldy);
-  for (int i = threadIdx.x; i < nv; i += RN_THREADS) {
-    float f[8], g[8];
-    bf8_to_f(src[i], f);
-    bf8_to_f(wr[i], g);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j];
-    yr[i] = f_to_bf8(f);
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * RN_THREADS;
+    if (i < nv) {
+      float g[8];
+      bf8_to_f(wr[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[k][j] = f[k][j] * rstd * g[j];
+      yr[i] = f_to_bf8(f[k]);
+    }
   }
+}
+
+template <typename... Args>
+void launch_rmsnorm_fwd(long rows, int H, cudaStream_t s, Args... args) {
+  const int vpt = (H / 8 + RN_THREADS - 1) / RN_THREADS;
+  if (vpt <= 1) rmsnorm_fwd_kernel<1><<<(unsigned)rows, RN_THREADS, 0, s>>>(args...);
+  else if (vpt == 2) rmsnorm_fwd_kernel<2><<<(unsigned)rows, RN_THREADS, 0, s>>>(args...);
+  else if (vpt <= 4) rmsnorm_fwd_kernel<4><<<(unsigned)rows, RN_THREADS, 0, s>>>(args...);
+  else rmsnorm_fwd_kernel<8><<<(unsigned)rows, RN_THREADS, 0, s>>>(args...);
 }
 
 // ------------------------------------------------------------------ RMSNorm backward
@@ -647,11 +665,10 @@ extern "C" {
 
 int pb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xsum, float* rstd,
                    long rows, int H, long ldx, long ldy, float eps, cudaStream_t s) {
-  if (H % 8 || ldx % 8 || ldy % 8) return -2;
+  if (H % 8 || ldx % 8 || ldy % 8 || H > 8 * 8 * RN_THREADS) return -2;
   if (rows == 0) return 0;
-  rmsnorm_fwd_kernel<<<(unsigned)rows, RN_THREADS, 0, s>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-      (__nv_bfloat16*)xsum, rstd, H, ldx, ldy, eps);
+  launch_rmsnorm_fwd(rows, H, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                     (__nv_bfloat16*)y, (__nv_bfloat16*)xsum, rstd, H, ldx, ldy, eps);
   PB_CHECK_LAUNCH();
 }
 

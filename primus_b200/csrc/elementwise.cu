@@ -219,12 +219,83 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Rows wider than 8192 elements (up to 16384): 8 vectors per thread; the weight is re-read per row (L1-resident) and
+// nothing is prefetched, which keeps the kernel inside the register file.
+__global__ void __launch_bounds__(RN_THREADS, 1)
+rmsnorm_bwd_wide_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ partial, int rows, int H, long ldx, long lddy) {
+  constexpr int VPT = 8;
+  __shared__ float red[32];
+  const int nv = H / 8;
+  float dw[VPT][8];
+  const Bf8* wr = reinterpret_cast<const Bf8*>(w);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[k][j] = 0.f;
+  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const Bf8* dyr = reinterpret_cast<const Bf8*>(dy + row * lddy);
+    const Bf8* xr = reinterpret_cast<const Bf8*>(x + row * ldx);
+    const float rs = rstd[row];
+    float fx[VPT][8], fg[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * RN_THREADS;
+      if (i < nv) {
+        float wv[8];
+        bf8_to_f(xr[i], fx[k]);
+        bf8_to_f(dyr[i], fg[k]);
+        bf8_to_f(wr[i], wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dw[k][j] += fg[k][j] * fx[k][j] * rs;
+          fg[k][j] *= wv[j];
+          dot += fg[k][j] * fx[k][j];
+        }
+      }
+    }
+    dot = block_sum<RN_THREADS>(dot, red);
+    const float c = dot * rs * rs * rs / H;
+    Bf8* dxr = reinterpret_cast<Bf8*>(dx + row * ldx);
+    const Bf8* drr = dres ? reinterpret_cast<const Bf8*>(dres + row * ldx) : nullptr;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * RN_THREADS;
+      if (i < nv) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = fg[k][j] * rs - fx[k][j] * c;
+        if (drr) {
+          float r[8];
+          bf8_to_f(drr[i], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        dxr[i] = f_to_bf8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * RN_THREADS;
+    if (i < nv) {
+      float* p = partial + (long)blockIdx.x * H + (long)i * 8;
+      *reinterpret_cast<float4*>(p) = make_float4(dw[k][0], dw[k][1], dw[k][2], dw[k][3]);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(dw[k][4], dw[k][5], dw[k][6], dw[k][7]);
+    }
+  }
+}
+
 template <typename... Args>
 void launch_rmsnorm_bwd(int P, int H, cudaStream_t s, Args... args) {
   const int vpt = (H / 8 + RN_THREADS - 1) / RN_THREADS;
   if (vpt <= 1) rmsnorm_bwd_kernel<1><<<P, RN_THREADS, 0, s>>>(args...);
   else if (vpt == 2) rmsnorm_bwd_kernel<2><<<P, RN_THREADS, 0, s>>>(args...);
-  else rmsnorm_bwd_kernel<4><<<P, RN_THREADS, 0, s>>>(args...);
+  else if (vpt <= 4) rmsnorm_bwd_kernel<4><<<P, RN_THREADS, 0, s>>>(args...);
+  else rmsnorm_bwd_wide_kernel<<<P, RN_THREADS, 0, s>>>(args...);
 }
 
 // dw[h] (+)= sum_p partial[p, h]
@@ -679,7 +750,7 @@ int pb_rmsnorm_bwd_num_partials(long rows) { return (int)(rows < 592 ? (rows < 1
 int pb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                    void* dx, float* dw, float* scratch, long rows, int H, long ldx, long lddy,
                    int dw_accumulate, cudaStream_t s) {
-  if (H % 8 || ldx % 8 || lddy % 8 || H > 8192) return -2;
+  if (H % 8 || ldx % 8 || lddy % 8 || H > 16384) return -2;
   if (rows == 0) return 0;
   const int P = pb_rmsnorm_bwd_num_partials(rows);
   launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,

@@ -14,7 +14,7 @@ def _close(a, b, rtol=2e-2, atol=2e-2):
     assert err <= atol + rtol * b.abs().max().item(), f"err {err}"
 
 
-@pytest.mark.parametrize("H", [128, 256, 4096, 2048 + 64, 7168, 8192])
+@pytest.mark.parametrize("H", [128, 256, 4096, 2048 + 64, 7168, 8192, 16384])
 @pytest.mark.parametrize("with_res", [False, True])
 def test_rmsnorm(H, with_res):
     T = 300

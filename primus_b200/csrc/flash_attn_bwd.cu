@@ -93,8 +93,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
                       const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                       const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
                       const float* __restrict__ lse, const float* __restrict__ delta, int seq, int seq_k, int q_off,
-                      int hq, int hkv, float scale, int causal, int window_arg, int* status) {
+                      int hq, int hkv, float scale, int causal, int window_arg, float softcap_arg, int* status) {
   const int window = WIN ? window_arg : 0;   // the instantiation without a window carries no code for it
+  // softcap > 0: scores were softcap * tanh(scale * s / softcap) in the forward pass
+  const float softcap = WIN ? softcap_arg : 0.f;
+  const float cap_a = (WIN && softcap > 0.f) ? scale / softcap : 0.f;
   // seq: query rows per sequence, seq_k: key rows per sequence, q_off: key position of query row 0 (multiple of 128);
   // window > 0 (causal self-attention only): a query sees its last `window` keys, itself included
   using C = BwCfg<DQK, DV, MODE>;
@@ -307,14 +310,21 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
             float pv[4], dv[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              float p = pb::fast_exp2(fmaf(__uint_as_float(s[c + u]), sl2, -l2[u]));
+              float sv = __uint_as_float(s[c + u]);
+              float dcap = 1.f;
+              if (WIN && softcap > 0.f) {
+                const float t = pb::fast_tanh(sv * cap_a);
+                sv = t / cap_a;                  // = softcap * tanh(scale * s / softcap) / scale
+                dcap = 1.f - t * t;              // derivative of the capped score with respect to scale * s
+              }
+              float p = pb::fast_exp2(fmaf(sv, sl2, -l2[u]));
               if (DIAG) {
                 const int col_g = cs_rel * BC + c + u;
                 const int diff = (MODE == MODE_DKDV) ? (col_g - row_g) : (row_g - col_g);   // query - key position
                 if (diff < 0 || (window > 0 && diff >= window)) p = 0.f;
               }
               pv[u] = p;
-              dv[u] = p * (__uint_as_float(dp[c + u]) - dl[u]) * scale;
+              dv[u] = p * (__uint_as_float(dp[c + u]) - dl[u]) * scale * dcap;
             }
             pk[e4 / 2] = pb::pack_bf16x2(pv[0], pv[1]);
             pk[e4 / 2 + 1] = pb::pack_bf16x2(pv[2], pv[3]);
@@ -419,6 +429,7 @@ struct BwdArgs {
   float* delta;
   void *dq, *dk, *dv;
   int batch, seq, seq_k, q_off, window, hq, hkv;
+  float softcap;
   long q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row;
   float scale;
   int causal;
@@ -453,31 +464,31 @@ int launch_bwd(const BwdArgs& a) {
 #undef MK
   {
     using C = BwCfg<DQK, DV, MODE_DKDV>;
-    auto kern = a.window > 0 ? flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, false>;
+    auto kern = (a.window > 0 || a.softcap > 0.f) ? flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DKDV, false>;
     static bool attr_set[2] = {false, false};
-    if (!attr_set[a.window > 0]) {
+    if (!attr_set[a.window > 0 || a.softcap > 0.f]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      attr_set[a.window > 0] = true;
+      attr_set[a.window > 0 || a.softcap > 0.f] = true;
     }
     dim3 grid(a.hkv * a.batch, a.seq_k / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(k128, v128, q64, do64, dk_m, dv_m,
                                                        a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
-                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.status);
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.softcap, a.status);
   }
   {
     using C = BwCfg<DQK, DV, MODE_DQ>;
-    auto kern = a.window > 0 ? flash_attn_bwd_kernel<DQK, DV, MODE_DQ, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DQ, false>;
+    auto kern = (a.window > 0 || a.softcap > 0.f) ? flash_attn_bwd_kernel<DQK, DV, MODE_DQ, true> : flash_attn_bwd_kernel<DQK, DV, MODE_DQ, false>;
     static bool attr_set[2] = {false, false};
-    if (!attr_set[a.window > 0]) {
+    if (!attr_set[a.window > 0 || a.softcap > 0.f]) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
       if (e != cudaSuccess) return (int)e;
-      attr_set[a.window > 0] = true;
+      attr_set[a.window > 0 || a.softcap > 0.f] = true;
     }
     dim3 grid(a.hq * a.batch, a.seq / BR, 1);
     kern<<<grid, BW_THREADS, C::SMEM_BYTES, a.stream>>>(q128, do128, k64, v64, dq_m, dq_m,
                                                        a.delta + (long)a.batch * a.hq * a.seq, a.delta, a.seq, a.seq_k,
-                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.status);
+                                                       a.q_off, a.hq, a.hkv, a.scale, a.causal, a.window, a.softcap, a.status);
   }
   return (int)cudaGetLastError();
 }
@@ -486,21 +497,32 @@ int launch_bwd(const BwdArgs& a) {
 
 // Layouts as in pb_flash_attn_fwd_ex (q / o / d_o / dq: batch*seq rows; k / v / dk / dv: batch*seq_k rows).
 // delta: fp32 scratch [2, batch, hq, seq] (written here: row sums of dO*O, then the log-sum-exp in log2 units).
+extern "C" int pb_flash_attn_bwd_cap(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                     const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
+                                     int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row,
+                                     long v_row, long o_row, long do_row, long dq_row, long dk_row, long dv_row,
+                                     float scale, int causal, int window, float softcap, int* status,
+                                     cudaStream_t stream) {
+  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv) return -2;
+  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
+  if (window < 0 || (window > 0 && (!causal || q_off != 0)) || softcap < 0.f) return -2;
+  if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
+  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, window, hq, hkv, softcap, q_row, k_row,
+            v_row, o_row, do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
+  if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
+  if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
+  if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
+  return -3;
+}
+
 extern "C" int pb_flash_attn_bwd_win(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                                      const float* lse, float* delta, void* dq, void* dk, void* dv, int batch, int seq,
                                      int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row, long k_row,
                                      long v_row, long o_row, long do_row, long dq_row, long dk_row, long dv_row,
                                      float scale, int causal, int window, int* status, cudaStream_t stream) {
-  if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv) return -2;
-  if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
-  if (window < 0 || (window > 0 && (!causal || q_off != 0))) return -2;
-  if ((q_row | k_row | v_row | o_row | do_row | dq_row | dk_row | dv_row) % 8) return -2;
-  BwdArgs a{d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, window, hq, hkv, q_row, k_row, v_row,
-            o_row, do_row, dq_row, dk_row, dv_row, scale, causal, status, stream};
-  if (d_qk == 128 && d_v == 128) return launch_bwd<128, 128>(a);
-  if (d_qk == 192 && d_v == 128) return launch_bwd<192, 128>(a);
-  if (d_qk == 64 && d_v == 64) return launch_bwd<64, 64>(a);
-  return -3;
+  return pb_flash_attn_bwd_cap(d_o, q, k, v, o, lse, delta, dq, dk, dv, batch, seq, seq_k, q_off, hq, hkv, d_qk, d_v,
+                               q_row, k_row, v_row, o_row, do_row, dq_row, dk_row, dv_row, scale, causal, window, 0.f,
+                               status, stream);
 }
 
 extern "C" int pb_flash_attn_bwd_ex(const void* d_o, const void* q, const void* k, const void* v, const void* o,

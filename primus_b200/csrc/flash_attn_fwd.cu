@@ -69,10 +69,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                       float* __restrict__ lse, int seq, int seq_k, int q_off_blocks, int hq, int hkv,
-                      float scale_log2, int causal, int window_arg, const float* __restrict__ sinks_arg, int* status) {
+                      float scale_log2, int causal, int window_arg, const float* __restrict__ sinks_arg, float softcap_arg,
+                      int* status) {
   // WIN = false: the plain instantiation carries no code for windows or sinks
   const int window = WIN ? window_arg : 0;
   const float* sinks = WIN ? sinks_arg : nullptr;
+  // softcap > 0: scores become softcap * tanh(scale * s / softcap) before the softmax
+  const float softcap = WIN ? softcap_arg : 0.f;
   // seq: query rows per sequence; seq_k: key rows per sequence; query row i sits at key position
   // q_off_blocks * 128 + i (causal masking is relative to that position).  window > 0 (causal only): a query attends
   // to its last `window` keys, itself included.  sinks: optional per-query-head logit (natural-log units) that only
@@ -244,6 +247,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
       for (int c = 0; c < 4; ++c) pb::tmem_ld_32x32b_x32(t_s + c * 32, sr + c * 32);
       pb::tmem_wait_ld();
+      if (WIN && softcap > 0.f) {
+        // keep the later `s * scale_log2` form: store softcap * tanh(scale * s / softcap) / scale
+        const float scale = scale_log2 * 0.6931471805599453f;
+        const float a = scale / softcap, b = softcap / scale;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) sr[i] = __float_as_uint(b * pb::fast_tanh(__uint_as_float(sr[i]) * a));
+      }
       if (diag) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
@@ -364,7 +374,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 template <int DQK, int DV>
 int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq, int seq_k,
                int q_off, int hq, int hkv, long q_row, long k_row, long v_row, long o_row, float scale, int causal,
-               int window, const float* sinks, int* status, cudaStream_t stream) {
+               int window, const float* sinks, float softcap, int* status, cudaStream_t stream) {
   using C = FaCfg<DQK, DV>;
   const auto bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
@@ -376,7 +386,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
   if ((rc = pbh::make_tmap_3d(&tk, k, bf, 2, TK, hkv, DQK, DQK, k_row, BKV, 1, 64, sw))) return rc;
   if ((rc = pbh::make_tmap_3d(&tv, v, bf, 2, TK, hkv, DV, DV, v_row, BKV, 1, 64, sw))) return rc;
   if ((rc = pbh::make_tmap_3d(&to, o, bf, 2, T, hq, DV, DV, o_row, BQ, 1, 64, sw))) return rc;
-  const bool win = window > 0 || sinks != nullptr;
+  const bool win = window > 0 || sinks != nullptr || softcap > 0.f;
   auto kern = win ? flash_attn_fwd_kernel<DQK, DV, true> : flash_attn_fwd_kernel<DQK, DV, false>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[win]) {
@@ -386,7 +396,7 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
   }
   dim3 grid(hq * batch, (seq / BQ + 1) / 2, 1);
   kern<<<grid, FA_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, to, lse, seq, seq_k, q_off / BQ, hq, hkv,
-                                                   scale * 1.4426950408889634f, causal, window, sinks, status);
+                                                   scale * 1.4426950408889634f, causal, window, sinks, softcap, status);
   return (int)cudaGetLastError();
 }
 
@@ -397,25 +407,34 @@ int launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
 // are multiples of 128.  Query row i of a sequence sits at key position q_off + i: with `causal` it attends to keys
 // [0, q_off + i] (the last `window` of them when window > 0) and q_off + seq must equal seq_k (the layout of a
 // sequence chunk attending to the gathered prefix).  sinks: null or one fp32 logit per query head.
-extern "C" int pb_flash_attn_fwd_win(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+extern "C" int pb_flash_attn_fwd_cap(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
                                      int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
                                      long k_row, long v_row, long o_row, float scale, int causal, int window,
-                                     const float* sinks, int* status, cudaStream_t stream) {
+                                     const float* sinks, float softcap, int* status, cudaStream_t stream) {
   if (seq % 128 || seq_k % 128 || q_off % 128 || q_off < 0 || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) ||
       (o_row % 8))
     return -2;
   if (causal ? (q_off + seq != seq_k) : (q_off != 0)) return -2;
-  if (window < 0 || (window > 0 && (!causal || q_off != 0))) return -2;
+  if (window < 0 || (window > 0 && (!causal || q_off != 0)) || softcap < 0.f) return -2;
   if (d_qk == 128 && d_v == 128)
     return launch_fwd<128, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                                causal, window, sinks, status, stream);
+                                causal, window, sinks, softcap, status, stream);
   if (d_qk == 192 && d_v == 128)
     return launch_fwd<192, 128>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                                causal, window, sinks, status, stream);
+                                causal, window, sinks, softcap, status, stream);
   if (d_qk == 64 && d_v == 64)
     return launch_fwd<64, 64>(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, q_row, k_row, v_row, o_row, scale,
-                              causal, window, sinks, status, stream);
+                              causal, window, sinks, softcap, status, stream);
   return -3;
+}
+
+// No logit soft-capping.
+extern "C" int pb_flash_attn_fwd_win(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
+                                     int seq, int seq_k, int q_off, int hq, int hkv, int d_qk, int d_v, long q_row,
+                                     long k_row, long v_row, long o_row, float scale, int causal, int window,
+                                     const float* sinks, int* status, cudaStream_t stream) {
+  return pb_flash_attn_fwd_cap(q, k, v, o, lse, batch, seq, seq_k, q_off, hq, hkv, d_qk, d_v, q_row, k_row, v_row, o_row,
+                               scale, causal, window, sinks, 0.f, status, stream);
 }
 
 // No sliding window, no sinks.

@@ -92,7 +92,7 @@ class TransformerConfig:
     mtp_loss_scaling_factor: float = 0.1
     final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)
     router_logit_softcapping: float | None = None   # same on the MoE router logits
-    attn_logit_softcapping: float | None = None     # accepted for config parity; not supported by the attention kernels
+    attn_logit_softcapping: float | None = None     # cap * tanh(scores / cap) inside attention (not for MLA / context parallel)
 
     def layer_window(self, layer_idx: int) -> int:
         """Sliding-window width of a layer (0 = full attention)."""
@@ -108,8 +108,6 @@ class TransformerConfig:
         return width if f[layer_idx % len(f)] else 0
 
     def __post_init__(self):
-        if self.attn_logit_softcapping:
-            raise NotImplementedError("attn_logit_softcapping is not supported by the flash-attention kernels")
         if self.num_query_groups is None:
             self.num_query_groups = self.num_attention_heads
         if self.kv_channels is None:

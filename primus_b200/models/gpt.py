@@ -88,7 +88,7 @@ class SelfAttention(nn.Module):
         cos, sin, pos = rope[:3]
         segments = rope[3] if len(rope) > 3 else None
         scale = cfg.attention_softmax_scale
-        if st.cp > 1 and (self.window or self.has_sinks or segments):
+        if st.cp > 1 and (self.window or self.has_sinks or segments or cfg.attn_logit_softcapping):
             raise NotImplementedError("sliding-window / sink / per-document attention is not available under context "
                                       "parallelism")
         if st.cp > 1 and cfg.cp_comm_type == "allgather":
@@ -108,7 +108,8 @@ class SelfAttention(nn.Module):
             sinks = self.core_attention.softmax_offset.float() if self.has_sinks else None
             ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
                                             rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
-                                            window=self.window, sinks=sinks, segments=segments)
+                                            window=self.window, sinks=sinks, segments=segments,
+                                            softcap=cfg.attn_logit_softcapping or 0.0)
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 

@@ -105,6 +105,8 @@ class MLASelfAttention(nn.Module):
         seq = T // batch
         cos, sin = self.rope_tables(y.device, seq * ps.get_state().cp)   # positions are global under context parallelism
         pos = rope[2]
+        if cfg.attn_logit_softcapping:
+            raise NotImplementedError("attn_logit_softcapping is not built for multi-latent attention")
         if len(rope) > 3 and rope[3]:
             raise NotImplementedError("per-document attention (packed sequences) is not built for multi-latent attention")
         if cfg.q_lora_rank:

@@ -18,7 +18,7 @@ from . import _lib
 
 
 def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None = None, q_off: int = 0,
-                  window: int = 0, sinks=None):
+                  window: int = 0, sinks=None, softcap: float = 0.0):
     """fp32 reference. Returns (out [T,Hq,Dv], lse [B,Hq,S]).  ``k`` / ``v`` may hold more rows per sequence than ``q``
     (a sequence chunk attending to a gathered prefix): query row i then sits at key position ``q_off + i``.
     ``window`` > 0: a query sees its last ``window`` keys (itself included).  ``sinks`` [Hq]: a learned logit per head
@@ -33,6 +33,8 @@ def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None 
     kf = k.float().reshape(batch, SK, hkv, dqk).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     vf = v.float().reshape(batch, SK, hkv, dv).permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if softcap and softcap > 0:          # scores soft-capped before masking and softmax
+        s = softcap * torch.tanh(s / softcap)
     if causal:
         mask = torch.ones(S, SK, dtype=torch.bool, device=q.device).tril(diagonal=q_off)
         if window and window > 0:
@@ -51,7 +53,8 @@ def _check_view(t, d):
     assert t.data_ptr() % 16 == 0
 
 
-def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int = 0, window: int = 0, sinks=None):
+def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int = 0, window: int = 0, sinks=None,
+                   softcap: float = 0.0):
     T, hq, dqk = q.shape
     hkv, dv = k.shape[1], v.shape[2]
     S = T // batch
@@ -62,13 +65,14 @@ def flash_attn_fwd(q, k, v, batch: int, causal: bool, scale: float, q_off: int =
     lse = torch.empty(batch, hq, S, dtype=torch.float32, device=q.device)
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.numel() == hq and sinks.is_contiguous()
-    _lib.call("flash_attn_fwd_win", q, k, v, o, lse, batch, S, SK, int(q_off), hq, hkv, dqk, dv, q.stride(0), k.stride(0),
-              v.stride(0), o.stride(0), float(scale), int(causal), int(window or 0), sinks, _lib.status_word(q.device))
+    _lib.call("flash_attn_fwd_cap", q, k, v, o, lse, batch, S, SK, int(q_off), hq, hkv, dqk, dv, q.stride(0), k.stride(0),
+              v.stride(0), o.stride(0), float(scale), int(causal), int(window or 0), sinks, float(softcap or 0.0),
+              _lib.status_word(q.device))
     return o, lse
 
 
 def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, dq=None, dk=None, dv=None,
-                   q_off: int = 0, window: int = 0):
+                   q_off: int = 0, window: int = 0, softcap: float = 0.0):
     """Returns (dq, dk, dv); optional pre-allocated outputs may be strided views (packed dQKV)."""
     T, hq, dqk = q.shape
     hkv, dvd = k.shape[1], v.shape[2]
@@ -82,9 +86,10 @@ def flash_attn_bwd(do, q, k, v, o, lse, batch: int, causal: bool, scale: float, 
     for t, d in ((q, dqk), (k, dqk), (v, dvd), (o, dvd), (do, dvd), (dq, dqk), (dk, dqk), (dv, dvd)):
         _check_view(t, d)
     delta = torch.empty(2, batch, hq, S, dtype=torch.float32, device=q.device)  # [rowsum(dO*O), lse*log2e]
-    _lib.call("flash_attn_bwd_win", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, SK, int(q_off), hq, hkv, dqk, dvd,
+    _lib.call("flash_attn_bwd_cap", do, q, k, v, o, lse, delta, dq, dk, dv, batch, S, SK, int(q_off), hq, hkv, dqk, dvd,
               q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dq.stride(0), dk.stride(0),
-              dv.stride(0), float(scale), int(causal), int(window or 0), _lib.status_word(q.device))
+              dv.stride(0), float(scale), int(causal), int(window or 0), float(softcap or 0.0),
+              _lib.status_word(q.device))
     return dq, dk, dv
 
 
@@ -100,23 +105,24 @@ def sink_grad(do, o, lse, sinks, batch: int):
 
 class FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, batch, causal, scale, q_off=0, window=0, sinks=None):
-        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale, q_off, window, sinks)
+    def forward(ctx, q, k, v, batch, causal, scale, q_off=0, window=0, sinks=None, softcap=0.0):
+        o, lse = flash_attn_fwd(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)
         ctx.save_for_backward(q, k, v, o, lse, sinks if sinks is not None else torch.empty(0))
-        ctx.args = (batch, causal, scale, q_off, window, sinks is not None)
+        ctx.args = (batch, causal, scale, q_off, window, sinks is not None, softcap)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse, sinks = ctx.saved_tensors
-        batch, causal, scale, q_off, window, has_sinks = ctx.args
-        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale, q_off=q_off, window=window)
+        batch, causal, scale, q_off, window, has_sinks, softcap = ctx.args
+        dq, dk, dv = flash_attn_bwd(do, q, k, v, o, lse, batch, causal, scale, q_off=q_off, window=window,
+                                    softcap=softcap)
         ds = sink_grad(do, o, lse, sinks, batch) if has_sinks else None
-        return dq, dk, dv, None, None, None, None, None, ds
+        return dq, dk, dv, None, None, None, None, None, ds, None
 
 
 def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float | None = None, q_off: int = 0,
-                    window: int = 0, sinks=None):
+                    window: int = 0, sinks=None, softcap: float = 0.0):
     """softmax(scale * Q K^T [+ causal mask]) V, token-major layout (see module docstring).  With ``q_off`` the queries
     are a chunk of a longer sequence whose keys / values ``[0, q_off + S)`` are given (sequence lengths and ``q_off``
     multiples of 128): the building block of all-gather context parallelism.  ``window`` / ``sinks``: sliding-window
@@ -124,5 +130,5 @@ def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float |
     (primus/backends/megatron/core/extensions/primus_turbo.py:876-883,924-942)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not q.is_cuda:
-        return attention_ref(q, k, v, batch, causal, scale, q_off, window, sinks)[0]
-    return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off, window, sinks)
+        return attention_ref(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)[0]
+    return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)

@@ -293,7 +293,7 @@ class RopeAttentionFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale, window=0, sinks=None,
-                segments=None):
+                segments=None, softcap=0.0):
         T = qkv.shape[0]
         q = qkv[:, : hq * d].view(T, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
@@ -307,22 +307,22 @@ class RopeAttentionFn(torch.autograd.Function):
             o = torch.empty(T, hq, d, dtype=qkv.dtype, device=qkv.device)
             lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
             for a, b in segments:
-                ob, lb = attention.flash_attn_fwd(q[a:b], k[a:b], v[a:b], 1, causal, scale, 0, window, sinks)
+                ob, lb = attention.flash_attn_fwd(q[a:b], k[a:b], v[a:b], 1, causal, scale, 0, window, sinks, softcap)
                 o[a:b] = ob
                 lse[:, a:b] = lb[0]
         else:
-            o, lse = attention.flash_attn_fwd(q, k, v, batch, causal, scale, 0, window, sinks)
+            o, lse = attention.flash_attn_fwd(q, k, v, batch, causal, scale, 0, window, sinks, softcap)
         ctx.save_for_backward(qkv, o, lse, cos if cos is not None else torch.empty(0),
                               sin if sin is not None else torch.empty(0), pos if pos is not None else torch.empty(0),
                               sinks if sinks is not None else torch.empty(0))
         ctx.meta = (batch, hq, hkv, d, rot_dim, causal, scale, cos is not None, pos is not None, window,
-                    sinks is not None, segments)
+                    sinks is not None, segments, softcap)
         return o.view(T, hq * d)
 
     @staticmethod
     def backward(ctx, do):
         qkv, o, lse, cos, sin, pos, sinks = ctx.saved_tensors
-        batch, hq, hkv, d, rot_dim, causal, scale, has_rope, has_pos, window, has_sinks, segments = ctx.meta
+        batch, hq, hkv, d, rot_dim, causal, scale, has_rope, has_pos, window, has_sinks, segments, softcap = ctx.meta
         T = qkv.shape[0]
         q = qkv[:, : hq * d].view(T, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].view(T, hkv, d)
@@ -337,20 +337,21 @@ class RopeAttentionFn(torch.autograd.Function):
             for a, b in segments:
                 lb = lse[:, a:b].unsqueeze(0).contiguous()
                 attention.flash_attn_bwd(do3[a:b], q[a:b], k[a:b], v[a:b], o[a:b], lb, 1, causal, scale, dq=dq[a:b],
-                                         dk=dk[a:b], dv=dv[a:b], window=window)
+                                         dk=dk[a:b], dv=dv[a:b], window=window, softcap=softcap)
                 if has_sinks:
                     ds += attention.sink_grad(do3[a:b], o[a:b], lb, sinks, 1)
         else:
-            attention.flash_attn_bwd(do3, q, k, v, o, lse, batch, causal, scale, dq=dq, dk=dk, dv=dv, window=window)
+            attention.flash_attn_bwd(do3, q, k, v, o, lse, batch, causal, scale, dq=dq, dk=dk, dv=dv, window=window,
+                                     softcap=softcap)
             ds = attention.sink_grad(do3, o, lse, sinks, batch) if has_sinks else None
         if has_rope:
             dqk = dqkv[:, : (hq + hkv) * d].view(T, hq + hkv, d)
             fused.rope_inplace_(dqk, cos, sin, pos if has_pos else None, rot_dim, backward=True)
-        return dqkv, None, None, None, None, None, None, None, None, None, None, None, ds, None
+        return dqkv, None, None, None, None, None, None, None, None, None, None, None, ds, None, None
 
 
 def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=True, scale=None, window=0, sinks=None,
-                   segments=None):
+                   segments=None, softcap=0.0):
     """Self-attention on a packed QKV tensor; returns [T, Hq*D].  ``window`` > 0: sliding-window attention; ``sinks``
     (fp32 [Hq]): learned per-head sink logits; ``segments``: [(start, end)] row ranges of the documents packed into
     the token dimension (attention stays inside each; on CUDA every range must be a multiple of 128 rows)."""
@@ -365,12 +366,13 @@ def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=T
             q = fused.rope_ref(q, cos, sin, pos, rot_dim)
             k = fused.rope_ref(k, cos, sin, pos, rot_dim)
         if segments:
-            o = torch.cat([attention.attention_ref(q[a:b], k[a:b], v[a:b], 1, causal, scale, 0, window, sinks)[0]
+            o = torch.cat([attention.attention_ref(q[a:b], k[a:b], v[a:b], 1, causal, scale, 0, window, sinks, softcap)[0]
                            for a, b in segments], 0)
         else:
-            o = attention.attention_ref(q, k, v, batch, causal, scale, 0, window, sinks)[0]
+            o = attention.attention_ref(q, k, v, batch, causal, scale, 0, window, sinks, softcap)[0]
         return o.reshape(T, hq * d)
-    return RopeAttentionFn.apply(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale, window, sinks, segments)
+    return RopeAttentionFn.apply(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim, causal, scale, window, sinks, segments,
+                                 softcap or 0.0)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -166,3 +166,24 @@ def test_packed_document_attention_forward_backward():
     assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
     err = (qkv.grad.float().cpu() - ref_in.grad).abs().max().item()
     assert err <= 3e-2 * ref_in.grad.abs().max().item() + 2e-2, err
+
+
+@pytest.mark.parametrize("case", [(1, 384, 4, 2, 128, 0, 30.0), (1, 512, 2, 2, 128, 200, 20.0), (2, 256, 4, 1, 64, 0, 50.0)])
+def test_flash_attn_softcapped_scores(case):
+    batch, seq, hq, hkv, d, window, cap = case
+    q, k, v = _inputs(batch, seq, hq, hkv, d, d, seed=11)
+    q, k = (q * 3).detach(), (k * 3).detach()                 # large scores, so that the cap bites
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = A.flash_attention(q, k, v, batch, True, None, 0, window, None, cap)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = A.attention_ref(qr, kr, vr, batch, True, None, 0, window, None, cap)
+    o_ref.backward(do.float())
+    assert (o.float() - o_ref.float()).abs().max().item() <= 3e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        tol = 4e-2 * b.abs().max().item() + 3e-2
+        assert err <= tol, f"{name}: err {err} tol {tol}"

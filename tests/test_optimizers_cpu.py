@@ -92,7 +92,7 @@ def test_profiler_trace_and_metrics_jsonl(tmp_path):
 
 def test_logit_softcapping_bounds_the_logits_and_trains():
     """final_logit_softcapping: logits stay inside (-cap, cap) and the model still trains; the attention variant is
-    rejected because the attention kernels do not implement it."""
+    also available inside attention."""
     import pytest
 
     from primus_b200.models.config import TransformerConfig
@@ -102,8 +102,15 @@ def test_logit_softcapping_bounds_the_logits_and_trains():
     y = fused.softcap(x, 30.0)
     assert y.abs().max() < 30.0 and torch.allclose(y, torch.tanh(x / 30.0) * 30.0)
     assert fused.softcap(x, None) is x
-    with pytest.raises(NotImplementedError):
-        TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, attn_logit_softcapping=50.0)
+    # soft-capped attention scores: the reference path bounds them, and a huge cap reproduces plain attention
+    from primus_b200.ops import attention as A
+
+    q, k, v = torch.randn(32, 2, 16) * 4, torch.randn(32, 2, 16) * 4, torch.randn(32, 2, 16)
+    plain = A.attention_ref(q, k, v, 1, True)[0]
+    assert torch.allclose(A.attention_ref(q, k, v, 1, True, softcap=1e6)[0], plain, atol=1e-4)
+    assert not torch.allclose(A.attention_ref(q, k, v, 1, True, softcap=2.0)[0], plain, atol=1e-3)
+    cfg = TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, attn_logit_softcapping=50.0)
+    assert cfg.attn_logit_softcapping == 50.0
 
 
 def test_multi_token_prediction_adds_a_trained_auxiliary_loss():

@@ -298,14 +298,25 @@ void launch_rmsnorm_bwd(int P, int H, cudaStream_t s, Args... args) {
   else rmsnorm_bwd_wide_kernel<<<P, RN_THREADS, 0, s>>>(args...);
 }
 
-// dw[h] (+)= sum_p partial[p, h]
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                         int P, int H, int accumulate) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
+// dw[h] (+)= sum_p partial[p, h].  A CTA owns 32 columns; its 16 thread rows each add every 16th partial (coalesced
+// 128-byte reads) and a fixed-order tree in shared memory folds them, so the result does not depend on scheduling.
+constexpr int DWR_COLS = 32, DWR_ROWS = 16;
+__global__ void __launch_bounds__(DWR_COLS * DWR_ROWS)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int P, int H, int accumulate) {
+  __shared__ float red[DWR_ROWS][DWR_COLS + 1];
+  const int c = threadIdx.x % DWR_COLS, g = threadIdx.x / DWR_COLS;
+  const int h = blockIdx.x * DWR_COLS + c;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[(long)p * H + h];
-  dw[h] = accumulate ? dw[h] + s : s;
+  if (h < H)
+    for (int p = g; p < P; p += DWR_ROWS) s += partial[(long)p * H + h];
+  red[g][c] = s;
+  __syncthreads();
+#pragma unroll
+  for (int step = DWR_ROWS / 2; step > 0; step >>= 1) {
+    if (g < step) red[g][c] += red[g + step][c];
+    __syncthreads();
+  }
+  if (g == 0 && h < H) dw[h] = accumulate ? dw[h] + red[0][c] : red[0][c];
 }
 
 // ------------------------------------------------------------------ logit soft-capping
@@ -755,7 +766,7 @@ int pb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   const int P = pb_rmsnorm_bwd_num_partials(rows);
   launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
-  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
+  rmsnorm_dw_reduce_kernel<<<(H + DWR_COLS - 1) / DWR_COLS, DWR_COLS * DWR_ROWS, 0, s>>>(scratch, dw, P, H, dw_accumulate);
   PB_CHECK_LAUNCH();
 }
 
@@ -938,7 +949,7 @@ extern "C" int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   // every one of the P partial rows is fully written by its CTA before the reduction reads it
   launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
                      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, (int)rows, H, ldx, lddy);
-  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, P, H, dw_accumulate);
+  rmsnorm_dw_reduce_kernel<<<(H + DWR_COLS - 1) / DWR_COLS, DWR_COLS * DWR_ROWS, 0, s>>>(scratch, dw, P, H, dw_accumulate);
   return (int)cudaGetLastError();
 }
 

@@ -45,12 +45,13 @@ __device__ __forceinline__ long sf_offset(int mn, int k_blk32, int k_groups) {
   return ((long)(mn >> 7) * k_groups + (k_blk32 >> 2)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (k_blk32 & 3);
 }
 
-constexpr int QPITCH = TILE + 16;  // bytes per row of the staged fp8 tiles (conflict-free 16-byte row accesses)
-constexpr int QUANT_SMEM = TILE * PITCH * 2 + 2 * TILE * QPITCH;
+constexpr int QUANT_SMEM = TILE * PITCH * 2;   // one staged bf16 tile; the fp8 results go from registers to global
 
 // Quantises the 128 x 128 bf16 tile staged in `tile` (row pitch PITCH) whose origin in the [R, C] tensor is
 // (row0, col0).  Called by all threads of a 256-thread CTA after the tile is complete (caller synchronises before).
-__device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, uint8_t* qr, uint8_t* qc, int R, int C,
+// Results are written straight from registers: 64 contiguous bytes per thread in the row direction, 8 bytes per row
+// (64 contiguous bytes per 8 lanes) in the column direction -- whole 32-byte sectors either way.
+__device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, int R, int C,
                                                      int row0, int col0, uint8_t* __restrict__ q_row,
                                                      uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
                                                      uint8_t* __restrict__ sf_col) {
@@ -83,7 +84,7 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       for (int i = 0; i < 8; ++i)
         w[i] = (uint32_t)cvt2(f[4 * i] * inv, f[4 * i + 1] * inv) |
                ((uint32_t)cvt2(f[4 * i + 2] * inv, f[4 * i + 3] * inv) << 16);
-      uint4* dst = reinterpret_cast<uint4*>(qr + r * QPITCH + j * 32);
+      uint4* dst = reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + j * 32);
       dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
       sf_row[sf_offset(row0 + r, (col0 >> 5) + j, C >> 7)] = (uint8_t)e;
@@ -137,7 +138,7 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
         w[u] = (uint32_t)cvt2(t0.x * inv[4 * u], t0.y * inv[4 * u + 1]) |
                ((uint32_t)cvt2(t1.x * inv[4 * u + 2], t1.y * inv[4 * u + 3]) << 16);
       }
-      *reinterpret_cast<uint2*>(qc + r * QPITCH + cbase) = make_uint2(w[0], w[1]);
+      *reinterpret_cast<uint2*>(q_col + (long)(row0 + r) * C + col0 + cbase) = make_uint2(w[0], w[1]);
     }
     // every lane of a column group holds the 8 scales; subset s writes those of columns 2s and 2s + 1
 #pragma unroll
@@ -148,28 +149,13 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       }
     }
   }
-  __syncthreads();
-  // coalesced 16-byte stores of the staged fp8 tiles (8 vectors per row)
-#pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int v = tid + it * 256;
-    const int r = v >> 3, c16 = (v & 7) * 16;
-    if (q_row)
-      *reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + c16) =
-          *reinterpret_cast<const uint4*>(qr + r * QPITCH + c16);
-    if (q_col)
-      *reinterpret_cast<uint4*>(q_col + (long)(row0 + r) * C + col0 + c16) =
-          *reinterpret_cast<const uint4*>(qc + r * QPITCH + c16);
-  }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
-  uint8_t* qr = smem_q + TILE * PITCH * 2;
-  uint8_t* qc = qr + TILE * QPITCH;
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
   const int tid = threadIdx.x;
   // load 128 x 128 bf16 (16 vectors of 16 B per row)
@@ -181,7 +167,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
   }
   __syncthreads();
-  quantize_staged_tile(tile, qr, qc, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
 }
 
 __device__ __forceinline__ void bf8_load(const __nv_bfloat16* p, float* f) {
@@ -205,13 +191,11 @@ __device__ __forceinline__ uint4 bf8_pack(const float* f) {
 
 // SwiGLU forward fused with the quantisation of its output: h1 [T, 2I] = [gate | up] -> MXFP8 of
 // act[T, I] = silu(gate) * up (rounded to bf16 first, so the values equal quantising the un-fused kernel's output).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 swiglu_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, int T, int I, float clamp, uint8_t* __restrict__ q_row,
                           uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
-  uint8_t* qr = smem_q + TILE * PITCH * 2;
-  uint8_t* qc = qr + TILE * QPITCH;
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
   const int tid = threadIdx.x;
 #pragma unroll
@@ -235,22 +219,20 @@ swiglu_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, int T, int I, fl
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = bf8_pack(o);
   }
   __syncthreads();
-  quantize_staged_tile(tile, qr, qc, T, I, row0, col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile(tile, T, I, row0, col0, q_row, sf_row, q_col, sf_col);
 }
 
 // SwiGLU backward fused with the quantisation of its output: (h1 [T, 2I], dact [T, I]) -> MXFP8 (both directions) of
 // dh1 [T, 2I] = [dgate | dup].  One CTA per 128 x 128 tile of the activation: it reads gate, up and dact once, stages
 // the dgate and the dup tile, and quantises one after the other.
-constexpr int QUANT_SMEM_BWD = 2 * TILE * PITCH * 2 + 2 * TILE * QPITCH;
-__global__ void __launch_bounds__(256)
+constexpr int QUANT_SMEM_BWD = 2 * TILE * PITCH * 2;
+__global__ void __launch_bounds__(256, 3)
 swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_bfloat16* __restrict__ dact, int T, int I,
                               float clamp, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
                               uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
   __nv_bfloat16* tile_g = reinterpret_cast<__nv_bfloat16*>(smem_q);
   __nv_bfloat16* tile_u = tile_g + TILE * PITCH;
-  uint8_t* qr = smem_q + 2 * TILE * PITCH * 2;
-  uint8_t* qc = qr + TILE * QPITCH;
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
   const int tid = threadIdx.x;
 #pragma unroll 2
@@ -282,9 +264,8 @@ swiglu_bwd_quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ h1, const __nv_b
     *reinterpret_cast<uint4*>(&tile_u[r * PITCH + c8]) = bf8_pack(ou);
   }
   __syncthreads();
-  quantize_staged_tile(tile_g, qr, qc, T, 2 * I, row0, col0, q_row, sf_row, q_col, sf_col);
-  __syncthreads();   // the staged fp8 tiles are read by the stores of the first call
-  quantize_staged_tile(tile_u, qr, qc, T, 2 * I, row0, I + col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile(tile_g, T, 2 * I, row0, col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile(tile_u, T, 2 * I, row0, I + col0, q_row, sf_row, q_col, sf_col);
 }
 
 // value [R, C] fp8 + scales (operand layout with MN = R or C) -> fp32 [R, C]; test / debugging helper

@@ -396,31 +396,35 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   }
 }
 
-// delta[b, h, s] = sum_d dO * O ;  lse2 = lse * log2(e) (so the main kernels need no per-element multiply)
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                  const float* __restrict__ lse, float* __restrict__ delta,
-                                  float* __restrict__ lse2, int seq, int hq, int dv, long o_row, long do_row,
-                                  long total_rows) {
-  const long wid = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (wid >= total_rows * hq) return;
-  const long t = wid / hq;
-  const int h = wid % hq;
-  const __nv_bfloat16* op = o + t * o_row + (long)h * dv;
-  const __nv_bfloat16* dp = d_o + t * do_row + (long)h * dv;
+// delta[b, h, s] = sum_d dO * O ;  lse2 = lse * log2(e) (so the main kernels need no per-element multiply).
+// One thread per (batch, head, position), position fastest: a thread streams its 2 * dv bf16 values with 16-byte
+// loads (many loads in flight per thread) and the per-row results are written coalesced.
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                  const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int seq, int hq,
+                  int dv, long o_row, long do_row, long total_rows) {
+  const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  if (i >= total_rows * hq) return;
+  const long pos = i % seq;
+  const int h = (int)((i / seq) % hq);
+  const long b = i / ((long)seq * hq);
+  const long t = b * seq + pos;
+  const uint4* op = reinterpret_cast<const uint4*>(o + t * o_row + (long)h * dv);
+  const uint4* dp = reinterpret_cast<const uint4*>(d_o + t * do_row + (long)h * dv);
   float s = 0.f;
-  for (int i = lane * 2; i < dv; i += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + i));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + i));
-    s += a.x * b.x + a.y * b.y;
+#pragma unroll 4
+  for (int v = 0; v < dv / 8; ++v) {
+    const uint4 x = op[v], y = dp[v];
+    const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162* ya = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 a = __bfloat1622float2(xa[u]), c = __bfloat1622float2(ya[u]);
+      s += a.x * c.x + a.y * c.y;
+    }
   }
-  s = pb::warp_sum(s);
-  if (lane == 0) {
-    const long b = t / seq, pos = t % seq;
-    const long idx = (b * hq + h) * seq + pos;
-    delta[idx] = s;
-    lse2[idx] = lse[idx] * 1.4426950408889634f;
-  }
+  delta[i] = s;
+  lse2[i] = lse[i] * 1.4426950408889634f;
 }
 
 struct BwdArgs {
@@ -443,9 +447,8 @@ int launch_bwd(const BwdArgs& a) {
   const auto sw = CU_TENSOR_MAP_SWIZZLE_128B;
   const long T = (long)a.batch * a.seq;
   {
-    const long warps = T * a.hq;
     const int threads = 256;
-    const long blocks = (warps * 32 + threads - 1) / threads;
+    const long blocks = (T * a.hq + threads - 1) / threads;
     attn_delta_kernel<<<(unsigned)blocks, threads, 0, a.stream>>>(
         (const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o, a.lse, a.delta, a.delta + (long)a.batch * a.hq * a.seq,
         a.seq, a.hq, DV, a.o_row, a.do_row, T);

@@ -38,6 +38,12 @@ template <int DQK, int DV, int MODE>
 struct BwCfg {
   static constexpr int ACC_COLS = (MODE == MODE_DKDV) ? (DQK + DV) : DQK;
   static constexpr int SBUF = (ACC_COLS + 256 <= 512) ? 2 : 1;
+  // MODE_DQ: when tensor memory has room, the resident tiles (Q, dO) are also kept there as packed bf16 and the first
+  // GEMMs of a step (S = Q K^T, dP = dO V^T) take their A operand from tensor memory: a both-operands-in-shared-memory
+  // MMA with a 64-wide N tile re-reads 128 x 16 A elements per 32 clocks, three times what shared memory delivers
+  static constexpr bool XA = (MODE == MODE_DQ) && (ACC_COLS + SBUF * 128 + DQK / 2 + DV / 2 <= 512);
+  static constexpr int XA1_COL = ACC_COLS + SBUF * 128;
+  static constexpr int XA2_COL = XA1_COL + DQK / 2;
   static constexpr int X1_BYTES = BR * DQK * 2;
   static constexpr int X2_BYTES = BR * DV * 2;
   static constexpr int Y1_BYTES = BC * DQK * 2;
@@ -58,6 +64,7 @@ struct BwBars {
   uint64_t s_full[2];
   uint64_t p_ready[2]; // per team: P / dS of its current step are in tensor memory (one arrival per warp)
   uint64_t acc_done;   // all MMAs of the CTA have completed
+  uint64_t xa_ready;   // resident tiles copied into tensor memory (one arrival per softmax warp)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -98,6 +105,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
   // softcap > 0: scores were softcap * tanh(scale * s / softcap) in the forward pass
   const float softcap = WIN ? softcap_arg : 0.f;
   const float cap_a = (WIN && softcap > 0.f) ? scale / softcap : 0.f;
+  const float cap_b = (WIN && softcap > 0.f) ? softcap / scale : 0.f;
   // seq: query rows per sequence, seq_k: key rows per sequence, q_off: key position of query row 0 (multiple of 128);
   // window > 0 (causal self-attention only): a query sees its last `window` keys, itself included
   using C = BwCfg<DQK, DV, MODE>;
@@ -147,6 +155,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
     for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->s_full[i], 1);
     for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->p_ready[i], BW_COMPUTE / BW_TEAMS / 32);
     pb::mbar_init(&bars->acc_done, 1);
+    pb::mbar_init(&bars->xa_ready, BW_COMPUTE / 32);
     bars->abort_flag = 0;
     pb::fence_barrier_init();
   }
@@ -206,16 +215,27 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
         const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
         const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
         const uint32_t ts = tmem_sbuf + (i % C::SBUF) * 128;
+        if (C::XA) {
 #pragma unroll
-        for (int k = 0; k < DQK / 16; ++k)
-          pb::umma_f16_ss(ts, pb::make_smem_desc(x1a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
-                          pb::make_smem_desc(y1a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
-                          k > 0 ? 1u : 0u);
+          for (int k = 0; k < DQK / 16; ++k)
+            pb::umma_f16_ts(ts, tmem_base + C::XA1_COL + 8 * k,
+                            pb::make_smem_desc(y1a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < DV / 16; ++k)
-          pb::umma_f16_ss(ts + 64, pb::make_smem_desc(x2a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
-                          pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
-                          k > 0 ? 1u : 0u);
+          for (int k = 0; k < DV / 16; ++k)
+            pb::umma_f16_ts(ts + 64, tmem_base + C::XA2_COL + 8 * k,
+                            pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s, k > 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < DQK / 16; ++k)
+            pb::umma_f16_ss(ts, pb::make_smem_desc(x1a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
+                            pb::make_smem_desc(y1a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
+                            k > 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < DV / 16; ++k)
+            pb::umma_f16_ss(ts + 64, pb::make_smem_desc(x2a + (k / 4) * XATOM + (k % 4) * 32, 0, 1024, 2),
+                            pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
+                            k > 0 ? 1u : 0u);
+        }
         pb::umma_commit(&bars->s_full[i & 1]);   // one barrier per softmax team (even / odd steps), also with one TMEM buffer
       };
       // The S / dP GEMMs run SBUF steps ahead.  Step i + SBUF reuses the TMEM buffer of step i; it is issued after
@@ -223,6 +243,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       // softmax threads to have replaced S / dP of step i by P / dS.
       do {
         BW_WAIT(&bars->x_full, 0, PB_ERR_TIMEOUT_MMA);
+        if (C::XA) {
+          BW_WAIT(&bars->xa_ready, 0, PB_ERR_TIMEOUT_MMA);
+          pb::tc_fence_after();
+        }
         for (int j = 0; j < C::SBUF && j < n_iter && ok; ++j) {
           BW_WAIT(&bars->y_full[j % C::NS], (j / C::NS) & 1, PB_ERR_TIMEOUT_MMA);
           pb::tc_fence_after();
@@ -270,6 +294,29 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       delta_row = delta[off];
     }
     bool ok = true;
+    if (C::XA) {
+      // team 0 copies its row of X1 (Q), team 1 its row of X2 (dO) from the 128-byte-swizzled shared tiles into
+      // tensor memory: word w of a row (elements 2w, 2w + 1) goes to column w, the layout of a TMEM A operand
+      do {
+        BW_WAIT(&bars->x_full, 0, PB_ERR_TIMEOUT_EPILOGUE);
+        const uint8_t* xs = team == 0 ? x1_smem : x2_smem;
+        const int natoms = (team == 0 ? DQK : DV) / 64;
+        const uint32_t dst = tmem_base + lane_addr + (team == 0 ? C::XA1_COL : C::XA2_COL);
+        for (int a = 0; a < natoms; ++a) {
+          uint32_t wds[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xs + a * XATOM + row * 128 + ((c ^ (row & 7)) << 4));
+            wds[4 * c] = v.x; wds[4 * c + 1] = v.y; wds[4 * c + 2] = v.z; wds[4 * c + 3] = v.w;
+          }
+          pb::tmem_st_32x32b_x32(dst + 32 * a, wds);
+        }
+        pb::tmem_wait_st();
+        pb::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) pb::mbar_arrive(&bars->xa_ready);
+      } while (false);
+    }
     for (int i = team; i < n_iter && ok; i += BW_TEAMS) {
       const int sb = i % C::SBUF;
       const int st = i % C::NS;
@@ -314,7 +361,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
               float dcap = 1.f;
               if (WIN && softcap > 0.f) {
                 const float t = pb::fast_tanh(sv * cap_a);
-                sv = t / cap_a;                  // = softcap * tanh(scale * s / softcap) / scale
+                sv = t * cap_b;                  // = softcap * tanh(scale * s / softcap) / scale
                 dcap = 1.f - t * t;              // derivative of the capped score with respect to scale * s
               }
               float p = pb::fast_exp2(fmaf(sv, sl2, -l2[u]));

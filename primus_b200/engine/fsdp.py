@@ -21,8 +21,9 @@ def shard_model(model: torch.nn.Module, device: torch.device, compute_dtype: tor
     world = dist.get_world_size()
     mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("dp",))
     model.float()                                   # sharded (master) parameters are fp32
+    # inputs are not cast: the layers receive fp32 rotary tables and integer position ids next to the bf16 activations
     mp = MixedPrecisionPolicy(param_dtype=compute_dtype if compute_dtype != torch.float32 else None,
-                              reduce_dtype=torch.float32)
+                              reduce_dtype=torch.float32, cast_forward_inputs=False)
     for layer in model.decoder.layers.values():
         fully_shard(layer, mesh=mesh, mp_policy=mp)
     fully_shard(model, mesh=mesh, mp_policy=mp)

@@ -37,7 +37,15 @@ enum { MODE_DKDV = 0, MODE_DQ = 1 };
 template <int DQK, int DV, int MODE>
 struct BwCfg {
   static constexpr int ACC_COLS = (MODE == MODE_DKDV) ? (DQK + DV) : DQK;
-  static constexpr int SBUF = (ACC_COLS + 256 <= 512) ? 2 : 1;
+  // S / dP buffers in tensor memory: 3 when they fit next to the accumulators and (MODE_DQ) the TMEM copies of the
+  // resident tiles, else 2, else 1.  For the dQ pass of 128-wide heads two buffers + the TMEM operands measured
+  // faster (2.217 ms for the whole backward at seq 8192) than three buffers without them (2.260 ms).
+  static constexpr int XA_COLS = (MODE == MODE_DQ) ? (DQK / 2 + DV / 2) : 0;
+  static constexpr int SBUF = (ACC_COLS + 384 + XA_COLS <= 512) ? 3 : ((ACC_COLS + 256 <= 512) ? 2 : 1);
+  // barrier of step i: one per buffer when there are three (steps i and i + 2 of a team can both be in flight), else
+  // one per softmax team
+  __host__ __device__ static constexpr int bar_idx(int i) { return SBUF == 3 ? i % 3 : (i & 1); }
+  __host__ __device__ static constexpr uint32_t bar_parity(int i) { return SBUF == 3 ? ((i / 3) & 1) : ((i >> 1) & 1); }
   // MODE_DQ: when tensor memory has room, the resident tiles (Q, dO) are also kept there as packed bf16 and the first
   // GEMMs of a step (S = Q K^T, dP = dO V^T) take their A operand from tensor memory: a both-operands-in-shared-memory
   // MMA with a 64-wide N tile re-reads 128 x 16 A elements per 32 clocks, three times what shared memory delivers
@@ -61,8 +69,8 @@ struct BwCfg {
 struct BwBars {
   uint64_t x_full;
   uint64_t y_full[4], y_empty[4];
-  uint64_t s_full[2];
-  uint64_t p_ready[2]; // per team: P / dS of its current step are in tensor memory (one arrival per warp)
+  uint64_t s_full[3];
+  uint64_t p_ready[3]; // per team: P / dS of its current step are in tensor memory (one arrival per warp)
   uint64_t acc_done;   // all MMAs of the CTA have completed
   uint64_t xa_ready;   // resident tiles copied into tensor memory (one arrival per softmax warp)
   uint32_t tmem_base;
@@ -152,8 +160,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       pb::mbar_init(&bars->y_full[i], 1);
       pb::mbar_init(&bars->y_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->s_full[i], 1);
-    for (int i = 0; i < 2; ++i) pb::mbar_init(&bars->p_ready[i], BW_COMPUTE / BW_TEAMS / 32);
+    for (int i = 0; i < 3; ++i) pb::mbar_init(&bars->s_full[i], 1);
+    for (int i = 0; i < 3; ++i) pb::mbar_init(&bars->p_ready[i], BW_COMPUTE / BW_TEAMS / 32);
     pb::mbar_init(&bars->acc_done, 1);
     pb::mbar_init(&bars->xa_ready, BW_COMPUTE / 32);
     bars->abort_flag = 0;
@@ -236,7 +244,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
                             pb::make_smem_desc(y2a + (k / 4) * YATOM + (k % 4) * 32, 0, 1024, 2), idesc_s,
                             k > 0 ? 1u : 0u);
         }
-        pb::umma_commit(&bars->s_full[i & 1]);   // one barrier per softmax team (even / odd steps), also with one TMEM buffer
+        pb::umma_commit(&bars->s_full[C::bar_idx(i)]);
       };
       // The S / dP GEMMs run SBUF steps ahead.  Step i + SBUF reuses the TMEM buffer of step i; it is issued after
       // the second GEMMs of step i (same thread: the tensor pipe keeps the order), which themselves wait for the
@@ -255,7 +263,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       } while (false);
       for (int i = 0; i < n_iter && ok; ++i) {
         const int st = i % C::NS;
-        BW_WAIT(&bars->p_ready[i & 1], (i >> 1) & 1, PB_ERR_TIMEOUT_MMA);
+        BW_WAIT(&bars->p_ready[C::bar_idx(i)], C::bar_parity(i), PB_ERR_TIMEOUT_MMA);
         pb::tc_fence_after();
         const uint32_t y1a = pb::smem_u32(y1_smem + st * C::Y1_BYTES);
         const uint32_t y2a = pb::smem_u32(y2_smem + st * C::Y2_BYTES);
@@ -321,7 +329,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       const int sb = i % C::SBUF;
       const int st = i % C::NS;
       const int cs = c_start + i % n_per_head;
-      BW_WAIT(&bars->s_full[team], (i >> 1) & 1, PB_ERR_TIMEOUT_EPILOGUE);
+      BW_WAIT(&bars->s_full[C::bar_idx(i)], C::bar_parity(i), PB_ERR_TIMEOUT_EPILOGUE);
       if (MODE == MODE_DKDV) {
         BW_WAIT(&bars->y_full[st], (i / C::NS) & 1, PB_ERR_TIMEOUT_EPILOGUE);  // lse / delta tile visible
       }
@@ -387,7 +395,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_con
       pb::tmem_wait_st();
       pb::tc_fence_before();
       __syncwarp();
-      if (lane == 0) pb::mbar_arrive(&bars->p_ready[team]);   // one arrival per warp
+      if (lane == 0) pb::mbar_arrive(&bars->p_ready[C::bar_idx(i)]);   // one arrival per warp
     }
     // ---- epilogue: accumulators -> bf16 -> (dead) resident tiles -> TMA store
     do {

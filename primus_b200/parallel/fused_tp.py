@@ -126,6 +126,8 @@ def ag_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, f
     Tl, K = x_shard.shape
     M = Tl * tp
     N = w.shape[1] if b_mn else w.shape[0]
+    # the fused kernels are bf16: under an MXFP8 recipe the collective stays on NCCL and the GEMM runs in MXFP8
+    fused = fused and gemm_ops.fp8_recipe() is None
     ctx = get_context(group) if (fused and x_shard.is_cuda) else None
     if ctx is None or not ctx.supported(M, N, K):
         g = tpc.all_gather_dim0(x_shard, group)
@@ -142,6 +144,7 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: 
     tp = dist.get_world_size(group)
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
+    fused = fused and gemm_ops.fp8_recipe() is None
     ctx = get_context(group) if (fused and x.is_cuda) else None
     if ctx is None or not ctx.supported(M, N, K) or not x.is_contiguous():
         return tpc.reduce_scatter_dim0(gemm_ops.gemm(x, w, b_mn=b_mn), group)

@@ -47,6 +47,7 @@ constexpr int MAX_TP = 8;
 struct TpArgs {
   int mode, tp, rank, epoch;
   int comm_ctas;
+  int rs_group;         // reduce-scatter: sources added per pass (1 .. 4)
   int rows_per_chunk;   // T / tp
   int M, N, K;          // GEMM problem of this rank: A [M, K] (K contiguous), B [N, K] or [K, N]
   // AG: peers' shards [rows_per_chunk, K] and the local gather buffer [M, K]
@@ -210,45 +211,58 @@ __device__ void comm_main(const TpArgs& a) {
     }
   } else {
     // reduce-scatter: my rows are [rank * rows_per_chunk, +rows_per_chunk) of every rank's partial buffer.
-    // Per 16 KiB piece a ring slot holds the source piece (bf16) and the matching accumulator piece (fp32);
-    // both arrive by bulk copies, the threads add in shared memory, and the result leaves by a bulk store
-    // (fp32 accumulator while sources remain, bf16 output after the last source).
-    constexpr int RS_SLOT = COMM_PIECE * 3;   // 16 KiB source + 32 KiB accumulator
+    // The sources are taken in arrival order (rank-1 finishes my rows first, my own tiles come last) in groups of up
+    // to `rs_group` (<= 4) ranks: per 8 KiB piece a ring slot receives one bulk copy per source of the group (plus
+    // the fp32 accumulator piece from the second group on), the threads add them in fp32, and the result leaves by a
+    // bulk store -- the bf16 output after the last group, the fp32 accumulator before.  With tp <= rs_group there is
+    // one pass and no accumulator traffic at all; tp = 8 takes two passes.
+    constexpr int RS_PIECE = 8192;
+    constexpr int RS_MAXG = 4;
+    constexpr int RS_SLOT = RS_PIECE * (RS_MAXG + 2);   // 4 source pieces + the fp32 accumulator piece
     constexpr int RS_NSLOT = 4;
+    const int G = a.rs_group < 1 ? 1 : (a.rs_group > RS_MAXG ? RS_MAXG : a.rs_group);
     const long total_bytes = (long)a.rows_per_chunk * a.N * 2;
     const long row_off_bytes = (long)a.rank * total_bytes;
-    const long pieces = (total_bytes + COMM_PIECE - 1) / COMM_PIECE;
+    const long pieces = (total_bytes + RS_PIECE - 1) / RS_PIECE;
     const long mine = (pieces - cta + a.comm_ctas - 1) / a.comm_ctas;
-    auto piece_off = [&](long i) { return ((long)cta + i * a.comm_ctas) * COMM_PIECE; };
+    auto piece_off = [&](long i) { return ((long)cta + i * a.comm_ctas) * RS_PIECE; };
     auto piece_len = [&](long i) {
       const long off = piece_off(i);
-      return (uint32_t)((total_bytes - off) < COMM_PIECE ? (total_bytes - off) : COMM_PIECE);
+      return (uint32_t)((total_bytes - off) < RS_PIECE ? (total_bytes - off) : RS_PIECE);
     };
-    for (int k = 1; k <= a.tp; ++k) {
-      const int p = (a.rank - k + a.tp) % a.tp;  // arrival order: rank-1 finishes my rows first; own rows last
-      const bool own = (p == a.rank);
-      const bool has_acc = k > 1;
-      const bool last = k == a.tp;
+    uint8_t* accg = reinterpret_cast<uint8_t*>(a.acc);
+    uint8_t* outg = reinterpret_cast<uint8_t*>(a.out);
+    for (int k0 = 1; k0 <= a.tp; k0 += G) {
+      const int cnt = (k0 + G - 1 <= a.tp) ? G : (a.tp - k0 + 1);
+      const bool has_acc = k0 > 1;
+      const bool last = k0 + cnt - 1 == a.tp;
+      const uint8_t* srcs[RS_MAXG];
+#pragma unroll
+      for (int j = 0; j < RS_MAXG; ++j) {
+        const int p = (a.rank - (k0 + (j < cnt ? j : 0)) + 2 * a.tp) % a.tp;
+        srcs[j] = reinterpret_cast<const uint8_t*>(a.peer_partial[p]) + row_off_bytes;
+      }
       if (tid == 0) {
-        const bool ok = own ? wait_counter_geq(a.counters + a.rank, a.epoch * a.tiles_per_chunk)
-                            : pb::wait_flag_geq(a.local_flags + p, a.epoch);
-        if (!ok) {
-          atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
-          s_ok = 0;
+        for (int j = 0; j < cnt; ++j) {
+          const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
+          const bool ok = (p == a.rank) ? wait_counter_geq(a.counters + a.rank, a.epoch * a.tiles_per_chunk)
+                                        : pb::wait_flag_geq(a.local_flags + p, a.epoch);
+          if (!ok) {
+            atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+            s_ok = 0;
+            break;
+          }
         }
       }
       __syncthreads();
       if (!s_ok) break;
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.peer_partial[p]) + row_off_bytes;
-      uint8_t* accg = reinterpret_cast<uint8_t*>(a.acc);
-      uint8_t* outg = reinterpret_cast<uint8_t*>(a.out);
       auto issue_load = [&](long i) {
         const int slot = (int)((g + i) % RS_NSLOT);
         const uint32_t len = piece_len(i);
         uint8_t* sb = bufs + slot * RS_SLOT;
-        pb::mbar_expect_tx(&bars[slot], len + (has_acc ? 2 * len : 0));
-        bulk_g2s(sb, src + piece_off(i), len, &bars[slot]);
-        if (has_acc) bulk_g2s(sb + COMM_PIECE, accg + 2 * piece_off(i), 2 * len, &bars[slot]);
+        pb::mbar_expect_tx(&bars[slot], cnt * len + (has_acc ? 2 * len : 0));
+        for (int j = 0; j < cnt; ++j) bulk_g2s(sb + j * RS_PIECE, srcs[j] + piece_off(i), len, &bars[slot]);
+        if (has_acc) bulk_g2s(sb + RS_MAXG * RS_PIECE, accg + 2 * piece_off(i), 2 * len, &bars[slot]);
       };
       long issued = 0;
       if (tid == 0) {
@@ -267,23 +281,27 @@ __device__ void comm_main(const TpArgs& a) {
         const uint32_t len = piece_len(done);
         const int nvec = len / 16;
         uint8_t* sb = bufs + slot * RS_SLOT;
-        const uint4* sp = reinterpret_cast<const uint4*>(sb);
-        float4* sacc = reinterpret_cast<float4*>(sb + COMM_PIECE);
+        float4* sacc = reinterpret_cast<float4*>(sb + RS_MAXG * RS_PIECE);
         uint4* sout = reinterpret_cast<uint4*>(sb);
         for (int i = tid; i < nvec; i += nthr) {
-          const uint4 v = sp[i];
           float f[8];
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 t = __bfloat1622float2(h[j]);
-            f[2 * j] = t.x;
-            f[2 * j + 1] = t.y;
-          }
           if (has_acc) {
             const float4 a0 = sacc[2 * i], a1 = sacc[2 * i + 1];
-            f[0] += a0.x; f[1] += a0.y; f[2] += a0.z; f[3] += a0.w;
-            f[4] += a1.x; f[5] += a1.y; f[6] += a1.z; f[7] += a1.w;
+            f[0] = a0.x; f[1] = a0.y; f[2] = a0.z; f[3] = a0.w;
+            f[4] = a1.x; f[5] = a1.y; f[6] = a1.z; f[7] = a1.w;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+          }
+          for (int sj = 0; sj < cnt; ++sj) {
+            const uint4 v = reinterpret_cast<const uint4*>(sb + sj * RS_PIECE)[i];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(h[j]);
+              f[2 * j] += t.x;
+              f[2 * j + 1] += t.y;
+            }
           }
           if (!last) {
             sacc[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
@@ -300,7 +318,7 @@ __device__ void comm_main(const TpArgs& a) {
         pb::fence_proxy_async_smem();
         __syncthreads();
         if (tid == 0) {
-          if (!last) bulk_s2g(accg + 2 * piece_off(done), sb + COMM_PIECE, 2 * len);
+          if (!last) bulk_s2g(accg + 2 * piece_off(done), sb + RS_MAXG * RS_PIECE, 2 * len);
           else bulk_s2g(outg + piece_off(done), sb, len);
           pb::tma_store_commit();
           pb::tma_store_wait_read<1>();  // every store but the newest has finished reading its slot
@@ -314,9 +332,13 @@ __device__ void comm_main(const TpArgs& a) {
       if (tid == 0) pb::tma_store_wait_all<0>();  // accumulator pieces must be complete before the next pass loads them
       g += mine;
       __syncthreads();
-      if (tid == 0 && !own) {
-        const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
-        if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
+      if (tid == 0) {
+        for (int j = 0; j < cnt; ++j) {
+          const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
+          if (p == a.rank) continue;
+          const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
+          if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
+        }
       }
     }
   }
@@ -559,6 +581,10 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   TpArgs a;
   memset(&a, 0, sizeof(a));
   a.mode = mode; a.tp = tp; a.rank = rank; a.epoch = epoch; a.comm_ctas = comm_ctas;
+  {
+    const char* e = getenv("PRIMUS_B200_RS_GROUP");
+    a.rs_group = e ? atoi(e) : 4;
+  }
   a.rows_per_chunk = M / tp;
   a.M = M; a.N = N; a.K = K;
   for (int r = 0; r < tp; ++r) {

@@ -7,8 +7,13 @@ from tests.mp_utils import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, shapes):
+def _worker(rank, world, shapes, rs_group=None):
+    import os
+
     import torch.distributed as dist
+
+    if rs_group is not None:
+        os.environ["PRIMUS_B200_RS_GROUP"] = str(rs_group)
 
     from primus_b200.ops import _lib
     from primus_b200.parallel import fused_tp
@@ -40,3 +45,11 @@ def _worker(rank, world, shapes):
 def test_fused_tp_matches_nccl_composition():
     shapes = [(512, 256, 128, False), (2048, 1280, 1024, False), (1024, 768, 512, True)]
     run_ranks(_worker, 2, "nccl", args=(shapes,), timeout=240)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_scatter_multi_pass():
+    """One source per pass: the partial sums travel through the fp32 accumulator between passes (the path that tensor
+    parallel sizes above the group size take)."""
+    shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
+    run_ranks(_worker, 2, "nccl", args=(shapes, 1), timeout=240)

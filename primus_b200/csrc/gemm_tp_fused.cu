@@ -43,6 +43,8 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_BUF_BYTES + 1024 + 256
 constexpr int TMEM_COLS = 2 * BN;
 enum { MODE_AG = 0, MODE_RS = 1 };
 constexpr int MAX_TP = 8;
+constexpr int RS_RING_BYTES = STAGES * STAGE_BYTES + 2 * EPI_BUF_BYTES;  // copy CTAs of the reduce-scatter: ring of slots
+constexpr int RS_MAX_SLOTS = 16;                                        // + their barriers in the 256 spare bytes
 
 struct TpArgs {
   int mode, tp, rank, epoch;
@@ -57,7 +59,8 @@ struct TpArgs {
   const __nv_bfloat16* peer_partial[MAX_TP];
   float* acc;
   __nv_bfloat16* out;
-  // local monotonic counters: [0,tp) chunk progress (AG: copy CTAs done, RS: tiles done), [tp,2tp) reads done
+  // local monotonic counters: [0,tp) chunk progress (AG: copy CTAs done; RS: tiles done, own slot: copy CTAs whose
+  // share of the accumulator is final), [tp,2tp) reads done
   int* counters;
   int tiles_per_chunk;
   // symmetric flags: slot r = "rank r's data is ready for me", slot tp + r = "rank r finished reading mine"
@@ -141,8 +144,10 @@ __device__ void comm_main(const TpArgs& a) {
   const int nthr = blockDim.x;
   if (tid == 0) {
     s_ok = 1;
-    for (int i = 0; i < COMM_NBUF; ++i) pb::mbar_init(&bars[i], 1);
-    pb::fence_barrier_init();
+    if (a.mode == MODE_AG) {  // the reduce-scatter lays its own ring (and barriers) over this memory
+      for (int i = 0; i < COMM_NBUF; ++i) pb::mbar_init(&bars[i], 1);
+      pb::fence_barrier_init();
+    }
   }
   __syncthreads();
   // announce: everything this rank produced before the launch is ready for its peers
@@ -210,32 +215,41 @@ __device__ void comm_main(const TpArgs& a) {
       }
     }
   } else {
-    // reduce-scatter: my rows are [rank * rows_per_chunk, +rows_per_chunk) of every rank's partial buffer.
-    // The sources are taken in arrival order (rank-1 finishes my rows first, my own tiles come last) in groups of up
-    // to `rs_group` (<= 4) ranks: per 8 KiB piece a ring slot receives one bulk copy per source of the group (plus
-    // the fp32 accumulator piece from the second group on), the threads add them in fp32, and the result leaves by a
-    // bulk store -- the bf16 output after the last group, the fp32 accumulator before.  With tp <= rs_group there is
-    // one pass and no accumulator traffic at all; tp = 8 takes two passes.
-    constexpr int RS_PIECE = 8192;
+    // reduce-scatter: my rows are [rank * rows_per_chunk, +rows_per_chunk) of every rank's partial buffer.  The copy
+    // CTAs add the REMOTE partials into the fp32 accumulator while the GEMM runs; this rank's own tiles of those rows
+    // come last in its tile order, and their epilogue adds the accumulator and writes the bf16 result, so nothing
+    // is left to do once the GEMM has finished.  The sources are taken in arrival order (rank-1 finishes my rows
+    // first) in groups of up to `rs_group` (<= 4): per piece a ring slot receives one bulk copy per source of the group
+    // (plus the accumulator piece from the second group on), the threads add them in fp32 and store the sums with
+    // ordinary coalesced stores.  tp <= 5 needs one pass, tp = 8 two.
     constexpr int RS_MAXG = 4;
-    constexpr int RS_SLOT = RS_PIECE * (RS_MAXG + 2);   // 4 source pieces + the fp32 accumulator piece
-    constexpr int RS_NSLOT = 4;
-    const int G = a.rs_group < 1 ? 1 : (a.rs_group > RS_MAXG ? RS_MAXG : a.rs_group);
+    const int nsrc = a.tp - 1;
+    int G = a.rs_group < 1 ? 1 : (a.rs_group > RS_MAXG ? RS_MAXG : a.rs_group);
+    if (G > nsrc) G = nsrc;
+    const bool multi = nsrc > G;  // several passes: the accumulator piece travels through the slot as well
+    const int PIECE = (G == 1) ? 32768 : ((G == 2) ? 16384 : 8192);
+    const int slot_bytes = G * PIECE + (multi ? 2 * PIECE : 0);
+    int nslot = RS_RING_BYTES / slot_bytes;
+    if (nslot > RS_MAX_SLOTS) nslot = RS_MAX_SLOTS;
+    uint64_t* rbars = reinterpret_cast<uint64_t*>(bufs + RS_RING_BYTES);
+    if (tid == 0) {
+      for (int i = 0; i < nslot; ++i) pb::mbar_init(&rbars[i], 1);
+      pb::fence_barrier_init();
+    }
+    __syncthreads();
     const long total_bytes = (long)a.rows_per_chunk * a.N * 2;
     const long row_off_bytes = (long)a.rank * total_bytes;
-    const long pieces = (total_bytes + RS_PIECE - 1) / RS_PIECE;
+    const long pieces = (total_bytes + PIECE - 1) / PIECE;
     const long mine = (pieces - cta + a.comm_ctas - 1) / a.comm_ctas;
-    auto piece_off = [&](long i) { return ((long)cta + i * a.comm_ctas) * RS_PIECE; };
+    auto piece_off = [&](long i) { return ((long)cta + i * a.comm_ctas) * PIECE; };
     auto piece_len = [&](long i) {
       const long off = piece_off(i);
-      return (uint32_t)((total_bytes - off) < RS_PIECE ? (total_bytes - off) : RS_PIECE);
+      return (uint32_t)((total_bytes - off) < PIECE ? (total_bytes - off) : PIECE);
     };
     uint8_t* accg = reinterpret_cast<uint8_t*>(a.acc);
-    uint8_t* outg = reinterpret_cast<uint8_t*>(a.out);
-    for (int k0 = 1; k0 <= a.tp; k0 += G) {
-      const int cnt = (k0 + G - 1 <= a.tp) ? G : (a.tp - k0 + 1);
+    for (int k0 = 1; k0 <= nsrc; k0 += G) {
+      const int cnt = (k0 + G - 1 <= nsrc) ? G : (nsrc - k0 + 1);
       const bool has_acc = k0 > 1;
-      const bool last = k0 + cnt - 1 == a.tp;
       const uint8_t* srcs[RS_MAXG];
 #pragma unroll
       for (int j = 0; j < RS_MAXG; ++j) {
@@ -245,9 +259,7 @@ __device__ void comm_main(const TpArgs& a) {
       if (tid == 0) {
         for (int j = 0; j < cnt; ++j) {
           const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
-          const bool ok = (p == a.rank) ? wait_counter_geq(a.counters + a.rank, a.epoch * a.tiles_per_chunk)
-                                        : pb::wait_flag_geq(a.local_flags + p, a.epoch);
-          if (!ok) {
+          if (!pb::wait_flag_geq(a.local_flags + p, a.epoch)) {
             atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
             s_ok = 0;
             break;
@@ -257,32 +269,31 @@ __device__ void comm_main(const TpArgs& a) {
       __syncthreads();
       if (!s_ok) break;
       auto issue_load = [&](long i) {
-        const int slot = (int)((g + i) % RS_NSLOT);
+        const int slot = (int)((g + i) % nslot);
         const uint32_t len = piece_len(i);
-        uint8_t* sb = bufs + slot * RS_SLOT;
-        pb::mbar_expect_tx(&bars[slot], cnt * len + (has_acc ? 2 * len : 0));
-        for (int j = 0; j < cnt; ++j) bulk_g2s(sb + j * RS_PIECE, srcs[j] + piece_off(i), len, &bars[slot]);
-        if (has_acc) bulk_g2s(sb + RS_MAXG * RS_PIECE, accg + 2 * piece_off(i), 2 * len, &bars[slot]);
+        uint8_t* sb = bufs + slot * slot_bytes;
+        pb::mbar_expect_tx(&rbars[slot], cnt * len + (has_acc ? 2 * len : 0));
+        for (int j = 0; j < cnt; ++j) bulk_g2s(sb + j * PIECE, srcs[j] + piece_off(i), len, &rbars[slot]);
+        if (has_acc) bulk_g2s(sb + G * PIECE, accg + 2 * piece_off(i), 2 * len, &rbars[slot]);
       };
       long issued = 0;
       if (tid == 0) {
-        asm volatile("fence.proxy.async;" ::: "memory");  // own rows were written by TMA stores of this kernel
-        for (; issued < mine && issued < RS_NSLOT; ++issued) issue_load(issued);
+        asm volatile("fence.proxy.async;" ::: "memory");  // accumulator pieces of the previous pass: ordinary stores
+        for (; issued < mine && issued < nslot; ++issued) issue_load(issued);
       }
       for (long done = 0; done < mine; ++done) {
         const long gi = g + done;
-        const int slot = (int)(gi % RS_NSLOT);
-        if (!pb::mbar_wait(&bars[slot], (uint32_t)((gi / RS_NSLOT) & 1))) {
+        const int slot = (int)(gi % nslot);
+        if (!pb::mbar_wait(&rbars[slot], (uint32_t)((gi / nslot) & 1))) {
           atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
           s_ok = 0;
         }
         __syncthreads();
         if (!s_ok) break;
-        const uint32_t len = piece_len(done);
-        const int nvec = len / 16;
-        uint8_t* sb = bufs + slot * RS_SLOT;
-        float4* sacc = reinterpret_cast<float4*>(sb + RS_MAXG * RS_PIECE);
-        uint4* sout = reinterpret_cast<uint4*>(sb);
+        const int nvec = piece_len(done) / 16;
+        const uint8_t* sb = bufs + slot * slot_bytes;
+        const float4* sacc = reinterpret_cast<const float4*>(sb + G * PIECE);
+        float4* gout = reinterpret_cast<float4*>(accg + 2 * piece_off(done));
         for (int i = tid; i < nvec; i += nthr) {
           float f[8];
           if (has_acc) {
@@ -294,7 +305,7 @@ __device__ void comm_main(const TpArgs& a) {
             for (int j = 0; j < 8; ++j) f[j] = 0.f;
           }
           for (int sj = 0; sj < cnt; ++sj) {
-            const uint4 v = reinterpret_cast<const uint4*>(sb + sj * RS_PIECE)[i];
+            const uint4 v = reinterpret_cast<const uint4*>(sb + sj * PIECE)[i];
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -303,43 +314,33 @@ __device__ void comm_main(const TpArgs& a) {
               f[2 * j + 1] += t.y;
             }
           }
-          if (!last) {
-            sacc[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
-            sacc[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
-          } else {
-            uint4 o;
-            o.x = pb::pack_bf16x2(f[0], f[1]);
-            o.y = pb::pack_bf16x2(f[2], f[3]);
-            o.z = pb::pack_bf16x2(f[4], f[5]);
-            o.w = pb::pack_bf16x2(f[6], f[7]);
-            sout[i] = o;
-          }
+          gout[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
+          gout[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
         }
-        pb::fence_proxy_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-          if (!last) bulk_s2g(accg + 2 * piece_off(done), sb + RS_MAXG * RS_PIECE, 2 * len);
-          else bulk_s2g(outg + piece_off(done), sb, len);
-          pb::tma_store_commit();
-          pb::tma_store_wait_read<1>();  // every store but the newest has finished reading its slot
-          if (issued < mine && done >= 1) {
-            issue_load(issued);          // goes to the slot of piece done-1
-            ++issued;
-          }
+        __syncthreads();  // every thread has read the slot: it can take the next piece
+        if (tid == 0 && issued < mine) {
+          issue_load(issued);
+          ++issued;
         }
       }
       if (!s_ok) break;
-      if (tid == 0) pb::tma_store_wait_all<0>();  // accumulator pieces must be complete before the next pass loads them
       g += mine;
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");  // the next pass reads these sums with bulk copies
       __syncthreads();
       if (tid == 0) {
         for (int j = 0; j < cnt; ++j) {
           const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
-          if (p == a.rank) continue;
           const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
           if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
         }
       }
+    }
+    // this CTA's share of the accumulator is final: the epilogue of this rank's own tiles may add it
+    __syncthreads();
+    if (tid == 0 && s_ok) {
+      __threadfence();
+      atomicAdd(a.counters + a.rank, 1);
     }
   }
   // leave only when every peer has finished reading this rank's buffers (they may be reused right after)
@@ -499,10 +500,24 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
+    bool acc_ready = false;
     for (int tile = gemm_cta; tile < num_tiles && ok; tile += num_gemm) {
       int chunk, mb, nb;
       tile_coords(a, tile, num_n, chunk, mb, nb);
       const int m0 = mb * BM, n0 = nb * BN;
+      // reduce-scatter, this rank's own rows: add the sum of the remote partials and write the final result
+      const bool fin = (a.mode == MODE_RS && chunk == a.rank);
+      if (fin && !acc_ready) {
+        if (et == 0 && !wait_counter_geq(a.counters + a.rank, a.epoch * a.comm_ctas)) {
+          atomicCAS(status, 0, PB_ERR_TIMEOUT_FLAG);
+          bars->abort_flag = 1;
+        }
+        pb::named_bar_sync(1, EPI_THREADS);
+        if (*abort_flag) break;
+        acc_ready = true;
+      }
+      const float4* acc_row =
+          fin ? reinterpret_cast<const float4*>(a.acc + (size_t)(m0 - a.rank * a.rows_per_chunk + row) * a.N + n0) : nullptr;
       if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort_flag)) {
         if (!*abort_flag) atomicCAS(status, 0, PB_ERR_TIMEOUT_EPILOGUE);
         bars->abort_flag = 1;
@@ -516,7 +531,22 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t r[64];
         pb::tmem_ld_32x32b_x32(t_row + c * 64, r);
         pb::tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
+        const bool add = fin && (n0 + c * 64 < a.N);
+        float4 av[16];
+        if (add) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) av[j] = __ldcg(acc_row + c * 16 + j);
+        }
         pb::tmem_wait_ld();
+        if (add) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + av[j].x);
+            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + av[j].y);
+            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + av[j].z);
+            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + av[j].w);
+          }
+        }
         if (et == 0) pb::tma_store_wait_read<1>();
         pb::named_bar_sync(1, EPI_THREADS);
         uint8_t* stage_buf = smem_epi + buf * EPI_BUF_BYTES;
@@ -533,7 +563,8 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         pb::fence_proxy_async_smem();
         pb::named_bar_sync(1, EPI_THREADS);
         if (et == 0) {
-          pb::tma_store_2d(&tmD, stage_buf, n0 + c * 64, m0);
+          if (fin) pb::tma_store_2d(&tmAown, stage_buf, n0 + c * 64, m0 - a.rank * a.rows_per_chunk);
+          else pb::tma_store_2d(&tmD, stage_buf, n0 + c * 64, m0);
           pb::tma_store_commit();
         }
         buf ^= 1;
@@ -544,12 +575,12 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         acc = 0;
         acc_phase ^= 1;
       }
-      if (a.mode == MODE_RS && et == 0) {
+      if (a.mode == MODE_RS && et == 0 && !fin) {
         // the tile's rows must be complete in global memory before the destination is told about them
         pb::tma_store_wait_all<0>();
         __threadfence_system();
         const int done = atomicAdd(a.counters + chunk, 1) + 1;
-        if (done == a.epoch * a.tiles_per_chunk && chunk != a.rank)
+        if (done == a.epoch * a.tiles_per_chunk)
           pb::set_flag_release(a.peer_flags[chunk] + a.rank, a.epoch);
       }
     }
@@ -614,6 +645,8 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   if (mode == MODE_AG && (rc = pbh::make_tmap_2d(&tAown, reinterpret_cast<const void*>(peer_x[rank]), bf, 2, M / tp, K, K, BM,
                                                   BK, sw)))
     return rc;
+  // reduce-scatter: the fourth map is the output [M / tp, N], written by the epilogue of this rank's own tiles
+  if (mode == MODE_RS && (rc = pbh::make_tmap_2d(&tAown, out, bf, 2, M / tp, N, N, BM, 64, sw))) return rc;
 
   static int num_sms = 0;
   if (!num_sms) {

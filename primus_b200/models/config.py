@@ -28,6 +28,11 @@ class TransformerConfig:
     rotary_base: float = 10000.0
     rotary_percent: float = 1.0
     rotary_scaling_factor: float = 1.0
+    use_rope_scaling: bool = False    # Llama-3.x frequency scaling: long wavelengths divided by rope_scaling_factor
+    rope_scaling_factor: float = 8.0
+    rope_scaling_low_freq_factor: float = 1.0
+    rope_scaling_high_freq_factor: float = 4.0
+    rope_scaling_original_max_position: int = 8192
     norm_epsilon: float = 1e-5
     qk_layernorm: bool = False
     untie_embeddings_and_output_weights: bool = True

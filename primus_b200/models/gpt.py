@@ -286,7 +286,10 @@ class GPTModel(nn.Module):
         d = cfg.qk_pos_emb_head_dim if cfg.multi_latent_attention else int(cfg.kv_channels * cfg.rotary_percent)
         key = (str(device), seq, d)
         if key not in self._rope_cache:
-            cos, sin = fused.rope_tables(max(seq, 1), d, cfg.rotary_base, device, cfg.rotary_scaling_factor)
+            l3 = dict(factor=cfg.rope_scaling_factor, low_freq_factor=cfg.rope_scaling_low_freq_factor,
+                      high_freq_factor=cfg.rope_scaling_high_freq_factor,
+                      original_max_pos=cfg.rope_scaling_original_max_position) if cfg.use_rope_scaling else None
+            cos, sin = fused.rope_tables(max(seq, 1), d, cfg.rotary_base, device, cfg.rotary_scaling_factor, l3)
             self._rope_cache[key] = (cos, sin)
         return self._rope_cache[key]
 

@@ -12,6 +12,8 @@ fused_residual_rmsnorm.py:327-453), swiglu_with_probs (primus_turbo.py:1954-1980
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.distributed as dist
 
@@ -107,8 +109,26 @@ def rmsnorm(x, w, eps=1e-5, residual=None):
 
 # ----------------------------------------------------------------------------------------------
 # RoPE (rotate-half convention, first ``rot_dim`` channels of each head)
-def rope_tables(max_pos: int, rot_dim: int, theta: float, device, scaling_factor: float = 1.0):
+def llama3_scale_frequencies(inv, factor: float, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
+                             original_max_pos: int = 8192):
+    """Llama-3.x long-context frequency scaling: wavelengths above ``original_max_pos / low_freq_factor`` are stretched by
+    ``factor``, those below ``original_max_pos / high_freq_factor`` stay, the band between is interpolated (the
+    ``use_rope_scaling`` / ``rope_scaling_factor`` switches of the reference's model presets,
+    primus/configs/models/megatron/language_model.yaml:46-47)."""
+    wavelen = 2.0 * math.pi / inv
+    low_wl = original_max_pos / low_freq_factor
+    high_wl = original_max_pos / high_freq_factor
+    smooth = ((original_max_pos / wavelen) - low_freq_factor) / (high_freq_factor - low_freq_factor)
+    mid = (1.0 - smooth) * inv / factor + smooth * inv
+    return torch.where(wavelen > low_wl, inv / factor, torch.where(wavelen < high_wl, inv, mid))
+
+
+def rope_tables(max_pos: int, rot_dim: int, theta: float, device, scaling_factor: float = 1.0, llama3_scaling=None):
+    """cos / sin tables [max_pos, rot_dim / 2] in fp32.  ``llama3_scaling``: None or the keyword arguments of
+    :func:`llama3_scale_frequencies`."""
     inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32, device=device) / rot_dim))
+    if llama3_scaling:
+        inv = llama3_scale_frequencies(inv, **llama3_scaling)
     t = torch.arange(max_pos, dtype=torch.float32, device=device) / scaling_factor
     f = torch.outer(t, inv)
     return f.cos().contiguous(), f.sin().contiguous()

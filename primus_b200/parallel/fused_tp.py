@@ -146,7 +146,8 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: 
     N = w.shape[1] if b_mn else w.shape[0]
     fused = fused and gemm_ops.fp8_recipe() is None
     ctx = get_context(group) if (fused and x.is_cuda) else None
-    if ctx is None or not ctx.supported(M, N, K) or not x.is_contiguous():
+    # N % 64: the epilogue of this rank's own tiles adds the accumulator in whole 64-column groups
+    if ctx is None or not ctx.supported(M, N, K) or N % 64 or not x.is_contiguous():
         return tpc.reduce_scatter_dim0(gemm_ops.gemm(x, w, b_mn=b_mn), group)
     inst = ctx.instance(1, M, N, K)
     partial = inst.sym.local(torch.bfloat16, M * N).view(M, N)

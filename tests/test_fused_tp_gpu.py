@@ -47,9 +47,15 @@ def test_fused_tp_matches_nccl_composition():
     run_ranks(_worker, 2, "nccl", args=(shapes,), timeout=240)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs (three remote sources)")
 def test_fused_reduce_scatter_multi_pass():
-    """One source per pass: the partial sums travel through the fp32 accumulator between passes (the path that tensor
-    parallel sizes above the group size take)."""
+    """Two sources per pass with three remote sources: the partial sums travel through the fp32 accumulator between the
+    passes (the path that tensor-parallel size 8 takes)."""
     shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
-    run_ranks(_worker, 2, "nccl", args=(shapes, 1), timeout=240)
+    run_ranks(_worker, 4, "nccl", args=(shapes, 2), timeout=240)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_fused_tp_on_four_gpus():
+    shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
+    run_ranks(_worker, 4, "nccl", args=(shapes,), timeout=240)

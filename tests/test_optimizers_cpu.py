@@ -246,3 +246,62 @@ def test_expert_bias_moves_towards_balanced_load():
     assert load.sum() == 4 * 32 * mc.moe_router_topk            # every routed copy of the global batch was counted
     assert torch.equal(bias, 0.01 * torch.sign(load.mean() - load))
     assert layer.router.local_tokens_per_expert.abs().sum() == 0
+
+
+def test_llama3_rope_scaling_and_a_llama4_style_model():
+    """use_rope_scaling stretches only the long wavelengths (Llama-3.x rule); a Llama-4-style layer stack (top-1 routed
+    experts with the softmax taken before the top-k, a shared expert, dense and routed layers alternating, QK-norm)
+    builds from the preset's switches and trains."""
+    import math
+
+    from primus_b200.core.config import presets
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.ops import fused
+    from primus_b200.parallel import state as ps
+
+    d, theta, factor, orig = 128, 500000.0, 8.0, 8192
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    got = fused.llama3_scale_frequencies(inv, factor, 1.0, 4.0, orig)
+    for f0, f1 in zip(inv.tolist(), got.tolist()):
+        wl = 2 * math.pi / f0
+        if wl < orig / 4.0:
+            want = f0
+        elif wl > orig / 1.0:
+            want = f0 / factor
+        else:
+            s = (orig / wl - 1.0) / (4.0 - 1.0)
+            want = (1 - s) * f0 / factor + s * f0
+        assert abs(f1 - want) <= 1e-6 * want
+    assert (got < inv).any() and (got == inv).any()
+    _, sin = fused.rope_tables(16, d, theta, "cpu", 1.0, dict(factor=factor))
+    _, sin0 = fused.rope_tables(16, d, theta, "cpu")
+    assert torch.equal(sin[:, 0], sin0[:, 0]) and torch.allclose(sin[:, -1] * factor, sin0[:, -1], rtol=1e-4)
+
+    preset = presets.load_preset("llama4_17B128E", "models")
+    assert preset["moe_layer_freq"] == 2 and preset["num_experts"] == 128 and preset["moe_router_topk"] == 1
+    scout = presets.load_preset("llama4_17B16E", "models")
+    assert scout["use_rope_scaling"] and scout["rope_scaling_factor"] == 16.0 and scout["qk_layernorm"]
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    cfg = TransformerConfig(num_layers=4, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+                            vocab_size=128, params_dtype="fp32", seq_length=32, qk_layernorm=True, use_rope_scaling=True,
+                            rope_scaling_factor=16.0, rope_scaling_original_max_position=16, num_experts=8,
+                            moe_router_topk=1, moe_router_pre_softmax=True, moe_layer_freq=2, moe_ffn_hidden_size=64,
+                            moe_shared_expert_intermediate_size=64, moe_aux_loss_coeff=0.001)
+    assert cfg.moe_layer_pattern == [1, 0, 1, 0]
+    torch.manual_seed(0)
+    m = GPTModel(cfg, "cpu")
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    tokens = torch.randint(0, 128, (2, 32))
+    labels = torch.roll(tokens, -1, 1)
+    w = torch.full((2, 32), 1.0 / 64)
+    losses = []
+    for _ in range(8):
+        opt.zero_grad()
+        loss = m(tokens, labels, loss_weights=w, unit_upstream=True)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < losses[0] - 0.3

@@ -222,7 +222,7 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (with sequence parallelism); dp = gpus / tp")
     ap.add_argument("--cp", type=int, default=1, help="context-parallel size; dp = gpus / (tp * cp)")
-    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather", "p2p"],
+    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather", "p2p", "a2a+p2p"],
                     help="context-parallel scheme: all-to-all over heads (Ulysses), K/V all-gather with zig-zag chunks, or ring (p2p)")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
@@ -261,7 +261,8 @@ def main() -> int:
         mdict["num_layers"] = args.layers
     mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
                              sequence_parallel=args.tp > 1, fp8="e4m3" if args.precision == "mxfp8" else None,
-                             fp8_recipe="mxfp8", context_parallel_size=args.cp, cp_comm_type=args.cp_comm)
+                             fp8_recipe="mxfp8", context_parallel_size=args.cp, cp_comm_type=args.cp_comm,
+                             hierarchical_context_parallel_sizes=[2, args.cp // 2] if args.cp_comm == "a2a+p2p" else None)
     if args.fused_tp:
         from primus_b200.parallel import fused_tp
 

@@ -183,7 +183,9 @@ class Trainer:
             st = ps.initialize_model_parallel(
                 tp=model_cfg.tensor_model_parallel_size, pp=model_cfg.pipeline_model_parallel_size,
                 cp=model_cfg.context_parallel_size, ep=model_cfg.expert_model_parallel_size,
-                etp=model_cfg.expert_tensor_parallel_size, virtual_pp=model_cfg.virtual_pipeline_model_parallel_size)
+                etp=model_cfg.expert_tensor_parallel_size, virtual_pp=model_cfg.virtual_pipeline_model_parallel_size,
+                hierarchical_cp_sizes=model_cfg.hierarchical_context_parallel_sizes
+                if model_cfg.cp_comm_type == "a2a+p2p" else None)
         self.st = st
         if device is None:
             device = f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu"
@@ -331,7 +333,22 @@ class Trainer:
             return mb
         b, S = mb["tokens"].shape
         dev = mb["tokens"].device
-        if getattr(self.mcfg, "cp_comm_type", "a2a") in ("allgather", "p2p"):
+        if getattr(self.mcfg, "cp_comm_type", "a2a") == "a2a+p2p":
+            # zig-zag over the ring (2 x p2p super-chunks), consecutive parts inside an all-to-all group
+            a, P = st.cp_a2a, st.cp_p2p
+            assert a * P == st.cp, "a2a+p2p context parallelism needs hierarchical_context_parallel_sizes"
+            assert S % (2 * st.cp) == 0, "sequence length must divide by 2 x the context-parallel size"
+            C, part = S // (2 * P), S // (2 * st.cp)
+            if self.is_cuda:
+                assert C % 128 == 0, "ring context parallelism needs seq / (2 p2p) to be a multiple of 128"
+            i, j = divmod(st.cp_rank, a)
+            pos = torch.cat([torch.arange(sc * C + j * part, sc * C + (j + 1) * part, device=dev)
+                             for sc in (i, 2 * P - 1 - i)])
+            out = {k: v.index_select(1, pos).contiguous() for k, v in mb.items()
+                   if torch.is_tensor(v) and v.dim() == 2 and v.shape[1] == S}
+            if "position_ids" not in mb:
+                out["position_ids"] = pos.repeat(b, 1)
+        elif getattr(self.mcfg, "cp_comm_type", "a2a") in ("allgather", "p2p"):
             assert S % (2 * st.cp) == 0, "sequence length must divide by 2 x the context-parallel size"
             c = S // (2 * st.cp)
             if self.is_cuda:

@@ -92,6 +92,7 @@ class TransformerConfig:
     window_size: object = None                      # sliding-window attention: W, or Megatron's (left, right) = (W - 1, 0)
     window_attn_skip_freq: object = None            # int N: every N-th layer attends fully; list: 1 = windowed, 0 = full
     softmax_type: str = "vanilla"                   # "learnable": per-head sink logit in the softmax denominator
+    hierarchical_context_parallel_sizes: Optional[list] = None   # [a2a, p2p] for cp_comm_type "a2a+p2p"
     cp_comm_type: str = "a2a"                      # context parallelism: "a2a" (Ulysses) or "allgather" (zig-zag chunks)
     mtp_num_layers: int | None = None               # multi-token prediction depths (DeepSeek-V3); None / 0: off
     mtp_loss_scaling_factor: float = 0.1

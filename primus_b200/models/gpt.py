@@ -98,10 +98,14 @@ class SelfAttention(nn.Module):
         elif st.cp > 1 and cfg.cp_comm_type == "p2p":
             ctx_out = layers.ring_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
                                                     rot_dim=int(d * cfg.rotary_percent), scale=scale)
+        elif st.cp > 1 and cfg.cp_comm_type == "a2a+p2p":
+            ctx_out = layers.hierarchical_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
+                                                            st.cp_a2a_group, st.cp_a2a, st.cp_p2p_group, st.cp_p2p,
+                                                            rot_dim=int(d * cfg.rotary_percent), scale=scale)
         elif st.cp > 1:
             if cfg.cp_comm_type != "a2a":
-                raise NotImplementedError(f"cp_comm_type {cfg.cp_comm_type!r}: a2a (Ulysses), allgather and p2p (ring) "
-                                          "are built")
+                raise NotImplementedError(f"cp_comm_type {cfg.cp_comm_type!r}: a2a (Ulysses), allgather, p2p (ring) "
+                                          "and a2a+p2p are built")
             ctx_out = layers.ulysses_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group, st.cp,
                                                     rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         else:

@@ -773,3 +773,49 @@ def ring_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, cp_group, cp, 
         k = rope_fn(k, cos, sin, pos, rot_dim or d)
     out = ring_cp_attention(q.contiguous(), k.contiguous(), v.contiguous(), batch, cp_group, cp, scale)
     return out.reshape(Tl, hq * d)
+
+
+# ----------------------------------------------------------------------------------------------
+# Context parallelism (hierarchical): all-to-all inside a group of neighbouring ranks, ring across the groups
+def hierarchical_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, a2a_group, a2a, p2p_group, p2p, rot_dim=None,
+                                   scale=None):
+    """Causal self-attention under two-level context parallelism (the reference's ``cp_comm_type: a2a+p2p`` with
+    ``hierarchical_context_parallel_sizes: [a2a, p2p]``; primus/configs/models/megatron/language_model.yaml).
+
+    A sequence is cut into ``2 * p2p`` super-chunks; ring position ``i`` owns super-chunks ``i`` and ``2 p2p - 1 - i``
+    (zig-zag, balanced causal work) and the ``a2a`` ranks of that position each hold a consecutive ``1 / a2a`` of both.
+    One all-to-all inside the group turns that split into a head split (every rank: both whole super-chunks,
+    ``heads / a2a`` heads), ring attention runs across the groups on those heads, and the inverse all-to-all restores
+    the token split.  Only ``heads / a2a`` must be whole, so the ring carries the scaling beyond the head count and
+    the all-to-all keeps its traffic on the nearest links.  Returns [T_local, hq * d]."""
+    if a2a == 1:
+        return ring_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, p2p_group, p2p, rot_dim, scale)
+    assert hq % a2a == 0 and hkv % a2a == 0, "a2a+p2p context parallelism needs heads divisible by the all-to-all size"
+    Tl = qkv.shape[0]
+    part = Tl // batch // 2                       # tokens of one super-chunk held by this rank
+    hq_l, hkv_l = hq // a2a, hkv // a2a
+    q = qkv[:, : hq * d].reshape(Tl, hq, d)
+    k = qkv[:, hq * d: (hq + hkv) * d].reshape(Tl, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(Tl, hkv, d)
+    if cos is not None:
+        rope_fn = fused.rope if qkv.is_cuda else fused.rope_ref
+        q = rope_fn(q, cos, sin, pos, rot_dim or d)
+        k = rope_fn(k, cos, sin, pos, rot_dim or d)
+    send = torch.cat([q.reshape(Tl, a2a, hq_l * d), k.reshape(Tl, a2a, hkv_l * d), v.reshape(Tl, a2a, hkv_l * d)], dim=2)
+    send = send.permute(1, 0, 2).contiguous()                          # [a2a (destination), Tl, chunk]
+    recv = _SeqHeadAllToAll.apply(send, a2a_group)                     # [a2a (source part), batch * 2 * part, chunk]
+    chunk = recv.shape[2]
+    # [part owner, batch, super-chunk slot, part] -> [batch, slot, part owner, part]: both super-chunks whole, in order
+    full = recv.view(a2a, batch, 2, part, chunk).permute(1, 2, 0, 3, 4).reshape(batch * 2 * a2a * part, chunk)
+    T2 = full.shape[0]
+    ql = full[:, : hq_l * d].reshape(T2, hq_l, d).contiguous()
+    kl = full[:, hq_l * d: (hq_l + hkv_l) * d].reshape(T2, hkv_l, d).contiguous()
+    vl = full[:, (hq_l + hkv_l) * d:].reshape(T2, hkv_l, d).contiguous()
+    if p2p > 1:
+        out = ring_cp_attention(ql, kl, vl, batch, p2p_group, p2p, scale)
+    else:  # a single ring position holds the whole sequence: plain causal attention
+        out = rope_attention(full.contiguous(), None, None, None, batch, hq_l, hkv_l, d, rot_dim=rot_dim, causal=True,
+                             scale=scale)
+    out = out.reshape(batch, 2, a2a, part, hq_l * d).permute(2, 0, 1, 3, 4).reshape(a2a, Tl, hq_l * d).contiguous()
+    got = _SeqHeadAllToAll.apply(out, a2a_group)                       # [a2a (head group), Tl, hq_l * d]
+    return got.permute(1, 0, 2).reshape(Tl, hq * d)

@@ -39,6 +39,11 @@ class ParallelState:
     edp_rank: int = 0
     tp_group: Optional[object] = None
     cp_group: Optional[object] = None
+    # hierarchical context parallelism (a2a inside, ring outside): cp_rank = p2p_rank * cp_a2a + a2a_rank
+    cp_a2a: int = 1
+    cp_p2p: int = 1
+    cp_a2a_group: Optional[object] = None
+    cp_p2p_group: Optional[object] = None
     pp_group: Optional[object] = None
     pp_fwd_group: Optional[object] = None  # forward-direction p2p communicator
     pp_bwd_group: Optional[object] = None  # backward-direction p2p communicator
@@ -130,8 +135,11 @@ def init_distributed(backend: Optional[str] = None, timeout_minutes: float = 10.
 
 
 def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, etp: int = 1,
-                              virtual_pp: Optional[int] = None) -> ParallelState:
-    """Create all groups. Every rank must call this with identical arguments."""
+                              virtual_pp: Optional[int] = None, hierarchical_cp_sizes=None) -> ParallelState:
+    """Create all groups. Every rank must call this with identical arguments.  ``hierarchical_cp_sizes``: ``[a2a, p2p]``
+    with ``a2a * p2p == cp`` splits every context-parallel group into all-to-all groups of neighbouring ranks and ring
+    groups across them (the reference's ``hierarchical_context_parallel_sizes``,
+    primus/configs/models/megatron/language_model.yaml)."""
     global _STATE
     if not dist.is_initialized():
         assert tp * pp * cp * ep == 1, "model parallelism needs an initialised process group"
@@ -155,6 +163,21 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1
 
     st.tp_group, st.tp_ranks = make("tp")
     st.cp_group, _ = make("cp")
+    if hierarchical_cp_sizes:
+        a2a, p2p = (int(x) for x in hierarchical_cp_sizes)
+        assert a2a * p2p == cp, f"hierarchical_context_parallel_sizes {hierarchical_cp_sizes} must multiply to cp={cp}"
+        st.cp_a2a, st.cp_p2p = a2a, p2p
+        for ranks in lists["cp"]:
+            for i in range(p2p):                      # neighbouring ranks exchange heads
+                sub = ranks[i * a2a:(i + 1) * a2a]
+                g = dist.new_group(sub) if len(sub) > 1 else None
+                if rank in sub:
+                    st.cp_a2a_group = g
+            for j in range(a2a):                      # the ring runs across the all-to-all groups
+                sub = ranks[j::a2a]
+                g = dist.new_group(sub) if len(sub) > 1 else None
+                if rank in sub:
+                    st.cp_p2p_group = g
     st.dp_group, st.dp_ranks = make("dp")
     st.dp_cp_group, _ = make("dp_cp")
     st.pp_group, st.pp_ranks = make("pp")

@@ -3,14 +3,15 @@ import torch
 
 
 def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
-              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False):
+              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False, cp_sizes=None):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
     kw = dict(num_layers=layers, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
               vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
               expert_model_parallel_size=ep, context_parallel_size=cp, sequence_parallel=sp, make_vocab_size_divisible_by=64,
-              virtual_pipeline_model_parallel_size=vpp, cp_comm_type=cp_comm)
+              virtual_pipeline_model_parallel_size=vpp, cp_comm_type=cp_comm,
+              hierarchical_context_parallel_sizes=cp_sizes)
     if mla:
         kw.update(multi_latent_attention=True, kv_lora_rank=32, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16)
     if moe:
@@ -76,7 +77,8 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
     ps.destroy_model_parallel()
     mc, tc = tiny_cfgs(**kwargs)
     ps.initialize_model_parallel(tp=mc.tensor_model_parallel_size, pp=mc.pipeline_model_parallel_size,
-                                 ep=mc.expert_model_parallel_size, cp=mc.context_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size)
+                                 ep=mc.expert_model_parallel_size, cp=mc.context_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size,
+                                 hierarchical_cp_sizes=mc.hierarchical_context_parallel_sizes)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     load_from_full(tr, full_sd)
     losses = tr.train()

@@ -49,6 +49,7 @@ CASES = {
     "cp2_allgather_mla": dict(world=2, kw=dict(cp=2, cp_comm="allgather", mla=True)),
     "cp2_ring": dict(world=2, kw=dict(cp=2, cp_comm="p2p")),
     "cp4_ring_mla": dict(world=4, kw=dict(cp=4, cp_comm="p2p", mla=True, seq=64)),
+    "cp4_a2a_p2p": dict(world=4, kw=dict(cp=4, cp_comm="a2a+p2p", cp_sizes=[2, 2], seq=64)),
 }
 
 

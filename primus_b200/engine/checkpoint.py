@@ -193,6 +193,8 @@ def save_checkpoint(trainer, root: str, release: bool = False) -> str:
         writer = (st.edp_rank == 0) if spec["kind"] == "ep" else (st.dp_rank == 0 and st.cp_rank == 0)
         if spec["kind"] == "replicated" and st.tp_rank != 0:
             writer = False
+        if getattr(p, "embedding_replica", False):   # the first pipeline stage writes the shared word embeddings
+            writer = False
         if not writer:
             continue
         t = to_saved_layout(name, p.detach(), cfg, st.tp).cpu().clone()

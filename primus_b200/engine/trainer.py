@@ -214,6 +214,7 @@ class Trainer:
                             manual_split=getattr(train_cfg, "decoder_pipeline_manual_split_list", None))
             self.model_chunks.append(m)
         self.model = self.model_chunks[0]
+        self._init_embedding_replica()
         # ---------------------------------------------------------------- buffers + optimizer
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
         self.fsdp = bool(train_cfg.use_torch_fsdp2) and st.world_size > 1
@@ -236,12 +237,49 @@ class Trainer:
                                              train_cfg.adam_eps, train_cfg.weight_decay, train_cfg.clip_grad,
                                              train_cfg.check_for_nan_in_loss_and_grad)
 
+    # ------------------------------------------------------------------ word embeddings shared by first and last stage
+    def _init_embedding_replica(self):
+        """A tied output head or multi-token prediction under pipeline parallelism: the last stage holds a replica of the
+        first stage's word embeddings (``models/gpt.py``).  The replica gets a gradient buffer of its own and the first
+        stage's initial values."""
+        params = [p for m in self.model_chunks for p in m.parameters()]
+        self._emb_primary = [p for p in params if getattr(p, "embedding_primary", False)]
+        self._emb_replica = [p for p in params if getattr(p, "embedding_replica", False)]
+        if not (self._emb_primary or self._emb_replica):
+            return
+        if self._emb_primary and self._emb_replica:
+            raise NotImplementedError("first and last pipeline stage on the same rank (V-shaped placement) with a tied "
+                                      "output head or multi-token prediction is not built")
+        assert self.st.embedding_group is not None, "the embedding group exists for pipeline_model_parallel_size > 1"
+        for p in self._emb_replica:
+            p.main_grad = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+        self._sync_embedding_replica()
+
+    def _sync_embedding_replica(self):
+        """First stage -> last stage: current word-embedding weights."""
+        for p in self._emb_primary + self._emb_replica:
+            dist.broadcast(p.data, src=self.st.pp_ranks[0], group=self.st.embedding_group)
+
+    def _reduce_embedding_replica_grads(self):
+        """Last stage -> first stage: the replica's gradient joins the primary's before the data-parallel reduction."""
+        for p in self._emb_primary + self._emb_replica:
+            dist.all_reduce(p.main_grad, group=self.st.embedding_group)
+        for p in self._emb_replica:
+            p.main_grad.zero_()
+
     def _init_buffers_and_optimizer(self):
         model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
         dense, expert = [], []
         for m in self.model_chunks:
             for p in m.parameters():
+                if getattr(p, "embedding_replica", False):
+                    continue        # follows the first stage's copy; not an optimizer parameter
                 (expert if getattr(p, "is_expert", False) else dense).append(p)
+        if self._emb_primary and train_cfg.overlap_grad_reduce:
+            # the replica's gradient must be added before the bucket of the embedding is reduced
+            train_cfg.overlap_grad_reduce = False
+            self.log("overlap_grad_reduce is off on this run: the word embeddings are shared between the first and the "
+                     "last pipeline stage")
         self.buffers = []
         if dense:
             self.buffers.append(ParamGradBuffer(
@@ -397,6 +435,8 @@ class Trainer:
                 if p.grad is not None:  # gradients that came through plain autograd
                     p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                     p.grad = None
+        if self._emb_primary or self._emb_replica:
+            self._reduce_embedding_replica_grads()
         for buf in self.buffers:
             buf.finish_grad_sync()
         # sequence-parallel: norm weights saw only this rank's token shard
@@ -472,6 +512,10 @@ class Trainer:
             self.lora.optimizer_step(lr)
         else:
             self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+        if self._emb_primary or self._emb_replica:
+            for buf in self.buffers:
+                buf.finish_param_sync()        # the updated embedding must be complete before it is re-sent
+            self._sync_embedding_replica()
         timers("optimizer", 1).stop()
         if self.mcfg.moe_router_enable_expert_bias:
             st = self.st

@@ -274,11 +274,21 @@ class GPTModel(nn.Module):
             self.output_layer.weight.tensor_model_parallel = tp > 1
             self.output_layer.weight.partition_dim = 0
             self.output_layer.weight._fp8_exempt = True   # the LM head stays in bf16 under an fp8 recipe
+        # Tied output head or multi-token prediction on a last stage that is not also the first: the stage holds a replica
+        # of the word embeddings.  The first stage's copy is the trained one ("primary"); the trainer adds the replica's
+        # gradient to it before the data-parallel reduction and re-sends the weights after every optimizer step (the
+        # job of Megatron's embedding group; the replica is not an optimizer parameter, so it is counted once in the
+        # gradient norm and saved once).
+        needs_embedding = (not cfg.untie_embeddings_and_output_weights) or bool(cfg.mtp_num_layers)
+        if needs_embedding and post_process and not pre_process:
+            self.embedding = LanguageModelEmbedding(cfg, device, tp)
+            self.embedding.word_embeddings.weight.embedding_replica = True
+        if needs_embedding and pre_process and not post_process:
+            self.embedding.word_embeddings.weight.embedding_primary = True
         if post_process and cfg.mtp_num_layers:
             st = ps.get_state()
-            if not pre_process or tp > 1 or st.cp > 1:
-                raise NotImplementedError("multi-token prediction needs the embedding on the last pipeline stage and "
-                                          "tensor / context parallel size 1 (pp = tp = cp = 1)")
+            if tp > 1 or st.cp > 1:
+                raise NotImplementedError("multi-token prediction is built for tensor / context parallel size 1")
             self.mtp = nn.Module()
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
                                              for _ in range(cfg.mtp_num_layers)])

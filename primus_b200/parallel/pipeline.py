@@ -112,7 +112,7 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 hidden_in = (x[0], x[1], batch, seq)
             if s == S - 1:
                 w = trainer._loss_weights(mb)
-                out = model(mb["tokens"] if s == 0 else None, mb["labels"], loss_weights=w, hidden_in=hidden_in,
+                out = model(mb["tokens"], mb["labels"], loss_weights=w, hidden_in=hidden_in,
                             unit_upstream=True, position_ids=_pos_ids(trainer, mb),
                             cu_seqlens=mb.get("host_cu_seqlens"))
                 outputs[k] = out
@@ -199,7 +199,7 @@ def pipeline_warmup(trainer, micro_batch: dict) -> None:
                 x.requires_grad_(True)
                 hidden_in = (x[0], x[1], batch, seq)
             if s == S - 1:
-                out = model(micro_batch["tokens"] if s == 0 else None, micro_batch["labels"],
+                out = model(micro_batch["tokens"], micro_batch["labels"],
                             loss_weights=trainer._loss_weights(micro_batch), hidden_in=hidden_in, unit_upstream=True,
                             position_ids=_pos_ids(trainer, micro_batch))
                 out.backward()

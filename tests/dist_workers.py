@@ -3,7 +3,7 @@ import torch
 
 
 def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
-              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False, cp_sizes=None):
+              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False, cp_sizes=None, tied=False, mtp=0):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
@@ -11,7 +11,8 @@ def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2,
               vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
               expert_model_parallel_size=ep, context_parallel_size=cp, sequence_parallel=sp, make_vocab_size_divisible_by=64,
               virtual_pipeline_model_parallel_size=vpp, cp_comm_type=cp_comm,
-              hierarchical_context_parallel_sizes=cp_sizes)
+              hierarchical_context_parallel_sizes=cp_sizes, untie_embeddings_and_output_weights=not tied,
+              mtp_num_layers=mtp)
     if mla:
         kw.update(multi_latent_attention=True, kv_lora_rank=32, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16)
     if moe:

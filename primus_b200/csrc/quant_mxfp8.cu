@@ -51,10 +51,13 @@ constexpr int QUANT_SMEM = TILE * PITCH * 2;   // one staged bf16 tile; the fp8 
 // (row0, col0).  Called by all threads of a 256-thread CTA after the tile is complete (caller synchronises before).
 // Results are written straight from registers: 64 contiguous bytes per thread in the row direction, 8 bytes per row
 // (64 contiguous bytes per 8 lanes) in the column direction -- whole 32-byte sectors either way.
+// FIXED: every block takes the scale exponent `fixed_e` (one power-of-two scale for the whole tensor) instead of the
+// exponent of its own maximum.
+template <bool FIXED = false>
 __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, int R, int C,
                                                      int row0, int col0, uint8_t* __restrict__ q_row,
                                                      uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
-                                                     uint8_t* __restrict__ sf_col) {
+                                                     uint8_t* __restrict__ sf_col, int fixed_e = 0) {
   const int tid = threadIdx.x;
   if (q_row) {
     // thread -> (row r, two 32-element blocks): 64 contiguous bytes of the row
@@ -77,7 +80,7 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
-      const int e = e8m0_from_amax(amax);
+      const int e = FIXED ? fixed_e : e8m0_from_amax(amax);
       const float inv = inv_scale_from_e8m0(e);
       uint32_t w[8];
 #pragma unroll
@@ -122,8 +125,8 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       o = __shfl_xor_sync(0xffffffffu, w, 16);
       m[u] = __hmax2(m[u], *reinterpret_cast<__nv_bfloat162*>(&o));
       const float2 a = __bfloat1622float2(m[u]);
-      e[2 * u] = e8m0_from_amax(a.x);
-      e[2 * u + 1] = e8m0_from_amax(a.y);
+      e[2 * u] = FIXED ? fixed_e : e8m0_from_amax(a.x);
+      e[2 * u + 1] = FIXED ? fixed_e : e8m0_from_amax(a.y);
       inv[2 * u] = inv_scale_from_e8m0(e[2 * u]);
       inv[2 * u + 1] = inv_scale_from_e8m0(e[2 * u + 1]);
     }
@@ -168,6 +171,56 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
   }
   __syncthreads();
   quantize_staged_tile(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
+}
+
+// Tensor-wise FP8 ("current scaling" with a power-of-two scale): one scale 2^e for the whole tensor,
+// e = ceil(log2(amax / 448)) from the tensor maximum `tensor_amax` (device, written by amax_bf16_kernel).  The output has
+// the MXFP8 layout with that exponent in every block, so the block-scaled GEMM consumes it unchanged.  The behaviour
+// of the reference's tensor-wise quantiser (primus_turbo_cpp_extension::quantize_fp8_tensorwise, called from
+// primus/backends/megatron/core/extensions/primus_turbo_float8_local.py:66-70).
+__global__ void __launch_bounds__(256, 4)
+quant_tensorwise_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, const float* __restrict__ tensor_amax,
+                        uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
+                        uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
+  }
+  const int fixed_e = e8m0_from_amax(*tensor_amax);
+  __syncthreads();
+  quantize_staged_tile<true>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col, fixed_e);
+}
+
+// max |x| over n bf16 values (n a multiple of 8) into *out, which the caller zeroes first (non-negative floats order
+// like their bit patterns, so the cross-CTA step is an integer atomicMax)
+__global__ void __launch_bounds__(256)
+amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long n8, float* __restrict__ out) {
+  __nv_bfloat162 m = __floats2bfloat162_rn(0.f, 0.f);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const uint4 d = reinterpret_cast<const uint4*>(x)[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) m = __hmax2(m, __habs2(h[u]));
+  }
+  const float2 f = __bfloat1622float2(m);
+  float v = fmaxf(f.x, f.y);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __shared__ float s[8];
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) v = fmaxf(v, s[i]);
+    if (v != v) v = __uint_as_float(0x7f800000u);   // NaN in the input: report +inf
+    atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(v));
+  }
 }
 
 __device__ __forceinline__ void bf8_load(const __nv_bfloat16* p, float* f) {
@@ -299,6 +352,27 @@ int pb_quant_mxfp8(const void* x, int R, int C, void* q_row, void* sf_row, void*
   quant_mxfp8_kernel<<<grid, 256, SMEM, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), R, C,
                                          reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row),
                                          reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+// Tensor-wise FP8 of x [R, C] (multiples of 128): amax[0] receives max |x|; outputs as pb_quant_mxfp8.
+int pb_quant_fp8_tensorwise(const void* x, int R, int C, float* amax, void* q_row, void* sf_row, void* q_col, void* sf_col,
+                            cudaStream_t s) {
+  if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(quant_tensorwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QUANT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+  if (e != cudaSuccess) return (int)e;
+  const long n8 = (long)R * C / 8;
+  const int blocks = (int)((n8 + 2047) / 2048 < 1184 ? (n8 + 2047) / 2048 : 1184);
+  amax_bf16_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), n8, amax);
+  quant_tensorwise_kernel<<<dim3(C / TILE, R / TILE), 256, QUANT_SMEM, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), R, C, amax, reinterpret_cast<uint8_t*>(q_row),
+      reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
   return (int)cudaGetLastError();
 }
 

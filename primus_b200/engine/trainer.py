@@ -193,7 +193,10 @@ class Trainer:
         from ..ops import gemm as _gemm
 
         # fp8 recipe of the linear-layer GEMMs (attention, the LM head and the router stay in bf16)
-        _gemm.set_fp8_recipe("mxfp8" if (model_cfg.fp8 and model_cfg.fp8_recipe == "mxfp8") else None)
+        if model_cfg.fp8 and model_cfg.fp8_recipe not in ("mxfp8", "tensorwise"):
+            raise NotImplementedError(f"fp8_recipe {model_cfg.fp8_recipe!r}: mxfp8 (a scale per 32 elements) and tensorwise "
+                                      "(one power-of-two scale per tensor) are built")
+        _gemm.set_fp8_recipe(model_cfg.fp8_recipe if model_cfg.fp8 else None)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
         # ---------------------------------------------------------------- model chunks

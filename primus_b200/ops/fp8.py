@@ -56,10 +56,18 @@ def _e8m0(amax: torch.Tensor) -> torch.Tensor:
     return torch.where(amax == 0, torch.zeros_like(e), e)
 
 
-def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) -> MXFP8Tensor:
+# Tensor-wise recipe: one power-of-two scale per tensor (every block carries the exponent of the tensor maximum).
+# Set by ``ops.gemm.set_fp8_recipe("tensorwise")``; ``quantize_mxfp8`` follows it unless told otherwise.
+TENSORWISE = False
+
+
+def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = True,
+                       tensorwise: Optional[bool] = None) -> MXFP8Tensor:
     R, C = x.shape
     assert R % TILE == 0 and C % TILE == 0
     xf = x.float()
+    tensorwise = TENSORWISE if tensorwise is None else tensorwise
+    e_all = _e8m0(xf.abs().amax().reshape(1)) if tensorwise else None
     out = MXFP8Tensor(shape=(R, C))
     dev = x.device
     for direction in ("row", "col"):
@@ -68,6 +76,7 @@ def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = Tr
         if direction == "row":
             blocks = xf.view(R, C // BLOCK, BLOCK)
             e = _e8m0(blocks.abs().amax(-1))                       # [R, C/32]
+            e = e_all.expand_as(e).contiguous() if tensorwise else e
             inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
             q = (blocks * inv[..., None]).reshape(R, C)
             mn = torch.arange(R, device=dev)[:, None].expand(R, C // BLOCK)
@@ -76,6 +85,7 @@ def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = Tr
         else:
             blocks = xf.view(R // BLOCK, BLOCK, C)
             e = _e8m0(blocks.abs().amax(1))                        # [R/32, C]
+            e = e_all.expand_as(e).contiguous() if tensorwise else e
             inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
             q = (blocks * inv[:, None, :]).reshape(R, C)
             mn = torch.arange(C, device=dev)[None, :].expand(R // BLOCK, C)
@@ -101,10 +111,14 @@ def dequantize_mxfp8_ref(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> to
     return q.view(torch.float8_e4m3fn).float() * torch.exp2(e - 127.0)
 
 
-def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) -> MXFP8Tensor:
-    """bf16 [R, C] (R, C multiples of 128) -> MXFP8 in the requested directions (one kernel)."""
+def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True,
+                   tensorwise: Optional[bool] = None) -> MXFP8Tensor:
+    """bf16 [R, C] (R, C multiples of 128) -> MXFP8 in the requested directions (one kernel).  ``tensorwise`` (default:
+    the module switch ``TENSORWISE``): a single power-of-two scale for the whole tensor (maximum reduction + quantiser,
+    ``pb_quant_fp8_tensorwise``) in the same storage layout."""
+    tensorwise = TENSORWISE if tensorwise is None else tensorwise
     if not x.is_cuda:
-        return quantize_mxfp8_ref(x, rowwise, colwise)
+        return quantize_mxfp8_ref(x, rowwise, colwise, tensorwise)
     R, C = x.shape
     assert R % TILE == 0 and C % TILE == 0, "MXFP8 quantisation needs dimensions that are multiples of 128"
     x = x.contiguous()
@@ -118,7 +132,11 @@ def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True) 
     if colwise:
         out.q_col = torch.empty(R, C, dtype=torch.uint8, device=dev)
         out.sf_col = torch.empty(R * C // BLOCK, dtype=torch.uint8, device=dev)
-    _lib.call("quant_mxfp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
+    if tensorwise:
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        _lib.call("quant_fp8_tensorwise", x, R, C, amax, out.q_row, out.sf_row, out.q_col, out.sf_col)
+    else:
+        _lib.call("quant_mxfp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
     return out
 
 

@@ -31,8 +31,12 @@ _ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
 
 def set_fp8_recipe(recipe: str | None) -> None:
     global _FP8_RECIPE, _WEIGHT_GEN
-    assert recipe in (None, "", "mxfp8"), f"unsupported fp8 recipe {recipe!r}"
+    assert recipe in (None, "", "mxfp8", "tensorwise"), f"unsupported fp8 recipe {recipe!r}"
     _FP8_RECIPE = recipe or None
+    # "tensorwise": one power-of-two scale per tensor, stored in the MXFP8 layout, so the GEMMs are the same kernels
+    from . import fp8
+
+    fp8.TENSORWISE = recipe == "tensorwise"
     _WEIGHT_GEN += 1        # quantised weights cached elsewhere (expert weights) are keyed on this counter
     _W_CACHE.clear()
     _ACT_CACHE.clear()

@@ -127,7 +127,8 @@ def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_p
 def _swiglu_fp8_fusable(h1, weight, probs, tp_group, act="silu") -> bool:
     """MXFP8 recipe on, plain (no routing probabilities, no tensor parallelism) and every dimension a multiple of 128:
     the SwiGLU kernels then emit MXFP8 directly for the GEMMs around them."""
-    if gemm.fp8_recipe() is None or not gemm.FUSE_SWIGLU_QUANT or probs is not None or tp_group is not None:
+    # the fused SwiGLU + quantisation kernels scale per block: only under the MXFP8 recipe
+    if gemm.fp8_recipe() != "mxfp8" or not gemm.FUSE_SWIGLU_QUANT or probs is not None or tp_group is not None:
         return False
     if fused.GATE_KINDS[act] != 0:      # the fused quantising kernels implement the SiLU gate only
         return False

@@ -41,3 +41,26 @@ def test_round_trip_error_and_cpu_linear():
     ref = x.float() @ w.float().t()
     cos = torch.nn.functional.cosine_similarity(y.float().flatten(), ref.flatten(), dim=0)
     assert cos > 0.995
+
+
+def test_tensorwise_recipe_uses_one_power_of_two_scale():
+    """fp8_recipe tensorwise: every block carries the exponent of the tensor maximum, the dequantised values are the
+    E4M3 rounding of x / 2^e, and both storage directions hold the same numbers."""
+    torch.manual_seed(0)
+    x = (torch.randn(256, 384) * 3).bfloat16()
+    q = fp8.quantize_mxfp8_ref(x, True, True, tensorwise=True)
+    e = fp8._e8m0(x.float().abs().amax().reshape(1)).item()
+    assert (q.sf_row == e).all() and (q.sf_col == e).all()
+    assert 448.0 / 2 < x.float().abs().max().item() / 2.0 ** (e - 127) <= 448.0
+    want = (x.float() / 2.0 ** (e - 127)).to(torch.float8_e4m3fn).float() * 2.0 ** (e - 127)
+    d_row = fp8.dequantize_mxfp8_ref(q.q_row, q.sf_row, False)
+    d_col = fp8.dequantize_mxfp8_ref(q.q_col, q.sf_col, True)
+    assert torch.equal(d_row, want) and torch.equal(d_col, want)
+    # the module switch (set by the recipe) is the default of the quantiser
+    from primus_b200.ops import gemm
+    try:
+        gemm.set_fp8_recipe("tensorwise")
+        assert fp8.TENSORWISE and torch.equal(fp8.quantize_mxfp8(x, True, False).sf_row, q.sf_row)
+    finally:
+        gemm.set_fp8_recipe(None)
+    assert not fp8.TENSORWISE

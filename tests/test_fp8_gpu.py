@@ -23,6 +23,22 @@ def test_quantize_matches_reference_bitwise(R, C):
         assert (err <= x.float().abs() * 0.0626 + 1e-30).all() or err.max() <= 0.07 * x.float().abs().max()
 
 
+@pytest.mark.parametrize("R,C", [(128, 128), (1024, 512), (4096, 2048)])
+def test_tensorwise_quantiser_matches_reference_bitwise(R, C):
+    """One power-of-two scale for the whole tensor (maximum reduction + quantiser), MXFP8 storage layout."""
+    torch.manual_seed(1)
+    x = (torch.randn(R, C, device="cuda") * torch.exp(torch.randn(R, 1, device="cuda") * 2)).bfloat16()
+    q = fp8.quantize_mxfp8(x, True, True, tensorwise=True)
+    ref = fp8.quantize_mxfp8_ref(x, True, True, tensorwise=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for name in ("q_row", "sf_row", "q_col", "sf_col"):
+        assert torch.equal(getattr(q, name), getattr(ref, name)), name
+    assert q.sf_row.unique().numel() == 1
+    only_row = fp8.quantize_mxfp8(x, True, False, tensorwise=True)
+    assert only_row.q_col is None and torch.equal(only_row.q_row, ref.q_row)
+
+
 def _ref_gemm(aq, asf, a_col, bq, bsf, b_col, a_mn, b_mn):
     A = fp8.dequantize_mxfp8(aq, asf, a_col)
     B = fp8.dequantize_mxfp8(bq, bsf, b_col)
@@ -97,22 +113,23 @@ def test_model_training_with_mxfp8_recipe_tracks_bf16():
     ps.initialize_model_parallel()
     losses = {}
     try:
-        for recipe in (None, "e4m3"):
+        for recipe, kind in ((None, "mxfp8"), ("e4m3", "mxfp8"), ("e4m3", "tensorwise")):
             mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2,
                                    num_query_groups=2, vocab_size=1024, params_dtype="bf16", seq_length=256, fp8=recipe,
-                                   fp8_recipe="mxfp8")
+                                   fp8_recipe=kind)
             tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=256, train_iters=6, lr=2e-3,
                              lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1)
             torch.manual_seed(0)
             tr = Trainer(mc, tc, device="cuda", log_fn=lambda s: None)
-            assert gemm.fp8_recipe() == ("mxfp8" if recipe else None)
-            losses[recipe] = tr.train()
+            assert gemm.fp8_recipe() == (kind if recipe else None)
+            losses[(recipe, kind)] = tr.train()
             torch.cuda.synchronize()
             _lib.check_status()
     finally:
         gemm.set_fp8_recipe(None)
-    a, b = losses[None], losses["e4m3"]
+    a, b, c = losses[(None, "mxfp8")], losses[("e4m3", "mxfp8")], losses[("e4m3", "tensorwise")]
     assert all(abs(x - y) <= 0.02 * abs(x) for x, y in zip(a, b)), (a, b)
+    assert all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, c)), (a, c)
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024)])

@@ -44,7 +44,8 @@ constexpr int TMEM_COLS = 2 * BN;
 enum { MODE_AG = 0, MODE_RS = 1 };
 constexpr int MAX_TP = 8;
 constexpr int RS_RING_BYTES = STAGES * STAGE_BYTES + 2 * EPI_BUF_BYTES;  // copy CTAs of the reduce-scatter: ring of slots
-constexpr int RS_MAX_SLOTS = 16;                                        // + their barriers in the 256 spare bytes
+constexpr int RS_MAX_SLOTS = 16;
+constexpr int MAX_RB = 256;                                             // 128-row blocks per chunk (rows / tp <= 32768)                                        // + their barriers in the 256 spare bytes
 
 struct TpArgs {
   int mode, tp, rank, epoch;
@@ -57,12 +58,18 @@ struct TpArgs {
   __nv_bfloat16* gather;
   // RS: peers' partial buffers [M, N], fp32 accumulator [rows_per_chunk, N], output [rows_per_chunk, N]
   const __nv_bfloat16* peer_partial[MAX_TP];
-  float* acc;
+  __nv_bfloat16* acc;
   __nv_bfloat16* out;
   // local monotonic counters: [0,tp) chunk progress (AG: copy CTAs done; RS: tiles done, own slot: copy CTAs whose
   // share of the accumulator is final), [tp,2tp) reads done
   int* counters;
   int tiles_per_chunk;
+  // reduce-scatter, per 128-row block (monotonic over epochs): rb_ready[b] = accumulator pieces of my row block b that are
+  // complete; rb_tiles[chunk * MAX_RB + b] = finished tiles of row block b of a remote chunk; published[chunk] = row blocks
+  // of that chunk announced to its owner, (epoch - 1) * blocks_per_chunk + count
+  int* rb_ready;
+  int* rb_tiles;
+  int* published;
   // symmetric flags: slot r = "rank r's data is ready for me", slot tp + r = "rank r finished reading mine"
   int* peer_flags[MAX_TP];
   int* local_flags;
@@ -74,6 +81,7 @@ struct Barriers {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t acc_full;   // reduce-scatter: accumulator tile of an own tile has landed in the staging buffer
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -98,17 +106,28 @@ __device__ __forceinline__ bool wait_counter_geq(const int* ctr, int value) {
   return false;
 }
 
+// reduce-scatter: bytes per accumulator piece (one bulk copy per source) for a tensor-parallel size
+__host__ __device__ __forceinline__ int rs_piece_bytes(int tp) {
+  const int g = tp - 1;
+  return (g <= 2) ? 16384 : 8192;
+}
+
 // chunk processed k-th by this rank
 __device__ __forceinline__ int chunk_at(const TpArgs& a, int k) {
   return (a.mode == MODE_AG) ? (a.rank + k) % a.tp : (a.rank + 1 + k) % a.tp;
 }
 
-// tile -> (chunk, m-block, n-block): chunk-major, inside a chunk m fastest (A tiles of one n sweep stay in L2)
+// tile -> (chunk, m-block, n-block): chunk-major; all-gather: inside a chunk m fastest (A tiles of one n sweep stay in L2)
 __device__ __forceinline__ void tile_coords(const TpArgs& a, int tile, int num_n, int& chunk, int& mb, int& nb) {
   const int k = tile / a.tiles_per_chunk;
   const int t = tile - k * a.tiles_per_chunk;
   const int mbc = a.rows_per_chunk / BM;
   chunk = chunk_at(a, k);
+  if (a.mode == MODE_RS) {  // row-block major: the 128-row blocks of a chunk finish in order and are handed on one by one
+    mb = chunk * mbc + t / num_n;
+    nb = t - (t / num_n) * num_n;
+    return;
+  }
   mb = chunk * mbc + t % mbc;
   nb = t / mbc;
 }
@@ -216,19 +235,16 @@ __device__ void comm_main(const TpArgs& a) {
     }
   } else {
     // reduce-scatter: my rows are [rank * rows_per_chunk, +rows_per_chunk) of every rank's partial buffer.  The copy
-    // CTAs add the REMOTE partials into the fp32 accumulator while the GEMM runs; this rank's own tiles of those rows
-    // come last in its tile order, and their epilogue adds the accumulator and writes the bf16 result, so nothing
-    // is left to do once the GEMM has finished.  The sources are taken in arrival order (rank-1 finishes my rows
-    // first) in groups of up to `rs_group` (<= 4): per piece a ring slot receives one bulk copy per source of the group
-    // (plus the accumulator piece from the second group on), the threads add them in fp32 and store the sums with
-    // ordinary coalesced stores.  tp <= 5 needs one pass, tp = 8 two.
-    constexpr int RS_MAXG = 4;
-    const int nsrc = a.tp - 1;
-    int G = a.rs_group < 1 ? 1 : (a.rs_group > RS_MAXG ? RS_MAXG : a.rs_group);
-    if (G > nsrc) G = nsrc;
-    const bool multi = nsrc > G;  // several passes: the accumulator piece travels through the slot as well
-    const int PIECE = (G == 1) ? 32768 : ((G == 2) ? 16384 : 8192);
-    const int slot_bytes = G * PIECE + (multi ? 2 * PIECE : 0);
+    // CTAs add the REMOTE partials of those rows into the bf16 accumulator while the GEMM runs; this rank's own tiles of
+    // the rows come last in its tile order, and their epilogue adds the accumulator tile and writes the result, so
+    // nothing is left to do once the GEMM has finished.  Everything moves in row-block (128 rows) order: a source
+    // publishes how many row blocks of my rows it has finished, a piece is fetched as soon as every source has
+    // published its row block, and the epilogue of an own tile waits only for the accumulator pieces of its row block.
+    // Per piece a ring slot receives one bulk copy per source; the threads add them in fp32 into the first copy
+    // (a single source needs no arithmetic) and the sum leaves by a bulk store.
+    const int G = a.tp - 1;  // sources per piece: every remote rank, one pass
+    const int PIECE = rs_piece_bytes(a.tp);
+    const int slot_bytes = G * PIECE;
     int nslot = RS_RING_BYTES / slot_bytes;
     if (nslot > RS_MAX_SLOTS) nslot = RS_MAX_SLOTS;
     uint64_t* rbars = reinterpret_cast<uint64_t*>(bufs + RS_RING_BYTES);
@@ -238,73 +254,127 @@ __device__ void comm_main(const TpArgs& a) {
     }
     __syncthreads();
     const long total_bytes = (long)a.rows_per_chunk * a.N * 2;
+    const long rb_bytes = (long)BM * a.N * 2;           // a multiple of PIECE (N % 128 == 0)
+    const int mbc = a.rows_per_chunk / BM;
+    const int flag_base = (a.epoch - 1) * mbc;
     const long row_off_bytes = (long)a.rank * total_bytes;
-    const long pieces = (total_bytes + PIECE - 1) / PIECE;
+    const long pieces = total_bytes / PIECE;
     const long mine = (pieces - cta + a.comm_ctas - 1) / a.comm_ctas;
     auto piece_off = [&](long i) { return ((long)cta + i * a.comm_ctas) * PIECE; };
-    auto piece_len = [&](long i) {
-      const long off = piece_off(i);
-      return (uint32_t)((total_bytes - off) < PIECE ? (total_bytes - off) : PIECE);
-    };
     uint8_t* accg = reinterpret_cast<uint8_t*>(a.acc);
-    for (int k0 = 1; k0 <= nsrc; k0 += G) {
-      const int cnt = (k0 + G - 1 <= nsrc) ? G : (nsrc - k0 + 1);
-      const bool has_acc = k0 > 1;
-      const uint8_t* srcs[RS_MAXG];
+    const uint8_t* srcs[MAX_TP];
+    int src_rank[MAX_TP];
 #pragma unroll
-      for (int j = 0; j < RS_MAXG; ++j) {
-        const int p = (a.rank - (k0 + (j < cnt ? j : 0)) + 2 * a.tp) % a.tp;
-        srcs[j] = reinterpret_cast<const uint8_t*>(a.peer_partial[p]) + row_off_bytes;
+    for (int j = 0; j < MAX_TP; ++j) {
+      const int p = (a.rank - 1 - (j < G ? j : 0) + 2 * a.tp) % a.tp;  // arrival order: rank-1 does my rows first
+      src_rank[j] = p;
+      srcs[j] = reinterpret_cast<const uint8_t*>(a.peer_partial[p]) + row_off_bytes;
+    }
+    int rb_known = -1;  // every source has published row blocks <= rb_known (thread 0 only)
+    // 0: issued; 1: a source has not published the row block yet (only when !blocking); 2: gave up waiting
+    auto issue_load = [&](long i, bool blocking) -> int {
+      const long off = piece_off(i);
+      const int rb = (int)(off / rb_bytes);
+      if (rb > rb_known) {
+        for (int j = 0; j < G; ++j) {
+          const int* f = a.local_flags + src_rank[j];
+          if (blocking) {
+            if (!pb::wait_flag_geq(f, flag_base + rb + 1)) return 2;
+          } else {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v < flag_base + rb + 1) return 1;
+          }
+        }
+        rb_known = rb;
+        asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written by the source's TMA stores
       }
+      const int slot = (int)(i % nslot);
+      uint8_t* sb = bufs + slot * slot_bytes;
+      pb::mbar_expect_tx(&rbars[slot], (uint32_t)(G * PIECE));
+      for (int j = 0; j < G; ++j) bulk_g2s(sb + j * PIECE, srcs[j] + off, PIECE, &rbars[slot]);
+      return 0;
+    };
+    // accumulator pieces whose bulk store has completed are announced to the epilogue (counter per row block)
+    // (batched per row block: one fence + one atomic when this CTA's pieces move on to the next row block)
+    int ann_rb = -1, ann_cnt = 0;
+    auto announce_flush = [&]() {
+      if (ann_cnt) {
+        __threadfence();
+        atomicAdd(a.rb_ready + ann_rb, ann_cnt);
+      }
+      ann_cnt = 0;
+    };
+    auto announce = [&](long i) {
+      const int rb = (int)(piece_off(i) / rb_bytes);
+      if (rb != ann_rb) announce_flush();
+      ann_rb = rb;
+      ++ann_cnt;
+    };
+    constexpr int STORE_LAG = 2;
+    long issued = 0;
+    // issue what the ring can take (slot of piece i is free once the store of piece i - nslot has read it, i.e.
+    // i <= last_read + nslot); wait for a source only if piece `needed` would otherwise not be in flight
+    auto top_up = [&](long last_read, long needed) {
+      while (issued < mine && issued <= last_read + nslot) {
+        const int rc = issue_load(issued, issued <= needed);
+        if (rc == 1) break;
+        if (rc == 2) {
+          atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+          s_ok = 0;
+          break;
+        }
+        ++issued;
+      }
+    };
+    if (tid == 0) top_up(-1, 0);
+    __syncthreads();
+    // thread 0: store the finished piece, announce older ones, refill the ring
+    auto finish_piece = [&](long done, uint8_t* sb) {
+      bulk_s2g(accg + piece_off(done), sb, PIECE);
+      pb::tma_store_commit();
+      pb::tma_store_wait_all<STORE_LAG>();   // stores of pieces <= done - STORE_LAG are complete in global memory
+      if (done >= STORE_LAG) announce(done - STORE_LAG);
+      pb::tma_store_wait_read<1>();          // the stores of pieces <= done - 1 have read their slots
+      top_up(done - 1, done + 1);
+    };
+    if (G == 1) {
+      // a single source: the accumulator is a copy; thread 0 runs the ring alone
       if (tid == 0) {
-        for (int j = 0; j < cnt; ++j) {
-          const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
-          if (!pb::wait_flag_geq(a.local_flags + p, a.epoch)) {
+        for (long done = 0; done < mine && s_ok; ++done) {
+          const int slot = (int)(done % nslot);
+          if (!pb::mbar_wait(&rbars[slot], (uint32_t)((done / nslot) & 1))) {
             atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
             s_ok = 0;
             break;
           }
+          finish_piece(done, bufs + slot * slot_bytes);
         }
       }
-      __syncthreads();
-      if (!s_ok) break;
-      auto issue_load = [&](long i) {
-        const int slot = (int)((g + i) % nslot);
-        const uint32_t len = piece_len(i);
-        uint8_t* sb = bufs + slot * slot_bytes;
-        pb::mbar_expect_tx(&rbars[slot], cnt * len + (has_acc ? 2 * len : 0));
-        for (int j = 0; j < cnt; ++j) bulk_g2s(sb + j * PIECE, srcs[j] + piece_off(i), len, &rbars[slot]);
-        if (has_acc) bulk_g2s(sb + G * PIECE, accg + 2 * piece_off(i), 2 * len, &rbars[slot]);
-      };
-      long issued = 0;
-      if (tid == 0) {
-        asm volatile("fence.proxy.async;" ::: "memory");  // accumulator pieces of the previous pass: ordinary stores
-        for (; issued < mine && issued < nslot; ++issued) issue_load(issued);
-      }
+    } else {
       for (long done = 0; done < mine; ++done) {
-        const long gi = g + done;
-        const int slot = (int)(gi % nslot);
-        if (!pb::mbar_wait(&rbars[slot], (uint32_t)((gi / nslot) & 1))) {
+        const int slot = (int)(done % nslot);
+        uint8_t* sb = bufs + slot * slot_bytes;
+        if (!pb::mbar_wait(&rbars[slot], (uint32_t)((done / nslot) & 1))) {
           atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
           s_ok = 0;
         }
         __syncthreads();
-        if (!s_ok) break;
-        const int nvec = piece_len(done) / 16;
-        const uint8_t* sb = bufs + slot * slot_bytes;
-        const float4* sacc = reinterpret_cast<const float4*>(sb + G * PIECE);
-        float4* gout = reinterpret_cast<float4*>(accg + 2 * piece_off(done));
-        for (int i = tid; i < nvec; i += nthr) {
+        if (!s_ok) break;   // uniform: s_ok is only written before this barrier
+        uint4* s0 = reinterpret_cast<uint4*>(sb);
+        for (int i = tid; i < PIECE / 16; i += nthr) {
           float f[8];
-          if (has_acc) {
-            const float4 a0 = sacc[2 * i], a1 = sacc[2 * i + 1];
-            f[0] = a0.x; f[1] = a0.y; f[2] = a0.z; f[3] = a0.w;
-            f[4] = a1.x; f[5] = a1.y; f[6] = a1.z; f[7] = a1.w;
-          } else {
+          const uint4 v0 = s0[i];
+          {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = 0.f;
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(h[j]);
+              f[2 * j] = t.x;
+              f[2 * j + 1] = t.y;
+            }
           }
-          for (int sj = 0; sj < cnt; ++sj) {
+          for (int sj = 1; sj < G; ++sj) {
             const uint4 v = reinterpret_cast<const uint4*>(sb + sj * PIECE)[i];
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -314,33 +384,30 @@ __device__ void comm_main(const TpArgs& a) {
               f[2 * j + 1] += t.y;
             }
           }
-          gout[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
-          gout[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
+          uint4 o;
+          o.x = pb::pack_bf16x2(f[0], f[1]);
+          o.y = pb::pack_bf16x2(f[2], f[3]);
+          o.z = pb::pack_bf16x2(f[4], f[5]);
+          o.w = pb::pack_bf16x2(f[6], f[7]);
+          s0[i] = o;
         }
-        __syncthreads();  // every thread has read the slot: it can take the next piece
-        if (tid == 0 && issued < mine) {
-          issue_load(issued);
-          ++issued;
-        }
+        pb::fence_proxy_async_smem();
+        __syncthreads();
+        if (tid == 0) finish_piece(done, sb);
       }
-      if (!s_ok) break;
-      g += mine;
-      __threadfence();
-      asm volatile("fence.proxy.async;" ::: "memory");  // the next pass reads these sums with bulk copies
-      __syncthreads();
-      if (tid == 0) {
-        for (int j = 0; j < cnt; ++j) {
-          const int p = (a.rank - (k0 + j) + 2 * a.tp) % a.tp;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      pb::tma_store_wait_all<0>();
+      if (s_ok) {
+        for (long i = (mine > STORE_LAG ? mine - STORE_LAG : 0); i < mine; ++i) announce(i);
+        announce_flush();
+        for (int j = 0; j < G; ++j) {   // every load from the sources has landed: they may reuse their buffers
+          const int p = src_rank[j];
           const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
           if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
         }
       }
-    }
-    // this CTA's share of the accumulator is final: the epilogue of this rank's own tiles may add it
-    __syncthreads();
-    if (tid == 0 && s_ok) {
-      __threadfence();
-      atomicAdd(a.counters + a.rank, 1);
     }
   }
   // leave only when every peer has finished reading this rank's buffers (they may be reused right after)
@@ -354,7 +421,7 @@ template <int B_MN>
 __global__ void __launch_bounds__(256, 1)
 gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAown,
-                     const __grid_constant__ TpArgs a) {
+                     const __grid_constant__ CUtensorMap tmAcc, const __grid_constant__ TpArgs a) {
   if (blockIdx.x < a.comm_ctas) {
     comm_main(a);
     return;
@@ -385,6 +452,7 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       pb::mbar_init(&bars->tmem_full[i], 1);
       pb::mbar_init(&bars->tmem_empty[i], EPI_THREADS);
     }
+    pb::mbar_init(&bars->acc_full, 1);
     bars->abort_flag = 0;
     pb::fence_barrier_init();
   }
@@ -500,24 +568,27 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
-    bool acc_ready = false;
+    uint32_t acc_full_phase = 0;
     for (int tile = gemm_cta; tile < num_tiles && ok; tile += num_gemm) {
       int chunk, mb, nb;
       tile_coords(a, tile, num_n, chunk, mb, nb);
       const int m0 = mb * BM, n0 = nb * BN;
-      // reduce-scatter, this rank's own rows: add the sum of the remote partials and write the final result
+      // reduce-scatter, this rank's own rows: add the sum of the remote partials (accumulator tile, fetched by TMA into
+      // the staging buffer) and write the final result.  Only the accumulator pieces of this row block must be there.
       const bool fin = (a.mode == MODE_RS && chunk == a.rank);
-      if (fin && !acc_ready) {
-        if (et == 0 && !wait_counter_geq(a.counters + a.rank, a.epoch * a.comm_ctas)) {
-          atomicCAS(status, 0, PB_ERR_TIMEOUT_FLAG);
-          bars->abort_flag = 1;
+      if (fin) {
+        if (et == 0) {
+          const int rb = mb - a.rank * (a.rows_per_chunk / BM);
+          const int want = a.epoch * (int)(((long)BM * a.N * 2) / rs_piece_bytes(a.tp));
+          if (!wait_counter_geq(a.rb_ready + rb, want)) {
+            atomicCAS(status, 0, PB_ERR_TIMEOUT_FLAG);
+            bars->abort_flag = 1;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");  // the pieces were written by other SMs' bulk stores
         }
         pb::named_bar_sync(1, EPI_THREADS);
         if (*abort_flag) break;
-        acc_ready = true;
       }
-      const float4* acc_row =
-          fin ? reinterpret_cast<const float4*>(a.acc + (size_t)(m0 - a.rank * a.rows_per_chunk + row) * a.N + n0) : nullptr;
       if (!wait_or_abort(&bars->tmem_full[acc], acc_phase, abort_flag)) {
         if (!*abort_flag) atomicCAS(status, 0, PB_ERR_TIMEOUT_EPILOGUE);
         bars->abort_flag = 1;
@@ -531,26 +602,39 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t r[64];
         pb::tmem_ld_32x32b_x32(t_row + c * 64, r);
         pb::tmem_ld_32x32b_x32(t_row + c * 64 + 32, r + 32);
-        const bool add = fin && (n0 + c * 64 < a.N);
-        float4 av[16];
-        if (add) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) av[j] = __ldcg(acc_row + c * 16 + j);
-        }
         pb::tmem_wait_ld();
-        if (add) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            r[4 * j + 0] = __float_as_uint(__uint_as_float(r[4 * j + 0]) + av[j].x);
-            r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + av[j].y);
-            r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + av[j].z);
-            r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + av[j].w);
-          }
-        }
-        if (et == 0) pb::tma_store_wait_read<1>();
-        pb::named_bar_sync(1, EPI_THREADS);
         uint8_t* stage_buf = smem_epi + buf * EPI_BUF_BYTES;
         uint8_t* my_row = stage_buf + row * 128;
+        const bool add = fin && (n0 + c * 64 < a.N);
+        if (et == 0) {
+          pb::tma_store_wait_read<1>();
+          if (add) {  // the accumulator tile lands where the result is staged (same 128-byte swizzle)
+            pb::mbar_expect_tx(&bars->acc_full, EPI_BUF_BYTES);
+            pb::tma_load_2d(stage_buf, &tmAcc, &bars->acc_full, n0 + c * 64, m0 - a.rank * a.rows_per_chunk);
+          }
+        }
+        pb::named_bar_sync(1, EPI_THREADS);
+        if (add) {
+          if (!wait_or_abort(&bars->acc_full, acc_full_phase, abort_flag)) {
+            if (!*abort_flag) atomicCAS(status, 0, PB_ERR_TIMEOUT_EPILOGUE);
+            bars->abort_flag = 1;
+            ok = false;
+          }
+          acc_full_phase ^= 1;
+          if (ok) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 v = *reinterpret_cast<const uint4*>(my_row + ((j ^ (row & 7)) << 4));
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 t = __bfloat1622float2(h[u]);
+                r[8 * j + 2 * u] = __float_as_uint(__uint_as_float(r[8 * j + 2 * u]) + t.x);
+                r[8 * j + 2 * u + 1] = __float_as_uint(__uint_as_float(r[8 * j + 2 * u + 1]) + t.y);
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint4 v;
@@ -579,9 +663,31 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         // the tile's rows must be complete in global memory before the destination is told about them
         pb::tma_store_wait_all<0>();
         __threadfence_system();
-        const int done = atomicAdd(a.counters + chunk, 1) + 1;
-        if (done == a.epoch * a.tiles_per_chunk)
-          pb::set_flag_release(a.peer_flags[chunk] + a.rank, a.epoch);
+        const int mbc = a.rows_per_chunk / BM;
+        const int rb = mb - chunk * mbc;
+        int* tiles_done = a.rb_tiles + chunk * MAX_RB;
+        const int full = a.epoch * num_n;
+        if (atomicAdd(tiles_done + rb, 1) + 1 == full) {
+          // a row block is complete: extend the published prefix over every complete block that follows it (whoever
+          // completes a later block first leaves it to the thread that closes the gap).  Two threads that complete
+          // neighbouring blocks at the same time must not both miss the other's count: sequentially consistent fence
+          // between the count and the reads below.
+          asm volatile("fence.sc.gpu;" ::: "memory");
+          const int base = (a.epoch - 1) * mbc;
+          for (;;) {
+            int p, t;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(p) : "l"(a.published + chunk) : "memory");
+            const int k = p - base;
+            if (k >= mbc) break;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(t) : "l"(tiles_done + k) : "memory");
+            if (t < full) break;
+            if (atomicCAS(a.published + chunk, p, p + 1) == p) {
+              __threadfence_system();
+              asm volatile("red.release.sys.global.max.s32 [%0], %1;" ::"l"(a.peer_flags[chunk] + a.rank), "r"(p + 1)
+                           : "memory");
+            }
+          }
+        }
       }
     }
     if (et == 0) pb::tma_store_wait_all<0>();
@@ -603,10 +709,11 @@ gemm_tp_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 // Host launcher. Pointer tables have `tp` valid entries.
 //  mode 0 (AG): A = gather buffer [M = tp*rows_per_chunk, K] (local), D = out [M, N].
 //  mode 1 (RS): A = x [M, K] (local), D = this rank's partial buffer [M, N] (symmetric), out = [rows_per_chunk, N].
-// b_mn: B stored [K, N].  counters: int[2*tp] local, zero-initialised once.  epoch: 1, 2, 3, ... per buffer set.
+// b_mn: B stored [K, N].  counters: int[3 * 8 + 256 + 8 * 256] local, zero-initialised once
+// (chunk progress, reads done, published row-block prefixes, accumulator row-block counts, tiles done per row block).  epoch: 1, 2, 3, ... per buffer set.
 extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_ctas, const void* A, const void* B,
                                 void* D, int M, int N, int K, long ldb, int b_mn, const long* peer_x,
-                                void* gather, const long* peer_partial, float* acc, void* out, int* counters,
+                                void* gather, const long* peer_partial, void* acc, void* out, int* counters,
                                 const long* peer_flags, int* local_flags, int* status, cudaStream_t stream) {
   if (tp < 2 || tp > MAX_TP || M % tp || (M / tp) % BM || K % 8 || N % 8) return -2;
   TpArgs a;
@@ -624,9 +731,12 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
     a.peer_flags[r] = reinterpret_cast<int*>(peer_flags[r]);
   }
   a.gather = reinterpret_cast<__nv_bfloat16*>(gather);
-  a.acc = acc;
+  a.acc = reinterpret_cast<__nv_bfloat16*>(acc);
   a.out = reinterpret_cast<__nv_bfloat16*>(out);
   a.counters = counters;
+  a.published = counters + 2 * MAX_TP;
+  a.rb_ready = counters + 3 * MAX_TP;
+  a.rb_tiles = counters + 3 * MAX_TP + MAX_RB;
   a.local_flags = local_flags;
   a.status = status;
   const int num_n = (N + BN - 1) / BN;
@@ -645,8 +755,14 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   if (mode == MODE_AG && (rc = pbh::make_tmap_2d(&tAown, reinterpret_cast<const void*>(peer_x[rank]), bf, 2, M / tp, K, K, BM,
                                                   BK, sw)))
     return rc;
-  // reduce-scatter: the fourth map is the output [M / tp, N], written by the epilogue of this rank's own tiles
-  if (mode == MODE_RS && (rc = pbh::make_tmap_2d(&tAown, out, bf, 2, M / tp, N, N, BM, 64, sw))) return rc;
+  // reduce-scatter: the fourth map is the output [M / tp, N], written by the epilogue of this rank's own tiles, the
+  // fifth the bf16 accumulator of the same shape, read by it
+  CUtensorMap tAcc = tA;
+  if (mode == MODE_RS) {
+    if (N % 128 || (M / tp) / BM > MAX_RB) return -2;
+    if ((rc = pbh::make_tmap_2d(&tAown, out, bf, 2, M / tp, N, N, BM, 64, sw))) return rc;
+    if ((rc = pbh::make_tmap_2d(&tAcc, acc, bf, 2, M / tp, N, N, BM, 64, sw))) return rc;
+  }
 
   static int num_sms = 0;
   if (!num_sms) {
@@ -666,7 +782,7 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   const int tiles = tp * a.tiles_per_chunk;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
   const int grid = comm_ctas + gemm_ctas;
-  if (b_mn) k1<<<grid, 256, SMEM_BYTES, stream>>>(tA, tB, tD, tAown, a);
-  else k0<<<grid, 256, SMEM_BYTES, stream>>>(tA, tB, tD, tAown, a);
+  if (b_mn) k1<<<grid, 256, SMEM_BYTES, stream>>>(tA, tB, tD, tAown, tAcc, a);
+  else k0<<<grid, 256, SMEM_BYTES, stream>>>(tA, tB, tD, tAown, tAcc, a);
   return (int)cudaGetLastError();
 }

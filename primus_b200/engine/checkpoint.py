@@ -189,6 +189,8 @@ def save_checkpoint(trainer, root: str, release: bool = False) -> str:
     shards, meta = {}, {}
     for name, p in model_named_parameters(trainer):
         spec = shard_spec(name, p, cfg, st)
+        if hasattr(p, "full_tensor"):      # sharded by FSDP2: gathered on every rank (a collective), written by one
+            p = p.full_tensor()
         # replicas: only the first data-parallel rank (expert data-parallel rank for experts) writes
         writer = (st.edp_rank == 0) if spec["kind"] == "ep" else (st.dp_rank == 0 and st.cp_rank == 0)
         if spec["kind"] == "replicated" and st.tp_rank != 0:
@@ -265,6 +267,10 @@ def load_checkpoint(trainer, root: str, finetune: bool = False, load_optim: bool
         mine = from_saved_layout(name, mine, cfg, st.tp)
         if tuple(mine.shape) != tuple(p.shape):
             raise ValueError(f"{name}: checkpoint shard {tuple(mine.shape)} does not fit parameter {tuple(p.shape)}")
+        if hasattr(p, "full_tensor"):      # sharded by FSDP2: every rank keeps its slice of the loaded tensor
+            from torch.distributed.tensor import distribute_tensor
+
+            mine = distribute_tensor(mine.to(device=p.device, dtype=p.dtype), p.device_mesh, p.placements)
         p.data.copy_(mine.to(p.dtype))
         loaded += 1
     if missing:

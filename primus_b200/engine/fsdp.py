@@ -6,7 +6,8 @@ Every transformer layer is one sharding unit (parameters all-gathered right befo
 gradients reduce-scattered in fp32 after its backward), the root module holds the embedding, the final norm and the
 output layer.  Sharded parameters and Adam state are fp32, compute parameters bf16.  Role of the reference's
 ``core/distributed/torch_fully_sharded_data_parallel.py`` and ``optimizer/fsdp2_fp32_master_weight_opt``; scope: data
-parallelism only (tp = pp = cp = ep = 1), bf16 compute (no MXFP8 recipe), AdamW.
+parallelism only (tp = pp = cp = ep = 1), bf16 compute (no MXFP8 recipe), AdamW.  Checkpoints: the parameters are
+written whole (gathered; ``engine/checkpoint.py``), each rank saves its own shards of the Adam moments.
 """
 from __future__ import annotations
 
@@ -51,6 +52,27 @@ class FSDP2Optimizer:
     def zero_grad(self):
         self.opt.zero_grad(set_to_none=True)
 
+    # ------------------------------------------------------------------ checkpoint: this rank's shards of the moments
+    def state_dict(self):
+        shards = []
+        for name, p in self.model.named_parameters():
+            st = self.opt.state.get(p)
+            if not st:
+                continue
+            shards.append({"name": name, "step": float(st["step"]),
+                           "exp_avg": _local(st["exp_avg"]).clone(), "exp_avg_sq": _local(st["exp_avg_sq"]).clone()})
+        return {"step_count": self.step_count, "shards": shards}
+
+    def load_state_dict(self, sd):
+        by_name = dict(self.model.named_parameters())
+        fused = bool(self.opt.param_groups[0].get("fused"))
+        for s in sd["shards"]:
+            p = by_name[s["name"]]
+            self.opt.state[p] = {
+                "step": torch.tensor(float(s["step"]), dtype=torch.float32, device=p.device if fused else "cpu"),
+                "exp_avg": _like(p, s["exp_avg"]), "exp_avg_sq": _like(p, s["exp_avg_sq"])}
+        self.step_count = int(sd.get("step_count", 0))
+
     def compute_grad_norm(self):
         n = torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.clip_grad if self.clip_grad else float("inf"))
         n = n.full_tensor() if hasattr(n, "full_tensor") else n
@@ -73,3 +95,17 @@ class FSDP2Optimizer:
         self.step_count += 1
         gemm.bump_weight_generation()
         return True
+
+
+def _local(t):
+    return t.to_local() if hasattr(t, "to_local") else t
+
+
+def _like(p, local):
+    """A moment tensor laid out like parameter ``p`` (sharded the same way) from this rank's saved shard."""
+    local = local.to(device=p.device, dtype=torch.float32)
+    if hasattr(p, "to_local"):
+        from torch.distributed.tensor import DTensor
+
+        return DTensor.from_local(local, p.device_mesh, p.placements, run_check=False, shape=p.shape, stride=p.stride())
+    return local

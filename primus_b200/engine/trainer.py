@@ -728,9 +728,6 @@ class Trainer:
     def save_checkpoint(self, path: Optional[str] = None):
         from . import checkpoint
 
-        if self.fsdp:
-            raise NotImplementedError("checkpointing under use_torch_fsdp2 is not built")
-
         return checkpoint.save_checkpoint(self, path or self.tcfg.save)
 
     def load_checkpoint(self, path: Optional[str] = None) -> int:

@@ -50,7 +50,9 @@ class _Instance:
         self.slot = _Instance._next_slot
         _Instance._next_slot += 1
         assert self.slot < 60, "too many distinct fused TP shapes"
-        self.counters = torch.zeros(2 * tp, dtype=torch.int32, device=dev)
+        # chunk progress + reads done + published prefixes (3 x 8), accumulator row-block counts (256), tiles done per
+        # row block of every chunk (8 x 256); monotonic over epochs, zeroed once
+        self.counters = torch.zeros(3 * 8 + 256 + 8 * 256, dtype=torch.int32, device=dev)
         Tl = M // tp
         if mode == 0:
             self.sym = SymmetricBuffer(Tl * K * 2, ctx.group, dev)       # activation shard of every rank
@@ -60,7 +62,7 @@ class _Instance:
         else:
             self.sym = SymmetricBuffer(M * N * 2, ctx.group, dev)        # partial product of every rank
             self.gather = None
-            self.acc = torch.empty(Tl, N, dtype=torch.float32, device=dev)
+            self.acc = torch.empty(Tl, N, dtype=torch.bfloat16, device=dev)   # sum of the remote partials of my rows
         # flag slot range of this instance inside the symmetric buffer's own flag area
         self.peer_payload = (ctypes.c_long * 8)(*[self.sym.peer_ptr(r) for r in range(tp)], *([0] * (8 - tp)))
         self.peer_flags = (ctypes.c_long * 8)(*[self.sym.peer_ptr(r) + self.sym.nbytes for r in range(tp)],
@@ -98,6 +100,17 @@ def get_context(group) -> FusedTPContext:
     return _CTX[key]
 
 
+def _comm_ctas(ctx, inst) -> int:
+    """Copy CTAs of a launch.  All-gather: the fixed default.  Reduce-scatter: the copy CTAs pull ``tp - 1`` partial
+    copies of this rank's rows while the GEMM runs; when that traffic (at ~600 GB/s) takes longer than the GEMM (at
+    ~1.4 PFLOP/s) they get a larger share of the SMs, up to 48."""
+    if inst.mode == 0 or "PRIMUS_B200_TP_COMM_CTAS" in os.environ or ctx.tp == 2:
+        return COMM_CTAS
+    t_gemm = 2.0 * inst.M * inst.N * inst.K / 1.4e15
+    t_comm = (ctx.tp - 1) / ctx.tp * inst.M * inst.N * 2 / 600e9
+    return int(min(48, max(COMM_CTAS, round(COMM_CTAS * t_comm / t_gemm / 8) * 8)))
+
+
 def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):
     null = ctypes.c_void_p(0)
     inst.epoch += 1
@@ -107,7 +120,7 @@ def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):
     vp = ctypes.c_void_p
     _lib.LAUNCH_COUNT += 1
     rc = fn(ctypes.c_int(inst.mode), ctypes.c_int(ctx.tp), ctypes.c_int(ctx.rank), ctypes.c_int(inst.epoch),
-            ctypes.c_int(COMM_CTAS), vp(A.data_ptr()), vp(B.data_ptr()), vp(D.data_ptr()), ctypes.c_int(inst.M),
+            ctypes.c_int(_comm_ctas(ctx, inst)), vp(A.data_ptr()), vp(B.data_ptr()), vp(D.data_ptr()), ctypes.c_int(inst.M),
             ctypes.c_int(inst.N), ctypes.c_int(inst.K), ctypes.c_long(B.stride(0)), ctypes.c_int(int(b_mn)),
             inst.peer_payload if inst.mode == 0 else null,
             vp(inst.gather.data_ptr()) if inst.mode == 0 else null,
@@ -146,8 +159,8 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: 
     N = w.shape[1] if b_mn else w.shape[0]
     fused = fused and gemm_ops.fp8_recipe() is None
     ctx = get_context(group) if (fused and x.is_cuda) else None
-    # N % 64: the epilogue of this rank's own tiles adds the accumulator in whole 64-column groups
-    if ctx is None or not ctx.supported(M, N, K) or N % 64 or not x.is_contiguous():
+    # N % 128: accumulator pieces are whole fractions of a 128-row block; at most 256 row blocks per rank
+    if ctx is None or not ctx.supported(M, N, K) or N % 128 or M // tp > 32768 or not x.is_contiguous():
         return tpc.reduce_scatter_dim0(gemm_ops.gemm(x, w, b_mn=b_mn), group)
     inst = ctx.instance(1, M, N, K)
     partial = inst.sym.local(torch.bfloat16, M * N).view(M, N)

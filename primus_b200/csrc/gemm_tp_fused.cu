@@ -50,7 +50,6 @@ constexpr int MAX_RB = 256;                                             // 128-r
 struct TpArgs {
   int mode, tp, rank, epoch;
   int comm_ctas;
-  int rs_group;         // reduce-scatter: sources added per pass (1 .. 4)
   int rows_per_chunk;   // T / tp
   int M, N, K;          // GEMM problem of this rank: A [M, K] (K contiguous), B [N, K] or [K, N]
   // AG: peers' shards [rows_per_chunk, K] and the local gather buffer [M, K]
@@ -719,10 +718,6 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   TpArgs a;
   memset(&a, 0, sizeof(a));
   a.mode = mode; a.tp = tp; a.rank = rank; a.epoch = epoch; a.comm_ctas = comm_ctas;
-  {
-    const char* e = getenv("PRIMUS_B200_RS_GROUP");
-    a.rs_group = e ? atoi(e) : 4;
-  }
   a.rows_per_chunk = M / tp;
   a.M = M; a.N = N; a.K = K;
   for (int r = 0; r < tp; ++r) {

@@ -101,14 +101,21 @@ def get_context(group) -> FusedTPContext:
 
 
 def _comm_ctas(ctx, inst) -> int:
-    """Copy CTAs of a launch.  All-gather: the fixed default.  Reduce-scatter: the copy CTAs pull ``tp - 1`` partial
-    copies of this rank's rows while the GEMM runs; when that traffic (at ~600 GB/s) takes longer than the GEMM (at
-    ~1.4 PFLOP/s) they get a larger share of the SMs, up to 48."""
-    if inst.mode == 0 or "PRIMUS_B200_TP_COMM_CTAS" in os.environ or ctx.tp == 2:
+    """Copy CTAs of a launch: the count (a multiple of 8, at most 48) that balances the two halves of the kernel under a
+    simple model -- a copy CTA moves ~17.5 GB/s (one thread drives its ring of bulk copies), all of them together at
+    most ~700 GB/s over NVLink, and the GEMM runs at ~1.4 PFLOP/s on the SMs that are left.  ``PRIMUS_B200_TP_COMM_CTAS``
+    fixes the count; TP = 2 keeps the default, which was measured."""
+    if "PRIMUS_B200_TP_COMM_CTAS" in os.environ or ctx.tp == 2:
         return COMM_CTAS
-    t_gemm = 2.0 * inst.M * inst.N * inst.K / 1.4e15
-    t_comm = (ctx.tp - 1) / ctx.tp * inst.M * inst.N * 2 / 600e9
-    return int(min(48, max(COMM_CTAS, round(COMM_CTAS * t_comm / t_gemm / 8) * 8)))
+    width = inst.K if inst.mode == 0 else inst.N      # gathered activations [M, K] / partial products [M, N]
+    nbytes = (ctx.tp - 1) / ctx.tp * inst.M * width * 2
+    flops = 2.0 * inst.M * inst.N * inst.K
+    best, best_t = COMM_CTAS, float("inf")
+    for c in (8, 16, 24, 32, 40, 48):
+        t = max(nbytes / min(c * 17.5e9, 700e9), flops / (1.4e15 * (148 - c) / 148))
+        if t < best_t * 0.97:     # prefer fewer copy CTAs unless more of them buy at least 3 %
+            best, best_t = c, t
+    return best
 
 
 def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):

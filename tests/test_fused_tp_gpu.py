@@ -7,13 +7,8 @@ from tests.mp_utils import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, shapes, rs_group=None):
-    import os
-
+def _worker(rank, world, shapes):
     import torch.distributed as dist
-
-    if rs_group is not None:
-        os.environ["PRIMUS_B200_RS_GROUP"] = str(rs_group)
 
     from primus_b200.ops import _lib
     from primus_b200.parallel import fused_tp
@@ -47,15 +42,10 @@ def test_fused_tp_matches_nccl_composition():
     run_ranks(_worker, 2, "nccl", args=(shapes,), timeout=240)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs (three remote sources)")
-def test_fused_reduce_scatter_multi_pass():
-    """Two sources per pass with three remote sources: the partial sums travel through the fp32 accumulator between the
-    passes (the path that tensor-parallel size 8 takes)."""
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_tp_with_several_remote_sources(world):
+    """More than one remote source: the copy CTAs add the partial products of all remote ranks per piece."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
-    run_ranks(_worker, 4, "nccl", args=(shapes, 2), timeout=240)
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
-def test_fused_tp_on_four_gpus():
-    shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
-    run_ranks(_worker, 4, "nccl", args=(shapes,), timeout=240)
+    run_ranks(_worker, world, "nccl", args=(shapes,), timeout=240)

@@ -50,6 +50,7 @@ constexpr int MAX_RB = 256;                                             // 128-r
 struct TpArgs {
   int mode, tp, rank, epoch;
   int comm_ctas;
+  int rs_test_repeat;   // test hook (tp = 2 only): the peer's partial product is added twice, in two passes
   int rows_per_chunk;   // T / tp
   int M, N, K;          // GEMM problem of this rank: A [M, K] (K contiguous), B [N, K] or [K, N]
   // AG: peers' shards [rows_per_chunk, K] and the local gather buffer [M, K]
@@ -108,7 +109,8 @@ __device__ __forceinline__ bool wait_counter_geq(const int* ctr, int value) {
 // reduce-scatter: bytes per accumulator piece (one bulk copy per source) for a tensor-parallel size
 __host__ __device__ __forceinline__ int rs_piece_bytes(int tp) {
   const int g = tp - 1;
-  return (g <= 2) ? 16384 : 8192;
+  (void)g;
+  return 16384;
 }
 
 // chunk processed k-th by this rank
@@ -237,13 +239,19 @@ __device__ void comm_main(const TpArgs& a) {
     // CTAs add the REMOTE partials of those rows into the bf16 accumulator while the GEMM runs; this rank's own tiles of
     // the rows come last in its tile order, and their epilogue adds the accumulator tile and writes the result, so
     // nothing is left to do once the GEMM has finished.  Everything moves in row-block (128 rows) order: a source
-    // publishes how many row blocks of my rows it has finished, a piece is fetched as soon as every source has
+    // publishes how many row blocks of my rows it has finished, a piece is fetched as soon as its sources have
     // published its row block, and the epilogue of an own tile waits only for the accumulator pieces of its row block.
-    // Per piece a ring slot receives one bulk copy per source; the threads add them in fp32 into the first copy
-    // (a single source needs no arithmetic) and the sum leaves by a bulk store.
-    const int G = a.tp - 1;  // sources per piece: every remote rank, one pass
+    // The sources finish my rows one after the other (rank-1 first, rank+1 after (tp-2)/tp of its GEMM), so they are
+    // added in that order, `gs` sources per pass: per piece a ring slot receives one bulk copy per source of the pass
+    // plus, from the second pass on, the accumulator piece of the pass before; the threads add them in fp32 into the
+    // first copy (a single input needs no arithmetic) and the sum leaves by a bulk store.  Only the last pass -- the
+    // last source's share -- is left when the own tiles begin.
+    const bool selftest = a.rs_test_repeat && a.tp == 2;   // test hook: the peer's partial is added twice, in two passes
+    const int n_in = selftest ? 2 : a.tp - 1;
+    const int gs = selftest ? 1 : 2;
     const int PIECE = rs_piece_bytes(a.tp);
-    const int slot_bytes = G * PIECE;
+    const int max_inputs = (n_in < gs ? n_in : gs) + (n_in > gs ? 1 : 0);
+    const int slot_bytes = max_inputs * PIECE;
     int nslot = RS_RING_BYTES / slot_bytes;
     if (nslot > RS_MAX_SLOTS) nslot = RS_MAX_SLOTS;
     uint64_t* rbars = reinterpret_cast<uint64_t*>(bufs + RS_RING_BYTES);
@@ -265,147 +273,162 @@ __device__ void comm_main(const TpArgs& a) {
     int src_rank[MAX_TP];
 #pragma unroll
     for (int j = 0; j < MAX_TP; ++j) {
-      const int p = (a.rank - 1 - (j < G ? j : 0) + 2 * a.tp) % a.tp;  // arrival order: rank-1 does my rows first
+      // arrival order: rank-1 does my rows first
+      const int p = selftest ? (a.rank ^ 1) : (a.rank - 1 - (j < n_in ? j : 0) + 2 * a.tp) % a.tp;
       src_rank[j] = p;
       srcs[j] = reinterpret_cast<const uint8_t*>(a.peer_partial[p]) + row_off_bytes;
     }
-    int rb_known = -1;  // every source has published row blocks <= rb_known (thread 0 only)
-    // 0: issued; 1: a source has not published the row block yet (only when !blocking); 2: gave up waiting
-    auto issue_load = [&](long i, bool blocking) -> int {
-      const long off = piece_off(i);
-      const int rb = (int)(off / rb_bytes);
-      if (rb > rb_known) {
-        for (int j = 0; j < G; ++j) {
-          const int* f = a.local_flags + src_rank[j];
-          if (blocking) {
-            if (!pb::wait_flag_geq(f, flag_base + rb + 1)) return 2;
-          } else {
-            int v;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if (v < flag_base + rb + 1) return 1;
-          }
-        }
-        rb_known = rb;
-        asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written by the source's TMA stores
-      }
-      const int slot = (int)(i % nslot);
-      uint8_t* sb = bufs + slot * slot_bytes;
-      pb::mbar_expect_tx(&rbars[slot], (uint32_t)(G * PIECE));
-      for (int j = 0; j < G; ++j) bulk_g2s(sb + j * PIECE, srcs[j] + off, PIECE, &rbars[slot]);
-      return 0;
-    };
-    // accumulator pieces whose bulk store has completed are announced to the epilogue (counter per row block)
-    // (batched per row block: one fence + one atomic when this CTA's pieces move on to the next row block)
-    int ann_rb = -1, ann_cnt = 0;
-    auto announce_flush = [&]() {
-      if (ann_cnt) {
-        __threadfence();
-        atomicAdd(a.rb_ready + ann_rb, ann_cnt);
-      }
-      ann_cnt = 0;
-    };
-    auto announce = [&](long i) {
-      const int rb = (int)(piece_off(i) / rb_bytes);
-      if (rb != ann_rb) announce_flush();
-      ann_rb = rb;
-      ++ann_cnt;
-    };
     constexpr int STORE_LAG = 2;
-    long issued = 0;
-    // issue what the ring can take (slot of piece i is free once the store of piece i - nslot has read it, i.e.
-    // i <= last_read + nslot); wait for a source only if piece `needed` would otherwise not be in flight
-    auto top_up = [&](long last_read, long needed) {
-      while (issued < mine && issued <= last_read + nslot) {
-        const int rc = issue_load(issued, issued <= needed);
-        if (rc == 1) break;
-        if (rc == 2) {
-          atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
-          s_ok = 0;
-          break;
+    long gp = 0;  // pieces this CTA has put through the ring in earlier passes (slot and barrier phase continue)
+    for (int k0 = 0; k0 < n_in && s_ok; k0 += gs) {
+      const int cnt = (k0 + gs <= n_in) ? gs : (n_in - k0);
+      const bool has_acc = k0 > 0;
+      const bool last = k0 + cnt >= n_in;
+      const int n_inputs = cnt + (has_acc ? 1 : 0);
+      int rb_known = -1;  // the sources of this pass have published row blocks <= rb_known (thread 0 only)
+      // 0: issued; 1: a source has not published the row block yet (only when !blocking); 2: gave up waiting
+      auto issue_load = [&](long i, bool blocking) -> int {
+        const long off = piece_off(i);
+        const int rb = (int)(off / rb_bytes);
+        if (rb > rb_known) {
+          for (int j = 0; j < cnt; ++j) {
+            const int* f = a.local_flags + src_rank[k0 + j];
+            if (blocking) {
+              if (!pb::wait_flag_geq(f, flag_base + rb + 1)) return 2;
+            } else {
+              int v;
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+              if (v < flag_base + rb + 1) return 1;
+            }
+          }
+          rb_known = rb;
+          asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written by the source's TMA stores
         }
-        ++issued;
-      }
-    };
-    if (tid == 0) top_up(-1, 0);
-    __syncthreads();
-    // thread 0: store the finished piece, announce older ones, refill the ring
-    auto finish_piece = [&](long done, uint8_t* sb) {
-      bulk_s2g(accg + piece_off(done), sb, PIECE);
-      pb::tma_store_commit();
-      pb::tma_store_wait_all<STORE_LAG>();   // stores of pieces <= done - STORE_LAG are complete in global memory
-      if (done >= STORE_LAG) announce(done - STORE_LAG);
-      pb::tma_store_wait_read<1>();          // the stores of pieces <= done - 1 have read their slots
-      top_up(done - 1, done + 1);
-    };
-    if (G == 1) {
-      // a single source: the accumulator is a copy; thread 0 runs the ring alone
-      if (tid == 0) {
-        for (long done = 0; done < mine && s_ok; ++done) {
-          const int slot = (int)(done % nslot);
-          if (!pb::mbar_wait(&rbars[slot], (uint32_t)((done / nslot) & 1))) {
+        const int slot = (int)((gp + i) % nslot);
+        uint8_t* sb = bufs + slot * slot_bytes;
+        pb::mbar_expect_tx(&rbars[slot], (uint32_t)(n_inputs * PIECE));
+        for (int j = 0; j < cnt; ++j) bulk_g2s(sb + j * PIECE, srcs[k0 + j] + off, PIECE, &rbars[slot]);
+        if (has_acc) bulk_g2s(sb + cnt * PIECE, accg + off, PIECE, &rbars[slot]);
+        return 0;
+      };
+      // last pass: accumulator pieces whose bulk store has completed are announced to the epilogue (counter per row
+      // block, batched: one fence + one atomic when this CTA's pieces move on to the next row block)
+      int ann_rb = -1, ann_cnt = 0;
+      auto announce_flush = [&]() {
+        if (ann_cnt) {
+          __threadfence();
+          atomicAdd(a.rb_ready + ann_rb, ann_cnt);
+        }
+        ann_cnt = 0;
+      };
+      auto announce = [&](long i) {
+        const int rb = (int)(piece_off(i) / rb_bytes);
+        if (rb != ann_rb) announce_flush();
+        ann_rb = rb;
+        ++ann_cnt;
+      };
+      long issued = 0;
+      // issue what the ring can take (the slot of piece i is free once the store of piece i - nslot has read it, i.e.
+      // i <= last_read + nslot); wait for a source only if piece `needed` would otherwise not be in flight
+      auto top_up = [&](long last_read, long needed) {
+        while (issued < mine && issued <= last_read + nslot) {
+          const int rc = issue_load(issued, issued <= needed);
+          if (rc == 1) break;
+          if (rc == 2) {
             atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
             s_ok = 0;
             break;
           }
-          finish_piece(done, bufs + slot * slot_bytes);
+          ++issued;
+        }
+      };
+      if (tid == 0) top_up(-1, 0);
+      __syncthreads();
+      // thread 0: store the finished piece, announce older ones, refill the ring
+      auto finish_piece = [&](long done, uint8_t* sb) {
+        bulk_s2g(accg + piece_off(done), sb, PIECE);
+        pb::tma_store_commit();
+        pb::tma_store_wait_all<STORE_LAG>();   // stores of pieces <= done - STORE_LAG are complete in global memory
+        if (last && done >= STORE_LAG) announce(done - STORE_LAG);
+        pb::tma_store_wait_read<1>();          // the stores of pieces <= done - 1 have read their slots
+        top_up(done - 1, done + 1);
+      };
+      if (n_inputs == 1) {
+        // a single input: the accumulator is a copy; thread 0 runs the ring alone
+        if (tid == 0) {
+          for (long done = 0; done < mine && s_ok; ++done) {
+            const long gi = gp + done;
+            const int slot = (int)(gi % nslot);
+            if (!pb::mbar_wait(&rbars[slot], (uint32_t)((gi / nslot) & 1))) {
+              atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+              s_ok = 0;
+              break;
+            }
+            finish_piece(done, bufs + slot * slot_bytes);
+          }
+        }
+      } else {
+        for (long done = 0; done < mine; ++done) {
+          const long gi = gp + done;
+          const int slot = (int)(gi % nslot);
+          uint8_t* sb = bufs + slot * slot_bytes;
+          if (!pb::mbar_wait(&rbars[slot], (uint32_t)((gi / nslot) & 1))) {
+            atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
+            s_ok = 0;
+          }
+          __syncthreads();
+          if (!s_ok) break;   // uniform: s_ok is only written before this barrier
+          uint4* s0 = reinterpret_cast<uint4*>(sb);
+          for (int i = tid; i < PIECE / 16; i += nthr) {
+            float f[8];
+            const uint4 v0 = s0[i];
+            {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 t = __bfloat1622float2(h[j]);
+                f[2 * j] = t.x;
+                f[2 * j + 1] = t.y;
+              }
+            }
+            for (int sj = 1; sj < n_inputs; ++sj) {
+              const uint4 v = reinterpret_cast<const uint4*>(sb + sj * PIECE)[i];
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 t = __bfloat1622float2(h[j]);
+                f[2 * j] += t.x;
+                f[2 * j + 1] += t.y;
+              }
+            }
+            uint4 o;
+            o.x = pb::pack_bf16x2(f[0], f[1]);
+            o.y = pb::pack_bf16x2(f[2], f[3]);
+            o.z = pb::pack_bf16x2(f[4], f[5]);
+            o.w = pb::pack_bf16x2(f[6], f[7]);
+            s0[i] = o;
+          }
+          pb::fence_proxy_async_smem();
+          __syncthreads();
+          if (tid == 0) finish_piece(done, sb);
         }
       }
-    } else {
-      for (long done = 0; done < mine; ++done) {
-        const int slot = (int)(done % nslot);
-        uint8_t* sb = bufs + slot * slot_bytes;
-        if (!pb::mbar_wait(&rbars[slot], (uint32_t)((done / nslot) & 1))) {
-          atomicCAS(a.status, 0, PB_ERR_TIMEOUT_FLAG);
-          s_ok = 0;
+      __syncthreads();
+      if (tid == 0) {
+        pb::tma_store_wait_all<0>();   // the next pass reads these accumulator pieces back
+        if (s_ok && last) {
+          for (long i = (mine > STORE_LAG ? mine - STORE_LAG : 0); i < mine; ++i) announce(i);
+          announce_flush();
         }
-        __syncthreads();
-        if (!s_ok) break;   // uniform: s_ok is only written before this barrier
-        uint4* s0 = reinterpret_cast<uint4*>(sb);
-        for (int i = tid; i < PIECE / 16; i += nthr) {
-          float f[8];
-          const uint4 v0 = s0[i];
-          {
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 t = __bfloat1622float2(h[j]);
-              f[2 * j] = t.x;
-              f[2 * j + 1] = t.y;
-            }
-          }
-          for (int sj = 1; sj < G; ++sj) {
-            const uint4 v = reinterpret_cast<const uint4*>(sb + sj * PIECE)[i];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 t = __bfloat1622float2(h[j]);
-              f[2 * j] += t.x;
-              f[2 * j + 1] += t.y;
-            }
-          }
-          uint4 o;
-          o.x = pb::pack_bf16x2(f[0], f[1]);
-          o.y = pb::pack_bf16x2(f[2], f[3]);
-          o.z = pb::pack_bf16x2(f[4], f[5]);
-          o.w = pb::pack_bf16x2(f[6], f[7]);
-          s0[i] = o;
-        }
-        pb::fence_proxy_async_smem();
-        __syncthreads();
-        if (tid == 0) finish_piece(done, sb);
       }
+      gp += mine;
+      __syncthreads();
     }
-    __syncthreads();
-    if (tid == 0) {
-      pb::tma_store_wait_all<0>();
-      if (s_ok) {
-        for (long i = (mine > STORE_LAG ? mine - STORE_LAG : 0); i < mine; ++i) announce(i);
-        announce_flush();
-        for (int j = 0; j < G; ++j) {   // every load from the sources has landed: they may reuse their buffers
-          const int p = src_rank[j];
-          const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
-          if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
-        }
+    if (tid == 0 && s_ok) {
+      for (int j = 0; j < a.tp - 1; ++j) {   // every load from the sources has landed: they may reuse their buffers
+        const int p = (a.rank - 1 - j + 2 * a.tp) % a.tp;
+        const int fin = atomicAdd(a.counters + a.tp + p, 1) + 1;
+        if (fin == a.epoch * a.comm_ctas) pb::set_flag_release(a.peer_flags[p] + a.tp + a.rank, a.epoch);
       }
     }
   }
@@ -718,6 +741,10 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   TpArgs a;
   memset(&a, 0, sizeof(a));
   a.mode = mode; a.tp = tp; a.rank = rank; a.epoch = epoch; a.comm_ctas = comm_ctas;
+  {
+    const char* e = getenv("PRIMUS_B200_RS_TEST_REPEAT");
+    a.rs_test_repeat = (e && e[0] == '1') ? 1 : 0;
+  }
   a.rows_per_chunk = M / tp;
   a.M = M; a.N = N; a.K = K;
   for (int r = 0; r < tp; ++r) {

@@ -23,8 +23,10 @@ _CACHE: dict = {}
 
 
 def _table(a: Sequence[torch.Tensor], b: Optional[Sequence[torch.Tensor]], out: Optional[Sequence[torch.Tensor]]):
-    key = (tuple((t.data_ptr(), t.numel()) for t in a), tuple(t.data_ptr() for t in b) if b else None,
-           tuple(t.data_ptr() for t in out) if out else None)
+    # element sizes are part of the key: chunk offsets depend on them, and the allocator hands freed addresses out again
+    key = (tuple((t.data_ptr(), t.numel()) for t in a), a[0].element_size(),
+           (tuple(t.data_ptr() for t in b), b[0].element_size()) if b else None,
+           (tuple(t.data_ptr() for t in out), out[0].element_size()) if out else None)
     hit = _CACHE.get(key)
     if hit is not None:
         return hit

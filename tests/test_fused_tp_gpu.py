@@ -49,3 +49,39 @@ def test_fused_tp_with_several_remote_sources(world):
         pytest.skip(f"needs {world} GPUs")
     shapes = [(2048, 1280, 1024, False), (1024, 768, 512, True)]
     run_ranks(_worker, world, "nccl", args=(shapes,), timeout=240)
+
+
+def _repeat_worker(rank, world, shapes):
+    import os
+
+    import torch.distributed as dist
+
+    from primus_b200.ops import _lib
+    from primus_b200.parallel import fused_tp
+
+    group = dist.group.WORLD
+    torch.manual_seed(4321 + rank)
+    os.environ["PRIMUS_B200_RS_TEST_REPEAT"] = "1"
+    try:
+        for (T, N, K) in shapes:
+            Tl = T // world
+            for it in range(3):
+                x = torch.randn(T, K, device="cuda").bfloat16()
+                w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+                out = fused_tp.gemm_rs(x, w, group, fused=True)
+                torch.cuda.synchronize()
+                _lib.check_status()
+                ref = fused_tp.gemm_rs(x, w, group, fused=False).float()
+                own = (x[rank * Tl:(rank + 1) * Tl].float() @ w.float().t())
+                want = 2.0 * ref - own          # own + 2 x (the peer's partial product)
+                err = (out.float() - want).abs().max().item()
+                assert err <= 3e-2 * want.abs().max().item() + 2e-2, f"T={T} it={it}: err {err}"
+    finally:
+        os.environ.pop("PRIMUS_B200_RS_TEST_REPEAT", None)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_reduce_scatter_accumulates_over_passes():
+    """The pass structure tensor-parallel sizes above 3 use (sources added in arrival order, the accumulator re-read
+    between passes), driven on 2 GPUs by the kernel's test hook: the peer's partial product is added in two passes."""
+    run_ranks(_repeat_worker, 2, "nccl", args=([(2048, 1280, 1024), (1024, 768, 512)],), timeout=240)

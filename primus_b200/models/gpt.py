@@ -247,6 +247,10 @@ class MultiTokenPredictionLayer(nn.Module):
         self.eh_proj = ParamHolder(weight=_param((h, 2 * h), cfg.init_method_std, cfg.torch_dtype, device))
         self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device, tp)
         self.final_layernorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
+        # replicated over the tensor-parallel ranks; under sequence parallelism each rank sees its token shard only, so
+        # their gradients are summed over the group like those of the other norm weights
+        for holder in (self.enorm, self.hnorm, self.eh_proj, self.final_layernorm):
+            holder.weight.sequence_parallel = cfg.sequence_parallel
 
 
 class GPTModel(nn.Module):
@@ -287,8 +291,8 @@ class GPTModel(nn.Module):
             self.embedding.word_embeddings.weight.embedding_primary = True
         if post_process and cfg.mtp_num_layers:
             st = ps.get_state()
-            if tp > 1 or st.cp > 1:
-                raise NotImplementedError("multi-token prediction is built for tensor / context parallel size 1")
+            if st.cp > 1:
+                raise NotImplementedError("multi-token prediction is not built for context parallelism")
             self.mtp = nn.Module()
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
                                              for _ in range(cfg.mtp_num_layers)])
@@ -373,6 +377,8 @@ class GPTModel(nn.Module):
         """sum_k scale / D * CE(depth k): depth k (1-based) sees tokens shifted left by k and predicts labels shifted
         left by k; the last k positions of every sequence carry no target and get weight 0."""
         cfg = self.cfg
+        st = ps.get_state()
+        sp = cfg.sequence_parallel and st.tp > 1
         h = hidden if residual is None else hidden + residual
         tok, lab = tokens.reshape(batch, seq), labels.reshape(batch, seq)
         wts = loss_weights.reshape(batch, seq)
@@ -381,13 +387,17 @@ class GPTModel(nn.Module):
             tok, lab, wts = torch.roll(tok, -1, 1), torch.roll(lab, -1, 1), torch.roll(wts, -1, 1).clone()
             wts[:, seq - k:] = 0
             e = self.embedding(tok.reshape(-1))
+            if st.tp > 1:   # vocab-parallel partial sums -> this rank's tokens (all of them, or its sequence shard)
+                e = tpc.reduce_scatter_seq(e, st.tp_group) if sp else tpc.all_reduce(e, st.tp_group)
             x = torch.cat([fused.rmsnorm(e, layer.enorm.weight, cfg.norm_epsilon),
                            fused.rmsnorm(h, layer.hnorm.weight, cfg.norm_epsilon)], -1)
             x = gemm.linear(x, layer.eh_proj.weight)
             hid, res = layer.transformer_layer(x, None, rope, batch)
-            logits, _ = layers.norm_linear(hid, res, layer.final_layernorm.weight, w_out, cfg.norm_epsilon, None, False)
+            logits, _ = layers.norm_linear(hid, res, layer.final_layernorm.weight, w_out, cfg.norm_epsilon,
+                                           st.tp_group, sp)
             logits = fused.softcap(logits, cfg.final_logit_softcapping)
-            lk = fused.cross_entropy(logits, lab.reshape(-1), 0, None, wts.reshape(-1), unit_upstream)
+            lk = fused.cross_entropy(logits, lab.reshape(-1), st.tp_rank * w_out.shape[0],
+                                     st.tp_group if st.tp > 1 else None, wts.reshape(-1), unit_upstream)
             total = lk if total is None else total + lk
             h = hid if res is None else hid + res
         return total * (cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers)

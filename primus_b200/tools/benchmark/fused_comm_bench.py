@@ -69,12 +69,15 @@ def bench_tp(model: str, tokens: int, iters: int):
             fn = lambda fused: (lambda i: fused_tp.gemm_rs(xs[i % 4], w, group, fused=fused))
         t_f = _max_over_ranks(time_cuda(fn(True), iters)["ms_median"])
         t_n = _max_over_ranks(time_cuda(fn(False), iters)["ms_median"])
+        ctx = fused_tp.get_context(group)
+        inst = ctx.instance(0 if kind == "ag" else 1, tokens, N, K)
         flops = 2.0 * tokens * N * K
         # bytes entering (AG) / leaving towards the owners (RS) each GPU over NVLink
         nv = (tokens // world) * (world - 1) * (K if kind == "ag" else N) * 2.0
         target = max(flops / peak, nv / link) * 1e3
         rows.append({"op": name, "tp": world, "M": tokens, "N/rank" if kind == "ag" else "N": N, "K": K,
-                     "fused_ms": t_f, "nccl+gemm_ms": t_n, "speedup": t_n / t_f, "roofline_ms": target,
+                     "copy_ctas": fused_tp._comm_ctas(ctx, inst), "fused_ms": t_f, "nccl+gemm_ms": t_n, "speedup": t_n / t_f,
+                     "roofline_ms": target,
                      "fraction_of_roofline": target / t_f, "bound": "compute" if flops / peak > nv / link else "nvlink"})
     return rows
 

@@ -51,6 +51,8 @@ CASES = {
     "cp4_ring_mla": dict(world=4, kw=dict(cp=4, cp_comm="p2p", mla=True, seq=64)),
     "pp2_tied_embeddings": dict(world=2, kw=dict(pp=2, tied=True)),
     "pp2_interleaved_tied": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", tied=True)),
+    "tp2_sp_mtp": dict(world=2, kw=dict(tp=2, sp=True, mtp=1)),
+    "tp2_nosp_mtp": dict(world=2, kw=dict(tp=2, sp=False, mtp=1)),
     "pp2_dp2_mtp": dict(world=4, kw=dict(pp=2, mtp=1)),
     "cp4_a2a_p2p": dict(world=4, kw=dict(cp=4, cp_comm="a2a+p2p", cp_sizes=[2, 2], seq=64)),
 }

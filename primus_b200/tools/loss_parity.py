@@ -27,7 +27,8 @@ def run(precision: str, a) -> list[float]:
     mc = TransformerConfig(num_layers=a.layers, hidden_size=a.hidden, ffn_hidden_size=a.hidden * 7 // 2 // 128 * 128,
                            num_attention_heads=a.hidden // 128, num_query_groups=max(1, a.hidden // 512), kv_channels=128,
                            vocab_size=a.vocab, params_dtype="bf16", seq_length=a.seq,
-                           fp8="e4m3" if precision == "mxfp8" else None, fp8_recipe="mxfp8")
+                           fp8="e4m3" if precision in ("mxfp8", "tensorwise") else None,
+                           fp8_recipe=precision if precision == "tensorwise" else "mxfp8")
     tc = TrainConfig(micro_batch_size=a.micro_batch, global_batch_size=a.global_batch, seq_length=a.seq,
                      train_iters=a.steps, lr=a.lr, min_lr=a.lr / 10, lr_warmup_iters=20, lr_decay_style="cosine",
                      weight_decay=0.1, clip_grad=1.0, log_interval=1, mock_data_period=a.period if a.data == "period" else 0,
@@ -54,7 +55,9 @@ def main(argv=None):
     ap.add_argument("--data", default="markov", choices=["markov", "period"],
                     help="markov: smooth curve (transition table); period: in-context copying (sudden phase changes)")
     ap.add_argument("--seed", type=int, default=1234)
-    ap.add_argument("--precisions", default="bf16,mxfp8")
+    ap.add_argument("--precisions", default="bf16,mxfp8",
+                    help="comma list of bf16, mxfp8 (scale per 32 elements), tensorwise (one power-of-two scale per tensor); "
+                         "the differences reported are first vs last")
     ap.add_argument("--output", default=None)
     a = ap.parse_args(argv)
     names = a.precisions.split(",")

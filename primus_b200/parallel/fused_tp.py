@@ -111,8 +111,11 @@ def _comm_ctas(ctx, inst) -> int:
     nbytes = (ctx.tp - 1) / ctx.tp * inst.M * width * 2
     flops = 2.0 * inst.M * inst.N * inst.K
     best, best_t = COMM_CTAS, float("inf")
-    for c in (8, 16, 24, 32, 40, 48):
-        t = max(nbytes / min(c * 17.5e9, 700e9), flops / (1.4e15 * (148 - c) / 148))
+    # the reduce-scatter's copy CTAs also add the copies (all threads, two barriers per piece): fewer bytes per CTA and
+    # never fewer than 16 of them (8 measured 0.67x of GEMM + NCCL on the TP = 4 FC2 shape)
+    rate = 17.5e9 if inst.mode == 0 else 12e9
+    for c in ((8, 16, 24, 32, 40, 48) if inst.mode == 0 else (16, 24, 32, 40, 48)):
+        t = max(nbytes / min(c * rate, 700e9), flops / (1.4e15 * (148 - c) / 148))
         if t < best_t * 0.97:     # prefer fewer copy CTAs unless more of them buy at least 3 %
             best, best_t = c, t
     return best

@@ -293,7 +293,8 @@ class Trainer:
         if expert:
             self.buffers.append(ParamGradBuffer(
                 expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
-                train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream))
+                train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream,
+                extra_grad_scale=float(st.edp) / float(st.dp * st.cp)))
         norm_groups = [st.mp_group] if (st.tp > 1 or st.pp > 1) else []
         from ..parallel import matrix_optimizers
 
@@ -314,7 +315,8 @@ class Trainer:
         self.optimizer = matrix_optimizers.build(
             train_cfg.optimizer, self.buffers, **extra, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
-            check_for_nan=train_cfg.check_for_nan_in_loss_and_grad)
+            check_for_nan=train_cfg.check_for_nan_in_loss_and_grad, tp_size=st.tp,
+            expert_norm_group=st.ep_group if (st.ep > 1 and not train_cfg.use_distributed_optimizer) else None)
 
     def _init_schedule_and_data(self):
         model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
@@ -486,6 +488,11 @@ class Trainer:
             buf.zero_grad()
         if self.fsdp:
             self.optimizer.zero_grad()
+        if self.mcfg.num_experts:
+            # the load-balancing loss of every micro-batch is weighted like the language-model loss
+            from ..models.moe import AuxLossScaler
+
+            AuxLossScaler.scale = 1.0 / float(self.num_microbatches)
         timers("forward-backward", 1).start()
         if self.st.pp > 1:
             from ..parallel.pipeline import run_pipeline_schedule
@@ -611,6 +618,7 @@ class Trainer:
                 profiler.step()
                 if self.iteration % tc.log_interval == 0 or on_step is not None:
                     lv = self.reduced_loss(loss)  # synchronises
+                    self._check_device_status()
                     dt = time.perf_counter() - t0
                     losses.append(lv)
                     self._log_step(lv, dt)
@@ -688,6 +696,7 @@ class Trainer:
                 total += self.model(mb["tokens"], mb["labels"], loss_weights=w, position_ids=pos,
                                     cu_seqlens=mb.get("host_cu_seqlens")).detach().float()
         val = self.reduced_loss(total / max(iters, 1))
+        self._check_device_status()
         ppl = math.exp(min(val, 20.0))
         self.last_metrics.update(validation_loss=val, validation_ppl=ppl)
         if self.st.rank == self.st.world_size - 1 or self.st.world_size == 1:
@@ -724,10 +733,27 @@ class Trainer:
             if text and (st.rank == st.world_size - 1 or st.world_size == 1):
                 self.log(text)
 
+    def _check_device_status(self):
+        """Reads the status word that kernels with bounded waits (mbarrier / flag / barrier) and the fused
+        expert-parallel capacity check write to.  Called where the loop synchronises anyway (after the loss has been
+        fetched, before a checkpoint is written, after an evaluation).  A recorded error means this step's results
+        cannot be trusted, so it is raised as a :class:`fault.PersistentFault`: the in-process restart (or the job-level
+        one) goes back to the newest checkpoint instead of training on."""
+        if not self.is_cuda:
+            return
+        from ..ops import _lib
+        from . import fault
+
+        try:
+            _lib.check_status(self.device)
+        except _lib.NativeLibraryError as e:
+            raise fault.PersistentFault(f"iteration {self.iteration}: {e}") from e
+
     # ------------------------------------------------------------------ checkpoint
     def save_checkpoint(self, path: Optional[str] = None):
         from . import checkpoint
 
+        self._check_device_status()   # never persist the state of a step whose kernels reported an error
         return checkpoint.save_checkpoint(self, path or self.tcfg.save)
 
     def load_checkpoint(self, path: Optional[str] = None) -> int:

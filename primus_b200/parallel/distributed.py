@@ -45,8 +45,15 @@ class Bucket:
 class ParamGradBuffer:
     def __init__(self, params: list[torch.nn.Parameter], dp_group, dp_size: int, dp_rank: int,
                  bucket_size: Optional[int] = None, grad_dtype=torch.float32, use_distributed_optimizer=True,
-                 overlap_grad_reduce=False, average_in_collective=True, comm_stream=None, symmetric=False):
+                 overlap_grad_reduce=False, average_in_collective=True, comm_stream=None, symmetric=False,
+                 extra_grad_scale: float = 1.0):
+        """``extra_grad_scale`` multiplies the gradients before the collective.  Expert parameters need it: every
+        expert-parallel rank accumulates the contributions of the tokens of all ``ep`` ranks, each normalised for its
+        own rank's micro-batches, and the buffer is then only averaged over the (smaller) expert-data-parallel group,
+        so the sum is ``dp / edp`` times the data-parallel mean the dense parameters get (Megatron's
+        ``expert_gradient_scaling_factor = edp / dp``)."""
         assert params, "empty parameter list"
+        self.extra_grad_scale = float(extra_grad_scale)
         self.params = params
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.use_distributed_optimizer = use_distributed_optimizer
@@ -141,6 +148,8 @@ class ParamGradBuffer:
 
             ctx = contextlib.nullcontext()
         with ctx:
+            if self.extra_grad_scale != 1.0:
+                g.mul_(self.extra_grad_scale)
             on_cpu = g.device.type == "cpu"
             # NCCL averages inside the collective; gloo has no AVG, so pre-scale there
             op = dist.ReduceOp.SUM if (on_cpu or self.grad_scale == 1.0) else dist.ReduceOp.AVG
@@ -164,6 +173,8 @@ class ParamGradBuffer:
     def finish_grad_sync(self):
         """Reduce every bucket that has not been started and wait for all of them."""
         if self.dp_size == 1 or self.symmetric:  # symmetric buffers: the fused optimizer kernels do the reduction
+            if self.extra_grad_scale != 1.0 and not self.symmetric:
+                self.grad_data.mul_(self.extra_grad_scale)
             return
         for b in self.buckets:
             if b.rs_handle is None:
@@ -201,9 +212,20 @@ class DistributedOptimizer:
 
     def __init__(self, buffers: list[ParamGradBuffer], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
                  clip_grad=1.0, no_wd_filter=None, norm_groups: Iterable = (), check_for_nan=True,
-                 state_dtype: torch.dtype = torch.float32):
+                 state_dtype: torch.dtype = torch.float32, tp_size: int = 1, expert_norm_group=None):
         """``state_dtype``: dtype of the two Adam moments (fp32, or bf16 with the precision-aware optimizer; the master
-        weights are always fp32 and the arithmetic of a step is fp32)."""
+        weights are always fp32 and the arithmetic of a step is fp32).
+
+        Global gradient norm: the squared sums of the local shards are added over the data-parallel group (when the
+        shards are disjoint) and over ``norm_groups`` (tensor x pipeline parallel ranks).  Parameters that every
+        tensor-parallel rank holds whole (norm weights, routers, biases of row-parallel layers: no
+        ``tensor_model_parallel`` attribute) would be counted ``tp_size`` times by the second reduction, so their
+        share is scaled by ``1 / tp_size`` first, as Megatron leaves tensor-parallel duplicates out of the norm.
+        ``expert_norm_group``: without the distributed optimizer every rank updates whole parameters and the dense
+        gradients are identical across data-parallel ranks, but each expert-parallel rank owns different experts:
+        their squared sum is reduced over this group."""
+        self.tp_size = max(int(tp_size), 1)
+        self.expert_norm_group = expert_norm_group
         self.buffers = buffers
         self.state_dtype = state_dtype
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
@@ -221,8 +243,10 @@ class DistributedOptimizer:
                 wd_ranges = self._wd_ranges(buf, b, s, e, no_wd_filter)
                 self.state.append(dict(buf=buf, bucket=b, s=s, e=e, master=master,
                                        m=torch.zeros_like(master, dtype=state_dtype),
-                                       v=torch.zeros_like(master, dtype=state_dtype), wd_ranges=wd_ranges))
+                                       v=torch.zeros_like(master, dtype=state_dtype), wd_ranges=wd_ranges,
+                                       dup_ranges=self._tp_duplicate_ranges(buf, b, s, e) if self.tp_size > 1 else []))
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.sumsq_part = torch.zeros(1, dtype=torch.float32, device=dev)
         self.coef = torch.ones(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.skip = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -255,22 +279,62 @@ class DistributedOptimizer:
                 merged.append(r)
         return merged
 
+    @staticmethod
+    def _tp_duplicate_ranges(buf, b, s, e):
+        """Sub-ranges of [s, e) that belong to parameters replicated over the tensor-parallel ranks."""
+        out = []
+        for p in b.params:
+            if getattr(p, "tensor_model_parallel", False) or getattr(p, "is_expert", False):
+                continue
+            o = buf.param_offsets[p]
+            lo, hi = max(o, s), min(o + p.numel(), e)
+            if lo < hi:
+                out.append((lo, hi))
+        return sorted(out)
+
+    def _discount_tp_duplicates(self):
+        """sumsq -= (tp - 1) / tp * (squared sum of the tensor-parallel duplicates in the local shards)."""
+        if self.tp_size == 1 or not any(st["dup_ranges"] for st in self.state):
+            return
+        self.sumsq_part.zero_()
+        for st in self.state:
+            for lo, hi in st["dup_ranges"]:
+                optim_ops.sumsq_(st["buf"].grad_data[lo:hi], self.sumsq_part, accumulate=True)
+        self.sumsq.add_(self.sumsq_part, alpha=-(self.tp_size - 1) / self.tp_size)
+
+    def _reduce_sumsq(self):
+        """Adds the squared sums over the ranks that hold disjoint parts of the gradients."""
+        if self.buffers[0].dp_size > 1 and self.buffers[0].use_distributed_optimizer:
+            dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
+        for g in self.norm_groups:
+            dist.all_reduce(self.sumsq, group=g)
+
     # ------------------------------------------------------------------
     def compute_grad_norm(self):
         """Global L2 norm of the (already reduced) gradients, left on the device."""
         self.sumsq.zero_()
         self.skip.zero_()
+        expert_sep = self.expert_norm_group is not None and any(
+            not st["buf"].use_distributed_optimizer and self._is_expert_buffer(st["buf"]) for st in self.state)
+        if expert_sep:
+            self.sumsq_part.zero_()
         for st in self.state:
             g = st["buf"].grad_data[st["s"]:st["e"]]
-            optim_ops.sumsq_(g, self.sumsq, accumulate=True)
-        if self.buffers[0].dp_size > 1 and self.buffers[0].use_distributed_optimizer:
-            dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
-        for g in self.norm_groups:
-            dist.all_reduce(self.sumsq, group=g)
+            sep = expert_sep and not st["buf"].use_distributed_optimizer and self._is_expert_buffer(st["buf"])
+            optim_ops.sumsq_(g, self.sumsq_part if sep else self.sumsq, accumulate=True)
+        if expert_sep:
+            dist.all_reduce(self.sumsq_part, group=self.expert_norm_group)
+            self.sumsq.add_(self.sumsq_part)
+        self._discount_tp_duplicates()
+        self._reduce_sumsq()
         if self.check_for_nan:
             self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
         optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
         return self.grad_norm
+
+    @staticmethod
+    def _is_expert_buffer(buf) -> bool:
+        return bool(getattr(buf.params[0], "is_expert", False))
 
     def _fused_step(self, lr: float, wd: float):
         """Reduce-scatter, clip and AdamW + all-gather through peer memory (``csrc/dp_fused.cu``)."""
@@ -297,9 +361,8 @@ class DistributedOptimizer:
         for buf in self.buffers:
             if buf.symmetric:
                 buf.sym_grad.barrier(1)  # everybody has read this rank's gradients: they may be zeroed again
-        dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
-        for g in self.norm_groups:
-            dist.all_reduce(self.sumsq, group=g)
+        self._discount_tp_duplicates()
+        self._reduce_sumsq()
         if self.check_for_nan:
             self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
         optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)

@@ -16,6 +16,7 @@ all-gather (primus/backends/megatron/core/distributed/sdma_param_gather.py:126-2
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -51,6 +52,15 @@ def probe_p2p(max_dev: int = 16) -> dict:
     nd = n.value
     return {"num_devices": nd, "matrix": [[mat[i * max_dev + j] for j in range(nd)] for i in range(nd)],
             "all_p2p": bool(caps.value & 1), "multicast": bool(caps.value & 2), "fabric": bool(caps.value & 4)}
+
+
+def barrier_wait_cycles() -> int:
+    """Cycle limit of the device-side barrier between ranks.  Ranks of one step can be skewed by far more than a
+    kernel-internal wait ever is (a checkpoint write, a slow data loader, Python garbage collection on one rank), so the
+    default is 60 s of SM clocks rather than the 1.5 s the in-kernel waits use; ``PRIMUS_B200_BARRIER_TIMEOUT_S``
+    overrides it.  The wait stays bounded: on expiry the kernel records status 4 and returns."""
+    sec = float(os.environ.get("PRIMUS_B200_BARRIER_TIMEOUT_S", "60"))
+    return int(max(sec, 0.001) * 1.9e9)
 
 
 class SymmetricBuffer:
@@ -126,7 +136,7 @@ class SymmetricBuffer:
         base = slot * self.world * 4
         tbl = self.peer_flag_table + base
         _lib.call("symm_barrier", tbl, self.flags[slot * self.world:], self.world, self.rank, self.epoch,
-                  _lib.status_word(self.device), 0)
+                  _lib.status_word(self.device), barrier_wait_cycles())
 
     def close(self):
         lib = _lib.require()

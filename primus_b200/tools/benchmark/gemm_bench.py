@@ -49,6 +49,11 @@ def bench_shape(name, M, N, K, iters, compare):
         t = time_cuda(fn, iters)
         rows.append({"gemm": name, "kind": kind, "M": M, "N": N, "K": K, "ms": t["ms_median"],
                      "TFLOP/s": fl / t["ms_median"] / 1e9})
+    by = {r["kind"]: r for r in rows}
+    for ours, lib in (("fprop", "cublas fprop"), ("dgrad", "cublas dgrad"), ("wgrad+acc", "cublas wgrad")):
+        if ours in by and lib in by:
+            rows.append({"gemm": name, "kind": f"ours/library {ours}", "M": M, "N": N, "K": K, "ms": by[ours]["ms"],
+                         "TFLOP/s": by[lib]["ms"] / by[ours]["ms"]})
     return rows
 
 
@@ -79,15 +84,62 @@ def bench_shape_mxfp8(name, M, N, K, iters):
                                                                         xs[i % n].q_col, xs[i % n].sf_col, N, K, M,
                                                                         a_mn=True, b_mn=True, out=mg, accumulate=True,
                                                                         two_cta=two))]
+    runs += _cublaslt_mxfp8_runs(M, N, K, n)
     rows = []
     for kind, fn in runs:
-        t = time_cuda(fn, iters)
+        try:
+            t = time_cuda(fn, iters)
+        except Exception as e:  # the library path is optional: report why it did not run
+            rows.append({"gemm": name, "kind": f"{kind}: {type(e).__name__}: {str(e)[:80]}", "M": M, "N": N, "K": K,
+                         "ms": float("nan"), "TFLOP/s": float("nan")})
+            continue
         rows.append({"gemm": name, "kind": kind, "M": M, "N": N, "K": K, "ms": t["ms_median"],
                      "TFLOP/s": fl / t["ms_median"] / 1e9})
+    _add_ratio_rows(rows, name, M, N, K)
     t = time_cuda(lambda i: fp8.quantize_mxfp8(xb[i % len(xb)]), iters)
     rows.append({"gemm": name, "kind": "quantize row+col (GB/s in TFLOP/s column)", "M": M, "N": 0, "K": K,
                  "ms": t["ms_median"], "TFLOP/s": M * K * (2 + 2 + 1 / 16) / t["ms_median"] / 1e6})
     return rows
+
+
+def _cublaslt_mxfp8_runs(M, N, K, n):
+    """cuBLASLt block-scaled MXFP8 GEMMs through ``torch._scaled_mm`` (E4M3 operands, E8M0 scales per 32 in the blocked
+    128x4 layout), timed on random bytes.  The library takes K-major operands only, so the data- and weight-gradient
+    GEMMs are timed the way Transformer-Engine runs them: as K-major GEMMs on transposed quantised copies, at the
+    permuted problem sizes (M,K,N) and (N,K,M)."""
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    if e8 is None or not hasattr(torch, "_scaled_mm"):
+        return []
+
+    def operand(rows, cols):
+        q = torch.randint(0, 120, (rows, cols), dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        nsf = (-(-rows // 128) * 128) * (-(-(cols // 32) // 4) * 4)
+        sf = torch.full((nsf,), 127, dtype=torch.uint8, device="cuda").view(e8)
+        return q, sf
+
+    runs = []
+    for tag, (m, nn, k) in (("fprop", (M, N, K)), ("dgrad", (M, K, N)), ("wgrad", (N, K, M))):
+        ab = [(operand(m, k), operand(nn, k)) for _ in range(n)]
+
+        def fn(i, ab=ab):
+            (a, sa), (b, sb) = ab[i % len(ab)]
+            return torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        runs.append((f"cublaslt mxfp8 {tag}", fn))
+    return runs
+
+
+def _add_ratio_rows(rows, name, M, N, K):
+    """ours / library for every GEMM kind that has both timings (> 1 means the kernel of this package is faster)."""
+    by = {r["kind"]: r for r in rows if r["gemm"] == name and r["ms"] == r["ms"]}
+    for kind in ("fprop", "dgrad", "wgrad"):
+        lib = by.get(f"cublaslt mxfp8 {kind}")
+        ours = [by.get(f"mxfp8 {kind}"), by.get(f"mxfp8 {kind}+acc"), by.get(f"mxfp8 cta-pair {kind}"),
+                by.get(f"mxfp8 cta-pair {kind}+acc")]
+        ours = [o for o in ours if o]
+        if lib and ours:
+            best = min(ours, key=lambda r: r["ms"])
+            rows.append({"gemm": name, "kind": f"ours/library {kind} ({best['kind']})", "M": M, "N": N, "K": K,
+                         "ms": best["ms"], "TFLOP/s": lib["ms"] / best["ms"]})
 
 
 def main(argv=None):

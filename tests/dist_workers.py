@@ -3,12 +3,14 @@ import torch
 
 
 def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2, iters=4, schedule="1f1b", vpp=None, layers=4,
-              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False, cp_sizes=None, tied=False, mtp=0):
+              pp_warmup=False, cp_comm="a2a", mla=False, fsdp=False, cp_sizes=None, tied=False, mtp=0, opt="adam",
+              distopt=True, hidden=64, heads=4, ffn=128, vocab=512, lr=1e-2, clip=1.0, recompute=None, extra_mc=None,
+              extra_tc=None):
     from primus_b200.engine.trainer import TrainConfig
     from primus_b200.models.config import TransformerConfig
 
-    kw = dict(num_layers=layers, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
-              vocab_size=512, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+    kw = dict(num_layers=layers, hidden_size=hidden, ffn_hidden_size=ffn, num_attention_heads=heads, num_query_groups=2,
+              vocab_size=vocab, params_dtype="fp32", tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
               expert_model_parallel_size=ep, context_parallel_size=cp, sequence_parallel=sp, make_vocab_size_divisible_by=64,
               virtual_pipeline_model_parallel_size=vpp, cp_comm_type=cp_comm,
               hierarchical_context_parallel_sizes=cp_sizes, untie_embeddings_and_output_weights=not tied,
@@ -18,10 +20,15 @@ def tiny_cfgs(tp=1, pp=1, ep=1, cp=1, sp=False, moe=False, seq=64, gbs=8, mbs=2,
     if moe:
         kw.update(num_experts=4, moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq=[0, 1] * (layers // 2),
                   moe_aux_loss_coeff=1e-2)
+    if recompute:
+        kw.update(recompute)
+    if extra_mc:
+        kw.update(extra_mc)
     mc = TransformerConfig(**kw)
-    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=iters, lr=1e-2,
-                     lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, pipeline_schedule=schedule,
-                     log_interval=1, pp_warmup=pp_warmup, use_torch_fsdp2=fsdp)
+    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=iters, lr=lr,
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=clip, pipeline_schedule=schedule,
+                     log_interval=1, pp_warmup=pp_warmup, use_torch_fsdp2=fsdp, optimizer=opt,
+                     use_distributed_optimizer=distopt, **(extra_tc or {}))
     return mc, tc
 
 
@@ -82,7 +89,10 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
                                  hierarchical_cp_sizes=mc.hierarchical_context_parallel_sizes)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     load_from_full(tr, full_sd)
-    losses = tr.train()
+    norms = []
+    losses = tr.train(on_step=lambda t, lv: norms.append(float(t.optimizer.grad_norm.item())))
     if rank == 0:
         with open(outq_path, "w") as f:
             json.dump(losses, f)
+        with open(outq_path + ".norms", "w") as f:
+            json.dump(norms, f)

@@ -21,8 +21,10 @@ def _single(kwargs):
     ps.initialize_model_parallel()
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     W.load_from_full(tr, full)
-    out = tr.train()
+    norms = []
+    out = tr.train(on_step=lambda t, lv: norms.append(float(t.optimizer.grad_norm.item())))
     ps.destroy_model_parallel()
+    _single.last_norms = norms
     return out, mck
 
 
@@ -70,3 +72,31 @@ def test_parallel_matches_single_process(name, tmp_path):
     assert len(got) == len(ref)
     for a, b in zip(got, ref):
         assert abs(a - b) <= 2e-3 * max(1.0, abs(b)), f"{name}: {got} vs {ref}"
+
+
+NORM_CASES = {
+    # norm weights (and, without sequence parallelism, nothing else) are replicated over the tensor-parallel ranks
+    "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
+    "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
+    "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
+    # whole-parameter optimizers: every expert-parallel rank owns different experts
+    "ep2_moe_sgd": dict(world=2, kw=dict(ep=2, moe=True, opt="sgd", distopt=False)),
+    "ep2_moe_adam": dict(world=2, kw=dict(ep=2, moe=True)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(NORM_CASES))
+def test_grad_norm_matches_single_process(name, tmp_path):
+    """The global gradient norm (and so the clip coefficient) must not depend on the parallel layout: tensor-parallel
+    duplicates are counted once, expert shards of all expert-parallel ranks are included."""
+    case = NORM_CASES[name]
+    kw = dict(seq=32, gbs=8, mbs=2, iters=2, layers=4, lr=1e-3)
+    kw.update(case["kw"])
+    ref, mck = _single(kw)
+    ref_norms = list(_single.last_norms)
+    out = tmp_path / "losses.json"
+    run_ranks(W.train_worker, case["world"], "gloo", args=(kw, mck, str(out)), timeout=240)
+    got = json.loads((tmp_path / "losses.json.norms").read_text())
+    assert len(got) == len(ref_norms) and all(n > 0 for n in ref_norms)
+    for a, b in zip(got, ref_norms):
+        assert abs(a - b) <= 2e-3 * b, f"{name}: grad norms {got} vs {ref_norms}"

@@ -20,6 +20,35 @@ EXTRA_KNOWN = {"trainer_class", "tp_comm_overlap", "tp_comm_overlap_rs", "pp_alg
                "disable_tensorboard", "disable_mlflow", "valid_data_path"}
 
 
+# Keys the presets carry for compatibility with the reference's configuration surface but that this engine does not
+# act on.  Setting one of them to something other than the preset's value is reported (an error under
+# PRIMUS_STRICT_CONFIG=1), so that no setting is accepted and then silently ignored.  tests/test_config_cpu.py checks
+# that every preset key is either read by the code base or listed here.
+INERT_KEYS = {
+    # numerics fixed by the design: bf16 parameters, fp32 main gradients and accumulation, no loss scaling
+    "accumulate_allreduce_grads_in_fp32", "loss_scale", "ddp_average_in_collective",
+    # model switches of architectures that are not built (biases, dropout, LayerNorm, learned positions)
+    "add_qkv_bias", "attention_dropout", "hidden_dropout", "normalization", "position_embedding_type", "lora_dropout",
+    # data loading is synchronous mock / indexed data staged by the trainer itself
+    "create_attention_mask_in_dataloader", "dataloader_type", "num_workers", "train_samples",
+    # kernel selection switches of the reference's operator library: one native implementation here
+    "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_autotune", "use_turbo_parallel_linear",
+    "use_turbo_rms_norm", "turbo_deepep_num_cu",
+    # services that are not built
+    "enable_ft_package", "enable_gloo_process_groups", "generate_tracelens_report", "straggler_ctrlr_port",
+    "non_persistent_ckpt_type", "non_persistent_save_interval", "weight_deosc", "weight_deosc_period",
+    "weight_deosc_ratio", "sft_grad_sanitize", "sft_pack_cache_dir", "trainable", "mlflow_run_name",
+    "log_throughput", "log_timers_to_tensorboard", "torch_profiler_record_shapes", "torch_profiler_use_gzip",
+    "torch_profiler_with_stack", "use_tp_pp_dp_mapping", "offload_ops",
+    # zero-bubble runtime knobs of the reference's second pipeline implementation (the schedule is chosen with
+    # pp_algorithm / pipeline_schedule here)
+    "enable_zero_bubble", "patch_primus_pipeline", "patch_zero_bubble", "pp_communication_method",
+    "zero_bubble_adaptive_memory_limit_percentile", "zero_bubble_max_pending_backward",
+    "zero_bubble_pipeline_timers_end_iter", "zero_bubble_pipeline_timers_start_iter", "zero_bubble_v_schedule",
+    "zero_bubble_v_schedule_mem_setup",
+}
+
+
 def known_keys(module_preset: str | None = None, model_preset: str | None = None, framework: str = "primus_b200") -> set:
     from ...engine.trainer import TrainConfig
     from ...models.config import TransformerConfig
@@ -53,4 +82,25 @@ def check_experiment(raw: dict, cli_overrides: dict | None = None) -> list[str]:
         for rec in check_keys(given, known):
             hint = f" (did you mean {', '.join(rec['suggestions'])}?)" if rec["suggestions"] else ""
             findings.append(f"modules.{name}: unknown key {rec['key']!r}{hint}")
+        findings += [f"modules.{name}: {msg}" for msg in
+                     check_inert({**(spec.get("overrides") or {}), **(cli_overrides or {})},
+                                 spec.get("config"), spec.get("model"), spec.get("framework", "primus_b200"))]
     return findings
+
+
+def check_inert(values: dict, module_preset: str | None = None, model_preset: str | None = None,
+                framework: str = "primus_b200") -> list[str]:
+    """Settings that parse but change nothing: a key of ``INERT_KEYS`` given a value other than its preset default."""
+    defaults: dict = {}
+    if module_preset:
+        defaults.update(load_preset(module_preset, "modules", framework))
+    if model_preset:
+        defaults.update(load_preset(model_preset, "models", framework))
+    out = []
+    for k, v in values.items():
+        if k in INERT_KEYS and k in defaults and v != defaults[k]:
+            out.append(f"key {k!r} = {v!r} is accepted for compatibility but has no effect in this engine "
+                       f"(preset value {defaults[k]!r})")
+        elif k in INERT_KEYS and k not in defaults and v not in (None, False, 0):
+            out.append(f"key {k!r} = {v!r} is accepted for compatibility but has no effect in this engine")
+    return out

@@ -85,6 +85,9 @@ class TransformerConfig:
     fp8: Optional[str] = None  # None | "e4m3"
     fp8_recipe: str = "mxfp8"
     recompute_granularity: Optional[str] = None  # None | selective | full
+    recompute_method: Optional[str] = None       # full: "uniform" (chunks of recompute_num_layers) | "block" (first N layers)
+    recompute_num_layers: Optional[int] = None
+    recompute_modules: Optional[List[str]] = None  # selective: "core_attn" (default), "mlp"
     recompute_layer_ids: Optional[List[int]] = None
     cpu_offloading: bool = False                   # keep the saved activations of the first layers in pinned host memory
     cpu_offloading_num_layers: int = 0

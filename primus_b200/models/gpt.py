@@ -110,10 +110,12 @@ class SelfAttention(nn.Module):
                                                     rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale)
         else:
             sinks = self.core_attention.softmax_offset.float() if self.has_sinks else None
-            ctx_out = layers.rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
-                                            rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
-                                            window=self.window, sinks=sinks, segments=segments,
-                                            softcap=cfg.attn_logit_softcapping or 0.0)
+            ctx_out = selective_checkpoint(
+                cfg, "core_attn",
+                lambda t: layers.rope_attention(t, cos, sin, pos, batch, self.hq, self.hkv, d,
+                                                rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
+                                                window=self.window, sinks=sinks, segments=segments,
+                                                softcap=cfg.attn_logit_softcapping or 0.0), qkv)
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 
@@ -199,8 +201,10 @@ class TransformerLayer(nn.Module):
         if self.is_moe:
             y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon, res1)
             mlp_out = self.mlp(y)
+        elif res1 is None:
+            mlp_out, res2 = selective_checkpoint(self.cfg, "mlp", lambda a: self.mlp(a, None), attn_out)
         else:
-            mlp_out, res2 = self.mlp(attn_out, res1)
+            mlp_out, res2 = selective_checkpoint(self.cfg, "mlp", self.mlp, attn_out, res1)
         return mlp_out, res2
 
 
@@ -339,9 +343,9 @@ class GPTModel(nn.Module):
             pos = (position_ids.reshape(-1).to(torch.int32) if position_ids is not None
                    else torch.arange(seq, device=device, dtype=torch.int32).repeat(batch))
         rope = (cos, sin, pos, _segments(cu_seqlens, batch, seq))
-        for i in self.decoder.layer_indices:
-            layer = self.decoder.layers[str(i)]
-            hidden, residual = _run_layer(layer, hidden, residual, rope, batch, cfg)
+        for group, ckpt in recompute_plan(cfg, self.decoder.layer_indices):
+            hidden, residual = _run_group([self.decoder.layers[str(i)] for i in group], hidden, residual, rope, batch,
+                                          cfg, ckpt)
         if not self.post_process:
             return hidden, residual, batch, seq
         w = self.output_weight()
@@ -415,15 +419,55 @@ def _segments(cu_seqlens, batch: int, seq: int):
     return segs
 
 
-def _run_layer(layer, hidden, residual, rope, batch, cfg):
-    recompute = cfg.recompute_granularity == "full" and (
-        cfg.recompute_layer_ids is None or layer.layer_idx in cfg.recompute_layer_ids)
-    if recompute and torch.is_grad_enabled():
+def recompute_plan(cfg, layer_indices) -> list:
+    """Groups of consecutive layers of this model chunk and whether each group is run under activation checkpointing
+    (only the group's input is kept; its layers run again in the backward pass).  ``recompute_granularity: full``:
+
+    * ``recompute_layer_ids`` given: exactly those (global) layers, one checkpoint each;
+    * ``recompute_method: uniform``: the chunk is cut into groups of ``recompute_num_layers`` layers, every group is one
+      checkpoint (larger groups keep fewer inputs and recompute the same amount);
+    * ``recompute_method: block``: the first ``recompute_num_layers`` layers of the chunk are checkpointed one by one,
+      the rest keep their activations (for when only part of the memory has to be saved);
+    * neither: every layer is its own checkpoint.
+
+    Semantics of Megatron's ``recompute_granularity / recompute_method / recompute_num_layers``
+    (primus/configs/modules/megatron/trainer_base.yaml:248-254 in the reference) plus the reference's explicit layer list
+    (primus/backends/megatron/patches/recompute_layer_patches.py:326)."""
+    idx = list(layer_indices)
+    if cfg.recompute_granularity != "full":
+        return [([i], False) for i in idx]
+    if cfg.recompute_layer_ids is not None:
+        ids = set(cfg.recompute_layer_ids)
+        return [([i], i in ids) for i in idx]
+    method = (cfg.recompute_method or "").lower() or None
+    n = cfg.recompute_num_layers
+    if method == "uniform":
+        n = max(int(n or 1), 1)
+        return [(idx[a:a + n], True) for a in range(0, len(idx), n)]
+    if method == "block":
+        n = len(idx) if n is None else max(int(n), 0)
+        return [([i], pos < n) for pos, i in enumerate(idx)]
+    if method is not None:
+        raise ValueError(f"recompute_method {cfg.recompute_method!r}: uniform or block")
+    return [([i], True) for i in idx]
+
+
+def _run_group(layers_, hidden, residual, rope, batch, cfg, checkpointed: bool):
+    def run(h, r):
+        for layer in layers_:
+            h, r = _run_layer(layer, h, r, rope, batch, cfg)
+        return h, r
+
+    if checkpointed and torch.is_grad_enabled():
         from torch.utils.checkpoint import checkpoint
 
         if residual is None:
-            return checkpoint(lambda h: layer(h, None, rope, batch), hidden, use_reentrant=False)
-        return checkpoint(lambda h, r: layer(h, r, rope, batch), hidden, residual, use_reentrant=False)
+            return checkpoint(lambda h: run(h, None), hidden, use_reentrant=False)
+        return checkpoint(run, hidden, residual, use_reentrant=False)
+    return run(hidden, residual)
+
+
+def _run_layer(layer, hidden, residual, rope, batch, cfg):
     if cfg.cpu_offloading and torch.is_grad_enabled() and hidden.is_cuda and (
             layer.layer_idx < (cfg.cpu_offloading_num_layers or 0)):
         from ..engine.offload import offload_saved_activations
@@ -431,6 +475,18 @@ def _run_layer(layer, hidden, residual, rope, batch, cfg):
         with offload_saved_activations():
             return layer(hidden, residual, rope, batch)
     return layer(hidden, residual, rope, batch)
+
+
+def selective_checkpoint(cfg, module: str, fn, *args):
+    """``recompute_granularity: selective``: run ``fn(*args)`` under activation checkpointing when ``module`` is in
+    ``recompute_modules`` (default: the core attention only, whose saved output and statistics are then rebuilt from
+    q / k / v in the backward pass)."""
+    if cfg.recompute_granularity == "selective" and torch.is_grad_enabled() and \
+            module in (cfg.recompute_modules or ["core_attn"]):
+        from torch.utils.checkpoint import checkpoint
+
+        return checkpoint(fn, *args, use_reentrant=False)
+    return fn(*args)
 
 
 def build_model(cfg: TransformerConfig, device="cpu", stage_id: int = 0, n_stages: int = 1,

@@ -45,7 +45,9 @@ class Candidate:
         if p.vpp > 1:
             out.append(f"--virtual_pipeline_model_parallel_size={p.vpp}")
         if p.recompute_layers:
-            out += ["--recompute_granularity=full", f"--recompute_num_layers={p.recompute_layers}"]
+            # the memory model counts `recompute_layers` layers per stage without saved activations: method "block"
+            out += ["--recompute_granularity=full", "--recompute_method=block",
+                    f"--recompute_num_layers={p.recompute_layers}"]
         return out
 
     def as_dict(self) -> dict:

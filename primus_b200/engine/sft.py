@@ -247,8 +247,11 @@ class LoRAEngine:
 
     @torch.no_grad()
     def refresh(self):
+        from ..ops import gemm as _gemm
+
         for h in self.holders:
             h.weight.data.copy_((h.base_weight.float() + h.lora.delta()).to(h.weight.dtype))
+        _gemm.bump_weight_generation()   # weights were rewritten in place: cached quantised copies expire
 
     @torch.no_grad()
     def optimizer_step(self, lr: Optional[float] = None):
@@ -281,6 +284,10 @@ def merge_lora(model: nn.Module) -> int:
                 mod.weight.data.copy_((mod.base_weight.float() + ad.delta()).to(mod.weight.dtype))
             del mod._modules["lora"]
             n += 1
+    if n:
+        from ..ops import gemm as _gemm
+
+        _gemm.bump_weight_generation()
     return n
 
 

@@ -75,6 +75,17 @@ class TrainConfig:
     save: Optional[str] = None
     load: Optional[str] = None
     save_interval: Optional[int] = None
+    ckpt_format: str = "torch_dist"          # torch_dist (torch.distributed.checkpoint files) | torch (pickle per rank)
+    auto_detect_ckpt_format: bool = False
+    async_save: bool = False                 # file writing on a side thread; the step loop continues after the D2H copy
+    ckpt_fully_parallel_save: bool = True    # replicated tensors are written by different data-parallel ranks
+    ckpt_fully_parallel_load: bool = False   # ... and read by one of them each, then broadcast
+    dist_ckpt_strictness: str = "assume_ok_unexpected"
+    finetune: bool = False                   # load weights only; iteration, optimizer and RNG start fresh
+    no_load_optim: bool = False
+    no_save_optim: bool = False
+    no_load_rng: bool = False
+    no_save_rng: bool = False
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
     exit_signal_handler: bool = False
@@ -650,6 +661,9 @@ class Trainer:
                 if tc.exit_duration_in_mins and (time.time() - start_wall) / 60.0 > tc.exit_duration_in_mins:
                     break
         finally:
+            from . import checkpoint as _ckpt
+
+            _ckpt.finalize_async_save()
             profiler.close()
             writer.close()
             if exit_flag is not None:

@@ -24,6 +24,12 @@ def test_qkv_layout_roundtrip():
     assert torch.equal(m[(g + 1) * d:(g + 2) * d], w[(hq + hkv) * d:(hq + hkv) * d + d])
 
 
+def _dcp_metadata(d):
+    from torch.distributed.checkpoint import FileSystemReader
+
+    return FileSystemReader(d).read_metadata().state_dict_metadata
+
+
 def _trainer(iters=6, **kw):
     ps.destroy_model_parallel()
     ps.initialize_model_parallel()
@@ -42,7 +48,7 @@ def test_save_layout_and_bitexact_resume(tmp_path):
     assert {"common.pt", ".metadata", "__0_0.distcp"} <= set(os.listdir(d))
     common = torch.load(os.path.join(d, "common.pt"), weights_only=False)
     assert "args" in common and common["iteration"] == 3
-    meta = json.load(open(os.path.join(d, ".metadata")))["tensors"]
+    meta = _dcp_metadata(d)
     assert "decoder.layers.0.self_attention.linear_qkv.layer_norm_weight" in meta
     assert "decoder.layers.0.mlp.linear_fc1.weight" in meta and "embedding.word_embeddings.weight" in meta
     assert "output_layer.weight" in meta and "decoder.final_layernorm.weight" in meta
@@ -82,10 +88,8 @@ def test_load_tp1_checkpoint_into_tp2(tmp_path):
     a.tcfg.use_distributed_optimizer = True
     a.train(2)
     a.save_checkpoint(root)
-    # continue without optimizer state on the reference too (layout change drops the moments)
-    b = _trainer(iters=4)
-    C.load_checkpoint(b, root, load_optim=False)
-    ref = b.train(2)
+    # the optimizer state is re-sliced for the new tensor-parallel layout: compare with the uninterrupted run
+    ref = a.train(2)
     outp = str(tmp_path / "l.json")
     run_ranks(_reshard_worker, 2, "gloo", args=(root, outp), timeout=200)
     got = json.load(open(outp))
@@ -126,5 +130,116 @@ def test_fsdp2_checkpoint_resume(tmp_path):
     run_ranks(_fsdp_ckpt_worker, 2, "gloo", args=(root, outp), timeout=240)
     r = json.load(open(outp))
     assert r["ref"] == r["got"], r
-    meta = json.load(open(os.path.join(root, "iter_0000002", ".metadata")))["tensors"]
-    assert "embedding.word_embeddings.weight" in meta and len(meta["embedding.word_embeddings.weight"]) == 1
+    meta = _dcp_metadata(os.path.join(root, "iter_0000002"))
+    emb = meta["embedding.word_embeddings.weight"]
+    assert len(emb.chunks) == 2 and tuple(emb.size) == (512, 64)      # one chunk per data-parallel rank
+
+
+def test_checkpoint_is_readable_by_plain_dcp(tmp_path):
+    """The files are stock torch.distributed.checkpoint files: ``dcp.load`` fills plain tensors of the global shapes
+    without any code of this package, and the values are the model's (QKV rows in the Megatron-core interleave)."""
+    import torch.distributed.checkpoint as dcp
+
+    root = str(tmp_path / "ckpt")
+    a = _trainer()
+    a.train(1)
+    d = a.save_checkpoint(root)
+    md = _dcp_metadata(d)
+    keys = ["decoder.layers.1.self_attention.linear_qkv.weight", "decoder.layers.0.mlp.linear_fc2.weight",
+            "optimizer.state.exp_avg.decoder.layers.0.mlp.linear_fc2.weight"]
+    sd = {k: torch.zeros(tuple(md[k].size), dtype=md[k].properties.dtype) for k in keys}
+    dcp.load(sd, checkpoint_id=d, no_dist=True)
+    params = dict(a.model.named_parameters())
+    cfg = a.mcfg
+    qkv = params["decoder.layers.1.self_attention.linear_qkv.weight"]
+    assert torch.equal(sd[keys[0]], C.qkv_internal_to_mcore(qkv.detach(), cfg.num_attention_heads, cfg.num_query_groups,
+                                                            cfg.kv_channels))
+    assert torch.equal(sd[keys[1]], params["decoder.layers.0.mlp.linear_fc2.weight"].detach())
+    assert sd[keys[2]].abs().sum() > 0
+
+
+def test_async_save_and_torch_format(tmp_path):
+    root = str(tmp_path / "a")
+    a = _trainer()
+    a.tcfg.async_save = True
+    a.train(2)
+    a.save_checkpoint(root)
+    ref = a.train(2)                       # training continues while the files are written
+    C.finalize_async_save()
+    b = _trainer()
+    assert b.load_checkpoint(root) == 2 and b.train(2) == ref
+    # legacy per-rank pickles, found by auto-detection
+    root2 = str(tmp_path / "t")
+    c = _trainer()
+    c.tcfg.ckpt_format = "torch"
+    c.train(2)
+    d = c.save_checkpoint(root2)
+    ref2 = c.train(2)
+    assert os.path.exists(os.path.join(d, "mp_rank_00", "model_optim_rng.pt"))
+    e = _trainer()
+    e.tcfg.auto_detect_ckpt_format = True
+    assert e.load_checkpoint(root2) == 2 and e.train(2) == ref2
+
+
+def test_strictness_and_missing_optimizer_state(tmp_path):
+    import pytest
+
+    root = str(tmp_path / "ckpt")
+    a = _trainer()
+    a.tcfg.no_save_optim = True
+    a.train(1)
+    a.save_checkpoint(root)
+    logs = []
+    b = _trainer()
+    b.log = logs.append
+    assert b.load_checkpoint(root) == 1            # weights load; the reset of the optimizer is said out loud
+    assert any("without optimizer state" in l for l in logs)
+    # a model with an extra layer: its tensors are missing from the checkpoint
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, layers=6)
+    c = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    with pytest.raises(KeyError, match="lacks"):
+        c.load_checkpoint(root)
+    c.tcfg.dist_ckpt_strictness = "log_all"
+    c.tcfg.no_load_optim = True
+    logs2 = []
+    c.log = logs2.append
+    assert c.load_checkpoint(root) == 1 and any("missing keys" in l for l in logs2)
+
+
+def _dp_worker(rank, world, root, outp, phase):
+    ps.destroy_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=8, mbs=1, iters=4)
+    tc.ckpt_fully_parallel_load = True
+    ps.initialize_model_parallel()
+    torch.manual_seed(5)
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    if phase == "save":
+        tr.train(2)
+        tr.save_checkpoint(root)
+        rest = tr.train(2)
+    else:
+        assert tr.load_checkpoint(root) == 2
+        rest = tr.train(2)
+    if rank == 0:
+        json.dump(rest, open(outp, "w"))
+
+
+def test_resume_with_another_data_parallel_size(tmp_path):
+    """Saved on 2 data-parallel ranks (each holds half of every ZeRO-1 shard), resumed on 4 and on 1: the optimizer
+    state is re-sliced from the chunk metadata and the next losses agree with the uninterrupted run."""
+    root = str(tmp_path / "ckpt")
+    run_ranks(_dp_worker, 2, "gloo", args=(root, str(tmp_path / "ref.json"), "save"), timeout=240)
+    ref = json.load(open(tmp_path / "ref.json"))
+    run_ranks(_dp_worker, 4, "gloo", args=(root, str(tmp_path / "dp4.json"), "load"), timeout=240)
+    got4 = json.load(open(tmp_path / "dp4.json"))
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=8, mbs=1, iters=4)
+    one = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    assert one.load_checkpoint(root) == 2
+    got1 = one.train(2)
+    for got in (got4, got1):
+        for x, y in zip(got, ref):
+            assert abs(x - y) <= 1e-5 * max(1.0, abs(y)), (got, ref)

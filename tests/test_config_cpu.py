@@ -181,3 +181,43 @@ def test_example_configs_pass_the_schema_check():
         with open(os.path.join(root, f)) as fh:
             raw = yaml.safe_load(fh)
         assert schema_check.check_experiment(raw) == [], f
+
+
+def test_every_preset_key_is_read_or_declared_inert():
+    """No key may parse and then silently do nothing: a key carried by a module / model preset is a field of the two
+    config dataclasses, is consumed somewhere in the package (its name appears in the Python sources), or is listed in
+    ``schema_check.INERT_KEYS`` (setting those is reported)."""
+    import dataclasses
+    import glob
+    import os
+    import re
+
+    from primus_b200.core.config import schema_check
+    from primus_b200.core.config.presets import load_preset
+    from primus_b200.engine.trainer import TrainConfig
+    from primus_b200.models.config import TransformerConfig
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "primus_b200")
+    keys = set()
+    for kind in ("modules", "models"):
+        for f in glob.glob(os.path.join(root, "configs", kind, "*.yaml")):
+            keys |= set(load_preset(os.path.basename(f), kind))
+    fields = {f.name for f in dataclasses.fields(TransformerConfig)} | {f.name for f in dataclasses.fields(TrainConfig)}
+    src = ""
+    for f in glob.glob(os.path.join(root, "**", "*.py"), recursive=True):
+        if not f.endswith(os.path.join("config", "schema_check.py")):
+            src += open(f).read()
+    words = set(re.findall(r"[A-Za-z_][A-Za-z0-9_]*", src))
+    orphan = sorted(k for k in keys if k not in fields and k not in schema_check.EXTRA_KNOWN and k not in words
+                    and k not in schema_check.INERT_KEYS)
+    assert not orphan, f"preset keys that nothing reads and that are not declared inert: {orphan}"
+    stale = sorted(k for k in schema_check.INERT_KEYS if k in fields)
+    assert not stale, f"declared inert but now a config field: {stale}"
+
+
+def test_inert_key_is_reported(tmp_path):
+    from primus_b200.core.config import schema_check
+
+    msgs = schema_check.check_inert({"hidden_dropout": 0.1, "lr": 1e-3}, "pre_trainer.yaml", "llama3.1_8B.yaml")
+    assert len(msgs) == 1 and "hidden_dropout" in msgs[0] and "no effect" in msgs[0]
+    assert schema_check.check_inert({"hidden_dropout": 0.0}, "pre_trainer.yaml", "llama3.1_8B.yaml") == []

@@ -226,6 +226,11 @@ def main() -> int:
                     help="context-parallel scheme: all-to-all over heads (Ulysses), K/V all-gather with zig-zag chunks, or ring (p2p)")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
     ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
+    ap.add_argument("--no-overlap-param-gather", action="store_true",
+                    help="NCCL path: wait for the parameter all-gather right after the optimizer step")
+    ap.add_argument("--grad-reduce", default="bf16", choices=["bf16", "fp32"],
+                    help="wire format of the data-parallel gradient reduction (accumulation stays fp32); the reference's "
+                         "MXFP8 recipe sets grad_reduce_in_bf16")
     ap.add_argument("--precision", default="mxfp8", choices=["bf16", "mxfp8"],
                     help="linear-layer GEMM precision: bf16, or MXFP8 (E4M3 values, UE8M0 scale per 32 elements; fp32 accumulation)")
     ap.add_argument("--ref-ac", default="auto", choices=["auto", "none", "selective", "full"],
@@ -271,7 +276,9 @@ def main() -> int:
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,
                        clip_grad=1.0, use_distributed_optimizer=True, overlap_grad_reduce=world > 1,
-                       log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp)
+                       log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp,
+                       overlap_param_gather=world > 1 and not args.no_overlap_param_gather,
+                       grad_reduce_in_bf16=world > 1 and args.grad_reduce == "bf16" and not args.fused_dp)
     ps.initialize_model_parallel(tp=args.tp, pp=1, cp=args.cp)
 
     def barrier():
@@ -362,7 +369,11 @@ def main() -> int:
             "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
             "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
                        "micro_batch": args.micro_batch, "parallelism": f"dp{world // (args.tp * args.cp)}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + (f"cp{args.cp}-{args.cp_comm}" if args.cp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
-                       "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0",
+                       "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0" + (
+                           "" if world == 1 else (", fused P2P reduce-scatter overlapped with backward" if args.fused_dp else
+                                                  f", NCCL reduce-scatter in {args.grad_reduce} overlapped with backward, "
+                                                  + ("parameter all-gather overlapped with the next forward"
+                                                     if not args.no_overlap_param_gather else "blocking parameter all-gather"))),
                        "recompute": f"full recomputation of the first {recomputed} layers (out-of-memory fallback)" if recomputed else "none",
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},
             "tokens_per_s_per_gpu": value / world,

@@ -57,6 +57,7 @@ class TrainConfig:
     muon_num_ns_steps: int = 5
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
+    grad_reduce_in_bf16: bool = False    # bf16 on the wire for the data-parallel gradient reduction (fp32 accumulation)
     ddp_bucket_size: Optional[int] = None
     seed: int = 1234
     data_seed: int = 1234
@@ -300,12 +301,14 @@ class Trainer:
                 dense, st.dp_cp_group if st.cp > 1 else st.dp_group, st.dp * st.cp, st.dp_rank * st.cp + st.cp_rank,
                 train_cfg.ddp_bucket_size, torch.float32, train_cfg.use_distributed_optimizer,
                 train_cfg.overlap_grad_reduce, True, self.comm_stream,
-                symmetric=train_cfg.fused_dp_optimizer and train_cfg.use_distributed_optimizer))
+                symmetric=train_cfg.fused_dp_optimizer and train_cfg.use_distributed_optimizer,
+                grad_reduce_in_bf16=train_cfg.grad_reduce_in_bf16))
         if expert:
             self.buffers.append(ParamGradBuffer(
                 expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
                 train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream,
-                extra_grad_scale=float(st.edp) / float(st.dp * st.cp)))
+                extra_grad_scale=float(st.edp) / float(st.dp * st.cp),
+                grad_reduce_in_bf16=train_cfg.grad_reduce_in_bf16))
         norm_groups = [st.mp_group] if (st.tp > 1 or st.pp > 1) else []
         from ..parallel import matrix_optimizers
 
@@ -328,6 +331,44 @@ class Trainer:
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
             check_for_nan=train_cfg.check_for_nan_in_loss_and_grad, tp_size=st.tp,
             expert_norm_group=st.ep_group if (st.ep > 1 and not train_cfg.use_distributed_optimizer) else None)
+        self._install_param_gather_waits()
+
+    # ------------------------------------------------------------------ overlap_param_gather
+    def _install_param_gather_waits(self):
+        """``overlap_param_gather``: after an optimizer step the bucket all-gathers run asynchronously; every transformer
+        layer waits, right before its forward, for the buckets that hold its parameters, and the model waits for the
+        embedding buckets at its start and for the final norm / output layer buckets before the head."""
+        tc = self.tcfg
+        active = tc.overlap_param_gather and tc.use_distributed_optimizer and not self._emb_primary and \
+            not self._emb_replica and any(b.dp_size > 1 and not b.symmetric for b in self.buffers)
+        self.optimizer.overlap_param_gather = bool(active)
+        if tc.overlap_param_gather and not active and any(b.dp_size > 1 for b in self.buffers):
+            self.log("overlap_param_gather is off on this run (it needs the distributed optimizer on the NCCL path and "
+                     "word embeddings that are not shared between pipeline stages)")
+        if not active:
+            return
+
+        def waiter(params):
+            todo = [(buf, b) for buf in self.buffers for b in buf.buckets_of(params)]
+
+            def wait(*_a):
+                for buf, b in todo:
+                    buf.wait_bucket_params(b)
+            return wait
+
+        for m in self.model_chunks:
+            layer_params = set()
+            for layer in m.decoder.layers.values():
+                ps_ = list(layer.parameters())
+                layer_params.update(ps_)
+                layer.register_forward_pre_hook(waiter(ps_))
+            head = [p for n, p in m.named_parameters() if p not in layer_params and not n.startswith("embedding.")]
+            emb = [p for n, p in m.named_parameters() if n.startswith("embedding.")]
+            m._param_waiters = {"embedding": waiter(emb), "head": waiter(head + emb)}
+
+    def finish_param_sync(self):
+        for buf in self.buffers:
+            buf.finish_param_sync()
 
     def _init_schedule_and_data(self):
         model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st

@@ -328,6 +328,9 @@ class GPTModel(nn.Module):
         cfg = self.cfg
         st = ps.get_state()
         sp = cfg.sequence_parallel and st.tp > 1
+        waiters = getattr(self, "_param_waiters", None)   # asynchronous parameter all-gathers (engine/trainer.py)
+        if waiters is not None:
+            waiters["embedding"]()
         if self.pre_process:
             batch, seq = tokens.shape
             x = self.embedding(tokens.reshape(-1))
@@ -348,6 +351,8 @@ class GPTModel(nn.Module):
                                           cfg, ckpt)
         if not self.post_process:
             return hidden, residual, batch, seq
+        if waiters is not None:
+            waiters["head"]()
         w = self.output_weight()
         mtp_loss = None
         if cfg.mtp_num_layers and labels is not None and loss_weights is not None:

@@ -46,7 +46,7 @@ class ParamGradBuffer:
     def __init__(self, params: list[torch.nn.Parameter], dp_group, dp_size: int, dp_rank: int,
                  bucket_size: Optional[int] = None, grad_dtype=torch.float32, use_distributed_optimizer=True,
                  overlap_grad_reduce=False, average_in_collective=True, comm_stream=None, symmetric=False,
-                 extra_grad_scale: float = 1.0):
+                 extra_grad_scale: float = 1.0, grad_reduce_in_bf16: bool = False):
         """``extra_grad_scale`` multiplies the gradients before the collective.  Expert parameters need it: every
         expert-parallel rank accumulates the contributions of the tokens of all ``ep`` ranks, each normalised for its
         own rank's micro-batches, and the buffer is then only averaged over the (smaller) expert-data-parallel group,
@@ -54,6 +54,10 @@ class ParamGradBuffer:
         ``expert_gradient_scaling_factor = edp / dp``)."""
         assert params, "empty parameter list"
         self.extra_grad_scale = float(extra_grad_scale)
+        # ``grad_reduce_in_bf16``: gradients are accumulated over the micro-batches in fp32 as always, but travel as bf16
+        # (half the bytes of the reduce-scatter / all-reduce); the reduced values are widened back into the fp32 buffer
+        self.grad_reduce_in_bf16 = bool(grad_reduce_in_bf16) and dp_size > 1
+        self._bf16_stage = None
         self.params = params
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.use_distributed_optimizer = use_distributed_optimizer
@@ -94,7 +98,7 @@ class ParamGradBuffer:
             self.sym_grad = SymmetricBuffer(self.numel * 4, dp_group, device)
             self.param_data = self.sym_param.local(torch.bfloat16, self.numel)
             self.grad_data = self.sym_grad.local(torch.float32, self.numel)
-            self.overlap_grad_reduce = False
+            self.fused_sumsq = torch.zeros(1, dtype=torch.float32, device=device)   # sum of squares of the reduced shards
         else:
             self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=device)
             self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=device)
@@ -123,6 +127,8 @@ class ParamGradBuffer:
 
     def zero_grad(self):
         self.grad_data.zero_()
+        if self.symmetric:
+            self.fused_sumsq.zero_()
         for b in self.buckets:
             b.pending = set(b.params)
             b.rs_handle = None
@@ -137,7 +143,41 @@ class ParamGradBuffer:
         if not b.pending and b.rs_handle is None:
             self._start_bucket_sync(b, async_op=True)
 
+    def _start_bucket_sync_fused(self, b: Bucket, async_op: bool):
+        """Symmetric buffers: this rank's shard of the bucket is summed straight from the peers' gradient buffers
+        (``csrc/dp_fused.cu``), in place, after a device-side barrier that tells every rank that all copies of the bucket
+        are final.  Under ``overlap_grad_reduce`` barrier and kernel run on the side stream while the backward pass of
+        the earlier layers continues; ranks reach the buckets in the same order, so the barrier slots line up."""
+        import ctypes
+
+        from ..ops import _lib
+        from ..ops.fused import scratch
+
+        stream = self.comm_stream if (async_op and self.comm_stream is not None) else None
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream)
+        else:
+            import contextlib
+
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if self.extra_grad_scale != 1.0:
+                self.grad_data[b.start:b.end].mul_(self.extra_grad_scale)
+            self.sym_grad.barrier(2 + b.index % 96)
+            s, e = self.shard_range(b)
+            tbl = (ctypes.c_long * self.dp_size)(*[self.sym_grad.peer_ptr(r) for r in range(self.dp_size)])
+            P = _lib.call_ret("dp_num_partials")
+            _lib.call("dp_reduce_scatter", tbl, self.dp_size, self.dp_rank, s, e - s, self.grad_data[s:e],
+                      self.grad_scale, scratch(self.device, "dp_partials", P), self.fused_sumsq, 1)
+            b.rs_handle = True
+            if stream is not None:
+                b.rs_event = torch.cuda.Event()
+                b.rs_event.record(stream)
+
     def _start_bucket_sync(self, b: Bucket, async_op: bool):
+        if self.symmetric:
+            return self._start_bucket_sync_fused(b, async_op)
         g = self.grad_data[b.start:b.end]
         stream = self.comm_stream if (async_op and self.comm_stream is not None) else None
         if stream is not None:
@@ -155,7 +195,9 @@ class ParamGradBuffer:
             op = dist.ReduceOp.SUM if (on_cpu or self.grad_scale == 1.0) else dist.ReduceOp.AVG
             if on_cpu and self.grad_scale != 1.0:
                 g.mul_(self.grad_scale)
-            if self.use_distributed_optimizer:
+            if self.grad_reduce_in_bf16:
+                self._reduce_bucket_bf16(b, g, op, on_cpu)
+            elif self.use_distributed_optimizer:
                 s, e = self.shard_range(b)
                 out = self.grad_data[s:e]
                 if on_cpu:
@@ -170,10 +212,27 @@ class ParamGradBuffer:
                 b.rs_event = torch.cuda.Event()
                 b.rs_event.record(stream)
 
+    def _reduce_bucket_bf16(self, b: Bucket, g: torch.Tensor, op, on_cpu: bool):
+        """bf16 on the wire: cast the bucket, reduce, widen the result back.  Runs on the stream the caller selected
+        (the side stream under ``overlap_grad_reduce``), so the collective itself is issued synchronously there."""
+        if self._bf16_stage is None:
+            self._bf16_stage = torch.empty(self.numel, dtype=torch.bfloat16, device=self.device)
+        lo = self._bf16_stage[b.start:b.end]
+        lo.copy_(g)
+        if self.use_distributed_optimizer and not on_cpu:
+            s, e = self.shard_range(b)
+            out = self._bf16_stage[s:e]
+            dist.reduce_scatter_tensor(out, lo, op=op, group=self.dp_group)
+            self.grad_data[s:e].copy_(out)
+        else:
+            dist.all_reduce(lo, op=op, group=self.dp_group)
+            g.copy_(lo)
+        b.rs_handle = True
+
     def finish_grad_sync(self):
         """Reduce every bucket that has not been started and wait for all of them."""
-        if self.dp_size == 1 or self.symmetric:  # symmetric buffers: the fused optimizer kernels do the reduction
-            if self.extra_grad_scale != 1.0 and not self.symmetric:
+        if self.dp_size == 1:
+            if self.extra_grad_scale != 1.0:
                 self.grad_data.mul_(self.extra_grad_scale)
             return
         for b in self.buckets:
@@ -200,11 +259,26 @@ class ParamGradBuffer:
             b.ag_handle = dist.all_gather_into_tensor(full, self.param_data[s:e], group=self.dp_group,
                                                       async_op=async_op)
 
+    def wait_bucket_params(self, b: Bucket):
+        """Make the current stream wait for the bucket's parameter all-gather (no-op when none is pending)."""
+        h = b.ag_handle
+        if h is not None:
+            if hasattr(h, "wait"):
+                h.wait()
+            b.ag_handle = None
+
+    def buckets_of(self, params) -> list:
+        seen, out = set(), []
+        for p in params:
+            b = self.param_to_bucket.get(p)
+            if b is not None and b.index not in seen:
+                seen.add(b.index)
+                out.append(b)
+        return out
+
     def finish_param_sync(self):
         for b in self.buckets:
-            if b.ag_handle is not None and hasattr(b.ag_handle, "wait"):
-                b.ag_handle.wait()
-            b.ag_handle = None
+            self.wait_bucket_params(b)
 
 
 class DistributedOptimizer:
@@ -232,6 +306,11 @@ class DistributedOptimizer:
         self.clip_grad = clip_grad
         self.norm_groups = [g for g in norm_groups if g is not None]
         self.check_for_nan = check_for_nan
+        # ``overlap_param_gather``: the bucket all-gathers after a step are issued asynchronously in forward order and
+        # the next forward pass waits per bucket, right before the first layer that reads it (the trainer installs
+        # those waits), as the reference overlaps its per-bucket parameter gather with the forward
+        # (primus/backends/megatron/patches/parallelism/sdma_param_all_gather_patches.py:49-130)
+        self.overlap_param_gather = False
         self.step_count = 0
         self.state = []
         dev = buffers[0].device
@@ -343,23 +422,17 @@ class DistributedOptimizer:
         from ..ops import _lib
         from ..ops.fused import scratch
 
+        # the reduce-scatter of every bucket has been issued by ``finish_grad_sync`` (or, overlapped, by the gradient
+        # hooks of the last micro-batch) and left this rank's reduced shards in place
         self.sumsq.zero_()
         self.skip.zero_()
-        P = _lib.call_ret("dp_num_partials")
-        for buf in self.buffers:
-            if buf.symmetric:
-                buf.sym_grad.barrier(0)  # every rank's gradients are final
         for st in self.state:
             buf = st["buf"]
             if not buf.symmetric:
                 optim_ops.sumsq_(buf.grad_data[st["s"]:st["e"]], self.sumsq, accumulate=True)
-                continue
-            tbl = (ctypes.c_long * buf.dp_size)(*[buf.sym_grad.peer_ptr(r) for r in range(buf.dp_size)])
-            n = st["e"] - st["s"]
-            _lib.call("dp_reduce_scatter", tbl, buf.dp_size, buf.dp_rank, st["s"], n, buf.grad_data[st["s"]:st["e"]],
-                      1.0 / buf.dp_size, scratch(buf.device, "dp_partials", P), self.sumsq, 1)
         for buf in self.buffers:
             if buf.symmetric:
+                self.sumsq.add_(buf.fused_sumsq)
                 buf.sym_grad.barrier(1)  # everybody has read this rank's gradients: they may be zeroed again
         self._discount_tp_duplicates()
         self._reduce_sumsq()
@@ -415,8 +488,9 @@ class DistributedOptimizer:
                 if out is None:
                     buf.param_data[lo:hi].copy_(st["master"][a:b_])
         for buf in self.buffers:
-            buf.start_param_sync(async_op=False)
-            buf.finish_param_sync()
+            buf.start_param_sync(async_op=self.overlap_param_gather)
+            if not self.overlap_param_gather:
+                buf.finish_param_sync()
         return self.grad_norm
 
     # ------------------------------------------------------------------ checkpoint

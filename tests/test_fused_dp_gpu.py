@@ -10,7 +10,7 @@ from tests.mp_utils import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, fused, outp):
+def _worker(rank, world, fused, outp, extra=None):
     from primus_b200.engine.trainer import TrainConfig, Trainer
     from primus_b200.models.config import TransformerConfig
     from primus_b200.ops import _lib
@@ -20,9 +20,10 @@ def _worker(rank, world, fused, outp):
     cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1408, num_attention_heads=4,
                             num_query_groups=2, kv_channels=128, vocab_size=8192, params_dtype="bf16")
     tc = TrainConfig(micro_batch_size=1, global_batch_size=4, seq_length=256, train_iters=4, lr=1e-3,
-                     lr_decay_style="constant", fused_dp_optimizer=fused, ddp_bucket_size=1_000_000)
+                     lr_decay_style="constant", fused_dp_optimizer=fused, ddp_bucket_size=1_000_000, **(extra or {}))
     tr = Trainer(cfg, tc, device=f"cuda:{rank}", log_fn=lambda s: None)
     losses = tr.train(4)
+    tr.finish_param_sync()
     torch.cuda.synchronize()
     _lib.check_status()
     checksum = float(sum(p.float().abs().sum() for p in tr.model.parameters()))
@@ -40,6 +41,27 @@ def test_fused_dp_optimizer_matches_nccl(tmp_path):
     for x, y in zip(ra["losses"], rb["losses"]):
         assert abs(x - y) <= 2e-3 * max(1.0, abs(x)), (ra, rb)
     assert abs(ra["checksum"] - rb["checksum"]) <= 1e-3 * ra["checksum"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_overlapped_variants_match_the_plain_nccl_path(tmp_path):
+    """Per-bucket overlap of the gradient reduction (NCCL and fused), bf16 on the wire, and the asynchronous parameter
+    all-gather with per-layer waits must not change the training trajectory."""
+    base = str(tmp_path / "base.json")
+    run_ranks(_worker, 2, "nccl", args=(False, base), timeout=240)
+    ref = json.load(open(base))
+    cases = {
+        "nccl_overlap": (False, dict(overlap_grad_reduce=True, overlap_param_gather=True), 1e-6),
+        "fused_overlap": (True, dict(overlap_grad_reduce=True), 2e-3),
+        "bf16_reduce": (False, dict(overlap_grad_reduce=True, grad_reduce_in_bf16=True), 2e-2),
+    }
+    for name, (fused, extra, tol) in cases.items():
+        outp = str(tmp_path / f"{name}.json")
+        run_ranks(_worker, 2, "nccl", args=(fused, outp, extra), timeout=240)
+        got = json.load(open(outp))
+        for x, y in zip(ref["losses"], got["losses"]):
+            assert abs(x - y) <= tol * max(1.0, abs(x)), (name, ref, got)
+        assert abs(ref["checksum"] - got["checksum"]) <= max(tol, 1e-3) * ref["checksum"], name
 
 
 def _fsdp_worker(rank, world, fsdp, outp):

@@ -225,7 +225,11 @@ def main() -> int:
     ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "allgather", "p2p", "a2a+p2p"],
                     help="context-parallel scheme: all-to-all over heads (Ulysses), K/V all-gather with zig-zag chunks, or ring (p2p)")
     ap.add_argument("--fused-tp", action="store_true", help="fused all-gather->GEMM / GEMM->reduce-scatter kernels")
-    ap.add_argument("--fused-dp", action="store_true", help="fused P2P reduce-scatter + AdamW + all-gather optimizer")
+    ap.add_argument("--fused-dp", dest="fused_dp", action="store_true", default=None,
+                    help="fused P2P reduce-scatter (overlapped with backward) + AdamW + all-gather by peer stores "
+                         "(default on more than one GPU)")
+    ap.add_argument("--no-fused-dp", dest="fused_dp", action="store_false",
+                    help="NCCL reduce-scatter / all-gather around the AdamW kernel instead")
     ap.add_argument("--no-overlap-param-gather", action="store_true",
                     help="NCCL path: wait for the parameter all-gather right after the optimizer step")
     ap.add_argument("--grad-reduce", default="bf16", choices=["bf16", "fp32"],
@@ -252,6 +256,8 @@ def main() -> int:
     from primus_b200.parallel import state as ps
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.fused_dp is None:
+        args.fused_dp = world > 1 and args.tp * args.cp < world
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"

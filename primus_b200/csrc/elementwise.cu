@@ -761,7 +761,7 @@ int pb_rmsnorm_bwd_num_partials(long rows) { return (int)(rows < 592 ? (rows < 1
 int pb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                    void* dx, float* dw, float* scratch, long rows, int H, long ldx, long lddy,
                    int dw_accumulate, cudaStream_t s) {
-  if (H % 8 || ldx % 8 || lddy % 8 || H > 16384) return -2;
+  if (H % 8 || ldx % 8 || lddy % 8 || H > 16384 || rows < 0 || rows > 2147483647L) return -2;   // 32-bit row indices
   if (rows == 0) return 0;
   const int P = pb_rmsnorm_bwd_num_partials(rows);
   launch_rmsnorm_bwd(P, H, s, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,
@@ -930,7 +930,8 @@ float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
 extern "C" int pb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
                                       const void* dres, void* dx, float* dw, long rows, int H, long ldx,
                                       long lddy, int dw_accumulate, cudaStream_t s) {
-  if (H <= 0 || H % 8 || ldx % 8 || lddy % 8 || rows < 0) return PB_NOALLOC_ERR_BAD_ARG;
+  // the kernels index rows with 32-bit integers: more than INT_MAX rows are rejected rather than truncated
+  if (H <= 0 || H % 8 || ldx % 8 || lddy % 8 || rows < 0 || rows > 2147483647L) return PB_NOALLOC_ERR_BAD_ARG;
   if (H > PB_NOALLOC_MAX_H) return PB_NOALLOC_ERR_TOO_LARGE;  // the built-in scratch holds rows of <= 8192 floats
   if (rows == 0) return 0;
   int dev = -1;

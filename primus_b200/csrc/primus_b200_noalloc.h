@@ -12,7 +12,8 @@
 // image instead of a buffer supplied by the caller.  Inputs and outputs are still caller-owned.
 //
 // Limits and rules
-//  * H (row width) <= PB_NOALLOC_MAX_H (8192), H % 8 == 0, row pitches % 8 == 0.  Any number of rows.
+//  * H (row width) <= PB_NOALLOC_MAX_H (8192), H % 8 == 0, row pitches % 8 == 0.  Up to 2^31 - 1 rows (more are
+//    rejected with PB_NOALLOC_ERR_BAD_ARG).
 //    Larger H is rejected with PB_NOALLOC_ERR_TOO_LARGE and nothing is launched.
 //  * The scratch is PB_NOALLOC_MAX_PARTIALS x PB_NOALLOC_MAX_H floats = 296 x 8192 x 4 B = 9.25 MiB.  It is
 //    part of the loaded library: every GPU on which the library is used holds that much memory until the

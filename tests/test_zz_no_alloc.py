@@ -37,7 +37,8 @@ def _reference(dy, x, w, rstd, dres):
     return dx, dw
 
 
-@pytest.mark.parametrize("rows,H,with_res", [(1000, 4096, True), (77, 512, False)])
+# (300, 8192): the documented maximum width, with more rows than the 296 partial rows of the built-in scratch
+@pytest.mark.parametrize("rows,H,with_res", [(1000, 4096, True), (77, 512, False), (300, 8192, True)])
 def test_noalloc_matches_regular_entry_point_twice(rows, H, with_res):
     lib = _lib.require()
     g = torch.Generator(device="cuda").manual_seed(rows + H)
@@ -57,7 +58,8 @@ def test_noalloc_matches_regular_entry_point_twice(rows, H, with_res):
         err_dx = (dx.float() - dx_ref.float()).abs().max().item()
         assert err_dx <= 2e-2 + 2e-2 * dx_ref.float().abs().max().item(), f"call {call}: dx err {err_dx}"
         err_dw = (dw - dw_ref).abs().max().item()
-        assert err_dw <= 0.3 + 2e-2 * dw_ref.abs().max().item(), f"call {call}: dw err {err_dw}"
+        # both entry points run the same kernels in the same order: a dropped or stale partial row would show
+        assert err_dw <= 1e-3 * dw_ref.abs().max().item() + 1e-5, f"call {call}: dw err {err_dw}"
         results.append((dx, dw))
     # accumulate mode adds onto the existing weight gradient
     dx2 = torch.empty_like(x)

@@ -242,7 +242,15 @@ def main() -> int:
     ap.add_argument("--ref-log", default=None, help="reference arm: copy rank 0's log of the reference run here")
     ap.add_argument("--mem-fraction", type=float, default=0.0,
                     help="cap this process's device memory (testing the out-of-memory fallback of the warm-up)")
-    ap.add_argument("--layers", type=int, default=0, help="profiling only: truncate the model (result is not a headline number)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="truncate the model to this many layers (stated in `config`; never for the headline number)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size")
+    ap.add_argument("--vpp", type=int, default=0, help="virtual pipeline stages per rank (interleaved schedule)")
+    ap.add_argument("--schedule", default=None, help="pipeline schedule: 1f1b | interleaved | zerobubble | zbv | v-half | v-min")
+    ap.add_argument("--ep", type=int, default=1, help="expert-parallel size (MoE models)")
+    ap.add_argument("--fused-ep", action="store_true", help="fused dispatch + GEMM / GEMM + combine kernels (use_turbo_mega_moe)")
+    ap.add_argument("--bf16-moments", action="store_true", help="Adam moments in bf16 (precision-aware optimizer)")
+    ap.add_argument("--recompute-layers", type=int, default=0, help="full recomputation of the first N layers of every stage")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -257,7 +265,7 @@ def main() -> int:
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.fused_dp is None:
-        args.fused_dp = world > 1 and args.tp * args.cp < world
+        args.fused_dp = world > 1 and args.tp * args.cp * args.pp < world and args.ep == 1 and not args.bf16_moments
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
@@ -267,25 +275,49 @@ def main() -> int:
     _lib.require()
     warmup = max(args.warmup, 3)
 
-    mdict = dict(MODELS[args.model])
+    par = dict(params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
+               sequence_parallel=args.tp > 1, fp8="e4m3" if args.precision == "mxfp8" else None,
+               fp8_recipe="mxfp8", context_parallel_size=args.cp, cp_comm_type=args.cp_comm,
+               hierarchical_context_parallel_sizes=[2, args.cp // 2] if args.cp_comm == "a2a+p2p" else None,
+               pipeline_model_parallel_size=args.pp, virtual_pipeline_model_parallel_size=args.vpp or None,
+               expert_model_parallel_size=args.ep)
+    if args.model in MODELS:
+        mdict = dict(MODELS[args.model])
+    else:       # any model preset of the package (primus_b200/configs/models/<name>.yaml)
+        import dataclasses
+
+        from primus_b200.core.config.presets import load_preset
+
+        names = {f.name for f in dataclasses.fields(TransformerConfig)}
+        mdict = {k: v for k, v in load_preset(args.model, "models").items() if k in names and k not in par}
+    full_layers = mdict["num_layers"]
     if args.layers:
         mdict["num_layers"] = args.layers
-    mcfg = TransformerConfig(**mdict, params_dtype="bf16", seq_length=args.seq, tensor_model_parallel_size=args.tp,
-                             sequence_parallel=args.tp > 1, fp8="e4m3" if args.precision == "mxfp8" else None,
-                             fp8_recipe="mxfp8", context_parallel_size=args.cp, cp_comm_type=args.cp_comm,
-                             hierarchical_context_parallel_sizes=[2, args.cp // 2] if args.cp_comm == "a2a+p2p" else None)
+        if isinstance(mdict.get("moe_layer_freq"), str) and mdict.get("num_experts"):
+            from primus_b200.models.config import parse_moe_layer_freq
+
+            mdict["moe_layer_freq"] = parse_moe_layer_freq(mdict["moe_layer_freq"], full_layers)[:args.layers]
+    if args.recompute_layers:
+        mdict.update(recompute_granularity="full", recompute_method="block", recompute_num_layers=args.recompute_layers)
+    if args.fused_ep:
+        mdict["use_turbo_mega_moe"] = True
+    mcfg = TransformerConfig(**mdict, **par)
     if args.fused_tp:
         from primus_b200.parallel import fused_tp
 
         fused_tp.ENABLED = True          # all-gather -> GEMM; the reduce-scatter side stays on NCCL (faster at tp = 8)
-    gbs = args.batch_per_gpu * world // (args.tp * args.cp)
+    gbs = args.batch_per_gpu * world // (args.tp * args.cp * args.pp)
+    schedule = args.schedule or ("interleaved" if args.vpp else "1f1b")
     tcfg = TrainConfig(micro_batch_size=args.micro_batch, global_batch_size=gbs, seq_length=args.seq,
                        train_iters=10 ** 6, lr=3e-4, lr_warmup_iters=100, lr_decay_iters=10 ** 6, weight_decay=0.1,
                        clip_grad=1.0, use_distributed_optimizer=True, overlap_grad_reduce=world > 1,
                        log_interval=10 ** 9, manual_gc=True, fused_dp_optimizer=args.fused_dp,
+                       pipeline_schedule=schedule, use_precision_aware_optimizer=args.bf16_moments,
+                       exp_avg_dtype="bf16" if args.bf16_moments else "fp32",
+                       exp_avg_sq_dtype="bf16" if args.bf16_moments else "fp32",
                        overlap_param_gather=world > 1 and not args.no_overlap_param_gather,
                        grad_reduce_in_bf16=world > 1 and args.grad_reduce == "bf16" and not args.fused_dp)
-    ps.initialize_model_parallel(tp=args.tp, pp=1, cp=args.cp)
+    ps.initialize_model_parallel(tp=args.tp, pp=args.pp, cp=args.cp, ep=args.ep, virtual_pp=args.vpp or None)
 
     def barrier():
         if world > 1:
@@ -373,14 +405,14 @@ def main() -> int:
             "vs_baseline": value / (BASELINE_TOK_S_GPU * world) if args.model == "llama3.1_8B" else None,
             "dtype": "bf16" if args.precision == "bf16" else "mxfp8 linear GEMMs (E4M3 + UE8M0 per 32, fp32 accumulate), bf16 attention / LM head / params, fp32 master",
             "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
-            "config": {"model": args.model + (f"[truncated to {args.layers} layers: profiling only]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
-                       "micro_batch": args.micro_batch, "parallelism": f"dp{world // (args.tp * args.cp)}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + (f"cp{args.cp}-{args.cp_comm}" if args.cp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
+            "config": {"model": args.model + (f"[truncated to {args.layers} of {full_layers} layers]" if args.layers else ""), "global_batch": gbs, "seq_len": args.seq,
+                       "micro_batch": args.micro_batch, "parallelism": f"dp{world // (args.tp * args.cp * args.pp)}" + (f"tp{args.tp}sp" if args.tp > 1 else "") + (f"pp{args.pp}" + (f"vpp{args.vpp}" if args.vpp else "") + f"-{schedule}" if args.pp > 1 else "") + (f"ep{args.ep}" + ("+fused_ep" if args.fused_ep else "") if args.ep > 1 or args.fused_ep else "") + (f"cp{args.cp}-{args.cp_comm}" if args.cp > 1 else "") + ("+fused_tp" if args.fused_tp else "") + ("+fused_dp" if args.fused_dp else ""),
                        "optimizer": "distributed AdamW, fp32 master + fp32 main grads, clip 1.0" + (
                            "" if world == 1 else (", fused P2P reduce-scatter overlapped with backward" if args.fused_dp else
                                                   f", NCCL reduce-scatter in {args.grad_reduce} overlapped with backward, "
                                                   + ("parameter all-gather overlapped with the next forward"
                                                      if not args.no_overlap_param_gather else "blocking parameter all-gather"))),
-                       "recompute": f"full recomputation of the first {recomputed} layers (out-of-memory fallback)" if recomputed else "none",
+                       "recompute": f"full recomputation of the first {recomputed} layers (out-of-memory fallback)" if recomputed else (f"full recomputation of the first {args.recompute_layers} layers of every stage" if args.recompute_layers else "none"),
                        "cache": "inputs_larger_than_L2 (per-step working set >> 126 MB)"},
             "tokens_per_s_per_gpu": value / world,
             "model_tflops_per_gpu": value / world * flops_tok / 1e12,

@@ -73,4 +73,11 @@ def main(argv: list[str] | None = None) -> int:
 
 
 if __name__ == "__main__":
+    if not __package__:
+        # started as a script (`torchrun primus_b200/cli/main.py ...`, the way the launcher starts the workers): run the
+        # module of the same name inside its package so that the relative imports resolve
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+        from primus_b200.cli.main import main as _package_main
+
+        sys.exit(_package_main())
     sys.exit(main())

@@ -84,3 +84,16 @@ def test_python_cli_help_and_dry_run(tmp_path):
     r = subprocess.run([sys.executable, "-m", "primus_b200.cli.main", "benchmark", "--nope"], capture_output=True,
                        text=True, env=env)
     assert r.returncode != 0
+
+
+def test_direct_mode_really_trains_on_cpu(tmp_path):
+    """Not a dry run: the launcher starts the worker script, which trains a tiny model for two iterations on the CPU
+    and leaves the completion line in the log file."""
+    log = tmp_path / "train.log"
+    r = run(["direct", "--single", "--log_file", str(log), "--", "train", "pretrain", "--config",
+             os.path.join(ROOT, "tests", "trainer_e2e.yaml")],
+            env={"CUDA_VISIBLE_DEVICES": "", "PRIMUS_WORKSPACE": str(tmp_path / "out"), "PRIMUS_NUM_LAYERS": "2",
+                 "PRIMUS_SEQ": "64", "PRIMUS_GBS": "2", "PRIMUS_TRAIN_ITERS": "2", "PRIMUS_OVERLAP": "false"})
+    text = log.read_text() if log.exists() else ""
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "Training completed." in text and text.count("lm loss:") == 2, text[-2000:]

@@ -50,7 +50,7 @@ def _p2p_shape(trainer, batch, seq):
     T = batch * seq
     if trainer.mcfg.sequence_parallel and st.tp > 1:
         T //= st.tp
-    return (2, T, trainer.mcfg.hidden_size)
+    return (T, trainer.mcfg.hidden_size)
 
 
 def _pos_ids(trainer, mb):
@@ -109,7 +109,7 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                     dist.recv(x, src=global_rank(pr), group=fwd_g)
                 x.requires_grad_(True)
                 inputs[k] = x
-                hidden_in = (x[0], x[1], batch, seq)
+                hidden_in = (x, None, batch, seq)
             if s == S - 1:
                 w = trainer._loss_weights(mb)
                 out = model(mb["tokens"], mb["labels"], loss_weights=w, hidden_in=hidden_in,
@@ -120,9 +120,9 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
             else:
                 h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in,
                                      position_ids=_pos_ids(trainer, mb), cu_seqlens=mb.get("host_cu_seqlens"))
-                if res is None:
-                    res = torch.zeros_like(h)
-                y = torch.stack([h, res])
+                # one tensor per stage boundary: the next stage's first layer only needs the residual stream
+                # hidden + residual (its fused add + norm starts from the sum), half the bytes of sending both
+                y = h if res is None else h + res
                 outputs[k] = y
                 nr, nc = sched.rank_of_stage(s + 1, pp, placement)
                 if nr == r:
@@ -197,7 +197,7 @@ def pipeline_warmup(trainer, micro_batch: dict) -> None:
             if s > 0:
                 x = torch.randn(_p2p_shape(trainer, batch, seq), device=dev).to(dtype) * 0.02
                 x.requires_grad_(True)
-                hidden_in = (x[0], x[1], batch, seq)
+                hidden_in = (x, None, batch, seq)
             if s == S - 1:
                 out = model(micro_batch["tokens"], micro_batch["labels"],
                             loss_weights=trainer._loss_weights(micro_batch), hidden_in=hidden_in, unit_upstream=True,
@@ -206,7 +206,7 @@ def pipeline_warmup(trainer, micro_batch: dict) -> None:
             else:
                 h, res, _, _ = model(micro_batch["tokens"] if s == 0 else None, hidden_in=hidden_in,
                                      position_ids=_pos_ids(trainer, micro_batch))
-                y = torch.stack([h, res if res is not None else torch.zeros_like(h)])
+                y = h if res is None else h + res
                 torch.autograd.backward(y, torch.randn_like(y) * 1e-3)
         gemm_ops.WGRAD_STORE.flush_all()
     finally:

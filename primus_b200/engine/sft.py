@@ -315,15 +315,31 @@ class SFTTrainer(PretrainTrainer):
                     pass
             ds = SFTDataset.from_jsonl(path, tok, eng.tcfg.seq_length, p.get("sft_dataset_format", "alpaca"),
                                        bool(p.get("sft_answer_only_loss", True)))
-            if p.get("sft_packing"):
+            if p.get("sft_lb_mini"):
+                # length-balanced dealing of every mini-batch over the data-parallel ranks, variable micro-batch counts
+                from .lb_mini import LBMiniStager
+
+                assert eng.st.pp == 1 and eng.st.cp == 1, "sft_lb_mini: data (and tensor) parallelism only"
+                reset = bool(p.get("reset_attention_mask", True))
+                eng.stager = LBMiniStager(ds, eng.tcfg.global_batch_size, eng.st.dp, eng.st.dp_rank, eng.device,
+                                          eng.tcfg.seq_length, align=128 if (reset and eng.is_cuda) else 1,
+                                          cost_model=p.get("sft_lb_mini_cost", "fit" if reset else "linear"),
+                                          same_num_in_dp=bool(p.get("sft_lb_mini_same_num_in_dp", False)),
+                                          boundaries=reset, log=eng.log if eng.st.rank == 0 else None)
+                eng.sampler = eng.stager.sampler
+                eng.use_position_ids = True
+                ds = None
+            elif p.get("sft_packing"):
                 # reset_attention_mask (default on): attention stays inside each packed sample; the GPU attention
                 # kernels need the samples aligned to their 128-token blocks
                 reset = bool(p.get("reset_attention_mask", True))
                 ds = PackedSFTDataset(ds, p.get("sft_packing_algorithm", "first_fit_decreasing"), eng.tcfg.seed,
                                       align=128 if (reset and eng.is_cuda) else 1, boundaries=reset)
-            eng.sampler = MicroBatchSampler(eng.tcfg.global_batch_size, eng.tcfg.micro_batch_size, eng.st.dp, eng.st.dp_rank)
-            eng.stager = BatchStager(ds, eng.sampler, eng.device)
-            eng.use_position_ids = True
+            if ds is not None:
+                eng.sampler = MicroBatchSampler(eng.tcfg.global_batch_size, eng.tcfg.micro_batch_size, eng.st.dp,
+                                                eng.st.dp_rank)
+                eng.stager = BatchStager(ds, eng.sampler, eng.device)
+                eng.use_position_ids = True
         if p.get("peft") == "lora":
             eng.lora = LoRAEngine(eng.model_chunks, int(p.get("lora_rank", 16)), float(p.get("lora_alpha", 32)),
                                   tuple(p.get("lora_target_modules") or ("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")),

@@ -409,6 +409,8 @@ class Trainer:
     # ------------------------------------------------------------------ one micro-batch
     def _loss_weights(self, batch: dict) -> torch.Tensor:
         mask = batch["loss_mask"]
+        if "_lb_mini_norm" in batch:     # variable micro-batch counts: normalise by the whole mini-batch's token count
+            return mask * batch["_lb_mini_norm"]
         if self.tcfg.calculate_per_token_loss:
             return mask / float(self.num_microbatches)  # normalised later by the global token count
         if "_mask_total" in batch:

@@ -58,6 +58,8 @@ class TrainConfig:
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     grad_reduce_in_bf16: bool = False    # bf16 on the wire for the data-parallel gradient reduction (fp32 accumulation)
+    enable_odc: bool = False             # on-demand communication: gradient pushes / parameter pulls, one meeting per step
+    odc_grad_spike_threshold: float = 1000.0
     ddp_bucket_size: Optional[int] = None
     seed: int = 1234
     data_seed: int = 1234
@@ -301,8 +303,9 @@ class Trainer:
                 dense, st.dp_cp_group if st.cp > 1 else st.dp_group, st.dp * st.cp, st.dp_rank * st.cp + st.cp_rank,
                 train_cfg.ddp_bucket_size, torch.float32, train_cfg.use_distributed_optimizer,
                 train_cfg.overlap_grad_reduce, True, self.comm_stream,
-                symmetric=train_cfg.fused_dp_optimizer and train_cfg.use_distributed_optimizer,
-                grad_reduce_in_bf16=train_cfg.grad_reduce_in_bf16))
+                symmetric=(train_cfg.fused_dp_optimizer or train_cfg.enable_odc) and train_cfg.use_distributed_optimizer,
+                grad_reduce_in_bf16=train_cfg.grad_reduce_in_bf16 and not train_cfg.enable_odc,
+                odc=train_cfg.enable_odc))
         if expert:
             self.buffers.append(ParamGradBuffer(
                 expert, st.edp_group, st.edp, st.edp_rank, train_cfg.ddp_bucket_size, torch.float32,
@@ -331,6 +334,8 @@ class Trainer:
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
             check_for_nan=train_cfg.check_for_nan_in_loss_and_grad, tp_size=st.tp,
             expert_norm_group=st.ep_group if (st.ep > 1 and not train_cfg.use_distributed_optimizer) else None)
+        if train_cfg.enable_odc:
+            self.optimizer.grad_spike_threshold = float(train_cfg.odc_grad_spike_threshold or 0.0)
         self._install_param_gather_waits()
 
     # ------------------------------------------------------------------ overlap_param_gather

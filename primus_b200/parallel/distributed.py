@@ -46,7 +46,7 @@ class ParamGradBuffer:
     def __init__(self, params: list[torch.nn.Parameter], dp_group, dp_size: int, dp_rank: int,
                  bucket_size: Optional[int] = None, grad_dtype=torch.float32, use_distributed_optimizer=True,
                  overlap_grad_reduce=False, average_in_collective=True, comm_stream=None, symmetric=False,
-                 extra_grad_scale: float = 1.0, grad_reduce_in_bf16: bool = False):
+                 extra_grad_scale: float = 1.0, grad_reduce_in_bf16: bool = False, odc: bool = False):
         """``extra_grad_scale`` multiplies the gradients before the collective.  Expert parameters need it: every
         expert-parallel rank accumulates the contributions of the tokens of all ``ep`` ranks, each normalised for its
         own rank's micro-batches, and the buffer is then only averaged over the (smaller) expert-data-parallel group,
@@ -102,6 +102,12 @@ class ParamGradBuffer:
         else:
             self.param_data = torch.zeros(self.numel, dtype=self.param_dtype, device=device)
             self.grad_data = torch.zeros(self.numel, dtype=self.grad_dtype, device=device)
+        # on-demand communication: gradients are pushed into the owners' accumulators, parameters pulled (parallel/odc.py)
+        self.odc = None
+        if odc and dp_size > 1 and use_distributed_optimizer and (self.symmetric or device.type == "cpu"):
+            from .odc import ODCReducer
+
+            self.odc = ODCReducer(self)
         self.param_offsets = offsets
         self.param_to_bucket = {}
         for b in buckets:
@@ -175,7 +181,25 @@ class ParamGradBuffer:
                 b.rs_event = torch.cuda.Event()
                 b.rs_event.record(stream)
 
+    def _start_bucket_sync_odc(self, b: Bucket, async_op: bool):
+        stream = self.comm_stream if (async_op and self.comm_stream is not None) else None
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                if self.extra_grad_scale != 1.0:
+                    self.grad_data[b.start:b.end].mul_(self.extra_grad_scale)
+                self.odc.push_bucket(b)
+                b.rs_event = torch.cuda.Event()
+                b.rs_event.record(stream)
+        else:
+            if self.extra_grad_scale != 1.0:
+                self.grad_data[b.start:b.end].mul_(self.extra_grad_scale)
+            self.odc.push_bucket(b)
+        b.rs_handle = True
+
     def _start_bucket_sync(self, b: Bucket, async_op: bool):
+        if self.odc is not None:
+            return self._start_bucket_sync_odc(b, async_op)
         if self.symmetric:
             return self._start_bucket_sync_fused(b, async_op)
         g = self.grad_data[b.start:b.end]
@@ -243,11 +267,15 @@ class ParamGradBuffer:
                 b.rs_handle.wait()
             if b.rs_event is not None:
                 torch.cuda.current_stream().wait_event(b.rs_event)
+        if self.odc is not None:
+            self.odc.finish()
 
     # ------------------------------------------------------------------ param sync
     def start_param_sync(self, async_op=False):
         if self.dp_size == 1 or not self.use_distributed_optimizer:
             return
+        if self.odc is not None:
+            return self.odc.gather_params()
         for b in reversed(self.buckets):  # forward order: the embedding-side buckets are needed first
             s, e = self.shard_range(b)
             full = self.param_data[b.start:b.end]
@@ -311,6 +339,7 @@ class DistributedOptimizer:
         # those waits), as the reference overlaps its per-bucket parameter gather with the forward
         # (primus/backends/megatron/patches/parallelism/sdma_param_all_gather_patches.py:49-130)
         self.overlap_param_gather = False
+        self.grad_spike_threshold = 0.0      # ``odc_grad_spike_threshold``: skip the step when the norm exceeds it
         self.step_count = 0
         self.state = []
         dev = buffers[0].device
@@ -408,6 +437,10 @@ class DistributedOptimizer:
         self._reduce_sumsq()
         if self.check_for_nan:
             self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
+        if self.grad_spike_threshold and self.grad_spike_threshold > 0:
+            # a gradient-norm spike is treated like a non-finite step: nothing is updated (device-side, no host sync)
+            spike = (self.sumsq > float(self.grad_spike_threshold) ** 2).to(torch.int32)
+            self.skip.copy_(torch.maximum(self.skip, spike))
         optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
         return self.grad_norm
 
@@ -473,7 +506,7 @@ class DistributedOptimizer:
         from ..ops import gemm as _gemm
 
         _gemm.bump_weight_generation()   # parameters change in place below: quantised copies expire
-        if any(buf.symmetric for buf in self.buffers):
+        if any(buf.symmetric and buf.odc is None for buf in self.buffers):
             return self._fused_step(lr, wd)
         self.compute_grad_norm()
         for st in self.state:

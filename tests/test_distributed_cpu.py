@@ -37,6 +37,7 @@ CASES = {
     "dp2": dict(world=2, kw=dict()),
     "dp2_fsdp2": dict(world=2, kw=dict(fsdp=True)),
     "dp2_bf16_grad_reduce": dict(world=2, kw=dict(extra_tc=dict(grad_reduce_in_bf16=True, overlap_grad_reduce=True))),
+    "dp2_odc": dict(world=2, kw=dict(extra_tc=dict(enable_odc=True, overlap_grad_reduce=True))),
     "dp2_overlap_param_gather": dict(world=2, kw=dict(extra_tc=dict(overlap_param_gather=True, overlap_grad_reduce=True))),
     "dp2_pp2_overlap_param_gather": dict(world=4, kw=dict(pp=2, extra_tc=dict(overlap_param_gather=True))),
     "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),

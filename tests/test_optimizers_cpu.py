@@ -305,3 +305,32 @@ def test_llama3_rope_scaling_and_a_llama4_style_model():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < losses[0] - 0.3
+
+
+def test_grad_spike_threshold_skips_the_step():
+    """``odc_grad_spike_threshold``: a step whose global gradient norm exceeds the threshold updates nothing."""
+    import torch
+
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.parallel import state as ps
+
+    def run(threshold):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc = TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+                               vocab_size=256, params_dtype="fp32", make_vocab_size_divisible_by=64)
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=1, lr=1e-2,
+                         lr_decay_style="constant", clip_grad=0.0)
+        torch.manual_seed(0)
+        tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+        tr.optimizer.grad_spike_threshold = threshold
+        before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+        tr.train(1)
+        moved = any(not torch.equal(p, before[n]) for n, p in tr.model.named_parameters())
+        return moved, float(tr.optimizer.grad_norm)
+
+    moved, norm = run(0.0)
+    assert moved and norm > 0
+    assert run(norm * 0.5)[0] is False          # the norm is above the threshold: step skipped
+    assert run(norm * 2.0)[0] is True

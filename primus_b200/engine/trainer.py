@@ -58,6 +58,9 @@ class TrainConfig:
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     grad_reduce_in_bf16: bool = False    # bf16 on the wire for the data-parallel gradient reduction (fp32 accumulation)
+    num_seq_splits: int = 1              # sequence chunks per micro-batch inside a pipeline (only 1 is built)
+    enable_optimizer_post_validation: bool = False        # pipeline parallel: update first, validate the global norm later
+    enable_exact_optimizer_post_validation: bool = True   # restore from a snapshot (exact) instead of inverting the update
     enable_odc: bool = False             # on-demand communication: gradient pushes / parameter pulls, one meeting per step
     odc_grad_spike_threshold: float = 1000.0
     ddp_bucket_size: Optional[int] = None
@@ -192,6 +195,11 @@ class Trainer:
                  log_fn: Callable[[str], None] = print):
         self.mcfg, self.tcfg = model_cfg, train_cfg
         self.log = log_fn
+        if int(train_cfg.num_seq_splits or 1) != 1:
+            raise NotImplementedError(
+                "num_seq_splits > 1 (sequence chunks that travel through the pipeline separately, with attention over the "
+                "earlier chunks' keys and values and reversed chunk order in the backward pass) is not built; use context "
+                "parallelism or a larger pipeline_model_parallel_size to cut activation memory")
         st = ps.get_state()
         if not st.initialized:
             st = ps.initialize_model_parallel(
@@ -334,6 +342,9 @@ class Trainer:
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
             check_for_nan=train_cfg.check_for_nan_in_loss_and_grad, tp_size=st.tp,
             expert_norm_group=st.ep_group if (st.ep > 1 and not train_cfg.use_distributed_optimizer) else None)
+        if train_cfg.enable_optimizer_post_validation:
+            self.optimizer.post_validation = True
+            self.optimizer.post_validation_exact = bool(train_cfg.enable_exact_optimizer_post_validation)
         if train_cfg.enable_odc:
             self.optimizer.grad_spike_threshold = float(train_cfg.odc_grad_spike_threshold or 0.0)
         self._install_param_gather_waits()

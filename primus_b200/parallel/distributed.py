@@ -340,6 +340,10 @@ class DistributedOptimizer:
         # (primus/backends/megatron/patches/parallelism/sdma_param_all_gather_patches.py:49-130)
         self.overlap_param_gather = False
         self.grad_spike_threshold = 0.0      # ``odc_grad_spike_threshold``: skip the step when the norm exceeds it
+        # ``enable_optimizer_post_validation``: update first, validate later (see ``_post_validated_step``)
+        self.post_validation = False
+        self.post_validation_exact = True
+        self.post_validation_redos = 0
         self.step_count = 0
         self.state = []
         dev = buffers[0].device
@@ -508,7 +512,17 @@ class DistributedOptimizer:
         _gemm.bump_weight_generation()   # parameters change in place below: quantised copies expire
         if any(buf.symmetric and buf.odc is None for buf in self.buffers):
             return self._fused_step(lr, wd)
+        if self.post_validation and self.norm_groups:
+            return self._post_validated_step(lr, wd)
         self.compute_grad_norm()
+        self._apply_adamw(lr, wd)
+        for buf in self.buffers:
+            buf.start_param_sync(async_op=self.overlap_param_gather)
+            if not self.overlap_param_gather:
+                buf.finish_param_sync()
+        return self.grad_norm
+
+    def _apply_adamw(self, lr: float, wd: float):
         for st in self.state:
             buf = st["buf"]
             for lo, hi, mult in st["wd_ranges"]:
@@ -520,11 +534,72 @@ class DistributedOptimizer:
                                       skip=self.skip)
                 if out is None:
                     buf.param_data[lo:hi].copy_(st["master"][a:b_])
+
+    def _post_validated_step(self, lr: float, wd: float):
+        """Optimizer step for pipeline schedules whose stages finish at different times (zero-bubble family).
+
+        The global gradient norm and the non-finite check need a reduction over the tensor x pipeline ranks, in which
+        early stages would sit idle until the last stage has finished its backward passes.  Here every rank updates
+        right away with its *local* information (no clipping, no skip), starts the reduction asynchronously, and
+        validates when it arrives: if the step had to be clipped or skipped after all, the state is restored and the
+        update is redone with the global coefficient.  ``post_validation_exact``: restore from a snapshot of the shards
+        (bit-identical to the plain step, costs a copy of the optimizer state while the reduction is in flight);
+        otherwise the update is inverted algebraically (no extra memory, the restored values differ in the last bits).
+        Role of the reference's post-validation optimizer for its zero-bubble schedules
+        (primus/backends/megatron/core/optimizer/zbpp_optimizer.py:120-246; keys ``enable_optimizer_post_validation``,
+        ``enable_exactly_numeric_match`` of primus/configs/modules/megatron/zero_bubble.yaml)."""
+        self.sumsq.zero_()
+        self.skip.zero_()
+        for st in self.state:
+            optim_ops.sumsq_(st["buf"].grad_data[st["s"]:st["e"]], self.sumsq, accumulate=True)
+        self._discount_tp_duplicates()
+        if self.buffers[0].dp_size > 1 and self.buffers[0].use_distributed_optimizer:
+            dist.all_reduce(self.sumsq, group=self.buffers[0].dp_group)
+        handles = [dist.all_reduce(self.sumsq, group=g, async_op=True) for g in self.norm_groups[:1]]
+        snap = [(st["master"].clone(), st["m"].clone(), st["v"].clone()) for st in self.state] \
+            if self.post_validation_exact else None
+        self.coef.fill_(1.0)
+        self._apply_adamw(lr, wd)                      # optimistic: as if the norm were below the clip threshold
+        for h in handles:
+            h.wait()
+        for g in self.norm_groups[1:]:
+            dist.all_reduce(self.sumsq, group=g)
+        if self.check_for_nan:
+            self.skip.copy_((~torch.isfinite(self.sumsq)).to(torch.int32))
+        if self.grad_spike_threshold and self.grad_spike_threshold > 0:
+            self.skip.copy_(torch.maximum(self.skip, (self.sumsq > float(self.grad_spike_threshold) ** 2).to(torch.int32)))
+        optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
+        redo = bool(self.skip.item()) or float(self.coef.item()) < 1.0      # the validation: one scalar read
+        if redo:
+            self.post_validation_redos += 1
+            if snap is not None:
+                for st, (ma, m, v) in zip(self.state, snap):
+                    st["master"].copy_(ma)
+                    st["m"].copy_(m)
+                    st["v"].copy_(v)
+            else:
+                self._invert_adamw(lr, wd)
+            self._apply_adamw(lr, wd)                  # the kernels read the global coefficient / skip flag now
         for buf in self.buffers:
             buf.start_param_sync(async_op=self.overlap_param_gather)
             if not self.overlap_param_gather:
                 buf.finish_param_sync()
         return self.grad_norm
+
+    def _invert_adamw(self, lr: float, wd: float):
+        """Undo one un-clipped AdamW update of ``_apply_adamw`` from the gradients that produced it."""
+        b1, b2 = self.betas
+        bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
+        for st in self.state:
+            buf = st["buf"]
+            for lo, hi, mult in st["wd_ranges"]:
+                a, b_ = lo - st["s"], hi - st["s"]
+                g = buf.grad_data[lo:hi].float()
+                m, v, p = st["m"][a:b_].float(), st["v"][a:b_].float(), st["master"][a:b_]
+                upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
+                p.add_(upd, alpha=lr).div_(1.0 - lr * wd * mult)
+                st["m"][a:b_].copy_((m - (1 - b1) * g) / b1)
+                st["v"][a:b_].copy_(((v - (1 - b2) * g * g) / b2).clamp_(min=0.0))
 
     # ------------------------------------------------------------------ checkpoint
     def state_dict(self):

@@ -47,6 +47,13 @@ CASES = {
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
+    # optimistic optimizer step validated after the cross-stage norm reduction; clip 1e-3 forces the redo path
+    "pp2_zerobubble_post_validation": dict(world=2, kw=dict(pp=2, schedule="zerobubble",
+                                                            extra_tc=dict(enable_optimizer_post_validation=True))),
+    "pp2_zerobubble_post_validation_redo": dict(world=2, kw=dict(pp=2, schedule="zerobubble", clip=1e-3,
+                                                                 extra_tc=dict(enable_optimizer_post_validation=True))),
+    "pp2_post_validation_inverse": dict(world=2, kw=dict(pp=2, schedule="zerobubble", clip=1e-3, extra_tc=dict(
+        enable_optimizer_post_validation=True, enable_exact_optimizer_post_validation=False))),
     "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
     "cp2": dict(world=2, kw=dict(cp=2)),

@@ -751,18 +751,20 @@ class Trainer:
 
     @torch.no_grad()
     def evaluate(self, iters: int) -> float:
-        """Mean validation loss over ``iters`` global batches (forward only; no pipeline parallelism).  Logs the
-        ``validation loss at iteration`` line of the reference's evaluator
+        """Mean validation loss over ``iters`` global batches (forward only; under pipeline parallelism the forward
+        nodes of the training schedule).  Logs the ``validation loss at iteration`` line of the reference's evaluator
         (primus/backends/megatron/training/evaluator.py:23-208)."""
-        if self.st.pp > 1:
-            self.log("evaluation skipped: forward-only pipeline schedule is not available")
-            return float("nan")
         stager = self._eval_stager()
         total = torch.zeros(1, dtype=torch.float32, device=self.device)
         for _ in range(iters):
             mbs = stager.next_step()
             if self.st.cp > 1:
                 mbs = [self._cp_shard(mb) for mb in mbs]
+            if self.st.pp > 1:
+                from ..parallel.pipeline import run_pipeline_schedule
+
+                total += run_pipeline_schedule(self, mbs, forward_only=True).detach().float()
+                continue
             for mb in mbs:
                 w = self._loss_weights(mb)
                 pos = mb.get("position_ids") if (getattr(self, "use_position_ids", False) or self.st.cp > 1) else None

@@ -58,7 +58,11 @@ def _pos_ids(trainer, mb):
     return mb.get("position_ids") if use else None
 
 
-def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: PipelineTimeline | None = None):
+def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: PipelineTimeline | None = None,
+                          forward_only: bool = False):
+    """Executes this rank's row of the schedule table.  ``forward_only`` (evaluation): only the forward nodes run, in
+    table order — they depend on forward nodes alone, so the sub-sequence is a valid forward schedule on every rank —
+    nothing is kept for a backward pass, and the summed loss is valid on the last stage."""
     st = trainer.st
     pp, r = st.pp, st.pp_rank
     m = len(micro_batches)
@@ -91,6 +95,8 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
         return st.pp_ranks[pp_rank]
 
     for node in nodes:
+        if forward_only and node.kind != "F":
+            continue
         t0 = time.perf_counter() if timeline is not None else 0.0
         s = sched.stage_of(r, node.chunk, pp, placement)
         mb = micro_batches[node.mb]
@@ -107,15 +113,17 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 else:
                     x = torch.empty(_p2p_shape(trainer, batch, seq), dtype=dtype, device=dev)
                     dist.recv(x, src=global_rank(pr), group=fwd_g)
-                x.requires_grad_(True)
-                inputs[k] = x
+                if not forward_only:
+                    x.requires_grad_(True)
+                    inputs[k] = x
                 hidden_in = (x, None, batch, seq)
             if s == S - 1:
                 w = trainer._loss_weights(mb)
                 out = model(mb["tokens"], mb["labels"], loss_weights=w, hidden_in=hidden_in,
                             unit_upstream=True, position_ids=_pos_ids(trainer, mb),
                             cu_seqlens=mb.get("host_cu_seqlens"))
-                outputs[k] = out
+                if not forward_only:
+                    outputs[k] = out
                 total += out.detach()
             else:
                 h, res, _, _ = model(mb["tokens"] if s == 0 else None, hidden_in=hidden_in,
@@ -123,7 +131,8 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 # one tensor per stage boundary: the next stage's first layer only needs the residual stream
                 # hidden + residual (its fused add + norm starts from the sum), half the bytes of sending both
                 y = h if res is None else h + res
-                outputs[k] = y
+                if not forward_only:
+                    outputs[k] = y
                 nr, nc = sched.rank_of_stage(s + 1, pp, placement)
                 if nr == r:
                     local_act[(node.mb, node.chunk)] = y.detach().clone()

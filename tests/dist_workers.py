@@ -91,6 +91,11 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
     load_from_full(tr, full_sd)
     norms = []
     losses = tr.train(on_step=lambda t, lv: norms.append(float(t.optimizer.grad_norm.item())))
+    if kwargs.get("extra_tc", {}) and kwargs["extra_tc"].get("eval_iters"):
+        val = tr.evaluate(kwargs["extra_tc"]["eval_iters"])
+        if rank == 0:
+            with open(outq_path + ".eval", "w") as f:
+                json.dump(val, f)
     if rank == 0:
         with open(outq_path, "w") as f:
             json.dump(losses, f)

@@ -68,6 +68,29 @@ def test_flash_attn_backward(case):
         assert err <= tol, f"{name}: err {err} tol {tol}"
 
 
+def test_flash_attn_fwd_bwd_at_the_benchmark_length():
+    """seq 8192 (64 key blocks, many waves of streamed tiles per CTA), one GQA group of the Llama-3.1-8B shape
+    (4 query heads on 1 KV head, d 128), forward and backward against the fp32 reference."""
+    batch, seq, hq, hkv, d = 1, 8192, 4, 1, 128
+    q, k, v = _inputs(batch, seq, hq, hkv, d, d, seed=7)
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    o = A.flash_attention(q, k, v, batch, True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    o_ref, _ = A.attention_ref(qr, kr, vr, batch, True)
+    o_ref.backward(do.float())
+    assert (o.float() - o_ref.float()).abs().max().item() <= 2e-2
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        tol = 3e-2 * b.abs().max().item() + 2e-2
+        assert err <= tol, f"{name}: err {err} tol {tol}"
+        rel = (a.float() - b).norm().item() / b.norm().item()
+        assert rel <= 1e-2, f"{name}: relative error {rel}"
+
+
 def test_flash_attn_deterministic():
     q, k, v = _inputs(1, 1024, 8, 2, 128, 128, seed=3)
     o1, l1 = A.flash_attn_fwd(q, k, v, 1, True, 0.088)

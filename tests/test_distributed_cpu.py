@@ -111,3 +111,25 @@ def test_grad_norm_matches_single_process(name, tmp_path):
     assert len(got) == len(ref_norms) and all(n > 0 for n in ref_norms)
     for a, b in zip(got, ref_norms):
         assert abs(a - b) <= 2e-3 * b, f"{name}: grad norms {got} vs {ref_norms}"
+
+
+def test_evaluation_under_pipeline_parallelism(tmp_path):
+    """The forward-only pipeline pass gives the validation loss of the single-process model."""
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+
+    kw = dict(seq=32, gbs=8, mbs=2, iters=2, layers=4, extra_tc=dict(eval_iters=2))
+    ref, mck = _single(kw)
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(**kw)
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    W.load_from_full(tr, W.full_reference_state(mck))
+    tr.train()
+    want = tr.evaluate(2)
+    ps.destroy_model_parallel()
+    for name, extra in (("pp2", dict(pp=2)), ("pp2i", dict(pp=2, vpp=2, schedule="interleaved"))):
+        out = tmp_path / f"{name}.json"
+        run_ranks(W.train_worker, 2, "gloo", args=({**kw, **extra}, mck, str(out)), timeout=240)
+        got = json.loads((tmp_path / f"{name}.json.eval").read_text())
+        assert abs(got - want) <= 2e-3 * max(1.0, abs(want)), (name, got, want)

@@ -24,7 +24,10 @@ def register_subcommand(subparsers):
     p.add_argument("--schedule", default=None)
     p.add_argument("--sync-free-stage", type=int, default=0, help="MoE sync-free stage (0-3): removes host syncs")
     p.add_argument("--comm-overlap", type=float, default=None, help="fraction of layer comm hidden (fused kernels)")
-    p.add_argument("--benchmark", action="store_true")
+    p.add_argument("--benchmark", action="store_true",
+                   help="time one real dense (and MoE) layer on the local GPU and use that instead of the kernel table")
+    p.add_argument("--precision", default=None, choices=["bf16", "mxfp8", "tensorwise"],
+                   help="kernel table to use (default: the configuration's fp8 recipe, else bf16)")
     p.add_argument("--json", action="store_true")
     p.set_defaults(func=run)
 
@@ -92,6 +95,9 @@ def benchmark_layers(cfg, plan):
     if not torch.cuda.is_available():
         raise RuntimeError("--benchmark needs a GPU")
     ps.initialize_model_parallel()
+    from ...ops import gemm as _gemm
+
+    _gemm.set_fp8_recipe(cfg.fp8_recipe if cfg.fp8 else None)   # time the layer in the precision it trains in
     out = {}
     T = plan.micro_batch * plan.seq
     for key, idx in (("dense", next((i for i in range(cfg.num_layers) if not cfg.is_moe_layer(i)), None)),
@@ -139,7 +145,8 @@ def run(args, overrides):
         res["memory"] = mem
     if args.suite in ("performance", "both"):
         lt = benchmark_layers(cfg, plan) if args.benchmark else None
-        res["performance"] = project_performance(cfg, plan, hw, sched, args.target_nodes, overlap, lt)
+        res["performance"] = project_performance(cfg, plan, hw, sched, args.target_nodes, overlap, lt,
+                                                 precision=getattr(args, "precision", None))
     if args.json:
         print(json.dumps(res, indent=1, default=str))
     else:
@@ -156,5 +163,6 @@ def run(args, overrides):
             print(f"perf    : {p['iteration_ms']:.1f} ms/iter | {p['tokens_per_s_per_gpu']:.0f} tokens/s/GPU | "
                   f"{p['tflops_per_gpu']:.0f} TFLOP/s/GPU | MFU {100 * p['mfu']:.1f}% | schedule {p['schedule']} "
                   f"bubble {100 * p['bubble_fraction']:.1f}%")
-            print("          " + " | ".join(f"{k} {v:.2f} ms" for k, v in p["breakdown_ms"].items()))
+            print("          " + " | ".join(f"{k} {v:.2f} ms" if isinstance(v, float) else f"{k} {v}"
+                                                 for k, v in p["breakdown_ms"].items()))
     return 0

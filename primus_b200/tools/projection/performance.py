@@ -18,12 +18,27 @@ from ...parallel import pipeline_schedules as pps
 from .collective_model import CollectiveModel, Hardware
 from .memory import ParallelPlan, param_counts
 
-# measured fractions of the bf16 burst peak reached by this framework's kernels on B200 (profiles/)
-GEMM_EFF = 0.86
-GEMM_WGRAD_EFF = 0.72
-ATTN_FWD_EFF = 0.57
-ATTN_BWD_EFF = 0.29
-ELEMENTWISE_BW_EFF = 0.75
+# Throughputs of this package's kernels on B200 *inside a training step* (sustained, power-capped, operands from
+# DRAM), as fractions of the measured bf16 burst peak of the hardware profile (1649 TFLOP/s) resp. of the measured
+# copy bandwidth (6551 GB/s).  Sources: profiles/gemm_mxfp8_8192x4096x4096.md (sustained, rotating operands),
+# profiles/gemm_bf16_8192x4096x4096.md, the per-kernel times of a profiled Llama-3.1-8B step
+# (attention 0.575 ms forward / 2.65 ms backward per layer and micro-batch at seq 8192; SwiGLU, norm and quantisation
+# kernels at roughly half their isolated speed because the SM clock is capped to ~1.6 GHz by the GEMMs around them).
+KERNEL_EFF = {
+    "bf16": dict(gemm_fprop=0.76, gemm_dgrad=0.76, gemm_wgrad=0.64, attn_fwd=0.63, attn_bwd=0.342, elementwise_bw=0.466,
+                 quant_passes=0.0),
+    # MXFP8 linears inside a step: 2.3 PFLOP/s fprop / dgrad, 2.0 wgrad + fp32 accumulate; attention and the LM head
+    # stay bf16; every linear input is quantised in a separate pass (bf16 read, two fp8 copies written)
+    "mxfp8": dict(gemm_fprop=1.41, gemm_dgrad=1.41, gemm_wgrad=1.21, attn_fwd=0.63, attn_bwd=0.342, elementwise_bw=0.466,
+                  quant_passes=1.0),
+}
+KERNEL_EFF["tensorwise"] = dict(KERNEL_EFF["mxfp8"], quant_passes=1.5)   # + one maximum reduction per quantised tensor
+# the LM head (one very large bf16 GEMM per pass: 1.49 / 1.43 / 1.34 PFLOP/s inside a step)
+GEMM_EFF, GEMM_DGRAD_EFF, GEMM_WGRAD_EFF = 0.90, 0.87, 0.81
+ELEMENTWISE_BW_EFF = KERNEL_EFF["bf16"]["elementwise_bw"]
+# whole step over the sum of its kernels (launch gaps, allocator, small optimizer-side kernels): the fit above already
+# reproduces the measured Llama-3.1-8B step (5514 ms MXFP8, 7486 ms bf16 on one GPU), so no further factor
+STEP_OVERHEAD = 1.0
 
 
 @dataclass
@@ -39,7 +54,9 @@ class LayerTime:
         return self.fwd + self.bwd_input + self.bwd_weight + self.comm_fwd + self.comm_bwd
 
 
-def layer_time(cfg, plan: ParallelPlan, hw: Hardware, moe: bool, coll: CollectiveModel, comm_overlap: float = 0.0) -> LayerTime:
+def layer_time(cfg, plan: ParallelPlan, hw: Hardware, moe: bool, coll: CollectiveModel, comm_overlap: float = 0.0,
+               precision: str = "bf16") -> LayerTime:
+    eff = KERNEL_EFF[precision]
     T = plan.micro_batch * plan.seq / plan.cp
     h = cfg.hidden_size
     peak = hw.bf16_tflops * 1e12
@@ -65,10 +82,15 @@ def layer_time(cfg, plan: ParallelPlan, hw: Hardware, moe: bool, coll: Collectiv
     # memory-bound part: norms, rope, swiglu, residuals ~ 14 passes over T x h plus 6 over T x ffn
     ffn_w = (cfg.moe_ffn_hidden_size * cfg.moe_router_topk) if moe else cfg.ffn_hidden_size / plan.tp
     ew_bytes = (14 * T * h / (plan.tp if plan.sequence_parallel else 1) + 6 * T * ffn_w) * 2.0
-    ew = ew_bytes / (hw.hbm_gbs * 1e9 * ELEMENTWISE_BW_EFF)
-    fwd = gemm_fl / (peak * GEMM_EFF) + attn_fl / (peak * ATTN_FWD_EFF) + ew
-    bwd_in = gemm_fl / (peak * GEMM_EFF) + 2.5 * attn_fl / (peak * ATTN_BWD_EFF) + 1.5 * ew
-    bwd_w = gemm_fl / (peak * GEMM_WGRAD_EFF)
+    # quantisation passes of the fp8 recipes: forward x (QKV, FC1 inputs) and the attention output, backward the
+    # three incoming gradients of width h and the FC1 gradient; 4 bytes per element moved (bf16 in, two fp8 out)
+    q_fwd = eff["quant_passes"] * (3 * T * h + 0 * ffn_w) * 4.0
+    q_bwd = eff["quant_passes"] * (3 * T * h + cfg.qkv_width / plan.tp * T) * 4.0
+    bw = hw.hbm_gbs * 1e9 * eff["elementwise_bw"]
+    ew = ew_bytes / bw
+    fwd = gemm_fl / (peak * eff["gemm_fprop"]) + attn_fl / (peak * eff["attn_fwd"]) + ew + q_fwd / bw
+    bwd_in = gemm_fl / (peak * eff["gemm_dgrad"]) + 2.5 * attn_fl / (peak * eff["attn_bwd"]) + 1.5 * ew + q_bwd / bw
+    bwd_w = gemm_fl / (peak * eff["gemm_wgrad"])
     cf = cb = 0.0
     if plan.tp > 1:
         act = T * h * 2.0
@@ -89,13 +111,16 @@ def layer_time(cfg, plan: ParallelPlan, hw: Hardware, moe: bool, coll: Collectiv
 
 
 def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "1f1b", target_nodes: int | None = None,
-                        comm_overlap: float = 0.0, layer_times: dict | None = None) -> dict:
-    """Returns iteration time, tokens/s/GPU, TFLOP/s/GPU, MFU and the component breakdown."""
+                        comm_overlap: float = 0.0, layer_times: dict | None = None, precision: str | None = None) -> dict:
+    """Returns iteration time, tokens/s/GPU, TFLOP/s/GPU, MFU and the component breakdown.  ``precision``: ``bf16`` |
+    ``mxfp8`` | ``tensorwise`` (default: the model configuration's fp8 recipe)."""
+    if precision is None:
+        precision = (cfg.fp8_recipe if cfg.fp8_recipe in KERNEL_EFF else "mxfp8") if getattr(cfg, "fp8", None) else "bf16"
     world = plan.world if target_nodes is None else target_nodes * hw.gpus_per_node
     plan = ParallelPlan(**{**plan.__dict__, "world": world})
     coll = CollectiveModel(hw)
-    lt_dense = layer_time(cfg, plan, hw, False, coll, comm_overlap)
-    lt_moe = layer_time(cfg, plan, hw, True, coll, comm_overlap) if cfg.num_experts else lt_dense
+    lt_dense = layer_time(cfg, plan, hw, False, coll, comm_overlap, precision)
+    lt_moe = layer_time(cfg, plan, hw, True, coll, comm_overlap, precision) if cfg.num_experts else lt_dense
     if layer_times:  # benchmark-anchored: replace compute terms
         for lt, key in ((lt_dense, "dense"), (lt_moe, "moe")):
             if key in layer_times:
@@ -108,7 +133,7 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
     peak = hw.bf16_tflops * 1e12
     head = 2.0 * T * cfg.hidden_size * cfg.padded_vocab_size / plan.tp
     head_fwd = head / (peak * GEMM_EFF) + T * cfg.padded_vocab_size / plan.tp * 2.0 * 3 / (hw.hbm_gbs * 1e9 * ELEMENTWISE_BW_EFF)
-    head_bwd = head / (peak * GEMM_EFF) + head / (peak * GEMM_WGRAD_EFF)
+    head_bwd = head / (peak * GEMM_DGRAD_EFF) + head / (peak * GEMM_WGRAD_EFF)
     # stage costs (slowest stage drives the pipeline): mix of dense / moe layers in proportion
     n_moe = sum(1 for i in range(L) if cfg.is_moe_layer(i))
     frac_moe = n_moe / L
@@ -131,6 +156,7 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
     else:
         pipe = m * (f_last + b_last + w_last)
         bubble = 0.0
+    pipe *= STEP_OVERHEAD
     # data parallel gradient reduce-scatter + parameter all-gather (distributed optimizer) and the update
     pc = param_counts(cfg)
     dense_params = (sum(l["dense"] for l in pc["layers"]) / plan.pp + pc["embedding"] + pc["output"]) / plan.tp
@@ -146,8 +172,12 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
         opt_elems = dense_params + expert_params
     optimizer = opt_elems * 30.0 / (hw.hbm_gbs * 1e9 * ELEMENTWISE_BW_EFF) + (dense_params + expert_params) * 4.0 / (
         hw.hbm_gbs * 1e9)  # update (read p,m,v,g; write p,m,v,bf16) + grad-buffer zeroing
-    dp_exposed = dp_comm * (0.25 if plan.pp == 1 else 0.5)  # bucketed overlap with the last micro-batch's backward
-    it = pipe + dp_exposed + optimizer
+    # The bucket reductions hide in the last micro-batch's backward and the parameter all-gather in the next forward:
+    # measured on 8 GPUs, halving the bytes and hiding the gather moved the step by 0.4 %.  What a synchronous step
+    # does pay is the spread of sustained clocks between the chips of a node (~2 % at 8 GPUs)
+    dp_exposed = dp_comm * (0.05 if plan.pp == 1 else 0.25)
+    rank_skew = 0.02 * pipe * (1.0 - 1.0 / max(world, 1)) / (1.0 - 1.0 / 8.0) if world > 1 else 0.0
+    it = pipe + dp_exposed + optimizer + rank_skew
     tokens = plan.global_batch * plan.seq
     tps_gpu = tokens / it / world
     fl_tok = model_flops_per_token(cfg, plan.seq)
@@ -155,7 +185,7 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
     return {"iteration_ms": it * 1e3, "tokens_per_s_per_gpu": tps_gpu, "tflops_per_gpu": tflops,
             "mfu": tflops / hw.bf16_tflops, "world": world, "dp": plan.dp, "grad_accum": m,
             "breakdown_ms": {"pipeline": pipe * 1e3, "dp_comm_total": dp_comm * 1e3, "dp_comm_exposed": dp_exposed * 1e3,
-                             "optimizer": optimizer * 1e3, "layer_fwd_dense": lt_dense.fwd * 1e3,
+                             "optimizer": optimizer * 1e3, "rank_skew": rank_skew * 1e3, "precision": precision, "layer_fwd_dense": lt_dense.fwd * 1e3,
                              "layer_bwd_dense": (lt_dense.bwd_input + lt_dense.bwd_weight) * 1e3,
                              "layer_comm_fwd": mix(lt_dense.comm_fwd, lt_moe.comm_fwd) * 1e3,
                              "layer_comm_bwd": mix(lt_dense.comm_bwd, lt_moe.comm_bwd) * 1e3,

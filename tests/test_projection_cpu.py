@@ -134,3 +134,29 @@ def test_model_stats_reproduce_known_parameter_counts():
     assert abs(rows["qwen3_30B_A3B"]["params_B"] - 30.5) < 0.1 and abs(rows["qwen3_30B_A3B"]["active_params_B"] - 3.3) < 0.1
     assert abs(rows["deepseek_v3"]["params_B"] - 671) < 2 and abs(rows["deepseek_v3"]["active_params_B"] - 37.5) < 0.5
     assert abs(rows["mixtral_8x7B_v0.1"]["params_B"] - 46.7) < 0.1
+
+
+# Measured steps of this package on B200 (device-timed, max over ranks): profiles/bench_llama3.1_8B_*.json.txt,
+# profiles/data_parallel_overlap_8gpu_llama3.1_8B.md, profiles/bench_other_configs_8gpu.md
+MEASURED_MS = [
+    ("llama3.1_8B", dict(world=1, global_batch=16), "1f1b", "mxfp8", 5514.0),
+    ("llama3.1_8B", dict(world=8, global_batch=128), "1f1b", "mxfp8", 5642.0),
+    ("llama3.1_8B", dict(world=1, global_batch=16), "1f1b", "bf16", 7486.0),
+    ("llama3.1_70B", dict(world=8, tp=8, global_batch=4), "1f1b", "mxfp8", 2340.0),
+    ("llama3.1_70B", dict(world=8, tp=4, pp=2, vpp=2, global_batch=8), "interleaved", "mxfp8", 3658.0),
+]
+
+
+def test_performance_projection_matches_measured_steps():
+    """The kernel table of the performance model is calibrated on measured runs: every projected iteration time must
+    stay within 10 % of its measurement (the reference validates its projection against measured runs the same way,
+    docs_deprecated/tech_blogs/projection/projection.md:454-456)."""
+    from primus_b200.core.config.presets import load_preset
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.tools.projection.collective_model import Hardware
+
+    hw = Hardware.from_yaml(load_preset("b200", "hardware"))
+    for model, plan_kw, sched, prec, ms in MEASURED_MS:
+        cfg = TransformerConfig.from_dict(load_preset(model, "models"))
+        got = project_performance(cfg, ParallelPlan(**plan_kw), hw, sched, precision=prec)["iteration_ms"]
+        assert abs(got - ms) <= 0.10 * ms, (model, plan_kw, prec, got, ms)

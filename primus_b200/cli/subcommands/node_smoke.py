@@ -1,6 +1,9 @@
-"""``primus node_smoke``: single-process acceptance test of one node — inventory, native-library check and, on
-every local GPU in turn, a tiny training step through the sm_100a kernels plus the tier-2 performance checks
-(primus/tools/preflight/node_smoke/* in the reference; the launcher runs it with ``--single``)."""
+"""``primus node_smoke``: acceptance test of one node — read-only collectors (clocks, kernel log, software
+fingerprint, GPU health counters, foreign GPU processes, host limits, NICs / RDMA ports, NVLink topology, tooling) and,
+per GPU in a child process with a time limit, tier 1 (a tiny MXFP8 training step through the sm_100a kernels) and
+tier 2 (GEMM / HBM / peer-copy thresholds).  ``--dump-dir`` writes ``<hostname>.json``; ``--aggregate DIR`` turns the
+dumps of many nodes into a cluster summary with an exclude list.
+(primus/tools/preflight/node_smoke/* in the reference; the launcher runs it with ``--single``.)"""
 from __future__ import annotations
 
 import json
@@ -8,41 +11,49 @@ import json
 
 def register_subcommand(subparsers):
     p = subparsers.add_parser("node_smoke", help="per-node smoke test")
-    p.add_argument("--no-perf", action="store_true")
+    p.add_argument("--tier", type=int, default=2, choices=[0, 1, 2], help="0: collectors only, 1: + training step, 2: + perf")
+    p.add_argument("--no-perf", action="store_true", help="same as --tier 1")
+    p.add_argument("--gpus", default=None, help="comma-separated GPU indices (default: all)")
+    p.add_argument("--timeout", type=float, default=300.0, help="seconds per GPU")
+    p.add_argument("--nic-selector", default="", help="NCCL_IB_HCA-style selector of the NICs that must be up")
+    p.add_argument("--dump-dir", default=None)
+    p.add_argument("--clean-dump", action="store_true")
+    p.add_argument("--aggregate", default=None, metavar="DIR", help="summarise the node dumps in DIR instead of testing")
+    p.add_argument("--report", default=None, help="with --aggregate: write a Markdown report here")
+    p.add_argument("--gemm-tflops", type=float, default=None)
+    p.add_argument("--hbm-gbs", type=float, default=None)
+    p.add_argument("--p2p-gbs", type=float, default=None)
     p.add_argument("--json", action="store_true")
     p.set_defaults(func=run)
 
 
 def run(args, unknown):
-    import torch
+    from ...tools.preflight import node_smoke as ns
+    from ...tools.preflight.node_smoke.aggregator import load_dumps
 
-    from ...tools.preflight.checks import run_preflight
-
-    rep = run_preflight(perf=not args.no_perf)
-    if torch.cuda.is_available() and rep["native"]["present"]:
-        from ...engine.trainer import TrainConfig, Trainer
-        from ...models.config import TransformerConfig
-        from ...ops import _lib
-        from ...parallel import state as ps
-
-        for d in range(torch.cuda.device_count()):
-            try:
-                torch.cuda.set_device(d)
-                ps.destroy_model_parallel()
-                cfg = TransformerConfig(num_layers=2, hidden_size=512, ffn_hidden_size=1408, num_attention_heads=4,
-                                        num_query_groups=2, kv_channels=128, vocab_size=32000, params_dtype="bf16")
-                tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=256, train_iters=2, log_interval=1)
-                losses = Trainer(cfg, tc, device=f"cuda:{d}", log_fn=lambda s: None).train(2)
-                torch.cuda.synchronize()
-                _lib.check_status(d)
-                ok = all(l == l for l in losses)
-                rep["checks"].append({"check": f"training step on GPU {d}", "status": "PASS" if ok else "FAIL",
-                                      "detail": f"losses {losses}"})
-            except Exception as e:  # noqa: BLE001
-                rep["checks"].append({"check": f"training step on GPU {d}", "status": "FAIL", "detail": repr(e)})
+    if args.aggregate:
+        summary = ns.summarize_cluster(load_dumps(args.aggregate))
+        if args.report:
+            ns.write_report(summary, args.report)
+        print(json.dumps(summary, indent=1, default=str))
+        return 1 if summary["fail"] else 0
+    extra = []
+    for flag, v in (("--gemm-tflops", args.gemm_tflops), ("--hbm-gbs", args.hbm_gbs), ("--p2p-gbs", args.p2p_gbs)):
+        if v is not None:
+            extra += [flag, str(v)]
+    tier = 1 if args.no_perf and args.tier > 1 else args.tier
+    gpus = [int(x) for x in args.gpus.split(",")] if args.gpus else None
+    rep = ns.run_node_smoke(tier=tier, gpus=gpus, timeout_s=args.timeout, dump_dir=args.dump_dir,
+                            nic_selector=args.nic_selector, extra_args=extra, clean_dump=args.clean_dump)
     if args.json:
         print(json.dumps(rep, indent=1, default=str))
     else:
-        for c in rep["checks"]:
-            print(f"  [{c['status']}] {c['check']}: {c['detail']}")
-    return 1 if any(c["status"] == "FAIL" for c in rep["checks"]) else 0
+        print(f"node {rep['hostname']}: {rep['status']}")
+        for name, c in rep["collectors"].items():
+            detail = "; ".join(c.get("problems") or []) or c.get("reason", "")
+            print(f"  [{c.get('status')}] {name}{': ' + detail if detail else ''}")
+        for g in rep["per_gpu"]:
+            for c in g["checks"]:
+                facts = {k: (round(v, 1) if isinstance(v, float) else v) for k, v in c.items() if k not in ("check", "status")}
+                print(f"  [{c['status']}] GPU{g['gpu']} {c['check']}: {facts}")
+    return 1 if rep["status"] == "FAIL" else 0

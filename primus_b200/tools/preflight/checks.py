@@ -149,11 +149,117 @@ def perf_allreduce(mib: int = 256, iters: int = 10) -> dict:
     return {"bytes": x.numel() * 2, "busbw_gbs": alg * 2 * (p - 1) / p, "ranks": p}
 
 
+def _time_collective(fn, iters: int = 8, warmup: int = 2) -> float:
+    """Device time per call in ms, maximum over ranks (the slowest rank defines a collective's time)."""
+    import torch
+    import torch.distributed as dist
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def perf_intra_node_comm(sizes_mib=(1, 64, 256)) -> dict:
+    """All-reduce / all-gather / reduce-scatter / all-to-all bus bandwidth inside the node for a few sizes
+    (primus/tools/preflight/intra_node_comm.py in the reference)."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return {"skipped": "single rank"}
+    p = dist.get_world_size()
+    rows = []
+    for mib in sizes_mib:
+        n = mib * 2**20 // 2 // p * p
+        x = torch.ones(n, dtype=torch.bfloat16, device="cuda")
+        shard = torch.empty(n // p, dtype=torch.bfloat16, device="cuda")
+        y = torch.empty_like(x)
+        by = n * 2
+        for name, fn, factor in (
+                ("all_reduce", lambda: dist.all_reduce(x), 2 * (p - 1) / p),
+                ("all_gather", lambda: dist.all_gather_into_tensor(y, shard), (p - 1) / p),
+                ("reduce_scatter", lambda: dist.reduce_scatter_tensor(shard, x), (p - 1) / p),
+                ("all_to_all", lambda: dist.all_to_all_single(y, x), (p - 1) / p)):
+            ms = _time_collective(fn)
+            rows.append({"op": name, "mib": mib, "ms": ms, "busbw_gbs": by / ms / 1e6 * factor})
+    return {"ranks": p, "rows": rows}
+
+
+def perf_ring_p2p(mib: int = 256) -> dict:
+    """Every rank sends to its right neighbour and receives from its left one at the same time (the traffic pattern of
+    pipeline parallelism and ring attention); reports the slowest hop.  Works inside a node and across nodes
+    (primus/tools/preflight/inter_node_ring_p2p.py, inter_node_comm_p2p.py in the reference)."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return {"skipped": "single rank"}
+    p, r = dist.get_world_size(), dist.get_rank()
+    n = mib * 2**20 // 2
+    send = torch.ones(n, dtype=torch.bfloat16, device="cuda")
+    recv = torch.empty_like(send)
+
+    def step():
+        ops = [dist.P2POp(dist.isend, send, (r + 1) % p), dist.P2POp(dist.irecv, recv, (r - 1) % p)]
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+
+    ms = _time_collective(step)
+    return {"ranks": p, "mib": mib, "ms": ms, "gbs_per_direction": n * 2 / ms / 1e6}
+
+
+def perf_pairwise_p2p(mib: int = 128, max_pairs: int = 64) -> dict:
+    """Unidirectional bandwidth of every (source, destination) rank pair, one pair at a time: finds the one bad link
+    that a ring or an all-reduce number hides in an average."""
+    import torch
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return {"skipped": "single rank"}
+    p, r = dist.get_world_size(), dist.get_rank()
+    n = mib * 2**20 // 2
+    buf = torch.ones(n, dtype=torch.bfloat16, device="cuda")
+    out, pairs = [], [(a, b) for a in range(p) for b in range(p) if a != b][:max_pairs]
+    for a, b in pairs:
+        def step(a=a, b=b):
+            if r == a:
+                dist.send(buf, b)
+            elif r == b:
+                dist.recv(buf, a)
+        ms = _time_collective(step, iters=4, warmup=1)
+        out.append({"src": a, "dst": b, "gbs": n * 2 / ms / 1e6})
+    worst = min(out, key=lambda x: x["gbs"])
+    return {"ranks": p, "mib": mib, "pairs": out, "worst": worst, "median_gbs": sorted(x["gbs"] for x in out)[len(out) // 2]}
+
+
+def network_inventory() -> dict:
+    """NICs with speed / MTU, RDMA devices with port state and rate, default route, NCCL-related environment
+    (primus/tools/preflight/network/{network_basic,network_standard,network_full}.py in the reference)."""
+    from .node_smoke.collectors import collect_nic_status
+
+    nic = collect_nic_status(selector=os.environ.get("NCCL_IB_HCA", ""))
+    route = _run(["ip", "route", "show", "default"]).splitlines()[:2]
+    return {"nics": nic["nics"], "rdma_ports": nic["rdma_ports"], "down": nic["down"], "default_route": route,
+            "master_addr": os.environ.get("MASTER_ADDR"), "nnodes": os.environ.get("NNODES") or os.environ.get("SLURM_NNODES"),
+            "nccl_env": {k: v for k, v in os.environ.items() if k.startswith(("NCCL_", "UCX_", "GLOO_"))}}
+
+
 def run_preflight(perf: bool = True, thresholds: dict | None = None) -> dict:
     import torch
 
     th = dict(DEFAULT_THRESHOLDS, **(thresholds or {}))
     rep = {"time": time.strftime("%Y-%m-%d %H:%M:%S"), "host": host_info(), "gpu": gpu_info(), "network": network_info(),
+           "network_inventory": network_inventory(),
            "native": native_lib_check(), "checks": []}
 
     def add(name, ok, detail):
@@ -178,4 +284,12 @@ def run_preflight(perf: bool = True, thresholds: dict | None = None) -> dict:
             add("node-local all-reduce", ar["busbw_gbs"] >= th["allreduce_busbw_gbs"],
                 f"{ar['busbw_gbs']:.0f} GB/s bus bandwidth (>= {th['allreduce_busbw_gbs']:.0f})")
         rep["perf"] = {"gemm": g, "hbm": h, "allreduce": ar}
+        if "busbw_gbs" in ar:
+            ring = perf_ring_p2p()
+            add("ring send / receive (every rank to its neighbour)", ring["gbs_per_direction"] >= th["p2p_gbs"],
+                f"{ring['gbs_per_direction']:.0f} GB/s per direction (>= {th['p2p_gbs']:.0f})")
+            pair = perf_pairwise_p2p()
+            add("slowest rank pair", pair["worst"]["gbs"] >= 0.8 * pair["median_gbs"],
+                f"{pair['worst']['src']} -> {pair['worst']['dst']}: {pair['worst']['gbs']:.0f} GB/s (median {pair['median_gbs']:.0f})")
+            rep["perf"].update(ring=ring, pairwise=pair, intra_node=perf_intra_node_comm())
     return rep

@@ -89,8 +89,8 @@ def _validate(ctx: PatchContext):
         if not (1 < ep <= 8):
             raise ValueError("use_turbo_mega_moe needs 1 < expert_model_parallel_size <= 8 "
                              "(the fused all-to-all rides intra-node peer memory)")
-    if p.get("fp8") and p.get("fp8_recipe", "mxfp8") not in ("tensorwise", "blockwise", "mxfp8"):
-        raise ValueError("fp8 GEMMs support recipes tensorwise | blockwise | mxfp8")
+    if p.get("fp8") and p.get("fp8_recipe", "mxfp8") not in ("tensorwise", "blockwise", "mxfp8", "delayed"):
+        raise ValueError("fp8 GEMMs support recipes delayed | tensorwise | blockwise | mxfp8")
     if p.get("fp4") and p.get("fp4_recipe", "mxfp4") != "mxfp4":
         raise ValueError("fp4 GEMMs support the mxfp4 recipe only")
     if p.get("deterministic_mode"):

@@ -51,13 +51,18 @@ constexpr int QUANT_SMEM = TILE * PITCH * 2;   // one staged bf16 tile; the fp8 
 // (row0, col0).  Called by all threads of a 256-thread CTA after the tile is complete (caller synchronises before).
 // Results are written straight from registers: 64 contiguous bytes per thread in the row direction, 8 bytes per row
 // (64 contiguous bytes per 8 lanes) in the column direction -- whole 32-byte sectors either way.
-// FIXED: every block takes the scale exponent `fixed_e` (one power-of-two scale for the whole tensor) instead of the
-// exponent of its own maximum.
-template <bool FIXED = false>
+// MODE selects where a block of 32 takes its scale exponent from:
+//   SCALE_BLOCK32 its own maximum (MXFP8);
+//   SCALE_FIXED   `fixed_e` for every block (one power-of-two scale for the tensor, or for this 128 x 128 tile);
+//   SCALE_VEC128  `e_rowv[r]` for the blocks of tile row r (row direction) and `e_colv[c]` for those of tile column c
+//                 (column direction): one scale per 1 x 128 / 128 x 1 vector, written into its four 32-blocks.
+enum { SCALE_BLOCK32 = 0, SCALE_FIXED = 1, SCALE_VEC128 = 2 };
+template <int MODE = SCALE_BLOCK32>
 __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, int R, int C,
                                                      int row0, int col0, uint8_t* __restrict__ q_row,
                                                      uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
-                                                     uint8_t* __restrict__ sf_col, int fixed_e = 0) {
+                                                     uint8_t* __restrict__ sf_col, int fixed_e = 0,
+                                                     const uint8_t* e_rowv = nullptr, const uint8_t* e_colv = nullptr) {
   const int tid = threadIdx.x;
   if (q_row) {
     // thread -> (row r, two 32-element blocks): 64 contiguous bytes of the row
@@ -80,7 +85,7 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
-      const int e = FIXED ? fixed_e : e8m0_from_amax(amax);
+      const int e = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_rowv[r] : e8m0_from_amax(amax));
       const float inv = inv_scale_from_e8m0(e);
       uint32_t w[8];
 #pragma unroll
@@ -125,8 +130,9 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       o = __shfl_xor_sync(0xffffffffu, w, 16);
       m[u] = __hmax2(m[u], *reinterpret_cast<__nv_bfloat162*>(&o));
       const float2 a = __bfloat1622float2(m[u]);
-      e[2 * u] = FIXED ? fixed_e : e8m0_from_amax(a.x);
-      e[2 * u + 1] = FIXED ? fixed_e : e8m0_from_amax(a.y);
+      e[2 * u] = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u] : e8m0_from_amax(a.x));
+      e[2 * u + 1] =
+          MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u + 1] : e8m0_from_amax(a.y));
       inv[2 * u] = inv_scale_from_e8m0(e[2 * u]);
       inv[2 * u + 1] = inv_scale_from_e8m0(e[2 * u + 1]);
     }
@@ -180,8 +186,8 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
 // primus/backends/megatron/core/extensions/primus_turbo_float8_local.py:66-70).
 __global__ void __launch_bounds__(256, 4)
 quant_tensorwise_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, const float* __restrict__ tensor_amax,
-                        uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
-                        uint8_t* __restrict__ sf_col) {
+                        const float* __restrict__ fallback_amax, uint8_t* __restrict__ q_row,
+                        uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
   extern __shared__ __align__(16) uint8_t smem_q[];
   __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
   const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
@@ -193,9 +199,71 @@ quant_tensorwise_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, const
     const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
   }
-  const int fixed_e = e8m0_from_amax(*tensor_amax);
+  // delayed scaling passes the maximum its history predicts as `tensor_amax` and this step's measured maximum as
+  // `fallback_amax`, which is used while the history is still empty (0)
+  float a = *tensor_amax;
+  if (a == 0.f && fallback_amax != nullptr) a = *fallback_amax;
+  const int fixed_e = e8m0_from_amax(a);
   __syncthreads();
-  quantize_staged_tile<true>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col, fixed_e);
+  quantize_staged_tile<SCALE_FIXED>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col, fixed_e);
+}
+
+// Block-wise FP8 (blocks of 128): activations and gradients take one power-of-two scale per 1 x 128 vector along the
+// reduced dimension (row direction: 128 consecutive columns of a row; column direction: 128 consecutive rows of a
+// column), weights (TILEWISE) one per 128 x 128 tile.  Stored in the MXFP8 layout with the exponent repeated in the
+// four 32-blocks it covers, so the block-scaled GEMM consumes it unchanged.  Granularity of the reference's
+// "blockwise" recipe (primus/backends/megatron/core/extensions/primus_turbo.py: Float8QuantConfig with
+// ScalingGranularity.BLOCKWISE, block_size 128), with scales restricted to powers of two.
+template <bool TILEWISE>
+__global__ void __launch_bounds__(256, 4)
+quant_blockwise_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
+                       uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
+  extern __shared__ __align__(16) uint8_t smem_q[];
+  __shared__ uint8_t e_rowv[TILE], e_colv[TILE];
+  __shared__ float warp_max[4];
+  __nv_bfloat16* tile = reinterpret_cast<__nv_bfloat16*>(smem_q);
+  const int row0 = blockIdx.y * TILE, col0 = blockIdx.x * TILE;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int v = tid + it * 256;
+    const int r = v >> 4, c8 = (v & 15) * 8;
+    const uint4 d = *reinterpret_cast<const uint4*>(x + (long)(row0 + r) * C + col0 + c8);
+    *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
+  }
+  __syncthreads();
+  // threads 0..127: maximum of tile row tid; threads 128..255: maximum of tile column tid - 128
+  float m = 0.f;
+  if (tid < TILE) {
+    __nv_bfloat162 mm = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int v = 0; v < 16; ++v) {
+      const uint4 d = *reinterpret_cast<const uint4*>(&tile[tid * PITCH + v * 8]);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) mm = __hmax2(mm, __habs2(h[u]));
+    }
+    const float2 f = __bfloat1622float2(mm);
+    m = fmaxf(f.x, f.y);
+  } else if (!TILEWISE) {
+    const int c = tid - TILE;
+#pragma unroll 8
+    for (int r = 0; r < TILE; ++r) m = fmaxf(m, fabsf(__bfloat162float(tile[r * PITCH + c])));
+  }
+  if (TILEWISE) {
+    float v = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (tid < TILE && (tid & 31) == 0) warp_max[tid >> 5] = v;
+    __syncthreads();
+    const int fixed_e = e8m0_from_amax(fmaxf(fmaxf(warp_max[0], warp_max[1]), fmaxf(warp_max[2], warp_max[3])));
+    quantize_staged_tile<SCALE_FIXED>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col, fixed_e);
+  } else {
+    if (tid < TILE) e_rowv[tid] = (uint8_t)e8m0_from_amax(m);
+    else e_colv[tid - TILE] = (uint8_t)e8m0_from_amax(m);
+    __syncthreads();
+    quantize_staged_tile<SCALE_VEC128>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col, 0, e_rowv, e_colv);
+  }
 }
 
 // max |x| over n bf16 values (n a multiple of 8) into *out, which the caller zeroes first (non-negative floats order
@@ -371,8 +439,53 @@ int pb_quant_fp8_tensorwise(const void* x, int R, int C, float* amax, void* q_ro
   const int blocks = (int)((n8 + 2047) / 2048 < 1184 ? (n8 + 2047) / 2048 : 1184);
   amax_bf16_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), n8, amax);
   quant_tensorwise_kernel<<<dim3(C / TILE, R / TILE), 256, QUANT_SMEM, s>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), R, C, amax, reinterpret_cast<uint8_t*>(q_row),
+      reinterpret_cast<const __nv_bfloat16*>(x), R, C, amax, nullptr, reinterpret_cast<uint8_t*>(q_row),
       reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+// Delayed-scaling FP8 of x [R, C]: the scale comes from scale_amax[0] (the maximum predicted from the history of
+// earlier steps; 0 = no history yet, then this call's own maximum is used), and max |x| is folded into amax_now[0]
+// with an atomic maximum -- the caller zeroes amax_now when it rolls the history, so several calls between two rolls
+// (micro-batches) record their overall maximum.  Values above the predicted range saturate at +-448.
+int pb_quant_fp8_delayed(const void* x, int R, int C, float* amax_now, const float* scale_amax, void* q_row,
+                         void* sf_row, void* q_col, void* sf_col, cudaStream_t s) {
+  if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(quant_tensorwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, QUANT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const long n8 = (long)R * C / 8;
+  const int blocks = (int)((n8 + 2047) / 2048 < 1184 ? (n8 + 2047) / 2048 : 1184);
+  amax_bf16_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), n8, amax_now);
+  quant_tensorwise_kernel<<<dim3(C / TILE, R / TILE), 256, QUANT_SMEM, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), R, C, scale_amax, amax_now, reinterpret_cast<uint8_t*>(q_row),
+      reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+// Block-wise FP8 of x [R, C] (multiples of 128): one power-of-two scale per 1 x 128 vector (tilewise = 0:
+// activations, gradients) or per 128 x 128 tile (tilewise = 1: weights); outputs as pb_quant_mxfp8.
+int pb_quant_fp8_blockwise(const void* x, int R, int C, int tilewise, void* q_row, void* sf_row, void* q_col,
+                           void* sf_col, cudaStream_t s) {
+  if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(quant_blockwise_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         QUANT_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(quant_blockwise_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QUANT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const dim3 grid(C / TILE, R / TILE);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  uint8_t *qr = reinterpret_cast<uint8_t*>(q_row), *sr = reinterpret_cast<uint8_t*>(sf_row);
+  uint8_t *qc = reinterpret_cast<uint8_t*>(q_col), *sc = reinterpret_cast<uint8_t*>(sf_col);
+  if (tilewise) quant_blockwise_kernel<true><<<grid, 256, QUANT_SMEM, s>>>(xp, R, C, qr, sr, qc, sc);
+  else quant_blockwise_kernel<false><<<grid, 256, QUANT_SMEM, s>>>(xp, R, C, qr, sr, qc, sc);
   return (int)cudaGetLastError();
 }
 

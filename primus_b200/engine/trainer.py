@@ -26,6 +26,7 @@ import torch.distributed as dist
 
 from ..models.config import TransformerConfig
 from ..models.gpt import build_model
+from ..ops import gemm as _gemm_ops
 from ..parallel import state as ps
 from ..parallel.distributed import DistributedOptimizer, ParamGradBuffer
 from . import schedules
@@ -215,10 +216,10 @@ class Trainer:
         from ..ops import gemm as _gemm
 
         # fp8 recipe of the linear-layer GEMMs (attention, the LM head and the router stay in bf16)
-        if model_cfg.fp8 and model_cfg.fp8_recipe not in ("mxfp8", "tensorwise"):
-            raise NotImplementedError(f"fp8_recipe {model_cfg.fp8_recipe!r}: mxfp8 (a scale per 32 elements) and tensorwise "
-                                      "(one power-of-two scale per tensor) are built")
-        _gemm.set_fp8_recipe(model_cfg.fp8_recipe if model_cfg.fp8 else None)
+        if model_cfg.fp8 and model_cfg.fp8_recipe not in _gemm.FP8_RECIPES:
+            raise NotImplementedError(f"fp8_recipe {model_cfg.fp8_recipe!r}: choose one of {_gemm.FP8_RECIPES}")
+        _gemm.set_fp8_recipe(model_cfg.fp8_recipe if model_cfg.fp8 else None, model_cfg.fp8_amax_history_len,
+                             model_cfg.fp8_amax_compute_algo, model_cfg.fp8_margin)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
         # ---------------------------------------------------------------- model chunks
@@ -592,6 +593,7 @@ class Trainer:
             self.lora.optimizer_step(lr)
         else:
             self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+        _gemm_ops.roll_fp8_scales()      # delayed scaling: this step's maxima become history (no-op for other recipes)
         if self._emb_primary or self._emb_replica:
             for buf in self.buffers:
                 buf.finish_param_sync()        # the updated embedding must be complete before it is re-sent

@@ -83,7 +83,10 @@ class TransformerConfig:
     # numerics / memory
     params_dtype: str = "bf16"  # bf16 | fp32
     fp8: Optional[str] = None  # None | "e4m3"
-    fp8_recipe: str = "mxfp8"
+    fp8_recipe: str = "mxfp8"  # mxfp8 | tensorwise | delayed | blockwise
+    fp8_amax_history_len: int = 1          # delayed scaling: steps of recorded maxima
+    fp8_amax_compute_algo: str = "most_recent"   # delayed scaling: most_recent | max over the history
+    fp8_margin: int = 0                    # delayed scaling: extra powers of two of headroom
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_method: Optional[str] = None       # full: "uniform" (chunks of recompute_num_layers) | "block" (first N layers)
     recompute_num_layers: Optional[int] = None

@@ -73,7 +73,7 @@ def stream_ptr() -> ctypes.c_void_p:
 
 
 # Number of device kernels each launcher enqueues (default 1); used for the launch counter below.
-_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "sumsq": 2, "flash_attn_bwd": 3}
+_KERNELS_PER_CALL = {"rmsnorm_bwd": 2, "sumsq": 2, "flash_attn_bwd": 3, "quant_fp8_tensorwise": 2, "quant_fp8_delayed": 2}
 LAUNCH_COUNT = 0
 
 

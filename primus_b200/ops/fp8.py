@@ -56,38 +56,133 @@ def _e8m0(amax: torch.Tensor) -> torch.Tensor:
     return torch.where(amax == 0, torch.zeros_like(e), e)
 
 
-# Tensor-wise recipe: one power-of-two scale per tensor (every block carries the exponent of the tensor maximum).
-# Set by ``ops.gemm.set_fp8_recipe("tensorwise")``; ``quantize_mxfp8`` follows it unless told otherwise.
-TENSORWISE = False
+# Scaling recipe of ``quantize_mxfp8`` (set by ``ops.gemm.set_fp8_recipe``).  All recipes store E4M3 values with UE8M0
+# exponents in the MXFP8 layout, so every GEMM runs on the same block-scaled kernel; they differ in which elements share
+# an exponent and where it comes from:
+#   "mxfp8"       every 32 elements along the reduced dimension, from their own maximum
+#   "tensorwise"  the whole tensor, from its current maximum ("current scaling")
+#   "delayed"     the whole tensor, from the maxima recorded in earlier steps (``DelayedScaling``)
+#   "blockwise"   activations / gradients: every 1 x 128 vector along the reduced dimension; weights: 128 x 128 tiles
+SCALING = "mxfp8"
+TENSORWISE = False      # kept in step with SCALING == "tensorwise" for callers that read the old switch
+
+
+class DelayedScaling:
+    """State of the delayed-scaling recipe: for every (tensor role) slot the maximum seen since the last roll
+    (``amax_now``, written by the quantiser with an atomic maximum), a history of the last ``history_len`` rolled
+    maxima, and the maximum the next quantisations scale by (``scale_amax``: the largest or the most recent history
+    entry, times ``2^margin``).  ``roll()`` runs once per optimizer step, entirely on the device; with a process
+    group the rolled maxima are first max-reduced over it, so ranks holding shards of one tensor use one scale.
+
+    Behaviour of Transformer-Engine's ``DelayedScaling(margin, amax_history_len, amax_compute_algo)`` as driven by the
+    reference's ``--fp8-amax-history-len / --fp8-amax-compute-algo / --fp8-margin`` arguments (the ``delayed`` entry of
+    ``fp8_recipe`` in primus/configs/modules/megatron/trainer_base.yaml), with power-of-two scales."""
+
+    def __init__(self, history_len: int = 1, algo: str = "most_recent", margin: int = 0, capacity: int = 1024):
+        assert algo in ("max", "most_recent"), algo
+        self.history_len, self.algo, self.margin = max(1, int(history_len)), algo, int(margin)
+        self.capacity = capacity
+        self.slots: dict = {}
+        self.amax_now = self.history = self.scale_amax = None
+
+    def _allocate(self, device):
+        self.amax_now = torch.zeros(self.capacity, dtype=torch.float32, device=device)
+        self.scale_amax = torch.zeros(self.capacity, dtype=torch.float32, device=device)
+        self.history = torch.zeros(self.history_len, self.capacity, dtype=torch.float32, device=device)
+
+    def slot(self, key, device) -> int:
+        i = self.slots.get(key)
+        if i is None:
+            i = self.slots[key] = len(self.slots)
+            if self.amax_now is None:
+                self._allocate(device)
+            elif i >= self.capacity:
+                old = (self.amax_now, self.scale_amax, self.history)
+                self.capacity *= 2
+                self._allocate(device)
+                n = old[0].numel()
+                self.amax_now[:n], self.scale_amax[:n], self.history[:, :n] = old
+        return i
+
+    def roll(self, group=None) -> None:
+        """Push the maxima of the step that just ended into the history and derive the next step's scales."""
+        if self.amax_now is None:
+            return
+        if group is not None and torch.distributed.get_world_size(group) > 1:
+            torch.distributed.all_reduce(self.amax_now, op=torch.distributed.ReduceOp.MAX, group=group)
+        seen = self.amax_now > 0            # a slot not used this step keeps its history
+        rolled = torch.roll(self.history, 1, 0)
+        rolled[0] = self.amax_now
+        self.history.copy_(torch.where(seen[None, :], rolled, self.history))
+        pick = self.history.amax(0) if self.algo == "max" else self.history[0]
+        self.scale_amax.copy_(pick * float(2.0 ** self.margin))
+        self.amax_now.zero_()
+
+    def state_dict(self) -> dict:
+        if self.amax_now is None:
+            return {}
+        return {"keys": list(self.slots), "history": self.history[:, :len(self.slots)].cpu(),
+                "scale_amax": self.scale_amax[:len(self.slots)].cpu()}
+
+
+DELAYED: Optional[DelayedScaling] = None
+
+
+def _block_exponents(xf: torch.Tensor, direction: str, scaling: str, is_weight: bool, e_all) -> torch.Tensor:
+    """UE8M0 exponent of every 32-block of ``xf`` [R, C]: [R, C/32] ("row") or [R/32, C] ("col")."""
+    R, C = xf.shape
+    a = xf.abs()
+    if direction == "row":
+        shape = (R, C // BLOCK)
+        if scaling in ("tensorwise", "delayed"):
+            return e_all.expand(shape).contiguous()
+        if scaling == "blockwise" and is_weight:
+            t = a.view(R // TILE, TILE, C // TILE, TILE).amax((1, 3))                       # [R/128, C/128]
+            return _e8m0(t).repeat_interleave(TILE, 0).repeat_interleave(TILE // BLOCK, 1)
+        if scaling == "blockwise":
+            return _e8m0(a.view(R, C // TILE, TILE).amax(-1)).repeat_interleave(TILE // BLOCK, 1)
+        return _e8m0(a.view(R, C // BLOCK, BLOCK).amax(-1))
+    shape = (R // BLOCK, C)
+    if scaling in ("tensorwise", "delayed"):
+        return e_all.expand(shape).contiguous()
+    if scaling == "blockwise" and is_weight:
+        t = a.view(R // TILE, TILE, C // TILE, TILE).amax((1, 3))
+        return _e8m0(t).repeat_interleave(TILE // BLOCK, 0).repeat_interleave(TILE, 1)
+    if scaling == "blockwise":
+        return _e8m0(a.view(R // TILE, TILE, C).amax(1)).repeat_interleave(TILE // BLOCK, 0)
+    return _e8m0(a.view(R // BLOCK, BLOCK, C).amax(1))
 
 
 def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = True,
-                       tensorwise: Optional[bool] = None) -> MXFP8Tensor:
+                       tensorwise: Optional[bool] = None, scaling: Optional[str] = None, is_weight: bool = False,
+                       scale_amax: Optional[torch.Tensor] = None) -> MXFP8Tensor:
+    """Plain-PyTorch statement of every recipe's rounding rules.  ``scale_amax`` (delayed scaling): the maximum the
+    scale is derived from; zero or None falls back to the tensor's own maximum."""
     R, C = x.shape
     assert R % TILE == 0 and C % TILE == 0
     xf = x.float()
-    tensorwise = TENSORWISE if tensorwise is None else tensorwise
-    e_all = _e8m0(xf.abs().amax().reshape(1)) if tensorwise else None
+    scaling = ("tensorwise" if tensorwise else "mxfp8") if tensorwise is not None and scaling is None else (scaling or SCALING)
+    e_all = None
+    if scaling in ("tensorwise", "delayed"):
+        amax = xf.abs().amax().reshape(1)
+        if scaling == "delayed" and scale_amax is not None:
+            sa = scale_amax.reshape(1).to(amax)
+            amax = torch.where(sa > 0, sa, amax)
+        e_all = _e8m0(amax)
     out = MXFP8Tensor(shape=(R, C))
     dev = x.device
     for direction in ("row", "col"):
         if (direction == "row" and not rowwise) or (direction == "col" and not colwise):
             continue
+        e = _block_exponents(xf, direction, scaling, is_weight, e_all)
+        inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
         if direction == "row":
-            blocks = xf.view(R, C // BLOCK, BLOCK)
-            e = _e8m0(blocks.abs().amax(-1))                       # [R, C/32]
-            e = e_all.expand_as(e).contiguous() if tensorwise else e
-            inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
-            q = (blocks * inv[..., None]).reshape(R, C)
+            q = (xf.view(R, C // BLOCK, BLOCK) * inv[..., None]).reshape(R, C)
             mn = torch.arange(R, device=dev)[:, None].expand(R, C // BLOCK)
             kb = torch.arange(C // BLOCK, device=dev)[None, :].expand(R, C // BLOCK)
             off = sf_offsets(mn, kb, C // TILE)
         else:
-            blocks = xf.view(R // BLOCK, BLOCK, C)
-            e = _e8m0(blocks.abs().amax(1))                        # [R/32, C]
-            e = e_all.expand_as(e).contiguous() if tensorwise else e
-            inv = ((254 - e).clamp(min=1) << 23).view(torch.float32)
-            q = (blocks * inv[:, None, :]).reshape(R, C)
+            q = (xf.view(R // BLOCK, BLOCK, C) * inv[:, None, :]).reshape(R, C)
             mn = torch.arange(C, device=dev)[None, :].expand(R // BLOCK, C)
             kb = torch.arange(R // BLOCK, device=dev)[:, None].expand(R // BLOCK, C)
             off = sf_offsets(mn, kb, R // TILE)
@@ -111,16 +206,30 @@ def dequantize_mxfp8_ref(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> to
     return q.view(torch.float8_e4m3fn).float() * torch.exp2(e - 127.0)
 
 
-def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True,
-                   tensorwise: Optional[bool] = None) -> MXFP8Tensor:
-    """bf16 [R, C] (R, C multiples of 128) -> MXFP8 in the requested directions (one kernel).  ``tensorwise`` (default:
-    the module switch ``TENSORWISE``): a single power-of-two scale for the whole tensor (maximum reduction + quantiser,
-    ``pb_quant_fp8_tensorwise``) in the same storage layout."""
-    tensorwise = TENSORWISE if tensorwise is None else tensorwise
+def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True, tensorwise: Optional[bool] = None,
+                   scaling: Optional[str] = None, is_weight: bool = False, slot_key=None) -> MXFP8Tensor:
+    """bf16 [R, C] (R, C multiples of 128) -> FP8 values + block exponents in the requested directions.
+
+    ``scaling`` (default: the module recipe ``SCALING``) picks the recipe; ``tensorwise=True/False`` is shorthand for
+    "tensorwise" / "mxfp8".  ``is_weight`` matters to "blockwise" (128 x 128 tiles instead of 1 x 128 vectors);
+    ``slot_key`` names the tensor's role for "delayed" (a tensor without a key is scaled by its current maximum)."""
+    if scaling is None:
+        scaling = SCALING if tensorwise is None else ("tensorwise" if tensorwise else "mxfp8")
+    delayed_slot = None
+    if scaling == "delayed":
+        if DELAYED is None or slot_key is None:
+            scaling = "tensorwise"
+        else:
+            delayed_slot = DELAYED.slot(slot_key, x.device)
     if not x.is_cuda:
-        return quantize_mxfp8_ref(x, rowwise, colwise, tensorwise)
+        if delayed_slot is not None:
+            out = quantize_mxfp8_ref(x, rowwise, colwise, None, "delayed", is_weight,
+                                     DELAYED.scale_amax[delayed_slot])
+            DELAYED.amax_now[delayed_slot] = torch.maximum(DELAYED.amax_now[delayed_slot], x.float().abs().amax())
+            return out
+        return quantize_mxfp8_ref(x, rowwise, colwise, None, scaling, is_weight)
     R, C = x.shape
-    assert R % TILE == 0 and C % TILE == 0, "MXFP8 quantisation needs dimensions that are multiples of 128"
+    assert R % TILE == 0 and C % TILE == 0, "FP8 quantisation needs dimensions that are multiples of 128"
     x = x.contiguous()
     if x.dtype != torch.bfloat16:
         x = x.bfloat16()
@@ -132,9 +241,14 @@ def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True,
     if colwise:
         out.q_col = torch.empty(R, C, dtype=torch.uint8, device=dev)
         out.sf_col = torch.empty(R * C // BLOCK, dtype=torch.uint8, device=dev)
-    if tensorwise:
+    if delayed_slot is not None:
+        _lib.call("quant_fp8_delayed", x, R, C, DELAYED.amax_now[delayed_slot:], DELAYED.scale_amax[delayed_slot:],
+                  out.q_row, out.sf_row, out.q_col, out.sf_col)
+    elif scaling == "tensorwise":
         amax = torch.empty(1, dtype=torch.float32, device=dev)
         _lib.call("quant_fp8_tensorwise", x, R, C, amax, out.q_row, out.sf_row, out.q_col, out.sf_col)
+    elif scaling == "blockwise":
+        _lib.call("quant_fp8_blockwise", x, R, C, int(is_weight), out.q_row, out.sf_row, out.q_col, out.sf_col)
     else:
         _lib.call("quant_mxfp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
     return out

@@ -29,14 +29,21 @@ _W_CACHE: dict = {}
 _ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
 
 
-def set_fp8_recipe(recipe: str | None) -> None:
+FP8_RECIPES = ("mxfp8", "tensorwise", "delayed", "blockwise")
+
+
+def set_fp8_recipe(recipe: str | None, amax_history_len: int = 1, amax_compute_algo: str = "most_recent",
+                   margin: int = 0) -> None:
+    """Select the FP8 recipe of all eligible GEMMs (None: bf16).  Every recipe stores its operands in the MXFP8 layout
+    (see ``ops.fp8.SCALING``), so the GEMM kernels are the same; the three keyword arguments configure "delayed"."""
     global _FP8_RECIPE, _WEIGHT_GEN
-    assert recipe in (None, "", "mxfp8", "tensorwise"), f"unsupported fp8 recipe {recipe!r}"
+    assert recipe in (None, "") + FP8_RECIPES, f"unsupported fp8 recipe {recipe!r}"
     _FP8_RECIPE = recipe or None
-    # "tensorwise": one power-of-two scale per tensor, stored in the MXFP8 layout, so the GEMMs are the same kernels
     from . import fp8
 
+    fp8.SCALING = recipe or "mxfp8"
     fp8.TENSORWISE = recipe == "tensorwise"
+    fp8.DELAYED = fp8.DelayedScaling(amax_history_len, amax_compute_algo, margin) if recipe == "delayed" else None
     _WEIGHT_GEN += 1        # quantised weights cached elsewhere (expert weights) are keyed on this counter
     _W_CACHE.clear()
     _ACT_CACHE.clear()
@@ -58,14 +65,24 @@ def bump_weight_generation() -> None:
     _ACT_CACHE.clear()
 
 
-def _quantized(t: torch.Tensor, direction: str, single_use: bool = False):
-    """(values, scales) of ``t`` quantised along ``direction`` ("row": blocks along the last dim, "col": along dim 0)."""
+def roll_fp8_scales(group=None) -> None:
+    """Once per optimizer step under the "delayed" recipe: record the step's maxima and derive the next scales."""
+    from . import fp8
+
+    if fp8.DELAYED is not None:
+        fp8.DELAYED.roll(group)
+
+
+def _quantized(t: torch.Tensor, direction: str, single_use: bool = False, role=None):
+    """(values, scales) of ``t`` quantised along ``direction`` ("row": blocks along the last dim, "col": along dim 0).
+    ``role``: (weight id, "x" | "dy") of an activation / gradient operand, the key of its delayed-scaling history."""
     from . import fp8
 
     if isinstance(t, torch.nn.Parameter) or getattr(t, "_is_weight", False):
         hit = _W_CACHE.get(id(t))
         if hit is None or hit[0] != _WEIGHT_GEN or hit[1] != t.data_ptr():
-            hit = (_WEIGHT_GEN, t.data_ptr(), fp8.quantize_mxfp8(t.detach(), True, True))
+            hit = (_WEIGHT_GEN, t.data_ptr(),
+                   fp8.quantize_mxfp8(t.detach(), True, True, is_weight=True, slot_key=(id(t), "w")))
             _W_CACHE[id(t)] = hit
         q = hit[2]
     else:
@@ -77,7 +94,7 @@ def _quantized(t: torch.Tensor, direction: str, single_use: bool = False):
                 break
         if q is None:
             both = not torch.is_grad_enabled() and not single_use   # backward pass: a gradient feeds two GEMMs
-            q = fp8.quantize_mxfp8(t, both or direction == "row", both or direction == "col")
+            q = fp8.quantize_mxfp8(t, both or direction == "row", both or direction == "col", slot_key=role)
             _ACT_CACHE.insert(0, (key, t, q))
             del _ACT_CACHE[4:]
     return (q.q_row, q.sf_row) if direction == "row" else (q.q_col, q.sf_col)
@@ -120,8 +137,10 @@ def gemm(
     accumulate: bool = False,
     max_ctas: int = 0,
     fp8: bool | None = None,
+    fp8_key=None,
 ) -> torch.Tensor:
-    """D[M,N] (+)= A . B^T with fp32 accumulation. See module docstring for layouts."""
+    """D[M,N] (+)= A . B^T with fp32 accumulation. See module docstring for layouts.  ``fp8_key``: identity of the
+    weight this GEMM belongs to when it is not operand B (weight-gradient GEMMs), for delayed scaling."""
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
@@ -157,8 +176,11 @@ def gemm(
         return out
     mode = 0 if out_dtype == torch.bfloat16 else (2 if accumulate else 1)
     if fp8 is not False and _fp8_eligible(a, b, out, M, N, K):
-        aq, asf = _quantized(a, "col" if a_mn else "row")
-        bq, bsf = _quantized(b, "col" if b_mn else "row", single_use=a_mn and b_mn)  # wgrad: B is the saved input
+        # operand roles (delayed scaling keeps one history per weight and role): fprop x . W, dgrad dy . W, wgrad dy . x
+        wid = fp8_key if fp8_key is not None else id(b)
+        aq, asf = _quantized(a, "col" if a_mn else "row", role=(wid, "x" if not (a_mn or b_mn) else "dy"))
+        bq, bsf = _quantized(b, "col" if b_mn else "row", single_use=a_mn and b_mn,   # wgrad: B is the saved input
+                             role=(wid, "x"))
         from . import fp8 as _fp8
 
         _fp8.launch_gemm(aq, asf, bq, bsf, out, M, N, K, a_mn, b_mn, mode, None, max_ctas)
@@ -237,7 +259,7 @@ WGRAD_STORE = WGradStore()
 
 def _wgrad_into_main_grad(dy2, x2, weight):
     gemm(dy2, x2, a_mn=True, b_mn=True, out=weight.main_grad, accumulate=True,
-         fp8=False if getattr(weight, "_fp8_exempt", False) else None)
+         fp8=False if getattr(weight, "_fp8_exempt", False) else None, fp8_key=id(weight))
     weight.grad_added_to_main_grad = True
     cb = getattr(weight, "_grad_ready_cb", None)
     if cb is not None:
@@ -254,7 +276,7 @@ def wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
         return None
     if dy2.is_cuda:
         return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype,
-                    fp8=False if getattr(weight, "_fp8_exempt", False) else None)
+                    fp8=False if getattr(weight, "_fp8_exempt", False) else None, fp8_key=id(weight))
     return (dy2.float().t() @ x2.float()).to(weight.dtype)
 
 

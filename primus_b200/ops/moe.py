@@ -298,7 +298,8 @@ def _quantized_expert_weight(w):
     hit = _EXPERT_W_CACHE.get(id(w))
     if hit is None or hit[0] != gen or hit[1] != w.data_ptr():
         E, N, K = w.shape
-        hit = (gen, w.data_ptr(), fp8.quantize_mxfp8(w.detach().view(E * N, K), True, True))
+        hit = (gen, w.data_ptr(), fp8.quantize_mxfp8(w.detach().view(E * N, K), True, True, is_weight=True,
+                                                         slot_key=(id(w), "w")))
         _EXPERT_W_CACHE[id(w)] = hit
     return hit[2]
 
@@ -315,8 +316,8 @@ def grouped_wgrad(dy, x, w, sched: Schedule, dyq=None):
         from . import fp8
 
         if dyq is None or dyq.q_col is None:
-            dyq = fp8.quantize_mxfp8(dy.contiguous(), False, True)
-        xq = fp8.quantize_mxfp8(x, False, True)
+            dyq = fp8.quantize_mxfp8(dy.contiguous(), False, True, slot_key=(id(w), "dy"))
+        xq = fp8.quantize_mxfp8(x, False, True, slot_key=(id(w), "x"))
         _lib.call("grouped_gemm_mxfp8", 2, dyq.q_col, dyq.sf_col, xq.q_col, xq.sf_col, tgt, x.shape[0], N, K, E,
                   sched.mblock_expert, sched.row_start, sched.padded, int(mg is not None), _lib.status_word(x.device))
     else:
@@ -341,7 +342,7 @@ class GroupedLinearFn(torch.autograd.Function):
         if ctx.fp8:
             from . import fp8
 
-            xq = fp8.quantize_mxfp8(x, True, False)
+            xq = fp8.quantize_mxfp8(x, True, False, slot_key=(id(w), "x"))
             wq = _quantized_expert_weight(w)
             _lib.call("grouped_gemm_mxfp8", 0, xq.q_row, xq.sf_row, wq.q_row, wq.sf_row, out, x.shape[0], N, K, E,
                       sched.mblock_expert, sched.row_start, sched.padded, 0, _lib.status_word(x.device))
@@ -363,7 +364,7 @@ class GroupedLinearFn(torch.autograd.Function):
         if ctx.fp8:
             from . import fp8
 
-            dyq = fp8.quantize_mxfp8(dy, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+            dyq = fp8.quantize_mxfp8(dy, ctx.needs_input_grad[0], ctx.needs_input_grad[1], slot_key=(id(w), "dy"))
             if ctx.needs_input_grad[0]:
                 wq = _quantized_expert_weight(w)
                 dx = torch.empty_like(x)

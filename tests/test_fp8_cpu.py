@@ -64,3 +64,81 @@ def test_tensorwise_recipe_uses_one_power_of_two_scale():
     finally:
         gemm.set_fp8_recipe(None)
     assert not fp8.TENSORWISE
+
+
+def test_blockwise_recipe_scales_vectors_of_128_and_weight_tiles():
+    """fp8_recipe blockwise: an activation takes one exponent per 1 x 128 vector along the reduced dimension (row
+    direction: along columns; column direction: along rows), a weight one per 128 x 128 tile; the four 32-blocks a
+    vector covers carry the same exponent."""
+    torch.manual_seed(0)
+    x = (torch.randn(256, 384) * torch.exp(torch.randn(256, 1) * 2)).bfloat16()
+    q = fp8.quantize_mxfp8_ref(x, True, True, scaling="blockwise")
+    R, C = x.shape
+    r = torch.arange(R)[:, None].expand(R, C // 32)
+    kb = torch.arange(C // 32)[None, :].expand(R, C // 32)
+    e_row = q.sf_row[fp8.sf_offsets(r, kb, C // 128).reshape(-1)].view(R, C // 128, 4)
+    assert (e_row == e_row[..., :1]).all()
+    want = fp8._e8m0(x.float().abs().view(R, C // 128, 128).amax(-1))
+    assert torch.equal(e_row[..., 0].int(), want)
+    d = fp8.dequantize_mxfp8_ref(q.q_row, q.sf_row, False)
+    assert ((d - x.float()).abs() <= x.float().abs().view(R, C // 128, 128).amax(-1).repeat_interleave(128, 1) * 0.0626 / 1.0).all()
+    # column direction: vectors of 128 rows
+    c = torch.arange(C)[None, :].expand(R // 32, C)
+    rb = torch.arange(R // 32)[:, None].expand(R // 32, C)
+    e_col = q.sf_col[fp8.sf_offsets(c, rb, R // 128).reshape(-1)].view(R // 128, 4, C)
+    assert (e_col == e_col[:, :1]).all()
+    assert torch.equal(e_col[:, 0].int(), fp8._e8m0(x.float().abs().view(R // 128, 128, C).amax(1)))
+    # weights: one exponent per tile, identical in both directions
+    w = fp8.quantize_mxfp8_ref(x, True, True, scaling="blockwise", is_weight=True)
+    e_tile = fp8._e8m0(x.float().abs().view(R // 128, 128, C // 128, 128).amax((1, 3)))
+    e_row_w = w.sf_row[fp8.sf_offsets(r, kb, C // 128).reshape(-1)].view(R // 128, 128, C // 128, 4)
+    assert (e_row_w.int() == e_tile[:, None, :, None]).all()
+    assert torch.equal(fp8.dequantize_mxfp8_ref(w.q_row, w.sf_row, False), fp8.dequantize_mxfp8_ref(w.q_col, w.sf_col, True))
+
+
+def test_delayed_scaling_history_and_fallback():
+    """fp8_recipe delayed: the first quantisation of a role falls back to the current maximum; after a roll the scale
+    comes from the history (most recent or maximum over ``history_len`` steps, times 2^margin); values beyond the
+    predicted range saturate; a slot that was not used keeps its history."""
+    from primus_b200.ops import gemm
+
+    torch.manual_seed(0)
+    x = torch.randn(128, 256).bfloat16()
+    try:
+        gemm.set_fp8_recipe("delayed", amax_history_len=3, amax_compute_algo="max", margin=1)
+        st = fp8.DELAYED
+        q0 = fp8.quantize_mxfp8(x, True, False, slot_key=("w0", "x"))
+        assert torch.equal(q0.sf_row, fp8.quantize_mxfp8_ref(x, True, False, scaling="tensorwise").sf_row)
+        slot = st.slots[("w0", "x")]
+        assert st.amax_now[slot].item() == x.float().abs().max().item()
+        fp8.quantize_mxfp8(x * 0.25, True, False, slot_key=("w0", "x"))           # a second micro-batch: max is kept
+        assert st.amax_now[slot].item() == x.float().abs().max().item()
+        gemm.roll_fp8_scales()
+        amax1 = x.float().abs().max().item()
+        assert st.scale_amax[slot].item() == 2 * amax1 and st.amax_now[slot].item() == 0
+        # step 2: an 8x larger tensor is scaled by the *old* maximum (x 2 margin) and saturates
+        big = (x.float() * 8).bfloat16()
+        q1 = fp8.quantize_mxfp8(big, True, False, slot_key=("w0", "x"))
+        e_used = int(q1.sf_row[0])
+        assert e_used == fp8._e8m0(torch.tensor([2 * amax1])).item()
+        assert (q1.q_row.view(torch.float8_e4m3fn).float().abs() == 448).any()
+        gemm.roll_fp8_scales()
+        assert st.scale_amax[slot].item() == 2 * big.float().abs().max().item()      # "max" over the history
+        # step 3: not used -> history stays; step 4: small tensor, the maximum of the history still rules
+        gemm.roll_fp8_scales()
+        assert st.history[0, slot].item() == big.float().abs().max().item()
+        fp8.quantize_mxfp8((x.float() * 0.01).bfloat16(), True, False, slot_key=("w0", "x"))
+        gemm.roll_fp8_scales()
+        assert st.scale_amax[slot].item() == 2 * big.float().abs().max().item()
+        # a tensor without a role is scaled by its current maximum
+        q = fp8.quantize_mxfp8(x, True, False)
+        assert torch.equal(q.sf_row, q0.sf_row)
+        # most_recent picks the last rolled value
+        gemm.set_fp8_recipe("delayed", amax_history_len=4, amax_compute_algo="most_recent")
+        for s in (1.0, 4.0, 0.5):
+            fp8.quantize_mxfp8((x.float() * s).bfloat16(), True, False, slot_key="k")
+            gemm.roll_fp8_scales()
+        assert fp8.DELAYED.scale_amax[fp8.DELAYED.slots["k"]].item() == (x.float() * 0.5).bfloat16().float().abs().max().item()
+    finally:
+        gemm.set_fp8_recipe(None)
+    assert fp8.DELAYED is None and fp8.SCALING == "mxfp8"

@@ -39,6 +39,50 @@ def test_tensorwise_quantiser_matches_reference_bitwise(R, C):
     assert only_row.q_col is None and torch.equal(only_row.q_row, ref.q_row)
 
 
+@pytest.mark.parametrize("R,C", [(128, 128), (512, 384), (2048, 1024)])
+@pytest.mark.parametrize("is_weight", [False, True])
+def test_blockwise_quantiser_matches_reference_bitwise(R, C, is_weight):
+    """One power-of-two scale per 1 x 128 vector (activations) or 128 x 128 tile (weights), MXFP8 storage layout."""
+    torch.manual_seed(2)
+    x = (torch.randn(R, C, device="cuda") * torch.exp(torch.randn(R, 1, device="cuda") * 2)).bfloat16()
+    x[3, 0:128] = 0
+    q = fp8.quantize_mxfp8(x, True, True, scaling="blockwise", is_weight=is_weight)
+    ref = fp8.quantize_mxfp8_ref(x, True, True, scaling="blockwise", is_weight=is_weight)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for name in ("q_row", "sf_row", "q_col", "sf_col"):
+        assert torch.equal(getattr(q, name), getattr(ref, name)), name
+    only_col = fp8.quantize_mxfp8(x, False, True, scaling="blockwise", is_weight=is_weight)
+    assert only_col.q_row is None and torch.equal(only_col.q_col, ref.q_col)
+
+
+def test_delayed_quantiser_uses_history_and_records_the_maximum():
+    from primus_b200.ops import gemm
+
+    torch.manual_seed(3)
+    x = torch.randn(512, 256, device="cuda").bfloat16()
+    try:
+        gemm.set_fp8_recipe("delayed", amax_history_len=2, amax_compute_algo="max")
+        st = fp8.DELAYED
+        q0 = fp8.quantize_mxfp8(x, True, True, slot_key="a")                 # empty history: current maximum
+        ref0 = fp8.quantize_mxfp8_ref(x, True, True, scaling="tensorwise")
+        assert torch.equal(q0.q_row, ref0.q_row) and torch.equal(q0.sf_col, ref0.sf_col)
+        slot = st.slots["a"]
+        assert st.amax_now[slot].item() == x.float().abs().max().item()
+        gemm.roll_fp8_scales()
+        big = (x.float() * 16).bfloat16()
+        q1 = fp8.quantize_mxfp8(big, True, True, slot_key="a")               # scaled by the previous step's maximum
+        ref1 = fp8.quantize_mxfp8_ref(big, True, True, scaling="delayed", scale_amax=st.scale_amax[slot])
+        for name in ("q_row", "sf_row", "q_col", "sf_col"):
+            assert torch.equal(getattr(q1, name), getattr(ref1, name)), name
+        assert (q1.q_row.view(torch.float8_e4m3fn).float().abs() == 448).any()
+        assert st.amax_now[slot].item() == big.float().abs().max().item()
+        torch.cuda.synchronize()
+        _lib.check_status()
+    finally:
+        gemm.set_fp8_recipe(None)
+
+
 def _ref_gemm(aq, asf, a_col, bq, bsf, b_col, a_mn, b_mn):
     A = fp8.dequantize_mxfp8(aq, asf, a_col)
     B = fp8.dequantize_mxfp8(bq, bsf, b_col)
@@ -113,7 +157,8 @@ def test_model_training_with_mxfp8_recipe_tracks_bf16():
     ps.initialize_model_parallel()
     losses = {}
     try:
-        for recipe, kind in ((None, "mxfp8"), ("e4m3", "mxfp8"), ("e4m3", "tensorwise")):
+        for recipe, kind in ((None, "mxfp8"), ("e4m3", "mxfp8"), ("e4m3", "tensorwise"), ("e4m3", "blockwise"),
+                             ("e4m3", "delayed")):
             mc = TransformerConfig(num_layers=2, hidden_size=256, ffn_hidden_size=512, num_attention_heads=2,
                                    num_query_groups=2, vocab_size=1024, params_dtype="bf16", seq_length=256, fp8=recipe,
                                    fp8_recipe=kind)
@@ -130,6 +175,9 @@ def test_model_training_with_mxfp8_recipe_tracks_bf16():
     a, b, c = losses[(None, "mxfp8")], losses[("e4m3", "mxfp8")], losses[("e4m3", "tensorwise")]
     assert all(abs(x - y) <= 0.02 * abs(x) for x, y in zip(a, b)), (a, b)
     assert all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, c)), (a, c)
+    for kind in ("blockwise", "delayed"):
+        d = losses[("e4m3", kind)]
+        assert all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, d)), (kind, a, d)
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024)])

@@ -425,6 +425,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // Resolves cuTensorMapEncodeTiled through the runtime so the library needs no link against libcuda.
+// SM count of the current device (148 on B200), read once per process.
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 inline EncodeTiledFn get_encode_fn() {
   // Driver entry points need a current context on the calling thread; threads created by the
   // framework (e.g. the autograd engine's) may not have touched the runtime yet.

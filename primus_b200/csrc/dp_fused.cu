@@ -161,7 +161,8 @@ int pb_dp_adamw_allgather(const long* param_ptrs, int dp, int rank, long offset,
   if (n == 0) return 0;
   const PeerPtrs p = make_ptrs(nullptr, param_ptrs, dp);
   long blocks = (n / 4 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long cap = (long)pbh::sm_count() * 8;      // 8 resident CTAs of 256 threads per SM
+  if (blocks > cap) blocks = cap;
   dp_adamw_allgather_kernel<<<(int)blocks, 256, 0, s>>>(p, dp, rank, offset, n, master, m, v, grad, lr, beta1, beta2,
                                                        eps, wd, bc1, bc2, grad_scale, skip);
   return (int)cudaGetLastError();

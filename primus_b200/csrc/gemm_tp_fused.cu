@@ -5,19 +5,20 @@
 //
 // The grid is split into `comm_ctas` communication CTAs and GEMM CTAs that run concurrently:
 //
-//  AG: communication CTAs pull the peers' activation shards with plain 16-byte P2P loads into a *local*
-//      gather buffer, one source rank after the other (own shard first, then rank+1, ...), and publish a
-//      per-chunk counter.  GEMM CTAs walk the output tiles in the same chunk order; their TMA producer
+//  AG: communication CTAs pull the peers' activation shards with non-multicast bulk copies (peer global ->
+//      shared ring -> local global) into a *local* gather buffer, one source rank after the other (own shard
+//      first, then rank+1, ...), and publish a per-chunk counter.  GEMM CTAs walk the output tiles in the same chunk order; their TMA producer
 //      waits (bounded) for the chunk counter and then loads A tiles from local memory, so every remote
 //      byte crosses NVLink exactly once and the transfer of chunk k+1 overlaps the math of chunk k.
 //  RS: GEMM CTAs compute the partial product tile by tile in destination order (rank+1 first, own rows
 //      last) and write it with TMA into a local symmetric partial buffer; the CTA that completes the
 //      last tile of a chunk raises a flag in the destination rank's memory.  Communication CTAs of the
-//      destination wait for those flags, pull the peers' partial rows over NVLink as they become ready,
-//      accumulate in fp32 and finally add their own partial and write the bf16 result.
+//      destination wait for those flags, pull the peers' partial rows over NVLink in arrival order, sum
+//      them (fp32 in registers, pairs of sources per pass) into a bf16 accumulator that is handed over per
+//      128-row block, and the GEMM epilogue of the own tiles adds it by TMA and writes the bf16 result.
 //
 // No TMA load ever targets peer memory with cluster multicast (none is used at all); peer data is
-// moved by ordinary loads of the communication CTAs.  Every wait (mbarrier, chunk counter, peer flag)
+// moved by the communication CTAs (bulk copies without multicast, plain loads for the summing passes).  Every wait (mbarrier, chunk counter, peer flag)
 // is bounded and reports through the status word.  Flags and counters are epoch based (monotonic), so
 // nothing has to be cleared between calls.
 //
@@ -742,8 +743,11 @@ extern "C" int pb_gemm_tp_fused(int mode, int tp, int rank, int epoch, int comm_
   memset(&a, 0, sizeof(a));
   a.mode = mode; a.tp = tp; a.rank = rank; a.epoch = epoch; a.comm_ctas = comm_ctas;
   {
-    const char* e = getenv("PRIMUS_B200_RS_TEST_REPEAT");
-    a.rs_test_repeat = (e && e[0] == '1') ? 1 : 0;
+    static const int rs_test_repeat = [] {          // read once per process: a test hook, not a tuning knob
+      const char* e = getenv("PRIMUS_B200_RS_TEST_REPEAT");
+      return (e && e[0] == '1') ? 1 : 0;
+    }();
+    a.rs_test_repeat = rs_test_repeat;
   }
   a.rows_per_chunk = M / tp;
   a.M = M; a.N = N; a.K = K;

@@ -143,15 +143,34 @@ def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):
         raise _lib.NativeLibraryError(f"pb_gemm_tp_fused failed with code {rc}")
 
 
+_FALLBACK_LOGGED: set = set()
+
+
+def _note_fallback(kind: str, reason: str) -> None:
+    """One log line per (kernel, reason) when a fused kernel was requested and the NCCL composition runs instead."""
+    if (kind, reason) not in _FALLBACK_LOGGED:
+        _FALLBACK_LOGGED.add((kind, reason))
+        import logging
+
+        logging.getLogger("primus_b200").warning("fused %s requested but not used: %s; running NCCL + GEMM", kind, reason)
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            print(f"[fused-tp] {kind} requested but not used: {reason}; running NCCL + GEMM", flush=True)
+
+
 def ag_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: bool = True):
     """Returns (all_gather(x_shard) @ W^T, gathered x). ``w``: [N, K] or, with ``b_mn``, [K, N]."""
     tp = dist.get_world_size(group)
     Tl, K = x_shard.shape
     M = Tl * tp
     N = w.shape[1] if b_mn else w.shape[0]
-    # the fused kernels are bf16: under an MXFP8 recipe the collective stays on NCCL and the GEMM runs in MXFP8
-    fused = fused and gemm_ops.fp8_recipe() is None
+    # the fused kernels are bf16: under an FP8 recipe the collective stays on NCCL and the GEMM runs in FP8
+    if fused and gemm_ops.fp8_recipe() is not None:
+        _note_fallback("all-gather -> GEMM", f"the fused kernel is bf16 and fp8_recipe is {gemm_ops.fp8_recipe()!r}")
+        fused = False
     ctx = get_context(group) if (fused and x_shard.is_cuda) else None
+    if fused and x_shard.is_cuda and (ctx is None or not ctx.supported(M, N, K)):
+        _note_fallback("all-gather -> GEMM", "no peer-memory context for this group" if ctx is None else
+                       f"shape M={M} N={N} K={K} is not supported")
     if ctx is None or not ctx.supported(M, N, K):
         g = tpc.all_gather_dim0(x_shard, group)
         return gemm_ops.gemm(g, w, b_mn=b_mn), g
@@ -167,9 +186,15 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: 
     tp = dist.get_world_size(group)
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
-    fused = fused and gemm_ops.fp8_recipe() is None
+    if fused and gemm_ops.fp8_recipe() is not None:
+        _note_fallback("GEMM -> reduce-scatter", f"the fused kernel is bf16 and fp8_recipe is {gemm_ops.fp8_recipe()!r}")
+        fused = False
     ctx = get_context(group) if (fused and x.is_cuda) else None
     # N % 128: accumulator pieces are whole fractions of a 128-row block; at most 256 row blocks per rank
+    if fused and x.is_cuda and (ctx is None or not ctx.supported(M, N, K) or N % 128 or M // tp > 32768
+                                or not x.is_contiguous()):
+        _note_fallback("GEMM -> reduce-scatter", "no peer-memory context for this group" if ctx is None else
+                       f"shape M={M} N={N} K={K} is not supported")
     if ctx is None or not ctx.supported(M, N, K) or N % 128 or M // tp > 32768 or not x.is_contiguous():
         return tpc.reduce_scatter_dim0(gemm_ops.gemm(x, w, b_mn=b_mn), group)
     inst = ctx.instance(1, M, N, K)

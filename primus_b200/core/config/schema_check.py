@@ -40,12 +40,9 @@ INERT_KEYS = {
     "weight_deosc_ratio", "sft_grad_sanitize", "sft_pack_cache_dir", "trainable", "mlflow_run_name",
     "log_throughput", "log_timers_to_tensorboard", "torch_profiler_record_shapes", "torch_profiler_use_gzip",
     "torch_profiler_with_stack", "use_tp_pp_dp_mapping", "offload_ops",
-    # zero-bubble runtime knobs of the reference's second pipeline implementation (the schedule is chosen with
-    # pp_algorithm / pipeline_schedule here)
-    "enable_zero_bubble", "patch_primus_pipeline", "patch_zero_bubble", "pp_communication_method",
-    "zero_bubble_adaptive_memory_limit_percentile", "zero_bubble_max_pending_backward",
-    "zero_bubble_pipeline_timers_end_iter", "zero_bubble_pipeline_timers_start_iter", "zero_bubble_v_schedule",
-    "zero_bubble_v_schedule_mem_setup",
+    # switches between the reference's two pipeline implementations (one runtime here; the schedule is chosen with
+    # pp_algorithm / pipeline_schedule or enable_zero_bubble + zero_bubble_v_schedule)
+    "patch_primus_pipeline", "patch_zero_bubble", "pp_communication_method",
 }
 
 

@@ -118,6 +118,12 @@ class TrainConfig:
     eval_interval: Optional[int] = None
     eval_iters: int = 0
     pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv | v-half | v-min
+    # cost-driven re-planning of the B / W-split schedules: node times (and, on GPUs, activation bytes) are measured in
+    # iterations [start, end) and the table for the following iterations is built from them (end <= start: off)
+    zero_bubble_pipeline_timers_start_iter: int = 0
+    zero_bubble_pipeline_timers_end_iter: int = 0
+    zero_bubble_adaptive_memory_limit_percentile: float = 85.0   # share of device memory the plan may fill
+    zero_bubble_max_pending_backward: object = "auto"   # int: activation budget per rank in forwards instead of adaptive
     pipeline_model_parallel_layout: Optional[str] = None
     decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
@@ -144,6 +150,10 @@ class TrainConfig:
         kw = {k: v for k, v in d.items() if k in names}
         if "pipeline_schedule" not in d and d.get("pp_algorithm"):
             kw["pipeline_schedule"] = d["pp_algorithm"]
+        if "pipeline_schedule" not in d and not d.get("pp_algorithm") and d.get("enable_zero_bubble"):
+            # the reference's switches: enable_zero_bubble (+ zero_bubble_v_schedule, ..._mem_setup zb | half | min)
+            v = {"zb": "zbv", "half": "v-half", "min": "v-min"}[str(d.get("zero_bubble_v_schedule_mem_setup", "zb"))]
+            kw["pipeline_schedule"] = v if d.get("zero_bubble_v_schedule") else "zerobubble"
         if d.get("tp_comm_overlap"):
             from ..parallel import fused_tp
 
@@ -569,12 +579,23 @@ class Trainer:
             from ..parallel.pipeline import run_pipeline_schedule
 
             timeline = None
-            if self.tcfg.dump_pp_data and self.st.dp_rank == 0 and self.st.tp_rank == 0:
+            it = self.iteration + 1
+            t0_, t1_ = self.tcfg.zero_bubble_pipeline_timers_start_iter, self.tcfg.zero_bubble_pipeline_timers_end_iter
+            measuring = t1_ > t0_ and t0_ <= it < t1_
+            if (self.tcfg.dump_pp_data and self.st.dp_rank == 0 and self.st.tp_rank == 0) or measuring:
                 from ..parallel.pipeline import PipelineTimeline
 
                 timeline = PipelineTimeline()
             loss = run_pipeline_schedule(self, micro_batches, timeline)
-            if timeline is not None:
+            if measuring:
+                self._pp_measured = getattr(self, "_pp_measured", []) + timeline.events
+                if it == t1_ - 1:
+                    from ..parallel.pipeline import replan_from_measurements
+
+                    self.pp_replan_report = replan_from_measurements(self, self._pp_measured, len(micro_batches),
+                                                                     self.log if (not dist.is_initialized() or dist.get_rank() == 0) else None)
+                    self._pp_measured = []
+            if timeline is not None and self.tcfg.dump_pp_data and self.st.dp_rank == 0 and self.st.tp_rank == 0:
                 d = self.tcfg.pp_dump_dir or os.path.join(self.tcfg.save or ".", "pp_data")
                 timeline.dump(os.path.join(d, f"pp_rank{self.st.pp_rank}_iter{self.iteration + 1}.json"), self.st.pp_rank,
                               self.iteration + 1, {"schedule": self.tcfg.pipeline_schedule, "pp": self.st.pp})

@@ -32,8 +32,14 @@ class PipelineTimeline:
     def __init__(self):
         self.events = []
 
-    def add(self, node, t0, t1):
-        self.events.append({"kind": node.kind, "mb": node.mb, "chunk": node.chunk, "start": t0, "end": t1})
+    def add(self, node, t0, t1, compute_start=None, mem_delta=None):
+        """``compute_start``: when the node's input had arrived (``start`` .. ``compute_start`` is time spent waiting
+        for the neighbouring stage); ``mem_delta``: bytes the node left allocated (activations a forward keeps)."""
+        ev = {"kind": node.kind, "mb": node.mb, "chunk": node.chunk, "start": t0, "end": t1,
+              "compute_start": t0 if compute_start is None else compute_start}
+        if mem_delta is not None:
+            ev["mem_delta"] = mem_delta
+        self.events.append(ev)
 
     def dump(self, path: str, pp_rank: int, iteration: int, extra: dict | None = None) -> None:
         """One JSON file per (rank, iteration); ``primus_b200.tools.pp_vis`` merges them."""
@@ -68,7 +74,7 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
     m = len(micro_batches)
     key = (trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp)
     cache = getattr(trainer, "_pp_schedule_cache", {})
-    if key not in cache:
+    if key not in cache:   # (a cost-driven table from ``replan_from_measurements`` replaces the entry later)
         algo = trainer.tcfg.pipeline_schedule
         if st.virtual_pp and st.virtual_pp > 1 and algo == "1f1b":
             algo = "interleaved"
@@ -98,6 +104,8 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
         if forward_only and node.kind != "F":
             continue
         t0 = time.perf_counter() if timeline is not None else 0.0
+        t_in = None
+        mem0 = torch.cuda.memory_allocated(dev) if (timeline is not None and trainer.is_cuda) else 0
         s = sched.stage_of(r, node.chunk, pp, placement)
         mb = micro_batches[node.mb]
         batch, seq = mb["tokens"].shape
@@ -113,6 +121,10 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 else:
                     x = torch.empty(_p2p_shape(trainer, batch, seq), dtype=dtype, device=dev)
                     dist.recv(x, src=global_rank(pr), group=fwd_g)
+                    if timeline is not None:
+                        if trainer.is_cuda:
+                            torch.cuda.synchronize()
+                        t_in = time.perf_counter()
                 if not forward_only:
                     x.requires_grad_(True)
                     inputs[k] = x
@@ -151,6 +163,10 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 else:
                     g = torch.empty_like(out)
                     dist.recv(g, src=global_rank(nr), group=bwd_g)
+                    if timeline is not None:
+                        if trainer.is_cuda:
+                            torch.cuda.synchronize()
+                        t_in = time.perf_counter()
                 torch.autograd.backward(out, g)
             if split_w and node.kind == "B":
                 gemm_ops.WGRAD_STORE.end()
@@ -166,13 +182,61 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
         if timeline is not None:
             if trainer.is_cuda:
                 torch.cuda.synchronize()
-            timeline.add(node, t0, time.perf_counter())
+            mem1 = torch.cuda.memory_allocated(dev) if trainer.is_cuda else 0
+            timeline.add(node, t0, time.perf_counter(), t_in, (mem1 - mem0) if trainer.is_cuda else None)
     for h, _keep in sends:
         h.wait()
     gemm_ops.WGRAD_STORE.flush_all()
     for buf in trainer.buffers:
         buf.is_last_microbatch = True
     return total
+
+
+def replan_from_measurements(trainer, events: list[dict], num_microbatches: int, log=None) -> dict | None:
+    """Cost-driven re-planning of a B / W-split schedule: gathers the timeline events every pipeline rank recorded in
+    the measurement window, derives per-stage F / B / W times (waiting for the neighbour excluded) and, on GPUs, an
+    activation budget from the bytes a forward leaves allocated and the memory still free under
+    ``zero_bubble_adaptive_memory_limit_percentile`` of the device, and installs the table ``auto_schedule`` picks for
+    the following iterations.  Every rank computes the same table from the same gathered data.  Returns the
+    scheduler's report (None when the schedule has no B / W split).  Role of the reference's zero-bubble runtime
+    timers + scheduler (primus/backends/megatron/core/pipeline_parallel/zerobubble/runtime.py,
+    scheduler/{zb,zbv}.py: ``zero_bubble_pipeline_timers_start_iter / end_iter``,
+    ``zero_bubble_adaptive_memory_limit_percentile``, ``zero_bubble_max_pending_backward``)."""
+    st = trainer.st
+    pp, m = st.pp, num_microbatches
+    algo = trainer.tcfg.pipeline_schedule.lower().replace("_", "-")
+    if algo not in ("zerobubble", "zero-bubble", "zb", "zbb", "zbv", "zbv-formatted", "zbv-greedy", "v-half", "v-min"):
+        return None
+    chunks, placement, base = sched.default_budget(algo, pp)
+    mine = {"events": events, "limit": None}
+    if trainer.is_cuda:
+        fwd = [e["mem_delta"] for e in events if e["kind"] == "F" and e.get("mem_delta", 0) > 0]
+        if fwd:
+            act = sum(fwd) / len(fwd)
+            total = torch.cuda.get_device_properties(trainer.device).total_memory
+            pct = float(getattr(trainer.tcfg, "zero_bubble_adaptive_memory_limit_percentile", 85)) / 100.0
+            peak = torch.cuda.max_memory_allocated(trainer.device)
+            # what the measured steps needed beyond their activations stays reserved; the rest may hold activations
+            static = max(0.0, peak - base[st.pp_rank] * act)
+            mine["limit"] = max(float(chunks) + 1.0, (pct * total - static) / act)
+    gathered = [None] * pp
+    dist.all_gather_object(gathered, mine, group=st.pp_group)
+    costs = sched.costs_from_events([g["events"] for g in gathered], pp, chunks, placement)
+    if all(g["limit"] is not None for g in gathered):
+        costs.mem_limit = [float(g["limit"]) for g in gathered]
+    manual = getattr(trainer.tcfg, "zero_bubble_max_pending_backward", "auto")
+    if manual not in (None, "auto"):       # manual activation budget, in forwards per rank
+        costs.mem_limit = [float(int(manual))] * pp
+    report = sched.auto_schedule(algo, pp, m, costs)
+    cache = getattr(trainer, "_pp_schedule_cache", {})
+    cache[(trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp)] = report
+    trainer._pp_schedule_cache = cache
+    if log is not None:
+        log(f"[pipeline] cost-driven schedule: {report['picked']}; simulated step {report['makespan']:.4g} vs "
+            f"{report['fixed_makespan']:.4g} for the fixed table (F {[round(x, 4) for x in costs.f]}, "
+            f"B {[round(x, 4) for x in costs.b]}, W {[round(x, 4) for x in costs.w]}); peak activations "
+            f"{report['peak_activations']}")
+    return report
 
 
 def pipeline_warmup(trainer, micro_batch: dict) -> None:

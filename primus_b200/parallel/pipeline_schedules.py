@@ -14,13 +14,29 @@ Algorithms (primus/core/pipeline_parallel/scheduler/algorithms/*.py in the refer
 * ``zerobubble``    B/W split, W fills the bubbles (zerobubble.py:52-213)
 * ``zbv`` / ``v-half`` / ``v-min``   V-shaped placement of two chunks per rank (chunk 1 runs the stages in
                     reverse rank order) with decreasing activation-memory budgets (zbv_greedy.py)
-The last four are produced by one dependency-driven greedy list scheduler with unit costs, so every
-table is valid by construction; ``validate`` re-checks any table independently.
+The last four are produced by one dependency-driven greedy list scheduler, so every table is valid by
+construction; ``validate`` re-checks any table independently.  The scheduler and the timeline simulator take
+per-stage costs of F, B and W and a transfer cost, and ``auto_schedule`` searches activation budgets and
+deferred-W limits for the table with the shortest simulated makespan under a memory limit -- the role of the
+reference's cost-driven zero-bubble scheduler, which re-plans from the F / B / W / communication times it
+measures between ``zero_bubble_pipeline_timers_start_iter`` and ``..._end_iter``
+(primus/backends/megatron/core/pipeline_parallel/zerobubble/scheduler/{zb,zbv,graph}.py, runtime.py timers).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Optional
+from dataclasses import dataclass, field
+from typing import Optional, Sequence, Union
+
+Cost = Union[float, Sequence[float]]
+
+
+def _per_stage(c: Cost, S: int) -> list[float]:
+    """A scalar cost, or one value per (virtual) stage."""
+    if isinstance(c, (int, float)):
+        return [float(c)] * S
+    c = [float(x) for x in c]
+    assert len(c) == S, f"expected {S} per-stage costs, got {len(c)}"
+    return c
 
 
 @dataclass(frozen=True)
@@ -94,11 +110,14 @@ def schedule_interleaved(pp: int, vpp: int, m: int) -> list[list[Node]]:
 
 # ------------------------------------------------------------------------------------------------
 def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interleaved", split_w: bool = True,
-                    max_inflight: Optional[list[float]] = None, cost_f: float = 1.0, cost_b: float = 1.0,
-                    cost_w: float = 1.0) -> list[list[Node]]:
+                    max_inflight: Optional[list[float]] = None, cost_f: Cost = 1.0, cost_b: Cost = 1.0,
+                    cost_w: Cost = 1.0, p2p: float = 0.0, max_pending_w: Optional[int] = None) -> list[list[Node]]:
     """Event-driven list scheduling.  ``max_inflight[r]``: activation budget of rank r in units of one
-    chunk-forward (a forward adds 1, its B releases ``1 - w_frac`` and its W the rest)."""
+    chunk-forward (a forward adds 1, its B releases ``1 - w_frac`` and its W the rest).  Costs are scalars or one
+    value per stage; ``p2p`` is added to a dependency that crosses ranks; ``max_pending_w`` caps the number of
+    deferred weight-gradient nodes of a rank (a further B has to wait for a W)."""
     S = pp * chunks
+    cost_f, cost_b, cost_w = _per_stage(cost_f, S), _per_stage(cost_b, S), _per_stage(cost_w, S)
     w_frac = 0.25 if split_w else 0.0
     if max_inflight is None:
         max_inflight = [float(S)] * pp
@@ -124,9 +143,12 @@ def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interlea
             for s in stages_of_rank[r]:
                 chunk = rank_of_stage(s, pp, placement)[1]
                 mb = next_b[s]
-                if mb < m and done_f[s][mb] is not None:
+                w_room = not split_w or max_pending_w is None or len(pending_w[r]) < max_pending_w
+                if mb < m and done_f[s][mb] is not None and w_room:
                     ready = done_f[s][mb] if s == S - 1 else done_b[s + 1][mb]
                     if ready is not None:
+                        if s < S - 1 and rank_of_stage(s + 1, pp, placement)[0] != r:
+                            ready += p2p
                         cands.append((max(ready, t_rank[r]), 0, -s, "B", s, mb, chunk))
                 mb = next_f[s]
                 # keep one activation slot free per deeper chunk of this rank, or shallow forwards could
@@ -135,6 +157,8 @@ def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interlea
                 if mb < m and mem[r] + 1.0 <= max_inflight[r] - reserve + 1e-9:
                     ready = 0.0 if s == 0 else done_f[s - 1][mb]
                     if ready is not None:
+                        if s > 0 and rank_of_stage(s - 1, pp, placement)[0] != r:
+                            ready += p2p
                         cands.append((max(ready, t_rank[r]), 1, -s, "F", s, mb, chunk))
             if split_w and pending_w[r]:
                 s, mb = pending_w[r][0]
@@ -150,13 +174,13 @@ def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interlea
             raise RuntimeError("deadlock while building the schedule")
         (start, _, _, kind, s, mb, chunk), r = best
         if kind == "F":
-            t_rank[r] = start + cost_f
+            t_rank[r] = start + cost_f[s]
             done_f[s][mb] = t_rank[r]
             next_f[s] += 1
             mem[r] += 1.0
             table[r].append(Node("F", mb, chunk))
         elif kind == "B":
-            t_rank[r] = start + cost_b + (0.0 if split_w else cost_w)
+            t_rank[r] = start + cost_b[s] + (0.0 if split_w else cost_w[s])
             done_b[s][mb] = t_rank[r]
             next_b[s] += 1
             mem[r] -= 1.0 - w_frac
@@ -166,7 +190,7 @@ def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interlea
             else:
                 table[r].append(Node("BW", mb, chunk))
         else:
-            t_rank[r] = start + cost_w
+            t_rank[r] = start + cost_w[s]
             pending_w[r].pop(0)
             mem[r] -= w_frac
             table[r].append(Node("W", mb, chunk))
@@ -273,10 +297,14 @@ def validate(table: list[list[Node]], pp: int, m: int, chunks: int, placement: s
     assert all(ptr[r] == len(comp[r]) for r in range(pp)), f"schedule deadlocks at {ptr}"
 
 
-def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost_f: float, cost_b: float,
-             cost_w: float, p2p: float = 0.0) -> dict:
-    """Timeline simulation: returns makespan, per-rank busy time and bubble fraction."""
+def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost_f: Cost, cost_b: Cost,
+             cost_w: Cost, p2p: float = 0.0) -> dict:
+    """Timeline simulation: returns makespan, per-rank busy time, bubble fraction and the peak number of
+    activations (in chunk-forwards; a split B keeps a quarter until its W) each rank holds."""
     S = pp * chunks
+    cost_f, cost_b, cost_w = _per_stage(cost_f, S), _per_stage(cost_b, S), _per_stage(cost_w, S)
+    mem = [0.0] * pp
+    peak = [0.0] * pp
     comp = [[n for n in seq if n.kind in ("F", "B", "W", "BW")] for seq in table]
     ptr = [0] * pp
     t = [0.0] * pp
@@ -295,7 +323,8 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                         break
                     if s > 0 and rank_of_stage(s - 1, pp, placement)[0] != r:
                         dep += p2p
-                    cost = cost_f
+                    cost = cost_f[s]
+                    mem[r] += 1.0
                 elif n.kind in ("B", "BW"):
                     if (s, n.mb) not in fdone:
                         break
@@ -304,9 +333,12 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                         break
                     if s < S - 1 and rank_of_stage(s + 1, pp, placement)[0] != r:
                         dep += p2p
-                    cost = cost_b + (cost_w if n.kind == "BW" else 0.0)
+                    cost = cost_b[s] + (cost_w[s] if n.kind == "BW" else 0.0)
+                    mem[r] -= 1.0 if n.kind == "BW" else 0.75
                 else:
-                    dep, cost = 0.0, cost_w
+                    dep, cost = 0.0, cost_w[s]
+                    mem[r] -= 0.25
+                peak[r] = max(peak[r], mem[r])
                 start = max(t[r], dep)
                 t[r] = start + cost
                 busy[r] += cost
@@ -317,4 +349,95 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                 ptr[r] += 1
                 progress = True
     makespan = max(t)
-    return {"makespan": makespan, "busy": busy, "bubble_fraction": 1.0 - sum(busy) / (pp * makespan) if makespan else 0.0}
+    return {"makespan": makespan, "busy": busy, "peak_activations": peak,
+            "bubble_fraction": 1.0 - sum(busy) / (pp * makespan) if makespan else 0.0}
+
+
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class StageCosts:
+    """Measured (or modelled) times of one micro-batch on every virtual stage, in any common unit."""
+    f: list[float]
+    b: list[float]
+    w: list[float]
+    p2p: float = 0.0
+    # activation budget of every rank in chunk-forwards (None: no limit beyond what the algorithm implies)
+    mem_limit: Optional[list[float]] = None
+    extra: dict = field(default_factory=dict)
+
+
+def default_budget(algorithm: str, pp: int) -> tuple[int, str, list[float]]:
+    """(chunks, placement, activation budget per rank) of the fixed-budget table of ``algorithm``."""
+    a = algorithm.lower().replace("_", "-")
+    if a in ("zerobubble", "zero-bubble", "zb", "zbb"):
+        return 1, "interleaved", [float(pp - r) + 1.0 for r in range(pp)]
+    full = 2.0 * pp
+    budget = {"zbv": full, "zbv-formatted": full, "zbv-greedy": full, "v-half": pp + 1.0, "v-min": pp / 2 + 2.0}[a]
+    return 2, "v", [budget] * pp
+
+
+def auto_schedule(algorithm: str, pp: int, m: int, costs: StageCosts, max_pending_w: Optional[int] = None) -> dict:
+    """Cost-driven variant of the B / W-split schedules: builds tables with the measured per-stage costs for a
+    ladder of activation budgets (from the algorithm's fixed budget up to ``costs.mem_limit``; without a limit the
+    fixed budget is kept, so the memory class of the algorithm is preserved) and deferred-W caps, simulates each with the same costs and returns the one with
+    the shortest makespan (ties: the smaller activation peak).  The unit-cost table of ``build_schedule`` is always
+    among the candidates, so the result is never slower in simulation than the fixed schedule."""
+    chunks, placement, base = default_budget(algorithm, pp)
+    S = pp * chunks
+    limit = costs.mem_limit if costs.mem_limit is not None else list(base)
+    floor = float(chunks) + 1.0        # below this the first micro-batch cannot reach its backward
+    ladder = []
+    for frac in (0.0, 0.25, 0.5, 0.75, 1.0):
+        budget = [max(floor, min(l, b + frac * max(l - b, 0.0))) if l >= b else max(floor, l) for b, l in zip(base, limit)]
+        if budget not in ladder:
+            ladder.append(budget)
+    caps = [max_pending_w] if max_pending_w is not None else [None, max(2, pp // 2)]
+    cands = []
+    fixed = build_schedule(algorithm, pp, m)
+    if all(p <= l + 1e-9 for p, l in zip(simulate(fixed["table"], pp, chunks, placement, 1, 1, 1)["peak_activations"], limit)):
+        cands.append(("fixed", fixed["table"]))
+    for budget in ladder:
+        for cap in caps:
+            try:
+                t = schedule_greedy(pp, m, chunks, placement, True, budget, costs.f, costs.b, costs.w, costs.p2p, cap)
+            except RuntimeError:
+                continue
+            cands.append((f"budget={[round(b, 2) for b in budget]} pending_w={cap}", t))
+    assert cands, "no schedule fits the activation limit"
+    best = None
+    for name, t in cands:
+        sim = simulate(t, pp, chunks, placement, costs.f, costs.b, costs.w, costs.p2p)
+        key = (round(sim["makespan"], 9), max(sim["peak_activations"]))
+        if best is None or key < best[0]:
+            best = (key, name, t, sim)
+    _, name, table, sim = best
+    validate(table, pp, m, chunks, placement)
+    base_sim = simulate(fixed["table"], pp, chunks, placement, costs.f, costs.b, costs.w, costs.p2p)
+    return {"table": table, "chunks": chunks, "placement": placement, "algorithm": fixed["algorithm"],
+            "picked": name, "makespan": sim["makespan"], "fixed_makespan": base_sim["makespan"],
+            "bubble_fraction": sim["bubble_fraction"], "peak_activations": sim["peak_activations"]}
+
+
+def costs_from_events(events_per_rank: list[list[dict]], pp: int, chunks: int, placement: str,
+                      p2p: float = 0.0) -> StageCosts:
+    """Per-stage mean compute times from timeline events (``kind``, ``chunk``, ``compute_start``, ``end``) of every
+    pipeline rank; a BW node is split 2 : 1 into B and W, the usual ratio of the two halves of a backward pass."""
+    S = pp * chunks
+    acc = {k: [[] for _ in range(S)] for k in "FBW"}
+    for r, events in enumerate(events_per_rank):
+        for e in events:
+            s = stage_of(r, e.get("chunk", 0), pp, placement)
+            d = e["end"] - e.get("compute_start", e["start"])
+            if e["kind"] == "BW":
+                acc["B"][s].append(d * 2 / 3)
+                acc["W"][s].append(d / 3)
+            elif e["kind"] in acc:
+                acc[e["kind"]][s].append(d)
+
+    def mean(xs, fallback):
+        return sum(xs) / len(xs) if xs else fallback
+
+    f = [mean(acc["F"][s], 1.0) for s in range(S)]
+    b = [mean(acc["B"][s], f[s]) for s in range(S)]
+    w = [mean(acc["W"][s], 0.5 * b[s]) for s in range(S)]
+    return StageCosts(f, b, w, p2p)

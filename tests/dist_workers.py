@@ -91,6 +91,11 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
     load_from_full(tr, full_sd)
     norms = []
     losses = tr.train(on_step=lambda t, lv: norms.append(float(t.optimizer.grad_norm.item())))
+    if (kwargs.get("extra_tc") or {}).get("zero_bubble_pipeline_timers_end_iter"):
+        rep = tr.pp_replan_report          # the cost-driven table was built and installed for the later iterations
+        assert rep is not None and rep["makespan"] <= rep["fixed_makespan"] + 1e-9, rep
+        key = (tc.pipeline_schedule, ps.get_state().pp, len(losses) and tr.num_microbatches, ps.get_state().virtual_pp)
+        assert tr._pp_schedule_cache[key] is rep
     if kwargs.get("extra_tc", {}) and kwargs["extra_tc"].get("eval_iters"):
         val = tr.evaluate(kwargs["extra_tc"]["eval_iters"])
         if rank == 0:

@@ -47,6 +47,12 @@ CASES = {
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
+    # node times measured in iterations 1-2, cost-driven table from iteration 3 on: same losses
+    "pp2_zerobubble_replanned": dict(world=2, kw=dict(pp=2, schedule="zerobubble", iters=4, extra_tc=dict(
+        zero_bubble_pipeline_timers_start_iter=1, zero_bubble_pipeline_timers_end_iter=3))),
+    "pp2_zbv_replanned": dict(world=2, kw=dict(pp=2, schedule="zbv", iters=4, extra_tc=dict(
+        zero_bubble_pipeline_timers_start_iter=1, zero_bubble_pipeline_timers_end_iter=3,
+        zero_bubble_max_pending_backward=4))),
     # optimistic optimizer step validated after the cross-stage norm reduction; clip 1e-3 forces the redo path
     "pp2_zerobubble_post_validation": dict(world=2, kw=dict(pp=2, schedule="zerobubble",
                                                             extra_tc=dict(enable_optimizer_post_validation=True))),

@@ -84,3 +84,52 @@ def test_pipeline_timeline_dump_and_viewer(tmp_path):
     assert "F" in lines[0] and "B" in lines[1]
     trace = json.loads((tmp_path / "t.json").read_text())
     assert len(trace["traceEvents"]) == 12
+
+
+def test_cost_driven_schedule_is_valid_and_never_slower_than_the_fixed_table():
+    """auto_schedule: tables built from per-stage costs are complete and deadlock-free, respect the activation limit,
+    and their simulated makespan is at most that of the unit-cost table under the same costs."""
+    import random
+
+    from primus_b200.parallel import pipeline_schedules as ps
+
+    random.seed(1)
+    gains = []
+    for algo, chunks in (("zerobubble", 1), ("zbv", 2), ("v-half", 2)):
+        for pp, m in ((2, 4), (4, 8), (4, 12), (8, 16)):
+            S = pp * chunks
+            f = [random.uniform(0.7, 1.5) for _ in range(S)]
+            b = [x * random.uniform(0.9, 1.6) for x in f]
+            w = [x * random.uniform(0.3, 0.9) for x in f]
+            _, placement, base = ps.default_budget(algo, pp)
+            for limit in (None, [1.5 * x for x in base]):
+                rep = ps.auto_schedule(algo, pp, m, ps.StageCosts(f, b, w, p2p=0.05, mem_limit=limit))
+                ps.validate(rep["table"], pp, m, chunks, placement)
+                assert rep["makespan"] <= rep["fixed_makespan"] + 1e-9
+                cap = limit if limit is not None else base
+                assert all(p <= c + 1e-9 for p, c in zip(rep["peak_activations"], cap)), (algo, pp, m, rep["picked"])
+                if limit is not None:
+                    gains.append(rep["fixed_makespan"] / rep["makespan"])
+    assert max(gains) > 1.03          # extra activation memory and real costs buy a shorter step somewhere
+
+
+def test_stage_costs_from_timeline_events_exclude_waiting():
+    from primus_b200.parallel import pipeline_schedules as ps
+
+    ev0 = [dict(kind="F", chunk=0, start=0.0, compute_start=0.0, end=1.0), dict(kind="B", chunk=0, start=5.0, compute_start=7.0, end=8.5),
+           dict(kind="W", chunk=0, start=8.5, compute_start=8.5, end=9.0)]
+    ev1 = [dict(kind="F", chunk=0, start=0.0, compute_start=1.0, end=3.0), dict(kind="BW", chunk=0, start=3.0, compute_start=3.0, end=6.0)]
+    c = ps.costs_from_events([ev0, ev1], 2, 1, "interleaved")
+    assert c.f == [1.0, 2.0] and c.b == [1.5, 2.0] and c.w == [0.5, 1.0]
+
+
+def test_per_stage_costs_and_pending_w_cap_in_the_greedy_scheduler():
+    from primus_b200.parallel import pipeline_schedules as ps
+
+    t = ps.schedule_greedy(4, 8, 1, "interleaved", True, [5.0, 4.0, 3.0, 2.0], [1, 1, 1, 2], [1, 1, 1, 2], [0.5] * 4, 0.1, 1)
+    ps.validate(t, 4, 8, 1, "interleaved")
+    for seq in t:          # with a cap of one deferred W, every B is followed by its W before the next B
+        pending = 0
+        for n in seq:
+            pending += (n.kind == "B") - (n.kind == "W")
+            assert pending <= 1

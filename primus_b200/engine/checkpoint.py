@@ -287,6 +287,12 @@ def _stable_hash(s: str) -> int:
     return zlib.crc32(s.encode())
 
 
+def _rng_tracker():
+    from ..parallel.random import get_rng_tracker
+
+    return get_rng_tracker()
+
+
 def _is_writer(spec: dict, key: str, st, fully_parallel: bool, replicated_over_dp: bool = True) -> bool:
     """Exactly one rank writes every chunk: replicas over tensor-parallel ranks are written by the first of them;
     replicas over data-parallel ranks by the first, or (``ckpt_fully_parallel_save``) by a rank picked per key."""
@@ -483,7 +489,7 @@ def save_checkpoint(trainer, root: str, release: bool = False) -> str:
     if not getattr(tc, "no_save_rng", False):
         objects[f"rng_state/rank_{st.rank}"] = {
             "cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
-            "world": st.world_size}
+            "tracker": _rng_tracker().state_dict(), "world": st.world_size}
     # device -> host now (the training step that follows may overwrite the tensors); the file I/O can run later
     async_save = bool(getattr(tc, "async_save", False))
     staged = [Piece(p.key, p.tensor.detach().to("cpu", copy=True).contiguous(), p.offsets, p.global_shape) for p in pieces]
@@ -625,6 +631,8 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
         torch.set_rng_state(rng["cpu"])
         if rng.get("cuda") is not None and torch.cuda.is_available():
             torch.cuda.set_rng_state(rng["cuda"])
+        if rng.get("tracker") and _rng_tracker().active:
+            _rng_tracker().load_state_dict(rng["tracker"])
     if finetune:
         trainer.iteration = 0
         _refresh_master_weights(trainer)
@@ -675,7 +683,7 @@ def _save_legacy(trainer, root: str, release: bool) -> str:
         payload["model"] = {saved_key(n): to_saved_layout(n, p.detach(), trainer.mcfg, st.tp).cpu()
                             for n, p in model_named_parameters(trainer) if not hasattr(p, "to_local")}
         if not getattr(tc, "no_save_rng", False):
-            payload["rng_state"] = {"cpu": torch.get_rng_state(),
+            payload["rng_state"] = {"cpu": torch.get_rng_state(), "tracker": _rng_tracker().state_dict(),
                                     "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}
         torch.save(payload, os.path.join(sub, "model_optim_rng.pt"))
     if not getattr(tc, "no_save_optim", False):
@@ -708,6 +716,8 @@ def _load_legacy(trainer, d: str, finetune: bool, load_optim: bool, load_rng: bo
         torch.set_rng_state(payload["rng_state"]["cpu"])
         if payload["rng_state"]["cuda"] is not None and torch.cuda.is_available():
             torch.cuda.set_rng_state(payload["rng_state"]["cuda"])
+        if payload["rng_state"].get("tracker") and _rng_tracker().active:
+            _rng_tracker().load_state_dict(payload["rng_state"]["tracker"])
     if finetune:
         trainer.iteration = 0
         _refresh_master_weights(trainer)

@@ -232,6 +232,16 @@ class Trainer:
                              model_cfg.fp8_amax_compute_algo, model_cfg.fp8_margin)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
+        if model_cfg.attention_dropout > 0.0:
+            raise NotImplementedError("attention_dropout > 0: the attention kernels have no dropout path "
+                                      "(hidden_dropout is built)")
+        from ..parallel import random as _prandom
+
+        if model_cfg.hidden_dropout > 0.0:
+            # named random streams: replicated activations share a stream over the tensor-parallel group, shards do not
+            _prandom.model_parallel_manual_seed(train_cfg.seed, self.device, st.tp_rank, st.pp_rank, st.ep_rank)
+        else:
+            _prandom.get_rng_tracker().reset()
         # ---------------------------------------------------------------- model chunks
         from ..parallel import pipeline_schedules as pps
 
@@ -779,6 +789,22 @@ class Trainer:
         (primus/backends/megatron/training/evaluator.py:23-208)."""
         stager = self._eval_stager()
         total = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for m in self.model_chunks:
+            m.eval()                      # no dropout in validation
+        try:
+            total = self._evaluate_batches(stager, iters, total)
+        finally:
+            for m in self.model_chunks:
+                m.train()
+        val = self.reduced_loss(total / max(iters, 1))
+        self._check_device_status()
+        ppl = math.exp(min(val, 20.0))
+        self.last_metrics.update(validation_loss=val, validation_ppl=ppl)
+        if self.st.rank == self.st.world_size - 1 or self.st.world_size == 1:
+            self.log(f" validation loss at iteration {self.iteration} | lm loss value: {val:.6E} | lm loss PPL: {ppl:.6E} |")
+        return val
+
+    def _evaluate_batches(self, stager, iters: int, total: torch.Tensor) -> torch.Tensor:
         for _ in range(iters):
             mbs = stager.next_step()
             if self.st.cp > 1:
@@ -793,13 +819,7 @@ class Trainer:
                 pos = mb.get("position_ids") if (getattr(self, "use_position_ids", False) or self.st.cp > 1) else None
                 total += self.model(mb["tokens"], mb["labels"], loss_weights=w, position_ids=pos,
                                     cu_seqlens=mb.get("host_cu_seqlens")).detach().float()
-        val = self.reduced_loss(total / max(iters, 1))
-        self._check_device_status()
-        ppl = math.exp(min(val, 20.0))
-        self.last_metrics.update(validation_loss=val, validation_ppl=ppl)
-        if self.st.rank == self.st.world_size - 1 or self.st.world_size == 1:
-            self.log(f" validation loss at iteration {self.iteration} | lm loss value: {val:.6E} | lm loss PPL: {ppl:.6E} |")
-        return val
+        return total
 
     def _log_step(self, loss: float, dt: float):
         tc, st = self.tcfg, self.st

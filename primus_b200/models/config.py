@@ -34,6 +34,8 @@ class TransformerConfig:
     rope_scaling_high_freq_factor: float = 4.0
     rope_scaling_original_max_position: int = 8192
     norm_epsilon: float = 1e-5
+    hidden_dropout: float = 0.0      # on the embedding output and on every sub-layer output before the residual add
+    attention_dropout: float = 0.0   # not built (the attention kernels have no dropout path): must stay 0
     qk_layernorm: bool = False
     untie_embeddings_and_output_weights: bool = True
     swiglu: bool = True

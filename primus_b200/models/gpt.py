@@ -22,6 +22,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import fused, gemm, layers
+from ..parallel import random as prandom
 from ..parallel import state as ps
 from ..parallel import tensor_parallel as tpc
 from .config import TransformerConfig
@@ -196,8 +197,18 @@ class TransformerLayer(nn.Module):
             self.mlp = MLP(cfg, device, tp)
             self.is_moe = False
 
+    def _drop(self, delta):
+        """Hidden dropout on a sub-layer's output before it joins the residual stream (the bias-dropout-add of the
+        reference's layers); sequence-parallel shards draw from the model-parallel stream."""
+        p = self.cfg.hidden_dropout
+        if p <= 0.0 or not self.training:
+            return delta
+        sp = self.cfg.sequence_parallel and ps.get_state().tp > 1
+        return prandom.dropout(delta, p, True, sp)
+
     def forward(self, hidden, residual, rope, batch):
         attn_out, res1 = self.self_attention(hidden, residual, rope, batch)
+        attn_out = self._drop(attn_out)
         if self.is_moe:
             y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon, res1)
             mlp_out = self.mlp(y)
@@ -205,7 +216,7 @@ class TransformerLayer(nn.Module):
             mlp_out, res2 = selective_checkpoint(self.cfg, "mlp", lambda a: self.mlp(a, None), attn_out)
         else:
             mlp_out, res2 = selective_checkpoint(self.cfg, "mlp", self.mlp, attn_out, res1)
-        return mlp_out, res2
+        return self._drop(mlp_out), res2
 
 
 class LanguageModelEmbedding(nn.Module):
@@ -336,6 +347,7 @@ class GPTModel(nn.Module):
             x = self.embedding(tokens.reshape(-1))
             if st.tp > 1:
                 x = tpc.reduce_scatter_seq(x, st.tp_group) if sp else tpc.all_reduce(x, st.tp_group)
+            x = prandom.dropout(x, cfg.hidden_dropout, self.training, sp)     # embedding dropout
             hidden, residual = x, None
         else:
             hidden, residual, batch, seq = hidden_in
@@ -464,11 +476,9 @@ def _run_group(layers_, hidden, residual, rope, batch, cfg, checkpointed: bool):
         return h, r
 
     if checkpointed and torch.is_grad_enabled():
-        from torch.utils.checkpoint import checkpoint
-
         if residual is None:
-            return checkpoint(lambda h: run(h, None), hidden, use_reentrant=False)
-        return checkpoint(run, hidden, residual, use_reentrant=False)
+            return prandom.checkpoint(lambda h: run(h, None), hidden)
+        return prandom.checkpoint(run, hidden, residual)
     return run(hidden, residual)
 
 
@@ -488,9 +498,7 @@ def selective_checkpoint(cfg, module: str, fn, *args):
     q / k / v in the backward pass)."""
     if cfg.recompute_granularity == "selective" and torch.is_grad_enabled() and \
             module in (cfg.recompute_modules or ["core_attn"]):
-        from torch.utils.checkpoint import checkpoint
-
-        return checkpoint(fn, *args, use_reentrant=False)
+        return prandom.checkpoint(fn, *args)
     return fn(*args)
 
 

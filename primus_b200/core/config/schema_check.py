@@ -28,7 +28,7 @@ INERT_KEYS = {
     # numerics fixed by the design: bf16 parameters, fp32 main gradients and accumulation, no loss scaling
     "accumulate_allreduce_grads_in_fp32", "loss_scale", "ddp_average_in_collective",
     # model switches of architectures that are not built (biases, LayerNorm, learned positions)
-    "add_qkv_bias", "normalization", "position_embedding_type", "lora_dropout",
+    "normalization", "position_embedding_type", "lora_dropout",
     # data loading is synchronous mock / indexed data staged by the trainer itself
     "create_attention_mask_in_dataloader", "dataloader_type", "num_workers", "train_samples",
     # kernel selection switches of the reference's operator library: one native implementation here

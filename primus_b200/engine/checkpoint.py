@@ -75,7 +75,7 @@ def shard_spec(name: str, p: torch.Tensor, cfg, st) -> dict:
         return {"kind": "ep", "axis": 0, "index": st.ep_rank, "count": st.ep}
     if not getattr(p, "tensor_model_parallel", False) or st.tp == 1:
         return {"kind": "replicated", "axis": 0, "index": 0, "count": 1}
-    if name.endswith("linear_qkv.weight"):
+    if name.endswith(("linear_qkv.weight", "linear_qkv.bias")):
         return {"kind": "qkv", "axis": 0, "index": st.tp_rank, "count": st.tp}
     if name.endswith("linear_fc1.weight"):
         return {"kind": "glu", "axis": 0, "index": st.tp_rank, "count": st.tp}
@@ -109,7 +109,7 @@ def _is_mla_rope_weight(name: str, cfg) -> bool:
 
 
 def to_saved_layout(name: str, t: torch.Tensor, cfg, tp: int) -> torch.Tensor:
-    if name.endswith("linear_qkv.weight") and not cfg.multi_latent_attention:
+    if name.endswith(("linear_qkv.weight", "linear_qkv.bias")) and not cfg.multi_latent_attention:
         return qkv_internal_to_mcore(t, cfg.num_attention_heads // tp, cfg.num_query_groups // tp, cfg.kv_channels)
     if _is_mla_rope_weight(name, cfg):
         return _mla_rope_rows(t, name, cfg, tp, to_internal=False)
@@ -117,7 +117,7 @@ def to_saved_layout(name: str, t: torch.Tensor, cfg, tp: int) -> torch.Tensor:
 
 
 def from_saved_layout(name: str, t: torch.Tensor, cfg, tp: int) -> torch.Tensor:
-    if name.endswith("linear_qkv.weight") and not cfg.multi_latent_attention:
+    if name.endswith(("linear_qkv.weight", "linear_qkv.bias")) and not cfg.multi_latent_attention:
         return qkv_mcore_to_internal(t, cfg.num_attention_heads // tp, cfg.num_query_groups // tp, cfg.kv_channels)
     if _is_mla_rope_weight(name, cfg):
         return _mla_rope_rows(t, name, cfg, tp, to_internal=True)

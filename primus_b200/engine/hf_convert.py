@@ -39,6 +39,8 @@ def config_from_hf(hf: dict) -> dict:
                kv_channels=hf.get("head_dim") or hf["hidden_size"] // nh)
     if mt in ("qwen3", "qwen3_moe"):
         out["qk_layernorm"] = True
+    if mt == "qwen2" or (mt == "llama" and hf.get("attention_bias")):
+        out["add_qkv_bias"] = True       # Qwen2 / Qwen2.5: biases on q, k and v (not on the output projection)
     E = hf.get("num_experts") or hf.get("num_local_experts") or hf.get("n_routed_experts")
     if E:
         out.update(num_experts=E, moe_router_topk=hf.get("num_experts_per_tok", 2),
@@ -129,6 +131,9 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
             sd[a + "linear_qkv.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
             sd[a + "linear_qkv.weight"] = torch.cat([hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"],
                                                      hf[h + "self_attn.v_proj.weight"]], 0)
+            if cfg.add_qkv_bias:
+                sd[a + "linear_qkv.bias"] = torch.cat([hf[h + "self_attn.q_proj.bias"], hf[h + "self_attn.k_proj.bias"],
+                                                       hf[h + "self_attn.v_proj.bias"]], 0)
             if cfg.qk_layernorm:
                 sd[a + "q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
                 sd[a + "k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
@@ -197,6 +202,11 @@ def internal_to_hf(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool = Fal
             hf[h + "self_attn.q_proj.weight"] = w[: hq * d]
             hf[h + "self_attn.k_proj.weight"] = w[hq * d:(hq + hkv) * d]
             hf[h + "self_attn.v_proj.weight"] = w[(hq + hkv) * d:]
+            if cfg.add_qkv_bias:
+                b = sd[a + "linear_qkv.bias"]
+                hf[h + "self_attn.q_proj.bias"] = b[: hq * d]
+                hf[h + "self_attn.k_proj.bias"] = b[hq * d:(hq + hkv) * d]
+                hf[h + "self_attn.v_proj.bias"] = b[(hq + hkv) * d:]
             if cfg.qk_layernorm:
                 hf[h + "self_attn.q_norm.weight"] = sd[a + "q_layernorm.weight"]
                 hf[h + "self_attn.k_norm.weight"] = sd[a + "k_layernorm.weight"]

@@ -34,6 +34,7 @@ class TransformerConfig:
     rope_scaling_high_freq_factor: float = 4.0
     rope_scaling_original_max_position: int = 8192
     norm_epsilon: float = 1e-5
+    add_qkv_bias: bool = False       # bias on the fused q / k / v projection (Qwen2 / Qwen2.5)
     hidden_dropout: float = 0.0      # on the embedding output and on every sub-layer output before the residual add
     attention_dropout: float = 0.0   # not built (the attention kernels have no dropout path): must stay 0
     qk_layernorm: bool = False
@@ -185,6 +186,8 @@ class TransformerConfig:
                 n += self.num_attention_heads * self.v_head_dim * h
             else:
                 n += h * self.qkv_width + self.num_attention_heads * self.kv_channels * h
+                if self.add_qkv_bias:
+                    n += self.qkv_width
                 if self.qk_layernorm:
                     n += 2 * self.kv_channels
             if self.is_moe_layer(i):

@@ -60,6 +60,11 @@ class SelfAttention(nn.Module):
             layer_norm_weight=_param((h,), 0, dt, device, is_norm=True),
             weight=_param(((self.hq + 2 * self.hkv) * d, h), std, dt, device),
         )
+        if cfg.add_qkv_bias:   # Qwen2 / Qwen2.5: a bias on the fused q / k / v projection (rows ordered like the weight)
+            self.linear_qkv.register_parameter(
+                "bias", nn.Parameter(torch.zeros((self.hq + 2 * self.hkv) * d, dtype=dt, device=device)))
+            self.linear_qkv.bias.tensor_model_parallel = tp > 1
+            self.linear_qkv.bias.partition_dim = 0
         self.linear_proj = ParamHolder(weight=_param((h, self.hq * d), out_std, dt, device))
         if cfg.qk_layernorm:
             self.q_layernorm = ParamHolder(weight=_param((d,), 0, dt, device, is_norm=True))
@@ -84,6 +89,8 @@ class SelfAttention(nn.Module):
         qkv, xsum = layers.norm_linear(hidden, residual, self.linear_qkv.layer_norm_weight,
                                        self.linear_qkv.weight, cfg.norm_epsilon, tpg, sp)
         d = cfg.kv_channels
+        if cfg.add_qkv_bias:
+            qkv = qkv + self.linear_qkv.bias
         if cfg.qk_layernorm:
             qkv = self._qk_norm(qkv, d)
         cos, sin, pos = rope[:3]

@@ -73,7 +73,7 @@ def test_finetune_load_resets_iteration(tmp_path):
 
 def _reshard_worker(rank, world, root, outp):
     ps.destroy_model_parallel()
-    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, tp=2, sp=True)
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, tp=2, sp=True, extra_mc=dict(add_qkv_bias=True))
     ps.initialize_model_parallel(tp=2)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     tr.load_checkpoint(root)
@@ -84,7 +84,7 @@ def _reshard_worker(rank, world, root, outp):
 
 def test_load_tp1_checkpoint_into_tp2(tmp_path):
     root = str(tmp_path / "ckpt")
-    a = _trainer(iters=4)
+    a = _trainer(iters=4, extra_mc=dict(add_qkv_bias=True))     # the q / k / v bias follows the weight's row layout
     a.tcfg.use_distributed_optimizer = True
     a.train(2)
     a.save_checkpoint(root)

@@ -218,7 +218,7 @@ def test_every_preset_key_is_read_or_declared_inert():
 def test_inert_key_is_reported(tmp_path):
     from primus_b200.core.config import schema_check
 
-    msgs = schema_check.check_inert({"add_qkv_bias": True, "lr": 1e-3}, "pre_trainer.yaml", "llama3.1_8B.yaml")
-    assert len(msgs) == 1 and "add_qkv_bias" in msgs[0] and "no effect" in msgs[0]
-    assert schema_check.check_inert({"add_qkv_bias": False}, "pre_trainer.yaml", "llama3.1_8B.yaml") == []
+    msgs = schema_check.check_inert({"normalization": "LayerNorm", "lr": 1e-3}, "pre_trainer.yaml", "llama3.1_8B.yaml")
+    assert len(msgs) == 1 and "normalization" in msgs[0] and "no effect" in msgs[0]
+    assert schema_check.check_inert({"normalization": "RMSNorm"}, "pre_trainer.yaml", "llama3.1_8B.yaml") == []
     assert schema_check.check_inert({"hidden_dropout": 0.1}, "pre_trainer.yaml", "llama3.1_8B.yaml") == []   # acted on

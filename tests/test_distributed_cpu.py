@@ -62,6 +62,7 @@ CASES = {
         enable_optimizer_post_validation=True, enable_exact_optimizer_post_validation=False))),
     "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
+    "tp2_qkv_bias": dict(world=2, kw=dict(tp=2, sp=True, extra_mc=dict(add_qkv_bias=True))),
     "cp2": dict(world=2, kw=dict(cp=2)),
     "cp2_pp2": dict(world=4, kw=dict(cp=2, pp=2)),
     "cp2_allgather": dict(world=2, kw=dict(cp=2, cp_comm="allgather")),

@@ -52,6 +52,19 @@ def test_llama_matches_hf():
     _check(LlamaForCausalLM(c), c, torch.randint(0, 250, (2, 24)))
 
 
+def test_qwen2_with_qkv_bias_matches_hf():
+    Q = pytest.importorskip("transformers.models.qwen2")
+    torch.manual_seed(5)
+    c = Q.Qwen2Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=250, rope_theta=1e6, max_position_embeddings=128,
+                      tie_word_embeddings=False, use_sliding_window=False)
+    m = Q.Qwen2ForCausalLM(c)
+    for n, p in m.named_parameters():
+        if n.endswith(("q_proj.bias", "k_proj.bias", "v_proj.bias")):
+            torch.nn.init.normal_(p, std=0.5)           # zero-initialised by default: make the biases matter
+    _check(m, c, torch.randint(0, 250, (2, 24)))
+
+
 def test_qwen3_dense_matches_hf():
     Q = pytest.importorskip("transformers.models.qwen3")
     torch.manual_seed(1)

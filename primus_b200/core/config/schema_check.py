@@ -32,7 +32,7 @@ INERT_KEYS = {
     # data loading is synchronous mock / indexed data staged by the trainer itself
     "create_attention_mask_in_dataloader", "dataloader_type", "num_workers", "train_samples",
     # kernel selection switches of the reference's operator library: one native implementation here
-    "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_autotune", "use_turbo_parallel_linear",
+    "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_parallel_linear",
     "use_turbo_rms_norm", "turbo_deepep_num_cu",
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "generate_tracelens_report", "straggler_ctrlr_port",

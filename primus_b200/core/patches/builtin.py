@@ -93,6 +93,12 @@ def _validate(ctx: PatchContext):
         raise ValueError("fp8 GEMMs support recipes delayed | tensorwise | blockwise | mxfp8")
     if p.get("fp4") and p.get("fp4_recipe", "mxfp4") != "mxfp4":
         raise ValueError("fp4 GEMMs support the mxfp4 recipe only")
+    if p.get("use_turbo_autotune") and not p.get("deterministic_mode"):
+        # online tile tuning of the tcgen05 GEMMs: each new shape times its candidates once (ops/autotune.py)
+        os.environ["PRIMUS_B200_AUTOTUNE"] = "1"
+        from ...ops import autotune
+
+        autotune.set_online(True)
     if p.get("deterministic_mode"):
         os.environ.setdefault("PRIMUS_DETERMINISTIC", "1")
         os.environ.setdefault("NCCL_ALGO", "Ring")

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, autotune
 
 _BLOCK_N_OVERRIDE: int | None = None
 
@@ -175,7 +175,11 @@ def gemm(
             out.zero_()
         return out
     mode = 0 if out_dtype == torch.bfloat16 else (2 if accumulate else 1)
-    if fp8 is not False and _fp8_eligible(a, b, out, M, N, K):
+    use_fp8 = fp8 is not False and _fp8_eligible(a, b, out, M, N, K)
+    tuned = None
+    if autotune.active() and not _BLOCK_N_OVERRIDE:
+        tuned = autotune.lookup(autotune.make_key("mxfp8" if use_fp8 else "bf16", M, N, K, a_mn, b_mn, mode))
+    if use_fp8:
         # operand roles (delayed scaling keeps one history per weight and role): fprop x . W, dgrad dy . W, wgrad dy . x
         wid = fp8_key if fp8_key is not None else id(b)
         aq, asf = _quantized(a, "col" if a_mn else "row", role=(wid, "x" if not (a_mn or b_mn) else "dy"))
@@ -183,13 +187,22 @@ def gemm(
                              role=(wid, "x"))
         from . import fp8 as _fp8
 
-        _fp8.launch_gemm(aq, asf, bq, bsf, out, M, N, K, a_mn, b_mn, mode, None, max_ctas)
+        _fp8.launch_gemm(aq, asf, bq, bsf, out, M, N, K, a_mn, b_mn, mode, tuned.get("block_n") if tuned else None,
+                         max_ctas or (tuned.get("max_ctas", 0) if tuned else 0),
+                         tuned.get("two_cta") if tuned else None)
         return out
+    launch_bf16(a, b, out, M, N, K, a_mn, b_mn, mode, (tuned.get("block_n") if tuned else None) or _pick_block_n(M, N),
+                max_ctas or (tuned.get("max_ctas", 0) if tuned else 0))
+    return out
+
+
+def launch_bf16(a, b, out, M: int, N: int, K: int, a_mn: bool, b_mn: bool, mode: int, block_n: int,
+                max_ctas: int = 0) -> None:
+    """Raw launch of the bf16 tcgen05 GEMM with explicit tile options (the autotuner times candidates through it)."""
     _lib.call(
         "gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
-        int(a_mn), int(b_mn), mode, _pick_block_n(M, N), max_ctas, _lib.status_word(a.device),
+        int(a_mn), int(b_mn), mode, block_n, max_ctas, _lib.status_word(a.device),
     )
-    return out
 
 
 class LinearFn(torch.autograd.Function):
@@ -282,3 +295,6 @@ def wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
 
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return LinearFn.apply(x, weight)
+
+
+autotune.configure_from_env()

@@ -13,6 +13,7 @@
 //
 // Replaces the Turbo / Transformer-Engine MXFP8 cast kernels
 // (primus/backends/megatron/core/extensions/primus_turbo.py: `pt.ops.quantize` users, float8 recipe mxfp8).
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -40,6 +41,36 @@ __device__ __forceinline__ uint16_t cvt2(float a, float b) {
   return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
 }
 
+// MXFP4 numerics on the FP8 data path: the block exponent leaves the block maximum at or below 6 (the largest E2M1
+// magnitude), values are rounded to E2M1 (RN-even, saturating) and stored as the E4M3 byte of the same number (every
+// E2M1 value is exact in E4M3), so the block-scaled FP8 GEMM consumes them unchanged.
+__device__ __forceinline__ int e8m0_from_amax_fp4(float amax) {
+  const float v = amax * (1.0f / 6.0f);
+  const uint32_t b = __float_as_uint(v);
+  int e = (int)((b >> 23) & 0xff);
+  if (b & 0x7fffff) e += 1;
+  if (e < 0) e = 0;
+  if (e > 254) e = 254;
+  return (amax == 0.f) ? 0 : e;
+}
+__device__ __forceinline__ uint16_t cvt2_fp4(float a, float b) {
+  const uint32_t packed = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
+  // E2M1 code (sign, 3 magnitude bits: 0, 0.5, 1, 1.5, 2, 3, 4, 6) -> E4M3 byte of the same value
+  constexpr unsigned long long lut = 0x4C4844403C383000ull;
+  const uint32_t c0 = packed & 0xf, c1 = (packed >> 4) & 0xf;
+  const uint32_t b0 = (uint32_t)((lut >> (8 * (c0 & 7))) & 0xff) | ((c0 & 8) << 4);
+  const uint32_t b1 = (uint32_t)((lut >> (8 * (c1 & 7))) & 0xff) | ((c1 & 8) << 4);
+  return (uint16_t)(b0 | (b1 << 8));
+}
+template <bool FP4>
+__device__ __forceinline__ uint16_t cvt2_sel(float a, float b) {
+  return FP4 ? cvt2_fp4(a, b) : cvt2(a, b);
+}
+template <bool FP4>
+__device__ __forceinline__ int e8m0_sel(float amax) {
+  return FP4 ? e8m0_from_amax_fp4(amax) : e8m0_from_amax(amax);
+}
+
 __device__ __forceinline__ long sf_offset(int mn, int k_blk32, int k_groups) {
   // block (mn / 128, k_blk32 / 4), K-fastest
   return ((long)(mn >> 7) * k_groups + (k_blk32 >> 2)) * 512 + (mn & 31) * 16 + ((mn & 127) >> 5) * 4 + (k_blk32 & 3);
@@ -57,7 +88,7 @@ constexpr int QUANT_SMEM = TILE * PITCH * 2;   // one staged bf16 tile; the fp8 
 //   SCALE_VEC128  `e_rowv[r]` for the blocks of tile row r (row direction) and `e_colv[c]` for those of tile column c
 //                 (column direction): one scale per 1 x 128 / 128 x 1 vector, written into its four 32-blocks.
 enum { SCALE_BLOCK32 = 0, SCALE_FIXED = 1, SCALE_VEC128 = 2 };
-template <int MODE = SCALE_BLOCK32>
+template <int MODE = SCALE_BLOCK32, bool FP4 = false>
 __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, int R, int C,
                                                      int row0, int col0, uint8_t* __restrict__ q_row,
                                                      uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col,
@@ -85,13 +116,13 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       float amax = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(f[i]));
-      const int e = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_rowv[r] : e8m0_from_amax(amax));
+      const int e = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_rowv[r] : e8m0_sel<FP4>(amax));
       const float inv = inv_scale_from_e8m0(e);
       uint32_t w[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        w[i] = (uint32_t)cvt2(f[4 * i] * inv, f[4 * i + 1] * inv) |
-               ((uint32_t)cvt2(f[4 * i + 2] * inv, f[4 * i + 3] * inv) << 16);
+        w[i] = (uint32_t)cvt2_sel<FP4>(f[4 * i] * inv, f[4 * i + 1] * inv) |
+               ((uint32_t)cvt2_sel<FP4>(f[4 * i + 2] * inv, f[4 * i + 3] * inv) << 16);
       uint4* dst = reinterpret_cast<uint4*>(q_row + (long)(row0 + r) * C + col0 + j * 32);
       dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -130,9 +161,9 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
       o = __shfl_xor_sync(0xffffffffu, w, 16);
       m[u] = __hmax2(m[u], *reinterpret_cast<__nv_bfloat162*>(&o));
       const float2 a = __bfloat1622float2(m[u]);
-      e[2 * u] = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u] : e8m0_from_amax(a.x));
+      e[2 * u] = MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u] : e8m0_sel<FP4>(a.x));
       e[2 * u + 1] =
-          MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u + 1] : e8m0_from_amax(a.y));
+          MODE == SCALE_FIXED ? fixed_e : (MODE == SCALE_VEC128 ? (int)e_colv[cbase + 2 * u + 1] : e8m0_sel<FP4>(a.y));
       inv[2 * u] = inv_scale_from_e8m0(e[2 * u]);
       inv[2 * u + 1] = inv_scale_from_e8m0(e[2 * u + 1]);
     }
@@ -144,8 +175,8 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const float2 t0 = __bfloat1622float2(h[2 * u]), t1 = __bfloat1622float2(h[2 * u + 1]);
-        w[u] = (uint32_t)cvt2(t0.x * inv[4 * u], t0.y * inv[4 * u + 1]) |
-               ((uint32_t)cvt2(t1.x * inv[4 * u + 2], t1.y * inv[4 * u + 3]) << 16);
+        w[u] = (uint32_t)cvt2_sel<FP4>(t0.x * inv[4 * u], t0.y * inv[4 * u + 1]) |
+               ((uint32_t)cvt2_sel<FP4>(t1.x * inv[4 * u + 2], t1.y * inv[4 * u + 3]) << 16);
       }
       *reinterpret_cast<uint2*>(q_col + (long)(row0 + r) * C + col0 + cbase) = make_uint2(w[0], w[1]);
     }
@@ -160,6 +191,7 @@ __device__ __forceinline__ void quantize_staged_tile(const __nv_bfloat16* tile, 
   }
 }
 
+template <bool FP4>
 __global__ void __launch_bounds__(256, 4)
 quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* __restrict__ q_row,
                    uint8_t* __restrict__ sf_row, uint8_t* __restrict__ q_col, uint8_t* __restrict__ sf_col) {
@@ -176,7 +208,7 @@ quant_mxfp8_kernel(const __nv_bfloat16* __restrict__ x, int R, int C, uint8_t* _
     *reinterpret_cast<uint4*>(&tile[r * PITCH + c8]) = d;
   }
   __syncthreads();
-  quantize_staged_tile(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
+  quantize_staged_tile<SCALE_BLOCK32, FP4>(tile, R, C, row0, col0, q_row, sf_row, q_col, sf_col);
 }
 
 // Tensor-wise FP8 ("current scaling" with a power-of-two scale): one scale 2^e for the whole tensor,
@@ -413,13 +445,30 @@ int pb_quant_mxfp8(const void* x, int R, int C, void* q_row, void* sf_row, void*
   constexpr int SMEM = QUANT_SMEM;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(quant_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(quant_mxfp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  quant_mxfp8_kernel<<<grid, 256, SMEM, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), R, C,
-                                         reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row),
-                                         reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  quant_mxfp8_kernel<false><<<grid, 256, SMEM, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), R, C,
+                                                reinterpret_cast<uint8_t*>(q_row), reinterpret_cast<uint8_t*>(sf_row),
+                                                reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
+  return (int)cudaGetLastError();
+}
+
+// MXFP4 numerics in FP8 storage: E2M1 values (as E4M3 bytes) with one UE8M0 scale per 32 elements; outputs and
+// constraints as pb_quant_mxfp8.
+int pb_quant_mxfp4_as_fp8(const void* x, int R, int C, void* q_row, void* sf_row, void* q_col, void* sf_col,
+                          cudaStream_t s) {
+  if (R % TILE || C % TILE || R <= 0 || C <= 0) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(quant_mxfp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QUANT_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  quant_mxfp8_kernel<true><<<dim3(C / TILE, R / TILE), 256, QUANT_SMEM, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), R, C, reinterpret_cast<uint8_t*>(q_row),
+      reinterpret_cast<uint8_t*>(sf_row), reinterpret_cast<uint8_t*>(q_col), reinterpret_cast<uint8_t*>(sf_col));
   return (int)cudaGetLastError();
 }
 

@@ -228,8 +228,13 @@ class Trainer:
         # fp8 recipe of the linear-layer GEMMs (attention, the LM head and the router stay in bf16)
         if model_cfg.fp8 and model_cfg.fp8_recipe not in _gemm.FP8_RECIPES:
             raise NotImplementedError(f"fp8_recipe {model_cfg.fp8_recipe!r}: choose one of {_gemm.FP8_RECIPES}")
-        _gemm.set_fp8_recipe(model_cfg.fp8_recipe if model_cfg.fp8 else None, model_cfg.fp8_amax_history_len,
-                             model_cfg.fp8_amax_compute_algo, model_cfg.fp8_margin)
+        if model_cfg.fp4 and model_cfg.fp4_recipe not in _gemm.FP4_RECIPES:
+            raise NotImplementedError(f"fp4_recipe {model_cfg.fp4_recipe!r}: choose one of {_gemm.FP4_RECIPES}")
+        if model_cfg.fp4 and model_cfg.fp8:
+            raise ValueError("set either fp8 or fp4, not both")
+        recipe = model_cfg.fp4_recipe if model_cfg.fp4 else (model_cfg.fp8_recipe if model_cfg.fp8 else None)
+        _gemm.set_fp8_recipe(recipe, model_cfg.fp8_amax_history_len, model_cfg.fp8_amax_compute_algo,
+                             model_cfg.fp8_margin)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
         if model_cfg.attention_dropout > 0.0:

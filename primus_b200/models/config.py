@@ -90,6 +90,8 @@ class TransformerConfig:
     fp8_amax_history_len: int = 1          # delayed scaling: steps of recorded maxima
     fp8_amax_compute_algo: str = "most_recent"   # delayed scaling: most_recent | max over the history
     fp8_margin: int = 0                    # delayed scaling: extra powers of two of headroom
+    fp4: Optional[str] = None  # None | "e2m1": MXFP4 numerics for the linear-layer GEMMs (carried in FP8 storage)
+    fp4_recipe: str = "mxfp4"
     recompute_granularity: Optional[str] = None  # None | selective | full
     recompute_method: Optional[str] = None       # full: "uniform" (chunks of recompute_num_layers) | "block" (first N layers)
     recompute_num_layers: Optional[int] = None

@@ -63,6 +63,9 @@ def _e8m0(amax: torch.Tensor) -> torch.Tensor:
 #   "tensorwise"  the whole tensor, from its current maximum ("current scaling")
 #   "delayed"     the whole tensor, from the maxima recorded in earlier steps (``DelayedScaling``)
 #   "blockwise"   activations / gradients: every 1 x 128 vector along the reduced dimension; weights: 128 x 128 tiles
+#   "mxfp4"       MXFP4 numerics (E2M1 values, one UE8M0 scale per 32 elements) in FP8 storage: values are rounded to
+#                 the E2M1 grid and kept as the E4M3 bytes of the same numbers, so convergence under 4-bit operands can
+#                 be studied on the FP8 tensor-core path (FP8 throughput, not the 2x of packed 4-bit operands)
 SCALING = "mxfp8"
 TENSORWISE = False      # kept in step with SCALING == "tensorwise" for callers that read the old switch
 
@@ -128,6 +131,28 @@ class DelayedScaling:
 DELAYED: Optional[DelayedScaling] = None
 
 
+def _e8m0_fp4(amax: torch.Tensor) -> torch.Tensor:
+    """Exponent that brings a block maximum to at most 6, the largest E2M1 magnitude."""
+    v = (amax.float() * torch.tensor(1.0 / 6.0, dtype=torch.float32, device=amax.device))
+    bits = v.view(torch.int32)
+    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return torch.where(amax == 0, torch.zeros_like(e), e.clamp(0, 254))
+
+
+_E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def round_to_e2m1(v: torch.Tensor) -> torch.Tensor:
+    """Round-to-nearest-even onto the E2M1 grid (saturating at +-6)."""
+    a = v.abs()
+    idx = torch.zeros_like(a, dtype=torch.int64)
+    for j in range(7):
+        mid = 0.5 * (_E2M1_GRID[j] + _E2M1_GRID[j + 1])
+        idx += (a > mid) if j % 2 == 0 else (a >= mid)      # a tie goes to the code with an even mantissa bit
+    grid = torch.tensor(_E2M1_GRID, dtype=torch.float32, device=v.device)
+    return torch.copysign(grid[idx], v)
+
+
 def _block_exponents(xf: torch.Tensor, direction: str, scaling: str, is_weight: bool, e_all) -> torch.Tensor:
     """UE8M0 exponent of every 32-block of ``xf`` [R, C]: [R, C/32] ("row") or [R/32, C] ("col")."""
     R, C = xf.shape
@@ -141,6 +166,8 @@ def _block_exponents(xf: torch.Tensor, direction: str, scaling: str, is_weight: 
             return _e8m0(t).repeat_interleave(TILE, 0).repeat_interleave(TILE // BLOCK, 1)
         if scaling == "blockwise":
             return _e8m0(a.view(R, C // TILE, TILE).amax(-1)).repeat_interleave(TILE // BLOCK, 1)
+        if scaling == "mxfp4":
+            return _e8m0_fp4(a.view(R, C // BLOCK, BLOCK).amax(-1))
         return _e8m0(a.view(R, C // BLOCK, BLOCK).amax(-1))
     shape = (R // BLOCK, C)
     if scaling in ("tensorwise", "delayed"):
@@ -150,6 +177,8 @@ def _block_exponents(xf: torch.Tensor, direction: str, scaling: str, is_weight: 
         return _e8m0(t).repeat_interleave(TILE // BLOCK, 0).repeat_interleave(TILE, 1)
     if scaling == "blockwise":
         return _e8m0(a.view(R // TILE, TILE, C).amax(1)).repeat_interleave(TILE // BLOCK, 0)
+    if scaling == "mxfp4":
+        return _e8m0_fp4(a.view(R // BLOCK, BLOCK, C).amax(1))
     return _e8m0(a.view(R // BLOCK, BLOCK, C).amax(1))
 
 
@@ -186,6 +215,8 @@ def quantize_mxfp8_ref(x: torch.Tensor, rowwise: bool = True, colwise: bool = Tr
             mn = torch.arange(C, device=dev)[None, :].expand(R // BLOCK, C)
             kb = torch.arange(R // BLOCK, device=dev)[:, None].expand(R // BLOCK, C)
             off = sf_offsets(mn, kb, R // TILE)
+        if scaling == "mxfp4":
+            q = round_to_e2m1(q)
         q8 = q.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
         sf = torch.zeros(R * C // BLOCK, dtype=torch.uint8, device=dev)
         sf[off.reshape(-1)] = e.reshape(-1).to(torch.uint8)
@@ -249,6 +280,8 @@ def quantize_mxfp8(x: torch.Tensor, rowwise: bool = True, colwise: bool = True, 
         _lib.call("quant_fp8_tensorwise", x, R, C, amax, out.q_row, out.sf_row, out.q_col, out.sf_col)
     elif scaling == "blockwise":
         _lib.call("quant_fp8_blockwise", x, R, C, int(is_weight), out.q_row, out.sf_row, out.q_col, out.sf_col)
+    elif scaling == "mxfp4":
+        _lib.call("quant_mxfp4_as_fp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
     else:
         _lib.call("quant_mxfp8", x, R, C, out.q_row, out.sf_row, out.q_col, out.sf_col)
     return out

@@ -30,6 +30,7 @@ _ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
 
 
 FP8_RECIPES = ("mxfp8", "tensorwise", "delayed", "blockwise")
+FP4_RECIPES = ("mxfp4",)     # 4-bit numerics carried in FP8 storage (ops/fp8.py)
 
 
 def set_fp8_recipe(recipe: str | None, amax_history_len: int = 1, amax_compute_algo: str = "most_recent",
@@ -37,7 +38,7 @@ def set_fp8_recipe(recipe: str | None, amax_history_len: int = 1, amax_compute_a
     """Select the FP8 recipe of all eligible GEMMs (None: bf16).  Every recipe stores its operands in the MXFP8 layout
     (see ``ops.fp8.SCALING``), so the GEMM kernels are the same; the three keyword arguments configure "delayed"."""
     global _FP8_RECIPE, _WEIGHT_GEN
-    assert recipe in (None, "") + FP8_RECIPES, f"unsupported fp8 recipe {recipe!r}"
+    assert recipe in (None, "") + FP8_RECIPES + FP4_RECIPES, f"unsupported low-precision recipe {recipe!r}"
     _FP8_RECIPE = recipe or None
     from . import fp8
 

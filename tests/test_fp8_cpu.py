@@ -142,3 +142,29 @@ def test_delayed_scaling_history_and_fallback():
     finally:
         gemm.set_fp8_recipe(None)
     assert fp8.DELAYED is None and fp8.SCALING == "mxfp8"
+
+
+def test_mxfp4_numerics_in_fp8_storage():
+    """fp4 recipe: values lie on the E2M1 grid scaled by the block's power of two, the block maximum maps to at most
+    6, ties round to even, and the stored bytes are E4M3 encodings of exactly those values."""
+    torch.manual_seed(0)
+    x = (torch.randn(128, 256) * torch.exp(torch.randn(128, 1))).bfloat16()
+    q = fp8.quantize_mxfp8_ref(x, True, True, scaling="mxfp4")
+    d = fp8.dequantize_mxfp8_ref(q.q_row, q.sf_row, False)
+    e = fp8._e8m0_fp4(x.float().abs().view(128, 8, 32).amax(-1))
+    scale = torch.exp2(e.float() - 127).repeat_interleave(32, 1)
+    grid = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6])
+    on_grid = ((d / scale).abs()[..., None] == grid).any(-1)
+    assert on_grid.all()
+    amax_scaled = (x.float().abs().view(128, 8, 32).amax(-1) / torch.exp2(e.float() - 127))
+    assert (amax_scaled <= 6).all() and (amax_scaled[amax_scaled > 0] > 3).all()
+    # error bound: half of the widest grid step (4 -> 6) in units of the block scale
+    assert ((d - x.float()).abs() <= 1.0 * scale + 1e-12).all()
+    v = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.25, -2.5, 0.26, 0.74])
+    assert fp8.round_to_e2m1(v).tolist() == [0.0, 1.0, 1.0, 2.0, 2.0, 4.0, 4.0, 6.0, -0.0, -2.0, 0.5, 0.5]
+    from primus_b200.ops import gemm
+    try:
+        gemm.set_fp8_recipe("mxfp4")
+        assert fp8.SCALING == "mxfp4" and torch.equal(fp8.quantize_mxfp8(x, True, False).q_row, q.q_row)
+    finally:
+        gemm.set_fp8_recipe(None)

@@ -195,9 +195,9 @@ def test_model_training_with_mxfp8_recipe_tracks_bf16():
         assert all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, d)), (kind, a, d)
 
 
-def test_model_training_with_mxfp4_numerics_still_learns():
-    """MXFP4 numerics on every linear-layer GEMM (no stochastic rounding, no Hadamard transform): the loss falls and
-    stays within 10 % of the bf16 trajectory on the tiny model."""
+def test_model_training_with_mxfp4_numerics_tracks_bf16():
+    """MXFP4 numerics on every linear-layer GEMM (no stochastic rounding, no Hadamard transform): the loss stays
+    within 3 % of the bf16 trajectory on the tiny model (random mock data: neither run's loss falls much)."""
     from primus_b200.engine.trainer import TrainConfig, Trainer
     from primus_b200.models.config import TransformerConfig
     from primus_b200.ops import gemm
@@ -221,7 +221,7 @@ def test_model_training_with_mxfp4_numerics_still_learns():
     finally:
         gemm.set_fp8_recipe(None)
     a, b = out[None], out["e2m1"]
-    assert b[-1] < b[0] and all(abs(x - y) <= 0.10 * abs(x) for x, y in zip(a, b)), (a, b)
+    assert a != b and all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, b)), (a, b)
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024)])

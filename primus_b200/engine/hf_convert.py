@@ -39,6 +39,10 @@ def config_from_hf(hf: dict) -> dict:
                kv_channels=hf.get("head_dim") or hf["hidden_size"] // nh)
     if mt in ("qwen3", "qwen3_moe"):
         out["qk_layernorm"] = True
+    if mt == "lfm2":        # gated short convolutions + grouped-query attention with per-head q / k norms
+        out.update(lfm_layer_types=list(hf["layer_types"]), conv_L_cache=hf.get("conv_L_cache", 3),
+                   conv_bias=bool(hf.get("conv_bias", False)), qk_layernorm=True, norm_epsilon=hf.get("norm_eps", 1e-5),
+                   ffn_hidden_size=hf.get("block_ff_dim") or hf.get("intermediate_size"))
     if mt == "qwen2" or (mt == "llama" and hf.get("attention_bias")):
         out["add_qkv_bias"] = True       # Qwen2 / Qwen2.5: biases on q, k and v (not on the output projection)
     E = hf.get("num_experts") or hf.get("num_local_experts") or hf.get("n_routed_experts")
@@ -105,7 +109,69 @@ def _mla_rows(w: torch.Tensor, cfg, kv_down: bool, perm: torch.Tensor) -> torch.
 
 
 # ----------------------------------------------------------------------------------------------
+def mamba2_config_from_hf(hf: dict) -> dict:
+    """TransformerConfig keyword arguments for a Hugging Face Mamba-2 config (a pure Mamba stack)."""
+    return dict(model_type="mamba", num_layers=hf["num_hidden_layers"], hidden_size=hf["hidden_size"],
+                num_attention_heads=hf["num_heads"], vocab_size=hf["vocab_size"], mamba_state_dim=hf["state_size"],
+                mamba_head_dim=hf["head_dim"], mamba_num_heads=hf["num_heads"], mamba_num_groups=hf["n_groups"],
+                mamba_expand=hf["expand"], mamba_d_conv=hf["conv_kernel"], mamba_chunk_size=hf.get("chunk_size", 128),
+                norm_epsilon=hf.get("layer_norm_epsilon", 1e-5),
+                untie_embeddings_and_output_weights=not hf.get("tie_word_embeddings", True))
+
+
+def _mamba2_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
+    sd: Dict[str, torch.Tensor] = {}
+    V = cfg.padded_vocab_size
+    sd["embedding.word_embeddings.weight"] = _pad_vocab(hf["backbone.embeddings.weight"], V)
+    sd["decoder.final_layernorm.weight"] = hf["backbone.norm_f.weight"]
+    if cfg.untie_embeddings_and_output_weights:
+        sd["output_layer.weight"] = _pad_vocab(hf.get("lm_head.weight", hf["backbone.embeddings.weight"]), V)
+    for L in range(cfg.num_layers):
+        p, h = f"decoder.layers.{L}.mixer.", f"backbone.layers.{L}."
+        sd[p + "in_proj.layer_norm_weight"] = hf[h + "norm.weight"]
+        for k in ("in_proj.weight", "conv1d.weight", "conv1d.bias", "dt_bias", "A_log", "D", "norm.weight", "out_proj.weight"):
+            sd[p + k] = hf[h + "mixer." + k]
+    return sd
+
+
+def _lfm2_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
+    sd: Dict[str, torch.Tensor] = {}
+    V = cfg.padded_vocab_size
+    sd["embedding.word_embeddings.weight"] = _pad_vocab(hf["model.embed_tokens.weight"], V)
+    sd["decoder.final_layernorm.weight"] = hf["model.embedding_norm.weight"]
+    if cfg.untie_embeddings_and_output_weights:
+        sd["output_layer.weight"] = _pad_vocab(hf.get("lm_head.weight", hf["model.embed_tokens.weight"]), V)
+    for L in range(cfg.num_layers):
+        p, h = f"decoder.layers.{L}.", f"model.layers.{L}."
+        a = p + "self_attention."
+        if cfg.layer_kinds[L][0] == "conv":
+            sd[a + "in_proj.layer_norm_weight"] = hf[h + "operator_norm.weight"]
+            sd[a + "in_proj.weight"] = hf[h + "conv.in_proj.weight"]
+            sd[a + "conv.weight"] = hf[h + "conv.conv.weight"]
+            sd[a + "out_proj.weight"] = hf[h + "conv.out_proj.weight"]
+            if cfg.conv_bias:
+                sd[a + "in_proj.bias"] = hf[h + "conv.in_proj.bias"]
+                sd[a + "conv.bias"] = hf[h + "conv.conv.bias"]
+                sd[a + "out_proj.bias"] = hf[h + "conv.out_proj.bias"]
+        else:
+            sd[a + "linear_qkv.layer_norm_weight"] = hf[h + "operator_norm.weight"]
+            sd[a + "linear_qkv.weight"] = torch.cat([hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"],
+                                                     hf[h + "self_attn.v_proj.weight"]], 0)
+            sd[a + "q_layernorm.weight"] = hf[h + "self_attn.q_layernorm.weight"]
+            sd[a + "k_layernorm.weight"] = hf[h + "self_attn.k_layernorm.weight"]
+            sd[a + "linear_proj.weight"] = hf[h + "self_attn.out_proj.weight"]
+        m = p + "mlp."
+        sd[m + "linear_fc1.layer_norm_weight"] = hf[h + "ffn_norm.weight"]
+        sd[m + "linear_fc1.weight"] = torch.cat([hf[h + "feed_forward.w1.weight"], hf[h + "feed_forward.w3.weight"]], 0)
+        sd[m + "linear_fc2.weight"] = hf[h + "feed_forward.w2.weight"]
+    return sd
+
+
 def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
+    if cfg.model_type == "mamba" and "backbone.embeddings.weight" in hf:
+        return _mamba2_to_internal(hf, cfg)
+    if cfg.lfm_layer_types:
+        return _lfm2_to_internal(hf, cfg)
     sd: Dict[str, torch.Tensor] = {}
     V = cfg.padded_vocab_size
     sd["embedding.word_embeddings.weight"] = _pad_vocab(hf["model.embed_tokens.weight"], V)

@@ -96,8 +96,24 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
     (primus/backends/megatron/patches/training_log/print_rank_last_patches.py:435-466)."""
     h, L, V = cfg.hidden_size, cfg.num_layers, cfg.padded_vocab_size
     fwd = 0.0
+    kinds = getattr(cfg, "layer_kinds", None) or [("attention", True)] * L
     for i in range(L):
-        if cfg.multi_latent_attention:
+        mixer, has_mlp = kinds[i]
+        if mixer == "conv":            # LFM2 short convolution: in_proj (3h), out_proj, the taps
+            fwd += 2 * h * 3 * h + 2 * h * h + 2 * h * cfg.conv_L_cache
+            attn = 0.0
+        elif mixer == "mamba":         # Mamba-2: projections, convolution, chunked scan (the reference's Zebra-Llama
+            # FLOPs patch counts the same terms: primus/backends/megatron/patches/zebra_llama_flops_patches.py)
+            di = cfg.mamba_expand * h
+            nh = cfg.mamba_num_heads or di // cfg.mamba_head_dim
+            conv_dim = di + 2 * cfg.mamba_num_groups * cfg.mamba_state_dim
+            fwd += 2 * h * (di + conv_dim + nh) + 2 * di * h + 2 * conv_dim * cfg.mamba_d_conv
+            c, n = cfg.mamba_chunk_size, cfg.mamba_state_dim
+            fwd += 2 * c * nh * n + 2 * c * di + 4 * di * n       # C B^T and (C B^T) x inside a chunk; state in / out
+            attn = 0.0
+        elif mixer is None:
+            attn = 0.0
+        elif cfg.multi_latent_attention:
             qd = cfg.qk_head_dim + cfg.qk_pos_emb_head_dim
             nh = cfg.num_attention_heads
             if cfg.q_lora_rank:
@@ -112,6 +128,8 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             fwd += 2 * h * cfg.qkv_width + 2 * cfg.num_attention_heads * cfg.kv_channels * h
             attn = 4 * seq_len * cfg.num_attention_heads * cfg.kv_channels
         fwd += attn * (0.5 if causal_half else 1.0)
+        if not has_mlp:
+            continue
         if cfg.is_moe_layer(i):
             fwd += 2 * h * cfg.num_experts
             fwd += cfg.moe_router_topk * 6 * h * cfg.moe_ffn_hidden_size

@@ -110,6 +110,22 @@ class TransformerConfig:
     final_logit_softcapping: float | None = None    # cap * tanh(logits / cap) before the loss (Grok-style)
     router_logit_softcapping: float | None = None   # same on the MoE router logits
     attn_logit_softcapping: float | None = None     # cap * tanh(scores / cap) inside attention (not for MLA / context parallel)
+    # sequence mixers other than attention (models/mixers.py)
+    model_type: str = "gpt"                         # "mamba": Mamba / hybrid stack, layer kinds from the hybrid pattern
+    lfm_layer_types: Optional[List[str]] = None     # LFM2: per layer "conv" (gated short convolution) | "full_attention"
+    conv_L_cache: int = 3                           # taps of the LFM2 short convolution
+    conv_bias: bool = False
+    mamba_state_dim: int = 128
+    mamba_head_dim: int = 64
+    mamba_num_groups: int = 8
+    mamba_num_heads: Optional[int] = None           # None: mamba_expand * hidden_size / mamba_head_dim
+    mamba_expand: int = 2
+    mamba_d_conv: int = 4
+    mamba_chunk_size: int = 128
+    is_hybrid_model: bool = False
+    hybrid_attention_ratio: float = 0.0             # share of the layers that are attention layers
+    hybrid_mlp_ratio: float = 0.0                   # share of the layers that are MLP layers
+    hybrid_override_pattern: Optional[str] = None   # one symbol per layer: M (Mamba), * (attention), - (MLP)
 
     def layer_window(self, layer_idx: int) -> int:
         """Sliding-window width of a layer (0 = full attention)."""
@@ -133,6 +149,7 @@ class TransformerConfig:
             self.moe_ffn_hidden_size = self.ffn_hidden_size
         self.moe_layer_pattern = parse_moe_layer_freq(self.moe_layer_freq, self.num_layers) \
             if self.num_experts else [0] * self.num_layers
+        self.layer_kinds = layer_kinds(self)
 
     # ------------------------------------------------------------------ derived
     @property
@@ -176,8 +193,18 @@ class TransformerConfig:
         V = self.padded_vocab_size
         n = V * h * (2 if self.untie_embeddings_and_output_weights else 1) + h
         for i in range(L):
-            n += 2 * h  # two norms
-            if self.multi_latent_attention:
+            mixer, has_mlp = self.layer_kinds[i]
+            n += h * (int(mixer is not None) + int(has_mlp))  # one norm per sub-layer
+            if mixer == "conv":
+                n += 3 * h * h + h * self.conv_L_cache + h * h + (5 * h if self.conv_bias else 0)
+            elif mixer == "mamba":
+                di = self.mamba_expand * h
+                nh = self.mamba_num_heads or di // self.mamba_head_dim
+                conv_dim = di + 2 * self.mamba_num_groups * self.mamba_state_dim
+                n += h * (di + conv_dim + nh) + conv_dim * (self.mamba_d_conv + 1) + 3 * nh + di + di * h
+            elif mixer is None:
+                pass
+            elif self.multi_latent_attention:
                 qd = self.qk_head_dim + self.qk_pos_emb_head_dim
                 if self.q_lora_rank:
                     n += h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * self.num_attention_heads * qd
@@ -192,6 +219,8 @@ class TransformerConfig:
                     n += self.qkv_width
                 if self.qk_layernorm:
                     n += 2 * self.kv_channels
+            if not has_mlp:
+                continue
             if self.is_moe_layer(i):
                 n += h * self.num_experts + self.num_experts * 3 * h * self.moe_ffn_hidden_size
                 if self.moe_shared_expert_intermediate_size:
@@ -199,6 +228,77 @@ class TransformerConfig:
             else:
                 n += 3 * h * self.ffn_hidden_size
         return n
+
+
+def hybrid_layer_pattern(num_layers: int, attention_ratio: float, mlp_ratio: float, override: Optional[str] = None,
+                         hybrid: bool = True) -> str:
+    """One symbol per layer of a Mamba / hybrid stack: ``M`` Mamba, ``*`` attention, ``-`` MLP.
+
+    * An override pattern is used as given (``|`` separators are dropped).
+    * A pure Mamba stack (``hybrid`` false) is all ``M``.
+    * A hybrid stack alternates mixer and MLP layers, so half of the layers are mixers; ``int(L / 2 x attention_ratio)`` of
+      the mixers are attention layers, each followed by an equal share of the Mamba mixers (the leftover Mamba mixers
+      close the stack); above a ratio of 0.5 the surplus attention layers come first.  This is the allocation of the
+      reference's hybrid stack (primus/backends/megatron/core/models/hybrid/hybrid_block.py:219-244), which ignores
+      ``hybrid_mlp_ratio``.
+    * With an explicit ``mlp_ratio`` > 0 the layers are instead spread evenly: ``round(L x attention_ratio)`` attention
+      layers between sections of Mamba layers, then ``round(L x mlp_ratio)`` of the Mamba layers turned into MLP layers."""
+    if override:
+        pat = override.replace("|", "")
+        assert len(pat) == num_layers and set(pat) <= set("M*-"), f"hybrid_override_pattern {override!r}: need " \
+            f"{num_layers} symbols out of M, *, -"
+        return pat
+    if not hybrid:
+        return "M" * num_layers
+    if mlp_ratio <= 0.0:
+        half = num_layers // 2
+        n_attn = int(half * attention_ratio)
+        n_mamba = half - n_attn
+        if n_attn == 0:
+            return "M-" * half
+        if attention_ratio <= 0.5:
+            return ("*-" + "M-" * (n_mamba // n_attn)) * n_attn + "M-" * (n_mamba % n_attn)
+        return "*-" * (n_attn - n_mamba) + "*-M-" * n_mamba
+    n_attn = int(round(num_layers * attention_ratio))
+    kinds = ["M"] * num_layers
+    n_mamba = num_layers - n_attn
+    if n_attn:
+        section = n_mamba / (n_attn + 1)
+        x = section
+        for i in range(num_layers):
+            if x < 0.5:
+                kinds[i] = "*"
+                x += section
+            else:
+                x -= 1
+    n_mlp = int(round(num_layers * mlp_ratio))
+    if n_mlp:
+        ratio = (n_mamba - n_mlp) / n_mlp
+        x = ratio
+        for i in range(num_layers):
+            if kinds[i] == "M":
+                if x < 0.5:
+                    kinds[i] = "-"
+                    x += ratio
+                else:
+                    x -= 1
+    return "".join(kinds)
+
+
+def layer_kinds(cfg) -> list:
+    """Per layer ``(mixer, has_mlp)``: mixer in ``"attention" | "conv" | "mamba" | None``.  A GPT-style layer is a mixer
+    followed by an MLP; the layers of a Mamba / hybrid stack hold one sub-layer each."""
+    L = cfg.num_layers
+    if cfg.model_type == "mamba":
+        pat = hybrid_layer_pattern(L, cfg.hybrid_attention_ratio, cfg.hybrid_mlp_ratio, cfg.hybrid_override_pattern,
+                                   hybrid=cfg.is_hybrid_model)
+        return [{"M": ("mamba", False), "*": ("attention", False), "-": (None, True)}[c] for c in pat]
+    if cfg.lfm_layer_types:
+        assert len(cfg.lfm_layer_types) == L, f"lfm_layer_types has {len(cfg.lfm_layer_types)} entries for {L} layers"
+        bad = set(cfg.lfm_layer_types) - {"conv", "full_attention"}
+        assert not bad, f"lfm_layer_types: unknown kinds {sorted(bad)}"
+        return [("conv" if t == "conv" else "attention", True) for t in cfg.lfm_layer_types]
+    return [("attention", True)] * L
 
 
 def parse_moe_layer_freq(freq, num_layers: int) -> list[int]:

@@ -183,16 +183,33 @@ class MLP(nn.Module):
 
 
 class TransformerLayer(nn.Module):
+    """One layer of the stack: a sequence mixer (attention, MLA, LFM2 short convolution or Mamba-2; ``None`` for the MLP
+    layers of a hybrid stack) followed by an MLP / MoE block (absent in the single-sub-layer layers of Mamba / hybrid
+    stacks).  The kinds come from ``TransformerConfig.layer_kinds``."""
+
     def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
         super().__init__()
         self.cfg = cfg
         self.layer_idx = layer_idx
-        if cfg.multi_latent_attention:
-            from .mla import MLASelfAttention
+        self.mixer_kind, self.has_mlp = cfg.layer_kinds[layer_idx]
+        if self.mixer_kind == "attention":
+            if cfg.multi_latent_attention:
+                from .mla import MLASelfAttention
 
-            self.self_attention = MLASelfAttention(cfg, layer_idx, device, tp)
-        else:
-            self.self_attention = SelfAttention(cfg, layer_idx, device, tp)
+                self.self_attention = MLASelfAttention(cfg, layer_idx, device, tp)
+            else:
+                self.self_attention = SelfAttention(cfg, layer_idx, device, tp)
+        elif self.mixer_kind == "conv":
+            from .mixers import ShortConvMixer
+
+            self.self_attention = ShortConvMixer(cfg, layer_idx, device, tp)
+        elif self.mixer_kind == "mamba":
+            from .mixers import Mamba2Mixer
+
+            self.mixer = Mamba2Mixer(cfg, layer_idx, device, tp)
+        self.is_moe = False
+        if not self.has_mlp:
+            return
         if cfg.is_moe_layer(layer_idx):
             from .moe import MoELayer
 
@@ -202,7 +219,6 @@ class TransformerLayer(nn.Module):
             self.is_moe = True
         else:
             self.mlp = MLP(cfg, device, tp)
-            self.is_moe = False
 
     def _drop(self, delta):
         """Hidden dropout on a sub-layer's output before it joins the residual stream (the bias-dropout-add of the
@@ -214,10 +230,19 @@ class TransformerLayer(nn.Module):
         return prandom.dropout(delta, p, True, sp)
 
     def forward(self, hidden, residual, rope, batch):
-        attn_out, res1 = self.self_attention(hidden, residual, rope, batch)
-        attn_out = self._drop(attn_out)
+        if self.mixer_kind is None:
+            attn_out, res1 = hidden, residual
+        else:
+            mixer = self.mixer if self.mixer_kind == "mamba" else self.self_attention
+            attn_out, res1 = mixer(hidden, residual, rope, batch)
+            attn_out = self._drop(attn_out)
+        if not self.has_mlp:
+            return attn_out, res1
         if self.is_moe:
-            y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon, res1)
+            if res1 is None:
+                y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon), attn_out
+            else:
+                y, res2 = fused.rmsnorm(attn_out, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon, res1)
             mlp_out = self.mlp(y)
         elif res1 is None:
             mlp_out, res2 = selective_checkpoint(self.cfg, "mlp", lambda a: self.mlp(a, None), attn_out)

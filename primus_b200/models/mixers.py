@@ -1,0 +1,223 @@
+"""Sequence mixers other than softmax attention: the LFM2 gated short convolution and the Mamba-2 state-space mixer.
+
+Both take the already-normalised hidden states of a layer ``[T, H]`` (T = batch x sequence, sequence fastest) and return
+the sub-layer output that joins the residual stream, like ``SelfAttention`` does; the linear projections run on this
+package's GEMM (bf16 or the active FP8 recipe), the sequence operations are written below in plain PyTorch with
+explicit formulas (they are also the CPU path and the test oracle).
+
+* ``ShortConvMixer`` — LFM2: ``B, C, x = in_proj(h)``; ``y = out_proj(C * causal_conv(B * x))`` with a depthwise causal
+  convolution of ``conv_L_cache`` taps.  Counterpart of ``Lfm2ShortConv`` in the reference
+  (primus/backends/megatron/core/transformer/attention.py:91-230; layer choice per
+  ``lfm_layer_types``: primus/backends/megatron/core/models/gpt/gpt_layer_specs.py:41-157).
+* ``Mamba2Mixer`` — Mamba-2 (state-space duality): ``z, xBC, dt = in_proj(h)``; causal depthwise convolution + SiLU on
+  ``xBC``; the selective state-space recurrence ``s_t = exp(dt_t A) s_{t-1} + dt_t B_t x_t``, ``y_t = C_t s_t + D x_t`` evaluated
+  chunk-wise as matrix products (``ssd_chunked``); gated RMSNorm ``norm(y * silu(z))`` per group; ``out_proj``.  The mixer of
+  the reference's Mamba and hybrid stacks (primus/backends/megatron/core/models/mamba/mamba_layer_specs.py,
+  primus/backends/megatron/core/models/hybrid/hybrid_block.py, presets ``mamba_370M`` and ``zebra_llama_*``).
+
+Tensor and context parallelism are not built for these mixers (they assert ``tp == cp == 1``); pipeline, data and
+expert parallelism work as for any layer.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import fused, gemm
+from ..parallel import state as ps
+
+
+def _param(shape, std, dtype, device):
+    p = nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
+    if std > 0:
+        nn.init.normal_(p, mean=0.0, std=std)
+    else:
+        nn.init.zeros_(p)
+    return p
+
+
+def _norm(hidden, residual, weight, eps):
+    """Fused residual add + RMSNorm of a sub-layer input: (normalised, summed residual stream)."""
+    if residual is None:
+        return fused.rmsnorm(hidden, weight, eps), hidden
+    return fused.rmsnorm(hidden, weight, eps, residual)
+
+
+def causal_depthwise_conv(x: torch.Tensor, weight: torch.Tensor, bias, batch: int) -> torch.Tensor:
+    """``x`` [batch * seq, C] (sequence fastest), ``weight`` [C, taps]: out[t, c] = sum_k weight[c, k] x[t - (taps-1) + k, c]
+    with zeros before the start of every sequence (the semantics of ``nn.Conv1d(groups=C, padding=taps-1)[..., :seq]``)."""
+    T, C = x.shape
+    taps = weight.shape[1]
+    xs = x.view(batch, T // batch, C)
+    out = None
+    for k in range(taps):
+        shift = taps - 1 - k
+        term = xs if shift == 0 else F.pad(xs, (0, 0, shift, 0))[:, : T // batch]
+        term = term * weight[:, k]
+        out = term if out is None else out + term
+    if bias is not None:
+        out = out + bias
+    return out.reshape(T, C)
+
+
+class ShortConvMixer(nn.Module):
+    """LFM2 double-gated short convolution (parameter names follow the reference: ``in_proj``, ``conv``, ``out_proj``)."""
+
+    def __init__(self, cfg, layer_idx: int, device, tp: int):
+        super().__init__()
+        assert tp == 1, "the short-convolution mixer is not built for tensor parallelism"
+        self.cfg = cfg
+        h, dt = cfg.hidden_size, cfg.torch_dtype
+        std = cfg.init_method_std
+        self.in_proj = nn.Module()
+        self.in_proj.register_parameter("layer_norm_weight", nn.Parameter(torch.ones(h, dtype=dt, device=device)))
+        self.in_proj.register_parameter("weight", _param((3 * h, h), std, dt, device))
+        self.conv = nn.Module()
+        self.conv.register_parameter("weight", _param((h, 1, cfg.conv_L_cache), std, dt, device))
+        self.out_proj = nn.Module()
+        self.out_proj.register_parameter("weight", _param((h, h), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
+        if cfg.conv_bias:
+            for m, n in ((self.in_proj, 3 * h), (self.conv, h), (self.out_proj, h)):
+                m.register_parameter("bias", nn.Parameter(torch.zeros(n, dtype=dt, device=device)))
+        for w in (self.in_proj.weight, self.out_proj.weight):
+            w._is_weight = True
+
+    def forward(self, hidden, residual, rope, batch):
+        cfg = self.cfg
+        assert ps.get_state().cp == 1, "the short-convolution mixer is not built for context parallelism"
+        y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        bcx = gemm.linear(y, self.in_proj.weight)
+        if cfg.conv_bias:
+            bcx = bcx + self.in_proj.bias
+        h = cfg.hidden_size
+        B, C, x = bcx[:, :h], bcx[:, h:2 * h], bcx[:, 2 * h:]
+        conv = causal_depthwise_conv(B * x, self.conv.weight[:, 0, :], self.conv.bias if cfg.conv_bias else None, batch)
+        out = gemm.linear((C * conv).contiguous(), self.out_proj.weight)
+        if cfg.conv_bias:
+            out = out + self.out_proj.bias
+        return out, xsum
+
+
+# ------------------------------------------------------------------------------------------------ Mamba-2
+def _segsum(a: torch.Tensor) -> torch.Tensor:
+    """a [..., L] -> S [..., L, L] with S[i, j] = sum_{j < k <= i} a[k] for i >= j and -inf above the diagonal."""
+    L = a.shape[-1]
+    c = torch.cumsum(a, -1)
+    s = c[..., :, None] - c[..., None, :]
+    mask = torch.ones(L, L, dtype=torch.bool, device=a.device).tril()
+    return s.masked_fill(~mask, float("-inf"))
+
+
+def ssd_chunked(x, dt, A, B, C, chunk: int):
+    """Selective state-space model, chunk-wise (state-space duality).
+
+    x [b, l, h, p], dt [b, l, h] (already positive), A [h] (negative), B and C [b, l, g, n] with h % g == 0.
+    Returns y [b, l, h, p] with ``s_t = exp(dt_t A) s_{t-1} + dt_t x_t B_t^T`` (state [p, n] per head) and ``y_t = s_t C_t``.
+    Inside a chunk the recurrence is a masked matrix product; between chunks only the [p, n] states are carried."""
+    b, l, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    pad = (-l) % chunk
+    if pad:
+        x, dt, B, C = (F.pad(t, (0, 0) * (t.dim() - 2) + (0, pad)) for t in (x, dt, B, C))
+    L = l + pad
+    c = L // chunk
+    rep = h // g
+    xf = (x.float() * dt.float()[..., None]).view(b, c, chunk, h, p)
+    a = (dt.float() * A.float()).view(b, c, chunk, h).permute(0, 3, 1, 2)            # [b, h, c, chunk] log-decays
+    Bf = B.float().repeat_interleave(rep, 2).view(b, c, chunk, h, n)
+    Cf = C.float().repeat_interleave(rep, 2).view(b, c, chunk, h, n)
+    a_cum = torch.cumsum(a, -1)
+    # within-chunk (diagonal blocks)
+    decay = torch.exp(_segsum(a))                                                     # [b, h, c, chunk, chunk]
+    y_diag = torch.einsum("bclhn,bcshn,bhcls,bcshp->bclhp", Cf, Bf, decay, xf)
+    # state each chunk hands on, then the recurrence over chunks
+    decay_states = torch.exp(a_cum[..., -1:] - a_cum)                                 # [b, h, c, chunk]
+    states = torch.einsum("bclhn,bhcl,bclhp->bchpn", Bf, decay_states, xf)
+    states = torch.cat([torch.zeros_like(states[:, :1]), states], 1)
+    decay_chunk = torch.exp(_segsum(F.pad(a_cum[..., -1], (1, 0))))                   # [b, h, c + 1, c + 1]
+    states = torch.einsum("bhzc,bchpn->bzhpn", decay_chunk, states)[:, :-1]
+    y_off = torch.einsum("bclhn,bchpn,bhcl->bclhp", Cf, states, torch.exp(a_cum))
+    y = (y_diag + y_off).reshape(b, L, h, p)
+    return y[:, :l]
+
+
+def ssd_sequential(x, dt, A, B, C):
+    """The recurrence of ``ssd_chunked`` one step at a time (test oracle)."""
+    b, l, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    rep = h // g
+    Bf, Cf = B.float().repeat_interleave(rep, 2), C.float().repeat_interleave(rep, 2)
+    s = torch.zeros(b, h, p, n, dtype=torch.float32, device=x.device)
+    ys = []
+    for t in range(l):
+        da = torch.exp(dt[:, t].float() * A.float())                                  # [b, h]
+        s = s * da[..., None, None] + (dt[:, t].float()[..., None] * x[:, t].float())[..., None] * Bf[:, t][:, :, None, :]
+        ys.append(torch.einsum("bhpn,bhn->bhp", s, Cf[:, t]))
+    return torch.stack(ys, 1)
+
+
+class Mamba2Mixer(nn.Module):
+    """Mamba-2 mixer; parameter names follow Megatron's ``MambaMixer`` (``in_proj``, ``conv1d``, ``dt_bias``, ``A_log``, ``D``,
+    ``norm``, ``out_proj``)."""
+
+    def __init__(self, cfg, layer_idx: int, device, tp: int):
+        super().__init__()
+        assert tp == 1, "the Mamba mixer is not built for tensor parallelism"
+        self.cfg = cfg
+        h, dt = cfg.hidden_size, cfg.torch_dtype
+        self.d_inner = cfg.mamba_expand * h
+        self.headdim = cfg.mamba_head_dim
+        self.nheads = cfg.mamba_num_heads or self.d_inner // self.headdim
+        assert self.nheads * self.headdim == self.d_inner, "mamba_expand * hidden_size must equal heads * head_dim"
+        self.ngroups, self.d_state = cfg.mamba_num_groups, cfg.mamba_state_dim
+        assert self.nheads % self.ngroups == 0
+        self.conv_dim = self.d_inner + 2 * self.ngroups * self.d_state
+        std = cfg.init_method_std
+        self.in_proj = nn.Module()
+        self.in_proj.register_parameter("layer_norm_weight", nn.Parameter(torch.ones(h, dtype=dt, device=device)))
+        self.in_proj.register_parameter("weight", _param((2 * self.d_inner + 2 * self.ngroups * self.d_state + self.nheads, h),
+                                                         std, dt, device))
+        self.conv1d = nn.Module()
+        self.conv1d.register_parameter("weight", _param((self.conv_dim, 1, cfg.mamba_d_conv), std * 5, dt, device))
+        self.conv1d.register_parameter("bias", nn.Parameter(torch.zeros(self.conv_dim, dtype=dt, device=device)))
+        # dt bias such that softplus(bias) is log-uniform in [1e-3, 1e-1]; A in [1, 16]: the published initialisation
+        u = torch.rand(self.nheads, device=device)
+        dt0 = torch.exp(u * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3)).clamp(min=1e-4)
+        self.dt_bias = nn.Parameter((dt0 + torch.log(-torch.expm1(-dt0))).float())
+        self.A_log = nn.Parameter(torch.log(torch.empty(self.nheads, device=device).uniform_(1, 16)).float())
+        self.D = nn.Parameter(torch.ones(self.nheads, dtype=torch.float32, device=device))
+        self.norm = nn.Module()
+        self.norm.register_parameter("weight", nn.Parameter(torch.ones(self.d_inner, dtype=dt, device=device)))
+        self.out_proj = nn.Module()
+        self.out_proj.register_parameter("weight", _param((h, self.d_inner), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
+        for w in (self.in_proj.weight, self.out_proj.weight):
+            w._is_weight = True
+        for p in (self.dt_bias, self.A_log, self.D):
+            p._no_weight_decay = True
+
+    def forward(self, hidden, residual, rope, batch):
+        cfg = self.cfg
+        assert ps.get_state().cp == 1, "the Mamba mixer is not built for context parallelism"
+        y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        zxbcdt = gemm.linear(y, self.in_proj.weight)
+        T = zxbcdt.shape[0]
+        seq = T // batch
+        di, gn = self.d_inner, self.ngroups * self.d_state
+        z, xBC, dt = zxbcdt[:, :di], zxbcdt[:, di:di + self.conv_dim], zxbcdt[:, di + self.conv_dim:]
+        xBC = F.silu(causal_depthwise_conv(xBC, self.conv1d.weight[:, 0, :], self.conv1d.bias, batch))
+        x = xBC[:, :di].view(batch, seq, self.nheads, self.headdim)
+        B = xBC[:, di:di + gn].view(batch, seq, self.ngroups, self.d_state)
+        C = xBC[:, di + gn:].view(batch, seq, self.ngroups, self.d_state)
+        dtp = F.softplus(dt.float() + self.dt_bias).view(batch, seq, self.nheads)
+        A = -torch.exp(self.A_log.float())
+        yss = ssd_chunked(x, dtp, A, B, C, cfg.mamba_chunk_size)
+        yss = yss + x.float() * self.D[None, None, :, None]
+        yss = yss.reshape(T, di)
+        # gated RMSNorm over each group's share of the inner dimension: norm(y * silu(z)) * weight
+        gated = (yss * F.silu(z.float())).view(T, self.ngroups, di // self.ngroups)
+        gated = gated * torch.rsqrt(gated.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon)
+        out = (gated.view(T, di) * self.norm.weight.float()).to(hidden.dtype)
+        return gemm.linear(out.contiguous(), self.out_proj.weight), xsum

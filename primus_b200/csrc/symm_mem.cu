@@ -116,6 +116,15 @@ int pb_probe_p2p(int* matrix_out, int max_dev, int* ndev_out, int* caps_out) {
   return 0;
 }
 
+// One device-to-device copy on the GPU's copy engines (no SM work): `src` may be a peer's memory mapped into this
+// process.  The parameter all-gather of the distributed optimizer issues one of these per peer and bucket on a side
+// stream, which leaves every SM to the compute stream (the role of the reference's SDMA all-gather,
+// primus/backends/megatron/core/distributed/sdma_param_gather.py).
+int pb_copy_engine_pull(void* dst, const void* src, long bytes, cudaStream_t s) {
+  if (bytes <= 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, s);
+}
+
 int pb_flag_set(int* flag, int value, cudaStream_t s) {
   flag_set_kernel<<<1, 1, 0, s>>>(flag, value);
   return (int)cudaGetLastError();

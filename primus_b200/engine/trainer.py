@@ -128,6 +128,10 @@ class TrainConfig:
     decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
+    # with fused_dp_optimizer: the updated parameter shards are pulled by the copy engines on a side stream (one
+    # cudaMemcpyAsync per peer and bucket, no SM time) instead of being stored to the peers by the AdamW kernel; also
+    # switched on by ENABLE_SDMA_ALLGATHER=1, the reference's switch for its copy-engine parameter all-gather
+    param_gather_copy_engine: bool = False
     profile: bool = False
     profile_step_start: int = 3
     profile_step_end: int = 4
@@ -346,6 +350,12 @@ class Trainer:
                 train_cfg.use_distributed_optimizer, train_cfg.overlap_grad_reduce, True, self.comm_stream,
                 extra_grad_scale=float(st.edp) / float(st.dp * st.cp),
                 grad_reduce_in_bf16=train_cfg.grad_reduce_in_bf16))
+        if train_cfg.param_gather_copy_engine or os.environ.get("ENABLE_SDMA_ALLGATHER", "0") == "1":
+            for buf in self.buffers:
+                buf.copy_engine_gather = buf.symmetric and buf.odc is None
+            if not any(buf.copy_engine_gather for buf in self.buffers):
+                self.log("param_gather_copy_engine needs fused_dp_optimizer with more than one data-parallel rank on "
+                         "GPUs: the parameter all-gather stays on its default path")
         norm_groups = [st.mp_group] if (st.tp > 1 or st.pp > 1) else []
         from ..parallel import matrix_optimizers
 
@@ -382,11 +392,11 @@ class Trainer:
         embedding buckets at its start and for the final norm / output layer buckets before the head."""
         tc = self.tcfg
         active = tc.overlap_param_gather and tc.use_distributed_optimizer and not self._emb_primary and \
-            not self._emb_replica and any(b.dp_size > 1 and not b.symmetric for b in self.buffers)
+            not self._emb_replica and any(b.dp_size > 1 and (not b.symmetric or b.copy_engine_gather) for b in self.buffers)
         self.optimizer.overlap_param_gather = bool(active)
         if tc.overlap_param_gather and not active and any(b.dp_size > 1 for b in self.buffers):
-            self.log("overlap_param_gather is off on this run (it needs the distributed optimizer on the NCCL path and "
-                     "word embeddings that are not shared between pipeline stages)")
+            self.log("overlap_param_gather is off on this run (it needs the distributed optimizer on the NCCL or the "
+                     "copy-engine path and word embeddings that are not shared between pipeline stages)")
         if not active:
             return
 

@@ -90,6 +90,9 @@ class ParamGradBuffer:
         self.numel = cur
         self.buckets = buckets
         self.symmetric = bool(symmetric and dp_size > 1 and device.type == "cuda" and self.param_dtype == torch.bfloat16)
+        # parameter all-gather by copy-engine pulls on a side stream instead of P2P stores from the AdamW kernel
+        self.copy_engine_gather = False
+        self._ce_stream = None
         if self.symmetric:
             # peer-mapped buffers: the fused optimizer kernels read peers' gradients and write peers' parameters
             from .symm_mem import SymmetricBuffer
@@ -287,6 +290,35 @@ class ParamGradBuffer:
             b.ag_handle = dist.all_gather_into_tensor(full, self.param_data[s:e], group=self.dp_group,
                                                       async_op=async_op)
 
+    def start_param_sync_copy_engine(self):
+        """Parameter all-gather on the copy engines: after a device barrier (every rank has written its updated shard
+        into its symmetric parameter buffer) this rank pulls the other ranks' shards of every bucket with one
+        ``cudaMemcpyAsync`` each on a side stream -- no SM runs for the transfer -- and records an event per bucket that
+        ``wait_bucket_params`` makes the compute stream wait for.  Buckets go in forward order and the source ranks are
+        rotated so that the ranks do not all read from the same peer at once.  The next overwrite of a shard happens
+        after the following step's gradient reduction, which every rank reaches only after its forward pass has waited
+        for these copies.  (The reference's SDMA parameter all-gather:
+        primus/backends/megatron/patches/parallelism/sdma_param_all_gather_patches.py:62-124.)"""
+        from ..ops import _lib
+
+        assert self.symmetric and self.odc is None
+        if self._ce_stream is None:
+            self._ce_stream = torch.cuda.Stream(device=self.param_data.device)
+        cs = self._ce_stream
+        cs.wait_stream(torch.cuda.current_stream())
+        esz = self.param_data.element_size()
+        with torch.cuda.stream(cs):
+            self.sym_param.barrier(1)
+            for b in reversed(self.buckets):
+                n = (b.end - b.start) // self.dp_size
+                for k in range(1, self.dp_size):
+                    r = (self.dp_rank + k) % self.dp_size
+                    lo = b.start + r * n
+                    _lib.call("copy_engine_pull", self.param_data[lo:lo + n], self.sym_param.peer_ptr(r, lo * esz), n * esz)
+                ev = torch.cuda.Event()
+                ev.record(cs)
+                b.ag_handle = _EventHandle(ev)
+
     def wait_bucket_params(self, b: Bucket):
         """Make the current stream wait for the bucket's parameter all-gather (no-op when none is pending)."""
         h = b.ag_handle
@@ -307,6 +339,16 @@ class ParamGradBuffer:
     def finish_param_sync(self):
         for b in self.buckets:
             self.wait_bucket_params(b)
+
+
+class _EventHandle:
+    """Completion handle of work on a side stream: ``wait()`` makes the current stream wait for the recorded event."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
 
 
 class DistributedOptimizer:
@@ -485,7 +527,7 @@ class DistributedOptimizer:
             for lo, hi, mult in st["wd_ranges"]:
                 hi4 = min(-(-hi // 4) * 4, st["e"])  # ranges end on parameter boundaries; padding follows
                 a, b_ = lo - st["s"], hi4 - st["s"]
-                if buf.symmetric:
+                if buf.symmetric and not buf.copy_engine_gather:
                     _lib.call("dp_adamw_allgather", tbl, buf.dp_size, buf.dp_rank, lo, hi4 - lo, st["master"][a:b_],
                               st["m"][a:b_], st["v"][a:b_], buf.grad_data[lo:hi4], float(lr), float(self.betas[0]),
                               float(self.betas[1]), float(self.eps), float(wd * mult), float(bc1), float(bc2),
@@ -496,7 +538,11 @@ class DistributedOptimizer:
                                           eps=self.eps, weight_decay=wd * mult, step=self.step_count,
                                           grad_scale=self.coef, skip=self.skip)
         for buf in self.buffers:
-            if buf.symmetric:
+            if buf.symmetric and buf.copy_engine_gather:
+                buf.start_param_sync_copy_engine()
+                if not self.overlap_param_gather:
+                    buf.finish_param_sync()
+            elif buf.symmetric:
                 buf.sym_param.barrier(0)  # all parameter shards have landed everywhere
             else:
                 buf.start_param_sync(async_op=False)

@@ -54,6 +54,10 @@ def test_overlapped_variants_match_the_plain_nccl_path(tmp_path):
         "nccl_overlap": (False, dict(overlap_grad_reduce=True, overlap_param_gather=True), 1e-6),
         "fused_overlap": (True, dict(overlap_grad_reduce=True), 2e-3),
         "bf16_reduce": (False, dict(overlap_grad_reduce=True, grad_reduce_in_bf16=True), 2e-2),
+        # parameter all-gather by copy-engine pulls on a side stream, with and without per-layer waits
+        "copy_engine": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True), 2e-3),
+        "copy_engine_overlap": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True,
+                                           overlap_param_gather=True), 2e-3),
         # on-demand communication: gradients pushed into the owners' accumulators with peer atomics, parameters pulled
         "odc": (False, dict(enable_odc=True, overlap_grad_reduce=True), 2e-3),
     }

@@ -767,6 +767,10 @@ class Trainer:
                     break
                 if tc.exit_duration_in_mins and (time.time() - start_wall) / 60.0 > tc.exit_duration_in_mins:
                     break
+            if any(getattr(buf, "copy_engine_gather", False) for buf in self.buffers):
+                # peers pull this rank's parameter shards: do not return (and possibly exit) while they are being read
+                self.finish_param_sync()
+                torch.cuda.current_stream().synchronize()
         finally:
             from . import checkpoint as _ckpt
 

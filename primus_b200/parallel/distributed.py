@@ -318,6 +318,12 @@ class ParamGradBuffer:
                 ev = torch.cuda.Event()
                 ev.record(cs)
                 b.ag_handle = _EventHandle(ev)
+            # nobody may free or overwrite a shard that a peer is still reading: a second barrier behind the copies.
+            # During training the next step's gradient reduction already orders this; at the end of a run (or before
+            # the buffers are released) ``finish_param_sync`` waits for it, so no rank leaves while it is being read.
+            self.sym_param.barrier(2)
+            self._ce_done = torch.cuda.Event()
+            self._ce_done.record(cs)
 
     def wait_bucket_params(self, b: Bucket):
         """Make the current stream wait for the bucket's parameter all-gather (no-op when none is pending)."""
@@ -339,6 +345,9 @@ class ParamGradBuffer:
     def finish_param_sync(self):
         for b in self.buckets:
             self.wait_bucket_params(b)
+        if getattr(self, "_ce_done", None) is not None:
+            torch.cuda.current_stream().wait_event(self._ce_done)
+            self._ce_done = None
 
 
 class _EventHandle:

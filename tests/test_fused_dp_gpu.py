@@ -26,7 +26,7 @@ def _worker(rank, world, fused, outp, extra=None):
     tr.finish_param_sync()
     torch.cuda.synchronize()
     _lib.check_status()
-    checksum = float(sum(p.float().abs().sum() for p in tr.model.parameters()))
+    checksum = float(sum(p.detach().float().abs().sum() for p in tr.model.parameters()))
     if rank == 0:
         json.dump({"losses": losses, "checksum": checksum, "symmetric": bool(tr.buffers[0].symmetric)}, open(outp, "w"))
 
@@ -43,31 +43,40 @@ def test_fused_dp_optimizer_matches_nccl(tmp_path):
     assert abs(ra["checksum"] - rb["checksum"]) <= 1e-3 * ra["checksum"]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_overlapped_variants_match_the_plain_nccl_path(tmp_path):
-    """Per-bucket overlap of the gradient reduction (NCCL and fused), bf16 on the wire, and the asynchronous parameter
-    all-gather with per-layer waits must not change the training trajectory."""
-    base = str(tmp_path / "base.json")
+VARIANTS = {
+    "nccl_overlap": (False, dict(overlap_grad_reduce=True, overlap_param_gather=True), 1e-6),
+    "fused_overlap": (True, dict(overlap_grad_reduce=True), 2e-3),
+    "bf16_reduce": (False, dict(overlap_grad_reduce=True, grad_reduce_in_bf16=True), 2e-2),
+    # parameter all-gather by copy-engine pulls on a side stream, with and without per-layer waits
+    "copy_engine": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True), 2e-3),
+    "copy_engine_overlap": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True,
+                                       overlap_param_gather=True), 2e-3),
+    # on-demand communication: gradients pushed into the owners' accumulators with peer atomics, parameters pulled
+    "odc": (False, dict(enable_odc=True, overlap_grad_reduce=True), 2e-3),
+}
+
+
+@pytest.fixture(scope="module")
+def plain_nccl_run(tmp_path_factory):
+    base = str(tmp_path_factory.mktemp("dp_base") / "base.json")
     run_ranks(_worker, 2, "nccl", args=(False, base), timeout=240)
-    ref = json.load(open(base))
-    cases = {
-        "nccl_overlap": (False, dict(overlap_grad_reduce=True, overlap_param_gather=True), 1e-6),
-        "fused_overlap": (True, dict(overlap_grad_reduce=True), 2e-3),
-        "bf16_reduce": (False, dict(overlap_grad_reduce=True, grad_reduce_in_bf16=True), 2e-2),
-        # parameter all-gather by copy-engine pulls on a side stream, with and without per-layer waits
-        "copy_engine": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True), 2e-3),
-        "copy_engine_overlap": (True, dict(overlap_grad_reduce=True, param_gather_copy_engine=True,
-                                           overlap_param_gather=True), 2e-3),
-        # on-demand communication: gradients pushed into the owners' accumulators with peer atomics, parameters pulled
-        "odc": (False, dict(enable_odc=True, overlap_grad_reduce=True), 2e-3),
-    }
-    for name, (fused, extra, tol) in cases.items():
-        outp = str(tmp_path / f"{name}.json")
-        run_ranks(_worker, 2, "nccl", args=(fused, outp, extra), timeout=240)
-        got = json.load(open(outp))
-        for x, y in zip(ref["losses"], got["losses"]):
-            assert abs(x - y) <= tol * max(1.0, abs(x)), (name, ref, got)
-        assert abs(ref["checksum"] - got["checksum"]) <= max(tol, 1e-3) * ref["checksum"], name
+    return json.load(open(base))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_overlapped_variants_match_the_plain_nccl_path(name, plain_nccl_run, tmp_path):
+    """Per-bucket overlap of the gradient reduction (NCCL and fused), bf16 on the wire, the asynchronous parameter
+    all-gather with per-layer waits (NCCL or copy engines) and on-demand communication must not change the training
+    trajectory."""
+    ref = plain_nccl_run
+    fused, extra, tol = VARIANTS[name]
+    outp = str(tmp_path / f"{name}.json")
+    run_ranks(_worker, 2, "nccl", args=(fused, outp, extra), timeout=240)
+    got = json.load(open(outp))
+    for x, y in zip(ref["losses"], got["losses"]):
+        assert abs(x - y) <= tol * max(1.0, abs(x)), (name, ref, got)
+    assert abs(ref["checksum"] - got["checksum"]) <= max(tol, 1e-3) * ref["checksum"], name
 
 
 def _fsdp_worker(rank, world, fsdp, outp):

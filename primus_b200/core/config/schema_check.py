@@ -37,7 +37,7 @@ INERT_KEYS = {
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "generate_tracelens_report", "straggler_ctrlr_port",
     "non_persistent_ckpt_type", "non_persistent_save_interval", "weight_deosc", "weight_deosc_period",
-    "weight_deosc_ratio", "sft_grad_sanitize", "sft_pack_cache_dir", "trainable", "mlflow_run_name",
+    "weight_deosc_ratio", "sft_grad_sanitize", "trainable", "mlflow_run_name",
     "log_throughput", "log_timers_to_tensorboard", "torch_profiler_record_shapes", "torch_profiler_use_gzip",
     "torch_profiler_with_stack", "use_tp_pp_dp_mapping", "offload_ops",
     # switches between the reference's two pipeline implementations (one runtime here; the schedule is chosen with

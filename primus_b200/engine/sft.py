@@ -14,6 +14,7 @@
 from __future__ import annotations
 
 import json
+import os
 import random
 from dataclasses import dataclass
 from typing import Callable, Optional
@@ -153,13 +154,13 @@ class PackedSFTDataset:
     role of the packed-sequence (THD) parameters of the reference (sft/forward_step.py:184-232)."""
 
     def __init__(self, base: SFTDataset, algorithm: str = "first_fit_decreasing", seed: int = 0, align: int = 1,
-                 boundaries: bool = True):
+                 boundaries: bool = True, bins: Optional[list] = None):
         self.base = base
         self.boundaries = boundaries
         self.align = max(1, int(align))
         assert base.seq_length % self.align == 0
         lengths = [-(-l // self.align) * self.align for l in base.lengths()]
-        self.bins = pack_bins(lengths, base.seq_length, algorithm, seed)
+        self.bins = bins if bins is not None else pack_bins(lengths, base.seq_length, algorithm, seed)
         self.max_docs = base.seq_length // self.align + 1 if self.align > 1 else base.seq_length + 1
 
     def __len__(self):
@@ -194,6 +195,141 @@ class PackedSFTDataset:
     def packing_efficiency(self) -> float:
         used = sum(min(l, self.base.seq_length) for l in self.base.lengths())
         return used / (len(self.bins) * self.base.seq_length)
+
+
+# ------------------------------------------------------------------------------------------------ pack cache
+PACK_FORMAT_VERSION = 1
+
+
+def pack_cache_dir(configured: Optional[str] = None) -> str:
+    """Directory of cached tokenised / packed SFT data: the configured ``sft_pack_cache_dir``, else
+    ``$PRIMUS_PACK_CACHE_DIR``, ``$HF_DATASETS_CACHE/primus_packed``, ``$HF_HOME/primus_packed``,
+    ``~/.cache/primus_packed_sft`` in that order (the reference's resolution, sft/packing.py:389-411)."""
+    base = configured or os.environ.get("PRIMUS_PACK_CACHE_DIR")
+    if not base:
+        for var in ("HF_DATASETS_CACHE", "HF_HOME"):
+            if os.environ.get(var):
+                base = os.path.join(os.environ[var], "primus_packed")
+                break
+    base = base or os.path.expanduser("~/.cache/primus_packed_sft")
+    os.makedirs(base, exist_ok=True)
+    return base
+
+
+def tokenizer_identity(tokenizer) -> str:
+    """A stable name for the tokenizer in cache keys (``$PRIMUS_PACK_TOKENIZER_ID`` overrides it)."""
+    if os.environ.get("PRIMUS_PACK_TOKENIZER_ID"):
+        return os.environ["PRIMUS_PACK_TOKENIZER_ID"]
+    for attr in ("name_or_path", "tokenizer_model_name", "vocab_file"):
+        v = getattr(tokenizer, attr, None)
+        if isinstance(v, str) and v:
+            return v
+    return f"{type(tokenizer).__name__}_vocab{getattr(tokenizer, 'vocab_size', None)}"
+
+
+def pack_cache_key(path: str, fmt: str, seq_length: int, pad_id: int, tokenizer_id: str, answer_only: bool,
+                   algorithm: str, align: int, seed: int) -> str:
+    """16 hex digits that change with anything that changes the tokenised or packed result, including the data file's
+    size and modification time."""
+    import hashlib
+
+    try:
+        st = os.stat(path)
+        stamp = f"{st.st_size}:{int(st.st_mtime)}"
+    except OSError:
+        stamp = "?"
+    blob = "|".join(str(x) for x in (PACK_FORMAT_VERSION, os.path.abspath(path), stamp, fmt, seq_length, pad_id,
+                                     tokenizer_id, int(answer_only), algorithm, align, seed))
+    return hashlib.sha256(blob.encode()).hexdigest()[:16]
+
+
+def load_or_build_packed(path: str, tokenizer, seq_length: int, fmt: str, answer_only: bool, algorithm: str, seed: int,
+                         align: int, boundaries: bool, cache_dir: Optional[str] = None, log=None) -> "PackedSFTDataset":
+    """``PackedSFTDataset`` for a jsonl file through the pack cache: tokenisation and bin packing of a large SFT set
+    take minutes, so their results (token ids, loss masks, bins) are stored once per cache key and every later run --
+    and every other rank of this run -- loads them.  Rank 0 of a job builds; the file appears atomically (rename)."""
+    d = pack_cache_dir(cache_dir)
+    key = pack_cache_key(path, fmt, seq_length, 0, tokenizer_identity(tokenizer), answer_only, algorithm, align, seed)
+    f = os.path.join(d, f"packed_{key}.pt")
+    if os.path.exists(f):
+        blob = torch.load(f, weights_only=False)
+        base = SFTDataset([], tokenizer, seq_length, fmt, answer_only)
+        base.samples = blob["samples"]
+        ds = PackedSFTDataset(base, algorithm, seed, align, boundaries, bins=blob["bins"])
+        if log:
+            log(f"[sft] packed dataset loaded from cache {f} ({len(base)} samples, {len(ds)} bins)")
+        return ds
+    base = SFTDataset.from_jsonl(path, tokenizer, seq_length, fmt, answer_only)
+    ds = PackedSFTDataset(base, algorithm, seed, align, boundaries)
+    tmp = f + f".tmp{os.getpid()}"
+    torch.save({"version": PACK_FORMAT_VERSION, "samples": base.samples, "bins": ds.bins}, tmp)
+    os.replace(tmp, f)
+    if log:
+        log(f"[sft] packed dataset built and cached at {f} ({len(base)} samples, {len(ds)} bins, "
+            f"efficiency {ds.packing_efficiency():.3f})")
+    return ds
+
+
+# ------------------------------------------------------------------------------------------------ MLPerf packed data
+MLPERF_FILES = ("train.npy", "validation.npy", "packed_metadata.jsonl")
+
+
+def is_mlperf_packed_dir(path: str) -> bool:
+    return os.path.isdir(path) and os.path.exists(os.path.join(path, "train.npy")) and \
+        os.path.exists(os.path.join(path, "packed_metadata.jsonl"))
+
+
+class MLPerfPackedDataset:
+    """Pre-tokenised, pre-packed SFT data in the layout of the MLPerf Llama-2-70B LoRA benchmark: ``train.npy`` /
+    ``validation.npy`` hold an object array of dicts ``{input_ids: int32[L], loss_mask: list[L], seq_start_id: list}``
+    and ``packed_metadata.jsonl`` the packing parameters.  Nothing is re-tokenised or re-packed; an item is one
+    stored pack with labels shifted by one inside every segment (no target crosses a segment start), per-segment
+    position ids and the segment boundaries for attention.  Counterpart of the reference's loader
+    (primus/backends/megatron/sft/mlperf_packed_dataset.py)."""
+
+    def __init__(self, directory: str, split: str = "train", seq_length: Optional[int] = None, pad_id: int = 0,
+                 align: int = 1, boundaries: bool = True):
+        import numpy as np
+
+        f = os.path.join(directory, "train.npy" if split == "train" else "validation.npy")
+        self.packs = np.load(f, allow_pickle=True)
+        with open(os.path.join(directory, "packed_metadata.jsonl")) as fh:
+            txt = fh.read().strip()
+        meta = json.loads(txt) if txt.startswith("[") else [json.loads(l) for l in txt.splitlines() if l.strip()]
+        self.metadata = meta[0] if meta else {}
+        self.seq_length = int(seq_length or self.metadata.get("dataset_max_seqlen") or len(self.packs[0]["input_ids"]))
+        self.pad_id, self.align, self.boundaries = pad_id, max(1, int(align)), boundaries
+        self.max_docs = self.seq_length // self.align + 1 if self.align > 1 else 64
+
+    def __len__(self):
+        return len(self.packs)
+
+    def __getitem__(self, i: int) -> dict:
+        rec = self.packs[i % len(self.packs)]
+        L = self.seq_length
+        ids = [int(x) for x in rec["input_ids"]][:L]
+        mask = [float(x) for x in rec["loss_mask"]][:L]
+        n = len(ids)
+        starts = sorted({int(s) for s in rec.get("seq_start_id", [0]) if 0 <= int(s) < n} | {0})
+        ends = starts[1:] + [n]
+        tokens = ids + [self.pad_id] * (L - n)
+        labels = [self.pad_id] * L
+        lmask = [0.0] * L
+        pos = [0] * L
+        for s, e in zip(starts, ends):
+            for t in range(s, e):
+                pos[t] = t - s
+                if t + 1 < e:                      # the target of a position is the next token of the same segment
+                    labels[t] = ids[t + 1]
+                    lmask[t] = mask[t + 1]
+        item = {"tokens": torch.tensor(tokens, dtype=torch.int64), "labels": torch.tensor(labels, dtype=torch.int64),
+                "loss_mask": torch.tensor(lmask, dtype=torch.float32), "position_ids": torch.tensor(pos, dtype=torch.int64)}
+        if self.boundaries:
+            cu = starts + [n] + ([L] if n < L else [])
+            if self.align > 1 and any(c % self.align for c in cu):
+                cu = [0, L]            # segments that do not sit on kernel block boundaries: one causal segment
+            item["host_cu_seqlens"] = torch.tensor(cu + [-1] * (self.max_docs + 1 - len(cu)), dtype=torch.int32)
+        return item
 
 
 # ------------------------------------------------------------------------------------------------ LoRA
@@ -313,9 +449,34 @@ class SFTTrainer(PretrainTrainer):
                     tok = AutoTokenizer.from_pretrained(p["tokenizer_model"])
                 except Exception:  # noqa: BLE001  (offline: keep the byte tokenizer)
                     pass
-            ds = SFTDataset.from_jsonl(path, tok, eng.tcfg.seq_length, p.get("sft_dataset_format", "alpaca"),
-                                       bool(p.get("sft_answer_only_loss", True)))
-            if p.get("sft_lb_mini"):
+            reset = bool(p.get("reset_attention_mask", True))
+            align = 128 if (reset and eng.is_cuda) else 1
+            log0 = eng.log if eng.st.rank == 0 else None
+            if is_mlperf_packed_dir(path):
+                # pre-tokenised, pre-packed benchmark data: used as stored
+                ds = MLPerfPackedDataset(path, "train", eng.tcfg.seq_length, align=align, boundaries=reset)
+                if log0:
+                    log0(f"[sft] MLPerf packed dataset {path}: {len(ds)} packs of {ds.seq_length} tokens")
+            elif p.get("sft_packing") and not p.get("sft_lb_mini") and p.get("sft_pack_cache", True):
+                args = (path, tok, eng.tcfg.seq_length, p.get("sft_dataset_format", "alpaca"),
+                        bool(p.get("sft_answer_only_loss", True)), p.get("sft_packing_algorithm", "first_fit_decreasing"),
+                        eng.tcfg.seed, align, reset, p.get("sft_pack_cache_dir"))
+                if eng.st.world_size > 1:          # rank 0 builds (or finds) the cache entry, the others then load it
+                    import torch.distributed as dist
+
+                    if eng.st.rank == 0:
+                        ds = load_or_build_packed(*args, log=log0)
+                    dist.barrier()
+                    if eng.st.rank != 0:
+                        ds = load_or_build_packed(*args)
+                else:
+                    ds = load_or_build_packed(*args, log=log0)
+            else:
+                ds = SFTDataset.from_jsonl(path, tok, eng.tcfg.seq_length, p.get("sft_dataset_format", "alpaca"),
+                                           bool(p.get("sft_answer_only_loss", True)))
+            if isinstance(ds, (MLPerfPackedDataset, PackedSFTDataset)):
+                pass
+            elif p.get("sft_lb_mini"):
                 # length-balanced dealing of every mini-batch over the data-parallel ranks, variable micro-batch counts
                 from .lb_mini import LBMiniStager
 

@@ -145,3 +145,62 @@ def test_attention_stays_inside_each_packed_document():
     assert torch.allclose(packed[:, :20], alone_a, atol=1e-5) and torch.allclose(packed[:, 20:], alone_b, atol=1e-5)
     leaky = m(tok, lab, position_ids=pos)
     assert torch.allclose(leaky[:, :20], alone_a, atol=1e-5) and not torch.allclose(leaky[:, 20:], alone_b, atol=1e-4)
+
+
+def test_pack_cache_roundtrip_and_key(tmp_path, monkeypatch):
+    """The packed dataset is built once, stored under a key that covers data file, tokenizer and packing settings, and
+    loaded bit-identically afterwards."""
+    import json as _json
+
+    from primus_b200.engine import sft as S
+
+    data = tmp_path / "d.jsonl"
+    recs = [{"instruction": f"q{i} " * (i % 7 + 1), "input": "", "output": f"a{i} " * (i % 5 + 1)} for i in range(40)]
+    data.write_text("\n".join(_json.dumps(r) for r in recs))
+    monkeypatch.setenv("PRIMUS_PACK_CACHE_DIR", str(tmp_path / "cache"))
+    tok = S.ByteTokenizer()
+    logs = []
+    a = S.load_or_build_packed(str(data), tok, 128, "alpaca", True, "first_fit_decreasing", 0, 1, True, log=logs.append)
+    files = list((tmp_path / "cache").glob("packed_*.pt"))
+    assert len(files) == 1 and "built and cached" in logs[-1]
+    b = S.load_or_build_packed(str(data), tok, 128, "alpaca", True, "first_fit_decreasing", 0, 1, True, log=logs.append)
+    assert "loaded from cache" in logs[-1] and len(a) == len(b) and a.bins == b.bins
+    for i in range(len(a)):
+        for k in a[i]:
+            assert torch.equal(a[i][k], b[i][k]), (i, k)
+    # another sequence length, algorithm or tokenizer is another entry
+    S.load_or_build_packed(str(data), tok, 256, "alpaca", True, "first_fit_decreasing", 0, 1, True)
+    S.load_or_build_packed(str(data), tok, 128, "alpaca", True, "first_fit", 0, 1, True)
+    monkeypatch.setenv("PRIMUS_PACK_TOKENIZER_ID", "other-tokenizer")
+    S.load_or_build_packed(str(data), tok, 128, "alpaca", True, "first_fit_decreasing", 0, 1, True)
+    assert len(list((tmp_path / "cache").glob("packed_*.pt"))) == 4
+    assert S.pack_cache_dir(str(tmp_path / "explicit")) == str(tmp_path / "explicit")
+
+
+def test_mlperf_packed_directory_is_used_as_stored(tmp_path):
+    """train.npy / packed_metadata.jsonl in the MLPerf layout: labels shifted inside each segment, no target across a
+    segment start, positions restart, boundaries exported."""
+    import json as _json
+
+    import numpy as np
+
+    from primus_b200.engine import sft as S
+
+    L = 16
+    packs = np.empty(2, dtype=object)
+    packs[0] = {"input_ids": np.arange(100, 100 + L, dtype=np.int32), "loss_mask": [0] * 4 + [1] * 12, "seq_start_id": [0]}
+    packs[1] = {"input_ids": np.arange(200, 200 + L, dtype=np.int32), "loss_mask": [0, 1] * 8, "seq_start_id": [0, 8]}
+    np.save(tmp_path / "train.npy", packs, allow_pickle=True)
+    np.save(tmp_path / "validation.npy", packs[:1], allow_pickle=True)
+    (tmp_path / "packed_metadata.jsonl").write_text(_json.dumps([{"max_samples_per_bin": 2, "dataset_max_seqlen": L}]))
+    assert S.is_mlperf_packed_dir(str(tmp_path)) and not S.is_mlperf_packed_dir(str(tmp_path / "train.npy"))
+    ds = S.MLPerfPackedDataset(str(tmp_path))
+    assert len(ds) == 2 and ds.seq_length == L
+    a = ds[0]
+    assert a["tokens"].tolist() == list(range(100, 116)) and a["labels"][:15].tolist() == list(range(101, 116))
+    assert a["loss_mask"].tolist() == [0.0] * 3 + [1.0] * 12 + [0.0]          # shifted by one, last position has no target
+    b = ds[1]
+    assert b["position_ids"].tolist() == list(range(8)) * 2
+    assert b["loss_mask"][7] == 0 and b["labels"][7] == 0                      # no target across the segment start
+    assert b["labels"][8] == 209 and b["host_cu_seqlens"][:3].tolist() == [0, 8, 16]
+    assert len(S.MLPerfPackedDataset(str(tmp_path), "validation")) == 1

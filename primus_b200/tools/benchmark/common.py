@@ -37,6 +37,10 @@ def emit(rows: list[dict], output: str | None = None, title: str = ""):
     if rows:
         print(f"\n== {title} ==" if title else "")
         print(tabulate(rows, headers="keys", floatfmt=".3f"))
-    if output:
+    if output and output.lower().endswith(".json"):
         with open(output, "w") as f:
             json.dump(rows, f, indent=1)
+    elif output:          # .md / .csv / .tsv / .jsonl (optionally .gz): the table writer picks the format
+        from ..report import write_records
+
+        write_records(output, rows, preamble=f"## {title}" if title else None)

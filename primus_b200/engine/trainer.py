@@ -59,7 +59,7 @@ class TrainConfig:
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     grad_reduce_in_bf16: bool = False    # bf16 on the wire for the data-parallel gradient reduction (fp32 accumulation)
-    num_seq_splits: int = 1              # sequence chunks per micro-batch inside a pipeline (only 1 is built)
+    num_seq_splits: int = 1              # sequence chunks per micro-batch that travel through the pipeline separately
     enable_optimizer_post_validation: bool = False        # pipeline parallel: update first, validate the global norm later
     enable_exact_optimizer_post_validation: bool = True   # restore from a snapshot (exact) instead of inverting the update
     enable_odc: bool = False             # on-demand communication: gradient pushes / parameter pulls, one meeting per step
@@ -210,11 +210,21 @@ class Trainer:
                  log_fn: Callable[[str], None] = print):
         self.mcfg, self.tcfg = model_cfg, train_cfg
         self.log = log_fn
-        if int(train_cfg.num_seq_splits or 1) != 1:
-            raise NotImplementedError(
-                "num_seq_splits > 1 (sequence chunks that travel through the pipeline separately, with attention over the "
-                "earlier chunks' keys and values and reversed chunk order in the backward pass) is not built; use context "
-                "parallelism or a larger pipeline_model_parallel_size to cut activation memory")
+        self.num_seq_splits = max(1, int(train_cfg.num_seq_splits or 1))
+        if self.num_seq_splits > 1:
+            # sequence chunks travel through the pipeline as separate units; attention keeps the earlier chunks' K / V
+            S = self.num_seq_splits
+            unit = 128 * S if str(device or "cuda").startswith("cuda") else S
+            assert train_cfg.seq_length % unit == 0, f"num_seq_splits = {S}: seq_length must be a multiple of {unit}"
+            bad = [n for n, on in (("context parallelism", model_cfg.context_parallel_size > 1),
+                                   ("multi-latent attention", model_cfg.multi_latent_attention),
+                                   ("Mamba / convolution mixers", model_cfg.model_type == "mamba" or bool(model_cfg.lfm_layer_types)),
+                                   ("activation recompute", bool(model_cfg.recompute_granularity)),
+                                   ("multi-token prediction", bool(model_cfg.mtp_num_layers)),
+                                   ("virtual pipeline stages", bool(model_cfg.virtual_pipeline_model_parallel_size)),
+                                   ("FSDP2", bool(train_cfg.use_torch_fsdp2))) if on]
+            if bad:
+                raise NotImplementedError(f"num_seq_splits > 1 is not built together with: {', '.join(bad)}")
         st = ps.get_state()
         if not st.initialized:
             st = ps.initialize_model_parallel(
@@ -518,7 +528,59 @@ class Trainer:
         out["_mask_total"] = mb["loss_mask"].sum()
         return out
 
+    def _seq_chunk(self, mb: dict, split: int) -> dict:
+        """Chunk ``split`` of ``num_seq_splits`` of a micro-batch along the sequence, with global position ids and the
+        whole micro-batch's loss-mask total (the loss normalisation must not depend on the chunking)."""
+        S = self.num_seq_splits
+        b, L = mb["tokens"].shape
+        c = L // S
+        sl = slice(split * c, (split + 1) * c)
+        out = {k: mb[k][:, sl].contiguous() for k in ("tokens", "labels", "loss_mask")}
+        pos = mb.get("position_ids")
+        out["position_ids"] = pos[:, sl].contiguous() if pos is not None else \
+            torch.arange(split * c, (split + 1) * c, device=mb["tokens"].device).expand(b, c).contiguous()
+        for k in ("_lb_mini_norm", "_mask_total"):
+            if k in mb:
+                out[k] = mb[k]
+        if "_mask_total" not in out and "_lb_mini_norm" not in out:
+            out["_mask_total"] = mb["loss_mask"].sum()
+        return out
+
+    def _forward_backward_seq_splits(self, micro_batches: list[dict]) -> torch.Tensor:
+        """No pipeline, ``num_seq_splits`` > 1: every micro-batch is forwarded chunk by chunk and its chunks' backward
+        passes run in reverse order (the activation footprint of the loss head and the MLPs is that of one chunk)."""
+        from ..ops import layers as _layers
+
+        model, S = self.model, self.num_seq_splits
+        total = self.loss_accum
+        total.zero_()
+        n = len(micro_batches)
+        try:
+            for i, mb in enumerate(micro_batches):
+                for buf in self.buffers:
+                    buf.is_last_microbatch = False
+                losses = []
+                for q in range(S):
+                    ch = self._seq_chunk(mb, q)
+                    _layers.SEQ_SPLIT.begin((i, 0), q, S)
+                    losses.append(model(ch["tokens"], ch["labels"], loss_weights=self._loss_weights(ch), unit_upstream=True,
+                                        position_ids=ch["position_ids"]))
+                for q in reversed(range(S)):
+                    for buf in self.buffers:       # the bucket reductions start with the very last backward pass only
+                        buf.is_last_microbatch = (i == n - 1 and q == 0)
+                    _layers.SEQ_SPLIT.begin((i, 0), q, S)
+                    losses[q].backward()
+                    total += losses[q].detach()
+                _layers.SEQ_SPLIT.drop((i, 0))
+        finally:
+            _layers.SEQ_SPLIT.clear()
+            for buf in self.buffers:
+                buf.is_last_microbatch = True
+        return total
+
     def forward_backward_no_pipelining(self, micro_batches: list[dict]) -> torch.Tensor:
+        if self.num_seq_splits > 1:
+            return self._forward_backward_seq_splits(micro_batches)
         model = self.model
         total = self.loss_accum
         total.zero_()

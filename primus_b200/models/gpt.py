@@ -99,7 +99,13 @@ class SelfAttention(nn.Module):
         if st.cp > 1 and (self.window or self.has_sinks or segments or cfg.attn_logit_softcapping):
             raise NotImplementedError("sliding-window / sink / per-document attention is not available under context "
                                       "parallelism")
-        if st.cp > 1 and cfg.cp_comm_type == "allgather":
+        if layers.SEQ_SPLIT.active:
+            if st.cp > 1 or self.window or self.has_sinks or segments or cfg.attn_logit_softcapping:
+                raise NotImplementedError("num_seq_splits > 1 is built for plain causal attention (no context "
+                                          "parallelism, sliding window, sinks, packed documents or soft-capping)")
+            ctx_out = layers.seq_split_rope_attention(id(self), qkv, cos, sin, pos, batch, self.hq, self.hkv, d,
+                                                      rot_dim=int(d * cfg.rotary_percent), scale=scale)
+        elif st.cp > 1 and cfg.cp_comm_type == "allgather":
             ctx_out = layers.allgather_cp_rope_attention(qkv, cos, sin, pos, batch, self.hq, self.hkv, d, st.cp_group,
                                                          st.cp, rot_dim=int(d * cfg.rotary_percent), causal=True,
                                                          scale=scale)
@@ -384,7 +390,9 @@ class GPTModel(nn.Module):
         else:
             hidden, residual, batch, seq = hidden_in
         device = hidden.device
-        cos, sin = self.rope_tables(device, seq * st.cp)   # a context-parallel rank holds seq / cp of every sequence
+        # a context-parallel rank holds seq / cp of every sequence; a sequence chunk inside a pipeline is 1 / num_splits
+        splits = layers.SEQ_SPLIT.num_splits if layers.SEQ_SPLIT.active else 1
+        cos, sin = self.rope_tables(device, seq * st.cp * splits)
         pos = None
         if batch > 1 or position_ids is not None:
             pos = (position_ids.reshape(-1).to(torch.int32) if position_ids is not None

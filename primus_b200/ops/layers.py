@@ -820,3 +820,127 @@ def hierarchical_cp_rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, a2a_gr
     out = out.reshape(batch, 2, a2a, part, hq_l * d).permute(2, 0, 1, 3, 4).reshape(a2a, Tl, hq_l * d).contiguous()
     got = _SeqHeadAllToAll.apply(out, a2a_group)                       # [a2a (head group), Tl, hq_l * d]
     return got.permute(1, 0, 2).reshape(Tl, hq * d)
+
+
+# ----------------------------------------------------------------------------------------------
+# Sequence splits inside a pipeline: a micro-batch travels through the stages as ``num_splits`` consecutive chunks of
+# its sequence.  Chunk j's queries attend to the keys of chunks 0..j, so every attention layer keeps the K / V of the
+# chunks it has already seen for that micro-batch, and the gradient a later chunk produces for an earlier chunk's K / V
+# waits in an accumulator until that chunk's own backward pass runs (the schedule runs the backward passes of a
+# micro-batch's chunks in reverse order).  The reference schedules such chunks (``num_seq_splits``,
+# primus/backends/megatron/core/pipeline_parallel/zerobubble/scheduler/seq1f1b.py:15-45) and slices the batch
+# (primus/backends/megatron/data_loader_store.py:45-70); the attention over the kept prefix is this engine's own.
+class SeqSplitState:
+    """What the pipeline runtime tells the attention layers about the chunk being processed."""
+
+    def __init__(self):
+        self.active = False
+        self.key = None           # (micro-batch, model chunk): one K / V cache per key and attention layer
+        self.split = 0
+        self.num_splits = 1
+        self.forward_only = False
+        self.cache: dict = {}     # (layer id, key) -> {"k": [batch, L, hkv, d], "v": ..., "dk": fp32 accumulator, "dv": ...}
+
+    def begin(self, key, split: int, num_splits: int, forward_only: bool = False):
+        self.active, self.key, self.split, self.num_splits, self.forward_only = True, key, split, num_splits, forward_only
+
+    def end(self):
+        self.active = False
+
+    def drop(self, key):
+        for k in [k for k in self.cache if k[1] == key]:
+            del self.cache[k]
+
+    def clear(self):
+        self.cache.clear()
+        self.active = False
+
+
+SEQ_SPLIT = SeqSplitState()
+
+
+class SeqSplitAttentionFn(torch.autograd.Function):
+    """Causal attention of one sequence chunk against the kept K / V prefix of its micro-batch (RoPE already applied
+    with the chunk's global positions).  q [batch * c, hq, d], k / v [batch * c, hkv, d]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, batch, scale, slot, split, num_splits, forward_only):
+        T, hq, d = q.shape
+        hkv, dv = k.shape[1], v.shape[2]
+        c = T // batch
+        q_off = split * c
+        kc, vc = k.reshape(batch, c, hkv, d), v.reshape(batch, c, hkv, dv)
+        if split == 0:
+            kf, vf = kc.contiguous(), vc.contiguous()
+        else:
+            kf = torch.cat([slot["k"], kc], dim=1)
+            vf = torch.cat([slot["v"], vc], dim=1)
+        assert kf.shape[1] == q_off + c, "sequence chunks of a micro-batch must reach an attention layer in order"
+        if split + 1 < num_splits:
+            slot["k"], slot["v"] = kf.detach(), vf.detach()
+        else:
+            slot.pop("k", None), slot.pop("v", None)
+        o = torch.empty(T, hq, dv, dtype=q.dtype, device=q.device)
+        lses = []
+        for b in range(batch):
+            qb = q[b * c:(b + 1) * c]
+            if q.is_cuda:
+                ob, lse = attention.flash_attn_fwd(qb, kf[b], vf[b], 1, True, scale, q_off)
+            else:
+                ob, lse = attention.attention_ref(qb, kf[b], vf[b], 1, True, scale, q_off)
+            o[b * c:(b + 1) * c] = ob
+            lses.append(lse)
+        ctx.save_for_backward(q, kf, vf, o, *lses)
+        ctx.meta = (batch, scale, slot, split, num_splits, c)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, kf, vf, o, *lses = ctx.saved_tensors
+        batch, scale, slot, split, num_splits, c = ctx.meta
+        hkv, d, dv = kf.shape[2], kf.shape[3], vf.shape[3]
+        q_off = split * c
+        L = q_off + c
+        do = do.contiguous()
+        dq = torch.empty_like(q)
+        if "dk" not in slot:        # the last chunk's backward comes first and sizes the accumulators
+            assert split == num_splits - 1, "the backward passes of a micro-batch's chunks must run in reverse order"
+            slot["dk"] = torch.zeros(batch, L, hkv, d, dtype=torch.float32, device=q.device)
+            slot["dv"] = torch.zeros(batch, L, hkv, dv, dtype=torch.float32, device=q.device)
+        for b in range(batch):
+            sl = slice(b * c, (b + 1) * c)
+            if q.is_cuda:
+                dqb, dkb, dvb = attention.flash_attn_bwd(do[sl], q[sl], kf[b], vf[b], o[sl], lses[b], 1, True, scale,
+                                                         q_off=q_off)
+            else:
+                with torch.enable_grad():
+                    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q[sl], kf[b], vf[b]))
+                    orf, _ = attention.attention_ref(qr, kr, vr, 1, True, scale, q_off)
+                    orf.backward(do[sl].float())
+                dqb, dkb, dvb = qr.grad.to(q.dtype), kr.grad, vr.grad
+            dq[sl] = dqb
+            slot["dk"][b, :L] += dkb.float()
+            slot["dv"][b, :L] += dvb.float()
+        dk = slot["dk"][:, q_off:L].reshape(batch * c, hkv, d).to(q.dtype)
+        dv_ = slot["dv"][:, q_off:L].reshape(batch * c, hkv, dv).to(q.dtype)
+        if split == 0:
+            slot.pop("dk"), slot.pop("dv")
+        return dq, dk, dv_, None, None, None, None, None, None
+
+
+def seq_split_rope_attention(layer_id, qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, scale=None):
+    """Packed-QKV causal attention of the chunk announced in ``SEQ_SPLIT`` (positions ``pos`` are global)."""
+    st = SEQ_SPLIT
+    T = qkv.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    q = qkv[:, : hq * d].reshape(T, hq, d)
+    k = qkv[:, hq * d: (hq + hkv) * d].reshape(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
+    if cos is not None:
+        rope_fn = fused.rope if qkv.is_cuda else fused.rope_ref
+        q = rope_fn(q, cos, sin, pos, rot_dim or d)
+        k = rope_fn(k, cos, sin, pos, rot_dim or d)
+    slot = st.cache.setdefault((layer_id, st.key), {})
+    out = SeqSplitAttentionFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), batch, scale, slot, st.split,
+                                    st.num_splits, st.forward_only)
+    return out.reshape(T, hq * d)

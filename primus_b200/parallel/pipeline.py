@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import gemm as gemm_ops
+from ..ops import layers as layers_ops
 from . import pipeline_schedules as sched
 from . import state as ps
 
@@ -60,7 +61,7 @@ def _p2p_shape(trainer, batch, seq):
 
 
 def _pos_ids(trainer, mb):
-    use = getattr(trainer, "use_position_ids", False) or trainer.st.cp > 1
+    use = getattr(trainer, "use_position_ids", False) or trainer.st.cp > 1 or getattr(trainer, "num_seq_splits", 1) > 1
     return mb.get("position_ids") if use else None
 
 
@@ -72,13 +73,15 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
     st = trainer.st
     pp, r = st.pp, st.pp_rank
     m = len(micro_batches)
-    key = (trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp)
+    nsplit = getattr(trainer, "num_seq_splits", 1)
+    key = (trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp) if nsplit == 1 else \
+        (trainer.tcfg.pipeline_schedule, pp, m, st.virtual_pp, nsplit)
     cache = getattr(trainer, "_pp_schedule_cache", {})
     if key not in cache:   # (a cost-driven table from ``replan_from_measurements`` replaces the entry later)
         algo = trainer.tcfg.pipeline_schedule
         if st.virtual_pp and st.virtual_pp > 1 and algo == "1f1b":
             algo = "interleaved"
-        cache[key] = sched.build_schedule(algo, pp, m, st.virtual_pp)
+        cache[key] = sched.build_schedule(algo, pp, m, st.virtual_pp, num_seq_splits=nsplit)
         trainer._pp_schedule_cache = cache
     sch = cache[key]
     chunks, placement = sch["chunks"], sch["placement"]
@@ -108,9 +111,13 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
         mem0 = torch.cuda.memory_allocated(dev) if (timeline is not None and trainer.is_cuda) else 0
         s = sched.stage_of(r, node.chunk, pp, placement)
         mb = micro_batches[node.mb]
+        if nsplit > 1:     # this node works on one sequence chunk; attention keeps the earlier chunks' keys and values
+            mb = trainer._seq_chunk(mb, node.split)
+            if node.kind in ("F", "B", "BW"):
+                layers_ops.SEQ_SPLIT.begin((node.mb, node.chunk), node.split, nsplit, forward_only)
         batch, seq = mb["tokens"].shape
         model = trainer.model_chunks[node.chunk]
-        k = (node.mb, node.chunk)
+        k = (node.mb, node.chunk) if nsplit == 1 else (node.mb, node.chunk, node.split)
         if node.kind == "F":
             if s == 0:
                 hidden_in = None
@@ -179,6 +186,11 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                     sends.append((dist.isend(x.grad, dst=global_rank(pr), group=bwd_g), x.grad))
         elif node.kind == "W":
             gemm_ops.WGRAD_STORE.flush(k)
+        if nsplit > 1:
+            layers_ops.SEQ_SPLIT.end()
+            done = (node.kind == "BW" and node.split == 0) or (forward_only and node.split == nsplit - 1)
+            if done:
+                layers_ops.SEQ_SPLIT.drop((node.mb, node.chunk))
         if timeline is not None:
             if trainer.is_cuda:
                 torch.cuda.synchronize()
@@ -186,6 +198,8 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
             timeline.add(node, t0, time.perf_counter(), t_in, (mem1 - mem0) if trainer.is_cuda else None)
     for h, _keep in sends:
         h.wait()
+    if nsplit > 1:
+        layers_ops.SEQ_SPLIT.clear()
     gemm_ops.WGRAD_STORE.flush_all()
     for buf in trainer.buffers:
         buf.is_last_microbatch = True

@@ -44,9 +44,10 @@ class Node:
     kind: str        # F | B | W | BW | RF | SF | RB | SB
     mb: int
     chunk: int = 0
+    split: int = 0   # sequence chunk of the micro-batch (schedules with sequence splits)
 
     def __repr__(self):
-        return f"{self.kind}{self.mb}" + (f".{self.chunk}" if self.chunk else "")
+        return f"{self.kind}{self.mb}" + (f".{self.chunk}" if self.chunk else "") + (f"s{self.split}" if self.split else "")
 
 
 def stage_of(rank: int, chunk: int, pp: int, placement: str = "interleaved") -> int:
@@ -76,6 +77,34 @@ def schedule_1f1b(pp: int, m: int) -> list[list[Node]]:
             seq.append(Node("BW", b)); b += 1
         while b < m:
             seq.append(Node("BW", b)); b += 1
+        table.append(seq)
+    return table
+
+
+def schedule_seq1f1b(pp: int, m: int, num_splits: int) -> list[list[Node]]:
+    """1F1B over sequence chunks: every micro-batch is ``num_splits`` units.  Forward passes run in (micro-batch, chunk)
+    order; the backward passes of a micro-batch run from its last chunk to its first, because a chunk's keys and values
+    collect gradients from all later chunks.  A rank therefore needs ``num_splits - 1`` more warm-up forwards than in
+    plain 1F1B before the first backward pass (the last chunk's) can start: ``pp - rank - 2 + num_splits`` in all
+    (the warm-up count of the reference's schedule,
+    primus/backends/megatron/core/pipeline_parallel/zerobubble/scheduler/seq1f1b.py:19-40)."""
+    S = num_splits
+    total = m * S
+
+    def fwd(i):
+        return Node("F", i // S, 0, i % S)
+
+    def bwd(i):
+        return Node("BW", i // S, 0, S - 1 - i % S)
+
+    table = []
+    for r in range(pp):
+        warm = min(pp - r - 2 + S, total)
+        seq = [fwd(i) for i in range(warm)]
+        for i in range(total - warm):
+            seq.append(fwd(warm + i))
+            seq.append(bwd(i))
+        seq += [bwd(i) for i in range(total - warm, total)]
         table.append(seq)
     return table
 
@@ -198,10 +227,16 @@ def schedule_greedy(pp: int, m: int, chunks: int = 1, placement: str = "interlea
     return table
 
 
-def build_schedule(algorithm: str, pp: int, num_microbatches: int, vpp: Optional[int] = None) -> dict:
+def build_schedule(algorithm: str, pp: int, num_microbatches: int, vpp: Optional[int] = None,
+                   num_seq_splits: int = 1) -> dict:
     """Returns {"table": per-rank node lists, "chunks": chunks per rank, "placement": ...}."""
     a = algorithm.lower().replace("_", "-")
     m = num_microbatches
+    if num_seq_splits > 1:
+        if a not in ("1f1b", "basic-1f1b", "seq1f1b") or (vpp and vpp > 1):
+            raise ValueError("num_seq_splits > 1 runs on the 1F1B schedule (no virtual stages, no B / W split)")
+        return {"table": schedule_seq1f1b(pp, m, num_seq_splits), "chunks": 1, "placement": "interleaved",
+                "algorithm": "seq1f1b", "num_seq_splits": num_seq_splits}
     if pp == 1:
         return {"table": [[n for i in range(m) for n in (Node("F", i), Node("BW", i))]], "chunks": 1,
                 "placement": "interleaved", "algorithm": a}
@@ -233,42 +268,50 @@ def expand_with_comm(table: list[list[Node]], pp: int, chunks: int, placement: s
             s = stage_of(r, n.chunk, pp, placement)
             if n.kind == "F":
                 if s > 0 and rank_of_stage(s - 1, pp, placement)[0] != r:
-                    res.append(Node("RF", n.mb, n.chunk))
+                    res.append(Node("RF", n.mb, n.chunk, n.split))
                 res.append(n)
                 if s < S - 1 and rank_of_stage(s + 1, pp, placement)[0] != r:
-                    res.append(Node("SF", n.mb, n.chunk))
+                    res.append(Node("SF", n.mb, n.chunk, n.split))
             elif n.kind in ("B", "BW"):
                 if s < S - 1 and rank_of_stage(s + 1, pp, placement)[0] != r:
-                    res.append(Node("RB", n.mb, n.chunk))
+                    res.append(Node("RB", n.mb, n.chunk, n.split))
                 res.append(n)
                 if s > 0 and rank_of_stage(s - 1, pp, placement)[0] != r:
-                    res.append(Node("SB", n.mb, n.chunk))
+                    res.append(Node("SB", n.mb, n.chunk, n.split))
             else:
                 res.append(n)
         out.append(res)
     return out
 
 
-def validate(table: list[list[Node]], pp: int, m: int, chunks: int, placement: str) -> None:
-    """Raises AssertionError unless the table is complete and executable without deadlock."""
+def validate(table: list[list[Node]], pp: int, m: int, chunks: int, placement: str, num_seq_splits: int = 1) -> None:
+    """Raises AssertionError unless the table is complete and executable without deadlock.  With sequence splits a
+    unit of work is a (micro-batch, sequence chunk) pair; a rank must forward the chunks of a micro-batch in order
+    and run their backward passes in reverse order."""
     S = pp * chunks
+    units = sorted((i, q) for i in range(m) for q in range(num_seq_splits))
     for r, seq in enumerate(table):
         comp = [n for n in seq if n.kind in ("F", "B", "W", "BW")]
         for c in range(chunks):
-            fs = [n.mb for n in comp if n.kind == "F" and n.chunk == c]
-            bs = [n.mb for n in comp if n.kind in ("B", "BW") and n.chunk == c]
-            assert sorted(fs) == list(range(m)), f"rank {r} chunk {c}: forwards {fs}"
-            assert sorted(bs) == list(range(m)), f"rank {r} chunk {c}: backwards {bs}"
-            nb = [n.mb for n in comp if n.kind == "B" and n.chunk == c]
-            ws = [n.mb for n in comp if n.kind == "W" and n.chunk == c]
+            fs = [(n.mb, n.split) for n in comp if n.kind == "F" and n.chunk == c]
+            bs = [(n.mb, n.split) for n in comp if n.kind in ("B", "BW") and n.chunk == c]
+            assert sorted(fs) == units, f"rank {r} chunk {c}: forwards {fs}"
+            assert sorted(bs) == units, f"rank {r} chunk {c}: backwards {bs}"
+            nb = [(n.mb, n.split) for n in comp if n.kind == "B" and n.chunk == c]
+            ws = [(n.mb, n.split) for n in comp if n.kind == "W" and n.chunk == c]
             assert sorted(nb) == sorted(ws), f"rank {r} chunk {c}: every B needs exactly one W"
         seen = set()
         for n in comp:
             if n.kind in ("B", "BW"):
-                assert ("F", n.mb, n.chunk) in seen, f"rank {r}: {n} before its forward"
+                assert ("F", n.mb, n.chunk, n.split) in seen, f"rank {r}: {n} before its forward"
+                assert n.split == num_seq_splits - 1 or ("B", n.mb, n.chunk, n.split + 1) in seen, \
+                    f"rank {r}: {n} before the backward of the next sequence chunk"
+            if n.kind == "F":
+                assert n.split == 0 or ("F", n.mb, n.chunk, n.split - 1) in seen, \
+                    f"rank {r}: {n} before the forward of the previous sequence chunk"
             if n.kind == "W":
-                assert ("B", n.mb, n.chunk) in seen, f"rank {r}: {n} before its B"
-            seen.add((n.kind if n.kind != "BW" else "B", n.mb, n.chunk))
+                assert ("B", n.mb, n.chunk, n.split) in seen, f"rank {r}: {n} before its B"
+            seen.add((n.kind if n.kind != "BW" else "B", n.mb, n.chunk, n.split))
     # executability: simulate with blocking dependencies
     ptr = [0] * pp
     fdone, bdone = set(), set()
@@ -280,18 +323,19 @@ def validate(table: list[list[Node]], pp: int, m: int, chunks: int, placement: s
             while ptr[r] < len(comp[r]):
                 n = comp[r][ptr[r]]
                 s = stage_of(r, n.chunk, pp, placement)
+                u = (n.mb, n.split)
                 if n.kind == "F":
-                    ok = s == 0 or (s - 1, n.mb) in fdone
+                    ok = s == 0 or (s - 1, u) in fdone
                 elif n.kind in ("B", "BW"):
-                    ok = (s, n.mb) in fdone and (s == S - 1 or (s + 1, n.mb) in bdone)
+                    ok = (s, u) in fdone and (s == S - 1 or (s + 1, u) in bdone)
                 else:
                     ok = True
                 if not ok:
                     break
                 if n.kind == "F":
-                    fdone.add((s, n.mb))
+                    fdone.add((s, u))
                 elif n.kind in ("B", "BW"):
-                    bdone.add((s, n.mb))
+                    bdone.add((s, u))
                 ptr[r] += 1
                 progress = True
     assert all(ptr[r] == len(comp[r]) for r in range(pp)), f"schedule deadlocks at {ptr}"
@@ -318,7 +362,7 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                 n = comp[r][ptr[r]]
                 s = stage_of(r, n.chunk, pp, placement)
                 if n.kind == "F":
-                    dep = 0.0 if s == 0 else fdone.get((s - 1, n.mb))
+                    dep = 0.0 if s == 0 else fdone.get((s - 1, n.mb, n.split))
                     if dep is None:
                         break
                     if s > 0 and rank_of_stage(s - 1, pp, placement)[0] != r:
@@ -326,9 +370,9 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                     cost = cost_f[s]
                     mem[r] += 1.0
                 elif n.kind in ("B", "BW"):
-                    if (s, n.mb) not in fdone:
+                    if (s, n.mb, n.split) not in fdone:
                         break
-                    dep = fdone[(s, n.mb)] if s == S - 1 else bdone.get((s + 1, n.mb))
+                    dep = fdone[(s, n.mb, n.split)] if s == S - 1 else bdone.get((s + 1, n.mb, n.split))
                     if dep is None:
                         break
                     if s < S - 1 and rank_of_stage(s + 1, pp, placement)[0] != r:
@@ -343,9 +387,9 @@ def simulate(table: list[list[Node]], pp: int, chunks: int, placement: str, cost
                 t[r] = start + cost
                 busy[r] += cost
                 if n.kind == "F":
-                    fdone[(s, n.mb)] = t[r]
+                    fdone[(s, n.mb, n.split)] = t[r]
                 elif n.kind in ("B", "BW"):
-                    bdone[(s, n.mb)] = t[r]
+                    bdone[(s, n.mb, n.split)] = t[r]
                 ptr[r] += 1
                 progress = True
     makespan = max(t)

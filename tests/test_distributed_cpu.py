@@ -47,6 +47,9 @@ CASES = {
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
+    # every micro-batch travels through the pipeline as two / four sequence chunks (attention over the kept K / V)
+    "pp2_seq_splits2": dict(world=2, kw=dict(pp=2, extra_tc=dict(num_seq_splits=2))),
+    "pp2_tp2_seq_splits4": dict(world=4, kw=dict(pp=2, tp=2, sp=True, extra_tc=dict(num_seq_splits=4))),
     # node times measured in iterations 1-2, cost-driven table from iteration 3 on: same losses
     "pp2_zerobubble_replanned": dict(world=2, kw=dict(pp=2, schedule="zerobubble", iters=4, extra_tc=dict(
         zero_bubble_pipeline_timers_start_iter=1, zero_bubble_pipeline_timers_end_iter=3))),

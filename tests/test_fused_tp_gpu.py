@@ -1,4 +1,5 @@
-"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels vs the NCCL + GEMM composition (2 GPUs)."""
+"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels vs the NCCL + GEMM composition and vs an fp32 evaluation of
+the same products (2 GPUs)."""
 import pytest
 import torch
 
@@ -15,6 +16,7 @@ def _worker(rank, world, shapes):
 
     group = dist.group.WORLD
     torch.manual_seed(1234 + rank)
+    torch.backends.cuda.matmul.allow_tf32 = False
     for (T, N, K, b_mn) in shapes:
         Tl = T // world
         for it in range(3):  # several epochs through the same workspace
@@ -27,6 +29,13 @@ def _worker(rank, world, shapes):
             assert torch.equal(gathered, gref), f"gathered activations differ (T={T} it={it})"
             err = (out.float() - ref.float()).abs().max().item()
             assert err <= 2e-2 * ref.float().abs().max().item() + 1e-3, f"ag_gemm err {err}"
+            # fp32 evaluation of the same product from the gathered operands (torch matmul in fp32, no TF32)
+            wf = w.float() if b_mn else w.float().t()
+            xs = [torch.empty_like(x_shard) for _ in range(world)]
+            dist.all_gather(xs, x_shard, group=group)
+            ref32 = torch.cat(xs).float() @ wf
+            err32 = (out.float() - ref32).abs().max().item()
+            assert err32 <= 1e-2 * ref32.abs().max().item() + 1e-3, f"ag_gemm vs fp32: {err32}"
             x = torch.randn(T, K, device="cuda").bfloat16()
             out2 = fused_tp.gemm_rs(x, w, group, b_mn=b_mn, fused=True)
             ref2 = fused_tp.gemm_rs(x, w, group, b_mn=b_mn, fused=False)
@@ -34,6 +43,12 @@ def _worker(rank, world, shapes):
             _lib.check_status()
             err2 = (out2.float() - ref2.float()).abs().max().item()
             assert err2 <= 3e-2 * ref2.float().abs().max().item() + 1e-2, f"gemm_rs err {err2}"
+            # fp32: every rank's partial product of its own (x, w), summed over the ranks, this rank's rows
+            part = (x.float() @ wf)
+            dist.all_reduce(part, group=group)
+            ref32 = part[rank * Tl:(rank + 1) * Tl]
+            err32 = (out2.float() - ref32).abs().max().item()
+            assert err32 <= 1.5e-2 * ref32.abs().max().item() + 1e-2, f"gemm_rs vs fp32: {err32}"
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

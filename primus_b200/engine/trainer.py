@@ -251,6 +251,9 @@ class Trainer:
                              model_cfg.fp8_margin)
         self.is_cuda = self.device.type == "cuda"
         model_cfg.seq_length = train_cfg.seq_length
+        if model_cfg.num_experts and st.tp > 1 and st.ep > 1 and not train_cfg.use_distributed_optimizer:
+            raise NotImplementedError("MoE with tensor and expert parallelism needs use_distributed_optimizer (the "
+                                      "gradient norm of replicated expert shards is only assembled for sharded state)")
         if model_cfg.attention_dropout > 0.0:
             raise NotImplementedError("attention_dropout > 0: the attention kernels have no dropout path "
                                       "(hidden_dropout is built)")

@@ -40,7 +40,12 @@ class MoELayer(nn.Module):
         super().__init__()
         from .gpt import MLP, ParamHolder, _param
 
-        assert tp == 1, "MoE layers run with tensor_model_parallel_size 1 (expert parallelism shards the experts)"
+        # Under tensor parallelism the layer works on each rank's sequence shard: the TP ranks are just more ranks with
+        # their own tokens (expert tensor parallelism 1), so experts are sharded over the expert-parallel group --
+        # which spans the TP ranks -- and router / shared-expert weights are replicated, with their gradients summed
+        # over the TP group like those of the norm weights.
+        if tp > 1 and not cfg.sequence_parallel:
+            raise ValueError("MoE layers under tensor parallelism need sequence_parallel (each rank routes its own tokens)")
         self.cfg = cfg
         self.layer_idx = layer_idx
         st = ps.get_state()
@@ -69,8 +74,17 @@ class MoELayer(nn.Module):
         for p in (self.experts.fc1_weight.weight, self.experts.fc2_weight.weight):
             p.is_expert = self.ep > 1
             p.expert_parallel = self.ep > 1
+            # without expert parallelism the experts are replicas that see one sequence shard each
+            p.sequence_parallel = tp > 1 and self.ep == 1
         if cfg.moe_shared_expert_intermediate_size:
             self.shared_experts = MLP(cfg, device, 1, ffn=cfg.moe_shared_expert_intermediate_size, with_norm=False)
+        if tp > 1:
+            replicated = [self.router.weight] + ([self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight]
+                                                 if hasattr(self, "shared_experts") else [])
+            for p in replicated:
+                p.sequence_parallel = True
+                if torch.distributed.is_initialized():      # drawn from per-rank streams: make the replicas equal
+                    torch.distributed.broadcast(p.data, src=st.tp_ranks[0], group=st.tp_group)
         self.last_aux_loss = None
         self.last_tokens_per_expert = None
 

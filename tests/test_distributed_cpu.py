@@ -64,6 +64,12 @@ CASES = {
     "pp2_post_validation_inverse": dict(world=2, kw=dict(pp=2, schedule="zerobubble", clip=1e-3, extra_tc=dict(
         enable_optimizer_post_validation=True, enable_exact_optimizer_post_validation=False))),
     "ep2_moe": dict(world=2, kw=dict(ep=2, moe=True)),
+    # MoE layers under tensor + sequence parallelism: every rank routes its own sequence shard; without the
+    # load-balancing loss, which is then a per-shard quantity, the trajectory is that of the single process
+    "tp2_moe": dict(world=2, kw=dict(tp=2, sp=True, moe=True, extra_mc=dict(moe_aux_loss_coeff=0.0))),
+    "tp2_ep2_moe": dict(world=4, kw=dict(tp=2, sp=True, ep=2, moe=True, extra_mc=dict(moe_aux_loss_coeff=0.0))),
+    "tp2_ep2_moe_shared": dict(world=4, kw=dict(tp=2, sp=True, ep=2, moe=True, extra_mc=dict(
+        moe_aux_loss_coeff=0.0, moe_shared_expert_intermediate_size=32))),
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
     "tp2_qkv_bias": dict(world=2, kw=dict(tp=2, sp=True, extra_mc=dict(add_qkv_bias=True))),
     "cp2": dict(world=2, kw=dict(cp=2)),
@@ -103,6 +109,7 @@ NORM_CASES = {
     # whole-parameter optimizers: every expert-parallel rank owns different experts
     "ep2_moe_sgd": dict(world=2, kw=dict(ep=2, moe=True, opt="sgd", distopt=False)),
     "ep2_moe_adam": dict(world=2, kw=dict(ep=2, moe=True)),
+    "tp2_ep2_moe": dict(world=4, kw=dict(tp=2, sp=True, ep=2, moe=True, extra_mc=dict(moe_aux_loss_coeff=0.0))),
 }
 
 

@@ -35,7 +35,7 @@ INERT_KEYS = {
     "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_parallel_linear",
     "use_turbo_rms_norm", "turbo_deepep_num_cu",
     # services that are not built
-    "enable_ft_package", "enable_gloo_process_groups", "generate_tracelens_report", "straggler_ctrlr_port",
+    "enable_ft_package", "enable_gloo_process_groups", "straggler_ctrlr_port",
     "non_persistent_ckpt_type", "non_persistent_save_interval", "weight_deosc", "weight_deosc_period",
     "weight_deosc_ratio", "sft_grad_sanitize", "trainable", "mlflow_run_name",
     "log_throughput", "log_timers_to_tensorboard", "torch_profiler_record_shapes", "torch_profiler_use_gzip",

@@ -135,6 +135,36 @@ class MetricsWriter:
         for _, fn, _ in self.sinks:
             fn(iteration, scalars)
 
+    def log_artifacts(self, paths, artifact_dir: Optional[str] = None, subdir: str = "artifacts", log=print) -> list:
+        """Hand files (profiler traces, trace reports, log files) to the sinks that keep artifacts: they are copied under
+        ``<artifact_dir>/<subdir>/`` (always, on the writer rank) and logged to MLflow / W&B when those sinks are
+        active.  The upload switches of the reference (``mlflow_upload_traces``, ``mlflow_upload_logs``,
+        ``mlflow_upload_tracelens_report``) map onto this call."""
+        import shutil
+
+        kept = []
+        if artifact_dir:
+            dst = os.path.join(artifact_dir, subdir)
+            os.makedirs(dst, exist_ok=True)
+            for p_ in paths:
+                if os.path.isfile(p_):
+                    kept.append(shutil.copy2(p_, dst))
+        for name, _, _ in self.sinks:
+            try:
+                if name == "mlflow":
+                    import mlflow
+
+                    for p_ in paths:
+                        mlflow.log_artifact(p_, artifact_path=subdir)
+                elif name == "wandb":
+                    import wandb
+
+                    for p_ in paths:
+                        wandb.save(p_)
+            except Exception as e:  # noqa: BLE001
+                log(f"[metrics] {name}: artifact upload failed: {e}")
+        return kept
+
     def close(self):
         if self.jsonl is not None:
             self.jsonl.close()

@@ -59,6 +59,12 @@ class TrainConfig:
     overlap_grad_reduce: bool = False
     overlap_param_gather: bool = False
     grad_reduce_in_bf16: bool = False    # bf16 on the wire for the data-parallel gradient reduction (fp32 accumulation)
+    # trace analysis and artifacts (role of the reference's TraceLens / MLflow upload switches)
+    generate_tracelens_report: bool = False        # write a kernel-category report of this rank's profiler traces
+    mlflow_upload_tracelens_report: bool = False   # also hand the reports to the artifact sinks (implies generation)
+    mlflow_upload_traces: bool = False             # hand the raw trace files to the artifact sinks
+    mlflow_tracelens_ranks: Optional[list] = None  # ranks that write a report (None: every profiled rank)
+    mlflow_tracelens_output_format: str = "md"     # md | csv | tsv | jsonl
     num_seq_splits: int = 1              # sequence chunks per micro-batch that travel through the pipeline separately
     enable_optimizer_post_validation: bool = False        # pipeline parallel: update first, validate the global norm later
     enable_exact_optimizer_post_validation: bool = True   # restore from a snapshot (exact) instead of inverting the update
@@ -768,6 +774,29 @@ class Trainer:
                 self.load_checkpoint(tc.save)
                 self.restarts = restarts
 
+    def _trace_reports(self, profiler, writer, out_dir) -> None:
+        """After the profiled window: kernel-level reports of this rank's traces (``generate_tracelens_report``, or
+        implied by ``mlflow_upload_tracelens_report``) and artifact hand-over (``mlflow_upload_traces``)."""
+        tc = self.tcfg
+        want_report = tc.generate_tracelens_report or tc.mlflow_upload_tracelens_report
+        if not (profiler.enabled and (want_report or tc.mlflow_upload_traces)):
+            return
+        try:
+            from ..tools import trace_report as TR
+
+            mine = [p for p in TR.find_traces(profiler.out_dir) if TR.rank_of(p) == self.st.rank]
+            files = []
+            if want_report and mine and (tc.mlflow_tracelens_ranks is None or self.st.rank in tc.mlflow_tracelens_ranks):
+                fmt = tc.mlflow_tracelens_output_format if tc.mlflow_tracelens_output_format in ("md", "csv", "tsv", "jsonl") \
+                    else "md"
+                files = TR.write_report(mine, os.path.join(profiler.out_dir, "trace_report"), fmt)
+                self.log(f"[profiler] trace report: {files[0] if files else 'no GPU events in the trace'}")
+            upload = (files if tc.mlflow_upload_tracelens_report else []) + (mine if tc.mlflow_upload_traces else [])
+            if upload:
+                writer.log_artifacts(upload, out_dir, log=self.log)
+        except Exception as e:  # noqa: BLE001  (a report must never take the training run down)
+            self.log(f"[profiler] trace report failed: {type(e).__name__}: {e}")
+
     def _train_loop(self, num_iters: Optional[int] = None, on_step: Optional[Callable] = None,
                     losses: Optional[list] = None) -> list[float]:
         tc = self.tcfg
@@ -841,6 +870,7 @@ class Trainer:
 
             _ckpt.finalize_async_save()
             profiler.close()
+            self._trace_reports(profiler, writer, out_dir)
             writer.close()
             if exit_flag is not None:
                 exit_flag.restore()

@@ -15,12 +15,21 @@ import torch
 import torch.distributed as dist
 
 
-def shard_model(model: torch.nn.Module, device: torch.device, compute_dtype: torch.dtype):
+def shard_model(model: torch.nn.Module, device: torch.device, compute_dtype: torch.dtype, replicate_degree: int = 1):
+    """``replicate_degree`` > 1: hybrid sharding (HSDP) -- the ranks form ``replicate_degree`` groups; parameters and
+    optimizer state are sharded inside a group (consecutive ranks: the NVLink domain) and replicated across the groups,
+    gradients are reduce-scattered inside and all-reduced across.  The reference's ``data_parallel_replicate_degree``
+    (primus/backends/megatron/patches/args/hsdp_args_patches.py:12-70)."""
     from torch.distributed.device_mesh import init_device_mesh
     from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
     world = dist.get_world_size()
-    mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("dp",))
+    if replicate_degree > 1:
+        assert world % replicate_degree == 0, f"data_parallel_replicate_degree {replicate_degree} must divide {world} ranks"
+        mesh = init_device_mesh(device.type, (replicate_degree, world // replicate_degree),
+                                mesh_dim_names=("replicate", "shard"))
+    else:
+        mesh = init_device_mesh(device.type, (world,), mesh_dim_names=("dp",))
     model.float()                                   # sharded (master) parameters are fp32
     # inputs are not cast: the layers receive fp32 rotary tables and integer position ids next to the bf16 activations
     mp = MixedPrecisionPolicy(param_dtype=compute_dtype if compute_dtype != torch.float32 else None,

@@ -108,6 +108,7 @@ class TrainConfig:
     timing_log_level: int = 0          # 0: no step timers; 1: forward-backward / optimizer ...; 2: + batch staging
     timing_log_option: str = "minmax"  # max | minmax | all (how the per-rank times are reported)
     use_torch_fsdp2: bool = False      # shard parameters / gradients / optimizer state over the data-parallel ranks
+    data_parallel_replicate_degree: int = 1   # with use_torch_fsdp2: HSDP, shard inside world / degree ranks, replicate across
     use_precision_aware_optimizer: bool = False   # Adam moments in exp_avg_dtype / exp_avg_sq_dtype ("fp32" | "bf16")
     exp_avg_dtype: str = "fp32"
     exp_avg_sq_dtype: str = "fp32"
@@ -305,7 +306,7 @@ class Trainer:
         assert st.tp == st.pp == st.cp == st.ep == 1, "use_torch_fsdp2: data parallelism only (tp = pp = cp = ep = 1)"
         assert not (model_cfg.fp8 and model_cfg.fp8_recipe), "use_torch_fsdp2 runs in bf16 (no MXFP8 recipe)"
         assert train_cfg.optimizer.lower() in ("adam", "adamw"), "use_torch_fsdp2 uses AdamW"
-        fsdp.shard_model(self.model, self.device, model_cfg.torch_dtype)
+        fsdp.shard_model(self.model, self.device, model_cfg.torch_dtype, int(train_cfg.data_parallel_replicate_degree or 1))
         self.buffers = []
         self.optimizer = fsdp.FSDP2Optimizer(self.model, train_cfg.lr, (train_cfg.adam_beta1, train_cfg.adam_beta2),
                                              train_cfg.adam_eps, train_cfg.weight_decay, train_cfg.clip_grad,

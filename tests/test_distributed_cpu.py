@@ -36,6 +36,8 @@ def _mc_kwargs(mc):
 CASES = {
     "dp2": dict(world=2, kw=dict()),
     "dp2_fsdp2": dict(world=2, kw=dict(fsdp=True)),
+    # hybrid sharding: two groups of two ranks, sharded inside a group, replicated across
+    "dp4_hsdp": dict(world=4, kw=dict(fsdp=True, extra_tc=dict(data_parallel_replicate_degree=2))),
     "dp2_bf16_grad_reduce": dict(world=2, kw=dict(extra_tc=dict(grad_reduce_in_bf16=True, overlap_grad_reduce=True))),
     "dp2_odc": dict(world=2, kw=dict(extra_tc=dict(enable_odc=True, overlap_grad_reduce=True))),
     "dp2_overlap_param_gather": dict(world=2, kw=dict(extra_tc=dict(overlap_param_gather=True, overlap_grad_reduce=True))),

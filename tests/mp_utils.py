@@ -17,6 +17,9 @@ def _entry(rank, world, port, backend, fn, args, errq):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
+    if backend != "nccl":
+        # several ranks share the host's cores: without a cap every rank starts one thread per core
+        torch.set_num_threads(max(1, (os.cpu_count() or 8) // max(world, 1)))
     try:
         if backend == "nccl":
             torch.cuda.set_device(rank)

@@ -27,6 +27,8 @@ _FP8_RECIPE: str | None = None
 _WEIGHT_GEN = 0
 _W_CACHE: dict = {}
 _ACT_CACHE: list = []   # [(key, pinned source tensor, MXFP8Tensor)]
+_PINNED: dict = {}      # key -> (placeholder tensor, MXFP8Tensor, direction whose use releases the entry)
+_PINNED_MAX = 16
 
 
 FP8_RECIPES = ("mxfp8", "tensorwise", "delayed", "blockwise")
@@ -48,6 +50,7 @@ def set_fp8_recipe(recipe: str | None, amax_history_len: int = 1, amax_compute_a
     _WEIGHT_GEN += 1        # quantised weights cached elsewhere (expert weights) are keyed on this counter
     _W_CACHE.clear()
     _ACT_CACHE.clear()
+    _PINNED.clear()
 
 
 def weight_generation() -> int:
@@ -89,6 +92,12 @@ def _quantized(t: torch.Tensor, direction: str, single_use: bool = False, role=N
     else:
         key = (t.data_ptr(), tuple(t.shape), t._version)
         q = None
+        pin = _PINNED.get(key)
+        if pin is not None and getattr(pin[1], "q_" + direction) is not None:
+            q = pin[1]
+            if direction == pin[2]:
+                del _PINNED[key]            # its last consumer
+            return (q.q_row, q.sf_row) if direction == "row" else (q.q_col, q.sf_col)
         for k_, _, q_ in _ACT_CACHE:
             if k_ == key and getattr(q_, "q_" + direction) is not None:
                 q = q_
@@ -101,11 +110,23 @@ def _quantized(t: torch.Tensor, direction: str, single_use: bool = False, role=N
     return (q.q_row, q.sf_row) if direction == "row" else (q.q_col, q.sf_col)
 
 
-def register_quantized(t: torch.Tensor, q) -> None:
+def register_quantized(t: torch.Tensor, q, pinned: bool = False) -> None:
     """Attach an already quantised copy (both directions) to ``t``: the next GEMMs that take ``t`` as an operand use
     it instead of quantising.  ``t``'s own bf16 contents are then never read by an fp8-eligible GEMM, which lets a
-    producer that can emit MXFP8 directly (fused SwiGLU backward) skip writing them."""
-    _ACT_CACHE.insert(0, ((t.data_ptr(), tuple(t.shape), t._version), t, q))
+    producer that can emit MXFP8 directly (fused SwiGLU backward) skip writing them.
+
+    ``pinned``: ``t`` is a placeholder without contents (a gathered tensor that only exists in quantised form): the
+    copy is kept until the GEMM that reads its last direction has run (column direction if present, else row) instead
+    of living in the small recent-use cache that other quantisations push it out of.  The table is small and bounded
+    (the oldest entries go first if a consumer never comes, e.g. frozen weights), so producers must not use
+    placeholders while weight-gradient GEMMs are being deferred (``WGRAD_STORE.current``)."""
+    key = (t.data_ptr(), tuple(t.shape), t._version)
+    if pinned:
+        _PINNED[key] = (t, q, "col" if q.q_col is not None else "row")
+        while len(_PINNED) > _PINNED_MAX:
+            del _PINNED[next(iter(_PINNED))]
+        return
+    _ACT_CACHE.insert(0, (key, t, q))
     del _ACT_CACHE[4:]
 
 

@@ -72,7 +72,10 @@ class NormLinearFn(torch.autograd.Function):
         _lib.call("rmsnorm_fwd", xsum, None, norm_w, y, None, None, rows, H, xsum.stride(0), y.stride(0),
                   float(ctx.eps))
         if sp:
-            y = tp_comm.all_gather_dim0(y, tp_group)
+            if fused_tp._quantized_gather_ok(y, weight, False) and dout2.shape[1] % 128 == 0:
+                y = fused_tp.all_gather_quantized(y, tp_group, row=False, col=True)   # MXFP8: gather the quantised copy
+            else:
+                y = tp_comm.all_gather_dim0(y, tp_group)
         dw = gemm.wgrad(dout2, y, weight_ref)
         del y
         if sp:
@@ -230,7 +233,7 @@ class SwiGLULinearFn(torch.autograd.Function):
         act = torch.empty(T, I, dtype=x2.dtype, device=x2.device)
         _lib.call("swiglu_fwd", x2, pp, act, T, I, float(ctx.clamp), ctx.kind)
         if sp:
-            dact, dout2 = fused_tp.ag_gemm(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED)
+            dact, dout2 = fused_tp.ag_gemm(dout2, weight, tp_group, b_mn=True, fused=fused_tp.ENABLED, gather_col=True)
             dw = gemm.wgrad(dout2, act, ctx.weight_ref)
         else:
             dw = gemm.wgrad(dout2, act, ctx.weight_ref)
@@ -273,7 +276,7 @@ class RowParallelLinearFn(torch.autograd.Function):
     def backward(ctx, dout):
         x, weight = ctx.saved_tensors
         dout = dout.contiguous()
-        dx, dout_full = fused_tp.ag_gemm(dout, weight, ctx.group, b_mn=True, fused=fused_tp.ENABLED)
+        dx, dout_full = fused_tp.ag_gemm(dout, weight, ctx.group, b_mn=True, fused=fused_tp.ENABLED, gather_col=True)
         dw = gemm.wgrad(dout_full, x, ctx.weight_ref)
         return dx, dw, None
 

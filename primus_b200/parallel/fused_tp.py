@@ -143,7 +143,52 @@ def _launch(ctx, inst, A, B, D, b_mn, out_rs=None):
         raise _lib.NativeLibraryError(f"pb_gemm_tp_fused failed with code {rc}")
 
 
+# Under the MXFP8 recipe the all-gather of a sequence-parallel activation moves its quantised copy (E4M3 values + UE8M0
+# block scales: 0.52 x the bytes of bf16 per direction) and every rank quantises only its own shard; blocks never
+# straddle shards because a shard is a multiple of 128 rows, so the gathered copy is bit-identical to quantising the
+# gathered tensor.
+QUANTIZED_GATHER = True
+
 _FALLBACK_LOGGED: set = set()
+
+
+def _quantized_gather_ok(x_shard, w, b_mn: bool) -> bool:
+    if not (QUANTIZED_GATHER and x_shard.is_cuda and gemm_ops.fp8_recipe() == "mxfp8"):
+        return False
+    if gemm_ops.WGRAD_STORE.current is not None:      # deferred weight-gradient GEMMs would outlive the placeholder table
+        return False
+    if x_shard.dtype != torch.bfloat16 or not x_shard.is_contiguous() or not w.is_contiguous():
+        return False
+    if getattr(w, "_fp8_exempt", False) or getattr(x_shard, "_fp8_exempt", False):
+        return False
+    Tl, K = x_shard.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    return Tl % 128 == 0 and K % 128 == 0 and N % 128 == 0
+
+
+def all_gather_quantized(x_shard: torch.Tensor, group, row: bool = True, col: bool = False) -> torch.Tensor:
+    """All-gather (dim 0) of the MXFP8 copies of ``x_shard`` [Tl, K].  Returns a bf16 placeholder [T, K] whose contents
+    are never written: its quantised copies are registered with ``ops.gemm``, so FP8-eligible GEMMs that take it as an
+    operand use them.  ``row``: blocks along K (forward / data-gradient operand); ``col``: blocks along the tokens
+    (weight-gradient operand)."""
+    from ..ops import fp8
+
+    tp = dist.get_world_size(group)
+    Tl, K = x_shard.shape
+    T = Tl * tp
+    q = fp8.quantize_mxfp8(x_shard, row, col, scaling="mxfp8")
+    full = fp8.MXFP8Tensor(shape=(T, K))
+    if row:
+        full.q_row = tpc.all_gather_dim0(q.q_row, group)
+        full.sf_row = tpc.all_gather_dim0(q.sf_row, group)           # [Tl/128][K/128][512]: row blocks are outermost
+    if col:
+        full.q_col = tpc.all_gather_dim0(q.q_col, group)
+        # column-direction scales are laid out [K/128][Tl/128][512]: the shards interleave in the middle dimension
+        sf = tpc.all_gather_dim0(q.sf_col.view(1, K // 128, Tl // 128, 512), group)
+        full.sf_col = sf.permute(1, 0, 2, 3).contiguous().view(-1)
+    placeholder = torch.empty(T, K, dtype=torch.bfloat16, device=x_shard.device)
+    gemm_ops.register_quantized(placeholder, full, pinned=True)
+    return placeholder
 
 
 def _note_fallback(kind: str, reason: str) -> None:
@@ -157,9 +202,15 @@ def _note_fallback(kind: str, reason: str) -> None:
             print(f"[fused-tp] {kind} requested but not used: {reason}; running NCCL + GEMM", flush=True)
 
 
-def ag_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: bool = True):
-    """Returns (all_gather(x_shard) @ W^T, gathered x). ``w``: [N, K] or, with ``b_mn``, [K, N]."""
+def ag_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, fused: bool = True,
+            gather_col: bool = False):
+    """Returns (all_gather(x_shard) @ W^T, gathered x). ``w``: [N, K] or, with ``b_mn``, [K, N].  Under the MXFP8
+    recipe the gathered tensor may be a placeholder that only carries quantised copies (``all_gather_quantized``);
+    ``gather_col`` asks for the token-direction copy as well (the caller feeds it to a weight-gradient GEMM)."""
     tp = dist.get_world_size(group)
+    if _quantized_gather_ok(x_shard, w, b_mn):
+        g = all_gather_quantized(x_shard, group, row=True, col=gather_col)
+        return gemm_ops.gemm(g, w, b_mn=b_mn), g
     Tl, K = x_shard.shape
     M = Tl * tp
     N = w.shape[1] if b_mn else w.shape[0]

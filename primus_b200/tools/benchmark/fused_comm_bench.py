@@ -1,6 +1,6 @@
 """Fused compute+collective kernels against their NCCL compositions, with roofline fractions.
 
-    torchrun --nproc-per-node N -m primus_b200.tools.benchmark.fused_comm_bench [--suite tp|dp|all] [--model llama3.1_70B]
+    torchrun --nproc-per-node N -m primus_b200.tools.benchmark.fused_comm_bench [--suite tp|tp-fp8|dp|all] [--model llama3.1_70B]
 
 * ``tp``: all-gather -> GEMM and GEMM -> reduce-scatter (``csrc/gemm_tp_fused.cu``) at the tensor-parallel shapes
   of the model (QKV / FC1 column-parallel, proj / FC2 row-parallel, sequence parallel) vs ``NCCL collective + GEMM``;
@@ -82,6 +82,43 @@ def bench_tp(model: str, tokens: int, iters: int):
     return rows
 
 
+def bench_tp_fp8(model: str, tokens: int, iters: int, emulate_tp: int = 0):
+    """MXFP8 recipe under sequence parallelism: all-gather of the quantised shard + MXFP8 GEMM against all-gather of
+    the bf16 shard + quantisation of the gathered tensor + the same GEMM.  ``emulate_tp`` > world: the weight shard has
+    the width of that tensor-parallel size (the gathered tensor still has ``tokens`` rows)."""
+    from ...core.config.presets import load_preset
+    from ...models.config import TransformerConfig
+    from ...ops import gemm as gemm_ops
+    from ...parallel import fused_tp
+
+    world = dist.get_world_size()
+    tp = max(emulate_tp, world)
+    cfg = TransformerConfig.from_dict(load_preset(model, "models"))
+    h, ffn = cfg.hidden_size, cfg.ffn_hidden_size
+    group = dist.group.WORLD
+    rows = []
+    gemm_ops.set_fp8_recipe("mxfp8")
+    try:
+        for name, N, K in (("qkv fprop", cfg.qkv_width // tp, h), ("fc1 fprop", 2 * ffn // tp, h)):
+            N = N // 128 * 128
+            w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+            w._is_weight = True
+            xs = [torch.randn(tokens // world, K, device="cuda").bfloat16() for _ in range(4)]
+            res = {}
+            for mode in (True, False):
+                fused_tp.QUANTIZED_GATHER = mode
+                res[mode] = _max_over_ranks(time_cuda(lambda i: fused_tp.ag_gemm(xs[i % 4], w, group, fused=False), iters)["ms_median"])
+            fused_tp.QUANTIZED_GATHER = True
+            gather_bf16 = (tokens // world) * (world - 1) * K * 2.0
+            rows.append({"op": name + " (MXFP8, AG + GEMM)", "ranks": world, "weight shard of tp": tp, "M": tokens, "N/rank": N,
+                         "K": K, "quantised_gather_ms": res[True], "bf16_gather_ms": res[False],
+                         "speedup": res[False] / res[True], "nvlink_MB_in_bf16": gather_bf16 / 1e6,
+                         "nvlink_MB_in_mxfp8": gather_bf16 * (1 + 1 / 32) / 2 / 1e6})
+    finally:
+        gemm_ops.set_fp8_recipe(None)
+    return rows
+
+
 def bench_dp(n_params: int, iters: int):
     from ...ops import _lib
     from ...ops import optim as optim_ops
@@ -141,7 +178,8 @@ def bench_dp(n_params: int, iters: int):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--suite", default="all", choices=["tp", "dp", "all"])
+    ap.add_argument("--suite", default="all", choices=["tp", "tp-fp8", "dp", "all"])
+    ap.add_argument("--emulate-tp", type=int, default=0, help="tp-fp8: width of the weight shard as under this TP size")
     ap.add_argument("--model", default="llama3.1_70B")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--dp-params", type=int, default=1 << 30)
@@ -155,6 +193,8 @@ def main(argv=None):
     rows = []
     if a.suite in ("tp", "all"):
         rows += bench_tp(a.model, a.tokens, a.iters)
+    if a.suite == "tp-fp8":
+        rows += bench_tp_fp8(a.model, a.tokens, a.iters, a.emulate_tp)
     if a.suite in ("dp", "all"):
         rows += bench_dp(a.dp_params, a.iters)
     if dist.get_rank() == 0:

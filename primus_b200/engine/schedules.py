@@ -111,6 +111,14 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             c, n = cfg.mamba_chunk_size, cfg.mamba_state_dim
             fwd += 2 * c * nh * n + 2 * c * di + 4 * di * n       # C B^T and (C B^T) x inside a chunk; state in / out
             attn = 0.0
+        elif mixer == "gdn":           # gated delta net: projections, convolution, chunked delta rule
+            qk = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+            vd = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+            conv_dim = 2 * qk + vd
+            fwd += 2 * h * (conv_dim + vd + 2 * cfg.linear_num_value_heads) + 2 * vd * h + 2 * conv_dim * cfg.linear_conv_kernel_dim
+            c, nv, dk, dv = cfg.linear_chunk_size, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+            fwd += nv * (4 * c * dk + 2 * c * c + 2 * c * (dv + dk) + 6 * dk * dv)      # scores, solve, deltas, state
+            attn = 0.0
         elif mixer is None:
             attn = 0.0
         elif cfg.multi_latent_attention:

@@ -225,7 +225,7 @@ class Trainer:
             assert train_cfg.seq_length % unit == 0, f"num_seq_splits = {S}: seq_length must be a multiple of {unit}"
             bad = [n for n, on in (("context parallelism", model_cfg.context_parallel_size > 1),
                                    ("multi-latent attention", model_cfg.multi_latent_attention),
-                                   ("Mamba / convolution mixers", model_cfg.model_type == "mamba" or bool(model_cfg.lfm_layer_types)),
+                                   ("Mamba / delta-net / convolution mixers", model_cfg.model_type == "mamba" or bool(model_cfg.lfm_layer_types)),
                                    ("activation recompute", bool(model_cfg.recompute_granularity)),
                                    ("multi-token prediction", bool(model_cfg.mtp_num_layers)),
                                    ("virtual pipeline stages", bool(model_cfg.virtual_pipeline_model_parallel_size)),

@@ -126,6 +126,13 @@ class TransformerConfig:
     hybrid_attention_ratio: float = 0.0             # share of the layers that are attention layers
     hybrid_mlp_ratio: float = 0.0                   # share of the layers that are MLP layers
     hybrid_override_pattern: Optional[str] = None   # one symbol per layer: M (Mamba), * (attention), - (MLP)
+    linear_attention_type: Optional[str] = None     # "gdn": the M layers are gated-delta-net mixers instead of Mamba-2
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 64
+    linear_value_head_dim: int = 64
+    linear_num_key_heads: int = 8
+    linear_num_value_heads: int = 16
+    linear_chunk_size: int = 64
 
     def layer_window(self, layer_idx: int) -> int:
         """Sliding-window width of a layer (0 = full attention)."""
@@ -202,6 +209,11 @@ class TransformerConfig:
                 nh = self.mamba_num_heads or di // self.mamba_head_dim
                 conv_dim = di + 2 * self.mamba_num_groups * self.mamba_state_dim
                 n += h * (di + conv_dim + nh) + conv_dim * (self.mamba_d_conv + 1) + 3 * nh + di + di * h
+            elif mixer == "gdn":
+                qk, vd = self.linear_num_key_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+                conv_dim = 2 * qk + vd
+                n += h * (conv_dim + vd + 2 * self.linear_num_value_heads) + conv_dim * self.linear_conv_kernel_dim
+                n += 2 * self.linear_num_value_heads + self.linear_value_head_dim + vd * h
             elif mixer is None:
                 pass
             elif self.multi_latent_attention:
@@ -292,7 +304,8 @@ def layer_kinds(cfg) -> list:
     if cfg.model_type == "mamba":
         pat = hybrid_layer_pattern(L, cfg.hybrid_attention_ratio, cfg.hybrid_mlp_ratio, cfg.hybrid_override_pattern,
                                    hybrid=cfg.is_hybrid_model)
-        return [{"M": ("mamba", False), "*": ("attention", False), "-": (None, True)}[c] for c in pat]
+        m_kind = "gdn" if (cfg.linear_attention_type or "").lower() in ("gdn", "gated_delta_net") else "mamba"
+        return [{"M": (m_kind, False), "*": ("attention", False), "-": (None, True)}[c] for c in pat]
     if cfg.lfm_layer_types:
         assert len(cfg.lfm_layer_types) == L, f"lfm_layer_types has {len(cfg.lfm_layer_types)} entries for {L} layers"
         bad = set(cfg.lfm_layer_types) - {"conv", "full_attention"}

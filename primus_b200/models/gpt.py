@@ -213,6 +213,10 @@ class TransformerLayer(nn.Module):
             from .mixers import Mamba2Mixer
 
             self.mixer = Mamba2Mixer(cfg, layer_idx, device, tp)
+        elif self.mixer_kind == "gdn":
+            from .mixers import GatedDeltaNetMixer
+
+            self.mixer = GatedDeltaNetMixer(cfg, layer_idx, device, tp)
         self.is_moe = False
         if not self.has_mlp:
             return
@@ -239,7 +243,7 @@ class TransformerLayer(nn.Module):
         if self.mixer_kind is None:
             attn_out, res1 = hidden, residual
         else:
-            mixer = self.mixer if self.mixer_kind == "mamba" else self.self_attention
+            mixer = self.mixer if self.mixer_kind in ("mamba", "gdn") else self.self_attention
             attn_out, res1 = mixer(hidden, residual, rope, batch)
             attn_out = self._drop(attn_out)
         if not self.has_mlp:

@@ -221,3 +221,128 @@ class Mamba2Mixer(nn.Module):
         gated = gated * torch.rsqrt(gated.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon)
         out = (gated.view(T, di) * self.norm.weight.float()).to(hidden.dtype)
         return gemm.linear(out.contiguous(), self.out_proj.weight), xsum
+
+
+# ------------------------------------------------------------------------------------------------ gated delta net
+def gated_delta_rule_sequential(q, k, v, g, beta, scale=None):
+    """The gated delta rule one token at a time (test oracle).  q, k [b, l, h, dk], v [b, l, h, dv], g [b, l, h]
+    (log-decay, <= 0), beta [b, l, h].  State S [dk, dv] per head:
+    ``S <- exp(g_t) S``; ``S <- S + k_t (beta_t (v_t - k_t^T S))^T``; ``o_t = (scale q_t)^T S``."""
+    b, l, h, dk = q.shape
+    dv = v.shape[-1]
+    scale = dk ** -0.5 if scale is None else scale
+    S = torch.zeros(b, h, dk, dv, dtype=torch.float32, device=q.device)
+    out = []
+    for t in range(l):
+        S = S * torch.exp(g[:, t].float())[..., None, None]
+        kt, vt = k[:, t].float(), v[:, t].float()
+        mem = torch.einsum("bhk,bhkv->bhv", kt, S)
+        delta = (vt - mem) * beta[:, t].float()[..., None]
+        S = S + kt[..., :, None] * delta[..., None, :]
+        out.append(torch.einsum("bhk,bhkv->bhv", q[:, t].float() * scale, S))
+    return torch.stack(out, 1)
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, chunk: int = 64, scale=None):
+    """The same recurrence chunk-wise.  Inside a chunk the deltas solve a unit lower-triangular system
+    ``(I + L) U = beta (V - decayed K S_in)`` with ``L = strict_lower(beta K K^T * decay)``, so one triangular solve
+    per chunk replaces the token loop; between chunks only the [dk, dv] state is carried."""
+    b, l, h, dk = q.shape
+    dv = v.shape[-1]
+    scale = dk ** -0.5 if scale is None else scale
+    pad = (-l) % chunk
+    if pad:
+        q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
+    L_ = l + pad
+    c = L_ // chunk
+    # [b, h, c, chunk, d]
+    qf = (q.float() * scale).permute(0, 2, 1, 3).reshape(b, h, c, chunk, dk)
+    kf = k.float().permute(0, 2, 1, 3).reshape(b, h, c, chunk, dk)
+    vf = v.float().permute(0, 2, 1, 3).reshape(b, h, c, chunk, dv)
+    gf = g.float().permute(0, 2, 1).reshape(b, h, c, chunk)
+    bf = beta.float().permute(0, 2, 1).reshape(b, h, c, chunk)
+    gc = torch.cumsum(gf, -1)                                           # log-decay from the chunk start to each token
+    lower = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
+    diff = (gc[..., :, None] - gc[..., None, :]).masked_fill(~lower, 0.0)
+    decay = torch.exp(diff).masked_fill(~lower, 0.0)                    # [.., i, j] = exp(gc_i - gc_j), j <= i
+    kb = kf * bf[..., None]
+    strict = decay * torch.ones(chunk, chunk, device=q.device).tril(-1)
+    A = torch.eye(chunk, device=q.device) + (kb @ kf.transpose(-1, -2)) * strict
+    # T = (I + L)^-1 applied to [beta V | beta K exp(gc)]
+    rhs = torch.cat([vf * bf[..., None], kb * torch.exp(gc)[..., None]], -1)
+    sol = torch.linalg.solve_triangular(A, rhs, upper=False)
+    u_v, u_k = sol[..., :dv], sol[..., dv:]                             # deltas without / per unit of the carried state
+    attn_in = (qf @ kf.transpose(-1, -2)) * decay                       # within-chunk scores (j <= i)
+    S = torch.zeros(b, h, dk, dv, dtype=torch.float32, device=q.device)
+    outs = []
+    for i in range(c):
+        delta = u_v[:, :, i] - u_k[:, :, i] @ S                          # [chunk, dv]
+        inter = (qf[:, :, i] * torch.exp(gc[:, :, i])[..., None]) @ S
+        outs.append(inter + attn_in[:, :, i] @ delta)
+        last = gc[:, :, i, -1]
+        S = S * torch.exp(last)[..., None, None] + \
+            (kf[:, :, i] * torch.exp(last[..., None] - gc[:, :, i])[..., None]).transpose(-1, -2) @ delta
+    o = torch.stack(outs, 2).reshape(b, h, L_, dv).permute(0, 2, 1, 3)
+    return o[:, :l]
+
+
+class GatedDeltaNetMixer(nn.Module):
+    """Gated delta net (linear attention with a decaying, delta-rule-corrected state): ``q, k, v, z, b, a = in_proj(h)``;
+    causal depthwise convolution + SiLU on ``[q | k | v]``; L2-normalised q / k; ``beta = sigmoid(b)``,
+    ``g = -exp(A_log) softplus(a + dt_bias)``; the gated delta rule; per-head RMSNorm gated by ``silu(z)``; ``out_proj``.
+    The 'M' layers of the reference's GDN hybrid stacks (primus/backends/megatron/core/models/hybrid/gated_delta_net.py,
+    ``gdn_hybrid_stack_spec`` in hybrid_mamba_mla_layer_specs.py:189-262; presets ``zebra_llama_*_gdn*``); parameter
+    names follow it (``in_proj``, ``conv1d``, ``A_log``, ``dt_bias``, ``out_norm``, ``out_proj``)."""
+
+    def __init__(self, cfg, layer_idx: int, device, tp: int):
+        super().__init__()
+        assert tp == 1, "the gated-delta-net mixer is not built for tensor parallelism"
+        self.cfg = cfg
+        h, dt = cfg.hidden_size, cfg.torch_dtype
+        self.nk, self.nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        assert self.nv % self.nk == 0
+        self.qk_dim, self.v_dim = self.nk * self.dk, self.nv * self.dv
+        self.conv_dim = 2 * self.qk_dim + self.v_dim
+        std = cfg.init_method_std
+        self.in_proj = nn.Module()
+        self.in_proj.register_parameter("layer_norm_weight", nn.Parameter(torch.ones(h, dtype=dt, device=device)))
+        self.in_proj.register_parameter("weight", _param((self.conv_dim + self.v_dim + 2 * self.nv, h), std, dt, device))
+        self.conv1d = nn.Module()
+        self.conv1d.register_parameter("weight", _param((self.conv_dim, 1, cfg.linear_conv_kernel_dim), std * 5, dt, device))
+        u = torch.rand(self.nv, device=device)
+        dt0 = torch.exp(u * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3)).clamp(min=1e-4)
+        self.dt_bias = nn.Parameter((dt0 + torch.log(-torch.expm1(-dt0))).float())
+        self.A_log = nn.Parameter(torch.log(torch.empty(self.nv, device=device).uniform_(1e-3, 16)).float())
+        self.out_norm = nn.Module()
+        self.out_norm.register_parameter("weight", nn.Parameter(torch.ones(self.dv, dtype=dt, device=device)))
+        self.out_proj = nn.Module()
+        self.out_proj.register_parameter("weight", _param((h, self.v_dim), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
+        for w in (self.in_proj.weight, self.out_proj.weight):
+            w._is_weight = True
+
+    def forward(self, hidden, residual, rope, batch):
+        cfg = self.cfg
+        assert ps.get_state().cp == 1, "the gated-delta-net mixer is not built for context parallelism"
+        y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        proj = gemm.linear(y, self.in_proj.weight)
+        T = proj.shape[0]
+        seq = T // batch
+        cd, vd, nv = self.conv_dim, self.v_dim, self.nv
+        qkv, z, b_, a_ = proj[:, :cd], proj[:, cd:cd + vd], proj[:, cd + vd:cd + vd + nv], proj[:, cd + vd + nv:]
+        qkv = F.silu(causal_depthwise_conv(qkv, self.conv1d.weight[:, 0, :], None, batch))
+        q = qkv[:, :self.qk_dim].view(batch, seq, self.nk, self.dk)
+        k = qkv[:, self.qk_dim:2 * self.qk_dim].view(batch, seq, self.nk, self.dk)
+        v = qkv[:, 2 * self.qk_dim:].view(batch, seq, nv, self.dv)
+        rep = nv // self.nk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2)
+        q = F.normalize(q.float(), dim=-1, eps=1e-6)
+        k = F.normalize(k.float(), dim=-1, eps=1e-6)
+        beta = torch.sigmoid(b_.float()).view(batch, seq, nv)
+        g = (-torch.exp(self.A_log.float()) * F.softplus(a_.float() + self.dt_bias)).view(batch, seq, nv)
+        o = gated_delta_rule_chunked(q, k, v, g, beta, cfg.linear_chunk_size)            # [b, l, nv, dv] fp32
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon) * self.out_norm.weight.float()
+        o = (o.reshape(T, vd) * F.silu(z.float())).to(hidden.dtype)
+        return gemm.linear(o.contiguous(), self.out_proj.weight), xsum

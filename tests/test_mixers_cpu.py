@@ -122,3 +122,56 @@ def test_hybrid_stack_trains_on_cpu():
     losses = tr.train()
     assert losses[-1] < losses[0] - 0.1, losses
     ps.destroy_model_parallel()
+
+
+@pytest.mark.parametrize("l,chunk", [(37, 8), (64, 16), (5, 8)])
+def test_chunked_gated_delta_rule_matches_the_recurrence_and_hf(l, chunk):
+    torch.manual_seed(2)
+    b, h, dk, dv = 2, 3, 8, 16
+    q = torch.nn.functional.normalize(torch.randn(b, l, h, dk), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(b, l, h, dk), dim=-1)
+    v, g, beta = torch.randn(b, l, h, dv), -torch.rand(b, l, h) * 0.5, torch.rand(b, l, h)
+    seq = M.gated_delta_rule_sequential(q, k, v, g, beta)
+    chk = M.gated_delta_rule_chunked(q, k, v, g, beta, chunk)
+    assert (seq - chk).abs().max() <= 1e-5 * max(1.0, seq.abs().max().item())
+    try:
+        from transformers.models.qwen3_next.modeling_qwen3_next import torch_recurrent_gated_delta_rule as hf_rule
+    except Exception:  # noqa: BLE001
+        return
+    ref, _ = hf_rule(q, k, v, g, beta, None, False, use_qk_l2norm_in_kernel=False)
+    assert (ref.float() - seq).abs().max() <= 1e-5
+
+
+def test_gated_delta_rule_gradients_match_the_recurrence():
+    torch.manual_seed(3)
+    b, l, h, dk, dv = 1, 19, 2, 4, 6
+    base = [torch.nn.functional.normalize(torch.randn(b, l, h, dk), dim=-1), torch.nn.functional.normalize(torch.randn(b, l, h, dk), dim=-1),
+            torch.randn(b, l, h, dv), -torch.rand(b, l, h) * 0.3, torch.rand(b, l, h)]
+    grads = []
+    for fn in (M.gated_delta_rule_sequential, lambda *a: M.gated_delta_rule_chunked(*a, 8)):
+        xs = [t.clone().requires_grad_() for t in base]
+        fn(*xs).pow(2).sum().backward()
+        grads.append([x.grad for x in xs])
+    for a, c in zip(*grads):
+        assert (a - c).abs().max() <= 1e-4 * max(1.0, a.abs().max().item())
+
+
+def test_gated_delta_net_stack_trains_and_counts_parameters():
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc = TransformerConfig(num_layers=4, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+                           vocab_size=256, params_dtype="fp32", model_type="mamba", is_hybrid_model=True,
+                           linear_attention_type="gdn", hybrid_override_pattern="M-*-", linear_num_key_heads=2,
+                           linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_chunk_size=16,
+                           untie_embeddings_and_output_weights=False)
+    assert mc.layer_kinds[0] == ("gdn", False)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_length=32, train_iters=12, lr=5e-3,
+                     lr_decay_style="constant", mock_data_kind="markov")
+    tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    assert sum(p.numel() for p in tr.model.parameters()) == mc.num_parameters()
+    losses = tr.train()
+    assert losses[-1] < losses[0] - 0.1, losses
+    ps.destroy_model_parallel()

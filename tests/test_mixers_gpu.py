@@ -29,7 +29,9 @@ def _pair(**kw):
     dict(num_layers=4, model_type="mamba", is_hybrid_model=True, hybrid_override_pattern="M-*-", mamba_head_dim=64,
          mamba_num_groups=2, mamba_state_dim=32, mamba_chunk_size=64),
     dict(num_layers=3, lfm_layer_types=["conv", "full_attention", "conv"], qk_layernorm=True),
-], ids=["mamba_hybrid", "lfm2"])
+    dict(num_layers=4, model_type="mamba", is_hybrid_model=True, linear_attention_type="gdn", hybrid_override_pattern="M-*-",
+         linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64, linear_value_head_dim=64),
+], ids=["mamba_hybrid", "lfm2", "gated_delta_net"])
 def test_mixer_stacks_match_fp32_cpu(kw):
     gpu, cpu = _pair(**kw)
     tokens = torch.randint(0, 1024, (2, 256))

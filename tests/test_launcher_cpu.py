@@ -97,3 +97,13 @@ def test_direct_mode_really_trains_on_cpu(tmp_path):
     text = log.read_text() if log.exists() else ""
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "Training completed." in text and text.count("lm loss:") == 2, text[-2000:]
+
+
+def test_deps_check_reports_toolchain_packages_and_native_library():
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run(["bash", os.path.join(root, "runner", "primus-cli"), "deps", "check"], capture_output=True, text=True,
+                       timeout=300)
+    assert "torch" in r.stdout and "native library" in r.stdout and "python3" in r.stdout, r.stdout + r.stderr
+    assert r.returncode in (0, 1)           # 1: something is missing or stale on this machine; the report still prints

@@ -197,8 +197,11 @@ PB_DEVICE uint32_t mapa_shared(const void* local, uint32_t cta) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(cta));
   return r;
 }
+// Arrival on a barrier in another CTA of the cluster.  The default (CTA-scope release) form: what the arrival hands
+// over is tensor-memory state, ordered by tcgen05.wait + tcgen05.fence::before_thread_sync, not global or shared
+// memory; a cluster-scope release per arrival costs on the order of a thousand cycles under load.
 PB_DEVICE void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile loads of a CTA pair: data lands in the executing CTA's shared memory, the transaction bytes are counted on
 // the mbarrier `bar_cluster_addr` (a shared::cluster address, typically the even CTA's barrier).  No multicast.

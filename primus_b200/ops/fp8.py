@@ -330,7 +330,7 @@ def dequantize_mxfp8(q: torch.Tensor, sf: torch.Tensor, colwise: bool) -> torch.
 
 # CTA-pair kernel (256 x 256 tiles, csrc/gemm_mxfp8_2cta.cu) for problems with at least this many rows / columns: each
 # CTA of a pair reads half of B, which takes the shared-memory operand reads off the critical path of the one-CTA kernel
-# (+2 % on the Llama-3.1-8B step under the power cap, same numerics).  PRIMUS_B200_TWO_CTA_MIN_DIM overrides the
+# (+2 % on single GEMMs in bursts, +0.5 % on the power-capped Llama-3.1-8B step, same numerics).  PRIMUS_B200_TWO_CTA_MIN_DIM overrides the
 # threshold; 0 disables the kernel.
 _env_min = os.environ.get("PRIMUS_B200_TWO_CTA_MIN_DIM")
 TWO_CTA_MIN_DIM: Optional[int] = (int(_env_min) or None) if _env_min else 256

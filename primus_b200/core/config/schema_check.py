@@ -36,10 +36,9 @@ INERT_KEYS = {
     "use_turbo_rms_norm", "turbo_deepep_num_cu",
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "straggler_ctrlr_port",
-    "non_persistent_ckpt_type", "non_persistent_save_interval", "weight_deosc", "weight_deosc_period",
-    "weight_deosc_ratio", "sft_grad_sanitize", "trainable", "mlflow_run_name",
-    "log_throughput", "log_timers_to_tensorboard", "torch_profiler_record_shapes", "torch_profiler_use_gzip",
-    "torch_profiler_with_stack", "use_tp_pp_dp_mapping", "offload_ops",
+    "weight_deosc", "weight_deosc_period",
+    "weight_deosc_ratio", "trainable",
+    "log_throughput", "use_tp_pp_dp_mapping", "offload_ops",
     # switches between the reference's two pipeline implementations (one runtime here; the schedule is chosen with
     # pp_algorithm / pipeline_schedule or enable_zero_bubble + zero_bubble_v_schedule)
     "patch_primus_pipeline", "patch_zero_bubble", "pp_communication_method",

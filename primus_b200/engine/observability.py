@@ -26,7 +26,7 @@ import torch
 class StepProfiler:
     def __init__(self, enabled: bool, rank: int, start: int = 3, end: int = 4, ranks=None, out_dir: Optional[str] = None,
                  exp_name: str = "exp", with_cpu: bool = True, record_shapes: bool = True, with_stack: bool = False,
-                 record_memory_history: bool = False, memory_snapshot_path: Optional[str] = None, log=print):
+                 use_gzip: bool = False, record_memory_history: bool = False, memory_snapshot_path: Optional[str] = None, log=print):
         self.rank, self.log = rank, log
         self.enabled = bool(enabled) and (ranks is None or rank in ranks)
         self.out_dir = out_dir or os.path.join(os.getcwd(), "profiler")
@@ -44,7 +44,7 @@ class StepProfiler:
         worker = f"primus-b200-exp[{exp_name}]-rank[{rank}]"
 
         def handler(p):
-            path = os.path.join(self.out_dir, f"{worker}.{int(time.time())}.pt.trace.json")
+            path = os.path.join(self.out_dir, f"{worker}.{int(time.time())}.pt.trace.json" + (".gz" if use_gzip else ""))
             p.export_chrome_trace(path)
             self.log(f"[profiler] trace written to {path}")
 

@@ -88,6 +88,7 @@ class Timers:
         assert log_option in ("max", "minmax", "all")
         self.log_level, self.log_option, self.cuda = log_level, log_option, cuda
         self.timers: dict[str, _Timer] = {}
+        self.last_max_ms: dict[str, float] = {}
         self._null = _Null()
 
     def __call__(self, name: str, log_level: int = 1):
@@ -127,4 +128,6 @@ class Timers:
             lines.append("max time across ranks (ms):")
             for j, n in enumerate(names):
                 lines.append(f"    {n + ' ':.<48s} {table[:, j].max():.2f}")
+        # the same numbers for the metric sinks (``log_timers_to_tensorboard``): max over ranks per timer
+        self.last_max_ms = {n: float(table[:, j].max()) for j, n in enumerate(names)}
         return "\n".join(lines)

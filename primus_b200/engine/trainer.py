@@ -107,6 +107,11 @@ class TrainConfig:
     pp_warmup: bool = False            # throw-away fwd + bwd on every pipeline stage at once before the first iteration
     timing_log_level: int = 0          # 0: no step timers; 1: forward-backward / optimizer ...; 2: + batch staging
     timing_log_option: str = "minmax"  # max | minmax | all (how the per-rank times are reported)
+    log_timers_to_tensorboard: bool = False   # also hand the step timers (max over ranks, ms) to the metric sinks
+    torch_profiler_record_shapes: bool = True
+    torch_profiler_with_stack: bool = False
+    torch_profiler_use_gzip: bool = False     # write <trace>.json.gz
+    mlflow_run_name: Optional[str] = None     # run name for the MLflow / W&B sinks (default: exp_name)
     use_torch_fsdp2: bool = False      # shard parameters / gradients / optimizer state over the data-parallel ranks
     data_parallel_replicate_degree: int = 1   # with use_torch_fsdp2: HSDP, shard inside world / degree ranks, replicate across
     use_precision_aware_optimizer: bool = False   # Adam moments in exp_avg_dtype / exp_avg_sq_dtype ("fp32" | "bf16")
@@ -135,6 +140,15 @@ class TrainConfig:
     decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
+    sft_grad_sanitize: bool = False   # zero non-finite gradient entries instead of skipping / failing the step
+    # frequent throw-away checkpoints next to the persistent ones: only the newest is kept, and a resume takes whichever
+    # of the two kinds is newer.  type: "global" (under <save>/non_persistent or non_persistent_global_ckpt_dir), "local"
+    # (a node-local directory: single-node jobs) or "in_memory" (a directory in /dev/shm: survives a process restart on
+    # the node, not a node loss)
+    non_persistent_ckpt_type: Optional[str] = None
+    non_persistent_save_interval: Optional[int] = None
+    non_persistent_global_ckpt_dir: Optional[str] = None
+    non_persistent_local_ckpt_dir: Optional[str] = None
     # with fused_dp_optimizer: the updated parameter shards are pulled by the copy engines on a side stream (one
     # cudaMemcpyAsync per peer and bucket, no SM time) instead of being stored to the peers by the AdamW kernel; also
     # switched on by ENABLE_SDMA_ALLGATHER=1, the reference's switch for its copy-engine parameter all-gather
@@ -403,6 +417,9 @@ class Trainer:
             self.optimizer.post_validation_exact = bool(train_cfg.enable_exact_optimizer_post_validation)
         if train_cfg.enable_odc:
             self.optimizer.grad_spike_threshold = float(train_cfg.odc_grad_spike_threshold or 0.0)
+        if train_cfg.sft_grad_sanitize:
+            assert not train_cfg.fused_dp_optimizer, "sft_grad_sanitize works on the NCCL optimizer path"
+            self.optimizer.sanitize_grads = True
         self._install_param_gather_waits()
 
     # ------------------------------------------------------------------ overlap_param_gather
@@ -818,11 +835,13 @@ class Trainer:
         out_dir = tc.tensorboard_dir or (os.path.join(tc.save, "tensorboard") if tc.save else None)
         profiler = obs.StepProfiler(tc.profile, st.rank, tc.profile_step_start, tc.profile_step_end, tc.profile_ranks,
                                     os.path.join(out_dir, "profiler") if out_dir else None, tc.exp_name,
-                                    not tc.disable_profiler_activity_cpu, record_memory_history=tc.record_memory_history,
+                                    not tc.disable_profiler_activity_cpu, record_shapes=tc.torch_profiler_record_shapes,
+                                    with_stack=tc.torch_profiler_with_stack, use_gzip=tc.torch_profiler_use_gzip,
+                                    record_memory_history=tc.record_memory_history,
                                     memory_snapshot_path=tc.memory_snapshot_path, log=self.log)
         writer = obs.MetricsWriter(st.rank, st.rank == st.world_size - 1 or st.world_size == 1, out_dir,
-                                   not tc.disable_tensorboard, tc.wandb_project, tc.mlflow_experiment_name, tc.exp_name,
-                                   log=self.log)
+                                   not tc.disable_tensorboard, tc.wandb_project, tc.mlflow_experiment_name,
+                                   tc.mlflow_run_name or tc.exp_name, log=self.log)
         try:
             for _ in range(n):
                 t0 = time.perf_counter()
@@ -853,6 +872,8 @@ class Trainer:
                     self.evaluate(tc.eval_iters)
                 if tc.save and tc.save_interval and self.iteration % tc.save_interval == 0:
                     self.save_checkpoint()
+                elif tc.non_persistent_save_interval and self.iteration % tc.non_persistent_save_interval == 0:
+                    self.save_non_persistent_checkpoint()
                 if exit_flag is not None and exit_flag.requested:
                     self.log(f"signal {exit_flag.signum} received: checkpointing at iteration {self.iteration} and leaving")
                     if tc.save:
@@ -965,6 +986,8 @@ class Trainer:
             self._steps_since_timer_log = 0
             if text and (st.rank == st.world_size - 1 or st.world_size == 1):
                 self.log(text)
+            if tc.log_timers_to_tensorboard:
+                self.last_metrics.update({f"timers/{k}": v for k, v in self.timers.last_max_ms.items()})
 
     def _check_device_status(self):
         """Reads the status word that kernels with bounded waits (mbarrier / flag / barrier) and the fused
@@ -989,7 +1012,49 @@ class Trainer:
         self._check_device_status()   # never persist the state of a step whose kernels reported an error
         return checkpoint.save_checkpoint(self, path or self.tcfg.save)
 
+    def non_persistent_root(self) -> Optional[str]:
+        tc = self.tcfg
+        kind = (tc.non_persistent_ckpt_type or "").lower()
+        if not kind:
+            return None
+        if kind == "global":
+            return tc.non_persistent_global_ckpt_dir or (os.path.join(tc.save, "non_persistent") if tc.save else None)
+        if kind == "local":
+            return tc.non_persistent_local_ckpt_dir or os.path.join("/tmp", "primus_b200_non_persistent", tc.exp_name)
+        if kind == "in_memory":
+            return os.path.join("/dev/shm", "primus_b200_non_persistent", tc.exp_name)
+        raise ValueError(f"non_persistent_ckpt_type {kind!r}: global | local | in_memory")
+
+    def save_non_persistent_checkpoint(self) -> Optional[str]:
+        """Write a throw-away checkpoint and drop the older ones of its kind."""
+        import shutil
+
+        from . import checkpoint
+
+        root = self.non_persistent_root()
+        if root is None:
+            return None
+        self._check_device_status()
+        d = checkpoint.save_checkpoint(self, root)
+        checkpoint.finalize_async_save()
+        if dist.is_initialized():
+            dist.barrier()
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            keep = os.path.basename(d)
+            for name in os.listdir(root):
+                if name.startswith("iter_") and name != keep:
+                    shutil.rmtree(os.path.join(root, name), ignore_errors=True)
+        return d
+
     def load_checkpoint(self, path: Optional[str] = None) -> int:
         from . import checkpoint
 
-        return checkpoint.load_checkpoint(self, path or self.tcfg.load)
+        path = path or self.tcfg.load
+        np_root = self.non_persistent_root()
+        if np_root and os.path.isdir(np_root):
+            newest_np = checkpoint.latest_iteration(np_root)
+            newest = checkpoint.latest_iteration(path) if path and os.path.isdir(path) else None
+            if newest_np is not None and (newest is None or newest_np > newest):
+                self.log(f"[checkpoint] resuming from the non-persistent checkpoint of iteration {newest_np} in {np_root}")
+                return checkpoint.load_checkpoint(self, np_root)
+        return checkpoint.load_checkpoint(self, path)

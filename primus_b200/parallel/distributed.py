@@ -390,6 +390,8 @@ class DistributedOptimizer:
         # those waits), as the reference overlaps its per-bucket parameter gather with the forward
         # (primus/backends/megatron/patches/parallelism/sdma_param_all_gather_patches.py:49-130)
         self.overlap_param_gather = False
+        self.sanitize_grads = False          # set by the trainer (sft_grad_sanitize)
+        self.sanitized_count = torch.zeros((), dtype=torch.int64, device=buffers[0].grad_data.device)
         self.grad_spike_threshold = 0.0      # ``odc_grad_spike_threshold``: skip the step when the norm exceeds it
         # ``enable_optimizer_post_validation``: update first, validate later (see ``_post_validated_step``)
         self.post_validation = False
@@ -477,6 +479,14 @@ class DistributedOptimizer:
         """Global L2 norm of the (already reduced) gradients, left on the device."""
         self.sumsq.zero_()
         self.skip.zero_()
+        if self.sanitize_grads:
+            # non-finite gradient entries become zero before the norm and the non-finite check see them: the affected
+            # elements simply get no update this step (the reference's SFT gradient sanitiser,
+            # primus/backends/megatron/patches/sft_grad_sanitize_patches.py:40-60)
+            for st in self.state:
+                g = st["buf"].grad_data[st["s"]:st["e"]]
+                self.sanitized_count += (~torch.isfinite(g)).sum()
+                torch.nan_to_num_(g, nan=0.0, posinf=0.0, neginf=0.0)
         expert_sep = self.expert_norm_group is not None and any(
             not st["buf"].use_distributed_optimizer and self._is_expert_buffer(st["buf"]) for st in self.state)
         if expert_sep:

@@ -243,3 +243,22 @@ def test_resume_with_another_data_parallel_size(tmp_path):
     for got in (got4, got1):
         for x, y in zip(got, ref):
             assert abs(x - y) <= 1e-5 * max(1.0, abs(y)), (got, ref)
+
+
+def test_non_persistent_checkpoints_keep_only_the_newest_and_win_when_newer(tmp_path):
+    root = str(tmp_path / "ckpt")
+    a = _trainer(iters=7, extra_tc=dict(save=root, save_interval=4, non_persistent_ckpt_type="global",
+                                        non_persistent_save_interval=1))
+    ref = a.train(7)
+    np_root = os.path.join(root, "non_persistent")
+    assert sorted(n for n in os.listdir(np_root) if n.startswith("iter_")) == ["iter_0000007"]
+    assert os.path.isdir(os.path.join(root, "iter_0000004")) and C.latest_iteration(root) == 4
+    # a fresh trainer resumes from the newer, non-persistent state (iteration 7), not from the persistent one (4)
+    logs = []
+    b = _trainer(iters=9, extra_tc=dict(save=root, non_persistent_ckpt_type="global"))
+    b.log = logs.append
+    assert b.load_checkpoint(root) == 7 and any("non-persistent" in l for l in logs)
+    c = _trainer(iters=9, extra_tc=dict(save=root))
+    assert c.load_checkpoint(root) == 4
+    more_ref = a.train(2)
+    assert b.train(2) == more_ref and len(ref) == 7

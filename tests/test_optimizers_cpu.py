@@ -334,3 +334,41 @@ def test_grad_spike_threshold_skips_the_step():
     assert moved and norm > 0
     assert run(norm * 0.5)[0] is False          # the norm is above the threshold: step skipped
     assert run(norm * 2.0)[0] is True
+
+
+def test_grad_sanitize_zeroes_non_finite_entries_instead_of_skipping_the_step():
+    """``sft_grad_sanitize``: a NaN / Inf in the gradient buffer makes the plain optimizer skip the whole step; with the
+    sanitiser only the poisoned elements lose their update."""
+    import torch
+
+    from primus_b200.engine.trainer import TrainConfig, Trainer
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.parallel import state as ps
+
+    def run(sanitize):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc = TransformerConfig(num_layers=2, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_query_groups=2,
+                               vocab_size=256, params_dtype="fp32", make_vocab_size_divisible_by=64)
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=1, lr=1e-2,
+                         lr_decay_style="constant", sft_grad_sanitize=sanitize)
+        torch.manual_seed(0)
+        tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+        before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+        # poison two gradient entries right before the optimizer looks at them
+        orig = tr.optimizer.compute_grad_norm
+
+        def poisoned():
+            g = tr.buffers[0].grad_data
+            g[5], g[77] = float("nan"), float("inf")
+            return orig()
+
+        tr.optimizer.compute_grad_norm = poisoned
+        tr.train(1)
+        moved = sum(int(not torch.equal(p, before[n])) for n, p in tr.model.named_parameters())
+        return moved, int(tr.optimizer.sanitized_count), float(tr.optimizer.grad_norm)
+
+    moved, count, norm = run(False)
+    assert moved == 0 and count == 0                      # non-finite norm: the step is skipped
+    moved, count, norm = run(True)
+    assert moved > 0 and count == 2 and norm == norm and norm < float("inf")

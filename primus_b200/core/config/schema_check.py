@@ -36,8 +36,7 @@ INERT_KEYS = {
     "use_turbo_rms_norm", "turbo_deepep_num_cu",
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "straggler_ctrlr_port",
-    "weight_deosc", "weight_deosc_period",
-    "weight_deosc_ratio", "trainable",
+    "trainable",
     "log_throughput", "use_tp_pp_dp_mapping", "offload_ops",
     # switches between the reference's two pipeline implementations (one runtime here; the schedule is chosen with
     # pp_algorithm / pipeline_schedule or enable_zero_bubble + zero_bubble_v_schedule)

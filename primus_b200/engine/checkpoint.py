@@ -490,6 +490,10 @@ def save_checkpoint(trainer, root: str, release: bool = False) -> str:
         objects[f"rng_state/rank_{st.rank}"] = {
             "cpu": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
             "tracker": _rng_tracker().state_dict(), "world": st.world_size}
+    deosc = getattr(trainer.optimizer, "deosc", None)
+    if save_optim and deosc is not None:
+        # windows of the MXFP4 weight de-oscillation detector: per rank, reusable under the same layout only
+        objects[f"weight_deosc/rank_{st.rank}"] = {"world": st.world_size, "state": deosc.state_dict()}
     # device -> host now (the training step that follows may overwrite the tensors); the file I/O can run later
     async_save = bool(getattr(tc, "async_save", False))
     staged = [Piece(p.key, p.tensor.detach().to("cpu", copy=True).contiguous(), p.offsets, p.global_shape) for p in pieces]
@@ -586,7 +590,7 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
     log = getattr(trainer, "log", print)
     pieces, finish = _collect_model_pieces(trainer, for_load=True)
     wanted = {p.key for p in pieces}
-    saved_model = {k for k in md if not k.startswith(("optimizer", "rng_state/"))}
+    saved_model = {k for k in md if not k.startswith(("optimizer", "rng_state/", "weight_deosc/"))}
     missing = sorted(wanted - saved_model)
     _strictness(getattr(tc, "dist_ckpt_strictness", None), missing, sorted(saved_model - wanted), log)
     pieces = [p for p in pieces if p.key in md]
@@ -603,6 +607,9 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
         obj_keys.append(f"rng_state/rank_{st.rank}")
     if with_optim and getattr(trainer, "fsdp", False):
         obj_keys.append(f"optimizer/fsdp2_rank_{st.rank}")
+    deosc = getattr(trainer.optimizer, "deosc", None)
+    if with_optim and deosc is not None and f"weight_deosc/rank_{st.rank}" in md:
+        obj_keys.append(f"weight_deosc/rank_{st.rank}")
     # ``ckpt_fully_parallel_load``: tensors replicated over the data-parallel ranks are read from disk by one of them
     # each and broadcast, instead of every rank reading everything
     spread = bool(getattr(tc, "ckpt_fully_parallel_load", False)) and st.dp > 1 and st.cp == 1 and \
@@ -646,6 +653,9 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
             trainer.optimizer.load_state_dict(sd)
         else:
             trainer.optimizer.step_count = int(common.get("optimizer", {}).get("step", 0))
+        saved_deosc = planner.loaded_objects.get(f"weight_deosc/rank_{st.rank}")
+        if deosc is not None and saved_deosc is not None and saved_deosc.get("world") == st.world_size:
+            deosc.load_state_dict(saved_deosc["state"])
     else:
         if load_optim and not finetune:
             log(f"[checkpoint] {d} was saved without optimizer state: master weights are re-derived from the "

@@ -141,6 +141,13 @@ class TrainConfig:
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
     sft_grad_sanitize: bool = False   # zero non-finite gradient entries instead of skipping / failing the step
+    # MXFP4 weight de-oscillation (parallel/weight_deosc.py): over windows of ``period`` steps, elements whose quantised
+    # value travelled ``ratio`` times further than their master value are snapped onto their current code
+    weight_deosc: bool = False
+    weight_deosc_period: int = 200
+    weight_deosc_ratio: float = 4.0
+    weight_deosc_start_step: int = 0
+    weight_deosc_log_freq: int = 0
     # frequent throw-away checkpoints next to the persistent ones: only the newest is kept, and a resume takes whichever
     # of the two kinds is newer.  type: "global" (under <save>/non_persistent or non_persistent_global_ckpt_dir), "local"
     # (a node-local directory: single-node jobs) or "in_memory" (a directory in /dev/shm: survives a process restart on
@@ -420,7 +427,24 @@ class Trainer:
         if train_cfg.sft_grad_sanitize:
             assert not train_cfg.fused_dp_optimizer, "sft_grad_sanitize works on the NCCL optimizer path"
             self.optimizer.sanitize_grads = True
+        if train_cfg.weight_deosc:
+            self._install_weight_deosc()
         self._install_param_gather_waits()
+
+    def _install_weight_deosc(self):
+        from ..parallel.weight_deosc import WeightDeOsc, WeightDeOscConfig
+
+        tc = self.tcfg
+        if not self.mcfg.fp4:
+            self.log("[weight de-osc] weight_deosc is set but fp4 is not: nothing is quantised to 4 bits, not installed")
+            return
+        if not hasattr(self.optimizer, "state") or not hasattr(self.optimizer, "deosc"):
+            self.log(f"[weight de-osc] the {tc.optimizer} optimizer keeps no flat fp32 master shards: not installed")
+            return
+        cfg = WeightDeOscConfig(True, int(tc.weight_deosc_period), float(tc.weight_deosc_ratio),
+                                int(tc.weight_deosc_start_step), int(tc.weight_deosc_log_freq))
+        self.optimizer.deosc = WeightDeOsc(cfg, log=self.log)
+        self.log(f"[weight de-osc] on: period {cfg.period}, ratio {cfg.ratio_threshold}, from step {cfg.start_step}")
 
     # ------------------------------------------------------------------ overlap_param_gather
     def _install_param_gather_waits(self):

@@ -397,6 +397,8 @@ class DistributedOptimizer:
         self.post_validation = False
         self.post_validation_exact = True
         self.post_validation_redos = 0
+        # MXFP4 weight de-oscillation (parallel/weight_deosc.py): runs on the master shards after every update
+        self.deosc = None
         self.step_count = 0
         self.state = []
         dev = buffers[0].device
@@ -556,6 +558,9 @@ class DistributedOptimizer:
                                           buf.param_data[lo:hi4], lr=lr, beta1=self.betas[0], beta2=self.betas[1],
                                           eps=self.eps, weight_decay=wd * mult, step=self.step_count,
                                           grad_scale=self.coef, skip=self.skip)
+        # a de-oscillation window that closes here may rewrite elements of the local shards (every rank closes its
+        # windows on the same step): pulled shards are read after it anyway, pushed ones are gathered once more
+        snapped = self.deosc.run(self) if self.deosc is not None else False
         for buf in self.buffers:
             if buf.symmetric and buf.copy_engine_gather:
                 buf.start_param_sync_copy_engine()
@@ -563,6 +568,9 @@ class DistributedOptimizer:
                     buf.finish_param_sync()
             elif buf.symmetric:
                 buf.sym_param.barrier(0)  # all parameter shards have landed everywhere
+                if snapped:
+                    buf.start_param_sync(async_op=False)
+                    buf.finish_param_sync()
             else:
                 buf.start_param_sync(async_op=False)
                 buf.finish_param_sync()
@@ -581,6 +589,8 @@ class DistributedOptimizer:
             return self._post_validated_step(lr, wd)
         self.compute_grad_norm()
         self._apply_adamw(lr, wd)
+        if self.deosc is not None:
+            self.deosc.run(self)
         for buf in self.buffers:
             buf.start_param_sync(async_op=self.overlap_param_gather)
             if not self.overlap_param_gather:
@@ -645,6 +655,8 @@ class DistributedOptimizer:
             else:
                 self._invert_adamw(lr, wd)
             self._apply_adamw(lr, wd)                  # the kernels read the global coefficient / skip flag now
+        if self.deosc is not None:
+            self.deosc.run(self)
         for buf in self.buffers:
             buf.start_param_sync(async_op=self.overlap_param_gather)
             if not self.overlap_param_gather:

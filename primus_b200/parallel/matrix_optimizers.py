@@ -74,6 +74,8 @@ class _PerParameterOptimizer(DistributedOptimizer):
         if not skip:
             self._update(lr, wd)
             self._write_back()
+        if self.deosc is not None:
+            self.deosc.run(self)
         return self.grad_norm
 
 

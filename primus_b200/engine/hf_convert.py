@@ -39,6 +39,21 @@ def config_from_hf(hf: dict) -> dict:
                kv_channels=hf.get("head_dim") or hf["hidden_size"] // nh)
     if mt in ("qwen3", "qwen3_moe"):
         out["qk_layernorm"] = True
+    if mt in ("qwen3_5_moe_text", "qwen3_5_text", "qwen3_5_moe", "qwen3_5", "qwen3_next"):
+        # gated-delta-net layers between gated full-attention layers, zero-centred norm gains, partial rotary embedding
+        kinds = hf.get("layer_types") or ["full_attention" if (i + 1) % hf.get("full_attention_interval", 4) == 0
+                                          else "linear_attention" for i in range(hf["num_hidden_layers"])]
+        out.update(qk_layernorm=True, attention_output_gate=True, apply_layernorm_1p=True,
+                   experimental_attention_variant="gated_delta_net",
+                   linear_attention_freq=[int(k == "linear_attention") for k in kinds],
+                   rotary_percent=float(rp.get("partial_rotary_factor", hf.get("partial_rotary_factor", 0.25))),
+                   linear_conv_kernel_dim=hf.get("linear_conv_kernel_dim", 4),
+                   linear_key_head_dim=hf["linear_key_head_dim"], linear_value_head_dim=hf["linear_value_head_dim"],
+                   linear_num_key_heads=hf["linear_num_key_heads"], linear_num_value_heads=hf["linear_num_value_heads"])
+        if hf.get("num_experts"):
+            out.update(moe_layer_freq=[1] * hf["num_hidden_layers"], moe_router_pre_softmax=False,
+                       moe_shared_expert_intermediate_size=hf.get("shared_expert_intermediate_size") or None,
+                       moe_shared_expert_gate=bool(hf.get("shared_expert_intermediate_size")))
     if mt == "lfm2":        # gated short convolutions + grouped-query attention with per-head q / k norms
         out.update(lfm_layer_types=list(hf["layer_types"]), conv_L_cache=hf.get("conv_L_cache", 3),
                    conv_bias=bool(hf.get("conv_bias", False)), qk_layernorm=True, norm_epsilon=hf.get("norm_eps", 1e-5),
@@ -193,9 +208,23 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
             sd[a + "linear_kv_down_proj.weight"] = _mla_rows(hf[h + "self_attn.kv_a_proj_with_mqa.weight"], cfg, True, perm)
             sd[a + "linear_kv_up_proj.layer_norm_weight"] = hf[h + "self_attn.kv_a_layernorm.weight"]
             sd[a + "linear_kv_up_proj.weight"] = hf[h + "self_attn.kv_b_proj.weight"]
+        elif cfg.layer_kinds[L][0] == "gdn":
+            g, x = h + "linear_attn.", p + "mixer."
+            sd[x + "in_proj.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
+            sd[x + "in_proj.weight"] = torch.cat([hf[g + "in_proj_qkv.weight"], hf[g + "in_proj_z.weight"],
+                                                  hf[g + "in_proj_b.weight"], hf[g + "in_proj_a.weight"]], 0)
+            sd[x + "conv1d.weight"] = hf[g + "conv1d.weight"]
+            sd[x + "dt_bias"], sd[x + "A_log"] = hf[g + "dt_bias"], hf[g + "A_log"]
+            sd[x + "out_norm.weight"] = hf[g + "norm.weight"]
+            sd[x + "out_proj.weight"] = hf[g + "out_proj.weight"]
         else:
             sd[a + "linear_qkv.layer_norm_weight"] = hf[h + "input_layernorm.weight"]
-            sd[a + "linear_qkv.weight"] = torch.cat([hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"],
+            wq = hf[h + "self_attn.q_proj.weight"]
+            if cfg.attention_output_gate:       # rows per head: [query (d) | gate (d)]
+                wq = wq.reshape(cfg.num_attention_heads, 2, cfg.kv_channels, -1)
+                sd[a + "linear_gate.weight"] = wq[:, 1].reshape(-1, wq.shape[-1])
+                wq = wq[:, 0].reshape(-1, wq.shape[-1])
+            sd[a + "linear_qkv.weight"] = torch.cat([wq, hf[h + "self_attn.k_proj.weight"],
                                                      hf[h + "self_attn.v_proj.weight"]], 0)
             if cfg.add_qkv_bias:
                 sd[a + "linear_qkv.bias"] = torch.cat([hf[h + "self_attn.q_proj.bias"], hf[h + "self_attn.k_proj.bias"],
@@ -203,7 +232,8 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
             if cfg.qk_layernorm:
                 sd[a + "q_layernorm.weight"] = hf[h + "self_attn.q_norm.weight"]
                 sd[a + "k_layernorm.weight"] = hf[h + "self_attn.k_norm.weight"]
-        sd[a + "linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
+        if cfg.layer_kinds[L][0] == "attention":
+            sd[a + "linear_proj.weight"] = hf[h + "self_attn.o_proj.weight"]
         m = p + "mlp."
         if cfg.is_moe_layer(L):
             sd[p + "pre_mlp_layernorm.weight"] = hf[h + "post_attention_layernorm.weight"]
@@ -229,9 +259,12 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
                 sd[m + "experts.fc2_weight.weight"] = torch.stack(
                     [hf[h + f"mlp.experts.{e}.down_proj.weight"] for e in range(cfg.num_experts)])
             if cfg.moe_shared_expert_intermediate_size:
+                se = h + ("mlp.shared_experts." if h + "mlp.shared_experts.gate_proj.weight" in hf else "mlp.shared_expert.")
                 sd[m + "shared_experts.linear_fc1.weight"] = torch.cat(
-                    [hf[h + "mlp.shared_experts.gate_proj.weight"], hf[h + "mlp.shared_experts.up_proj.weight"]], 0)
-                sd[m + "shared_experts.linear_fc2.weight"] = hf[h + "mlp.shared_experts.down_proj.weight"]
+                    [hf[se + "gate_proj.weight"], hf[se + "up_proj.weight"]], 0)
+                sd[m + "shared_experts.linear_fc2.weight"] = hf[se + "down_proj.weight"]
+                if cfg.moe_shared_expert_gate:
+                    sd[m + "shared_experts.gate_weight"] = hf[h + "mlp.shared_expert_gate.weight"]
         else:
             sd[m + "linear_fc1.layer_norm_weight"] = hf[h + "post_attention_layernorm.weight"]
             sd[m + "linear_fc1.weight"] = torch.cat([hf[h + "mlp.gate_proj.weight"], hf[h + "mlp.up_proj.weight"]], 0)
@@ -262,10 +295,26 @@ def internal_to_hf(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool = Fal
             hf[h + "self_attn.kv_a_proj_with_mqa.weight"] = _mla_rows(sd[a + "linear_kv_down_proj.weight"], cfg, True, perm)
             hf[h + "self_attn.kv_a_layernorm.weight"] = sd[a + "linear_kv_up_proj.layer_norm_weight"]
             hf[h + "self_attn.kv_b_proj.weight"] = sd[a + "linear_kv_up_proj.weight"]
+        elif cfg.layer_kinds[L][0] == "gdn":
+            g, x = h + "linear_attn.", p + "mixer."
+            qk = cfg.linear_num_key_heads * cfg.linear_key_head_dim
+            vd = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+            w = sd[x + "in_proj.weight"]
+            hf[h + "input_layernorm.weight"] = sd[x + "in_proj.layer_norm_weight"]
+            hf[g + "in_proj_qkv.weight"], hf[g + "in_proj_z.weight"] = w[: 2 * qk + vd], w[2 * qk + vd: 2 * qk + 2 * vd]
+            hf[g + "in_proj_b.weight"] = w[2 * qk + 2 * vd: 2 * qk + 2 * vd + cfg.linear_num_value_heads]
+            hf[g + "in_proj_a.weight"] = w[2 * qk + 2 * vd + cfg.linear_num_value_heads:]
+            hf[g + "conv1d.weight"] = sd[x + "conv1d.weight"]
+            hf[g + "dt_bias"], hf[g + "A_log"] = sd[x + "dt_bias"], sd[x + "A_log"]
+            hf[g + "norm.weight"] = sd[x + "out_norm.weight"]
+            hf[g + "out_proj.weight"] = sd[x + "out_proj.weight"]
         else:
             w = sd[a + "linear_qkv.weight"]
             hf[h + "input_layernorm.weight"] = sd[a + "linear_qkv.layer_norm_weight"]
             hf[h + "self_attn.q_proj.weight"] = w[: hq * d]
+            if cfg.attention_output_gate:
+                both = torch.stack([w[: hq * d].reshape(hq, d, -1), sd[a + "linear_gate.weight"].reshape(hq, d, -1)], 1)
+                hf[h + "self_attn.q_proj.weight"] = both.reshape(2 * hq * d, -1)
             hf[h + "self_attn.k_proj.weight"] = w[hq * d:(hq + hkv) * d]
             hf[h + "self_attn.v_proj.weight"] = w[(hq + hkv) * d:]
             if cfg.add_qkv_bias:
@@ -276,7 +325,8 @@ def internal_to_hf(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool = Fal
             if cfg.qk_layernorm:
                 hf[h + "self_attn.q_norm.weight"] = sd[a + "q_layernorm.weight"]
                 hf[h + "self_attn.k_norm.weight"] = sd[a + "k_layernorm.weight"]
-        hf[h + "self_attn.o_proj.weight"] = sd[a + "linear_proj.weight"]
+        if cfg.layer_kinds[L][0] == "attention":
+            hf[h + "self_attn.o_proj.weight"] = sd[a + "linear_proj.weight"]
         m = p + "mlp."
         if cfg.is_moe_layer(L):
             hf[h + "post_attention_layernorm.weight"] = sd[p + "pre_mlp_layernorm.weight"]
@@ -294,9 +344,12 @@ def internal_to_hf(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool = Fal
                 hf[h + f"mlp.experts.{e}.down_proj.weight"] = w2[e]
             if cfg.moe_shared_expert_intermediate_size:
                 ws = sd[m + "shared_experts.linear_fc1.weight"]
-                hf[h + "mlp.shared_experts.gate_proj.weight"] = ws[: ws.shape[0] // 2]
-                hf[h + "mlp.shared_experts.up_proj.weight"] = ws[ws.shape[0] // 2:]
-                hf[h + "mlp.shared_experts.down_proj.weight"] = sd[m + "shared_experts.linear_fc2.weight"]
+                se = h + ("mlp.shared_expert." if cfg.moe_shared_expert_gate else "mlp.shared_experts.")   # Qwen | DeepSeek
+                hf[se + "gate_proj.weight"] = ws[: ws.shape[0] // 2]
+                hf[se + "up_proj.weight"] = ws[ws.shape[0] // 2:]
+                hf[se + "down_proj.weight"] = sd[m + "shared_experts.linear_fc2.weight"]
+                if cfg.moe_shared_expert_gate:
+                    hf[h + "mlp.shared_expert_gate.weight"] = sd[m + "shared_experts.gate_weight"]
         else:
             w = sd[m + "linear_fc1.weight"]
             hf[h + "post_attention_layernorm.weight"] = sd[m + "linear_fc1.layer_norm_weight"]

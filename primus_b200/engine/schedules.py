@@ -134,6 +134,8 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             attn = 2 * seq_len * nh * (qd + cfg.v_head_dim)
         else:
             fwd += 2 * h * cfg.qkv_width + 2 * cfg.num_attention_heads * cfg.kv_channels * h
+            if cfg.attention_output_gate:
+                fwd += 2 * h * cfg.num_attention_heads * cfg.kv_channels
             attn = 4 * seq_len * cfg.num_attention_heads * cfg.kv_channels
         fwd += attn * (0.5 if causal_half else 1.0)
         if not has_mlp:

@@ -133,6 +133,14 @@ class TransformerConfig:
     linear_num_key_heads: int = 8
     linear_num_value_heads: int = 16
     linear_chunk_size: int = 64
+    # Qwen3.5-style stacks: linear-attention layers between full-attention layers in a GPT-style stack (every layer keeps
+    # its MLP / MoE block).  ``linear_attention_freq``: int N -> every N-th layer attends fully, the others are linear;
+    # a list (or a list expression such as "([1]*3+[0])*10") marks the linear layers with 1.
+    experimental_attention_variant: Optional[str] = None     # "gated_delta_net"
+    linear_attention_freq: object = None
+    attention_output_gate: bool = False     # softmax attention output multiplied by sigmoid(gate), gate projected like q
+    apply_layernorm_1p: bool = False        # norm gains stored as (gain - 1)
+    moe_shared_expert_gate: bool = False    # shared-expert output multiplied by sigmoid(hidden . gate_weight)
 
     def layer_window(self, layer_idx: int) -> int:
         """Sliding-window width of a layer (0 = full attention)."""
@@ -227,6 +235,8 @@ class TransformerConfig:
                 n += self.num_attention_heads * self.v_head_dim * h
             else:
                 n += h * self.qkv_width + self.num_attention_heads * self.kv_channels * h
+                if self.attention_output_gate:
+                    n += h * self.num_attention_heads * self.kv_channels
                 if self.add_qkv_bias:
                     n += self.qkv_width
                 if self.qk_layernorm:
@@ -236,7 +246,7 @@ class TransformerConfig:
             if self.is_moe_layer(i):
                 n += h * self.num_experts + self.num_experts * 3 * h * self.moe_ffn_hidden_size
                 if self.moe_shared_expert_intermediate_size:
-                    n += 3 * h * self.moe_shared_expert_intermediate_size
+                    n += 3 * h * self.moe_shared_expert_intermediate_size + (h if self.moe_shared_expert_gate else 0)
             else:
                 n += 3 * h * self.ffn_hidden_size
         return n
@@ -311,6 +321,17 @@ def layer_kinds(cfg) -> list:
         bad = set(cfg.lfm_layer_types) - {"conv", "full_attention"}
         assert not bad, f"lfm_layer_types: unknown kinds {sorted(bad)}"
         return [("conv" if t == "conv" else "attention", True) for t in cfg.lfm_layer_types]
+    variant = (cfg.experimental_attention_variant or "").lower()
+    if variant and cfg.linear_attention_freq:
+        kinds = {"gated_delta_net": "gdn", "gdn": "gdn"}
+        if variant not in kinds:
+            raise NotImplementedError(f"experimental_attention_variant {variant!r}: gated_delta_net is built")
+        freq = cfg.linear_attention_freq
+        if isinstance(freq, int):
+            linear = [int((i + 1) % freq != 0) for i in range(L)]
+        else:
+            linear = parse_moe_layer_freq(freq, L)      # the same restricted list expressions
+        return [(kinds[variant] if x else "attention", True) for x in linear]
     return [("attention", True)] * L
 
 

@@ -36,6 +36,12 @@ def _param(shape, std, dtype, device, is_norm=False, seed_offset=0):
     return nn.Parameter(p)
 
 
+def is_norm_gain(name: str) -> bool:
+    """Is this parameter the gain of an RMSNorm that ``apply_layernorm_1p`` stores centred on zero?  (Not the gated
+    norms inside the Mamba / gated-delta-net mixers, ``norm.weight`` / ``out_norm.weight``.)"""
+    return name.endswith("layer_norm_weight") or name.endswith(("layernorm.weight", "enorm.weight", "hnorm.weight"))
+
+
 class ParamHolder(nn.Module):
     """A module that only owns named parameters (keeps checkpoint key paths identical to mcore)."""
 
@@ -66,6 +72,13 @@ class SelfAttention(nn.Module):
             self.linear_qkv.bias.tensor_model_parallel = tp > 1
             self.linear_qkv.bias.partition_dim = 0
         self.linear_proj = ParamHolder(weight=_param((h, self.hq * d), out_std, dt, device))
+        if cfg.attention_output_gate:
+            # Qwen3.5 / Qwen3-Next: a gate projected from the same normalised input as q, one value per output channel;
+            # the attention output is multiplied by its sigmoid before the output projection.  Kept as a projection of
+            # its own (column-parallel like q), so the [q | k | v] layout of linear_qkv is the same with and without it.
+            self.linear_gate = ParamHolder(weight=_param((self.hq * d, h), std, dt, device))
+            self.linear_gate.weight.tensor_model_parallel = tp > 1
+            self.linear_gate.weight.partition_dim = 0
         if cfg.qk_layernorm:
             self.q_layernorm = ParamHolder(weight=_param((d,), 0, dt, device, is_norm=True))
             self.k_layernorm = ParamHolder(weight=_param((d,), 0, dt, device, is_norm=True))
@@ -130,6 +143,10 @@ class SelfAttention(nn.Module):
                                                 rot_dim=int(d * cfg.rotary_percent), causal=True, scale=scale,
                                                 window=self.window, sinks=sinks, segments=segments,
                                                 softcap=cfg.attn_logit_softcapping or 0.0), qkv)
+        if cfg.attention_output_gate:
+            gate, _ = layers.norm_linear(hidden, residual, self.linear_qkv.layer_norm_weight, self.linear_gate.weight,
+                                         cfg.norm_epsilon, tpg, sp)
+            ctx_out = (ctx_out.reshape(gate.shape) * torch.sigmoid(gate.float()).to(ctx_out.dtype)).contiguous()
         out = layers.row_parallel_linear(ctx_out, self.linear_proj.weight, tpg, sp)
         return out, xsum
 
@@ -354,6 +371,12 @@ class GPTModel(nn.Module):
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
                                              for _ in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
+        fused.set_zero_centered_gamma(cfg.apply_layernorm_1p)
+        if cfg.apply_layernorm_1p:
+            with torch.no_grad():
+                for name, p in self.named_parameters():
+                    if is_norm_gain(name):
+                        p.zero_()
 
     # ------------------------------------------------------------------ helpers
     def rope_tables(self, device, seq: int):

@@ -78,8 +78,10 @@ class MoELayer(nn.Module):
             p.sequence_parallel = tp > 1 and self.ep == 1
         if cfg.moe_shared_expert_intermediate_size:
             self.shared_experts = MLP(cfg, device, 1, ffn=cfg.moe_shared_expert_intermediate_size, with_norm=False)
+            if cfg.moe_shared_expert_gate:      # Qwen MoE: the shared expert's output is scaled by sigmoid(y . gate)
+                self.shared_experts.register_parameter("gate_weight", _param((1, H), std, dt, device))
         if tp > 1:
-            replicated = [self.router.weight] + ([self.shared_experts.linear_fc1.weight, self.shared_experts.linear_fc2.weight]
+            replicated = [self.router.weight] + ([p for p in self.shared_experts.parameters()]
                                                  if hasattr(self, "shared_experts") else [])
             for p in replicated:
                 p.sequence_parallel = True
@@ -152,7 +154,11 @@ class MoELayer(nn.Module):
         else:
             out = self._forward_ep(y, probs, flat_e, counts_global, T, k)
         if hasattr(self, "shared_experts"):
-            out = out + self.shared_experts.forward_normed(y)
+            shared = self.shared_experts.forward_normed(y)
+            if cfg.moe_shared_expert_gate:
+                g = torch.sigmoid(torch.nn.functional.linear(y.float(), self.shared_experts.gate_weight.float()))
+                shared = shared * g.to(shared.dtype)
+            out = out + shared
         return out
 
     # ------------------------------------------------------------------ single rank

@@ -48,6 +48,25 @@ def attention_ref(q, k, v, batch: int, causal: bool = True, scale: float | None 
     return o.to(q.dtype), lse
 
 
+KERNEL_HEAD_DIMS = ((128, 128), (192, 128), (64, 64))     # (d_qk, d_v) the flash-attention kernels are instantiated for
+_WARNED: set = set()
+
+
+def kernel_supports(d_qk: int, d_v: int) -> bool:
+    return (d_qk, d_v) in KERNEL_HEAD_DIMS
+
+
+def warn_composed(d_qk: int, d_v: int) -> None:
+    """Head sizes without a kernel (256 in Qwen3.5) run as composed PyTorch operations that materialise the score
+    matrix: correct, but neither fast nor memory-lean.  Said once per size."""
+    if (d_qk, d_v) not in _WARNED:
+        _WARNED.add((d_qk, d_v))
+        import warnings
+
+        warnings.warn(f"no flash-attention kernel for head sizes ({d_qk}, {d_v}): attention runs as composed PyTorch "
+                      f"operations with the full score matrix (kernels exist for {KERNEL_HEAD_DIMS})", stacklevel=3)
+
+
 def _check_view(t, d):
     assert t.stride(2) == 1 and t.stride(1) == d, "heads must be contiguous [.., H, D] views"
     assert t.data_ptr() % 16 == 0
@@ -129,6 +148,9 @@ def flash_attention(q, k, v, batch: int = 1, causal: bool = True, scale: float |
     attention and learned per-head sink logits (fp32 [Hq]) as the reference passes them to ``flash_attn_func``
     (primus/backends/megatron/core/extensions/primus_turbo.py:876-883,924-942)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and not kernel_supports(q.shape[-1], v.shape[-1]):
+        warn_composed(q.shape[-1], v.shape[-1])
+        return attention_ref(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)[0]
     if not q.is_cuda:
         return attention_ref(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)[0]
     return FlashAttnFn.apply(q, k, v, batch, causal, scale, q_off, window, sinks, softcap)

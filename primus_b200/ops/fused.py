@@ -100,8 +100,25 @@ class RMSNormFn(torch.autograd.Function):
         return dx, dw, None, None
 
 
+# ``apply_layernorm_1p``: the norm weights are stored centred on zero and the norm multiplies by ``1 + weight`` (weight
+# decay then pulls the gain towards 1 instead of 0).  Set by the model from its configuration; the gated norms inside the
+# Mamba / gated-delta-net mixers keep plain weights.
+ZERO_CENTERED_GAMMA = False
+
+
+def set_zero_centered_gamma(flag: bool) -> None:
+    global ZERO_CENTERED_GAMMA
+    ZERO_CENTERED_GAMMA = bool(flag)
+
+
+def gamma(w):
+    """The gain a norm applies for the stored weight ``w``."""
+    return w + 1.0 if ZERO_CENTERED_GAMMA else w
+
+
 def rmsnorm(x, w, eps=1e-5, residual=None):
     """RMSNorm over the last dim. ``residual`` given -> returns (y, x + residual)."""
+    w = gamma(w)
     if not x.is_cuda:
         return rmsnorm_ref(x, w, eps, residual)
     return RMSNormFn.apply(x, w, eps, residual)

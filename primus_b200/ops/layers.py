@@ -113,6 +113,7 @@ def norm_linear(hidden, residual, norm_w, weight, eps, tp_group=None, sequence_p
     shard is all-gathered over ``tp_group`` before the GEMM (reduce-scatter of the input gradient in
     backward); without it the input gradient is all-reduced."""
     sp = bool(sequence_parallel and tp_group is not None)
+    norm_w = fused.gamma(norm_w)
     if not hidden.is_cuda:
         if residual is not None:
             y, xsum = fused.rmsnorm_ref(hidden, norm_w, eps, residual)
@@ -361,7 +362,10 @@ def rope_attention(qkv, cos, sin, pos, batch, hq, hkv, d, rot_dim=None, causal=T
     the token dimension (attention stays inside each; on CUDA every range must be a multiple of 128 rows)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     rot_dim = rot_dim or d
-    if not qkv.is_cuda:
+    composed = qkv.is_cuda and not attention.kernel_supports(d, d)
+    if composed:
+        attention.warn_composed(d, d)
+    if not qkv.is_cuda or composed:
         T = qkv.shape[0]
         q = qkv[:, : hq * d].reshape(T, hq, d)
         k = qkv[:, hq * d: (hq + hkv) * d].reshape(T, hkv, d)

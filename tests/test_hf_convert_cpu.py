@@ -129,3 +129,27 @@ def test_mixtral_matches_hf():
             old[h + f"block_sparse_moe.experts.{e}.w2.weight"] = dn[e]
     conv = H.hf_to_internal(old, cfg)
     assert conv.keys() == new.keys() and all(torch.equal(conv[k], new[k]) for k in new)
+
+
+def test_qwen3_5_moe_matches_hf():
+    """Gated-delta-net layers with grouped key heads, gated full attention with partial rotary embedding, zero-centred norm
+    gains and a gated shared expert."""
+    Q = pytest.importorskip("transformers.models.qwen3_5_moe")
+    torch.manual_seed(7)
+    c = Q.Qwen3_5MoeTextConfig(vocab_size=256, hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+                               num_key_value_heads=2, head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=16,
+                               linear_value_head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+                               moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts_per_tok=2,
+                               num_experts=4, full_attention_interval=4, max_position_embeddings=256,
+                               tie_word_embeddings=False)
+    m = Q.Qwen3_5MoeForCausalLM(c)
+    with torch.no_grad():       # the published initialisation leaves several tensors at zero / one: make every term count
+        for n, p in m.named_parameters():
+            if "norm" in n or "gate.weight" in n or "experts" in n or "dt_bias" in n:
+                p.normal_(0.0, 0.1)
+    try:
+        _check(m, c, torch.randint(0, 256, (2, 96)), tol=5e-4, linear_chunk_size=32)
+    finally:
+        from primus_b200.ops import fused
+
+        fused.set_zero_centered_gamma(False)

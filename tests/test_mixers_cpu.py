@@ -175,3 +175,41 @@ def test_gated_delta_net_stack_trains_and_counts_parameters():
     losses = tr.train()
     assert losses[-1] < losses[0] - 0.1, losses
     ps.destroy_model_parallel()
+
+
+def test_qwen3_5_style_stack_trains_and_resumes(tmp_path):
+    """Linear-attention layers inside a GPT-style stack (``linear_attention_freq``), gated attention output, zero-centred
+    norm gains and a gated shared expert through the trainer and a checkpoint round trip."""
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.ops import fused
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    extra = dict(experimental_attention_variant="gated_delta_net", linear_attention_freq=2, linear_num_key_heads=2,
+                 linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_chunk_size=16,
+                 attention_output_gate=True, apply_layernorm_1p=True, rotary_percent=0.5, qk_layernorm=True,
+                 moe_shared_expert_intermediate_size=32, moe_shared_expert_gate=True)
+
+    def make(iters):
+        mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=iters, layers=4, moe=True, extra_mc=extra)
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        return Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+
+    try:
+        tr = make(4)
+        assert [k for k, _ in tr.mcfg.layer_kinds] == ["gdn", "attention", "gdn", "attention"]
+        gains = [p for n, p in tr.model.named_parameters() if n.endswith("layer_norm_weight")]
+        assert gains and all(float(p.detach().abs().max()) == 0.0 for p in gains)          # stored as gain - 1
+        losses = tr.train()
+        assert len(losses) == 4 and all(x == x and abs(x) < 1e3 for x in losses)
+        assert any(float(p.detach().abs().max()) > 0.0 for p in gains)                      # and trained
+        tr.tcfg.save = str(tmp_path)
+        tr.save_checkpoint()
+        tr2 = make(6)
+        assert tr2.load_checkpoint(str(tmp_path)) == 4
+        for (n, a), (_, b) in zip(tr.model.named_parameters(), tr2.model.named_parameters()):
+            assert torch.equal(a, b), n
+    finally:
+        fused.set_zero_centered_gamma(False)
+        ps.destroy_model_parallel()

@@ -186,9 +186,15 @@ def saved_key(name: str) -> str:
 
 
 def model_named_parameters(trainer):
+    """Everything of the model that a checkpoint holds: the parameters and the persistent buffers (the router's
+    selection bias of auxiliary-loss-free / quantile load balancing is state that training changes, not a parameter)."""
     for m in trainer.model_chunks:
         for name, p in m.named_parameters():
             yield name, p
+        for mod_name, mod in m.named_modules():
+            for bn, b in mod._buffers.items():
+                if b is not None and bn not in mod._non_persistent_buffers_set:
+                    yield (f"{mod_name}.{bn}" if mod_name else bn), b
 
 
 # ----------------------------------------------------------------------------------------------

@@ -119,6 +119,14 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             c, nv, dk, dv = cfg.linear_chunk_size, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
             fwd += nv * (4 * c * dk + 2 * c * c + 2 * c * (dv + dk) + 6 * dk * dv)      # scores, solve, deltas, state
             attn = 0.0
+        elif mixer == "kda":           # Kimi delta attention: projections, gate bottleneck, convolution, chunked rule
+            nh, dk, dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+            qk, vd = nh * dk, nh * dv
+            conv_dim = 2 * qk + vd
+            fwd += 2 * h * (conv_dim + vd + dk + nh) + 2 * dk * qk + 2 * vd * h + 2 * conv_dim * cfg.linear_conv_kernel_dim
+            c = cfg.kda_chunk_size
+            fwd += nh * (4 * c * dk + 2 * c * c + 2 * c * (dv + dk) + 6 * dk * dv)
+            attn = 0.0
         elif mixer is None:
             attn = 0.0
         elif cfg.multi_latent_attention:
@@ -131,6 +139,8 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             fwd += 2 * h * (cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim)
             fwd += 2 * cfg.kv_lora_rank * nh * (cfg.qk_head_dim + cfg.v_head_dim)
             fwd += 2 * nh * cfg.v_head_dim * h
+            if getattr(cfg, "mla_use_output_gate", False):
+                fwd += 2 * h * nh * cfg.v_head_dim
             attn = 2 * seq_len * nh * (qd + cfg.v_head_dim)
         else:
             fwd += 2 * h * cfg.qkv_width + 2 * cfg.num_attention_heads * cfg.kv_channels * h
@@ -142,7 +152,8 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             continue
         if cfg.is_moe_layer(i):
             fwd += 2 * h * cfg.num_experts
-            fwd += cfg.moe_router_topk * 6 * h * cfg.moe_ffn_hidden_size
+            lat = getattr(cfg, "routed_expert_hidden_size", None) or h      # latent experts + the two shared projections
+            fwd += cfg.moe_router_topk * 6 * lat * cfg.moe_ffn_hidden_size + (4 * h * lat if lat != h else 0)
             if cfg.moe_shared_expert_intermediate_size:
                 fwd += 6 * h * cfg.moe_shared_expert_intermediate_size
         else:

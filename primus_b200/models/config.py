@@ -141,6 +141,41 @@ class TransformerConfig:
     attention_output_gate: bool = False     # softmax attention output multiplied by sigmoid(gate), gate projected like q
     apply_layernorm_1p: bool = False        # norm gains stored as (gain - 1)
     moe_shared_expert_gate: bool = False    # shared-expert output multiplied by sigmoid(hidden . gate_weight)
+    # Kimi-K3 (models/kimi_k3.py): ``model_type: kimi_k3`` makes the layers marked 1 in ``linear_attention_freq`` Kimi
+    # delta attention and the others multi-latent attention without rotary embedding and with an output gate
+    kda_gate_lower_bound: Optional[float] = -5.0    # bounded log-decay lower_bound * sigmoid(.); None: -exp(A) softplus(.)
+    kda_chunk_size: int = 64
+    kda_use_full_rank_gate: bool = True             # the low-rank output gate of Kimi Linear is not built
+    mla_use_nope: bool = False                      # multi-latent attention without rotation (the "rope" dims stay)
+    mla_use_output_gate: bool = False               # attention output times sigmoid(linear_o_gate(h)) before the projection
+    attn_res_block_size: Optional[int] = None       # attention residuals: every N-th layer sets a checkpoint aside
+    routed_expert_hidden_size: Optional[int] = None     # latent MoE: routed experts work in this (smaller) width
+    latent_moe_use_norm: bool = True                # RMSNorm on the combined expert output before the up-projection
+    activation_situ_beta: float = 4.0               # gated_activation "situ": beta tanh(g / beta) sigmoid(g) ...
+    activation_situ_linear_beta: float = 25.0       # ... times linear_beta tanh(u / linear_beta)
+    moe_router_bias_update_rule: str = "sign"       # "quantile": Kimi-K3 quantile balancing
+    # DeepSeek-V4 (models/deepseek_v4.py): ``model_type: deepseek_v4``
+    hc_mult: int = 1                                # hyper-connections: parallel residual streams (1: plain residual)
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    compress_ratios: object = None                  # per layer 0 (local attention only) | 4 (indexed) | 128 (pooled)
+    compress_rope_theta: float = 160000.0           # rotary base of the layers with a compressed branch
+    index_topk: int = 512
+    index_head_dim: int = 128
+    index_n_heads: int = 64
+    attn_sliding_window: int = 128                  # local branch: the last N keys (0: all earlier keys)
+    attn_sink: bool = True                          # learned per-head sink logit
+    o_groups: int = 8                               # grouped low-rank output projection
+    o_lora_rank: int = 1024                         # 0: one flat output projection
+    v4_indexer_distill_loss_coeff: float = 0.0      # > 0: the indexer learns from the attention it feeds (KL on its picks)
+    num_hash_layers: int = 0                        # the first N MoE layers pick experts from a token-id table
+    hash_router_seed: int = 1234
+    quantile_balancing_num_bins: int = 1024
+    quantile_balancing_margin_min: float = -1.0
+    quantile_balancing_margin_max: float = 1.0
+    quantile_balancing_center_bias: bool = True
+    quantile_balancing_update_interval: int = 1
+    quantile_balancing_ema_decay: Optional[float] = None
 
     def layer_window(self, layer_idx: int) -> int:
         """Sliding-window width of a layer (0 = full attention)."""
@@ -162,6 +197,20 @@ class TransformerConfig:
             self.kv_channels = self.hidden_size // self.num_attention_heads
         if self.moe_ffn_hidden_size is None:
             self.moe_ffn_hidden_size = self.ffn_hidden_size
+        self.compress_ratio_list = None
+        if self.model_type == "deepseek_v4":
+            r = self.compress_ratios
+            if isinstance(r, str):
+                r = ast.literal_eval(r)
+            self.compress_ratio_list = [0] * self.num_layers if r is None else [int(x) for x in r]
+            # the published lists carry one more entry per multi-token-prediction depth behind the decoder layers
+            if len(self.compress_ratio_list) > self.num_layers:
+                self.compress_ratio_list = self.compress_ratio_list[:self.num_layers]
+            if len(self.compress_ratio_list) != self.num_layers:
+                raise ValueError(f"compress_ratios has {len(self.compress_ratio_list)} entries for {self.num_layers} layers")
+        if self.model_type == "kimi_k3":
+            self.multi_latent_attention = True      # the full-attention layers of the stack
+            self.mla_use_nope = True
         self.moe_layer_pattern = parse_moe_layer_freq(self.moe_layer_freq, self.num_layers) \
             if self.num_experts else [0] * self.num_layers
         self.layer_kinds = layer_kinds(self)
@@ -207,6 +256,10 @@ class TransformerConfig:
         h, L = self.hidden_size, self.num_layers
         V = self.padded_vocab_size
         n = V * h * (2 if self.untie_embeddings_and_output_weights else 1) + h
+        if self.attn_res_block_size:
+            n += 2 * h                              # the mix after the last layer
+        if self.hc_mult > 1:
+            n += self.hc_mult * (self.hc_mult * h + 1) + 1      # the collapse after the last layer
         for i in range(L):
             mixer, has_mlp = self.layer_kinds[i]
             n += h * (int(mixer is not None) + int(has_mlp))  # one norm per sub-layer
@@ -222,6 +275,27 @@ class TransformerConfig:
                 conv_dim = 2 * qk + vd
                 n += h * (conv_dim + vd + 2 * self.linear_num_value_heads) + conv_dim * self.linear_conv_kernel_dim
                 n += 2 * self.linear_num_value_heads + self.linear_value_head_dim + vd * h
+            elif mixer == "v4":
+                nh, hd = self.num_attention_heads, self.kv_channels
+                n += h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * hd + h * hd + hd
+                n += nh if self.attn_sink else 0
+                n += (nh * hd * self.o_lora_rank + h * self.o_groups * self.o_lora_rank) if self.o_lora_rank else nh * hd * h
+                ratio = self.compress_ratio_list[i]
+
+                def comp(d):       # a compressor of width d: projection, position term, norm
+                    c = 2 if ratio == 4 else 1
+                    return 2 * c * d * h + c * ratio * d + d
+                if ratio:
+                    n += comp(hd)
+                if ratio == 4:
+                    n += h * (self.index_head_dim + self.index_n_heads) + self.index_n_heads * self.index_head_dim ** 2
+                    n += comp(self.index_head_dim)
+            elif mixer == "kda":
+                qk, vd = self.linear_num_value_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+                conv_dim = 2 * qk + vd
+                n += h * (conv_dim + vd + self.linear_key_head_dim + self.linear_num_value_heads)
+                n += conv_dim * self.linear_conv_kernel_dim + qk * self.linear_key_head_dim
+                n += self.linear_num_value_heads + qk + self.linear_value_head_dim + vd * h
             elif mixer is None:
                 pass
             elif self.multi_latent_attention:
@@ -233,6 +307,8 @@ class TransformerConfig:
                 n += h * (self.kv_lora_rank + self.qk_pos_emb_head_dim) + self.kv_lora_rank
                 n += self.kv_lora_rank * self.num_attention_heads * (self.qk_head_dim + self.v_head_dim)
                 n += self.num_attention_heads * self.v_head_dim * h
+                if self.mla_use_output_gate:
+                    n += h * self.num_attention_heads * self.v_head_dim
             else:
                 n += h * self.qkv_width + self.num_attention_heads * self.kv_channels * h
                 if self.attention_output_gate:
@@ -243,8 +319,16 @@ class TransformerConfig:
                     n += 2 * self.kv_channels
             if not has_mlp:
                 continue
+            if self.hc_mult > 1:                    # two hyper-connection mixers: projection, three scales, offsets
+                K = self.hc_mult
+                n += 2 * ((2 + K) * K * (K * h + 1) + 3)
+            if self.attn_res_block_size:
+                n += 2 * h * (2 if i else 1)        # rank-1 scorers before the mixer (not in layer 0) and before the MLP
             if self.is_moe_layer(i):
-                n += h * self.num_experts + self.num_experts * 3 * h * self.moe_ffn_hidden_size
+                lat = self.routed_expert_hidden_size or h
+                n += h * self.num_experts + self.num_experts * 3 * lat * self.moe_ffn_hidden_size
+                if self.routed_expert_hidden_size:
+                    n += 2 * h * lat + (lat if self.latent_moe_use_norm else 0)
                 if self.moe_shared_expert_intermediate_size:
                     n += 3 * h * self.moe_shared_expert_intermediate_size + (h if self.moe_shared_expert_gate else 0)
             else:
@@ -311,6 +395,8 @@ def layer_kinds(cfg) -> list:
     """Per layer ``(mixer, has_mlp)``: mixer in ``"attention" | "conv" | "mamba" | None``.  A GPT-style layer is a mixer
     followed by an MLP; the layers of a Mamba / hybrid stack hold one sub-layer each."""
     L = cfg.num_layers
+    if cfg.model_type == "deepseek_v4":
+        return [("v4", True)] * L
     if cfg.model_type == "mamba":
         pat = hybrid_layer_pattern(L, cfg.hybrid_attention_ratio, cfg.hybrid_mlp_ratio, cfg.hybrid_override_pattern,
                                    hybrid=cfg.is_hybrid_model)
@@ -322,10 +408,12 @@ def layer_kinds(cfg) -> list:
         assert not bad, f"lfm_layer_types: unknown kinds {sorted(bad)}"
         return [("conv" if t == "conv" else "attention", True) for t in cfg.lfm_layer_types]
     variant = (cfg.experimental_attention_variant or "").lower()
+    if cfg.model_type == "kimi_k3":
+        variant = "kda"
     if variant and cfg.linear_attention_freq:
-        kinds = {"gated_delta_net": "gdn", "gdn": "gdn"}
+        kinds = {"gated_delta_net": "gdn", "gdn": "gdn", "kda": "kda", "kimi_delta_attention": "kda"}
         if variant not in kinds:
-            raise NotImplementedError(f"experimental_attention_variant {variant!r}: gated_delta_net is built")
+            raise NotImplementedError(f"experimental_attention_variant {variant!r}: gated_delta_net and kda are built")
         freq = cfg.linear_attention_freq
         if isinstance(freq, int):
             linear = [int((i + 1) % freq != 0) for i in range(L)]

@@ -39,7 +39,8 @@ def _param(shape, std, dtype, device, is_norm=False, seed_offset=0):
 def is_norm_gain(name: str) -> bool:
     """Is this parameter the gain of an RMSNorm that ``apply_layernorm_1p`` stores centred on zero?  (Not the gated
     norms inside the Mamba / gated-delta-net mixers, ``norm.weight`` / ``out_norm.weight``.)"""
-    return name.endswith("layer_norm_weight") or name.endswith(("layernorm.weight", "enorm.weight", "hnorm.weight"))
+    return name.endswith("layer_norm_weight") or name.endswith(("layernorm.weight", "enorm.weight", "hnorm.weight",
+                                                                "latent_norm.weight"))
 
 
 class ParamHolder(nn.Module):
@@ -234,6 +235,35 @@ class TransformerLayer(nn.Module):
             from .mixers import GatedDeltaNetMixer
 
             self.mixer = GatedDeltaNetMixer(cfg, layer_idx, device, tp)
+        elif self.mixer_kind == "kda":
+            from .kimi_k3 import KimiDeltaAttentionMixer
+
+            self.mixer = KimiDeltaAttentionMixer(cfg, layer_idx, device, tp)
+        elif self.mixer_kind == "v4":
+            from .deepseek_v4 import V4Attention
+
+            self.self_attention = V4Attention(cfg, layer_idx, device, tp)
+        # hyper-connections (DeepSeek-V4): the residual stream is ``hc_mult`` parallel streams [T, K, H]; every sub-layer
+        # reads a learned mixture of them and writes back through learned weights (models/deepseek_v4.py)
+        self.hyper = cfg.hc_mult > 1
+        if self.hyper:
+            from .deepseek_v4 import HyperMixer
+
+            assert self.mixer_kind is not None and self.has_mlp, "hyper-connections: layers of a mixer and an MLP"
+            self.attn_hc = HyperMixer(cfg.hidden_size, cfg.hc_mult, cfg.hc_eps, cfg.hc_sinkhorn_iters, device)
+            self.ffn_hc = HyperMixer(cfg.hidden_size, cfg.hc_mult, cfg.hc_eps, cfg.hc_sinkhorn_iters, device)
+        # attention residuals (Kimi-K3): the sub-layers read a learned mixture of the running stream and the checkpoints
+        # that every ``attn_res_block_size``-th layer sets aside; the checkpoints travel in the ``residual`` slot
+        self.attn_res = bool(cfg.attn_res_block_size)
+        if self.attn_res:
+            from .kimi_k3 import AttentionResidualMixer, checkpoints_before
+
+            assert self.mixer_kind is not None and self.has_mlp, "attention residuals: layers of a mixer and an MLP"
+            self.appends_checkpoint = layer_idx % cfg.attn_res_block_size == 0
+            self.checkpoints_in = checkpoints_before(layer_idx, cfg.attn_res_block_size)
+            if self.checkpoints_in:
+                self.attn_res_mixer = AttentionResidualMixer(cfg, device)
+            self.mlp_res_mixer = AttentionResidualMixer(cfg, device)
         self.is_moe = False
         if not self.has_mlp:
             return
@@ -256,11 +286,47 @@ class TransformerLayer(nn.Module):
         sp = self.cfg.sequence_parallel and ps.get_state().tp > 1
         return prandom.dropout(delta, p, True, sp)
 
+    def _forward_attn_res(self, stream, checkpoints, rope, batch):
+        """``stream`` [T, H]: the running residual sum since the last checkpoint; ``checkpoints`` [T, n, H] or None.
+        Order of the reference's layer (primus/backends/megatron/core/models/kimi_k3/kimi_k3_block.py:521-552): mix,
+        set the stream aside as a checkpoint and restart it (every ``attn_res_block_size``-th layer), mixer, mix, MLP."""
+        n_in = 0 if checkpoints is None else checkpoints.shape[1]
+        assert n_in == self.checkpoints_in, f"layer {self.layer_idx}: {n_in} checkpoints arrived, {self.checkpoints_in} expected"
+        h = self.attn_res_mixer(stream, checkpoints) if self.checkpoints_in else stream
+        if self.appends_checkpoint:
+            checkpoints = stream[:, None] if checkpoints is None else torch.cat([checkpoints, stream[:, None]], 1)
+            stream = None
+        mixer = self.mixer if self.mixer_kind in ("mamba", "gdn", "kda") else self.self_attention
+        attn_out = self._drop(mixer(h, None, rope, batch)[0])
+        stream = attn_out if stream is None else stream + attn_out
+        h = self.mlp_res_mixer(stream, checkpoints)
+        if self.is_moe:
+            mlp_out = self.mlp(fused.rmsnorm(h, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon))
+        else:
+            mlp_out = self.mlp(h, None)[0]
+        return stream + self._drop(mlp_out), checkpoints
+
+    def _forward_hyper(self, streams, rope, batch):
+        """``streams`` [T, K, H].  The sub-layers see one collapsed stream each and carry their own input norms."""
+        mixer = self.mixer if self.mixer_kind in ("mamba", "gdn", "kda") else self.self_attention
+        streams = self.attn_hc.apply(streams, lambda h: self._drop(mixer(h, None, rope, batch)[0]))
+        if self.is_moe:
+            def ffn(h):
+                return self._drop(self.mlp(fused.rmsnorm(h, self.pre_mlp_layernorm.weight, self.cfg.norm_epsilon)))
+        else:
+            def ffn(h):
+                return self._drop(self.mlp(h, None)[0])
+        return self.ffn_hc.apply(streams, ffn), None
+
     def forward(self, hidden, residual, rope, batch):
+        if self.hyper:
+            return self._forward_hyper(hidden, rope, batch)
+        if self.attn_res:
+            return self._forward_attn_res(hidden, residual, rope, batch)
         if self.mixer_kind is None:
             attn_out, res1 = hidden, residual
         else:
-            mixer = self.mixer if self.mixer_kind in ("mamba", "gdn") else self.self_attention
+            mixer = self.mixer if self.mixer_kind in ("mamba", "gdn", "kda") else self.self_attention
             attn_out, res1 = mixer(hidden, residual, rope, batch)
             attn_out = self._drop(attn_out)
         if not self.has_mlp:
@@ -305,6 +371,14 @@ class Decoder(nn.Module):
         if post_process:
             self.final_layernorm = ParamHolder(weight=_param((cfg.hidden_size,), 0, cfg.torch_dtype, device, True))
             self.final_layernorm.weight.sequence_parallel = cfg.sequence_parallel
+            if cfg.hc_mult > 1:                 # collapse of the hyper-connection streams after the last layer
+                from .deepseek_v4 import HyperHead
+
+                self.hc_head = HyperHead(cfg.hidden_size, cfg.hc_mult, cfg.hc_eps, device)
+            if cfg.attn_res_block_size:         # one more mix after the last layer collapses stream + checkpoints
+                from .kimi_k3 import AttentionResidualMixer
+
+                self.attn_res_head = AttentionResidualMixer(cfg, device)
 
 
 class MultiTokenPredictionLayer(nn.Module):
@@ -371,6 +445,18 @@ class GPTModel(nn.Module):
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
                                              for _ in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
+        if cfg.attn_res_block_size and not (pre_process and post_process):
+            raise NotImplementedError("attention residuals: the checkpoints do not cross pipeline stages yet "
+                                      "(pipeline_model_parallel_size 1)")
+        if cfg.hc_mult > 1 and not (pre_process and post_process):
+            raise NotImplementedError("hyper-connections: the parallel streams do not cross pipeline stages yet "
+                                      "(pipeline_model_parallel_size 1)")
+        if cfg.model_type == "deepseek_v4" and cfg.mtp_num_layers:
+            raise NotImplementedError("multi-token prediction is not built for the DeepSeek-V4 family: set mtp_num_layers "
+                                      "to 0")
+        if cfg.attn_res_block_size and cfg.mtp_num_layers:
+            raise NotImplementedError("attention residuals together with multi-token prediction are not built")
+        fused.set_situ_betas(cfg.activation_situ_beta, cfg.activation_situ_linear_beta)
         fused.set_zero_centered_gamma(cfg.apply_layernorm_1p)
         if cfg.apply_layernorm_1p:
             with torch.no_grad():
@@ -413,9 +499,14 @@ class GPTModel(nn.Module):
             if st.tp > 1:
                 x = tpc.reduce_scatter_seq(x, st.tp_group) if sp else tpc.all_reduce(x, st.tp_group)
             x = prandom.dropout(x, cfg.hidden_dropout, self.training, sp)     # embedding dropout
+            if cfg.hc_mult > 1:
+                x = x[:, None, :].expand(-1, cfg.hc_mult, -1).contiguous()    # every stream starts as the embedding
             hidden, residual = x, None
         else:
             hidden, residual, batch, seq = hidden_in
+        from . import moe as _moe
+
+        _moe.TOKEN_IDS.current = tokens.reshape(-1) if tokens is not None else None
         device = hidden.device
         # a context-parallel rank holds seq / cp of every sequence; a sequence chunk inside a pipeline is 1 / num_splits
         splits = layers.SEQ_SPLIT.num_splits if layers.SEQ_SPLIT.active else 1
@@ -430,6 +521,10 @@ class GPTModel(nn.Module):
                                           cfg, ckpt)
         if not self.post_process:
             return hidden, residual, batch, seq
+        if cfg.attn_res_block_size:
+            hidden, residual = self.decoder.attn_res_head(hidden, residual), None
+        if cfg.hc_mult > 1:
+            hidden = self.decoder.hc_head(hidden)
         if waiters is not None:
             waiters["head"]()
         w = self.output_weight()

@@ -76,6 +76,10 @@ class MLASelfAttention(nn.Module):
         self.linear_kv_up_proj = ParamHolder(layer_norm_weight=_param((cfg.kv_lora_rank,), 0, dt, device, True),
                                              weight=_param((nh * (self.dn + self.dv), cfg.kv_lora_rank), std, dt, device))
         self.linear_proj = ParamHolder(weight=_param((h, nh * self.dv), out_std, dt, device))
+        if cfg.mla_use_output_gate:
+            # Kimi-K3: attention output times sigmoid(gate), the gate projected from the normalised layer input
+            # (primus/backends/megatron/core/transformer/kimi_k3/kimi_k3_mla_attention.py:68-92 in the reference)
+            self.linear_o_gate = ParamHolder(weight=_param((nh * self.dv, h), std, dt, device))
         factor = cfg.rotary_scaling_factor or 1.0
         m = yarn_mscale(factor, cfg.mscale)
         self.softmax_scale = (m * m) / math.sqrt(qd)
@@ -121,8 +125,13 @@ class MLASelfAttention(nn.Module):
                                cfg.norm_epsilon)
         k_pe = c[:, cfg.kv_lora_rank:].reshape(T, 1, dr)
         kv = gemm.linear(latent, self.linear_kv_up_proj.weight).view(T, nh, dn + dv)
-        q_pe = fused.rope(q[..., dn:].contiguous(), cos, sin, pos, dr)
-        k_pe = fused.rope(k_pe.contiguous(), cos, sin, pos, dr)
+        if cfg.mla_use_nope:
+            # no rotation: the dr "rope" dims of q and the shared key dims are ordinary learned features; the head
+            # geometry and the softmax scale stay those of the rotary layout (kimi_k3_mla_attention.py:24-60)
+            q_pe = q[..., dn:]
+        else:
+            q_pe = fused.rope(q[..., dn:].contiguous(), cos, sin, pos, dr)
+            k_pe = fused.rope(k_pe.contiguous(), cos, sin, pos, dr)
         q_full = torch.cat([q_pe, q[..., :dn]], dim=-1)
         k_full = torch.cat([k_pe.expand(T, nh, dr), kv[..., :dn]], dim=-1)
         v = kv[..., dn:].contiguous()
@@ -139,5 +148,9 @@ class MLASelfAttention(nn.Module):
                                                         st.cp, True, self.softmax_scale)
         else:
             ctx_out = attention.flash_attention(q_full, k_full, v, batch, True, self.softmax_scale)
-        out = gemm.linear(ctx_out.reshape(T, nh * dv), self.linear_proj.weight)
+        ctx_out = ctx_out.reshape(T, nh * dv)
+        if cfg.mla_use_output_gate:
+            gate = gemm.linear(y, self.linear_o_gate.weight)
+            ctx_out = (ctx_out * torch.sigmoid(gate.float()).to(ctx_out.dtype)).contiguous()
+        out = gemm.linear(ctx_out, self.linear_proj.weight)
         return out, xsum

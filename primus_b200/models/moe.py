@@ -35,6 +35,15 @@ class AuxLossScaler(torch.autograd.Function):
         return g, torch.ones_like(aux) * AuxLossScaler.scale
 
 
+class _TokenIds:
+    """Token ids of the micro-batch in flight ([batch * seq], set by the model's forward pass): hash-routed layers
+    index their expert table with them."""
+    current = None
+
+
+TOKEN_IDS = _TokenIds()
+
+
 class MoELayer(nn.Module):
     def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
         super().__init__()
@@ -51,6 +60,12 @@ class MoELayer(nn.Module):
         st = ps.get_state()
         self.ep, self.ep_rank = st.ep, st.ep_rank
         E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_ffn_hidden_size
+        # latent mixture of experts (Kimi-K3): one down- and one up-projection shared by all experts of the layer put
+        # the routed experts in a narrower space; the router and the shared experts read the full-width input, and the
+        # combined expert output is normalised before it is lifted back
+        # (primus/backends/megatron/core/transformer/kimi_k3/moe/k3_stable_latent_moe.py:14-45 in the reference)
+        self.latent = int(cfg.routed_expert_hidden_size or 0)
+        Hx = self.latent or H
         assert E % self.ep == 0
         self.e_local = E // self.ep
         dt = cfg.torch_dtype
@@ -66,8 +81,8 @@ class MoELayer(nn.Module):
         # initial weights do not depend on the EP size
         g = torch.Generator(device="cpu").manual_seed(977 + 31 * layer_idx)
         lo, hi = self.ep_rank * self.e_local, (self.ep_rank + 1) * self.e_local
-        w1 = torch.empty(E, 2 * I, H).normal_(0.0, std, generator=g)[lo:hi].to(dt).to(device)
-        w2 = torch.empty(E, H, I).normal_(0.0, out_std, generator=g)[lo:hi].to(dt).to(device)
+        w1 = torch.empty(E, 2 * I, Hx).normal_(0.0, std, generator=g)[lo:hi].to(dt).to(device)
+        w2 = torch.empty(E, Hx, I).normal_(0.0, out_std, generator=g)[lo:hi].to(dt).to(device)
         self.experts = nn.Module()
         self.experts.fc1_weight = ParamHolder(weight=nn.Parameter(w1.contiguous()))
         self.experts.fc2_weight = ParamHolder(weight=nn.Parameter(w2.contiguous()))
@@ -76,6 +91,24 @@ class MoELayer(nn.Module):
             p.expert_parallel = self.ep > 1
             # without expert parallelism the experts are replicas that see one sequence shard each
             p.sequence_parallel = tp > 1 and self.ep == 1
+        if self.latent:
+            self.fc1_latent_proj = ParamHolder(weight=_param((Hx, H), std, dt, device))
+            self.fc2_latent_proj = ParamHolder(weight=_param((H, Hx), out_std, dt, device))
+            if cfg.latent_moe_use_norm:
+                self.latent_norm = ParamHolder(weight=_param((Hx,), 0, dt, device, True))
+        if cfg.moe_router_enable_expert_bias and cfg.moe_router_bias_update_rule == "quantile":
+            # quantile balancing (models/kimi_k3.py): histograms of this rank's routing margins since the last update
+            self.router.register_buffer("local_margin_histogram", torch.zeros(
+                E, cfg.quantile_balancing_num_bins, dtype=torch.int64, device=device), persistent=False)
+            self._qb_steps = 0
+        # DeepSeek-V4: the first ``num_hash_layers`` MoE layers take their experts from a fixed table indexed by the token
+        # id (the weights still come from the learned gate); the table travels with the checkpoint
+        moe_rank = sum(cfg.moe_layer_pattern[:layer_idx])
+        if cfg.num_hash_layers and moe_rank < cfg.num_hash_layers:
+            from .deepseek_v4 import hash_table
+
+            self.router.register_buffer("tid2eid", hash_table(
+                cfg.padded_vocab_size, E, cfg.moe_router_topk, cfg.hash_router_seed + layer_idx).to(device))
         if cfg.moe_shared_expert_intermediate_size:
             self.shared_experts = MLP(cfg, device, 1, ffn=cfg.moe_shared_expert_intermediate_size, with_norm=False)
             if cfg.moe_shared_expert_gate:      # Qwen MoE: the shared expert's output is scaled by sigmoid(y . gate)
@@ -83,6 +116,9 @@ class MoELayer(nn.Module):
         if tp > 1:
             replicated = [self.router.weight] + ([p for p in self.shared_experts.parameters()]
                                                  if hasattr(self, "shared_experts") else [])
+            for name in ("fc1_latent_proj", "fc2_latent_proj", "latent_norm"):
+                if hasattr(self, name):
+                    replicated.append(getattr(self, name).weight)
             for p in replicated:
                 p.sequence_parallel = True
                 if torch.distributed.is_initialized():      # drawn from per-rank streams: make the replicas equal
@@ -95,10 +131,16 @@ class MoELayer(nn.Module):
         cfg = self.cfg
         logits = fused.softcap(gemm.linear(y, self.router.weight), cfg.router_logit_softcapping)
         bias = getattr(self.router, "expert_bias", None)
+        fixed = None
+        if hasattr(self.router, "tid2eid"):
+            if TOKEN_IDS.current is None or TOKEN_IDS.current.numel() != y.shape[0]:
+                raise RuntimeError("hash-routed MoE layer: the token ids of the micro-batch are not available "
+                                   "(pipeline stages after the first and sequence-parallel shards do not have them)")
+            fixed = self.router.tid2eid[TOKEN_IDS.current.long()]
         probs, idx, full, counts = moe_ops.router_scores(
             logits, cfg.moe_router_topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, bias,
             cfg.moe_router_topk_scaling_factor, cfg.moe_router_num_groups, cfg.moe_router_group_topk,
-            return_counts=True)
+            return_counts=True, fixed_idx=fixed)
         if cfg.moe_router_force_load_balancing:
             T = y.shape[0]
             k = cfg.moe_router_topk
@@ -107,6 +149,12 @@ class MoELayer(nn.Module):
             counts = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(torch.int32)
         if bias is not None and torch.is_grad_enabled():
             self.router.local_tokens_per_expert += counts.float()
+            if hasattr(self.router, "local_margin_histogram") and self.training:
+                from .kimi_k3 import margin_histogram
+
+                self.router.local_margin_histogram += margin_histogram(
+                    full.detach(), bias, cfg.moe_router_topk, cfg.quantile_balancing_num_bins,
+                    cfg.quantile_balancing_margin_min, cfg.quantile_balancing_margin_max)
         aux = None
         if cfg.moe_aux_loss_coeff and cfg.moe_router_load_balancing_type in ("aux_loss", "seq_aux_loss") \
                 and torch.is_grad_enabled():
@@ -125,6 +173,8 @@ class MoELayer(nn.Module):
         (``groups``: the process groups whose ranks saw different tokens).  The reference takes this from Megatron's
         router (``moe_router_enable_expert_bias`` / ``moe_router_bias_update_rate`` in its DeepSeek-V3 presets)."""
         r = self.router
+        if hasattr(r, "local_margin_histogram"):
+            return self._update_expert_bias_quantile(groups)
         if not hasattr(r, "expert_bias") or not self.cfg.moe_router_bias_update_rate:
             return
         load = r.local_tokens_per_expert.clone()
@@ -132,6 +182,31 @@ class MoELayer(nn.Module):
             if g is not None and torch.distributed.get_world_size(g) > 1:
                 torch.distributed.all_reduce(load, group=g)
         r.expert_bias += self.cfg.moe_router_bias_update_rate * torch.sign(load.mean() - load)
+        r.local_tokens_per_expert.zero_()
+
+    @torch.no_grad()
+    def _update_expert_bias_quantile(self, groups=()) -> None:
+        """Quantile balancing: the bias is *set* to minus the ``1 - k/E`` quantile of every expert's routing margins over
+        the global batch (histograms summed over micro-batches and, by one all-reduce per group, over ranks), mean
+        removed; ``quantile_balancing_update_interval`` widens the window and ``quantile_balancing_ema_decay`` blends
+        the new value into the old one.  The reference's replacement for the sign rule
+        (primus/backends/megatron/core/transformer/kimi_k3/moe/k3_quantile_balancing.py:14-60,232-250)."""
+        from .kimi_k3 import quantile_bias
+
+        cfg, r = self.cfg, self.router
+        self._qb_steps += 1
+        if self._qb_steps % max(int(cfg.quantile_balancing_update_interval), 1):
+            return
+        hist = r.local_margin_histogram.clone()
+        for g in groups:
+            if g is not None and torch.distributed.get_world_size(g) > 1:
+                torch.distributed.all_reduce(hist, group=g)
+        if int(hist.sum()) > 0:
+            new = quantile_bias(hist, cfg.moe_router_topk, cfg.quantile_balancing_margin_min,
+                                cfg.quantile_balancing_margin_max, cfg.quantile_balancing_center_bias).to(r.expert_bias)
+            d = cfg.quantile_balancing_ema_decay
+            r.expert_bias.copy_(new if not d else d * r.expert_bias + (1.0 - d) * new)
+        r.local_margin_histogram.zero_()
         r.local_tokens_per_expert.zero_()
 
     def experts_forward(self, x_perm, probs_perm, sched):
@@ -147,12 +222,17 @@ class MoELayer(nn.Module):
         probs, idx, counts_global = self.route(y)
         flat_e = idx.reshape(-1)
         self.last_tokens_per_expert = counts_global
+        x = gemm.linear(y, self.fc1_latent_proj.weight) if self.latent else y
         if cfg.use_turbo_mega_moe and y.is_cuda:
-            out = self._forward_fused(y, probs, idx, T, k)
+            out = self._forward_fused(x, probs, idx, T, k)
         elif self.ep == 1:
-            out = self._forward_local(y, probs, flat_e, counts_global, T, k)
+            out = self._forward_local(x, probs, flat_e, counts_global, T, k)
         else:
-            out = self._forward_ep(y, probs, flat_e, counts_global, T, k)
+            out = self._forward_ep(x, probs, flat_e, counts_global, T, k)
+        if self.latent:
+            if hasattr(self, "latent_norm"):
+                out = fused.rmsnorm(out, self.latent_norm.weight, cfg.norm_epsilon)
+            out = gemm.linear(out, self.fc2_latent_proj.weight)
         if hasattr(self, "shared_experts"):
             shared = self.shared_experts.forward_normed(y)
             if cfg.moe_shared_expert_gate:
@@ -181,7 +261,7 @@ class MoELayer(nn.Module):
 
         cfg = self.cfg
         st = ps.get_state()
-        ws = fused_ep.get_workspace(st.ep_group if self.ep > 1 else None, T, k, cfg.num_experts, cfg.hidden_size,
+        ws = fused_ep.get_workspace(st.ep_group if self.ep > 1 else None, T, k, cfg.num_experts, y.shape[1],
                                     cfg.moe_fused_capacity_factor)
         plan = ws.plan(idx, probs)
         h1, probs_perm = fused_ep.dispatch_gemm1(y, probs, self.experts.fc1_weight.weight, ws, plan)

@@ -211,12 +211,26 @@ def rope(x, cos, sin, pos=None, rot_dim=None):
 
 # ----------------------------------------------------------------------------------------------
 # SwiGLU: in [T, 2I] = [gate | up]
-GATE_KINDS = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1}
+GATE_KINDS = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1, "situ": 2}
+# "situ" (Kimi-K3): SiLU whose linear factor is soft-clamped, times a soft-clamped up branch,
+# ``beta tanh(g / beta) sigmoid(g) * linear_beta tanh(u / linear_beta)``; runs as composed fp32 operations on every
+# device (primus/backends/megatron/core/transformer/kimi_k3/situ_activation.py:8-24 in the reference).
+SITU_BETAS = [4.0, 25.0]
+
+
+def set_situ_betas(beta: float, linear_beta) -> None:
+    SITU_BETAS[0], SITU_BETAS[1] = float(beta), (float(linear_beta) if linear_beta else 0.0)
 
 
 def swiglu_ref(x, probs=None, clamp=0.0, act="silu"):
     I = x.shape[-1] // 2
     g, u = x[..., :I].float(), x[..., I:].float()
+    if GATE_KINDS[act] == 2:
+        b, lb = SITU_BETAS
+        y = b * torch.tanh(g / b) * torch.sigmoid(g) * (lb * torch.tanh(u / lb) if lb else u)
+        if probs is not None:
+            y = y * probs.float().reshape(*y.shape[:-1], 1)
+        return y.to(x.dtype)
     if clamp and clamp > 0:
         g = g.clamp(max=clamp)
         u = u.clamp(-clamp, clamp)
@@ -263,7 +277,7 @@ def swiglu(x, probs=None, clamp=0.0, act="silu"):
     """Gated linear unit ``act(gate) * up [* probs]`` for x = [gate | up]; ``act``: "silu" (SwiGLU) or "gelu" (GEGLU,
     tanh approximation) -- the reference's swiglu_with_probs / geglu_with_probs
     (primus/backends/megatron/core/extensions/primus_turbo.py:1954-1980)."""
-    if not x.is_cuda:
+    if not x.is_cuda or GATE_KINDS[act] == 2:
         return swiglu_ref(x, probs, clamp, act)
     return SwiGLUFn.apply(x, probs, clamp, act)
 

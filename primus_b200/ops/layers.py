@@ -254,6 +254,8 @@ def swiglu_linear(h1, weight, probs=None, clamp=0.0, tp_group=None, sequence_par
     row-parallel shard: the partial outputs are reduce-scattered over tokens (sequence parallel) or
     all-reduced over ``tp_group``."""
     sp = bool(sequence_parallel and tp_group is not None)
+    if h1.is_cuda and fused.GATE_KINDS[act] == 2:      # no fused kernel for this gate: composed activation, then the GEMM
+        return row_parallel_linear(fused.swiglu_ref(h1, probs, clamp, act), weight, tp_group, sp)
     if not h1.is_cuda:
         out = gemm.linear(fused.swiglu_ref(h1, probs, clamp, act), weight)
         if sp:

@@ -64,17 +64,20 @@ class RouterFn(torch.autograd.Function):
 
 def router_scores(logits: torch.Tensor, topk: int, score_function: str = "softmax", pre_softmax: bool = False,
                   expert_bias: Optional[torch.Tensor] = None, scaling_factor: Optional[float] = None,
-                  num_groups: Optional[int] = None, group_topk: Optional[int] = None, return_counts: bool = False):
+                  num_groups: Optional[int] = None, group_topk: Optional[int] = None, return_counts: bool = False,
+                  fixed_idx: Optional[torch.Tensor] = None):
     """Returns (probs [T, k] fp32, idx [T, k] int64, full scores [T, E] fp32 used by the aux losses) and, with
-    ``return_counts``, the per-expert token counts (int32 [E])."""
-    if score_function not in ("softmax", "sigmoid"):
+    ``return_counts``, the per-expert token counts (int32 [E]).  ``score_function`` "sqrtsoftplus" (DeepSeek-V4:
+    ``sqrt(softplus(logit))``, handled like sigmoid scores) and ``fixed_idx`` (hash routing: the experts are given, only
+    the weights come from the scores) run as composed PyTorch operations on every device."""
+    if score_function not in ("softmax", "sigmoid", "sqrtsoftplus"):
         raise ValueError(f"unknown moe_router_score_function {score_function!r}")
-    if logits.is_cuda and logits.shape[1] <= 1024 and topk <= 32:
+    if logits.is_cuda and logits.shape[1] <= 1024 and topk <= 32 and fixed_idx is None and score_function != "sqrtsoftplus":
         probs, idx, full, counts = RouterFn.apply(logits, expert_bias, topk, score_function == "sigmoid", pre_softmax,
                                                   num_groups, group_topk, scaling_factor or 1.0)
         return (probs, idx, full, counts) if return_counts else (probs, idx, full)
     out = router_scores_ref(logits, topk, score_function, pre_softmax, expert_bias, scaling_factor, num_groups,
-                            group_topk)
+                            group_topk, fixed_idx)
     if return_counts:
         return (*out, torch.bincount(out[1].reshape(-1), minlength=logits.shape[1]).to(torch.int32))
     return out
@@ -82,12 +85,15 @@ def router_scores(logits: torch.Tensor, topk: int, score_function: str = "softma
 
 def router_scores_ref(logits: torch.Tensor, topk: int, score_function: str = "softmax", pre_softmax: bool = False,
                       expert_bias: Optional[torch.Tensor] = None, scaling_factor: Optional[float] = None,
-                      num_groups: Optional[int] = None, group_topk: Optional[int] = None):
+                      num_groups: Optional[int] = None, group_topk: Optional[int] = None,
+                      fixed_idx: Optional[torch.Tensor] = None):
     """Plain PyTorch router (CPU path and numerics oracle of the fused kernel)."""
     lf = logits.float()
     T, E = lf.shape
 
     def select(scores_for_choice):
+        if fixed_idx is not None:
+            return fixed_idx.long()
         if num_groups and group_topk and num_groups > 1:
             g = scores_for_choice.view(T, num_groups, E // num_groups)
             gscore = g.topk(min(2, E // num_groups), dim=-1).values.sum(-1) if expert_bias is not None \
@@ -107,8 +113,8 @@ def router_scores_ref(logits: torch.Tensor, topk: int, score_function: str = "so
             full = torch.softmax(lf, dim=-1)
             idx = select(lf)
             probs = torch.softmax(lf.gather(1, idx), dim=-1)
-    elif score_function == "sigmoid":
-        full = torch.sigmoid(lf)
+    elif score_function in ("sigmoid", "sqrtsoftplus"):
+        full = torch.sigmoid(lf) if score_function == "sigmoid" else torch.sqrt(torch.nn.functional.softplus(lf))
         choice = full + expert_bias.float()[None, :] if expert_bias is not None else full
         idx = select(choice)
         probs = full.gather(1, idx)

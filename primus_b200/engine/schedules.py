@@ -119,6 +119,24 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
             c, nv, dk, dv = cfg.linear_chunk_size, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
             fwd += nv * (4 * c * dk + 2 * c * c + 2 * c * (dv + dk) + 6 * dk * dv)      # scores, solve, deltas, state
             attn = 0.0
+        elif mixer == "v4":            # DeepSeek-V4: low-rank q, one shared latent, grouped low-rank output, compressed branches
+            nh, hd = cfg.num_attention_heads, cfg.kv_channels
+            fwd += (2 * h * cfg.q_lora_rank + 2 * cfg.q_lora_rank * nh * hd) if cfg.q_lora_rank else 2 * h * nh * hd
+            fwd += 2 * h * hd
+            fwd += (2 * nh * hd * cfg.o_lora_rank + 2 * cfg.o_groups * cfg.o_lora_rank * h) if cfg.o_lora_rank \
+                else 2 * nh * hd * h
+            ratio = cfg.compress_ratio_list[i]
+            keys = min(cfg.attn_sliding_window or seq_len, seq_len)       # local keys per query
+            if ratio == 128:
+                fwd += 4 * h * hd
+                keys += seq_len / ratio * (0.5 if causal_half else 1.0)
+            elif ratio == 4:
+                fwd += 8 * h * hd + 2 * h * (cfg.index_head_dim + cfg.index_n_heads) \
+                    + 2 * cfg.index_n_heads * cfg.index_head_dim ** 2 + 8 * h * cfg.index_head_dim
+                fwd += 2 * cfg.index_n_heads * cfg.index_head_dim * seq_len / ratio * (0.5 if causal_half else 1.0)
+                keys += min(cfg.index_topk, seq_len // ratio)
+            fwd += 4 * nh * hd * keys
+            attn = 0.0
         elif mixer == "kda":           # Kimi delta attention: projections, gate bottleneck, convolution, chunked rule
             nh, dk, dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
             qk, vd = nh * dk, nh * dv
@@ -148,6 +166,9 @@ def model_flops_per_token(cfg, seq_len: int, causal_half: bool = False) -> float
                 fwd += 2 * h * cfg.num_attention_heads * cfg.kv_channels
             attn = 4 * seq_len * cfg.num_attention_heads * cfg.kv_channels
         fwd += attn * (0.5 if causal_half else 1.0)
+        if getattr(cfg, "hc_mult", 1) > 1:          # two hyper-connection mixers: the projection of the flattened streams
+            K = cfg.hc_mult
+            fwd += 2 * 2 * K * h * (2 + K) * K + 2 * 4 * K * K * h
         if not has_mlp:
             continue
         if cfg.is_moe_layer(i):

@@ -277,7 +277,11 @@ class TransformerConfig:
                 n += 2 * self.linear_num_value_heads + self.linear_value_head_dim + vd * h
             elif mixer == "v4":
                 nh, hd = self.num_attention_heads, self.kv_channels
-                n += h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * hd + h * hd + hd
+                if self.q_lora_rank:
+                    n += h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * hd
+                else:
+                    n += h * nh * hd
+                n += h * hd + hd
                 n += nh if self.attn_sink else 0
                 n += (nh * hd * self.o_lora_rank + h * self.o_groups * self.o_lora_rank) if self.o_lora_rank else nh * hd * h
                 ratio = self.compress_ratio_list[i]
@@ -293,8 +297,10 @@ class TransformerConfig:
             elif mixer == "kda":
                 qk, vd = self.linear_num_value_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
                 conv_dim = 2 * qk + vd
-                n += h * (conv_dim + vd + self.linear_key_head_dim + self.linear_num_value_heads)
-                n += conv_dim * self.linear_conv_kernel_dim + qk * self.linear_key_head_dim
+                full = self.kda_use_full_rank_gate
+                fa = self.linear_key_head_dim if full else self.linear_value_head_dim
+                n += h * (conv_dim + (vd if full else self.linear_value_head_dim) + fa + self.linear_num_value_heads)
+                n += conv_dim * self.linear_conv_kernel_dim + qk * fa + (0 if full else vd * self.linear_value_head_dim)
                 n += self.linear_num_value_heads + qk + self.linear_value_head_dim + vd * h
             elif mixer is None:
                 pass
@@ -400,7 +406,8 @@ def layer_kinds(cfg) -> list:
     if cfg.model_type == "mamba":
         pat = hybrid_layer_pattern(L, cfg.hybrid_attention_ratio, cfg.hybrid_mlp_ratio, cfg.hybrid_override_pattern,
                                    hybrid=cfg.is_hybrid_model)
-        m_kind = "gdn" if (cfg.linear_attention_type or "").lower() in ("gdn", "gated_delta_net") else "mamba"
+        lat = (cfg.linear_attention_type or "").lower()
+        m_kind = "gdn" if lat in ("gdn", "gated_delta_net") else ("kda" if lat in ("kda", "kimi_delta_attention") else "mamba")
         return [{"M": (m_kind, False), "*": ("attention", False), "-": (None, True)}[c] for c in pat]
     if cfg.lfm_layer_types:
         assert len(cfg.lfm_layer_types) == L, f"lfm_layer_types has {len(cfg.lfm_layer_types)} entries for {L} layers"

@@ -279,9 +279,12 @@ class V4Attention(nn.Module):
 
         ones = lambda n: nn.Parameter(torch.ones(n, dtype=dt, device=device))      # noqa: E731
         self.input_layernorm = holder(weight=ones(h))
-        self.linear_q_down_proj = holder(weight=_param((cfg.q_lora_rank, h), std, dt, device))
-        self.linear_q_up_proj = holder(layer_norm_weight=ones(cfg.q_lora_rank),
-                                       weight=_param((self.nh * self.hd, cfg.q_lora_rank), std, dt, device))
+        if cfg.q_lora_rank:
+            self.linear_q_down_proj = holder(weight=_param((cfg.q_lora_rank, h), std, dt, device))
+            self.linear_q_up_proj = holder(layer_norm_weight=ones(cfg.q_lora_rank),
+                                           weight=_param((self.nh * self.hd, cfg.q_lora_rank), std, dt, device))
+        else:
+            self.linear_q_proj = holder(weight=_param((self.nh * self.hd, h), std, dt, device))
         self.linear_kv = holder(weight=_param((self.hd, h), std, dt, device))
         self.kv_layernorm = holder(weight=ones(self.hd))
         if cfg.attn_sink:
@@ -304,8 +307,7 @@ class V4Attention(nn.Module):
         self.register_buffer("inv_freq", inv, persistent=False)
         if self.ratio == 4:
             self.indexer = Indexer(cfg, self.ratio, inv, self.dr, device)
-        for w in (self.linear_q_down_proj.weight, self.linear_q_up_proj.weight, self.linear_kv.weight):
-            w._is_weight = True
+        self.linear_kv.weight._is_weight = True
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
@@ -319,9 +321,13 @@ class V4Attention(nn.Module):
         nh, hd, dr = self.nh, self.hd, self.dr
         pos = rope[2]
         pos = (torch.arange(S, device=y.device).repeat(batch) if pos is None else pos.long()).view(batch, S)
-        ql = fused.rmsnorm(gemm.linear(y, self.linear_q_down_proj.weight), self.linear_q_up_proj.layer_norm_weight,
-                           cfg.norm_epsilon)
-        q = gemm.linear(ql, self.linear_q_up_proj.weight).view(batch, S, nh, hd).float()
+        if cfg.q_lora_rank:
+            ql = fused.rmsnorm(gemm.linear(y, self.linear_q_down_proj.weight), self.linear_q_up_proj.layer_norm_weight,
+                               cfg.norm_epsilon)
+            q = gemm.linear(ql, self.linear_q_up_proj.weight)
+        else:
+            q = gemm.linear(y, self.linear_q_proj.weight)
+        q = q.view(batch, S, nh, hd).float()
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon)            # per head, no gain
         kv = fused.rmsnorm(gemm.linear(y, self.linear_kv.weight), self.kv_layernorm.weight, cfg.norm_epsilon)
         q = rope_interleaved(q, pos, self.inv_freq, dr)

@@ -445,12 +445,6 @@ class GPTModel(nn.Module):
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
                                              for _ in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
-        if cfg.attn_res_block_size and not (pre_process and post_process):
-            raise NotImplementedError("attention residuals: the checkpoints do not cross pipeline stages yet "
-                                      "(pipeline_model_parallel_size 1)")
-        if cfg.hc_mult > 1 and not (pre_process and post_process):
-            raise NotImplementedError("hyper-connections: the parallel streams do not cross pipeline stages yet "
-                                      "(pipeline_model_parallel_size 1)")
         if cfg.model_type == "deepseek_v4" and cfg.mtp_num_layers:
             raise NotImplementedError("multi-token prediction is not built for the DeepSeek-V4 family: set mtp_num_layers "
                                       "to 0")
@@ -463,6 +457,34 @@ class GPTModel(nn.Module):
                 for name, p in self.named_parameters():
                     if is_norm_gain(name):
                         p.zero_()
+
+    # ------------------------------------------------------------------ pipeline hand-off
+    # One tensor crosses a stage boundary.  Plain stacks send the residual stream ``hidden + residual`` [T, H];
+    # hyper-connections send the K streams [T, K, H]; attention residuals send the running stream together with the
+    # checkpoints set aside so far [T, 1 + n, H] -- n depends only on the index of the stage's first layer (the
+    # reference folds the same extra axes into the sequence axis at stage boundaries:
+    # primus/backends/megatron/core/models/deepseek_v4/deepseek_v4_block.py:341-432,
+    # models/kimi_k3/kimi_k3_block.py:23-60).
+    def handoff_shape(self, tokens: int) -> tuple:
+        """Shape of the tensor this stage receives for ``tokens`` local tokens."""
+        cfg = self.cfg
+        if cfg.hc_mult > 1:
+            return (tokens, cfg.hc_mult, cfg.hidden_size)
+        if cfg.attn_res_block_size:
+            from .kimi_k3 import checkpoints_before
+
+            return (tokens, 1 + checkpoints_before(self.decoder.layer_indices[0], cfg.attn_res_block_size), cfg.hidden_size)
+        return (tokens, cfg.hidden_size)
+
+    def pack_handoff(self, hidden, residual):
+        if self.cfg.attn_res_block_size:
+            return hidden[:, None] if residual is None else torch.cat([hidden[:, None], residual], 1)
+        return hidden if residual is None else hidden + residual
+
+    def unpack_handoff(self, x):
+        if self.cfg.attn_res_block_size:
+            return x[:, 0].contiguous(), (x[:, 1:].contiguous() if x.shape[1] > 1 else None)
+        return x, None
 
     # ------------------------------------------------------------------ helpers
     def rope_tables(self, device, seq: int):
@@ -504,9 +526,12 @@ class GPTModel(nn.Module):
             hidden, residual = x, None
         else:
             hidden, residual, batch, seq = hidden_in
-        from . import moe as _moe
+            if residual is None:
+                hidden, residual = self.unpack_handoff(hidden)
+        if tokens is not None:      # later pipeline stages get the ids from the schedule runner
+            from . import moe as _moe
 
-        _moe.TOKEN_IDS.current = tokens.reshape(-1) if tokens is not None else None
+            _moe.TOKEN_IDS.current = tokens.reshape(-1)
         device = hidden.device
         # a context-parallel rank holds seq / cp of every sequence; a sequence chunk inside a pipeline is 1 / num_splits
         splits = layers.SEQ_SPLIT.num_splits if layers.SEQ_SPLIT.active else 1

@@ -146,11 +146,20 @@ class KimiDeltaAttentionMixer(nn.Module):
         std = cfg.init_method_std
         self.in_proj = nn.Module()
         self.in_proj.register_parameter("layer_norm_weight", nn.Parameter(torch.ones(h, dtype=dt, device=device)))
-        self.in_proj.register_parameter("weight", _param((self.conv_dim + self.v_dim + self.dk + self.nh, h), std, dt, device))
+        # the output gate is a full projection (Kimi-K3) or goes through a ``dv``-wide bottleneck ``g_b(g_a(h))`` like the
+        # forget gate (Kimi Linear, the delta-attention stacks of the hybrid presets:
+        # primus/backends/megatron/core/models/hybrid/kimi_delta_attention.py:278-311,397-410 in the reference)
+        self.full_gate = bool(cfg.kda_use_full_rank_gate)
+        self.gate_in = self.v_dim if self.full_gate else self.dv
+        self.fa = self.dk if self.full_gate else self.dv
+        self.in_proj.register_parameter("weight", _param((self.conv_dim + self.gate_in + self.fa + self.nh, h), std, dt, device))
         self.conv1d = nn.Module()
         self.conv1d.register_parameter("weight", _param((self.conv_dim, 1, cfg.linear_conv_kernel_dim), std * 5, dt, device))
         self.f_b_proj = nn.Module()
-        self.f_b_proj.register_parameter("weight", _param((self.qk_dim, self.dk), std, dt, device))
+        self.f_b_proj.register_parameter("weight", _param((self.qk_dim, self.fa), std, dt, device))
+        if not self.full_gate:
+            self.g_b_proj = nn.Module()
+            self.g_b_proj.register_parameter("weight", _param((self.v_dim, self.dv), std, dt, device))
         # exp(A_log) = 1 at the start; the bias puts the initial retention near one (dt ~ logU(1e-3, 1e-1), bias =
         # softplus^-1(dt)), the initialisation the reference settles on (kimi_delta_attention.py:579-602)
         self.A_log = nn.Parameter(torch.zeros(self.nh, dtype=torch.float32, device=device))
@@ -173,9 +182,12 @@ class KimiDeltaAttentionMixer(nn.Module):
         seq = T // batch
         cd, vd, nh, dk = self.conv_dim, self.v_dim, self.nh, self.dk
         qkv = F.silu(causal_depthwise_conv(proj[:, :cd], self.conv1d.weight[:, 0, :], None, batch))
-        gate = proj[:, cd:cd + vd]
-        f_a = proj[:, cd + vd:cd + vd + dk].contiguous()
-        b_ = proj[:, cd + vd + dk:]
+        gi, fa = self.gate_in, self.fa
+        gate = proj[:, cd:cd + gi]
+        if not self.full_gate:
+            gate = gemm.linear(gate.contiguous(), self.g_b_proj.weight)
+        f_a = proj[:, cd + gi:cd + gi + fa].contiguous()
+        b_ = proj[:, cd + gi + fa:]
         q = F.normalize(qkv[:, :self.qk_dim].float().view(batch, seq, nh, dk), dim=-1, eps=1e-6)
         k = F.normalize(qkv[:, self.qk_dim:2 * self.qk_dim].float().view(batch, seq, nh, dk), dim=-1, eps=1e-6)
         v = qkv[:, 2 * self.qk_dim:].view(batch, seq, nh, self.dv)

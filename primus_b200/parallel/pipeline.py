@@ -52,11 +52,14 @@ class PipelineTimeline:
             json.dump({"pp_rank": pp_rank, "iteration": iteration, "events": self.events, **(extra or {})}, f)
 
 
-def _p2p_shape(trainer, batch, seq):
+def _p2p_shape(trainer, batch, seq, model=None):
+    """Shape of the tensor the stage held by ``model`` receives (models/gpt.py::handoff_shape)."""
     st = trainer.st
     T = batch * seq
     if trainer.mcfg.sequence_parallel and st.tp > 1:
         T //= st.tp
+    if model is not None and hasattr(model, "handoff_shape"):
+        return model.handoff_shape(T)
     return (T, trainer.mcfg.hidden_size)
 
 
@@ -117,6 +120,10 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 layers_ops.SEQ_SPLIT.begin((node.mb, node.chunk), node.split, nsplit, forward_only)
         batch, seq = mb["tokens"].shape
         model = trainer.model_chunks[node.chunk]
+        if trainer.mcfg.num_hash_layers:    # hash-routed MoE layers index their table with the ids of *this* micro-batch
+            from ..models import moe as _moe    # (also when a checkpointed layer runs again inside a backward node)
+
+            _moe.TOKEN_IDS.current = mb["tokens"].reshape(-1)
         k = (node.mb, node.chunk) if nsplit == 1 else (node.mb, node.chunk, node.split)
         if node.kind == "F":
             if s == 0:
@@ -126,7 +133,7 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                 if pr == r:
                     x = local_act.pop((node.mb, pc))
                 else:
-                    x = torch.empty(_p2p_shape(trainer, batch, seq), dtype=dtype, device=dev)
+                    x = torch.empty(_p2p_shape(trainer, batch, seq, model), dtype=dtype, device=dev)
                     dist.recv(x, src=global_rank(pr), group=fwd_g)
                     if timeline is not None:
                         if trainer.is_cuda:
@@ -149,7 +156,7 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
                                      position_ids=_pos_ids(trainer, mb), cu_seqlens=mb.get("host_cu_seqlens"))
                 # one tensor per stage boundary: the next stage's first layer only needs the residual stream
                 # hidden + residual (its fused add + norm starts from the sum), half the bytes of sending both
-                y = h if res is None else h + res
+                y = model.pack_handoff(h, res) if hasattr(model, "pack_handoff") else (h if res is None else h + res)
                 if not forward_only:
                     outputs[k] = y
                 nr, nc = sched.rank_of_stage(s + 1, pp, placement)
@@ -282,7 +289,7 @@ def pipeline_warmup(trainer, micro_batch: dict) -> None:
             s = sched.stage_of(st.pp_rank, c, pp, placement)
             hidden_in = None
             if s > 0:
-                x = torch.randn(_p2p_shape(trainer, batch, seq), device=dev).to(dtype) * 0.02
+                x = torch.randn(_p2p_shape(trainer, batch, seq, model), device=dev).to(dtype) * 0.02
                 x.requires_grad_(True)
                 hidden_in = (x, None, batch, seq)
             if s == S - 1:
@@ -293,7 +300,7 @@ def pipeline_warmup(trainer, micro_batch: dict) -> None:
             else:
                 h, res, _, _ = model(micro_batch["tokens"] if s == 0 else None, hidden_in=hidden_in,
                                      position_ids=_pos_ids(trainer, micro_batch))
-                y = h if res is None else h + res
+                y = model.pack_handoff(h, res) if hasattr(model, "pack_handoff") else (h if res is None else h + res)
                 torch.autograd.backward(y, torch.randn_like(y) * 1e-3)
         gemm_ops.WGRAD_STORE.flush_all()
     finally:

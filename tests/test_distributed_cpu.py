@@ -86,6 +86,20 @@ CASES = {
     "tp2_nosp_mtp": dict(world=2, kw=dict(tp=2, sp=False, mtp=1)),
     "pp2_dp2_mtp": dict(world=4, kw=dict(pp=2, mtp=1)),
     "cp4_a2a_p2p": dict(world=4, kw=dict(cp=4, cp_comm="a2a+p2p", cp_sizes=[2, 2], seq=64)),
+    # Kimi-K3: the running stream and the attention-residual checkpoints cross the stage boundary as one tensor
+    "pp2_kimi_k3": dict(world=2, kw=dict(pp=2, layers=6, extra_mc=dict(
+        model_type="kimi_k3", q_lora_rank=32, kv_lora_rank=24, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16,
+        mla_use_output_gate=True, linear_attention_freq="([1]*2+[0])*2", linear_num_key_heads=4, linear_num_value_heads=4,
+        linear_key_head_dim=16, linear_value_head_dim=16, kda_chunk_size=16, attn_res_block_size=2, num_experts=4,
+        moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq="([0]*1+[1]*5)", moe_shared_expert_intermediate_size=32,
+        routed_expert_hidden_size=32, moe_router_score_function="sigmoid", gated_activation="situ"))),
+    # DeepSeek-V4: the hyper-connection streams cross the stage boundary; hash-routed layers on both stages
+    "pp2_deepseek_v4": dict(world=2, kw=dict(pp=2, layers=4, seq=128, extra_mc=dict(
+        model_type="deepseek_v4", num_query_groups=1, kv_channels=32, qk_pos_emb_head_dim=8, q_lora_rank=32, o_lora_rank=16,
+        o_groups=2, hc_mult=3, hc_sinkhorn_iters=6, compress_ratios="[0, 4, 128, 4]", compress_rope_theta=40000.0,
+        index_topk=4, index_head_dim=16, index_n_heads=2, attn_sliding_window=8, num_experts=4, moe_router_topk=2,
+        moe_ffn_hidden_size=32, moe_layer_freq=1, moe_shared_expert_intermediate_size=32,
+        moe_router_score_function="sqrtsoftplus", num_hash_layers=3, activation_func_clamp_value=10.0))),
 }
 
 

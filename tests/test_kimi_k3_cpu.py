@@ -245,5 +245,31 @@ def test_presets_resolve():
     kinds = [k for k, _ in c.layer_kinds]
     assert kinds.count("kda") == 69 and kinds.count("attention") == 24 and c.multi_latent_attention and c.mla_use_nope
     assert sum(c.moe_layer_pattern) == 92 and c.routed_expert_hidden_size == 3584
-    c8 = TransformerConfig.from_dict(load_preset("kimi_k3_8L.yaml", "models", "primus_b200"))
+    c8 = TransformerConfig.from_dict(load_preset("kimi_k3_8L_official.yaml", "models", "primus_b200"))
     assert [k for k, _ in c8.layer_kinds] == ["kda"] * 3 + ["attention"] + ["kda"] * 3 + ["attention"]
+
+
+def test_delta_attention_stack_of_the_hybrid_presets():
+    """``linear_attention_type: kda`` in a Mamba-style stack: mixer layers alternate with MLP layers, key heads narrower than
+    value heads, output gate and forget gate through bottlenecks, unbounded softplus decay."""
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    torch.manual_seed(9)
+    cfg = TransformerConfig(model_type="mamba", is_hybrid_model=True, linear_attention_type="kda", num_layers=4,
+                            hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, vocab_size=256, params_dtype="fp32",
+                            linear_num_key_heads=4, linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=16,
+                            kda_use_full_rank_gate=False, kda_gate_lower_bound=None, kda_chunk_size=16)
+    assert cfg.layer_kinds == [("kda", False), (None, True)] * 2
+    m = GPTModel(cfg)
+    assert sum(p.numel() for p in m.parameters()) == cfg.num_parameters()
+    mixer = m.decoder.layers["0"].mixer
+    assert mixer.f_b_proj.weight.shape == (32, 16) and mixer.g_b_proj.weight.shape == (64, 16)
+    tok = torch.randint(0, 256, (2, 40))
+    loss = m(tok, tok, None).mean()
+    loss.backward()
+    assert math.isfinite(float(loss)) and all(p.grad is not None for p in m.parameters())
+    ps.destroy_model_parallel()

@@ -19,7 +19,7 @@ from __future__ import annotations
 import glob
 import json
 import os
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -402,6 +402,71 @@ def load_full_into_trainer(trainer, full_sd: Dict[str, torch.Tensor]) -> None:
 
 def load_hf_into_trainer(trainer, path: str) -> None:
     load_full_into_trainer(trainer, hf_to_internal(read_hf_weights(path), trainer.mcfg))
+
+
+def gather_full_state(trainer) -> Optional[Dict[str, torch.Tensor]]:
+    """The whole model in the internal layout on rank 0 (None elsewhere): every rank contributes the shards it owns
+    (tensor-, expert- and pipeline-parallel), data-parallel replicas are taken from the first replica."""
+    import torch.distributed as dist
+
+    from . import checkpoint as C
+
+    st, cfg = trainer.st, trainer.mcfg
+    mine = []
+    for name, p in C.model_named_parameters(trainer):
+        if getattr(p, "embedding_replica", False):
+            continue
+        spec = C.shard_spec(name, p, cfg, st)
+        if C._is_writer(spec, C.saved_key(name), st, False):
+            mine.append((name, spec, C.to_saved_layout(name, p.detach().cpu(), cfg, st.tp)))
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        everything = [mine]
+    else:
+        everything = [None] * dist.get_world_size() if dist.get_rank() == 0 else None
+        dist.gather_object(mine, everything, dst=0)
+        if dist.get_rank() != 0:
+            return None
+    shards: Dict[str, list] = {}
+    for part in everything:
+        for name, spec, t in part:
+            shards.setdefault(name, []).append((spec, t))
+    return {name: C.from_saved_layout(name, C.assemble_global(name, sh), cfg, 1) for name, sh in shards.items()}
+
+
+def export_trainer_to_hf(trainer, path: str) -> None:
+    sd = gather_full_state(trainer)
+    if sd is not None:
+        save_hf(sd, trainer.mcfg, path)
+        trainer.log(f"[hf] wrote {len(sd)} tensors in Hugging Face layout to {path}")
+
+
+def read_engine_checkpoint(root: str, iteration: Optional[int] = None):
+    """(full internal state dict, TransformerConfig) of a ``torch_dist`` checkpoint, read in one process without
+    building a trainer: the global tensors come straight from the checkpoint's metadata."""
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint import FileSystemReader
+    from torch.distributed.checkpoint.metadata import TensorStorageMetadata
+
+    from ..models.config import TransformerConfig
+    from . import checkpoint as C
+
+    it = iteration if iteration is not None else C.latest_iteration(root)
+    d = C.checkpoint_dir(root, it) if it is not None else os.path.join(root, "release")
+    common = torch.load(os.path.join(d, "common.pt"), map_location="cpu", weights_only=False)
+    cfg = TransformerConfig.from_dict(common["args"]["model"])
+    reader = FileSystemReader(d)
+    md = reader.read_metadata().state_dict_metadata
+    sd = {k: torch.empty(tuple(m.size), dtype=m.properties.dtype) for k, m in md.items()
+          if isinstance(m, TensorStorageMetadata) and not k.startswith(("optimizer", "rng_state/", "weight_deosc/"))}
+    dcp.load(sd, storage_reader=reader, no_dist=True)
+    back = {b: a for a, b in C._RENAMES}
+    out = {}
+    for k, t in sd.items():
+        name = k
+        for saved, internal in back.items():
+            name = name.replace(saved, internal)
+        out[name] = C.from_saved_layout(name, t, cfg, 1)
+    return out, cfg
 
 
 def save_hf(trainer_or_sd, cfg, path: str) -> None:

@@ -43,6 +43,12 @@ class PretrainTrainer(BaseTrainer):
         self.engine = Trainer(mcfg, tcfg, log_fn=logutil.log_rank_all)
         if tcfg.load:
             self.engine.load_checkpoint()
+        if tcfg.pretrained_hf_path and self.engine.iteration == 0:
+            # start from published Hugging Face weights (every rank reads the files and keeps its own slices)
+            from . import hf_convert
+
+            hf_convert.load_hf_into_trainer(self.engine, tcfg.pretrained_hf_path)
+            logutil.log_rank_0(f"loaded Hugging Face weights from {tcfg.pretrained_hf_path}")
         logutil.log_rank_0(f"model parameters: {mcfg.num_parameters() / 1e9:.3f} B; "
                            f"dp={ps.dp_size()} tp={ps.tp_size()} pp={ps.pp_size()} ep={ps.ep_size()}")
 
@@ -55,6 +61,10 @@ class PretrainTrainer(BaseTrainer):
         tc = self.engine.tcfg
         if tc.save and not self.params.get("disable_last_saving", False):
             self.engine.save_checkpoint()
+        if tc.export_hf_path:
+            from . import hf_convert
+
+            hf_convert.export_trainer_to_hf(self.engine, tc.export_hf_path)
         logutil.log_rank_0(COMPLETED_MESSAGE)
 
     def cleanup(self):

@@ -140,6 +140,8 @@ class TrainConfig:
     decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
+    pretrained_hf_path: Optional[str] = None     # directory of Hugging Face weights to start from (when no checkpoint is loaded)
+    export_hf_path: Optional[str] = None         # write the trained weights in Hugging Face layout after the last step
     sft_grad_sanitize: bool = False   # zero non-finite gradient entries instead of skipping / failing the step
     # MXFP4 weight de-oscillation (parallel/weight_deosc.py): over windows of ``period`` steps, elements whose quantised
     # value travelled ``ratio`` times further than their master value are snapped onto their current code

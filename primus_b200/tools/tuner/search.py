@@ -66,7 +66,7 @@ def enumerate_plans(cfg, world: int, global_batch: int, seq: int, gpus_per_node:
         if world % (tp * pp * cp):
             continue
         if cfg.num_experts and tp > 1:
-            continue  # MoE layers run with tensor_model_parallel_size 1 in this engine
+            continue  # the projection has no model of MoE layers under tensor parallelism: such plans are not proposed
         dp = world // (tp * pp * cp)
         eps = [e for e in _divisors(cfg.num_experts, tp * cp * dp) if (tp * cp * dp) % e == 0] if cfg.num_experts else [1]
         for ep in eps:

@@ -153,3 +153,48 @@ def test_qwen3_5_moe_matches_hf():
         from primus_b200.ops import fused
 
         fused.set_zero_centered_gamma(False)
+
+
+def test_train_from_hf_weights_export_and_offline_conversion(tmp_path):
+    """``pretrained_hf_path`` -> a step of training -> ``export_hf_path``; the exported weights load into the Hugging Face
+    model again, and the offline converter reads the engine checkpoint of the same run into the same tensors."""
+    from safetensors.torch import load_file, save_file
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from primus_b200.engine.pretrain import PretrainTrainer
+    from primus_b200.parallel import state as ps
+    from primus_b200.tools import convert_checkpoint
+
+    torch.manual_seed(11)
+    c = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                    num_key_value_heads=2, vocab_size=256, max_position_embeddings=128, tie_word_embeddings=False)
+    hf = LlamaForCausalLM(c)
+    src = tmp_path / "hf_in"
+    src.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(src / "model.safetensors"))
+    (src / "config.json").write_text(c.to_json_string())
+    params = dict(H.config_from_hf(c.to_dict()), params_dtype="fp32", make_vocab_size_divisible_by=64, seq_length=32,
+                  micro_batch_size=2, global_batch_size=2, train_iters=1, lr=0.0, weight_decay=0.0, mock_data=True,
+                  log_interval=1, pretrained_hf_path=str(src), export_hf_path=str(tmp_path / "hf_out"),
+                  save=str(tmp_path / "ckpt"), use_distributed_optimizer=True)
+    ps.destroy_model_parallel()
+    try:
+        tr = PretrainTrainer.__new__(PretrainTrainer)
+        tr.params, tr.runtime_state, tr.world_size, tr.local_rank = params, None, 1, 0
+        tr.init()
+        tok = torch.randint(0, 256, (1, 16))
+        with torch.no_grad():
+            assert torch.allclose(tr.engine.model(tok)[:, :256], hf(tok).logits.reshape(-1, 256), atol=2e-4)
+        tr.train()
+    finally:
+        ps.destroy_model_parallel()
+    out = load_file(str(tmp_path / "hf_out" / "model.safetensors"))
+    for k, v in hf.state_dict().items():        # learning rate 0: the exported weights are the imported ones
+        assert torch.equal(out[k], v), k
+    assert convert_checkpoint.main(["engine-to-hf", "--load", str(tmp_path / "ckpt"), "--output", str(tmp_path / "hf2")]) == 0
+    out2 = load_file(str(tmp_path / "hf2" / "model.safetensors"))
+    assert all(torch.equal(out2[k], v) for k, v in hf.state_dict().items())
+    assert convert_checkpoint.main(["hf-to-engine", "--hf", str(src), "--output", str(tmp_path / "full.pt"),
+                                    "--params-dtype", "fp32"]) == 0
+    full = torch.load(tmp_path / "full.pt", weights_only=False)
+    assert set(full["state"]) == set(tr.engine.model.state_dict())

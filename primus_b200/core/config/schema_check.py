@@ -28,16 +28,18 @@ INERT_KEYS = {
     # numerics fixed by the design: bf16 parameters, fp32 main gradients and accumulation, no loss scaling
     "accumulate_allreduce_grads_in_fp32", "loss_scale", "ddp_average_in_collective",
     # model switches of architectures that are not built (biases, LayerNorm, learned positions)
-    "normalization", "position_embedding_type", "lora_dropout",
-    # data loading is synchronous mock / indexed data staged by the trainer itself
-    "create_attention_mask_in_dataloader", "dataloader_type", "num_workers", "train_samples",
+    "normalization", "position_embedding_type",
+    # adapters are folded into the effective weight before the forward pass: there is no separate adapter input to drop
+    "lora_dropout",
+    # the trainer stages its own batches (sequential sample order; attention masks come from the kernels)
+    "create_attention_mask_in_dataloader", "dataloader_type",
     # kernel selection switches of the reference's operator library: one native implementation here
     "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_parallel_linear",
     "use_turbo_rms_norm", "turbo_deepep_num_cu",
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "straggler_ctrlr_port",
     "trainable",
-    "log_throughput", "use_tp_pp_dp_mapping", "offload_ops",
+    "offload_ops",
     # switches between the reference's two pipeline implementations (one runtime here; the schedule is chosen with
     # pp_algorithm / pipeline_schedule or enable_zero_bubble + zero_bubble_v_schedule)
     "patch_primus_pipeline", "patch_zero_bubble", "pp_communication_method",

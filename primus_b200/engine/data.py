@@ -128,24 +128,54 @@ def collate(samples: list[dict]) -> dict:
 
 
 class BatchStager:
-    """Double-buffered pinned-host -> device staging of micro-batches on a side stream."""
+    """Double-buffered pinned-host -> device staging of micro-batches on a side stream.
 
-    def __init__(self, dataset, sampler: MicroBatchSampler, device, pin: Optional[bool] = None):
+    ``num_workers`` > 0: the host side of a step (reading / tokenising the samples, collating, pinning) runs on worker
+    threads, one step ahead of the device copy, so that it overlaps the training step instead of sitting between two of
+    them; the samples of a step are fetched by up to ``num_workers`` threads.  The order of the samples is the
+    sampler's in every case.  (The reference hands this to the data loader's worker processes: ``num_workers`` in
+    primus/configs/modules/megatron/trainer_base.yaml.)"""
+
+    def __init__(self, dataset, sampler: MicroBatchSampler, device, pin: Optional[bool] = None, num_workers: int = 0):
         self.dataset, self.sampler, self.device = dataset, sampler, torch.device(device)
         self.cuda = self.device.type == "cuda"
         self.pin = self.cuda if pin is None else pin
         self.stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self._next = None
+        self._host_future = None
         self.h2d_bytes_last_step = 0
+        self.num_workers = int(num_workers or 0)
+        self._pool = self._loader = None
+        if self.num_workers > 0:
+            from concurrent.futures import ThreadPoolExecutor
 
-    def _load_host(self) -> list[dict]:
+            self._pool = ThreadPoolExecutor(self.num_workers, thread_name_prefix="primus-b200-data")
+            self._loader = ThreadPoolExecutor(1, thread_name_prefix="primus-b200-batch")
+
+    def _build_host(self, index_lists: list) -> list[dict]:
+        if self.cuda and self._loader is not None:
+            torch.cuda.set_device(self.device)      # a new thread starts on device 0: pin through this rank's context
         mbs = []
-        for idxs in self.sampler.next_global_batch():
-            b = collate([self.dataset[i] for i in idxs])
+        for idxs in index_lists:
+            samples = list(self._pool.map(self.dataset.__getitem__, idxs)) if self._pool else [self.dataset[i] for i in idxs]
+            b = collate(samples)
             if self.pin:
                 b = {k: (v if k.startswith("host_") else v.pin_memory()) for k, v in b.items()}
             mbs.append(b)
         return mbs
+
+    def _load_host(self) -> list[dict]:
+        if self._loader is None:
+            return self._build_host(self.sampler.next_global_batch())
+        if self._host_future is None:       # first step: nothing is in flight yet
+            self._host_future = self._loader.submit(self._build_host, self.sampler.next_global_batch())
+        host = self._host_future.result()
+        self._host_future = self._loader.submit(self._build_host, self.sampler.next_global_batch())
+        return host
+
+    def _pending_steps(self) -> int:
+        """Steps the sampler has handed out that training has not consumed (replayed after a resume)."""
+        return int(self._next is not None) + int(self._host_future is not None)
 
     def _to_device(self, host_mbs: list[dict]):
         if not self.cuda:
@@ -186,9 +216,12 @@ class BatchStager:
 
     def state_dict(self):
         # a prefetched-but-unconsumed step must be replayed after a resume
-        c = self.sampler.consumed - (self.sampler.gbs if self._next is not None else 0)
+        c = self.sampler.consumed - self.sampler.gbs * self._pending_steps()
         return {"consumed_samples": c}
 
     def load_state_dict(self, sd):
         self._next = None
+        if self._host_future is not None:
+            self._host_future.result()          # let the worker finish before the sampler is rewound
+            self._host_future = None
         self.sampler.load_state_dict(sd)

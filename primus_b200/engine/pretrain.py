@@ -12,7 +12,7 @@ from ..core.utils import logger as logutil
 from ..models.config import TransformerConfig
 from ..parallel import state as ps
 from .base_trainer import BaseTrainer
-from .trainer import TrainConfig, Trainer
+from .trainer import init_parallel_state, TrainConfig, Trainer
 
 COMPLETED_MESSAGE = "Training completed."
 
@@ -36,10 +36,7 @@ class PretrainTrainer(BaseTrainer):
 
     def init(self):
         mcfg, tcfg = self.build_configs()
-        ps.initialize_model_parallel(
-            tp=mcfg.tensor_model_parallel_size, pp=mcfg.pipeline_model_parallel_size, cp=mcfg.context_parallel_size,
-            ep=mcfg.expert_model_parallel_size, etp=mcfg.expert_tensor_parallel_size or 1,
-            virtual_pp=mcfg.virtual_pipeline_model_parallel_size)
+        init_parallel_state(mcfg, tcfg)
         self.engine = Trainer(mcfg, tcfg, log_fn=logutil.log_rank_all)
         if tcfg.load:
             self.engine.load_checkpoint()

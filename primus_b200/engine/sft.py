@@ -499,7 +499,7 @@ class SFTTrainer(PretrainTrainer):
             if ds is not None:
                 eng.sampler = MicroBatchSampler(eng.tcfg.global_batch_size, eng.tcfg.micro_batch_size, eng.st.dp,
                                                 eng.st.dp_rank)
-                eng.stager = BatchStager(ds, eng.sampler, eng.device)
+                eng.stager = BatchStager(ds, eng.sampler, eng.device, num_workers=eng.tcfg.num_workers)
                 eng.use_position_ids = True
         if p.get("peft") == "lora":
             eng.lora = LoRAEngine(eng.model_chunks, int(p.get("lora_rank", 16)), float(p.get("lora_alpha", 32)),

@@ -140,6 +140,10 @@ class TrainConfig:
     decoder_pipeline_manual_split_list: Optional[list] = None
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
+    num_workers: int = 0                         # data loading threads (0: the training thread loads its own batches)
+    use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
+    log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
+    train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
     pretrained_hf_path: Optional[str] = None     # directory of Hugging Face weights to start from (when no checkpoint is loaded)
     export_hf_path: Optional[str] = None         # write the trained weights in Hugging Face layout after the last step
     sft_grad_sanitize: bool = False   # zero non-finite gradient entries instead of skipping / failing the step
@@ -193,6 +197,8 @@ class TrainConfig:
 
             fused_tp.ENABLED = True
             fused_tp.ENABLED_RS = bool(d.get("tp_comm_overlap_rs", False))
+        if d.get("train_samples"):      # sample-based run length (Megatron's train_samples): whole global batches
+            kw["train_iters"] = int(d["train_samples"]) // int(kw.get("global_batch_size", cls.global_batch_size))
         return cls(**kw)
 
 
@@ -235,6 +241,17 @@ class ThroughputMeter:
         return self.n / self.inv_sum
 
 
+def init_parallel_state(model_cfg, train_cfg):
+    """Process groups for the configured parallel sizes (``use_tp_pp_dp_mapping``: pipeline stages on neighbouring ranks,
+    data-parallel replicas far apart, instead of the other way round)."""
+    return ps.initialize_model_parallel(
+        tp=model_cfg.tensor_model_parallel_size, pp=model_cfg.pipeline_model_parallel_size,
+        cp=model_cfg.context_parallel_size, ep=model_cfg.expert_model_parallel_size,
+        etp=model_cfg.expert_tensor_parallel_size or 1, virtual_pp=model_cfg.virtual_pipeline_model_parallel_size,
+        hierarchical_cp_sizes=model_cfg.hierarchical_context_parallel_sizes if model_cfg.cp_comm_type == "a2a+p2p" else None,
+        tp_pp_dp_mapping=bool(getattr(train_cfg, "use_tp_pp_dp_mapping", False)))
+
+
 class Trainer:
     def __init__(self, model_cfg: TransformerConfig, train_cfg: TrainConfig, device: Optional[str] = None,
                  log_fn: Callable[[str], None] = print):
@@ -257,12 +274,7 @@ class Trainer:
                 raise NotImplementedError(f"num_seq_splits > 1 is not built together with: {', '.join(bad)}")
         st = ps.get_state()
         if not st.initialized:
-            st = ps.initialize_model_parallel(
-                tp=model_cfg.tensor_model_parallel_size, pp=model_cfg.pipeline_model_parallel_size,
-                cp=model_cfg.context_parallel_size, ep=model_cfg.expert_model_parallel_size,
-                etp=model_cfg.expert_tensor_parallel_size, virtual_pp=model_cfg.virtual_pipeline_model_parallel_size,
-                hierarchical_cp_sizes=model_cfg.hierarchical_context_parallel_sizes
-                if model_cfg.cp_comm_type == "a2a+p2p" else None)
+            st = init_parallel_state(model_cfg, train_cfg)
         self.st = st
         if device is None:
             device = f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu"
@@ -508,7 +520,7 @@ class Trainer:
         else:
             ds = _open_corpus(train_cfg.data_path, train_cfg.seq_length, train_cfg.data_seed, train_cfg)
         self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank)
-        self.stager = BatchStager(ds, self.sampler, self.device)
+        self.stager = BatchStager(ds, self.sampler, self.device, num_workers=train_cfg.num_workers)
         if train_cfg.reset_position_ids:
             self.use_position_ids = True
         self.iteration = 0
@@ -1003,8 +1015,9 @@ class Trainer:
             moe_text = f" load balancing loss: {v:.6E} |"
         if st.rank == st.world_size - 1 or st.world_size == 1:
             self.log(
-                f" iteration {self.iteration:8d}/{tc.train_iters:8d} | elapsed time per iteration (ms): {dt * 1e3:.1f} | "
-                f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
+                f" iteration {self.iteration:8d}/{tc.train_iters:8d} | elapsed time per iteration (ms): {dt * 1e3:.1f} | " +
+                (f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
+                 if tc.log_throughput else "") +
                 f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
                 f"lm loss: {loss:.6E} |{moe_text} grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
         if tc.timing_log_level > 0:

@@ -68,16 +68,22 @@ def get_state() -> ParallelState:
     return _STATE
 
 
-def rank_coords(rank: int, tp: int, cp: int, dp: int, pp: int) -> tuple[int, int, int, int]:
-    """(tp_rank, cp_rank, dp_rank, pp_rank) of a global rank."""
+def rank_coords(rank: int, tp: int, cp: int, dp: int, pp: int, tp_pp_dp: bool = False) -> tuple[int, int, int, int]:
+    """(tp_rank, cp_rank, dp_rank, pp_rank) of a global rank.  Default order of the ranks: tensor fastest, then context,
+    data, pipeline (a pipeline's stages are far apart, a data-parallel group is close together); ``tp_pp_dp``: tensor,
+    context, pipeline, data (the stages of a pipeline are neighbours, data-parallel replicas far apart) -- the
+    reference's ``use_tp_pp_dp_mapping`` (primus/configs/modules/megatron/trainer_base.yaml)."""
     t = rank % tp
     c = (rank // tp) % cp
+    if tp_pp_dp:
+        return t, c, rank // (tp * cp * pp), (rank // (tp * cp)) % pp
     d = (rank // (tp * cp)) % dp
     p = rank // (tp * cp * dp)
     return t, c, d, p
 
 
-def group_rank_lists(world: int, tp: int, cp: int, pp: int, ep: int = 1, etp: int = 1) -> dict[str, list[list[int]]]:
+def group_rank_lists(world: int, tp: int, cp: int, pp: int, ep: int = 1, etp: int = 1,
+                     tp_pp_dp: bool = False) -> dict[str, list[list[int]]]:
     """Pure function: every group of every kind as lists of global ranks (tested on CPU)."""
     assert world % (tp * cp * pp) == 0, f"world {world} not divisible by tp*cp*pp={tp * cp * pp}"
     dp = world // (tp * cp * pp)
@@ -85,6 +91,8 @@ def group_rank_lists(world: int, tp: int, cp: int, pp: int, ep: int = 1, etp: in
     out: dict[str, list[list[int]]] = {k: [] for k in ("tp", "cp", "dp", "dp_cp", "pp", "ep", "edp", "mp", "stage")}
 
     def gid(t, c, d, p):
+        if tp_pp_dp:
+            return t + tp * (c + cp * (p + pp * d))
         return t + tp * (c + cp * (d + dp * p))
 
     for p in range(pp):
@@ -108,13 +116,13 @@ def group_rank_lists(world: int, tp: int, cp: int, pp: int, ep: int = 1, etp: in
     assert per_stage % (etp * ep) == 0, f"tp*cp*dp={per_stage} not divisible by etp*ep={etp * ep}"
     edp = per_stage // (etp * ep)
     for p in range(pp):
-        base = p * per_stage
+        stage = out["stage"][p]            # this stage's ranks, tensor fastest, then context, then data
         for e_d in range(edp):
             for e_t in range(etp):
-                out["ep"].append([base + e_t + etp * (e + ep * e_d) for e in range(ep)])
+                out["ep"].append([stage[e_t + etp * (e + ep * e_d)] for e in range(ep)])
         for e in range(ep):
             for e_t in range(etp):
-                out["edp"].append([base + e_t + etp * (e + ep * e_d) for e_d in range(edp)])
+                out["edp"].append([stage[e_t + etp * (e + ep * e_d)] for e_d in range(edp)])
     return out
 
 
@@ -135,7 +143,8 @@ def init_distributed(backend: Optional[str] = None, timeout_minutes: float = 10.
 
 
 def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1, etp: int = 1,
-                              virtual_pp: Optional[int] = None, hierarchical_cp_sizes=None) -> ParallelState:
+                              virtual_pp: Optional[int] = None, hierarchical_cp_sizes=None,
+                              tp_pp_dp_mapping: bool = False) -> ParallelState:
     """Create all groups. Every rank must call this with identical arguments.  ``hierarchical_cp_sizes``: ``[a2a, p2p]``
     with ``a2a * p2p == cp`` splits every context-parallel group into all-to-all groups of neighbouring ranks and ring
     groups across them (the reference's ``hierarchical_context_parallel_sizes``,
@@ -147,11 +156,11 @@ def initialize_model_parallel(tp: int = 1, pp: int = 1, cp: int = 1, ep: int = 1
         return _STATE
     world = dist.get_world_size()
     rank = dist.get_rank()
-    lists = group_rank_lists(world, tp, cp, pp, ep, etp)
+    lists = group_rank_lists(world, tp, cp, pp, ep, etp, tp_pp_dp_mapping)
     dp = world // (tp * cp * pp)
     st = ParallelState(world_size=world, rank=rank, tp=tp, cp=cp, pp=pp, dp=dp, ep=ep, etp=etp,
                        edp=(tp * cp * dp) // (etp * ep), virtual_pp=virtual_pp, initialized=True)
-    st.tp_rank, st.cp_rank, st.dp_rank, st.pp_rank = rank_coords(rank, tp, cp, dp, pp)
+    st.tp_rank, st.cp_rank, st.dp_rank, st.pp_rank = rank_coords(rank, tp, cp, dp, pp, tp_pp_dp_mapping)
 
     def make(kind: str):
         mine, mine_ranks = None, None

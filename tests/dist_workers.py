@@ -86,7 +86,8 @@ def train_worker(rank, world, kwargs, mc_kwargs_full, outq_path):
     mc, tc = tiny_cfgs(**kwargs)
     ps.initialize_model_parallel(tp=mc.tensor_model_parallel_size, pp=mc.pipeline_model_parallel_size,
                                  ep=mc.expert_model_parallel_size, cp=mc.context_parallel_size, virtual_pp=mc.virtual_pipeline_model_parallel_size,
-                                 hierarchical_cp_sizes=mc.hierarchical_context_parallel_sizes)
+                                 hierarchical_cp_sizes=mc.hierarchical_context_parallel_sizes,
+                                 tp_pp_dp_mapping=tc.use_tp_pp_dp_mapping)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     load_from_full(tr, full_sd)
     norms = []

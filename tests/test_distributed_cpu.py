@@ -45,6 +45,9 @@ CASES = {
     "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
     "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
+    "dp2_pp2_tp_pp_dp_mapping": dict(world=4, kw=dict(pp=2, extra_tc=dict(use_tp_pp_dp_mapping=True))),
+    "tp2_pp2_ep2_tp_pp_dp_mapping": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, moe=True,
+                                                          extra_tc=dict(use_tp_pp_dp_mapping=True))),
     "pp2_interleaved": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved")),
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),

@@ -24,6 +24,7 @@ import torch.nn as nn
 
 from ..ops import attention, fused, gemm, layers
 from ..parallel import state as ps
+from ..parallel import tensor_parallel as tpc
 from .config import TransformerConfig
 
 
@@ -56,10 +57,14 @@ class MLASelfAttention(nn.Module):
         super().__init__()
         from .gpt import ParamHolder, _param
 
-        assert tp == 1, "MLA is implemented for tensor_model_parallel_size 1"
+        # Tensor parallelism splits the heads: the up-projections are column-parallel, the output projection is
+        # row-parallel; the two down-projections and the norms are replicated and work on this rank's tokens (under
+        # sequence parallelism their gradients are partial sums, added over the group like those of the norm weights).
+        assert cfg.num_attention_heads % tp == 0, "attention heads must divide by the tensor-parallel size"
         self.cfg = cfg
+        self.tp = tp
         dt = cfg.torch_dtype
-        h, nh = cfg.hidden_size, cfg.num_attention_heads
+        h, nh = cfg.hidden_size, cfg.num_attention_heads // tp
         self.nh = nh
         self.dn, self.dr, self.dv = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
         std = cfg.init_method_std
@@ -80,6 +85,24 @@ class MLASelfAttention(nn.Module):
             # Kimi-K3: attention output times sigmoid(gate), the gate projected from the normalised layer input
             # (primus/backends/megatron/core/transformer/kimi_k3/kimi_k3_mla_attention.py:68-92 in the reference)
             self.linear_o_gate = ParamHolder(weight=_param((nh * self.dv, h), std, dt, device))
+        if tp > 1:
+            sp = bool(cfg.sequence_parallel)
+            split = [(self.linear_kv_up_proj.weight, 0), (self.linear_proj.weight, 1)]
+            replicated = [self.input_layernorm.weight, self.linear_kv_down_proj.weight, self.linear_kv_up_proj.layer_norm_weight]
+            if cfg.q_lora_rank:
+                split.append((self.linear_q_up_proj.weight, 0))
+                replicated += [self.linear_q_down_proj.weight, self.linear_q_up_proj.layer_norm_weight]
+            else:
+                split.append((self.linear_q_proj.weight, 0))
+            if cfg.mla_use_output_gate:
+                split.append((self.linear_o_gate.weight, 0))
+            for w, dim in split:
+                w.tensor_model_parallel, w.partition_dim = True, dim
+            st = ps.get_state()
+            for w in replicated:
+                w.sequence_parallel = sp
+                if w.dim() == 2 and torch.distributed.is_initialized():     # drawn per rank: make the replicas equal
+                    torch.distributed.broadcast(w.data, src=st.tp_ranks[0], group=st.tp_group)
         factor = cfg.rotary_scaling_factor or 1.0
         m = yarn_mscale(factor, cfg.mscale)
         self.softmax_scale = (m * m) / math.sqrt(qd)
@@ -105,9 +128,20 @@ class MLASelfAttention(nn.Module):
             y, xsum = fused.rmsnorm(hidden, self.input_layernorm.weight, cfg.norm_epsilon, residual)
         else:
             y, xsum = fused.rmsnorm(hidden, self.input_layernorm.weight, cfg.norm_epsilon), hidden
-        T = y.shape[0]
+        st = ps.get_state()
+        tpg = st.tp_group if self.tp > 1 else None
+        sp = bool(cfg.sequence_parallel) and self.tp > 1
+
+        def everywhere(t):
+            """Input of a column-parallel projection: all tokens on every rank (gathered under sequence parallelism;
+            otherwise already there, and the gradients of the ranks' head slices are added in the backward pass)."""
+            if tpg is None:
+                return t
+            return tpc.gather_seq(t, tpg) if sp else tpc.copy_to_tp(t, tpg)
+
+        T = y.shape[0] * (self.tp if sp else 1)
         seq = T // batch
-        cos, sin = self.rope_tables(y.device, seq * ps.get_state().cp)   # positions are global under context parallelism
+        cos, sin = self.rope_tables(y.device, seq * st.cp)   # positions are global under context parallelism
         pos = rope[2]
         if cfg.attn_logit_softcapping:
             raise NotImplementedError("attn_logit_softcapping is not built for multi-latent attention")
@@ -116,15 +150,15 @@ class MLASelfAttention(nn.Module):
         if cfg.q_lora_rank:
             ql = gemm.linear(y, self.linear_q_down_proj.weight)
             ql = fused.rmsnorm(ql, self.linear_q_up_proj.layer_norm_weight, cfg.norm_epsilon)
-            q = gemm.linear(ql, self.linear_q_up_proj.weight)
+            q = gemm.linear(everywhere(ql), self.linear_q_up_proj.weight)
         else:
-            q = gemm.linear(y, self.linear_q_proj.weight)
+            q = gemm.linear(everywhere(y), self.linear_q_proj.weight)
         q = q.view(T, nh, dn + dr)
         c = gemm.linear(y, self.linear_kv_down_proj.weight)
         latent = fused.rmsnorm(c[:, :cfg.kv_lora_rank].contiguous(), self.linear_kv_up_proj.layer_norm_weight,
                                cfg.norm_epsilon)
-        k_pe = c[:, cfg.kv_lora_rank:].reshape(T, 1, dr)
-        kv = gemm.linear(latent, self.linear_kv_up_proj.weight).view(T, nh, dn + dv)
+        k_pe = everywhere(c[:, cfg.kv_lora_rank:].contiguous()).reshape(T, 1, dr)
+        kv = gemm.linear(everywhere(latent), self.linear_kv_up_proj.weight).view(T, nh, dn + dv)
         if cfg.mla_use_nope:
             # no rotation: the dr "rope" dims of q and the shared key dims are ordinary learned features; the head
             # geometry and the softmax scale stay those of the rotary layout (kimi_k3_mla_attention.py:24-60)
@@ -135,7 +169,6 @@ class MLASelfAttention(nn.Module):
         q_full = torch.cat([q_pe, q[..., :dn]], dim=-1)
         k_full = torch.cat([k_pe.expand(T, nh, dr), kv[..., :dn]], dim=-1)
         v = kv[..., dn:].contiguous()
-        st = ps.get_state()
         if st.cp > 1:
             if cfg.cp_comm_type == "p2p":
                 ctx_out = layers.ring_cp_attention(q_full.contiguous(), k_full.contiguous(), v, batch, st.cp_group, st.cp,
@@ -150,7 +183,7 @@ class MLASelfAttention(nn.Module):
             ctx_out = attention.flash_attention(q_full, k_full, v, batch, True, self.softmax_scale)
         ctx_out = ctx_out.reshape(T, nh * dv)
         if cfg.mla_use_output_gate:
-            gate = gemm.linear(y, self.linear_o_gate.weight)
+            gate = gemm.linear(everywhere(y), self.linear_o_gate.weight)
             ctx_out = (ctx_out * torch.sigmoid(gate.float()).to(ctx_out.dtype)).contiguous()
-        out = gemm.linear(ctx_out, self.linear_proj.weight)
+        out = layers.row_parallel_linear(ctx_out.contiguous(), self.linear_proj.weight, tpg, sp)
         return out, xsum

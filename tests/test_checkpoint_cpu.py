@@ -71,9 +71,9 @@ def test_finetune_load_resets_iteration(tmp_path):
         assert torch.equal(p, pa[n])
 
 
-def _reshard_worker(rank, world, root, outp):
+def _reshard_worker(rank, world, root, outp, kw=None):
     ps.destroy_model_parallel()
-    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, tp=2, sp=True, extra_mc=dict(add_qkv_bias=True))
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, tp=2, sp=True, **(kw or dict(extra_mc=dict(add_qkv_bias=True))))
     ps.initialize_model_parallel(tp=2)
     tr = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
     tr.load_checkpoint(root)
@@ -92,6 +92,22 @@ def test_load_tp1_checkpoint_into_tp2(tmp_path):
     ref = a.train(2)
     outp = str(tmp_path / "l.json")
     run_ranks(_reshard_worker, 2, "gloo", args=(root, outp), timeout=200)
+    got = json.load(open(outp))
+    for x, y in zip(got, ref):
+        assert abs(x - y) <= 2e-3 * max(1.0, abs(y)), (got, ref)
+
+
+def test_load_tp1_mla_checkpoint_into_tp2(tmp_path):
+    """Multi-latent attention under tensor parallelism: head-split up-projections and output projection, replicated
+    down-projections; weights and optimizer state of a tp = 1 checkpoint are re-sliced."""
+    root = str(tmp_path / "ckpt")
+    a = _trainer(iters=4, mla=True)
+    a.tcfg.use_distributed_optimizer = True
+    a.train(2)
+    a.save_checkpoint(root)
+    ref = a.train(2)
+    outp = str(tmp_path / "l.json")
+    run_ranks(_reshard_worker, 2, "gloo", args=(root, outp, dict(mla=True)), timeout=200)
     got = json.load(open(outp))
     for x, y in zip(got, ref):
         assert abs(x - y) <= 2e-3 * max(1.0, abs(y)), (got, ref)

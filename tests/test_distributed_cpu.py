@@ -44,6 +44,9 @@ CASES = {
     "dp2_pp2_overlap_param_gather": dict(world=4, kw=dict(pp=2, extra_tc=dict(overlap_param_gather=True))),
     "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
     "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
+    "tp2_sp_mla": dict(world=2, kw=dict(tp=2, sp=True, mla=True)),
+    "tp2_nosp_mla": dict(world=2, kw=dict(tp=2, sp=False, mla=True)),
+    "tp2_pp2_ep2_mla_moe": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, mla=True, moe=True)),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
     "dp2_pp2_tp_pp_dp_mapping": dict(world=4, kw=dict(pp=2, extra_tc=dict(use_tp_pp_dp_mapping=True))),
     "tp2_pp2_ep2_tp_pp_dp_mapping": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, moe=True,
@@ -125,6 +128,9 @@ NORM_CASES = {
     "tp2_sp": dict(world=2, kw=dict(tp=2, sp=True)),
     "tp2_nosp": dict(world=2, kw=dict(tp=2, sp=False)),
     "tp2_pp2": dict(world=4, kw=dict(tp=2, pp=2, sp=True)),
+    # multi-latent attention: the down-projections are replicated as well
+    "tp2_sp_mla": dict(world=2, kw=dict(tp=2, sp=True, mla=True)),
+    "tp2_nosp_mla": dict(world=2, kw=dict(tp=2, sp=False, mla=True)),
     # whole-parameter optimizers: every expert-parallel rank owns different experts
     "ep2_moe_sgd": dict(world=2, kw=dict(ep=2, moe=True, opt="sgd", distopt=False)),
     "ep2_moe_adam": dict(world=2, kw=dict(ep=2, moe=True)),

@@ -79,6 +79,8 @@ def shard_spec(name: str, p: torch.Tensor, cfg, st) -> dict:
         return {"kind": "qkv", "axis": 0, "index": st.tp_rank, "count": st.tp}
     if name.endswith("linear_fc1.weight"):
         return {"kind": "glu", "axis": 0, "index": st.tp_rank, "count": st.tp}
+    if getattr(p, "tp_parts", None):     # several head-split blocks stacked on dim 0 (fused projections of the mixers)
+        return {"kind": "parts", "axis": 0, "index": st.tp_rank, "count": st.tp, "sizes": list(p.tp_parts)}
     return {"kind": "tp", "axis": int(getattr(p, "partition_dim", 0)), "index": st.tp_rank, "count": st.tp}
 
 
@@ -132,6 +134,12 @@ def assemble_global(name: str, shards: list[tuple[dict, torch.Tensor]]) -> torch
         return shards[0][1]
     by_idx = {s["index"]: t for s, t in shards}
     parts = [by_idx[i] for i in range(spec0["count"])]
+    if kind == "parts":  # every shard holds its slice of every block, blocks in order
+        n, blocks, lo = spec0["count"], [], 0
+        for size in spec0["sizes"]:
+            blocks += [p[lo:lo + size // n] for p in parts]
+            lo += size // n
+        return torch.cat(blocks, dim=0)
     if kind == "glu":  # every shard holds [gate_i; up_i]
         gates = [p[: p.shape[0] // 2] for p in parts]
         ups = [p[p.shape[0] // 2:] for p in parts]
@@ -143,6 +151,13 @@ def slice_global(name: str, full: torch.Tensor, spec: dict) -> torch.Tensor:
     kind, idx, n = spec["kind"], spec["index"], spec["count"]
     if kind == "replicated":
         return full
+    if kind == "parts":
+        out, off = [], 0
+        for size in spec["sizes"]:
+            w = size // n
+            out.append(full[off + idx * w: off + (idx + 1) * w])
+            off += size
+        return torch.cat(out, dim=0)
     if kind == "glu":
         half = full.shape[0] // 2
         c = half // n
@@ -217,6 +232,13 @@ def _segments(spec: dict, local_shape, cfg, tp: int, internal_qkv: bool) -> tupl
     ax = spec["axis"]
     g = list(shape)
     g[ax] = shape[ax] * n
+    if kind == "parts":
+        segs, loc, goff = [], 0, 0
+        for size in spec["sizes"]:
+            w = size // n
+            segs.append((0, loc, loc + w, goff + idx * w))
+            loc, goff = loc + w, goff + size
+        return tuple(g), segs
     if kind == "glu":
         h = shape[0] // 2
         return tuple(g), [(0, 0, h, idx * h), (0, h, 2 * h, n * h + idx * h)]

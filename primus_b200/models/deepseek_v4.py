@@ -35,7 +35,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import fused, gemm
+from ..ops import fused, gemm, layers
 from ..parallel import state as ps
 from .mixers import _param
 
@@ -57,6 +57,17 @@ def _flat_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)
 
 
+def _replicated_over_tp(module) -> None:
+    """Parameters every tensor-parallel rank holds whole but that see this rank's token shard only (sequence
+    parallelism): equal initial values, gradients added over the group."""
+    st = ps.get_state()
+    if st.tp > 1:
+        for p in module.parameters():
+            p.sequence_parallel = True
+            if p.dim() >= 2 and torch.distributed.is_initialized():
+                torch.distributed.broadcast(p.data, src=st.tp_ranks[0], group=st.tp_group)
+
+
 class HyperMixer(nn.Module):
     def __init__(self, hidden: int, K: int, eps: float, iters: int, device):
         super().__init__()
@@ -67,6 +78,7 @@ class HyperMixer(nn.Module):
             torch.empty(out, K * hidden, dtype=torch.float32, device=device).normal_(0.0, 1.0 / math.sqrt(K * hidden))))
         self.scale = nn.Parameter(torch.ones(3, dtype=torch.float32, device=device))
         self.base = nn.Parameter(torch.zeros(out, dtype=torch.float32, device=device))
+        _replicated_over_tp(self)
 
     def weights(self, x):
         """x [T, K, D] -> pre [T, K], post [T, K], comb [T, K, K] (fp32)."""
@@ -94,6 +106,7 @@ class HyperHead(nn.Module):
             torch.empty(K, K * hidden, dtype=torch.float32, device=device).normal_(0.0, 1.0 / math.sqrt(K * hidden))))
         self.scale = nn.Parameter(torch.ones((), dtype=torch.float32, device=device))
         self.base = nn.Parameter(torch.zeros(K, dtype=torch.float32, device=device))
+        _replicated_over_tp(self)
 
     def forward(self, x):
         w = torch.sigmoid(F.linear(_flat_rms(x, self.eps), self.fn.weight) * self.scale + self.base) + self.eps
@@ -262,10 +275,14 @@ def joint_attention(q, kv, sink, window: int, scale: float, pool=None, pool_mask
 class V4Attention(nn.Module):
     def __init__(self, cfg, layer_idx: int, device, tp: int):
         super().__init__()
-        assert tp == 1, "DeepSeek-V4 attention is not built for tensor parallelism"
-        self.cfg = cfg
+        # Tensor parallelism (with sequence parallelism) splits the query heads and, with them, the groups of the output
+        # projection; the shared latent, the query bottleneck, the compressor and the indexer are replicated
+        assert tp == 1 or cfg.sequence_parallel, "DeepSeek-V4 attention under tensor parallelism needs sequence_parallel"
+        assert cfg.num_attention_heads % tp == 0 and (not cfg.o_lora_rank or cfg.o_groups % tp == 0), \
+            "heads and output-projection groups must divide by the tensor-parallel size"
+        self.cfg, self.tp = cfg, tp
         h, dt, std = cfg.hidden_size, cfg.torch_dtype, cfg.init_method_std
-        self.nh, self.hd, self.dr = cfg.num_attention_heads, cfg.kv_channels, cfg.qk_pos_emb_head_dim
+        self.nh, self.hd, self.dr = cfg.num_attention_heads // tp, cfg.kv_channels, cfg.qk_pos_emb_head_dim
         self.ratio = int(cfg.compress_ratio_list[layer_idx])
         if self.ratio not in (0, 4, 128):
             raise ValueError(f"compress_ratios: 0 (local only), 4 (indexed) or 128 (pooled), got {self.ratio}")
@@ -289,7 +306,7 @@ class V4Attention(nn.Module):
         self.kv_layernorm = holder(weight=ones(self.hd))
         if cfg.attn_sink:
             self.attn_sink = nn.Parameter(torch.zeros(self.nh, dtype=torch.float32, device=device))
-        self.G, self.r = cfg.o_groups, cfg.o_lora_rank
+        self.G, self.r = cfg.o_groups // tp if cfg.o_lora_rank else cfg.o_groups, cfg.o_lora_rank
         if self.r:
             assert (self.nh * self.hd) % self.G == 0
             self.linear_o_a = holder(weight=_param((self.G * self.r, self.nh * self.hd // self.G), std, dt, device))
@@ -308,15 +325,48 @@ class V4Attention(nn.Module):
         if self.ratio == 4:
             self.indexer = Indexer(cfg, self.ratio, inv, self.dr, device)
         self.linear_kv.weight._is_weight = True
+        if tp > 1:
+            from .mixers import _mark_tp
+
+            _mark_tp(self.linear_q_up_proj.weight if cfg.q_lora_rank else self.linear_q_proj.weight, 0)
+            if cfg.attn_sink:
+                _mark_tp(self.attn_sink, 0)
+            if self.r:
+                _mark_tp(self.linear_o_a.weight, 0)
+                _mark_tp(self.linear_o_b.weight, 1)
+            else:
+                _mark_tp(self.linear_proj.weight, 1)
+            st = ps.get_state()
+            split = {id(p) for p in self.parameters() if getattr(p, "tensor_model_parallel", False)}
+            index_only = {id(p) for p in self.indexer.parameters()} if self.ratio == 4 else set()
+            for p in self.parameters():
+                if id(p) in split:
+                    continue
+                if torch.distributed.is_initialized():          # drawn per rank: make the replicas equal
+                    torch.distributed.broadcast(p.data, src=st.tp_ranks[0], group=st.tp_group)
+                # replicated parameters see this rank's tokens or heads only: their gradients are partial sums, added
+                # over the group -- except the indexer's, whose loss every rank computes in full
+                if id(p) not in index_only:
+                    p.sequence_parallel = True
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
-        assert ps.get_state().cp == 1, "DeepSeek-V4 attention is not built for context parallelism"
+        st = ps.get_state()
+        assert st.cp == 1, "DeepSeek-V4 attention is not built for context parallelism"
         if residual is not None:
             y, xsum = fused.rmsnorm(hidden, self.input_layernorm.weight, cfg.norm_epsilon, residual)
         else:
             y, xsum = fused.rmsnorm(hidden, self.input_layernorm.weight, cfg.norm_epsilon), hidden
-        T = y.shape[0]
+        tpg = st.tp_group if self.tp > 1 else None
+
+        def everywhere(t):          # all tokens on every rank; the backward pass adds the ranks' contributions
+            if tpg is None:
+                return t
+            from ..parallel import tensor_parallel as tpc
+
+            return tpc.gather_seq(t, tpg)
+
+        T = y.shape[0] * self.tp
         S = T // batch
         nh, hd, dr = self.nh, self.hd, self.dr
         pos = rope[2]
@@ -324,12 +374,14 @@ class V4Attention(nn.Module):
         if cfg.q_lora_rank:
             ql = fused.rmsnorm(gemm.linear(y, self.linear_q_down_proj.weight), self.linear_q_up_proj.layer_norm_weight,
                                cfg.norm_epsilon)
-            q = gemm.linear(ql, self.linear_q_up_proj.weight)
+            q = gemm.linear(everywhere(ql), self.linear_q_up_proj.weight)
         else:
-            q = gemm.linear(y, self.linear_q_proj.weight)
+            q = gemm.linear(everywhere(y), self.linear_q_proj.weight)
         q = q.view(batch, S, nh, hd).float()
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon)            # per head, no gain
-        kv = fused.rmsnorm(gemm.linear(y, self.linear_kv.weight), self.kv_layernorm.weight, cfg.norm_epsilon)
+        kv = everywhere(fused.rmsnorm(gemm.linear(y, self.linear_kv.weight), self.kv_layernorm.weight, cfg.norm_epsilon))
+        if self.ratio:
+            y = everywhere(y)               # the compressor and the indexer pool whole windows of tokens
         q = rope_interleaved(q, pos, self.inv_freq, dr)
         kv = rope_interleaved(kv.view(batch, S, 1, hd), pos, self.inv_freq, dr)[:, :, 0]
         extra = {}
@@ -355,7 +407,10 @@ class V4Attention(nn.Module):
             if distill:
                 from .moe import AuxLossScaler
 
-                aux = cfg.v4_indexer_distill_loss_coeff * indexer_distill_loss(index_scores, picked_probs, ok)
+                mass = picked_probs.detach().sum(1, keepdim=True)       # over this rank's heads ...
+                if tpg is not None:
+                    torch.distributed.all_reduce(mass, group=tpg)       # ... and over all of them
+                aux = cfg.v4_indexer_distill_loss_coeff * indexer_distill_loss(index_scores, mass, ok)
                 self.last_distill_loss = aux.detach()
                 out = AuxLossScaler.apply(out, aux)
         out = out.permute(0, 2, 1, 3)                                                       # [B, S, H, hd]
@@ -366,8 +421,9 @@ class V4Attention(nn.Module):
             g = out.reshape(T, self.G, nh * hd // self.G)
             wa = self.linear_o_a.weight.view(self.G, self.r, nh * hd // self.G)
             low = torch.einsum("tgd,grd->tgr", g, wa).reshape(T, self.G * self.r)
-            return gemm.linear(low.contiguous(), self.linear_o_b.weight), xsum
-        return gemm.linear(out.reshape(T, nh * hd).contiguous(), self.linear_proj.weight), xsum
+            return layers.row_parallel_linear(low.contiguous(), self.linear_o_b.weight, tpg, tpg is not None), xsum
+        return layers.row_parallel_linear(out.reshape(T, nh * hd).contiguous(), self.linear_proj.weight, tpg,
+                                          tpg is not None), xsum
 
 
 # ------------------------------------------------------------------------------------------------ hash router

@@ -131,16 +131,18 @@ def kda_chunked(q, k, v, g, beta, chunk: int = 64, scale=None, sub: int = SUB):
 class KimiDeltaAttentionMixer(nn.Module):
     """``q, k, v = silu(causal_conv(proj(h)))`` (q, k L2-normalised); log-decay from a rank-``dk`` bottleneck
     ``f_b(f_a(h))``; ``beta = sigmoid(b(h))``; the recurrence; per-head RMSNorm gated by ``sigmoid(g(h))``; ``o_proj``.
-    The six projections that read the layer input are one GEMM (``in_proj``, rows ``[q | k | v | g | f_a | b]``) and the
-    three depthwise convolutions one convolution over the concatenated channels."""
+    The per-head projections that read the layer input are one GEMM (``in_proj``, rows ``[q | k | v | g | b]``), the
+    bottlenecks every head shares another (``in_proj_shared``), and the three depthwise convolutions one convolution over
+    the concatenated channels.  Tensor parallelism (with sequence parallelism) splits the heads."""
 
     def __init__(self, cfg, layer_idx: int, device, tp: int):
         super().__init__()
-        assert tp == 1, "the Kimi-delta-attention mixer is not built for tensor parallelism"
+        assert tp == 1 or cfg.sequence_parallel, "Kimi delta attention under tensor parallelism needs sequence_parallel"
         assert cfg.linear_num_key_heads == cfg.linear_num_value_heads, "Kimi delta attention: as many key as value heads"
-        self.cfg = cfg
+        assert cfg.linear_num_value_heads % tp == 0, "heads must divide by the tensor-parallel size"
+        self.cfg, self.tp = cfg, tp
         h, dt = cfg.hidden_size, cfg.torch_dtype
-        self.nh, self.dk, self.dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.nh, self.dk, self.dv = cfg.linear_num_value_heads // tp, cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.qk_dim, self.v_dim = self.nh * self.dk, self.nh * self.dv
         self.conv_dim = 2 * self.qk_dim + self.v_dim
         std = cfg.init_method_std
@@ -150,9 +152,14 @@ class KimiDeltaAttentionMixer(nn.Module):
         # forget gate (Kimi Linear, the delta-attention stacks of the hybrid presets:
         # primus/backends/megatron/core/models/hybrid/kimi_delta_attention.py:278-311,397-410 in the reference)
         self.full_gate = bool(cfg.kda_use_full_rank_gate)
-        self.gate_in = self.v_dim if self.full_gate else self.dv
         self.fa = self.dk if self.full_gate else self.dv
-        self.in_proj.register_parameter("weight", _param((self.conv_dim + self.gate_in + self.fa + self.nh, h), std, dt, device))
+        # per-head rows [q | k | v | (g) | b] and, apart from them, the rows every head shares: the bottleneck of the
+        # forget gate (and of the output gate); under tensor parallelism the first are split by heads, the second replicated
+        self.head_rows = self.conv_dim + (self.v_dim if self.full_gate else 0) + self.nh
+        self.shared_rows = self.fa + (0 if self.full_gate else self.dv)
+        self.in_proj.register_parameter("weight", _param((self.head_rows, h), std, dt, device))
+        self.in_proj_shared = nn.Module()
+        self.in_proj_shared.register_parameter("weight", _param((self.shared_rows, h), std, dt, device))
         self.conv1d = nn.Module()
         self.conv1d.register_parameter("weight", _param((self.conv_dim, 1, cfg.linear_conv_kernel_dim), std * 5, dt, device))
         self.f_b_proj = nn.Module()
@@ -172,22 +179,44 @@ class KimiDeltaAttentionMixer(nn.Module):
         self.out_proj.register_parameter("weight", _param((h, self.v_dim), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
         for w in (self.in_proj.weight, self.out_proj.weight, self.f_b_proj.weight):
             w._is_weight = True
+        if tp > 1:
+            from .mixers import _mark_tp
+
+            QK, V, NH = self.qk_dim * tp, self.v_dim * tp, self.nh * tp
+            _mark_tp(self.in_proj.weight, 0, [QK, QK, V] + ([V] if self.full_gate else []) + [NH])
+            _mark_tp(self.conv1d.weight, 0, [QK, QK, V])
+            _mark_tp(self.f_b_proj.weight, 0)
+            if not self.full_gate:
+                _mark_tp(self.g_b_proj.weight, 0)
+            _mark_tp(self.dt_bias, 0)
+            _mark_tp(self.A_log, 0)
+            _mark_tp(self.out_proj.weight, 1)
+            st = ps.get_state()
+            for w in (self.in_proj.layer_norm_weight, self.out_norm.weight, self.in_proj_shared.weight):
+                w.sequence_parallel = True          # replicated, gradients are partial sums: added over the group
+            if torch.distributed.is_initialized():
+                torch.distributed.broadcast(self.in_proj_shared.weight.data, src=st.tp_ranks[0], group=st.tp_group)
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
-        assert ps.get_state().cp == 1, "the Kimi-delta-attention mixer is not built for context parallelism"
+        st = ps.get_state()
+        assert st.cp == 1, "the Kimi-delta-attention mixer is not built for context parallelism"
         y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        if self.tp > 1:
+            from ..parallel import tensor_parallel as tpc
+
+            y = tpc.gather_seq(y, st.tp_group)
         proj = gemm.linear(y, self.in_proj.weight)
+        shared = gemm.linear(y, self.in_proj_shared.weight)
         T = proj.shape[0]
         seq = T // batch
         cd, vd, nh, dk = self.conv_dim, self.v_dim, self.nh, self.dk
         qkv = F.silu(causal_depthwise_conv(proj[:, :cd], self.conv1d.weight[:, 0, :], None, batch))
-        gi, fa = self.gate_in, self.fa
-        gate = proj[:, cd:cd + gi]
-        if not self.full_gate:
-            gate = gemm.linear(gate.contiguous(), self.g_b_proj.weight)
-        f_a = proj[:, cd + gi:cd + gi + fa].contiguous()
-        b_ = proj[:, cd + gi + fa:]
+        f_a = shared[:, :self.fa].contiguous()
+        if self.full_gate:
+            gate, b_ = proj[:, cd:cd + vd], proj[:, cd + vd:]
+        else:
+            gate, b_ = gemm.linear(shared[:, self.fa:].contiguous(), self.g_b_proj.weight), proj[:, cd:]
         q = F.normalize(qkv[:, :self.qk_dim].float().view(batch, seq, nh, dk), dim=-1, eps=1e-6)
         k = F.normalize(qkv[:, self.qk_dim:2 * self.qk_dim].float().view(batch, seq, nh, dk), dim=-1, eps=1e-6)
         v = qkv[:, 2 * self.qk_dim:].view(batch, seq, nh, self.dv)
@@ -197,6 +226,10 @@ class KimiDeltaAttentionMixer(nn.Module):
         o = kda_chunked(q, k, v, g, beta, cfg.kda_chunk_size)
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon) * self.out_norm.weight.float()
         o = (o.reshape(T, vd) * torch.sigmoid(gate.float())).to(hidden.dtype)
+        if self.tp > 1:
+            from ..ops import layers
+
+            return layers.row_parallel_linear(o.contiguous(), self.out_proj.weight, st.tp_group, True), xsum
         return gemm.linear(o.contiguous(), self.out_proj.weight), xsum
 
 

@@ -15,8 +15,11 @@ explicit formulas (they are also the CPU path and the test oracle).
   the reference's Mamba and hybrid stacks (primus/backends/megatron/core/models/mamba/mamba_layer_specs.py,
   primus/backends/megatron/core/models/hybrid/hybrid_block.py, presets ``mamba_370M`` and ``zebra_llama_*``).
 
-Tensor and context parallelism are not built for these mixers (they assert ``tp == cp == 1``); pipeline, data and
-expert parallelism work as for any layer.
+Tensor parallelism splits the heads of the Mamba-2 and gated-delta-net mixers (together with sequence parallelism: the
+mixer gathers the normalised tokens, works on its own heads and reduce-scatters its output projection; fused projections
+are marked with the sizes of their blocks so that checkpoints re-tile them); the short convolution and context
+parallelism are not built (``tp == 1`` / ``cp == 1`` asserted); pipeline, data and expert parallelism work as for any
+layer.
 """
 from __future__ import annotations
 
@@ -26,8 +29,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import fused, gemm
+from ..ops import fused, gemm, layers
 from ..parallel import state as ps
+from ..parallel import tensor_parallel as tpc
 
 
 def _param(shape, std, dtype, device):
@@ -37,6 +41,14 @@ def _param(shape, std, dtype, device):
     else:
         nn.init.zeros_(p)
     return p
+
+
+def _mark_tp(p, dim: int, parts=None):
+    """Head-split parameter: ``parts`` lists the global sizes of the blocks stacked on dim 0 when there are several
+    (every rank holds its heads' slice of each block; the checkpoint code re-tiles them)."""
+    p.tensor_model_parallel, p.partition_dim = True, dim
+    if parts:
+        p.tp_parts = list(parts)
 
 
 def _norm(hidden, residual, weight, eps):
@@ -165,15 +177,18 @@ class Mamba2Mixer(nn.Module):
 
     def __init__(self, cfg, layer_idx: int, device, tp: int):
         super().__init__()
-        assert tp == 1, "the Mamba mixer is not built for tensor parallelism"
-        self.cfg = cfg
+        # Tensor parallelism splits the heads and the B / C groups (needs sequence parallelism, like the other mixers)
+        assert tp == 1 or cfg.sequence_parallel, "the Mamba mixer under tensor parallelism needs sequence_parallel"
+        self.cfg, self.tp = cfg, tp
         h, dt = cfg.hidden_size, cfg.torch_dtype
-        self.d_inner = cfg.mamba_expand * h
+        d_inner = cfg.mamba_expand * h
         self.headdim = cfg.mamba_head_dim
-        self.nheads = cfg.mamba_num_heads or self.d_inner // self.headdim
-        assert self.nheads * self.headdim == self.d_inner, "mamba_expand * hidden_size must equal heads * head_dim"
-        self.ngroups, self.d_state = cfg.mamba_num_groups, cfg.mamba_state_dim
-        assert self.nheads % self.ngroups == 0
+        nheads = cfg.mamba_num_heads or d_inner // self.headdim
+        assert nheads * self.headdim == d_inner, "mamba_expand * hidden_size must equal heads * head_dim"
+        assert nheads % cfg.mamba_num_groups == 0
+        assert nheads % tp == 0 and cfg.mamba_num_groups % tp == 0, "heads and groups must divide by tp"
+        self.d_inner, self.nheads = d_inner // tp, nheads // tp                 # this rank's share
+        self.ngroups, self.d_state = cfg.mamba_num_groups // tp, cfg.mamba_state_dim
         self.conv_dim = self.d_inner + 2 * self.ngroups * self.d_state
         std = cfg.init_method_std
         self.in_proj = nn.Module()
@@ -197,11 +212,23 @@ class Mamba2Mixer(nn.Module):
             w._is_weight = True
         for p in (self.dt_bias, self.A_log, self.D):
             p._no_weight_decay = True
+        if tp > 1:
+            DI, GN, NH = self.d_inner * tp, self.ngroups * self.d_state * tp, self.nheads * tp
+            _mark_tp(self.in_proj.weight, 0, [DI, DI, GN, GN, NH])
+            _mark_tp(self.conv1d.weight, 0, [DI, GN, GN])
+            _mark_tp(self.conv1d.bias, 0, [DI, GN, GN])
+            for p in (self.dt_bias, self.A_log, self.D, self.norm.weight):
+                _mark_tp(p, 0)
+            _mark_tp(self.out_proj.weight, 1)
+            self.in_proj.layer_norm_weight.sequence_parallel = True
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
-        assert ps.get_state().cp == 1, "the Mamba mixer is not built for context parallelism"
+        st = ps.get_state()
+        assert st.cp == 1, "the Mamba mixer is not built for context parallelism"
         y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        if self.tp > 1:
+            y = tpc.gather_seq(y, st.tp_group)
         zxbcdt = gemm.linear(y, self.in_proj.weight)
         T = zxbcdt.shape[0]
         seq = T // batch
@@ -220,6 +247,8 @@ class Mamba2Mixer(nn.Module):
         gated = (yss * F.silu(z.float())).view(T, self.ngroups, di // self.ngroups)
         gated = gated * torch.rsqrt(gated.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon)
         out = (gated.view(T, di) * self.norm.weight.float()).to(hidden.dtype)
+        if self.tp > 1:
+            return layers.row_parallel_linear(out.contiguous(), self.out_proj.weight, st.tp_group, True), xsum
         return gemm.linear(out.contiguous(), self.out_proj.weight), xsum
 
 
@@ -297,10 +326,13 @@ class GatedDeltaNetMixer(nn.Module):
 
     def __init__(self, cfg, layer_idx: int, device, tp: int):
         super().__init__()
-        assert tp == 1, "the gated-delta-net mixer is not built for tensor parallelism"
-        self.cfg = cfg
+        # Tensor parallelism splits the heads (needs sequence parallelism: the mixer gathers the normalised tokens,
+        # works on its own heads and reduce-scatters the output projection)
+        assert tp == 1 or cfg.sequence_parallel, "the gated-delta-net mixer under tensor parallelism needs sequence_parallel"
+        assert cfg.linear_num_key_heads % tp == 0 and cfg.linear_num_value_heads % tp == 0, "heads must divide by tp"
+        self.cfg, self.tp = cfg, tp
         h, dt = cfg.hidden_size, cfg.torch_dtype
-        self.nk, self.nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.nk, self.nv = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp      # this rank's heads
         self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         assert self.nv % self.nk == 0
         self.qk_dim, self.v_dim = self.nk * self.dk, self.nv * self.dv
@@ -321,11 +353,24 @@ class GatedDeltaNetMixer(nn.Module):
         self.out_proj.register_parameter("weight", _param((h, self.v_dim), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
         for w in (self.in_proj.weight, self.out_proj.weight):
             w._is_weight = True
+        if tp > 1:
+            QK, V, NV = self.qk_dim * tp, self.v_dim * tp, self.nv * tp
+            _mark_tp(self.in_proj.weight, 0, [QK, QK, V, V, NV, NV])
+            _mark_tp(self.conv1d.weight, 0, [QK, QK, V])
+            _mark_tp(self.dt_bias, 0)
+            _mark_tp(self.A_log, 0)
+            _mark_tp(self.out_proj.weight, 1)
+            # replicated; their gradients are partial sums (over this rank's tokens / heads): added over the group
+            self.in_proj.layer_norm_weight.sequence_parallel = True
+            self.out_norm.weight.sequence_parallel = True
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
-        assert ps.get_state().cp == 1, "the gated-delta-net mixer is not built for context parallelism"
+        st = ps.get_state()
+        assert st.cp == 1, "the gated-delta-net mixer is not built for context parallelism"
         y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        if self.tp > 1:
+            y = tpc.gather_seq(y, st.tp_group)
         proj = gemm.linear(y, self.in_proj.weight)
         T = proj.shape[0]
         seq = T // batch
@@ -345,4 +390,6 @@ class GatedDeltaNetMixer(nn.Module):
         o = gated_delta_rule_chunked(q, k, v, g, beta, cfg.linear_chunk_size)            # [b, l, nv, dv] fp32
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.norm_epsilon) * self.out_norm.weight.float()
         o = (o.reshape(T, vd) * F.silu(z.float())).to(hidden.dtype)
+        if self.tp > 1:
+            return layers.row_parallel_linear(o.contiguous(), self.out_proj.weight, st.tp_group, True), xsum
         return gemm.linear(o.contiguous(), self.out_proj.weight), xsum

@@ -133,10 +133,13 @@ class MoELayer(nn.Module):
         bias = getattr(self.router, "expert_bias", None)
         fixed = None
         if hasattr(self.router, "tid2eid"):
-            if TOKEN_IDS.current is None or TOKEN_IDS.current.numel() != y.shape[0]:
-                raise RuntimeError("hash-routed MoE layer: the token ids of the micro-batch are not available "
-                                   "(pipeline stages after the first and sequence-parallel shards do not have them)")
-            fixed = self.router.tid2eid[TOKEN_IDS.current.long()]
+            ids = TOKEN_IDS.current
+            st_ = ps.get_state()
+            if ids is not None and st_.tp > 1 and ids.numel() == y.shape[0] * st_.tp:
+                ids = ids.reshape(-1)[st_.tp_rank * y.shape[0]:(st_.tp_rank + 1) * y.shape[0]]   # this rank's sequence shard
+            if ids is None or ids.numel() != y.shape[0]:
+                raise RuntimeError("hash-routed MoE layer: the token ids of the micro-batch are not available")
+            fixed = self.router.tid2eid[ids.long()]
         probs, idx, full, counts = moe_ops.router_scores(
             logits, cfg.moe_router_topk, cfg.moe_router_score_function, cfg.moe_router_pre_softmax, bias,
             cfg.moe_router_topk_scaling_factor, cfg.moe_router_num_groups, cfg.moe_router_group_topk,

@@ -113,6 +113,26 @@ def test_load_tp1_mla_checkpoint_into_tp2(tmp_path):
         assert abs(x - y) <= 2e-3 * max(1.0, abs(y)), (got, ref)
 
 
+def test_load_tp1_delta_net_checkpoint_into_tp2(tmp_path):
+    """Head-split mixers keep several blocks in one fused weight: a tp = 1 checkpoint is re-tiled block by block (weights
+    and optimizer state) for tp = 2."""
+    kw = dict(layers=4, extra_mc=dict(
+        model_type="kimi_k3", q_lora_rank=32, kv_lora_rank=24, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16,
+        mla_use_output_gate=True, linear_attention_freq="[1, 0, 1, 0]", linear_num_key_heads=4, linear_num_value_heads=4,
+        linear_key_head_dim=16, linear_value_head_dim=16, kda_chunk_size=16, attn_res_block_size=2))
+    root = str(tmp_path / "ckpt")
+    a = _trainer(iters=4, **kw)
+    a.tcfg.use_distributed_optimizer = True
+    a.train(2)
+    a.save_checkpoint(root)
+    ref = a.train(2)
+    outp = str(tmp_path / "l.json")
+    run_ranks(_reshard_worker, 2, "gloo", args=(root, outp, kw), timeout=200)
+    got = json.load(open(outp))
+    for x, y in zip(got, ref):
+        assert abs(x - y) <= 2e-3 * max(1.0, abs(y)), (got, ref)
+
+
 def _fsdp_ckpt_worker(rank, world, root, outp):
     import json as _json
 

@@ -47,6 +47,31 @@ CASES = {
     "tp2_sp_mla": dict(world=2, kw=dict(tp=2, sp=True, mla=True)),
     "tp2_nosp_mla": dict(world=2, kw=dict(tp=2, sp=False, mla=True)),
     "tp2_pp2_ep2_mla_moe": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, mla=True, moe=True)),
+    # head-split gated-delta-net / Kimi-delta-attention mixers (fused projections re-tiled block by block)
+    "tp2_sp_qwen3_5": dict(world=2, kw=dict(tp=2, sp=True, layers=4, extra_mc=dict(
+        experimental_attention_variant="gated_delta_net", linear_attention_freq=2, linear_num_key_heads=2,
+        linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_chunk_size=16,
+        attention_output_gate=True, apply_layernorm_1p=True, rotary_percent=0.5, qk_layernorm=True))),
+    "tp2_sp_pp2_kimi_k3": dict(world=4, kw=dict(tp=2, sp=True, pp=2, layers=6, extra_mc=dict(
+        model_type="kimi_k3", q_lora_rank=32, kv_lora_rank=24, qk_head_dim=16, qk_pos_emb_head_dim=8, v_head_dim=16,
+        mla_use_output_gate=True, linear_attention_freq="([1]*2+[0])*2", linear_num_key_heads=4, linear_num_value_heads=4,
+        linear_key_head_dim=16, linear_value_head_dim=16, kda_chunk_size=16, attn_res_block_size=2, num_experts=4,
+        moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq="([0]*1+[1]*5)", moe_shared_expert_intermediate_size=32,
+        routed_expert_hidden_size=32, moe_router_score_function="sigmoid", gated_activation="situ"))),
+    "tp2_sp_kda_hybrid": dict(world=2, kw=dict(tp=2, sp=True, layers=4, extra_mc=dict(
+        model_type="mamba", is_hybrid_model=True, linear_attention_type="kda", linear_num_key_heads=4,
+        linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=16, kda_use_full_rank_gate=False,
+        kda_gate_lower_bound=None, kda_chunk_size=16))),
+    "tp2_sp_mamba_hybrid": dict(world=2, kw=dict(tp=2, sp=True, layers=6, extra_mc=dict(
+        model_type="mamba", is_hybrid_model=True, hybrid_attention_ratio=0.34, mamba_state_dim=16, mamba_head_dim=16,
+        mamba_num_groups=2, mamba_chunk_size=16))),
+    "tp2_sp_pp2_deepseek_v4": dict(world=4, kw=dict(tp=2, sp=True, pp=2, layers=4, seq=128, extra_mc=dict(
+        model_type="deepseek_v4", num_query_groups=1, kv_channels=32, qk_pos_emb_head_dim=8, q_lora_rank=32, o_lora_rank=16,
+        o_groups=2, hc_mult=3, hc_sinkhorn_iters=6, compress_ratios="[0, 4, 128, 4]", compress_rope_theta=40000.0,
+        index_topk=4, index_head_dim=16, index_n_heads=2, attn_sliding_window=8, num_experts=4, moe_router_topk=2,
+        moe_ffn_hidden_size=32, moe_layer_freq=1, moe_shared_expert_intermediate_size=32,
+        moe_router_score_function="sqrtsoftplus", activation_func_clamp_value=10.0, v4_indexer_distill_loss_coeff=0.1,
+        num_hash_layers=3))),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
     "dp2_pp2_tp_pp_dp_mapping": dict(world=4, kw=dict(pp=2, extra_tc=dict(use_tp_pp_dp_mapping=True))),
     "tp2_pp2_ep2_tp_pp_dp_mapping": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, moe=True,
@@ -131,6 +156,10 @@ NORM_CASES = {
     # multi-latent attention: the down-projections are replicated as well
     "tp2_sp_mla": dict(world=2, kw=dict(tp=2, sp=True, mla=True)),
     "tp2_nosp_mla": dict(world=2, kw=dict(tp=2, sp=False, mla=True)),
+    "tp2_sp_kda_hybrid": dict(world=2, kw=dict(tp=2, sp=True, layers=4, extra_mc=dict(
+        model_type="mamba", is_hybrid_model=True, linear_attention_type="kda", linear_num_key_heads=4,
+        linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=16, kda_use_full_rank_gate=False,
+        kda_gate_lower_bound=None, kda_chunk_size=16))),
     # whole-parameter optimizers: every expert-parallel rank owns different experts
     "ep2_moe_sgd": dict(world=2, kw=dict(ep=2, moe=True, opt="sgd", distopt=False)),
     "ep2_moe_adam": dict(world=2, kw=dict(ep=2, moe=True)),

@@ -197,7 +197,7 @@ class TransformerConfig:
             self.kv_channels = self.hidden_size // self.num_attention_heads
         if self.moe_ffn_hidden_size is None:
             self.moe_ffn_hidden_size = self.ffn_hidden_size
-        self.compress_ratio_list = None
+        self.compress_ratio_list, self.compress_ratio_mtp = None, []
         if self.model_type == "deepseek_v4":
             r = self.compress_ratios
             if isinstance(r, str):
@@ -205,6 +205,7 @@ class TransformerConfig:
             self.compress_ratio_list = [0] * self.num_layers if r is None else [int(x) for x in r]
             # the published lists carry one more entry per multi-token-prediction depth behind the decoder layers
             if len(self.compress_ratio_list) > self.num_layers:
+                self.compress_ratio_mtp = self.compress_ratio_list[self.num_layers:]
                 self.compress_ratio_list = self.compress_ratio_list[:self.num_layers]
             if len(self.compress_ratio_list) != self.num_layers:
                 raise ValueError(f"compress_ratios has {len(self.compress_ratio_list)} entries for {self.num_layers} layers")

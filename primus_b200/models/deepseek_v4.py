@@ -273,7 +273,7 @@ def joint_attention(q, kv, sink, window: int, scale: float, pool=None, pool_mask
 
 
 class V4Attention(nn.Module):
-    def __init__(self, cfg, layer_idx: int, device, tp: int):
+    def __init__(self, cfg, layer_idx: int, device, tp: int, mtp_depth=None):
         super().__init__()
         # Tensor parallelism (with sequence parallelism) splits the query heads and, with them, the groups of the output
         # projection; the shared latent, the query bottleneck, the compressor and the indexer are replicated
@@ -284,6 +284,8 @@ class V4Attention(nn.Module):
         h, dt, std = cfg.hidden_size, cfg.torch_dtype, cfg.init_method_std
         self.nh, self.hd, self.dr = cfg.num_attention_heads // tp, cfg.kv_channels, cfg.qk_pos_emb_head_dim
         self.ratio = int(cfg.compress_ratio_list[layer_idx])
+        if mtp_depth is not None and mtp_depth < len(cfg.compress_ratio_mtp):
+            self.ratio = int(cfg.compress_ratio_mtp[mtp_depth])      # the entries behind the decoder layers
         if self.ratio not in (0, 4, 128):
             raise ValueError(f"compress_ratios: 0 (local only), 4 (indexed) or 128 (pooled), got {self.ratio}")
         out_std = std / math.sqrt(2.0 * cfg.num_layers)

@@ -211,7 +211,10 @@ class TransformerLayer(nn.Module):
     layers of a hybrid stack) followed by an MLP / MoE block (absent in the single-sub-layer layers of Mamba / hybrid
     stacks).  The kinds come from ``TransformerConfig.layer_kinds``."""
 
-    def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int):
+    def __init__(self, cfg: TransformerConfig, layer_idx: int, device, tp: int, mtp_depth: Optional[int] = None):
+        """``mtp_depth`` (0-based): the layer is the inner layer of a multi-token-prediction depth, built like decoder
+        layer ``layer_idx`` but without attention residuals (there are no checkpoints to mix behind the stack) and, in
+        the DeepSeek-V4 family, with the compression ratio the preset lists for that depth."""
         super().__init__()
         self.cfg = cfg
         self.layer_idx = layer_idx
@@ -242,7 +245,7 @@ class TransformerLayer(nn.Module):
         elif self.mixer_kind == "v4":
             from .deepseek_v4 import V4Attention
 
-            self.self_attention = V4Attention(cfg, layer_idx, device, tp)
+            self.self_attention = V4Attention(cfg, layer_idx, device, tp, mtp_depth)
         # hyper-connections (DeepSeek-V4): the residual stream is ``hc_mult`` parallel streams [T, K, H]; every sub-layer
         # reads a learned mixture of them and writes back through learned weights (models/deepseek_v4.py)
         self.hyper = cfg.hc_mult > 1
@@ -254,7 +257,7 @@ class TransformerLayer(nn.Module):
             self.ffn_hc = HyperMixer(cfg.hidden_size, cfg.hc_mult, cfg.hc_eps, cfg.hc_sinkhorn_iters, device)
         # attention residuals (Kimi-K3): the sub-layers read a learned mixture of the running stream and the checkpoints
         # that every ``attn_res_block_size``-th layer sets aside; the checkpoints travel in the ``residual`` slot
-        self.attn_res = bool(cfg.attn_res_block_size)
+        self.attn_res = bool(cfg.attn_res_block_size) and mtp_depth is None
         if self.attn_res:
             from .kimi_k3 import AttentionResidualMixer, checkpoints_before
 
@@ -387,13 +390,20 @@ class MultiTokenPredictionLayer(nn.Module):
     transformer layer; the shared output head then predicts the token after that.  Parameter names follow mcore:
     ``mtp.layers.{k}.{enorm,hnorm,eh_proj,transformer_layer.*,final_layernorm}``."""
 
-    def __init__(self, cfg: TransformerConfig, device, tp: int):
+    def __init__(self, cfg: TransformerConfig, device, tp: int, depth: int = 0):
         super().__init__()
         h = cfg.hidden_size
         self.enorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
         self.hnorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
         self.eh_proj = ParamHolder(weight=_param((h, 2 * h), cfg.init_method_std, cfg.torch_dtype, device))
-        self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device, tp)
+        self.transformer_layer = TransformerLayer(cfg, cfg.num_layers - 1, device, tp, mtp_depth=depth)
+        if cfg.hc_mult > 1:
+            # hyper-connections: the projected input is copied into the streams, the inner layer mixes them, and every
+            # depth collapses them with a head of its own (the reference's per-depth ``hc_head_fn``:
+            # primus/backends/megatron/core/models/deepseek_v4/deepseek_v4_mtp_layer.py:10-22)
+            from .deepseek_v4 import HyperHead
+
+            self.hc_head = HyperHead(h, cfg.hc_mult, cfg.hc_eps, device)
         self.final_layernorm = ParamHolder(weight=_param((h,), 0, cfg.torch_dtype, device, True))
         # replicated over the tensor-parallel ranks; under sequence parallelism each rank sees its token shard only, so
         # their gradients are summed over the group like those of the other norm weights
@@ -442,14 +452,9 @@ class GPTModel(nn.Module):
             if st.cp > 1:
                 raise NotImplementedError("multi-token prediction is not built for context parallelism")
             self.mtp = nn.Module()
-            self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp)
-                                             for _ in range(cfg.mtp_num_layers)])
+            self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp, depth)
+                                             for depth in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
-        if cfg.model_type == "deepseek_v4" and cfg.mtp_num_layers:
-            raise NotImplementedError("multi-token prediction is not built for the DeepSeek-V4 family: set mtp_num_layers "
-                                      "to 0")
-        if cfg.attn_res_block_size and cfg.mtp_num_layers:
-            raise NotImplementedError("attention residuals together with multi-token prediction are not built")
         fused.set_situ_betas(cfg.activation_situ_beta, cfg.activation_situ_linear_beta)
         fused.set_zero_centered_gamma(cfg.apply_layernorm_1p)
         if cfg.apply_layernorm_1p:
@@ -600,7 +605,11 @@ class GPTModel(nn.Module):
             x = torch.cat([fused.rmsnorm(e, layer.enorm.weight, cfg.norm_epsilon),
                            fused.rmsnorm(h, layer.hnorm.weight, cfg.norm_epsilon)], -1)
             x = gemm.linear(x, layer.eh_proj.weight)
+            if cfg.hc_mult > 1:
+                x = x[:, None, :].expand(-1, cfg.hc_mult, -1).contiguous()
             hid, res = layer.transformer_layer(x, None, rope, batch)
+            if cfg.hc_mult > 1:
+                hid, res = layer.hc_head(hid), None
             logits, _ = layers.norm_linear(hid, res, layer.final_layernorm.weight, w_out, cfg.norm_epsilon,
                                            st.tp_group, sp)
             logits = fused.softcap(logits, cfg.final_logit_softcapping)

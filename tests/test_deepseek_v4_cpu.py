@@ -279,3 +279,29 @@ def test_presets_resolve():
     assert 280e9 < flash.num_parameters() < 290e9
     pro = TransformerConfig.from_dict(load_preset("deepseek_v4_pro.yaml", "models", "primus_b200"))
     assert len(pro.compress_ratio_list) == 61 and pro.o_groups == 16 and pro.hc_mult == 4
+
+
+def test_multi_token_prediction_with_hyper_connections():
+    """Every depth copies its projected input into the streams, runs a layer of the family's kind (with the compression
+    ratio listed behind the decoder layers) and collapses the streams with a head of its own."""
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    torch.manual_seed(10)
+    cfg = _v4_cfg(compress_ratios="[0, 4, 128, 4, 128]", mtp_num_layers=1)
+    assert cfg.compress_ratio_list == [0, 4, 128, 4] and cfg.compress_ratio_mtp == [128]
+    m = GPTModel(cfg)
+    inner = m.mtp.layers[0].transformer_layer
+    assert inner.self_attention.ratio == 128 and inner.hyper and hasattr(m.mtp.layers[0], "hc_head")
+    tok = torch.randint(0, 256, (2, 128))
+    w = torch.full((2, 128), 1.0 / 256)
+    with_mtp = m(tok, tok, w)
+    cfg0 = _v4_cfg(compress_ratios="[0, 4, 128, 4, 128]")
+    torch.manual_seed(10)
+    plain = GPTModel(cfg0)(tok, tok, w)
+    assert float(with_mtp) > float(plain) > 0            # the depth adds its scaled loss on top of the same main loss
+    with_mtp.backward()
+    assert all(p.grad is not None for n, p in m.named_parameters() if n.startswith("mtp.") and ".indexer." not in n)
+    ps.destroy_model_parallel()

@@ -125,9 +125,9 @@ CASES = {
         moe_router_topk=2, moe_ffn_hidden_size=32, moe_layer_freq="([0]*1+[1]*5)", moe_shared_expert_intermediate_size=32,
         routed_expert_hidden_size=32, moe_router_score_function="sigmoid", gated_activation="situ"))),
     # DeepSeek-V4: the hyper-connection streams cross the stage boundary; hash-routed layers on both stages
-    "pp2_deepseek_v4": dict(world=2, kw=dict(pp=2, layers=4, seq=128, extra_mc=dict(
+    "pp2_deepseek_v4": dict(world=2, kw=dict(pp=2, layers=4, seq=128, mtp=1, extra_mc=dict(
         model_type="deepseek_v4", num_query_groups=1, kv_channels=32, qk_pos_emb_head_dim=8, q_lora_rank=32, o_lora_rank=16,
-        o_groups=2, hc_mult=3, hc_sinkhorn_iters=6, compress_ratios="[0, 4, 128, 4]", compress_rope_theta=40000.0,
+        o_groups=2, hc_mult=3, hc_sinkhorn_iters=6, compress_ratios="[0, 4, 128, 4, 0]", compress_rope_theta=40000.0,
         index_topk=4, index_head_dim=16, index_n_heads=2, attn_sliding_window=8, num_experts=4, moe_router_topk=2,
         moe_ffn_hidden_size=32, moe_layer_freq=1, moe_shared_expert_intermediate_size=32,
         moe_router_score_function="sqrtsoftplus", num_hash_layers=3, activation_func_clamp_value=10.0))),

@@ -273,3 +273,20 @@ def test_delta_attention_stack_of_the_hybrid_presets():
     loss.backward()
     assert math.isfinite(float(loss)) and all(p.grad is not None for p in m.parameters())
     ps.destroy_model_parallel()
+
+
+def test_multi_token_prediction_layer_has_no_attention_residuals():
+    from primus_b200.models.gpt import GPTModel
+    from primus_b200.parallel import state as ps
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    torch.manual_seed(12)
+    m = GPTModel(_k3_cfg(mtp_num_layers=1))
+    inner = m.mtp.layers[0].transformer_layer
+    assert not inner.attn_res and not hasattr(inner, "mlp_res_mixer") and m.decoder.layers["5"].attn_res
+    tok = torch.randint(0, 256, (2, 64))
+    loss = m(tok, tok, torch.full((2, 64), 1.0 / 128))
+    loss.backward()
+    assert math.isfinite(float(loss)) and all(p.grad is not None for n, p in m.named_parameters() if n.startswith("mtp."))
+    ps.destroy_model_parallel()

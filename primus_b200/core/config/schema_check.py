@@ -16,7 +16,7 @@ from typing import Iterable
 from .presets import load_preset
 
 # keys consumed outside the two config dataclasses (launcher, patches, logging, optional features)
-EXTRA_KNOWN = {"trainer_class", "tp_comm_overlap", "tp_comm_overlap_rs", "pp_algorithm", "stage", "framework", "disable_wandb",
+EXTRA_KNOWN = {"train_samples", "lr_warmup_samples", "lr_decay_samples", "trainer_class", "tp_comm_overlap", "tp_comm_overlap_rs", "pp_algorithm", "stage", "framework", "disable_wandb",
                "disable_tensorboard", "disable_mlflow", "valid_data_path"}
 
 

@@ -49,7 +49,27 @@ class PretrainTrainer(BaseTrainer):
         logutil.log_rank_0(f"model parameters: {mcfg.num_parameters() / 1e9:.3f} B; "
                            f"dp={ps.dp_size()} tp={ps.tp_size()} pp={ps.pp_size()} ep={ps.ep_size()}")
 
+    def convert_checkpoint(self) -> str:
+        """``ckpt_convert_format`` / ``ckpt_convert_save``: the loaded state written in the other checkpoint format."""
+        tc = self.engine.tcfg
+        if not tc.load or not tc.ckpt_convert_save:
+            raise ValueError("ckpt_convert_format needs load (the checkpoint to read) and ckpt_convert_save (where to write)")
+        was = tc.ckpt_format
+        tc.ckpt_format = tc.ckpt_convert_format
+        try:
+            d = self.engine.save_checkpoint(tc.ckpt_convert_save)
+        finally:
+            tc.ckpt_format = was
+        logutil.log_rank_0(f"converted the checkpoint of iteration {self.engine.iteration} from {tc.load} to "
+                           f"{tc.ckpt_convert_format} format in {d}")
+        return d
+
     def train(self):
+        if self.engine.tcfg.ckpt_convert_format:
+            self.convert_checkpoint()
+            logutil.log_rank_0(COMPLETED_MESSAGE)
+            return
+
         def publish(tr, loss):
             if self.runtime_state is not None:
                 self.runtime_state.update_metrics(**tr.last_metrics)

@@ -144,6 +144,17 @@ class TrainConfig:
     use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
     log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
     train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
+    # checkpoint format conversion: load as usual, write in ``ckpt_convert_format`` (torch | torch_dist) under
+    # ``ckpt_convert_save`` and leave without training
+    ckpt_convert_format: Optional[str] = None
+    ckpt_convert_save: Optional[str] = None
+    # MLPerf-style structured log (engine/mlperf_logging.py); training ends when the validation loss reaches the target
+    mlperf_mode: bool = False
+    mlperf_benchmark: str = "llm_pretraining"
+    mlperf_target_eval_loss: Optional[float] = None
+    mlperf_submission_org: str = "primus_b200"
+    mlperf_submission_platform: str = "B200"
+    mlperf_log_path: Optional[str] = None
     pretrained_hf_path: Optional[str] = None     # directory of Hugging Face weights to start from (when no checkpoint is loaded)
     export_hf_path: Optional[str] = None         # write the trained weights in Hugging Face layout after the last step
     sft_grad_sanitize: bool = False   # zero non-finite gradient entries instead of skipping / failing the step
@@ -197,8 +208,12 @@ class TrainConfig:
 
             fused_tp.ENABLED = True
             fused_tp.ENABLED_RS = bool(d.get("tp_comm_overlap_rs", False))
+        gbs = int(kw.get("global_batch_size", cls.global_batch_size))
         if d.get("train_samples"):      # sample-based run length (Megatron's train_samples): whole global batches
-            kw["train_iters"] = int(d["train_samples"]) // int(kw.get("global_batch_size", cls.global_batch_size))
+            kw["train_iters"] = int(d["train_samples"]) // gbs
+        for samples, iters in (("lr_warmup_samples", "lr_warmup_iters"), ("lr_decay_samples", "lr_decay_iters")):
+            if d.get(samples):          # sample-based schedule lengths
+                kw[iters] = int(d[samples]) // gbs
         return cls(**kw)
 
 
@@ -880,9 +895,13 @@ class Trainer:
         writer = obs.MetricsWriter(st.rank, st.rank == st.world_size - 1 or st.world_size == 1, out_dir,
                                    not tc.disable_tensorboard, tc.wandb_project, tc.mlflow_experiment_name,
                                    tc.mlflow_run_name or tc.exp_name, log=self.log)
+        ml = self._mlperf_logger()
+        last_ml_step = self.iteration
         try:
             for _ in range(n):
                 t0 = time.perf_counter()
+                if ml is not None:
+                    ml.run_start()
                 with obs.nvtx_range(f"iteration {self.iteration + 1}", tc.nvtx_ranges):
                     loss = self.train_step()
                 profiler.step()
@@ -906,8 +925,19 @@ class Trainer:
                                 self.log(f"[straggler] slow ranks {rep['stragglers']} (median {rep['median_s']:.3f} s)")
                     if on_step is not None:
                         on_step(self, lv)
+                    if ml is not None:
+                        ml.on_step(self.iteration, lv, self.last_metrics.get("lr", tc.lr), self.iteration - last_ml_step)
+                        last_ml_step = self.iteration
                 if tc.eval_interval and tc.eval_iters and self.iteration % tc.eval_interval == 0:
-                    self.evaluate(tc.eval_iters)
+                    if ml is not None:
+                        ml.clock.step(self.iteration - last_ml_step)
+                        last_ml_step = self.iteration
+                        ml.eval_begin(self.iteration)
+                    val = self.evaluate(tc.eval_iters)
+                    if ml is not None and ml.eval_end(self.iteration, val):      # every rank sees the same reduced loss
+                        self.log(f"[mlperf] validation loss {val:.4f} reached the target {ml.target} at iteration "
+                                 f"{self.iteration}: run complete")
+                        break
                 if tc.save and tc.save_interval and self.iteration % tc.save_interval == 0:
                     self.save_checkpoint()
                 elif tc.non_persistent_save_interval and self.iteration % tc.non_persistent_save_interval == 0:
@@ -929,6 +959,9 @@ class Trainer:
             from . import checkpoint as _ckpt
 
             _ckpt.finalize_async_save()
+            if ml is not None and (self.iteration >= tc.train_iters or ml.converged):
+                ml.run_stop(ml.converged, self.iteration)
+                ml.close()
             profiler.close()
             self._trace_reports(profiler, writer, out_dir)
             writer.close()
@@ -938,6 +971,23 @@ class Trainer:
                 gc.enable()
                 self._gc_disabled = False
         return losses
+
+    def _mlperf_logger(self):
+        """The run's MLPerf logger (``mlperf_mode``), created once; only the logging rank writes."""
+        tc, st = self.tcfg, self.st
+        if not tc.mlperf_mode:
+            return None
+        if getattr(self, "_mlperf", None) is None:
+            from .mlperf_logging import MLPerfLogger
+
+            self._mlperf = MLPerfLogger(tc.mlperf_benchmark, tc.global_batch_size, tc.mlperf_target_eval_loss,
+                                        tc.mlperf_submission_org, tc.mlperf_submission_platform,
+                                        enabled=st.rank == st.world_size - 1 or st.world_size == 1,
+                                        sink=self.log, path=tc.mlperf_log_path)
+            self._mlperf.log_init(tc.seed)
+            self._mlperf.log_hyperparams(tc, self.num_microbatches, tc.train_iters * tc.global_batch_size,
+                                         (tc.eval_iters or 0) * tc.global_batch_size)
+        return self._mlperf
 
     # ------------------------------------------------------------------ evaluation
     def _eval_stager(self):

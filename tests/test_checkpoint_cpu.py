@@ -298,3 +298,29 @@ def test_non_persistent_checkpoints_keep_only_the_newest_and_win_when_newer(tmp_
     assert c.load_checkpoint(root) == 4
     more_ref = a.train(2)
     assert b.train(2) == more_ref and len(ref) == 7
+
+
+def test_checkpoint_format_conversion_run(tmp_path):
+    """``ckpt_convert_format``: a run that loads a torch_dist checkpoint, writes it in the legacy torch layout and leaves;
+    training from the converted checkpoint continues like from the original."""
+    from primus_b200.engine.pretrain import PretrainTrainer
+
+    a = _trainer()
+    a.train(2)
+    a.save_checkpoint(str(tmp_path / "dist"))
+    ref = a.train(2)
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=6)
+    params = dict(vars(mc), **vars(tc))
+    params.update(load=str(tmp_path / "dist"), ckpt_convert_format="torch", ckpt_convert_save=str(tmp_path / "legacy"),
+                  mock_data=True)
+    ps.destroy_model_parallel()
+    t = PretrainTrainer.__new__(PretrainTrainer)
+    t.params, t.runtime_state, t.world_size, t.local_rank = params, None, 1, 0
+    t.init()
+    t.train()
+    assert t.engine.iteration == 2 and os.path.isdir(tmp_path / "legacy" / "iter_0000002" / "mp_rank_00")
+    b = _trainer()
+    b.tcfg.auto_detect_ckpt_format = True
+    assert b.load_checkpoint(str(tmp_path / "legacy")) == 2
+    got = b.train(2)
+    assert all(abs(x - y) < 1e-5 for x, y in zip(got, ref)), (got, ref)

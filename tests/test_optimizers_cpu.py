@@ -372,3 +372,51 @@ def test_grad_sanitize_zeroes_non_finite_entries_instead_of_skipping_the_step():
     assert moved == 0 and count == 0                      # non-finite norm: the step is skipped
     moved, count, norm = run(True)
     assert moved > 0 and count == 2 and norm == norm and norm < float("inf")
+
+
+def test_mlperf_log_events_order_and_convergence_stop(tmp_path):
+    """``mlperf_mode``: header, init / run / block / eval intervals in the order the compliance checker expects, tracked
+    stats per logged step, and the run ends with status success at the first evaluation that reaches the target."""
+    import json
+
+    from primus_b200.engine.mlperf_logging import PREFIX, MLPerfLogger, ThroughputClock
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    t = [0.0]
+    clock = ThroughputClock(8, now=lambda: t[0])
+    clock.begin(); t[0] = 2.0; clock.step(4); clock.pause(); t[0] = 5.0; clock.resume(); t[0] = 6.0
+    assert clock.samples_per_s() == 32 / 3.0 and clock.samples_per_s(include_eval=True) == 32 / 6.0
+
+    def run(target):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=6, layers=2, extra_tc=dict(
+            mlperf_mode=True, mlperf_target_eval_loss=target, eval_interval=2, eval_iters=1,
+            mlperf_log_path=str(tmp_path / f"mllog_{target}.txt")))
+        lines = []
+        tr = Trainer(mc, tc, device="cpu", log_fn=lines.append)
+        losses = tr.train()
+        ps.destroy_model_parallel()
+        ev = [json.loads(l[len(PREFIX):]) for l in lines if l.startswith(PREFIX)]
+        assert [json.loads(l[len(PREFIX):]) for l in open(tc.mlperf_log_path)] == ev
+        return losses, ev
+
+    losses, ev = run(100.0)                 # any loss is below this target: the first evaluation ends the run
+    keys = [e["key"] for e in ev]
+    assert len(losses) == 2 and keys[-1] == "run_stop" and ev[-1]["metadata"]["status"] == "success"
+    assert keys[0] == "init_start" and keys.index("submission_benchmark") < keys.index("init_stop") < keys.index("run_start")
+    order = [k for k in keys if k in ("init_stop", "run_start", "block_start", "block_stop", "eval_start", "eval_accuracy",
+                                      "eval_stop", "run_stop")]
+    assert order == ["init_stop", "run_start", "block_start", "block_stop", "eval_start", "eval_accuracy", "eval_stop", "run_stop"]
+    assert keys.count("tracked_stats") == 2 and ev[keys.index("global_batch_size")]["value"] == 4
+    acc = ev[keys.index("eval_accuracy")]
+    assert acc["metadata"]["samples_count"] == 8 and acc["value"] > 0 and acc["event_type"] == "POINT_IN_TIME"
+    assert all(set(e) == {"namespace", "time_ms", "event_type", "key", "value", "metadata"} for e in ev)
+    losses, ev = run(0.001)                 # never reached: all iterations run, status aborted
+    keys = [e["key"] for e in ev]
+    assert len(losses) == 6 and keys.count("eval_accuracy") == 3 and ev[-1]["metadata"]["status"] == "aborted"
+    assert keys.count("block_start") == 4 and keys.count("block_stop") == 3
+    lg = MLPerfLogger("x", 4, enabled=False, sink=lambda l: (_ for _ in ()).throw(AssertionError("disabled logger wrote")))
+    lg.log_init(1); lg.run_start(); lg.on_step(1, 1.0, 1e-3); lg.run_stop(True, 1)

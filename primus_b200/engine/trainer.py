@@ -128,6 +128,8 @@ class TrainConfig:
     error_injection_type: str = "transient_error"
     log_straggler: bool = False
     eval_interval: Optional[int] = None
+    split: Optional[str] = None           # "99,1,0": train / validation / test shares of the samples of ``data_path``
+    valid_data_path: Optional[str] = None
     eval_iters: int = 0
     pipeline_schedule: str = "1f1b"  # 1f1b | interleaved | zerobubble | zbv | v-half | v-min
     # cost-driven re-planning of the B / W-split schedules: node times (and, on GPUs, activation bytes) are measured in
@@ -233,6 +235,33 @@ def _open_corpus(data_path, seq_length: int, seed: int, tc):
                                  eod_mask_loss=bool(getattr(tc, "eod_mask_loss", False)),
                                  reset_position_ids=bool(getattr(tc, "reset_position_ids", False)))
     return IndexedTokenDataset(parts[0], seq_length)
+
+
+class SplitView:
+    """Samples ``[lo, hi)`` of a dataset, repeated when a run reads past the end."""
+
+    def __init__(self, dataset, lo: int, hi: int):
+        assert hi > lo, "an empty share of the data: check the split weights"
+        self.dataset, self.lo, self.n = dataset, lo, hi - lo
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i: int):
+        return self.dataset[self.lo + i % self.n]
+
+
+def split_view(dataset, split: str, which: int):
+    """Share ``which`` (0 train, 1 validation, 2 test) of a dataset cut by the weights ``split`` ("99,1,0": the first
+    99 % of the samples for training, the next 1 % for validation), as Megatron's ``--split`` cuts its sample index."""
+    w = [float(x) for x in str(split).replace("/", ",").split(",")]
+    w += [0.0] * (3 - len(w))
+    total, n = sum(w), len(dataset)
+    edges = [0]
+    for x in w:
+        edges.append(edges[-1] + x / total)
+    lo, hi = int(round(edges[which] * n)), int(round(edges[which + 1] * n))
+    return SplitView(dataset, lo, hi)
 
 
 class ThroughputMeter:
@@ -534,6 +563,8 @@ class Trainer:
                 ds = MockGPTDataset(model_cfg.vocab_size, train_cfg.seq_length, train_cfg.data_seed)
         else:
             ds = _open_corpus(train_cfg.data_path, train_cfg.seq_length, train_cfg.data_seed, train_cfg)
+            if train_cfg.split and not train_cfg.valid_data_path:
+                ds = split_view(ds, train_cfg.split, 0)            # the training share of the samples
         self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank)
         self.stager = BatchStager(ds, self.sampler, self.device, num_workers=train_cfg.num_workers)
         if train_cfg.reset_position_ids:
@@ -1000,8 +1031,10 @@ class Trainer:
             else:
                 from .data import IndexedTokenDataset
 
-                ds = _open_corpus(getattr(tc, "valid_data_path", None) or tc.data_path, tc.seq_length,
-                                  tc.data_seed + 1000003, tc)
+                if tc.valid_data_path or not tc.split:
+                    ds = _open_corpus(tc.valid_data_path or tc.data_path, tc.seq_length, tc.data_seed + 1000003, tc)
+                else:       # the validation share of the same sample order as training: disjoint from what is trained on
+                    ds = split_view(_open_corpus(tc.data_path, tc.seq_length, tc.data_seed, tc), tc.split, 1)
             sampler = MicroBatchSampler(tc.global_batch_size, tc.micro_batch_size, st.dp, st.dp_rank)
             self._eval_stager_obj = BatchStager(ds, sampler, self.device)
         return self._eval_stager_obj

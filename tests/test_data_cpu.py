@@ -108,3 +108,41 @@ def test_worker_threads_keep_the_sample_order_and_resume_exactly():
     assert resumed == run(0, 6)[0][4:]
     st.load_state_dict({"consumed_samples": 8})
     assert [mb["tokens"][:, 0].tolist() for mb in st.next_step()] == plain[1]
+
+
+def test_split_gives_disjoint_training_and_validation_samples(tmp_path):
+    import numpy as np
+    import torch
+
+    from primus_b200.engine.trainer import split_view
+
+    class Ten:
+        def __len__(self):
+            return 200
+
+        def __getitem__(self, i):
+            return {"tokens": torch.tensor([i])}
+
+    tr, va = split_view(Ten(), "99,1,0", 0), split_view(Ten(), "99,1,0", 1)
+    assert len(tr) == 198 and len(va) == 2 and int(tr[197]["tokens"]) == 197 and int(va[0]["tokens"]) == 198
+    assert int(tr[198]["tokens"]) == 0 and int(va[5]["tokens"]) == 199                 # wraps inside its own share
+    a, b = split_view(Ten(), "8,1,1", 1), split_view(Ten(), "8,1,1", 2)
+    assert (a.lo, a.n, b.lo, b.n) == (160, 20, 180, 20)
+    # through the trainer: the validation stream never touches the training share of a token file
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    path = str(tmp_path / "corpus.bin")
+    np.arange(33 * 400, dtype=np.int32).tofile(path)          # sample i holds tokens [33 i, 33 i + 33): recognisable
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, layers=2, vocab=16384,
+                         extra_tc=dict(mock_data=False, data_path=path, split="90,10,0", eval_iters=2))
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    t = Trainer(mc, tc, device="cpu", log_fn=lambda s: None)
+    n = len(t.stager.dataset.dataset)
+    train_first = [int(mb["tokens"][0, 0]) for mb in t.stager.next_step()]
+    valid_first = [int(mb["tokens"][0, 0]) for mb in t._eval_stager().next_step()]
+    assert len(t.stager.dataset) == round(0.9 * n) and all(v >= 32 * round(0.9 * n) for v in valid_first)
+    assert all(x < 32 * round(0.9 * n) for x in train_first)
+    ps.destroy_model_parallel()

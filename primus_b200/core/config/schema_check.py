@@ -35,7 +35,10 @@ INERT_KEYS = {
     "create_attention_mask_in_dataloader", "dataloader_type",
     # kernel selection switches of the reference's operator library: one native implementation here
     "cross_entropy_fusion_impl", "use_turbo_attention", "use_turbo_parallel_linear",
-    "use_turbo_rms_norm", "turbo_deepep_num_cu",
+    "use_turbo_rms_norm", "turbo_deepep_num_cu", "use_turbo_deepep", "use_turbo_grouped_gemm",
+    "use_turbo_fused_act_with_probs", "moe_permute_fusion", "moe_router_padding_for_quantization",
+    # the profiler is torch.profiler whenever ``profile`` is set
+    "use_pytorch_profiler",
     # services that are not built
     "enable_ft_package", "enable_gloo_process_groups", "straggler_ctrlr_port",
     "trainable",

@@ -44,7 +44,14 @@ class TrainConfig:
     min_lr: float = 0.0
     lr_decay_style: str = "cosine"
     lr_warmup_iters: int = 0
+    lr_warmup_fraction: Optional[float] = None    # warm-up as a share of the decay length (instead of lr_warmup_iters)
+    lr_warmup_init: float = 0.0                   # learning rate the warm-up starts from
     lr_decay_iters: Optional[int] = None
+    lr_wsd_decay_style: str = "exponential"       # shape of the final anneal of lr_decay_style WSD
+    lr_wsd_decay_iters: Optional[int] = None      # length of that anneal
+    start_weight_decay: Optional[float] = None    # weight-decay schedule: from here ...
+    end_weight_decay: Optional[float] = None      # ... to here ...
+    weight_decay_incr_style: str = "constant"     # ... constant | linear | cosine over the decay length
     weight_decay: float = 0.1
     adam_beta1: float = 0.9
     adam_beta2: float = 0.95
@@ -543,10 +550,20 @@ class Trainer:
 
     def _init_schedule_and_data(self):
         model_cfg, train_cfg, st = self.mcfg, self.tcfg, self.st
+        decay_iters = train_cfg.lr_decay_iters or train_cfg.train_iters
+        warmup = train_cfg.lr_warmup_iters
+        if train_cfg.lr_warmup_fraction is not None:
+            assert not warmup, "give lr_warmup_iters or lr_warmup_fraction, not both"
+            warmup = int(train_cfg.lr_warmup_fraction * decay_iters)
+        start_wd = train_cfg.weight_decay if train_cfg.start_weight_decay is None else train_cfg.start_weight_decay
+        end_wd = train_cfg.weight_decay if train_cfg.end_weight_decay is None else train_cfg.end_weight_decay
+        if train_cfg.weight_decay_incr_style == "constant":
+            assert start_wd == end_wd, "a constant weight decay with different start and end values"
         self.scheduler = schedules.LRScheduler(
-            max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_iters=train_cfg.lr_warmup_iters,
-            decay_iters=train_cfg.lr_decay_iters or train_cfg.train_iters, decay_style=train_cfg.lr_decay_style,
-            start_wd=train_cfg.weight_decay, end_wd=train_cfg.weight_decay)
+            max_lr=train_cfg.lr, min_lr=train_cfg.min_lr, warmup_iters=warmup, warmup_init=train_cfg.lr_warmup_init,
+            decay_iters=decay_iters, decay_style=train_cfg.lr_decay_style,
+            wsd_decay_iters=int(train_cfg.lr_wsd_decay_iters or 0), wsd_decay_style=train_cfg.lr_wsd_decay_style,
+            start_wd=start_wd, end_wd=end_wd, wd_incr_style=train_cfg.weight_decay_incr_style)
         # ---------------------------------------------------------------- data
         self.num_microbatches = schedules.num_microbatches(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp)
         if train_cfg.mock_data or not train_cfg.data_path:

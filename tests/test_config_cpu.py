@@ -185,8 +185,9 @@ def test_example_configs_pass_the_schema_check():
 
 def test_every_preset_key_is_read_or_declared_inert():
     """No key may parse and then silently do nothing: a key carried by a module / model preset is a field of the two
-    config dataclasses, is consumed somewhere in the package (its name appears in the Python sources), or is listed in
-    ``schema_check.INERT_KEYS`` (setting those is reported)."""
+    config dataclasses, is consumed somewhere in the package (looked up by name as a quoted string or read as an
+    attribute in the Python sources; a mention in a comment or a method of the same name does not count), or is listed
+    in ``schema_check.INERT_KEYS`` (setting those is reported)."""
     import dataclasses
     import glob
     import os
@@ -207,7 +208,7 @@ def test_every_preset_key_is_read_or_declared_inert():
     for f in glob.glob(os.path.join(root, "**", "*.py"), recursive=True):
         if not f.endswith(os.path.join("config", "schema_check.py")):
             src += open(f).read()
-    words = set(re.findall(r"[A-Za-z_][A-Za-z0-9_]*", src))
+    words = set(re.findall(r"[\"']([A-Za-z_][A-Za-z0-9_]*)[\"']", src)) | set(re.findall(r"\.([A-Za-z_][A-Za-z0-9_]*)\b(?!\()", src))
     orphan = sorted(k for k in keys if k not in fields and k not in schema_check.EXTRA_KNOWN and k not in words
                     and k not in schema_check.INERT_KEYS)
     assert not orphan, f"preset keys that nothing reads and that are not declared inert: {orphan}"

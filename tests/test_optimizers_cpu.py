@@ -420,3 +420,22 @@ def test_mlperf_log_events_order_and_convergence_stop(tmp_path):
     assert keys.count("block_start") == 4 and keys.count("block_stop") == 3
     lg = MLPerfLogger("x", 4, enabled=False, sink=lambda l: (_ for _ in ()).throw(AssertionError("disabled logger wrote")))
     lg.log_init(1); lg.run_start(); lg.on_step(1, 1.0, 1e-3); lg.run_stop(True, 1)
+
+
+def test_schedule_keys_reach_the_scheduler():
+    """Warm-up fraction / start value, the WSD anneal and the weight-decay ramp are read from the training config."""
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=100, layers=2, lr=1.0, extra_tc=dict(
+        lr_warmup_fraction=0.1, lr_warmup_init=0.2, lr_decay_iters=100, min_lr=0.0, lr_wsd_decay_iters=20,
+        lr_wsd_decay_style="linear", start_weight_decay=0.0, end_weight_decay=0.2, weight_decay_incr_style="linear"))
+    tc.lr_decay_style, tc.weight_decay = "WSD", 0.2
+    s = Trainer(mc, tc, device="cpu", log_fn=lambda m: None).scheduler
+    assert s.warmup_iters == 10 and abs(s.get_lr(5) - 0.6) < 1e-9 and s.get_lr(10) == 1.0      # from 0.2 to 1.0 in 10 steps
+    assert s.get_lr(80) == 1.0 and abs(s.get_lr(90) - 0.5) < 1e-9 and s.get_lr(100) == 0.0     # stable, then a linear anneal
+    assert abs(s.get_wd(50) - 0.1) < 1e-9 and s.get_wd(100) == 0.2
+    ps.destroy_model_parallel()

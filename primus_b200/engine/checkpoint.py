@@ -591,8 +591,9 @@ def _strictness(mode: str, missing: list, unexpected: list, log) -> None:
 
 
 def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_optim: Optional[bool] = None,
-                    load_rng: Optional[bool] = None) -> int:
-    """Loads the latest checkpoint under ``root``; returns the iteration (0 when nothing was found)."""
+                    load_rng: Optional[bool] = None, iteration: Optional[int] = None) -> int:
+    """Loads the latest checkpoint under ``root`` (or the one of ``iteration`` / ``ckpt_step``); returns the iteration
+    (0 when nothing was found)."""
     tc = trainer.tcfg
     finetune = bool(getattr(tc, "finetune", False)) if finetune is None else finetune
     load_optim = (not getattr(tc, "no_load_optim", False)) if load_optim is None else load_optim
@@ -600,6 +601,11 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
     finalize_async_save()
     st = ps.get_state()
     tag = read_tracker(root)
+    step = iteration if iteration is not None else getattr(tc, "ckpt_step", None)
+    if step is not None:
+        tag = str(int(step))
+        if not os.path.isdir(os.path.join(root, f"iter_{int(step):07d}")):
+            raise FileNotFoundError(f"no checkpoint of iteration {step} under {root}")
     if tag is None:
         return 0
     d = os.path.join(root, "release" if tag == "release" else f"iter_{int(tag):07d}")
@@ -690,7 +696,11 @@ def load_checkpoint(trainer, root: str, finetune: Optional[bool] = None, load_op
                 "parameters and the Adam moments start from zero")
         _refresh_master_weights(trainer)
     trainer.iteration = int(common["iteration"])
-    trainer.scheduler.load_state_dict(common["scheduler"])
+    # ``override_opt_param_scheduler`` (the default behaviour): this run's schedule continues at the loaded step;
+    # ``use_checkpoint_opt_param_scheduler``: the schedule the checkpoint was written with
+    trainer.scheduler.load_state_dict(
+        common["scheduler"], bool(getattr(tc, "use_checkpoint_opt_param_scheduler", False))
+        and not getattr(tc, "override_opt_param_scheduler", False), log)
     trainer.stager.load_state_dict(common["data"])
     if group is not None:
         dist.barrier(group=group)

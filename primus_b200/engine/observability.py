@@ -92,7 +92,8 @@ def nvtx_range(name: str, enabled: bool):
 class MetricsWriter:
     def __init__(self, rank: int, is_writer_rank: bool, log_dir: Optional[str] = None, tensorboard: bool = False,
                  wandb_project: Optional[str] = None, mlflow_experiment: Optional[str] = None, run_name: str = "run",
-                 config: Optional[dict] = None, log=print):
+                 config: Optional[dict] = None, log=print, wandb_options: Optional[dict] = None):
+        """``wandb_options``: extra keyword arguments of ``wandb.init`` (``name``: wandb_exp_name, ``entity``, ``dir``)."""
         self.sinks = []
         self.jsonl = None
         if not is_writer_rank:
@@ -113,7 +114,9 @@ class MetricsWriter:
             try:
                 import wandb
 
-                run = wandb.init(project=wandb_project, name=run_name, config=config or {})
+                kw = dict(name=run_name, config=config or {})
+                kw.update({k: v for k, v in (wandb_options or {}).items() if v})
+                run = wandb.init(project=wandb_project, **kw)
                 self.sinks.append(("wandb", lambda it, m: wandb.log(m, step=it), run.finish))
             except Exception as e:  # noqa: BLE001
                 log(f"[metrics] wandb sink disabled: {e}")

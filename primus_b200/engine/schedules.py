@@ -75,11 +75,24 @@ class LRScheduler:
     def step(self, n: int = 1):
         self.num_iters += n
 
-    def state_dict(self):
-        return {"num_iters": self.num_iters}
+    HYPER = ("max_lr", "min_lr", "warmup_iters", "warmup_init", "decay_iters", "decay_style", "wsd_decay_iters",
+             "wsd_decay_style", "start_wd", "end_wd", "wd_incr_style")
 
-    def load_state_dict(self, sd):
+    def state_dict(self):
+        return {"num_iters": self.num_iters, **{k: getattr(self, k) for k in self.HYPER}}
+
+    def load_state_dict(self, sd, use_checkpoint_values: bool = False, log=None):
+        """The position in the schedule always comes from the checkpoint.  The schedule itself is this run's unless
+        ``use_checkpoint_values`` (``use_checkpoint_opt_param_scheduler``); differences are reported either way."""
         self.num_iters = sd["num_iters"]
+        diff = {k: (sd[k], getattr(self, k)) for k in self.HYPER if k in sd and sd[k] != getattr(self, k)}
+        if use_checkpoint_values:
+            for k, (saved, _) in diff.items():
+                setattr(self, k, saved)
+        if diff and log is not None:
+            which = "the checkpoint's" if use_checkpoint_values else "this run's"
+            log("[scheduler] the checkpoint was written with another schedule (" +
+                ", ".join(f"{k}: {a} -> {b}" for k, (a, b) in diff.items()) + f"): using {which} values")
 
 
 def num_microbatches(global_batch: int, micro_batch: int, dp: int) -> int:

@@ -153,6 +153,21 @@ class TrainConfig:
     use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
     log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
     train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
+    ckpt_step: Optional[int] = None              # load the checkpoint of this iteration instead of the newest
+    exit_on_missing_checkpoint: bool = False     # ``load`` is set but holds no checkpoint: stop instead of starting fresh
+    pretrained_checkpoint: Optional[str] = None  # weights to start from when ``load`` holds nothing (iteration 0, no optimizer state)
+    override_opt_param_scheduler: bool = False   # after a load keep this run's LR / WD schedule (what happens by default)
+    use_checkpoint_opt_param_scheduler: bool = False   # after a load continue with the schedule stored in the checkpoint
+    save_retain_interval: Optional[int] = None   # keep only the checkpoints of multiples of this (and the newest)
+    iterations_to_skip: Optional[list] = None    # iterations whose batch is read but not trained on
+    skip_train: bool = False                     # no training: load, evaluate if asked, leave
+    log_params_norm: bool = False                # L2 norm of the parameters in the log line and the metrics
+    log_num_zeros_in_grad: bool = False          # number of exactly-zero gradient entries
+    manual_gc_interval: int = 0                  # with manual_gc: collect every N iterations (0: never during training)
+    check_weight_hash_across_dp_replicas_interval: Optional[int] = None   # compare the replicas' parameters every N steps
+    wandb_exp_name: Optional[str] = None
+    wandb_entity: Optional[str] = None
+    wandb_save_dir: Optional[str] = None
     # checkpoint format conversion: load as usual, write in ``ckpt_convert_format`` (torch | torch_dist) under
     # ``ckpt_convert_save`` and leave without training
     ckpt_convert_format: Optional[str] = None
@@ -773,6 +788,14 @@ class Trainer:
         timers = self.timers
         with timers("batch-generator", 2):
             micro_batches = self.stager.next_step()
+            if self.tcfg.iterations_to_skip and (self.iteration + 1) in self.tcfg.iterations_to_skip:
+                # a batch known to be bad: it is consumed (the data order of the other steps stays what it was) and
+                # nothing is trained on it
+                self.log(f"[skip] iteration {self.iteration + 1} is listed in iterations_to_skip: batch dropped")
+                self.stager.prefetch()
+                self.scheduler.step()
+                self.iteration += 1
+                return self.loss_accum.zero_().clone().reshape(())
             if self.st.cp > 1:
                 micro_batches = [self._cp_shard(mb) for mb in micro_batches]
         if self.st.pp > 1 and self.tcfg.pp_warmup and not getattr(self, "_pp_warmed", False):
@@ -870,6 +893,10 @@ class Trainer:
         of the reference's in-process restart wrapper, primus/backends/megatron/megatron_pretrain_trainer.py:195-204).
         Failures that only one rank can see are re-raised: they need the job-level restart."""
         tc = self.tcfg
+        if tc.skip_train:
+            if tc.eval_iters:
+                self.evaluate(tc.eval_iters)
+            return []
         if not tc.inprocess_restart:
             return self._train_loop(num_iters, on_step)
         from . import checkpoint, fault
@@ -942,7 +969,8 @@ class Trainer:
                                     memory_snapshot_path=tc.memory_snapshot_path, log=self.log)
         writer = obs.MetricsWriter(st.rank, st.rank == st.world_size - 1 or st.world_size == 1, out_dir,
                                    not tc.disable_tensorboard, tc.wandb_project, tc.mlflow_experiment_name,
-                                   tc.mlflow_run_name or tc.exp_name, log=self.log)
+                                   tc.mlflow_run_name or tc.exp_name, log=self.log,
+                                   wandb_options=dict(name=tc.wandb_exp_name, entity=tc.wandb_entity, dir=tc.wandb_save_dir))
         ml = self._mlperf_logger()
         last_ml_step = self.iteration
         try:
@@ -976,6 +1004,11 @@ class Trainer:
                     if ml is not None:
                         ml.on_step(self.iteration, lv, self.last_metrics.get("lr", tc.lr), self.iteration - last_ml_step)
                         last_ml_step = self.iteration
+                if tc.manual_gc and tc.manual_gc_interval and self.iteration % tc.manual_gc_interval == 0:
+                    gc.collect()
+                n_hash = tc.check_weight_hash_across_dp_replicas_interval
+                if n_hash and self.iteration % n_hash == 0:
+                    self.check_replicas_agree()
                 if tc.eval_interval and tc.eval_iters and self.iteration % tc.eval_interval == 0:
                     if ml is not None:
                         ml.clock.step(self.iteration - last_ml_step)
@@ -1019,6 +1052,26 @@ class Trainer:
                 gc.enable()
                 self._gc_disabled = False
         return losses
+
+    @torch.no_grad()
+    def check_replicas_agree(self) -> None:
+        """``check_weight_hash_across_dp_replicas_interval``: the parameters every data-parallel replica holds must be the
+        same bits.  Every rank sums its parameters in fp64 (per buffer); the minimum and the maximum of the sums over the
+        data-parallel group must coincide.  Expert parameters are compared over their own, smaller replica group."""
+        st = self.st
+        for buf in self.buffers:
+            group, size = buf.dp_group, buf.dp_size
+            if size <= 1:
+                continue
+            self.finish_param_sync()
+            v = buf.param_data.double()
+            sig = torch.stack([v.sum(), (v * v).sum()])
+            lo, hi = sig.clone(), sig.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+            if not torch.equal(lo, hi):
+                raise RuntimeError(f"iteration {self.iteration}: the data-parallel replicas of a parameter buffer differ "
+                                   f"(checksums {lo.tolist()} .. {hi.tolist()}, rank {st.rank})")
 
     def _mlperf_logger(self):
         """The run's MLPerf logger (``mlperf_mode``), created once; only the logging rank writes."""
@@ -1108,6 +1161,22 @@ class Trainer:
                                  lr=self.scheduler.get_lr(self.iteration))
         aux = [m_.last_aux_loss for mc_ in self.model_chunks for m_ in mc_.modules()
                if getattr(m_, "last_aux_loss", None) is not None]
+        extra_text = ""
+        if tc.log_params_norm:
+            sq = torch.zeros((), dtype=torch.float64, device=self.device)
+            for m in self.model_chunks:
+                for p in m.parameters():
+                    sq += p.detach().double().pow(2).sum()
+            if dist.is_initialized() and st.world_size > 1:      # every parameter shard once: model-parallel ranks add up
+                for g in (st.tp_group, st.pp_group):
+                    if g is not None:
+                        dist.all_reduce(sq, group=g)
+            self.last_metrics["params_norm"] = float(sq.sqrt())
+            extra_text += f" params norm: {self.last_metrics['params_norm']:.3f} |"
+        if tc.log_num_zeros_in_grad:
+            z = sum(int((buf.grad_data == 0).sum()) for buf in self.buffers)
+            self.last_metrics["num_zeros_in_grad"] = z
+            extra_text += f" num zeros: {z} |"
         moe_text = ""
         if aux:   # per-layer load-balancing losses of the last micro-batch, averaged over this rank's MoE layers
             v = float(torch.stack([a.detach().float().reshape(()) for a in aux]).mean().item())
@@ -1119,7 +1188,7 @@ class Trainer:
                 (f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
                  if tc.log_throughput else "") +
                 f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
-                f"lm loss: {loss:.6E} |{moe_text} grad norm: {gn:.3f} | max mem (GiB): {mem:.2f} |")
+                f"lm loss: {loss:.6E} |{moe_text} grad norm: {gn:.3f} |{extra_text} max mem (GiB): {mem:.2f} |")
         if tc.timing_log_level > 0:
             text = self.timers.log(normalizer=max(getattr(self, "_steps_since_timer_log", 1), 1))
             self._steps_since_timer_log = 0
@@ -1149,7 +1218,18 @@ class Trainer:
         from . import checkpoint
 
         self._check_device_status()   # never persist the state of a step whose kernels reported an error
-        return checkpoint.save_checkpoint(self, path or self.tcfg.save)
+        root = path or self.tcfg.save
+        d = checkpoint.save_checkpoint(self, root)
+        keep = self.tcfg.save_retain_interval
+        if keep and not self.tcfg.async_save and (not dist.is_initialized() or dist.get_rank() == 0):
+            import re
+            import shutil
+
+            for name in os.listdir(root):       # older checkpoints off the retention grid go; the newest always stays
+                m = re.fullmatch(r"iter_(\d{7})", name)
+                if m and int(m.group(1)) != self.iteration and int(m.group(1)) % int(keep):
+                    shutil.rmtree(os.path.join(root, name), ignore_errors=True)
+        return d
 
     def non_persistent_root(self) -> Optional[str]:
         tc = self.tcfg
@@ -1196,4 +1276,12 @@ class Trainer:
             if newest_np is not None and (newest is None or newest_np > newest):
                 self.log(f"[checkpoint] resuming from the non-persistent checkpoint of iteration {newest_np} in {np_root}")
                 return checkpoint.load_checkpoint(self, np_root)
-        return checkpoint.load_checkpoint(self, path)
+        it = checkpoint.load_checkpoint(self, path) if path and os.path.isdir(path) else 0
+        tc = self.tcfg
+        if it == 0 and path and checkpoint.read_tracker(path) is None:
+            if tc.pretrained_checkpoint:
+                self.log(f"[checkpoint] nothing under {path}: starting from the weights in {tc.pretrained_checkpoint}")
+                checkpoint.load_checkpoint(self, tc.pretrained_checkpoint, finetune=True)
+            elif tc.exit_on_missing_checkpoint:
+                raise SystemExit(f"no checkpoint under {path} and exit_on_missing_checkpoint is set")
+        return it

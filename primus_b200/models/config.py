@@ -90,6 +90,9 @@ class TransformerConfig:
     fp8_amax_history_len: int = 1          # delayed scaling: steps of recorded maxima
     fp8_amax_compute_algo: str = "most_recent"   # delayed scaling: most_recent | max over the history
     fp8_margin: int = 0                    # delayed scaling: extra powers of two of headroom
+    first_last_layers_bf16: bool = False            # keep the first / last decoder layers' GEMMs in bf16 under fp8 / fp4
+    num_layers_at_start_in_bf16: int = 1
+    num_layers_at_end_in_bf16: int = 1
     fp4: Optional[str] = None  # None | "e2m1": MXFP4 numerics for the linear-layer GEMMs (carried in FP8 storage)
     fp4_recipe: str = "mxfp4"
     recompute_granularity: Optional[str] = None  # None | selective | full

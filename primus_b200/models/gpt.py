@@ -355,6 +355,7 @@ class LanguageModelEmbedding(nn.Module):
         self.word_embeddings.weight.tensor_model_parallel = tp > 1
         self.word_embeddings.weight.partition_dim = 0
         self.word_embeddings.weight._fp8_exempt = True   # also the LM head when embeddings are tied
+        self.word_embeddings.weight._embedding_like = True
         self.vocab_local = V
 
     def forward(self, tokens_flat):
@@ -436,6 +437,7 @@ class GPTModel(nn.Module):
             self.output_layer.weight.tensor_model_parallel = tp > 1
             self.output_layer.weight.partition_dim = 0
             self.output_layer.weight._fp8_exempt = True   # the LM head stays in bf16 under an fp8 recipe
+            self.output_layer.weight._embedding_like = True
         # Tied output head or multi-token prediction on a last stage that is not also the first: the stage holds a replica
         # of the word embeddings.  The first stage's copy is the trained one ("primary"); the trainer adds the replica's
         # gradient to it before the data-parallel reduction and re-sends the weights after every optimizer step (the
@@ -455,6 +457,17 @@ class GPTModel(nn.Module):
             self.mtp.layers = nn.ModuleList([MultiTokenPredictionLayer(cfg, device, tp, depth)
                                              for depth in range(cfg.mtp_num_layers)])
         self._rope_cache = {}
+        # ``first_last_layers_bf16``: under a low-precision recipe the GEMMs of the first ``num_layers_at_start_in_bf16``
+        # and the last ``num_layers_at_end_in_bf16`` decoder layers stay in bf16 (the layers most sensitive to
+        # quantisation noise; Transformer Engine's switch of the same name in the reference's argument set)
+        if cfg.first_last_layers_bf16:
+            keep = set(range(cfg.num_layers_at_start_in_bf16)) | \
+                set(range(cfg.num_layers - cfg.num_layers_at_end_in_bf16, cfg.num_layers))
+            for i in layer_indices:
+                if i in keep:
+                    for p_ in self.decoder.layers[str(i)].parameters():
+                        if p_.dim() >= 2:
+                            p_._fp8_exempt = True
         fused.set_situ_betas(cfg.activation_situ_beta, cfg.activation_situ_linear_beta)
         fused.set_zero_centered_gamma(cfg.apply_layernorm_1p)
         if cfg.apply_layernorm_1p:

@@ -101,7 +101,7 @@ class Muon(_PerParameterOptimizer):
 
     @staticmethod
     def is_matrix(p) -> bool:
-        return p.dim() == 2 and not getattr(p, "_fp8_exempt", False)   # embeddings / LM head are marked exempt
+        return p.dim() == 2 and not getattr(p, "_embedding_like", False)   # embeddings / LM head: element-wise update
 
     def _update(self, lr, wd):
         b1, b2 = self.betas

@@ -439,3 +439,62 @@ def test_schedule_keys_reach_the_scheduler():
     assert s.get_lr(80) == 1.0 and abs(s.get_lr(90) - 0.5) < 1e-9 and s.get_lr(100) == 0.0     # stable, then a linear anneal
     assert abs(s.get_wd(50) - 0.1) < 1e-9 and s.get_wd(100) == 0.2
     ps.destroy_model_parallel()
+
+
+def test_run_control_keys(tmp_path):
+    """iterations_to_skip, skip_train, ckpt_step, override_opt_param_scheduler, save_retain_interval, pretrained_checkpoint,
+    exit_on_missing_checkpoint, log_params_norm / log_num_zeros_in_grad, manual_gc_interval."""
+    import os
+
+    import pytest
+
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    def make(iters=6, lr=1e-2, **extra):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=iters, layers=2, lr=lr, extra_tc=extra)
+        logs = []
+        tr = Trainer(mc, tc, device="cpu", log_fn=logs.append)
+        return tr, logs
+
+    try:
+        ref, _ = make()
+        ref_losses = ref.train()
+        sk, logs = make(iterations_to_skip=[2], log_params_norm=True, log_num_zeros_in_grad=True, manual_gc_interval=2)
+        before = [p.detach().clone() for p in sk.model.parameters()]
+        l1 = sk.train(1)
+        mid = [p.detach().clone() for p in sk.model.parameters()]
+        l2 = sk.train(1)                                      # the listed iteration: batch read, nothing updated
+        assert l1[0] == ref_losses[0] and l2[0] == 0.0 and sk.iteration == 2
+        assert any(not torch.equal(a, b) for a, b in zip(before, mid))
+        assert all(torch.equal(a, b) for a, b in zip(mid, sk.model.parameters()))
+        assert sk.stager.state_dict()["consumed_samples"] == 8 and any("iterations_to_skip" in m for m in logs)
+        assert sk.last_metrics["params_norm"] > 0 and "num_zeros_in_grad" in sk.last_metrics
+        assert any("params norm:" in m and "num zeros:" in m for m in logs)
+        # checkpoints every 1 step, retained every 2: 1 and 3 go once a newer one exists
+        root = str(tmp_path / "ck")
+        a, _ = make(save=root, save_interval=1, save_retain_interval=2)
+        a.train(5)
+        assert sorted(n for n in os.listdir(root) if n.startswith("iter_")) == ["iter_0000002", "iter_0000004", "iter_0000005"]
+        b, logs = make(ckpt_step=2, lr=5e-3)
+        assert b.load_checkpoint(root) == 2 and b.scheduler.max_lr == 5e-3 and b.scheduler.num_iters == 2
+        assert any("another schedule" in m and "this run's" in m for m in logs)   # this run's schedule, and it says so
+        c, _ = make(lr=5e-3, use_checkpoint_opt_param_scheduler=True)
+        assert c.load_checkpoint(root) == 5 and c.scheduler.max_lr == 1e-2        # the checkpoint's schedule on request
+        with pytest.raises(FileNotFoundError):
+            make(ckpt_step=3)[0].load_checkpoint(root)
+        # nothing under load: weights from pretrained_checkpoint (iteration 0, fresh optimizer), or a clean stop
+        empty = str(tmp_path / "empty")
+        os.makedirs(empty)
+        d, logs = make(pretrained_checkpoint=root)
+        assert d.load_checkpoint(empty) == 0 and d.iteration == 0 and any("starting from the weights" in m for m in logs)
+        assert all(torch.equal(x, y) for x, y in zip(d.model.parameters(), a.model.parameters()))
+        with pytest.raises(SystemExit):
+            make(exit_on_missing_checkpoint=True)[0].load_checkpoint(empty)
+        e, logs = make(skip_train=True, eval_iters=1)
+        assert e.train() == [] and e.iteration == 0 and any("validation loss" in m for m in logs)
+    finally:
+        ps.destroy_model_parallel()

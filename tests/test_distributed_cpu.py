@@ -72,6 +72,8 @@ CASES = {
         moe_ffn_hidden_size=32, moe_layer_freq=1, moe_shared_expert_intermediate_size=32,
         moe_router_score_function="sqrtsoftplus", activation_func_clamp_value=10.0, v4_indexer_distill_loss_coeff=0.1,
         num_hash_layers=3))),
+    "dp2_tp2_replica_check": dict(world=4, kw=dict(tp=2, sp=True, extra_tc=dict(
+        check_weight_hash_across_dp_replicas_interval=1, log_params_norm=True))),
     "pp2_1f1b": dict(world=2, kw=dict(pp=2)),
     "dp2_pp2_tp_pp_dp_mapping": dict(world=4, kw=dict(pp=2, extra_tc=dict(use_tp_pp_dp_mapping=True))),
     "tp2_pp2_ep2_tp_pp_dp_mapping": dict(world=8, kw=dict(tp=2, pp=2, ep=2, sp=True, moe=True,

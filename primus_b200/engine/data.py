@@ -104,16 +104,41 @@ class MicroBatchSampler:
     ``r`` takes micro-batch ``m`` = samples ``g*gbs + (m*dp + r)*mbs + [0, mbs)`` (Megatron's
     interleaving).  ``consumed_samples`` makes the stream resumable."""
 
-    def __init__(self, global_batch: int, micro_batch: int, dp_size: int, dp_rank: int, consumed_samples: int = 0):
+    def __init__(self, global_batch: int, micro_batch: int, dp_size: int, dp_rank: int, consumed_samples: int = 0,
+                 rampup=None):
+        """``rampup``: ``(start, increment, samples)`` -- the global batch grows from ``start`` by ``increment`` in equal
+        stretches of the first ``samples`` samples until it reaches ``global_batch`` (Megatron's ``rampup_batch_size``);
+        every size on the way must be a multiple of ``micro_batch x dp_size``."""
         assert global_batch % (micro_batch * dp_size) == 0
         self.gbs, self.mbs, self.dp, self.rank = global_batch, micro_batch, dp_size, dp_rank
         self.consumed = consumed_samples
         self.num_micro = global_batch // (micro_batch * dp_size)
+        self.rampup = None
+        if rampup:
+            start, incr, samples = (int(x) for x in rampup)
+            assert incr > 0 and (global_batch - start) % incr == 0 and start > 0, \
+                "rampup_batch_size: the increments must lead from the start size exactly to global_batch_size"
+            for b in range(start, global_batch + 1, incr):
+                assert b % (micro_batch * dp_size) == 0, f"rampup_batch_size: {b} is not a multiple of micro batch x dp"
+            self.rampup = (start, incr, samples)
+
+    def batch_size_at(self, consumed: int) -> int:
+        """Global batch size of the step that starts after ``consumed`` samples."""
+        if not self.rampup:
+            return self.gbs
+        start, incr, samples = self.rampup
+        steps = (self.gbs - start) // incr
+        if consumed >= samples or steps == 0:
+            return self.gbs
+        return start + incr * int(consumed / (samples / steps))
 
     def next_global_batch(self) -> list[list[int]]:
         base = self.consumed
-        out = [[base + (m * self.dp + self.rank) * self.mbs + i for i in range(self.mbs)] for m in range(self.num_micro)]
-        self.consumed += self.gbs
+        gbs = self.batch_size_at(base)
+        out = [[base + (m * self.dp + self.rank) * self.mbs + i for i in range(self.mbs)]
+               for m in range(gbs // (self.mbs * self.dp))]
+        self.consumed += gbs
+        self.last_batch_size = gbs
         return out
 
     def state_dict(self):
@@ -143,6 +168,7 @@ class BatchStager:
         self.stream = torch.cuda.Stream(device=self.device) if self.cuda else None
         self._next = None
         self._host_future = None
+        self._starts: list = []             # sample offsets of the steps handed out but not yet trained on
         self.h2d_bytes_last_step = 0
         self.num_workers = int(num_workers or 0)
         self._pool = self._loader = None
@@ -164,18 +190,19 @@ class BatchStager:
             mbs.append(b)
         return mbs
 
+    def _hand_out(self) -> list:
+        """The next step's index lists; its start is remembered until training has consumed the step."""
+        self._starts.append(self.sampler.consumed)
+        return self.sampler.next_global_batch()
+
     def _load_host(self) -> list[dict]:
         if self._loader is None:
-            return self._build_host(self.sampler.next_global_batch())
+            return self._build_host(self._hand_out())
         if self._host_future is None:       # first step: nothing is in flight yet
-            self._host_future = self._loader.submit(self._build_host, self.sampler.next_global_batch())
+            self._host_future = self._loader.submit(self._build_host, self._hand_out())
         host = self._host_future.result()
-        self._host_future = self._loader.submit(self._build_host, self.sampler.next_global_batch())
+        self._host_future = self._loader.submit(self._build_host, self._hand_out())
         return host
-
-    def _pending_steps(self) -> int:
-        """Steps the sampler has handed out that training has not consumed (replayed after a resume)."""
-        return int(self._next is not None) + int(self._host_future is not None)
 
     def _to_device(self, host_mbs: list[dict]):
         if not self.cuda:
@@ -205,6 +232,7 @@ class BatchStager:
         self.prefetch()
         dev, ev, nbytes = self._next
         self._next = None
+        self._starts.pop(0)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
             for b in dev:
@@ -216,12 +244,13 @@ class BatchStager:
 
     def state_dict(self):
         # a prefetched-but-unconsumed step must be replayed after a resume
-        c = self.sampler.consumed - self.sampler.gbs * self._pending_steps()
-        return {"consumed_samples": c}
+        # steps staged or in flight are replayed after a resume: the stream continues where the oldest of them starts
+        return {"consumed_samples": self._starts[0] if self._starts else self.sampler.consumed}
 
     def load_state_dict(self, sd):
         self._next = None
         if self._host_future is not None:
             self._host_future.result()          # let the worker finish before the sampler is rewound
             self._host_future = None
+        self._starts = []
         self.sampler.load_state_dict(sd)

@@ -153,6 +153,7 @@ class TrainConfig:
     use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
     log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
     train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
+    rampup_batch_size: Optional[list] = None     # [start, increment, samples]: the global batch grows during the first samples
     ckpt_step: Optional[int] = None              # load the checkpoint of this iteration instead of the newest
     exit_on_missing_checkpoint: bool = False     # ``load`` is set but holds no checkpoint: stop instead of starting fresh
     pretrained_checkpoint: Optional[str] = None  # weights to start from when ``load`` holds nothing (iteration 0, no optimizer state)
@@ -597,7 +598,8 @@ class Trainer:
             ds = _open_corpus(train_cfg.data_path, train_cfg.seq_length, train_cfg.data_seed, train_cfg)
             if train_cfg.split and not train_cfg.valid_data_path:
                 ds = split_view(ds, train_cfg.split, 0)            # the training share of the samples
-        self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank)
+        self.sampler = MicroBatchSampler(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp, st.dp_rank,
+                                         rampup=train_cfg.rampup_batch_size)
         self.stager = BatchStager(ds, self.sampler, self.device, num_workers=train_cfg.num_workers)
         if train_cfg.reset_position_ids:
             self.use_position_ids = True
@@ -788,6 +790,9 @@ class Trainer:
         timers = self.timers
         with timers("batch-generator", 2):
             micro_batches = self.stager.next_step()
+            if self.tcfg.rampup_batch_size:     # the global batch is still growing: this step's number of micro-batches
+                self.num_microbatches = len(micro_batches)
+                self.current_global_batch = len(micro_batches) * self.tcfg.micro_batch_size * self.st.dp
             if self.tcfg.iterations_to_skip and (self.iteration + 1) in self.tcfg.iterations_to_skip:
                 # a batch known to be bad: it is consumed (the data order of the other steps stays what it was) and
                 # nothing is trained on it
@@ -1150,7 +1155,7 @@ class Trainer:
 
     def _log_step(self, loss: float, dt: float):
         tc, st = self.tcfg, self.st
-        tokens = tc.seq_length * tc.global_batch_size
+        tokens = tc.seq_length * getattr(self, "current_global_batch", tc.global_batch_size)
         tps_gpu = tokens / dt / max(st.world_size, 1)
         avg = self.meter.update(tps_gpu)
         tflops = tokens * self.flops_per_token / dt / max(st.world_size, 1) / 1e12
@@ -1187,7 +1192,7 @@ class Trainer:
                 f" iteration {self.iteration:8d}/{tc.train_iters:8d} | elapsed time per iteration (ms): {dt * 1e3:.1f} | " +
                 (f"throughput per GPU (TFLOP/s/GPU): {tflops:.1f} | tokens/s/GPU: {tps_gpu:.1f} (avg {avg:.1f}) | "
                  if tc.log_throughput else "") +
-                f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {tc.global_batch_size:5d} | "
+                f"learning rate: {self.last_metrics['lr']:.6E} | global batch size: {getattr(self, 'current_global_batch', tc.global_batch_size):5d} | "
                 f"lm loss: {loss:.6E} |{moe_text} grad norm: {gn:.3f} |{extra_text} max mem (GiB): {mem:.2f} |")
         if tc.timing_log_level > 0:
             text = self.timers.log(normalizer=max(getattr(self, "_steps_since_timer_log", 1), 1))

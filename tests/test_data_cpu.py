@@ -146,3 +146,42 @@ def test_split_gives_disjoint_training_and_validation_samples(tmp_path):
     assert len(t.stager.dataset) == round(0.9 * n) and all(v >= 32 * round(0.9 * n) for v in valid_first)
     assert all(x < 32 * round(0.9 * n) for x in train_first)
     ps.destroy_model_parallel()
+
+
+def test_batch_size_rampup(tmp_path):
+    """``rampup_batch_size: [start, increment, samples]``: the global batch grows in equal stretches of the first samples;
+    the trainer follows with its number of micro-batches and the stream stays resumable in the middle of the ramp."""
+    import torch
+
+    from primus_b200.engine.data import BatchStager, MicroBatchSampler, MockGPTDataset
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    s = MicroBatchSampler(16, 2, 2, 1, rampup=(4, 4, 48))          # 4 -> 8 -> 12 -> 16 over 48 samples: 16 samples each
+    sizes, firsts = [], []
+    for _ in range(10):
+        mbs = s.next_global_batch()
+        sizes.append(s.last_batch_size)
+        firsts.append(mbs[0][0])
+    assert sizes == [4, 4, 4, 4, 8, 8, 12, 12, 16, 16] and s.consumed == sum(sizes)
+    assert firsts[0] == 2 and firsts[4] == 16 + 2                   # rank 1 of 2: the second micro-batch of every pair
+    import pytest
+    with pytest.raises(AssertionError):
+        MicroBatchSampler(16, 2, 2, 0, rampup=(4, 5, 48))
+    with pytest.raises(AssertionError):
+        MicroBatchSampler(16, 4, 2, 0, rampup=(4, 4, 48))           # 4 is not a multiple of micro batch x dp = 8
+    ds = MockGPTDataset(100, 8)
+    st = BatchStager(ds, MicroBatchSampler(8, 2, 1, 0, rampup=(2, 2, 12)), "cpu", num_workers=2)
+    seen = [len(st.next_step()) for _ in range(3)]
+    assert seen == [1, 1, 2] and st.state_dict() == {"consumed_samples": 8}   # 2 + 2 + 4; what is in flight is not counted
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel()
+    mc, tc = W.tiny_cfgs(seq=32, gbs=8, mbs=2, iters=5, layers=2, extra_tc=dict(rampup_batch_size=[2, 2, 12]))
+    logs = []
+    tr = Trainer(mc, tc, device="cpu", log_fn=logs.append)
+    counts = []
+    tr.train(on_step=lambda t, lv: counts.append((t.num_microbatches, t.current_global_batch)))
+    assert counts == [(1, 2), (1, 2), (2, 4), (3, 6), (4, 8)]        # stretches of 4 samples: 2, 2 | 4 | 6 | 8
+    assert any("global batch size:     6" in m for m in logs)
+    ps.destroy_model_parallel()

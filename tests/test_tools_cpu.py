@@ -234,3 +234,13 @@ def test_tuning_agent_loop_history_legality_and_llm_fallback(tmp_path):
     assert "overrides of the best plan" in text and "#" in text
     assert A.main(["--model", "llama3.1_8B", "--world", "8", "--global-batch", "128", "--rounds", "1", "--per-round", "3",
                    "--report", str(tmp_path / "r.md")]) == 0
+
+
+def test_config_reference_is_current():
+    """docs/config-reference.md is generated from the configuration dataclasses: regenerate it when a key is added."""
+    import os
+
+    from primus_b200.tools import config_reference
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "docs", "config-reference.md")
+    assert open(path).read() == config_reference.render(), "run: python -m primus_b200.tools.config_reference > docs/config-reference.md"

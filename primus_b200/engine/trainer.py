@@ -153,6 +153,9 @@ class TrainConfig:
     use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
     log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
     train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
+    decoupled_lr: Optional[float] = None         # own learning rate (and decoupled_min_lr) for the embeddings and the output layer
+    decoupled_min_lr: Optional[float] = None
+    head_lr_mult: float = 1.0                    # learning-rate multiplier of the output layer
     rampup_batch_size: Optional[list] = None     # [start, increment, samples]: the global batch grows during the first samples
     ckpt_step: Optional[int] = None              # load the checkpoint of this iteration instead of the newest
     exit_on_missing_checkpoint: bool = False     # ``load`` is set but holds no checkpoint: stop instead of starting fresh
@@ -495,6 +498,22 @@ class Trainer:
         elif train_cfg.optimizer.lower() == "muon":
             extra = dict(muon_momentum=train_cfg.muon_momentum, muon_use_nesterov=train_cfg.muon_use_nesterov,
                          muon_num_ns_steps=train_cfg.muon_num_ns_steps)
+        # learning-rate groups: 1 = embeddings and output layer under ``decoupled_lr``, 2 = the output layer under
+        # ``head_lr_mult`` (Megatron's switches of the same names); the optimizer reads the ``lr_group`` attribute
+        self._lr_groups = set()
+        if train_cfg.decoupled_lr is not None or train_cfg.head_lr_mult != 1.0:
+            for m in self.model_chunks:
+                for name, p in m.named_parameters():
+                    head = name.startswith("output_layer.")
+                    emb = name.startswith("embedding.")
+                    if head and train_cfg.head_lr_mult != 1.0:
+                        p.lr_group = 2
+                    elif (head or emb) and train_cfg.decoupled_lr is not None:
+                        p.lr_group = 1
+                    if getattr(p, "lr_group", 0):
+                        self._lr_groups.add(p.lr_group)
+            if train_cfg.decoupled_lr is not None:
+                self._lr_groups.add(1)
         self.optimizer = matrix_optimizers.build(
             train_cfg.optimizer, self.buffers, **extra, lr=train_cfg.lr, betas=(train_cfg.adam_beta1, train_cfg.adam_beta2), eps=train_cfg.adam_eps,
             weight_decay=train_cfg.weight_decay, clip_grad=train_cfg.clip_grad, norm_groups=norm_groups,
@@ -580,6 +599,13 @@ class Trainer:
             decay_iters=decay_iters, decay_style=train_cfg.lr_decay_style,
             wsd_decay_iters=int(train_cfg.lr_wsd_decay_iters or 0), wsd_decay_style=train_cfg.lr_wsd_decay_style,
             start_wd=start_wd, end_wd=end_wd, wd_incr_style=train_cfg.weight_decay_incr_style)
+        self._decoupled_scheduler = None
+        if train_cfg.decoupled_lr is not None:      # the same shape, between the decoupled maximum and minimum
+            import dataclasses as _dc
+
+            self._decoupled_scheduler = _dc.replace(
+                self.scheduler, max_lr=train_cfg.decoupled_lr,
+                min_lr=train_cfg.min_lr if train_cfg.decoupled_min_lr is None else train_cfg.decoupled_min_lr)
         # ---------------------------------------------------------------- data
         self.num_microbatches = schedules.num_microbatches(train_cfg.global_batch_size, train_cfg.micro_batch_size, st.dp)
         if train_cfg.mock_data or not train_cfg.data_path:
@@ -856,7 +882,15 @@ class Trainer:
             self.optimizer.compute_grad_norm()
             self.lora.optimizer_step(lr)
         else:
-            self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
+            group_lr = None
+            if getattr(self, "_lr_groups", None):
+                group_lr = {1: self._decoupled_scheduler.get_lr(self.iteration + 1)} if 1 in self._lr_groups else {}
+                if 2 in self._lr_groups:
+                    group_lr[2] = (group_lr.get(1, lr) if self.tcfg.decoupled_lr is not None else lr) * self.tcfg.head_lr_mult
+            if group_lr and not self.fsdp:
+                self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1), group_lr=group_lr)
+            else:
+                self.optimizer.step(lr=lr, weight_decay=self.scheduler.get_wd(self.iteration + 1))
         _gemm_ops.roll_fp8_scales()      # delayed scaling: this step's maxima become history (no-op for other recipes)
         if self._emb_primary or self._emb_replica:
             for buf in self.buffers:

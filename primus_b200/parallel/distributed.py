@@ -397,6 +397,7 @@ class DistributedOptimizer:
         self.post_validation = False
         self.post_validation_exact = True
         self.post_validation_redos = 0
+        self._group_lr: dict = {}
         # MXFP4 weight de-oscillation (parallel/weight_deosc.py): runs on the master shards after every update
         self.deosc = None
         self.step_count = 0
@@ -420,7 +421,8 @@ class DistributedOptimizer:
 
     @staticmethod
     def _wd_ranges(buf, b, s, e, no_wd_filter):
-        """Sub-ranges of [s, e) with their weight-decay multiplier (1-D params get 0)."""
+        """Sub-ranges of [s, e) as (lo, hi, weight-decay multiplier, learning-rate group): 1-D params get no weight decay;
+        the group is the parameter's ``lr_group`` attribute (0: the run's learning rate; others: see ``step``)."""
         no_wd_filter = no_wd_filter or (lambda p: p.dim() <= 1)
         ranges = []
         items = sorted(((buf.param_offsets[p], p) for p in b.params), key=lambda t: t[0])
@@ -432,16 +434,16 @@ class DistributedOptimizer:
             if lo >= hi:
                 continue
             if lo > pos:
-                ranges.append((pos, lo, 0.0))  # alignment padding
-            ranges.append((lo, hi, 0.0 if no_wd_filter(p) else 1.0))
+                ranges.append((pos, lo, 0.0, 0))  # alignment padding
+            ranges.append((lo, hi, 0.0 if no_wd_filter(p) else 1.0, int(getattr(p, "lr_group", 0))))
             pos = hi
         if pos < e:
-            ranges.append((pos, e, 0.0))
-        # merge neighbours with the same multiplier
+            ranges.append((pos, e, 0.0, 0))
+        # merge neighbours with the same multiplier and group
         merged = []
         for r in ranges:
-            if merged and merged[-1][2] == r[2] and merged[-1][1] == r[0]:
-                merged[-1] = (merged[-1][0], r[1], r[2])
+            if merged and merged[-1][2:] == r[2:] and merged[-1][1] == r[0]:
+                merged[-1] = (merged[-1][0], r[1], r[2], r[3])
             else:
                 merged.append(r)
         return merged
@@ -541,11 +543,13 @@ class DistributedOptimizer:
         optim_ops.clip_coef_(self.sumsq, self.clip_grad if self.clip_grad else 0.0, self.coef, self.grad_norm)
         bc1 = 1.0 - self.betas[0] ** self.step_count
         bc2 = 1.0 - self.betas[1] ** self.step_count
+        base_lr = lr
         for st in self.state:
             buf = st["buf"]
             tbl = (ctypes.c_long * buf.dp_size)(*[buf.sym_param.peer_ptr(r) for r in range(buf.dp_size)]) \
                 if buf.symmetric else None
-            for lo, hi, mult in st["wd_ranges"]:
+            for lo, hi, mult, grp in st["wd_ranges"]:
+                lr = self._group_lr.get(grp, base_lr)
                 hi4 = min(-(-hi // 4) * 4, st["e"])  # ranges end on parameter boundaries; padding follows
                 a, b_ = lo - st["s"], hi4 - st["s"]
                 if buf.symmetric and not buf.copy_engine_gather:
@@ -576,7 +580,10 @@ class DistributedOptimizer:
                 buf.finish_param_sync()
         return self.grad_norm
 
-    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None):
+    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None, group_lr: Optional[dict] = None):
+        """``group_lr``: learning rates of the parameters whose ``lr_group`` attribute is not 0 (``{group: lr}``;
+        embeddings / output layer under ``decoupled_lr``, the head under ``head_lr_mult``)."""
+        self._group_lr = dict(group_lr or {})
         lr = self.lr if lr is None else lr
         wd = self.weight_decay if weight_decay is None else weight_decay
         self.step_count += 1
@@ -598,9 +605,11 @@ class DistributedOptimizer:
         return self.grad_norm
 
     def _apply_adamw(self, lr: float, wd: float):
+        base_lr = lr
         for st in self.state:
             buf = st["buf"]
-            for lo, hi, mult in st["wd_ranges"]:
+            for lo, hi, mult, grp in st["wd_ranges"]:
+                lr = self._group_lr.get(grp, base_lr)
                 a, b_ = lo - st["s"], hi - st["s"]
                 out = buf.param_data[lo:hi] if buf.param_dtype == torch.bfloat16 else None
                 optim_ops.adamw_step_(st["master"][a:b_], st["m"][a:b_], st["v"][a:b_], buf.grad_data[lo:hi], out,
@@ -667,9 +676,11 @@ class DistributedOptimizer:
         """Undo one un-clipped AdamW update of ``_apply_adamw`` from the gradients that produced it."""
         b1, b2 = self.betas
         bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
+        base_lr = lr
         for st in self.state:
             buf = st["buf"]
-            for lo, hi, mult in st["wd_ranges"]:
+            for lo, hi, mult, grp in st["wd_ranges"]:
+                lr = self._group_lr.get(grp, base_lr)
                 a, b_ = lo - st["s"], hi - st["s"]
                 g = buf.grad_data[lo:hi].float()
                 m, v, p = st["m"][a:b_].float(), st["v"][a:b_].float(), st["master"][a:b_]

@@ -498,3 +498,42 @@ def test_run_control_keys(tmp_path):
         assert e.train() == [] and e.iteration == 0 and any("validation loss" in m for m in logs)
     finally:
         ps.destroy_model_parallel()
+
+
+def test_decoupled_and_head_learning_rates():
+    """``decoupled_lr``: embeddings and output layer follow their own learning rate; ``head_lr_mult`` scales the output
+    layer's.  With learning rate 0 for the rest, only those parameters move."""
+    from primus_b200.engine.trainer import Trainer
+    from primus_b200.parallel import state as ps
+    from tests import dist_workers as W
+
+    def moved(**extra):
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel()
+        mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=2, layers=2, lr=0.0, extra_tc=extra)
+        tr = Trainer(mc, tc, device="cpu", log_fn=lambda m: None)
+        before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+        tr.train()
+        return {n for n, p in tr.model.named_parameters() if not torch.equal(p, before[n])}, tr
+
+    try:
+        assert moved()[0] == set()
+        names, tr = moved(decoupled_lr=1e-2)
+        assert names == {"embedding.word_embeddings.weight", "output_layer.weight"}
+        assert tr._decoupled_scheduler.max_lr == 1e-2 and tr._decoupled_scheduler.decay_style == tr.scheduler.decay_style
+        groups = {g for st in tr.optimizer.state for *_, g in st["wd_ranges"]}
+        assert groups == {0, 1}
+        names, _ = moved(decoupled_lr=1e-2, head_lr_mult=0.0)
+        assert names == {"embedding.word_embeddings.weight"}
+        # a multiplier on the head alone: compare the size of its update with and without
+        def head_delta(**extra):
+            ps.destroy_model_parallel()
+            ps.initialize_model_parallel()
+            mc, tc = W.tiny_cfgs(seq=32, gbs=4, mbs=2, iters=1, layers=2, lr=1e-3, extra_tc=extra)
+            tr = Trainer(mc, tc, device="cpu", log_fn=lambda m: None)
+            w0 = tr.model.output_layer.weight.detach().clone()
+            tr.train()
+            return (tr.model.output_layer.weight - w0).abs().mean().item()
+        assert 2.5 < head_delta(head_lr_mult=3.0) / head_delta() < 3.5
+    finally:
+        ps.destroy_model_parallel()

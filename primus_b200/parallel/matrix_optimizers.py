@@ -64,7 +64,8 @@ class _PerParameterOptimizer(DistributedOptimizer):
         for st in self.state:
             st["buf"].param_data[st["s"]:st["e"]].copy_(st["master"])
 
-    def step(self, lr=None, weight_decay=None):
+    def step(self, lr=None, weight_decay=None, group_lr=None):
+        assert not group_lr, "decoupled_lr / head_lr_mult are built for the Adam optimizer"
         lr = self.lr if lr is None else lr
         wd = self.weight_decay if weight_decay is None else weight_decay
         self.step_count += 1

@@ -153,6 +153,12 @@ class TrainConfig:
     use_tp_pp_dp_mapping: bool = False           # rank order tensor, context, pipeline, data (default: ..., data, pipeline)
     log_throughput: bool = True                  # TFLOP/s/GPU and tokens/s/GPU in the per-iteration log line
     train_samples: Optional[int] = None          # alternative to train_iters: stop after this many samples
+    # costs for the cost-driven zero-bubble tables, given instead of measured (a number, or one per virtual stage)
+    pp_cost_f: object = None
+    pp_cost_b: object = None
+    pp_cost_w: object = None
+    pp_max_mem: object = None                    # activation limit per pipeline rank, in chunk-forwards
+    debug_scheduler_table: bool = False          # print the schedule table when it is built
     decoupled_lr: Optional[float] = None         # own learning rate (and decoupled_min_lr) for the embeddings and the output layer
     decoupled_min_lr: Optional[float] = None
     head_lr_mult: float = 1.0                    # learning-rate multiplier of the output layer

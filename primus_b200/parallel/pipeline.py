@@ -63,6 +63,28 @@ def _p2p_shape(trainer, batch, seq, model=None):
     return (T, trainer.mcfg.hidden_size)
 
 
+def manual_costs(tc, pp: int, chunks: int):
+    """``StageCosts`` from the config's ``pp_cost_f`` / ``pp_cost_b`` / ``pp_cost_w`` (a number for every stage or one per
+    virtual stage; missing ones default to 1000 like the reference's heuristic) and ``pp_max_mem`` (activation limit per
+    rank in chunk-forwards); None when none of them is set.  (primus/configs/modules/megatron/primus_pipeline.yaml:14-17.)"""
+    vals = [getattr(tc, k, None) for k in ("pp_cost_f", "pp_cost_b", "pp_cost_w")]
+    mem = getattr(tc, "pp_max_mem", None)
+    if all(v is None for v in vals) and mem is None:
+        return None
+    S = pp * chunks
+
+    def per_stage(v):
+        if v is None:
+            return [1000.0] * S
+        if isinstance(v, (int, float)):
+            return [float(v)] * S
+        assert len(v) == S, f"pipeline costs: {len(v)} values for {S} virtual stages"
+        return [float(x) for x in v]
+
+    limit = None if mem is None else ([float(mem)] * pp if isinstance(mem, (int, float)) else [float(x) for x in mem])
+    return sched.StageCosts(per_stage(vals[0]), per_stage(vals[1]), per_stage(vals[2]), 0.0, limit)
+
+
 def _pos_ids(trainer, mb):
     use = getattr(trainer, "use_position_ids", False) or trainer.st.cp > 1 or getattr(trainer, "num_seq_splits", 1) > 1
     return mb.get("position_ids") if use else None
@@ -85,6 +107,15 @@ def run_pipeline_schedule(trainer, micro_batches: list[dict], timeline: Pipeline
         if st.virtual_pp and st.virtual_pp > 1 and algo == "1f1b":
             algo = "interleaved"
         cache[key] = sched.build_schedule(algo, pp, m, st.virtual_pp, num_seq_splits=nsplit)
+        manual = manual_costs(trainer.tcfg, pp, cache[key]["chunks"])
+        if manual is not None and nsplit == 1 and algo.lower().replace("_", "-") in (
+                "zerobubble", "zero-bubble", "zb", "zbv", "zbv-greedy", "zbv-formatted", "v-half", "v-min"):
+            # costs given in the config (``pp_cost_f / _b / _w``, ``pp_max_mem``): the cost-driven table from the start
+            cache[key] = sched.auto_schedule(algo, pp, m, manual)
+        if getattr(trainer.tcfg, "debug_scheduler_table", False) and r == 0 and st.dp_rank == 0 and st.tp_rank == 0:
+            rows = ["  ".join(f"{n.kind}{n.mb}" + (f".{n.chunk}" if cache[key]["chunks"] > 1 else "") for n in row)
+                    for row in cache[key]["table"]]
+            trainer.log("[pipeline] schedule table (one row per rank):\n" + "\n".join(rows))
         trainer._pp_schedule_cache = cache
     sch = cache[key]
     chunks, placement = sch["chunks"], sch["placement"]

@@ -82,6 +82,8 @@ CASES = {
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
+    "pp2_zerobubble_manual_costs": dict(world=2, kw=dict(pp=2, schedule="zerobubble", extra_tc=dict(
+        pp_cost_f=[1000, 1400], pp_cost_b=1200, pp_cost_w=700, pp_max_mem=4, debug_scheduler_table=True))),
     # every micro-batch travels through the pipeline as two / four sequence chunks (attention over the kept K / V)
     "pp2_seq_splits2": dict(world=2, kw=dict(pp=2, extra_tc=dict(num_seq_splits=2))),
     "pp2_tp2_seq_splits4": dict(world=4, kw=dict(pp=2, tp=2, sp=True, extra_tc=dict(num_seq_splits=4))),

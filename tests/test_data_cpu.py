@@ -185,3 +185,39 @@ def test_batch_size_rampup(tmp_path):
     assert counts == [(1, 2), (1, 2), (2, 4), (3, 6), (4, 8)]        # stretches of 4 samples: 2, 2 | 4 | 6 | 8
     assert any("global batch size:     6" in m for m in logs)
     ps.destroy_model_parallel()
+
+
+def test_data_subcommand_blend_inspect_and_pack(tmp_path, capsys):
+    import argparse
+    import json
+
+    import numpy as np
+
+    from primus_b200.cli.subcommands import data as D
+    from primus_b200.engine.indexed_dataset import write_indexed_dataset
+
+    def run(*argv):
+        ap = argparse.ArgumentParser()
+        D.register_subcommand(ap.add_subparsers(dest="cmd"))
+        a = ap.parse_args(["data", *argv])
+        assert D.run(a, []) == 0
+        return capsys.readouterr().out
+
+    rng = np.random.default_rng(0)
+    for name, docs in (("a", 40), ("b", 10)):
+        write_indexed_dataset(str(tmp_path / name), [rng.integers(0, 100, size=100).astype(np.int32) for _ in range(docs)],
+                              dtype=np.int32)
+    info = json.loads(run("inspect", "--path", str(tmp_path / "a"), "--seq-length", "32"))
+    assert info["format"] == "megatron" and info["documents"] == 40 and info["tokens"] == 4000 and info["samples"] == 124
+    plan = json.loads(run("blend", "--data-path", f"3 {tmp_path / 'a'} 1 {tmp_path / 'b'}", "--seq-length", "32",
+                          "--samples", "400"))
+    a, b = plan["datasets"]
+    assert (a["weight"], b["weight"]) == (0.75, 0.25) and a["samples_drawn"] == 300 and b["samples_drawn"] == 100
+    assert a["epochs"] == round(300 / 124, 3) and b["epochs"] == round(100 / 31, 3)      # the small corpus repeats more
+    recs = tmp_path / "sft.jsonl"
+    recs.write_text("\n".join(json.dumps({"instruction": f"add {i}", "input": "", "output": str(i) * 5}) for i in range(30)))
+    out = run("pack-sft", "--input", str(recs), "--seq-length", "256", "--cache-dir", str(tmp_path / "cache"))
+    res = json.loads(out.strip().splitlines()[-1])
+    assert res["packs"] >= 1 and len(list((tmp_path / "cache").iterdir())) == 1
+    again = run("pack-sft", "--input", str(recs), "--seq-length", "256", "--cache-dir", str(tmp_path / "cache"))
+    assert json.loads(again.strip().splitlines()[-1]) == res and len(list((tmp_path / "cache").iterdir())) == 1

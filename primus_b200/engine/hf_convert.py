@@ -54,10 +54,16 @@ def config_from_hf(hf: dict) -> dict:
             out.update(moe_layer_freq=[1] * hf["num_hidden_layers"], moe_router_pre_softmax=False,
                        moe_shared_expert_intermediate_size=hf.get("shared_expert_intermediate_size") or None,
                        moe_shared_expert_gate=bool(hf.get("shared_expert_intermediate_size")))
-    if mt == "lfm2":        # gated short convolutions + grouped-query attention with per-head q / k norms
+    if mt in ("lfm2", "lfm2_moe"):   # gated short convolutions + grouped-query attention with per-head q / k norms
         out.update(lfm_layer_types=list(hf["layer_types"]), conv_L_cache=hf.get("conv_L_cache", 3),
                    conv_bias=bool(hf.get("conv_bias", False)), qk_layernorm=True, norm_epsilon=hf.get("norm_eps", 1e-5),
                    ffn_hidden_size=hf.get("block_ff_dim") or hf.get("intermediate_size"))
+    if mt == "lfm2_moe":    # dense first layers, then sigmoid-scored experts chosen with a selection-only bias
+        k_dense = hf.get("num_dense_layers", 0)
+        out.update(moe_layer_freq=[int(i >= k_dense) for i in range(hf["num_hidden_layers"])],
+                   ffn_hidden_size=hf["intermediate_size"], moe_router_score_function="sigmoid",
+                   moe_router_enable_expert_bias=bool(hf.get("use_expert_bias", True)),
+                   moe_router_topk_scaling_factor=hf.get("routed_scaling_factor") or None)
     if mt == "qwen2" or (mt == "llama" and hf.get("attention_bias")):
         out["add_qkv_bias"] = True       # Qwen2 / Qwen2.5: biases on q, k and v (not on the output projection)
     E = hf.get("num_experts") or hf.get("num_local_experts") or hf.get("n_routed_experts")
@@ -175,11 +181,73 @@ def _lfm2_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tenso
             sd[a + "q_layernorm.weight"] = hf[h + "self_attn.q_layernorm.weight"]
             sd[a + "k_layernorm.weight"] = hf[h + "self_attn.k_layernorm.weight"]
             sd[a + "linear_proj.weight"] = hf[h + "self_attn.out_proj.weight"]
-        m = p + "mlp."
+        m, f = p + "mlp.", h + "feed_forward."
+        if cfg.is_moe_layer(L):     # Lfm2Moe: stacked experts [E, 2 * ffn (gate | up), hidden], bias used for selection only
+            sd[p + "pre_mlp_layernorm.weight"] = hf[h + "ffn_norm.weight"]
+            sd[m + "router.weight"] = hf[f + "gate.weight"]
+            if cfg.moe_router_enable_expert_bias:
+                sd[m + "router.expert_bias"] = hf[f + "expert_bias"].float()
+            if f + "experts.gate_up_proj" in hf:
+                sd[m + "experts.fc1_weight.weight"] = hf[f + "experts.gate_up_proj"]
+                sd[m + "experts.fc2_weight.weight"] = hf[f + "experts.down_proj"]
+            else:                   # published checkpoints: one w1 (gate) / w3 (up) / w2 (down) per expert
+                sd[m + "experts.fc1_weight.weight"] = torch.stack(
+                    [torch.cat([hf[f + f"experts.{e}.w1.weight"], hf[f + f"experts.{e}.w3.weight"]], 0)
+                     for e in range(cfg.num_experts)])
+                sd[m + "experts.fc2_weight.weight"] = torch.stack(
+                    [hf[f + f"experts.{e}.w2.weight"] for e in range(cfg.num_experts)])
+            continue
         sd[m + "linear_fc1.layer_norm_weight"] = hf[h + "ffn_norm.weight"]
-        sd[m + "linear_fc1.weight"] = torch.cat([hf[h + "feed_forward.w1.weight"], hf[h + "feed_forward.w3.weight"]], 0)
-        sd[m + "linear_fc2.weight"] = hf[h + "feed_forward.w2.weight"]
+        sd[m + "linear_fc1.weight"] = torch.cat([hf[f + "w1.weight"], hf[f + "w3.weight"]], 0)
+        sd[m + "linear_fc2.weight"] = hf[f + "w2.weight"]
     return sd
+
+
+def _lfm2_from_internal(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool) -> Dict[str, torch.Tensor]:
+    """Inverse of `_lfm2_to_internal` (names of transformers' Lfm2 / Lfm2Moe models)."""
+    hf: Dict[str, torch.Tensor] = {}
+    V = cfg.vocab_size
+    hf["model.embed_tokens.weight"] = sd["embedding.word_embeddings.weight"][:V]
+    hf["model.embedding_norm.weight"] = sd["decoder.final_layernorm.weight"]
+    if cfg.untie_embeddings_and_output_weights:
+        hf["lm_head.weight"] = sd["output_layer.weight"][:V]
+    nq, nkv = cfg.num_attention_heads * cfg.kv_channels, cfg.num_query_groups * cfg.kv_channels
+    for L in range(cfg.num_layers):
+        p, h = f"decoder.layers.{L}.", f"model.layers.{L}."
+        a = p + "self_attention."
+        if cfg.layer_kinds[L][0] == "conv":
+            hf[h + "operator_norm.weight"] = sd[a + "in_proj.layer_norm_weight"]
+            for ours, theirs in (("in_proj", "conv.in_proj"), ("conv", "conv.conv"), ("out_proj", "conv.out_proj")):
+                hf[h + theirs + ".weight"] = sd[a + ours + ".weight"]
+                if cfg.conv_bias:
+                    hf[h + theirs + ".bias"] = sd[a + ours + ".bias"]
+        else:
+            hf[h + "operator_norm.weight"] = sd[a + "linear_qkv.layer_norm_weight"]
+            w = sd[a + "linear_qkv.weight"]
+            hf[h + "self_attn.q_proj.weight"], hf[h + "self_attn.k_proj.weight"], hf[h + "self_attn.v_proj.weight"] = \
+                w[:nq], w[nq:nq + nkv], w[nq + nkv:]
+            hf[h + "self_attn.q_layernorm.weight"] = sd[a + "q_layernorm.weight"]
+            hf[h + "self_attn.k_layernorm.weight"] = sd[a + "k_layernorm.weight"]
+            hf[h + "self_attn.out_proj.weight"] = sd[a + "linear_proj.weight"]
+        m, f = p + "mlp.", h + "feed_forward."
+        if cfg.is_moe_layer(L):
+            hf[h + "ffn_norm.weight"] = sd[p + "pre_mlp_layernorm.weight"]
+            hf[f + "gate.weight"] = sd[m + "router.weight"]
+            if cfg.moe_router_enable_expert_bias:
+                hf[f + "expert_bias"] = sd[m + "router.expert_bias"]
+            w1, w2 = sd[m + "experts.fc1_weight.weight"], sd[m + "experts.fc2_weight.weight"]
+            I = w1.shape[1] // 2
+            if stacked_experts:
+                hf[f + "experts.gate_up_proj"], hf[f + "experts.down_proj"] = w1, w2
+            for e in range(0 if stacked_experts else cfg.num_experts):
+                hf[f + f"experts.{e}.w1.weight"], hf[f + f"experts.{e}.w3.weight"] = w1[e, :I], w1[e, I:]
+                hf[f + f"experts.{e}.w2.weight"] = w2[e]
+            continue
+        hf[h + "ffn_norm.weight"] = sd[m + "linear_fc1.layer_norm_weight"]
+        w = sd[m + "linear_fc1.weight"]
+        hf[f + "w1.weight"], hf[f + "w3.weight"] = w[: w.shape[0] // 2], w[w.shape[0] // 2:]
+        hf[f + "w2.weight"] = sd[m + "linear_fc2.weight"]
+    return hf
 
 
 def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
@@ -273,6 +341,8 @@ def hf_to_internal(hf: Dict[str, torch.Tensor], cfg) -> Dict[str, torch.Tensor]:
 
 
 def internal_to_hf(sd: Dict[str, torch.Tensor], cfg, stacked_experts: bool = False) -> Dict[str, torch.Tensor]:
+    if cfg.lfm_layer_types:
+        return _lfm2_from_internal(sd, cfg, stacked_experts)
     hf: Dict[str, torch.Tensor] = {}
     V = cfg.vocab_size
     hf["model.embed_tokens.weight"] = sd["embedding.word_embeddings.weight"][:V]

@@ -131,6 +131,28 @@ def test_mixtral_matches_hf():
     assert conv.keys() == new.keys() and all(torch.equal(conv[k], new[k]) for k in new)
 
 
+def test_lfm2_moe_matches_hf():
+    """Short convolutions + attention, two dense layers, then sigmoid-scored experts whose bias only steers the selection."""
+    T = pytest.importorskip("transformers.models.lfm2_moe")
+
+    torch.manual_seed(6)
+    c = T.Lfm2MoeConfig(vocab_size=250, hidden_size=64, intermediate_size=128, moe_intermediate_size=48,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                        layer_types=["conv", "full_attention", "conv", "full_attention"], conv_L_cache=3, conv_bias=False,
+                        num_dense_layers=1, num_experts=8, num_experts_per_tok=2, use_expert_bias=True,
+                        norm_topk_prob=True, routed_scaling_factor=1.5, tie_word_embeddings=True)
+    m = T.Lfm2MoeForCausalLM(c)
+    with torch.no_grad():
+        for layer in m.model.layers[1:]:
+            layer.feed_forward.expert_bias.copy_(torch.randn(8) * 0.3)      # makes the selection differ from plain top-k
+            layer.feed_forward.experts.gate_up_proj.normal_(0, 0.05)
+            layer.feed_forward.experts.down_proj.normal_(0, 0.05)
+    _check(m, c, torch.randint(0, 250, (2, 24)))
+    kw = H.config_from_hf(c.to_dict())
+    assert kw["moe_layer_freq"] == [0, 1, 1, 1] and kw["moe_router_score_function"] == "sigmoid"
+    assert kw["moe_router_topk_scaling_factor"] == 1.5 and kw["moe_ffn_hidden_size"] == 48
+
+
 def test_qwen3_5_moe_matches_hf():
     """Gated-delta-net layers with grouped key heads, gated full attention with partial rotary embedding, zero-centred norm
     gains and a gated shared expert."""

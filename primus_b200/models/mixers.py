@@ -76,38 +76,60 @@ def causal_depthwise_conv(x: torch.Tensor, weight: torch.Tensor, bias, batch: in
 
 
 class ShortConvMixer(nn.Module):
-    """LFM2 double-gated short convolution (parameter names follow the reference: ``in_proj``, ``conv``, ``out_proj``)."""
+    """LFM2 double-gated short convolution (parameter names follow the reference: ``in_proj``, ``conv``, ``out_proj``).
+
+    Tensor parallelism splits the channels: every rank holds its slice of the three ``in_proj`` blocks (B, C, x), of the
+    depthwise filter and of the columns of ``out_proj``; with sequence parallelism the normalised tokens are gathered
+    before ``in_proj`` and the output projection is reduce-scattered."""
 
     def __init__(self, cfg, layer_idx: int, device, tp: int):
         super().__init__()
-        assert tp == 1, "the short-convolution mixer is not built for tensor parallelism"
-        self.cfg = cfg
+        assert tp == 1 or cfg.sequence_parallel, "the short-convolution mixer under tensor parallelism needs sequence_parallel"
+        assert cfg.hidden_size % tp == 0, "hidden_size must divide by the tensor-parallel size"
+        self.cfg, self.tp = cfg, tp
         h, dt = cfg.hidden_size, cfg.torch_dtype
+        self.hl = hl = h // tp                     # this rank's channels
         std = cfg.init_method_std
         self.in_proj = nn.Module()
         self.in_proj.register_parameter("layer_norm_weight", nn.Parameter(torch.ones(h, dtype=dt, device=device)))
-        self.in_proj.register_parameter("weight", _param((3 * h, h), std, dt, device))
+        self.in_proj.register_parameter("weight", _param((3 * hl, h), std, dt, device))
         self.conv = nn.Module()
-        self.conv.register_parameter("weight", _param((h, 1, cfg.conv_L_cache), std, dt, device))
+        self.conv.register_parameter("weight", _param((hl, 1, cfg.conv_L_cache), std, dt, device))
         self.out_proj = nn.Module()
-        self.out_proj.register_parameter("weight", _param((h, h), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
+        self.out_proj.register_parameter("weight", _param((h, hl), std / math.sqrt(2.0 * cfg.num_layers), dt, device))
         if cfg.conv_bias:
-            for m, n in ((self.in_proj, 3 * h), (self.conv, h), (self.out_proj, h)):
+            for m, n in ((self.in_proj, 3 * hl), (self.conv, hl), (self.out_proj, h)):
                 m.register_parameter("bias", nn.Parameter(torch.zeros(n, dtype=dt, device=device)))
         for w in (self.in_proj.weight, self.out_proj.weight):
             w._is_weight = True
+        if tp > 1:
+            _mark_tp(self.in_proj.weight, 0, [h, h, h])
+            _mark_tp(self.conv.weight, 0)
+            _mark_tp(self.out_proj.weight, 1)
+            # replicated, each rank sees its tokens only: gradients are summed over the group
+            self.in_proj.layer_norm_weight.sequence_parallel = True
+            if cfg.conv_bias:
+                _mark_tp(self.in_proj.bias, 0, [h, h, h])
+                _mark_tp(self.conv.bias, 0)
+                self.out_proj.bias.sequence_parallel = True
 
     def forward(self, hidden, residual, rope, batch):
         cfg = self.cfg
-        assert ps.get_state().cp == 1, "the short-convolution mixer is not built for context parallelism"
+        st = ps.get_state()
+        assert st.cp == 1, "the short-convolution mixer is not built for context parallelism"
         y, xsum = _norm(hidden, residual, self.in_proj.layer_norm_weight, cfg.norm_epsilon)
+        if self.tp > 1:
+            y = tpc.gather_seq(y, st.tp_group)
         bcx = gemm.linear(y, self.in_proj.weight)
         if cfg.conv_bias:
             bcx = bcx + self.in_proj.bias
-        h = cfg.hidden_size
+        h = self.hl
         B, C, x = bcx[:, :h], bcx[:, h:2 * h], bcx[:, 2 * h:]
         conv = causal_depthwise_conv(B * x, self.conv.weight[:, 0, :], self.conv.bias if cfg.conv_bias else None, batch)
-        out = gemm.linear((C * conv).contiguous(), self.out_proj.weight)
+        if self.tp > 1:
+            out = layers.row_parallel_linear((C * conv).contiguous(), self.out_proj.weight, st.tp_group, True)
+        else:
+            out = gemm.linear((C * conv).contiguous(), self.out_proj.weight)
         if cfg.conv_bias:
             out = out + self.out_proj.bias
         return out, xsum

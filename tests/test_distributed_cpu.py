@@ -62,6 +62,9 @@ CASES = {
         model_type="mamba", is_hybrid_model=True, linear_attention_type="kda", linear_num_key_heads=4,
         linear_num_value_heads=4, linear_key_head_dim=8, linear_value_head_dim=16, kda_use_full_rank_gate=False,
         kda_gate_lower_bound=None, kda_chunk_size=16))),
+    # LFM2: channel-split gated short convolutions (with biases) between grouped-query attention layers
+    "tp2_sp_lfm2": dict(world=2, kw=dict(tp=2, sp=True, layers=4, extra_mc=dict(
+        lfm_layer_types=["conv", "full_attention", "conv", "conv"], conv_L_cache=3, conv_bias=True, qk_layernorm=True))),
     "tp2_sp_mamba_hybrid": dict(world=2, kw=dict(tp=2, sp=True, layers=6, extra_mc=dict(
         model_type="mamba", is_hybrid_model=True, hybrid_attention_ratio=0.34, mamba_state_dim=16, mamba_head_dim=16,
         mamba_num_groups=2, mamba_chunk_size=16))),

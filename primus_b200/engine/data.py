@@ -232,7 +232,8 @@ class BatchStager:
         self.prefetch()
         dev, ev, nbytes = self._next
         self._next = None
-        self._starts.pop(0)
+        if self._starts:            # a stager that overrides _load_host without recording starts keeps working
+            self._starts.pop(0)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
             for b in dev:

@@ -201,6 +201,7 @@ class LBMiniStager(BatchStager):
 
     def _load_host(self) -> list[dict]:
         n = len(self.base)
+        self._starts.append(self.sampler.consumed)      # kept until the step has been trained on (exact resume)
         ids = [(self.sampler.consumed + i) % n for i in range(self.gbs)]
         self.sampler.consumed += self.gbs
         lengths = [self._aligned(len(self.base.samples[j][0]) - 1) for j in ids]

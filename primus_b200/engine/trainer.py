@@ -147,6 +147,12 @@ class TrainConfig:
     zero_bubble_max_pending_backward: object = "auto"   # int: activation budget per rank in forwards instead of adaptive
     pipeline_model_parallel_layout: Optional[str] = None
     decoder_pipeline_manual_split_list: Optional[list] = None
+    # uneven splits without a layout string: sizes of the first / last stage (the others share the rest evenly), or the
+    # embedding / output layer counted as one layer of their stage
+    decoder_first_pipeline_num_layers: Optional[int] = None
+    decoder_last_pipeline_num_layers: Optional[int] = None
+    account_for_embedding_in_pipeline_split: bool = False
+    account_for_loss_in_pipeline_split: bool = False
     manual_gc: bool = True
     fused_dp_optimizer: bool = False  # P2P reduce-scatter + AdamW kernel over symmetric memory
     num_workers: int = 0                         # data loading threads (0: the training thread loads its own batches)
@@ -393,11 +399,17 @@ class Trainer:
         n_stages = st.pp * self.pp_chunks
         self.loss_pp_rank = pps.rank_of_stage(n_stages - 1, st.pp, self.pp_placement)[0] if st.pp > 1 else 0
         self.model_chunks = []
+        from ..parallel.pipeline_layout import uneven_split
+
+        manual_split = train_cfg.decoder_pipeline_manual_split_list or uneven_split(
+            model_cfg.num_layers, n_stages, train_cfg.decoder_first_pipeline_num_layers,
+            train_cfg.decoder_last_pipeline_num_layers, train_cfg.account_for_embedding_in_pipeline_split,
+            train_cfg.account_for_loss_in_pipeline_split)
         for c in range(self.pp_chunks):
             sid = pps.stage_of(st.pp_rank, c, st.pp, self.pp_placement) if st.pp > 1 else 0
             m = build_model(model_cfg, self.device, sid, n_stages, seed=train_cfg.seed,
                             layout=getattr(train_cfg, "pipeline_model_parallel_layout", None),
-                            manual_split=getattr(train_cfg, "decoder_pipeline_manual_split_list", None))
+                            manual_split=manual_split)
             self.model_chunks.append(m)
         self.model = self.model_chunks[0]
         self._init_embedding_replica()

@@ -46,14 +46,22 @@ class ParallelPlan:
     def grad_accum(self) -> int:
         return max(1, self.global_batch // (self.micro_batch * self.dp))
 
+    def layers_per_stage(self, num_layers: int) -> int:
+        """Layers of every stage but the last (the last one is shorter when the depth has no even split:
+        ``decoder_last_pipeline_num_layers``)."""
+        return -(-num_layers // (self.pp * self.vpp))
+
+    def last_stage_layers(self, num_layers: int) -> int:
+        return num_layers - self.layers_per_stage(num_layers) * (self.pp * self.vpp - 1)
+
     def validate(self, cfg) -> list[str]:
         errs = []
         if self.world % (self.tp * self.pp * self.cp):
             errs.append("world size not divisible by tp*pp*cp")
         if cfg.num_attention_heads % self.tp or cfg.num_query_groups % self.tp:
             errs.append("attention heads not divisible by tp")
-        if cfg.num_layers % (self.pp * self.vpp):
-            errs.append("layers not divisible by pp*vpp")
+        if cfg.num_layers % (self.pp * self.vpp) and (self.vpp > 1 or self.last_stage_layers(cfg.num_layers) < 1):
+            errs.append("layers not divisible by pp*vpp")       # vpp = 1: a shorter last stage takes the remainder
         if cfg.num_experts and (cfg.num_experts % self.ep or (self.tp * self.cp * self.dp) % self.ep):
             errs.append("experts / ranks not divisible by ep")
         if self.global_batch % (self.micro_batch * self.dp):
@@ -115,11 +123,11 @@ def project_memory(cfg, plan: ParallelPlan, margin: float = 0.05, context_reserv
     pc = param_counts(cfg)
     L = cfg.num_layers
     stages = plan.pp * plan.vpp
-    per_stage = L // stages
+    per_stage = plan.layers_per_stage(L)
     # worst stage: first (embedding) or last (output layer + logits); take both and report the max
     results = {}
     for which in ("first", "last"):
-        idx = list(range(0, per_stage)) if which == "first" else list(range(L - per_stage, L))
+        idx = list(range(0, per_stage)) if which == "first" else list(range(L - plan.last_stage_layers(L), L))
         layer_sets = [idx]
         if plan.vpp > 1:  # a rank owns vpp chunks; approximate with vpp copies of this stage's layer mix
             layer_sets = [idx] * plan.vpp

@@ -128,7 +128,7 @@ def project_performance(cfg, plan: ParallelPlan, hw: Hardware, schedule: str = "
     L = cfg.num_layers
     chunks = 2 if schedule in ("zbv", "v-half", "v-min", "zbv-formatted") else plan.vpp
     stages = plan.pp * chunks
-    per_stage = L // stages
+    per_stage = -(-L // stages)         # the slowest stage; a shorter last stage takes the remainder of an uneven depth
     T = plan.micro_batch * plan.seq / plan.cp
     peak = hw.bf16_tflops * 1e12
     head = 2.0 * T * cfg.hidden_size * cfg.padded_vocab_size / plan.tp

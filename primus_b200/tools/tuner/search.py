@@ -35,6 +35,7 @@ class Candidate:
     mfu: float
     iteration_ms: float
     bubble: float
+    last_stage_layers: int = 0       # > 0: the depth has no even split and the last stage holds this many layers
 
     def overrides(self) -> list[str]:
         p = self.plan
@@ -44,6 +45,8 @@ class Candidate:
                f"--sequence_parallel={'true' if p.tp > 1 else 'false'}", f"--pp_algorithm={self.schedule}"]
         if p.vpp > 1:
             out.append(f"--virtual_pipeline_model_parallel_size={p.vpp}")
+        if self.last_stage_layers:
+            out.append(f"--decoder_last_pipeline_num_layers={self.last_stage_layers}")
         if p.recompute_layers:
             # the memory model counts `recompute_layers` layers per stage without saved activations: method "block"
             out += ["--recompute_granularity=full", "--recompute_method=block",
@@ -55,15 +58,33 @@ class Candidate:
         return {"tp": p.tp, "pp": p.pp, "vpp": p.vpp, "ep": p.ep, "cp": p.cp, "dp": p.dp, "micro_batch": p.micro_batch,
                 "grad_accum": p.grad_accum, "recompute_layers": p.recompute_layers, "schedule": self.schedule,
                 "peak_gb": round(self.peak_gb, 1), "tokens_per_s_per_gpu": round(self.tokens_per_s_per_gpu, 1),
-                "mfu": round(self.mfu, 4), "iteration_ms": round(self.iteration_ms, 1), "bubble": round(self.bubble, 4)}
+                "mfu": round(self.mfu, 4), "iteration_ms": round(self.iteration_ms, 1), "bubble": round(self.bubble, 4),
+                **({"last_stage_layers": self.last_stage_layers} if self.last_stage_layers else {})}
+
+
+def context_parallel_supported(cfg) -> bool:
+    """Context parallelism is built for softmax attention that runs on the flash-attention kernels: not for the
+    recurrent / convolution mixers, the DeepSeek-V4 attention, sliding windows, sinks, soft-capped scores, or head sizes
+    that fall back to composed operations."""
+    from ...ops.attention import kernel_supports
+
+    if any(kind[0] not in (None, "attention") for kind in cfg.layer_kinds):
+        return False
+    if getattr(cfg, "window_size", None) or getattr(cfg, "softmax_type", "vanilla") != "vanilla" \
+            or getattr(cfg, "attn_logit_softcapping", None):
+        return False
+    if cfg.multi_latent_attention:
+        return kernel_supports(cfg.qk_head_dim + cfg.qk_pos_emb_head_dim, cfg.v_head_dim)
+    return kernel_supports(cfg.kv_channels, cfg.kv_channels)
 
 
 def enumerate_plans(cfg, world: int, global_batch: int, seq: int, gpus_per_node: int = 8, max_micro_batch: int = 8,
                     fused_tp: bool = True) -> Iterable[tuple[ParallelPlan, str]]:
     L = cfg.num_layers
+    cp_ok = context_parallel_supported(cfg)
     for tp, pp, cp in itertools.product(_divisors(world, gpus_per_node), _divisors(world, min(world, L)),
                                         _divisors(world, gpus_per_node)):
-        if world % (tp * pp * cp):
+        if world % (tp * pp * cp) or (cp > 1 and not cp_ok):
             continue
         if cfg.num_experts and tp > 1:
             continue  # the projection has no model of MoE layers under tensor parallelism: such plans are not proposed
@@ -101,8 +122,10 @@ def search(cfg, hw: Hardware, world: int, global_batch: int, seq: int, top: int 
             perf = project_performance(cfg, plan, hw, schedule, comm_overlap=comm_overlap if plan.fused_tp else 0.0)
         except Exception:  # noqa: BLE001  (a schedule that cannot be built for this (pp, micro-batch count))
             continue
+        uneven = cfg.num_layers % (plan.pp * plan.vpp) != 0
         cands.append(Candidate(plan, schedule, mem["peak_gb"], perf["tokens_per_s_per_gpu"], perf["mfu"],
-                               perf["iteration_ms"], perf["bubble_fraction"]))
+                               perf["iteration_ms"], perf["bubble_fraction"],
+                               plan.last_stage_layers(cfg.num_layers) if uneven else 0))
     cands.sort(key=lambda c: -c.tokens_per_s_per_gpu)
     return {"enumerated": seen, "fit_in_memory": fits, "best": cands[:top]}
 

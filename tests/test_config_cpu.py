@@ -177,10 +177,49 @@ def test_example_configs_pass_the_schema_check():
     from primus_b200.core.config import schema_check
 
     root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "configs")
-    for f in sorted(os.listdir(root)):
-        with open(os.path.join(root, f)) as fh:
+    files = [os.path.join(d, f) for d, _, fs in os.walk(root) for f in fs if f.endswith(".yaml")]
+    assert len(files) > 100
+    for f in sorted(files):
+        with open(f) as fh:
             raw = yaml.safe_load(fh)
         assert schema_check.check_experiment(raw) == [], f
+
+
+def test_recipe_book_plans_are_legal_and_fit():
+    """Every generated recipe loads, names a plan that the legality check accepts on its node count, and fits the
+    memory of the part according to the projection that the generator used."""
+    import re
+
+    from primus_b200.core.config.presets import load_preset
+    from primus_b200.models.config import TransformerConfig
+    from primus_b200.tools import recipes
+    from primus_b200.tools.projection.memory import ParallelPlan, project_memory
+
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "configs", "b200")
+    files = sorted(f for f in os.listdir(root) if f.endswith(".yaml"))
+    # one BF16 and one MXFP8 recipe per model, except those the index lists as not fitting
+    index = open(os.path.join(root, "index.md")).read()
+    for m in recipes.model_names():
+        for prec in ("BF16", "MXFP8"):
+            assert f"{m}-{prec}-pretrain.yaml" in files or f"{m} ({prec})" in index, (m, prec)
+    for f in files:
+        head = open(os.path.join(root, f)).readline()
+        nodes = int(re.search(r"(\d+) node", head).group(1))
+        e = experiment.load_experiment(os.path.join(root, f))
+        ov = e.modules["pre_trainer"].params
+        g = lambda k, d=1: int(ov.get(k) or d)
+        d = dict(load_preset(f.split("-")[0], "models"))
+        cfg = TransformerConfig.from_dict(d)
+        plan = ParallelPlan(world=8 * nodes, tp=g("tensor_model_parallel_size"), pp=g("pipeline_model_parallel_size"),
+                            cp=g("context_parallel_size"), ep=g("expert_model_parallel_size"),
+                            vpp=g("virtual_pipeline_model_parallel_size"), micro_batch=g("micro_batch_size"),
+                            global_batch=g("global_batch_size"), seq=g("seq_length"),
+                            recompute_layers=g("recompute_num_layers", 0), sequence_parallel=g("tensor_model_parallel_size") > 1,
+                            fused_tp=g("tensor_model_parallel_size") > 1)
+        assert plan.validate(cfg) == [], (f, plan.validate(cfg))
+        assert project_memory(cfg, plan)["peak_gb"] <= 180.0, f
+        if cfg.num_layers % (plan.pp * plan.vpp):
+            assert g("decoder_last_pipeline_num_layers", 0) == plan.last_stage_layers(cfg.num_layers), f
 
 
 def test_every_preset_key_is_read_or_declared_inert():

@@ -83,6 +83,12 @@ CASES = {
                                                           extra_tc=dict(use_tp_pp_dp_mapping=True))),
     "pp2_interleaved": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved")),
     "pp2_warmup": dict(world=2, kw=dict(pp=2, vpp=2, schedule="interleaved", pp_warmup=True)),
+    # uneven stages: a short last stage, a layout string, the embedding counted as a layer, interleaved chunks of 2-1-1-1
+    "pp2_uneven_last": dict(world=2, kw=dict(pp=2, extra_tc=dict(decoder_last_pipeline_num_layers=1))),
+    "pp2_layout_string": dict(world=2, kw=dict(pp=2, extra_tc=dict(pipeline_model_parallel_layout="Et|tttL"))),
+    "pp2_account_embedding": dict(world=2, kw=dict(pp=2, layers=5, extra_tc=dict(account_for_embedding_in_pipeline_split=True))),
+    "pp2_interleaved_uneven": dict(world=2, kw=dict(pp=2, vpp=2, layers=5, schedule="interleaved",
+                                                    extra_tc=dict(decoder_first_pipeline_num_layers=2))),
     "pp2_zerobubble": dict(world=2, kw=dict(pp=2, schedule="zerobubble")),
     "pp2_zbv": dict(world=2, kw=dict(pp=2, schedule="zbv")),
     "pp2_zerobubble_manual_costs": dict(world=2, kw=dict(pp=2, schedule="zerobubble", extra_tc=dict(

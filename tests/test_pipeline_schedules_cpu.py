@@ -155,3 +155,22 @@ def test_seq1f1b_schedule_orders_chunks_and_shrinks_the_bubble():
     with pytest.raises(AssertionError):        # backward passes of a micro-batch's chunks in ascending order: invalid
         bad = [[ps.Node("F", 0, 0, 0), ps.Node("F", 0, 0, 1), ps.Node("BW", 0, 0, 0), ps.Node("BW", 0, 0, 1)]]
         ps.validate(bad, 1, 1, 1, "interleaved", 2)
+
+
+def test_uneven_split_counts():
+    import pytest
+
+    from primus_b200.parallel.pipeline_layout import layers_for_stage, uneven_split
+
+    assert uneven_split(78, 8) is None
+    assert uneven_split(78, 8, last=8) == [10] * 7 + [8]                     # a 78-layer stack on 8 stages
+    assert uneven_split(61, 8, first=4, last=3) == [4] + [9] * 6 + [3]
+    assert uneven_split(30, 4, account_for_embedding=True, account_for_loss=True) == [7, 8, 8, 7]
+    assert uneven_split(7, 1, last=3) == [7]
+    with pytest.raises(AssertionError):
+        uneven_split(78, 8, last=7)                                         # 71 layers over 7 stages
+    with pytest.raises(AssertionError):
+        uneven_split(8, 2, first=4, account_for_loss=True)
+    counts = uneven_split(61, 8, first=4, last=3)
+    got = [layers_for_stage(61, 8, r, manual_split=counts) for r in range(8)]
+    assert [len(g) for g in got] == counts and sum(got, []) == list(range(61))

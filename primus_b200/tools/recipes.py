@@ -95,18 +95,21 @@ def render(model: str, precision: str, cand: Candidate, world: int, hw: Hardware
         ("use_distributed_optimizer", "true"), ("overlap_grad_reduce", "true"), ("overlap_param_gather", "true"),
         ("seq_length", p.seq), ("micro_batch_size", p.micro_batch), ("global_batch_size", p.global_batch),
     ]
+    # every parallel size is written, also when it is 1: a model preset may carry a default of its own
+    ov += [("tensor_model_parallel_size", p.tp), ("sequence_parallel", "true" if p.tp > 1 else "false")]
     if p.tp > 1:
-        ov += [("tensor_model_parallel_size", p.tp), ("sequence_parallel", "true"), ("tp_comm_overlap", "true")]
+        ov.append(("tp_comm_overlap", "true"))
+    ov.append(("pipeline_model_parallel_size", p.pp))
     if p.pp > 1:
-        ov += [("pipeline_model_parallel_size", p.pp), ("pipeline_schedule", cand.schedule)]
+        ov.append(("pipeline_schedule", cand.schedule))
         if p.vpp > 1:
             ov.append(("virtual_pipeline_model_parallel_size", p.vpp))
         if cand.last_stage_layers:
             ov.append(("decoder_last_pipeline_num_layers", cand.last_stage_layers))
+    ov.append(("context_parallel_size", p.cp))
     if p.cp > 1:
-        ov += [("context_parallel_size", p.cp), ("cp_comm_type", "p2p")]
-    if p.ep > 1:
-        ov.append(("expert_model_parallel_size", p.ep))
+        ov.append(("cp_comm_type", "p2p"))
+    ov.append(("expert_model_parallel_size", p.ep))
     if p.recompute_layers:
         ov += [("recompute_granularity", "full"), ("recompute_method", "block"), ("recompute_num_layers", p.recompute_layers)]
     if precision == "mxfp8":
